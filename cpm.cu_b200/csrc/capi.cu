@@ -1,0 +1,406 @@
+// extern "C" surface of libcpmcu_b200.so (declared in include/cpmcu_b200.h).
+// Holds the single global model the reference keeps in src/entry.cu:98 and
+// turns C++ exceptions into return codes + a thread-local message.
+#include <cstdio>
+#include <memory>
+#include <vector>
+
+#include "../../include/cpmcu_b200.h"
+#include "engine.cuh"
+
+namespace {
+
+thread_local std::string g_error;
+std::unique_ptr<Engine> g_engine;
+
+template <typename F>
+int guarded(F&& f) {
+    try {
+        g_error.clear();
+        return f();
+    } catch (const std::exception& e) {
+        g_error = e.what();
+        return -1;
+    } catch (...) {
+        g_error = "unknown error";
+        return -1;
+    }
+}
+
+Engine& engine() {
+    if (!g_engine) throw std::runtime_error("cpmcu_b200: no model initialised");
+    return *g_engine;
+}
+
+void require_bf16(int torch_dtype) {
+    if (torch_dtype != 1) throw std::invalid_argument("cpmcu_b200: only torch_dtype 1 (bfloat16) is supported");
+}
+
+int not_built(const char* what) {
+    g_error = std::string("cpmcu_b200: ") + what + " is not built in this library";
+    return -1;
+}
+
+struct DeviceBuf {
+    void* p = nullptr;
+    explicit DeviceBuf(size_t bytes) { CUDA_CHECK(cudaMalloc(&p, bytes ? bytes : 1)); }
+    ~DeviceBuf() { cudaFree(p); }
+    DeviceBuf(const DeviceBuf&) = delete;
+    DeviceBuf& operator=(const DeviceBuf&) = delete;
+};
+
+void sync_and_check(const char* where) {
+    const int e = read_and_clear_error();
+    if (e != 0) throw std::runtime_error(std::string("cpmcu_b200: kernel error flags ") + std::to_string(e) + " in " + where);
+}
+
+}  // namespace
+
+extern "C" {
+
+const char* cpmcu_last_error(void) { return g_error.c_str(); }
+
+int cpmcu_init_base_model(float memory_limit, int vocab_size, int num_hidden_layers, int hidden_size,
+                          int intermediate_size, int num_attention_heads, int num_key_value_heads, int head_dim,
+                          float rms_norm_eps, int torch_dtype, int chunk_length, float scale_embed,
+                          float scale_lmhead, float scale_residual) {
+    return guarded([&] {
+        require_bf16(torch_dtype);
+        ModelConfig mc;
+        mc.memory_limit = memory_limit;
+        mc.vocab = vocab_size;
+        mc.layers = num_hidden_layers;
+        mc.hidden = hidden_size;
+        mc.inter = intermediate_size;
+        mc.hq = num_attention_heads;
+        mc.hkv = num_key_value_heads;
+        mc.head_dim = head_dim;
+        mc.eps = rms_norm_eps;
+        mc.chunk_length = chunk_length;
+        mc.scale_embed = scale_embed;
+        mc.scale_lmhead = scale_lmhead;
+        mc.scale_residual = scale_residual;
+        g_engine.reset();  // one model per process, like the reference's global
+        g_engine = std::make_unique<Engine>(mc);
+        return 0;
+    });
+}
+
+int cpmcu_init_minicpm4_model(float memory_limit, int vocab_size, int num_hidden_layers, int hidden_size,
+                              int intermediate_size, int num_attention_heads, int num_key_value_heads,
+                              int head_dim, float rms_norm_eps, int torch_dtype, int chunk_length,
+                              float scale_embed, float scale_lmhead, float scale_residual, int sink_window_size,
+                              int block_window_size, int sparse_topk_k, int sparse_switch, int apply_compress_lse) {
+    (void)sink_window_size; (void)block_window_size; (void)sparse_topk_k; (void)apply_compress_lse;
+    if (sparse_switch < (1 << 30)) return not_built("InfLLM-v2 block-sparse attention (init_minicpm4_model with a reachable sparse_switch)");
+    return cpmcu_init_base_model(memory_limit, vocab_size, num_hidden_layers, hidden_size, intermediate_size,
+                                 num_attention_heads, num_key_value_heads, head_dim, rms_norm_eps, torch_dtype,
+                                 chunk_length, scale_embed, scale_lmhead, scale_residual);
+}
+
+int cpmcu_init_w4a16_gptq_marlin_base_model(float, int, int, int, int, int, int, int, float, int, int, int, float, float,
+                                            float) {
+    return not_built("the W4A16 GPTQ-Marlin target");
+}
+int cpmcu_init_w4a16_gptq_marlin_minicpm4_model(float, int, int, int, int, int, int, int, float, int, int, int, float,
+                                                float, float, int, int, int, int, int) {
+    return not_built("the W4A16 GPTQ-Marlin sparse target");
+}
+
+int cpmcu_init_eagle_model(int num_layers, int num_iter, int topk_per_iter, int tree_size, int torch_dtype) {
+    return guarded([&] {
+        require_bf16(torch_dtype);
+        EagleConfig ec;
+        ec.num_layers = num_layers;
+        ec.num_iter = num_iter;
+        ec.topk = topk_per_iter;
+        ec.tree_size = tree_size;
+        ec.minicpm4_variant = false;
+        engine().attach_eagle(ec);
+        return 0;
+    });
+}
+
+int cpmcu_init_minicpm4_eagle_model(int num_layers, int num_iter, int topk_per_iter, int tree_size, int torch_dtype,
+                                    int apply_eagle_quant, int group_size, int eagle_window_size,
+                                    int frspec_vocab_size, float residual_scale, int use_input_norm,
+                                    int use_attn_norm) {
+    (void)group_size;
+    if (apply_eagle_quant) return not_built("the W4A16 EAGLE drafter (apply_eagle_quant)");
+    return guarded([&] {
+        require_bf16(torch_dtype);
+        EagleConfig ec;
+        ec.num_layers = num_layers;
+        ec.num_iter = num_iter;
+        ec.topk = topk_per_iter;
+        ec.tree_size = tree_size;
+        ec.window = eagle_window_size;
+        ec.frspec_vocab = frspec_vocab_size;
+        ec.residual_scale = residual_scale;
+        ec.use_input_norm = use_input_norm != 0;
+        ec.use_attn_norm = use_attn_norm != 0;
+        ec.minicpm4_variant = true;
+        engine().attach_eagle(ec);
+        return 0;
+    });
+}
+
+int cpmcu_init_w4a16_gm_spec_w4a16_gm_model(void) { return not_built("sequence speculative decoding with a quantised draft LLM"); }
+int cpmcu_init_hier_eagle_w4a16_gm_spec_w4a16_gm_model(void) { return not_built("hierarchical speculative decoding"); }
+int cpmcu_init_hier_eagle_w4a16_gm_rot_spec_w4a16_gm_model(void) { return not_built("hierarchical speculative decoding"); }
+
+int cpmcu_init_storage(void) {
+    return guarded([&] { return engine().init_storage(); });
+}
+
+int cpmcu_load_model(const char* name, const void* param) {
+    return guarded([&] {
+        engine().load(name, param);
+        return 0;
+    });
+}
+
+int cpmcu_prefill(int input_length, int history_length, const int32_t* input, const int32_t* position_ids,
+                  void* output) {
+    return guarded([&] {
+        engine().prefill(input_length, history_length, input, position_ids, static_cast<bf16*>(output));
+        return 0;
+    });
+}
+
+int cpmcu_decode(int input_length, int padded_length, const int32_t* input, const int32_t* position_ids,
+                 const int32_t* cache_length, const uint64_t* mask_2d, void* output, int cuda_graph) {
+    return guarded([&] {
+        engine().decode(input_length, padded_length, input, position_ids, cache_length, mask_2d,
+                        static_cast<bf16*>(output), cuda_graph != 0);
+        return 0;
+    });
+}
+
+int cpmcu_draft(int32_t* tree_draft_ids, int32_t* tree_position_ids, const int32_t* cache_length,
+                uint64_t* attn_mask, int32_t* tree_parent) {
+    return guarded([&] {
+        engine().draft(tree_draft_ids, tree_position_ids, cache_length, attn_mask, tree_parent);
+        return 0;
+    });
+}
+
+int cpmcu_verify_and_fix(int num_tokens, int32_t* pred, const int32_t* gt, const int32_t* position_ids,
+                         const int32_t* cache_length, const uint64_t* attn_mask, const int32_t* tree_parent) {
+    return guarded([&] {
+        return engine().verify_and_fix(num_tokens, pred, gt, position_ids, cache_length, attn_mask, tree_parent);
+    });
+}
+
+void cpmcu_print_perf_summary(void) {
+    try {
+        printf("cpmcu_b200: %ld kernels launched so far", runtime().launches);
+        if (g_engine && g_engine->launches_per_step() > 0) {
+            printf(", %ld kernels per captured speculative step, last step %.3f ms", g_engine->launches_per_step(),
+                   g_engine->last_step_device_ms());
+        }
+        printf("\n");
+    } catch (...) {
+    }
+}
+
+int cpmcu_begin_generation(int prefix_length, int32_t root_token) {
+    return guarded([&] {
+        engine().begin_generation(prefix_length, root_token);
+        return 0;
+    });
+}
+
+int cpmcu_spec_step(int32_t* out_tokens, int max_tokens) {
+    return guarded([&] { return engine().spec_step(out_tokens, max_tokens); });
+}
+
+double cpmcu_last_step_ms(void) { return g_engine ? g_engine->last_step_device_ms() : 0.0; }
+long cpmcu_launches_per_step(void) { return g_engine ? g_engine->launches_per_step() : 0; }
+long cpmcu_total_launches(void) {
+    try {
+        return runtime().launches;
+    } catch (...) {
+        return 0;
+    }
+}
+
+int cpmcu_get_tree(int32_t* ids, int32_t* pos, int32_t* parent, int32_t* gt, uint64_t* mask, int32_t* state) {
+    return guarded([&] {
+        Engine& e = engine();
+        cudaStream_t s = runtime().stream;
+        void* dst[6] = {ids, pos, parent, gt, mask, state};
+        const size_t bytes[6] = {256, 256, 256, 256, 512, 64};
+        for (int i = 0; i < 6; ++i) {
+            if (dst[i]) CUDA_CHECK(cudaMemcpyAsync(dst[i], e.tree_buffers(i), bytes[i], cudaMemcpyDeviceToHost, s));
+        }
+        CUDA_CHECK(cudaStreamSynchronize(s));
+        return 0;
+    });
+}
+
+void cpmcu_release(void) { g_engine.reset(); }
+
+// ------------------------------------------------------------------ kernel-level entry points
+int cpmcu_linear_bf16(const void* x, const void* w, const void* bias, void* y, int M, int N, int K, int grid_limit) {
+    return guarded([&] {
+        Runtime& rt = runtime();
+        const int limit = (grid_limit > 0) ? grid_limit : rt.num_sms;
+        const int mt = linear_pick_mt(M);
+        DeviceBuf ws(linear_workspace_bytes(mt, limit));
+        const size_t tiles = static_cast<size_t>(ceil_div(N, 128)) * ceil_div(M, mt);
+        DeviceBuf tickets(tiles * sizeof(int));
+        CUDA_CHECK(cudaMemsetAsync(tickets.p, 0, tiles * sizeof(int), rt.stream));
+        LinearPlan p = make_linear_plan(static_cast<const bf16*>(x), M, static_cast<const bf16*>(w), M, N, K,
+                                        static_cast<bf16*>(y), N, static_cast<const bf16*>(bias),
+                                        static_cast<float*>(ws.p), static_cast<int*>(tickets.p), limit);
+        launch_linear(p, rt.stream);
+        sync_and_check("linear");
+        return 0;
+    });
+}
+
+int cpmcu_tree_attention(const void* q, int q_ld, const void* k_cache, const void* v_cache, int budget, int tq,
+                         int hq, int hkv, const int32_t* kv_len, int kv_len_add, const int32_t* n_valid,
+                         const uint64_t* mask, int mask_k, int window, int splits, void* out, int out_ld) {
+    return guarded([&] {
+        Runtime& rt = runtime();
+        CPM_REQUIRE(splits >= 1 && splits <= 64, "attention: splits must be in [1,64]");
+        const size_t rows = static_cast<size_t>(tq) * hq;
+        DeviceBuf ws_o(splits > 1 ? rows * splits * 128 * sizeof(float) : 0);
+        DeviceBuf ws_ml(splits > 1 ? rows * splits * 2 * sizeof(float) : 0);
+        AttnPlan p = make_attn_plan(static_cast<const bf16*>(q), q_ld, static_cast<const bf16*>(k_cache),
+                                    static_cast<const bf16*>(v_cache), budget, tq, hq, hkv, 128, splits,
+                                    static_cast<bf16*>(out), out_ld, static_cast<float*>(ws_o.p),
+                                    static_cast<float*>(ws_ml.p));
+        p.kv_len = kv_len;
+        p.kv_len_add = kv_len_add;
+        p.n_valid = n_valid;
+        p.mask = mask;
+        p.mask_k = mask ? mask_k : 0;
+        p.window = window;
+        launch_tree_attention(p, rt.stream);
+        sync_and_check("tree_attention");
+        return 0;
+    });
+}
+
+int cpmcu_rms_norm(void* x, const void* delta, float delta_scale, const void* weight, void* y, int rows, int dim,
+                   float eps) {
+    return guarded([&] {
+        cudaStream_t s = runtime().stream;
+        if (delta) launch_add_rms_norm(static_cast<bf16*>(x), static_cast<const bf16*>(delta), delta_scale,
+                                       static_cast<const bf16*>(weight), static_cast<bf16*>(y), rows, dim, eps, s);
+        else launch_rms_norm(static_cast<const bf16*>(x), dim, static_cast<const bf16*>(weight), static_cast<bf16*>(y), dim,
+                             rows, dim, eps, s);
+        sync_and_check("rms_norm");
+        return 0;
+    });
+}
+
+int cpmcu_rope_append(void* qkv, int rows, int hq, int hkv, const float* inv_freq, const int32_t* pos, void* k_cache,
+                      void* v_cache, const int32_t* kv_len, int kv_off) {
+    return guarded([&] {
+        launch_rope_append(static_cast<bf16*>(qkv), rows, hq, hkv, 128, inv_freq, pos, nullptr, 0, 0,
+                           static_cast<bf16*>(k_cache), static_cast<bf16*>(v_cache), kv_len, kv_off, nullptr,
+                           runtime().stream);
+        sync_and_check("rope_append");
+        return 0;
+    });
+}
+
+int cpmcu_silu_gate(const void* gate_up, void* out, int rows, int inter) {
+    return guarded([&] {
+        launch_silu_gate(static_cast<const bf16*>(gate_up), static_cast<bf16*>(out), rows, inter, runtime().stream);
+        sync_and_check("silu_gate");
+        return 0;
+    });
+}
+
+int cpmcu_argmax(const void* logits, int rows, int vocab, int32_t* out) {
+    return guarded([&] {
+        launch_argmax(static_cast<const bf16*>(logits), rows, vocab, vocab, out, runtime().stream);
+        sync_and_check("argmax");
+        return 0;
+    });
+}
+
+int cpmcu_draft_tree_from_logits(const void* logits, int vocab, int k, int num_iter, int tree_size,
+                                 const int32_t* token_id_remap, const int32_t* cache_length, int32_t* tree_ids,
+                                 int32_t* tree_pos, uint64_t* tree_mask, int32_t* tree_parent, void* tried_val,
+                                 int32_t* tried_pos, int32_t* tried_parent) {
+    return guarded([&] {
+        Runtime& rt = runtime();
+        cudaStream_t s = rt.stream;
+        CPM_REQUIRE(k >= 1 && k <= 32 && num_iter >= 1 && k * num_iter <= 64, "draft tree: k / num_iter out of range");
+        CPM_REQUIRE(tree_size >= 2 && tree_size <= 64, "draft tree: tree_size out of range");
+        DraftTreeState st;
+        st.k = k;
+        st.num_iter = num_iter;
+        st.tree_size = tree_size;
+        st.total_tried = k + k * k * (num_iter - 1);
+        CPM_REQUIRE(tree_size - 1 <= st.total_tried, "draft tree: tree larger than the candidate set");
+        const int hidden = 8;  // dummy hidden rows: the hidden-state gather is exercised but unused
+        DeviceBuf tv((st.total_tried + 64) * 2), tp((st.total_tried + 64) * 4), tpar((k * num_iter + 64) * 4);
+        DeviceBuf fs(64 * 2), fi(64 * 4), fm(64 * 8), sp(64 * 4);
+        DeviceBuf h(static_cast<size_t>(32) * hidden * 2), hid(static_cast<size_t>(32) * hidden * 2);
+        DeviceBuf scan(draft_scan_workspace_bytes(32, vocab, 32));
+        CUDA_CHECK(cudaMemsetAsync(h.p, 0, static_cast<size_t>(32) * hidden * 2, s));
+        st.tried_val = static_cast<bf16*>(tv.p);
+        st.tried_pos = static_cast<int32_t*>(tp.p);
+        st.tried_parent = static_cast<int32_t*>(tpar.p);
+        st.fr_score = static_cast<bf16*>(fs.p);
+        st.fr_id = static_cast<int32_t*>(fi.p);
+        st.fr_mask = static_cast<uint64_t*>(fm.p);
+        st.sel_pos = static_cast<int32_t*>(sp.p);
+        st.token_id_remap = token_id_remap;
+        const bf16* lg = static_cast<const bf16*>(logits);
+        for (int d = 0; d < num_iter; ++d) {
+            const bf16* rows = (d == 0) ? lg : lg + static_cast<size_t>(1 + (d - 1) * k) * vocab;
+            launch_draft_topk_expand(st, rows, vocab, vocab, d, scan.p, static_cast<bf16*>(h.p), hidden, nullptr,
+                                     static_cast<bf16*>(hid.p), hidden, hidden, s);
+        }
+        launch_tree_finalize(st, cache_length, tree_ids, tree_pos, tree_mask, tree_parent, s);
+        if (tried_val) CUDA_CHECK(cudaMemcpyAsync(tried_val, st.tried_val, st.total_tried * 2, cudaMemcpyDeviceToDevice, s));
+        if (tried_pos) CUDA_CHECK(cudaMemcpyAsync(tried_pos, st.tried_pos, st.total_tried * 4, cudaMemcpyDeviceToDevice, s));
+        if (tried_parent && num_iter > 1) {
+            CUDA_CHECK(cudaMemcpyAsync(tried_parent, st.tried_parent, static_cast<size_t>(k) * (num_iter - 1) * 4,
+                                       cudaMemcpyDeviceToDevice, s));
+        }
+        sync_and_check("draft_tree_from_logits");
+        return 0;
+    });
+}
+
+int cpmcu_verify_and_compact(int tree_size, int32_t* pred, const int32_t* gt, const int32_t* position_ids,
+                             const int32_t* cache_length, const uint64_t* attn_mask, const int32_t* tree_parent,
+                             void* const* caches, int num_caches, int kv_dim, int max_accept, int32_t* result) {
+    return guarded([&] {
+        cudaStream_t s = runtime().stream;
+        AcceptIO io;
+        io.tree_size = tree_size;
+        io.pred = pred;
+        io.gt = gt;
+        io.position_ids = position_ids;
+        io.cache_length = cache_length;
+        io.attn_mask = attn_mask;
+        io.tree_parent = tree_parent;
+        io.result = result;
+        launch_verify_accept(io, s);
+        if (num_caches > 0) {
+            FixupArgs f;
+            f.result = result;
+            f.cache_length = cache_length;
+            f.caches = reinterpret_cast<bf16* const*>(caches);
+            f.num_caches = num_caches;
+            f.kv_dim = kv_dim;
+            f.max_accept = max_accept;
+            f.hidden = 0;
+            launch_accept_fixup(f, s);
+        }
+        sync_and_check("verify_and_compact");
+        return 0;
+    });
+}
+
+}  // extern "C"

@@ -1,0 +1,129 @@
+// Shared declarations for the speculative-decoding kernels: error handling,
+// the per-process runtime (stream, device error word, TMA encoder), and the
+// launch prototypes each .cu file exports to the engine and to the C ABI.
+#pragma once
+#include <cuda_runtime.h>
+#include <cuda_bf16.h>
+#include <cuda.h>
+#include <stdint.h>
+#include <stdexcept>
+#include <string>
+
+typedef __nv_bfloat16 bf16;
+
+#define CUDA_CHECK(expr)                                                                            \
+    do {                                                                                            \
+        cudaError_t err__ = (expr);                                                                 \
+        if (err__ != cudaSuccess) {                                                                 \
+            throw std::runtime_error(std::string("CUDA error: ") + cudaGetErrorString(err__) + " at " + \
+                                     __FILE__ + ":" + std::to_string(__LINE__) + " (" #expr ")");   \
+        }                                                                                           \
+    } while (0)
+
+#define CPM_REQUIRE(cond, msg)                                                        \
+    do {                                                                              \
+        if (!(cond)) throw std::invalid_argument(std::string("cpmcu_b200: ") + (msg)); \
+    } while (0)
+
+static inline int ceil_div(int a, int b) { return (a + b - 1) / b; }
+static inline int64_t align_up(int64_t x, int64_t a) { return (x + a - 1) / a * a; }
+
+// ---------------------------------------------------------------- runtime
+// Error word bits written by kernels (device memory, read by the host).
+enum KernelError : int {
+    ERR_NONE = 0,
+    ERR_GEMM_TIMEOUT = 1,
+    ERR_ATTN_TIMEOUT = 2,
+    ERR_BAD_TREE = 4,
+};
+
+struct Runtime {
+    cudaStream_t stream = nullptr;
+    int* d_error = nullptr;  // device error word, or-ed into by kernels
+    int num_sms = 148;
+    int device = 0;
+    long launches = 0;  // kernels launched (or captured) so far by this library
+};
+Runtime& runtime();          // lazily initialised, one per process
+int read_and_clear_error();  // synchronises the stream
+
+// 2-D / 3-D bf16 tensor maps with 128-byte swizzle; inner box extent is 64
+// elements (128 B).  Strides are in bytes and must be multiples of 16.
+CUtensorMap make_tmap_2d(const void* base, uint64_t inner, uint64_t outer, uint64_t outer_stride_bytes,
+                         uint32_t box_inner, uint32_t box_outer);
+CUtensorMap make_tmap_3d(const void* base, uint64_t d0, uint64_t d1, uint64_t d2, uint64_t stride1_bytes,
+                         uint64_t stride2_bytes, uint32_t b0, uint32_t b1, uint32_t b2);
+
+// ---------------------------------------------------------------- GEMM
+// Y[M,N] = X[M,K] * W[N,K]^T (+ bias[N]); bf16 in, fp32 accumulate in TMEM.
+struct LinearPlan {
+    CUtensorMap tm_w;   // W  [N,K], box 64 x 128
+    CUtensorMap tm_x;   // X  [Mrows,K], box 64 x MT
+    int M = 0, N = 0, K = 0;
+    int mt = 0;         // token tile: 16, 32, 64, 128 or 256
+    int grid = 0;
+    bf16* y = nullptr;
+    int ldy = 0;
+    const bf16* bias = nullptr;
+    float* workspace = nullptr;  // split-K partials: grid * 2 * mt * 128 floats
+    int* tickets = nullptr;      // one counter per output tile, zero between launches
+    // Optional fused epilogue: y = silu(gate) * up where gate/up rows alternate
+    // in 64-row halves of each 128-row weight tile (see make_linear_plan).
+    int epilogue = 0;
+    // Optional row-wise argmax partials (LM head): per (n_tile, m) best value/index.
+    float* amax_val = nullptr;
+    int* amax_idx = nullptr;
+};
+enum LinearEpilogue { EPI_STORE = 0, EPI_SILU_GATE = 1 };
+
+size_t linear_workspace_bytes(int mt, int grid);
+int linear_pick_mt(int M);
+LinearPlan make_linear_plan(const bf16* x, int x_rows, const bf16* w, int M, int N, int K, bf16* y, int ldy,
+                            const bf16* bias, float* workspace, int* tickets, int grid_limit);
+void launch_linear(const LinearPlan& plan, cudaStream_t stream);
+
+// ---------------------------------------------------------------- small ops
+void launch_rms_norm(const bf16* x, int ldx, const bf16* w, bf16* y, int ldy, int rows, int dim, float eps,
+                     cudaStream_t s);
+// x += delta * scale (in bf16, in place), then y = rmsnorm(x) * w
+void launch_add_rms_norm(bf16* x, const bf16* delta, float delta_scale, const bf16* w, bf16* y, int rows, int dim,
+                         float eps, cudaStream_t s);
+void launch_embedding(const int32_t* ids, const bf16* table, bf16* out, int ld_out, int rows, int dim, float scale,
+                      cudaStream_t s);
+// qkv: [rows, (hq + 2 hkv) * d].  Applies NeoX RoPE to q (in place) and k, then
+// writes k,v into the cache at row (*kv_len + kv_off + r) for r < *n_valid
+// (n_valid may be null = rows).  Position of row r: pos[r], or when pos is
+// null *pos_base + pos_off + r * pos_step.
+void launch_rope_append(bf16* qkv, int rows, int hq, int hkv, int d, const float* inv_freq, const int32_t* pos,
+                        const int32_t* pos_base, int pos_off, int pos_step, bf16* k_cache, bf16* v_cache,
+                        const int32_t* kv_len, int kv_off, const int32_t* n_valid, cudaStream_t s);
+void launch_silu_gate(const bf16* gate_up, bf16* out, int rows, int inter, cudaStream_t s);
+void launch_add_scaled(bf16* x, const bf16* a, const bf16* b, float scale_b, int rows, int dim,
+                       cudaStream_t s);  // x = a + b*scale
+void launch_scale(bf16* out, const bf16* in, float scale, size_t n, cudaStream_t s);
+void launch_argmax(const bf16* logits, int rows, int vocab, int ld, int32_t* out, cudaStream_t s);
+
+// ---------------------------------------------------------------- attention
+struct AttnPlan {
+    CUtensorMap tm_q;  // [tq, hq, d] viewed as 3-D (d, heads, tokens)
+    CUtensorMap tm_k;  // [budget, hkv*d]
+    CUtensorMap tm_v;
+    int tq = 0, hq = 0, hkv = 0, d = 128;
+    int splits = 1;
+    const int32_t* kv_len = nullptr;  // device scalar
+    int kv_len_add = 0;               // keys visible = *kv_len + kv_len_add
+    const int32_t* n_valid = nullptr; // device scalar: valid query rows (null = tq)
+    const uint64_t* mask = nullptr;   // per-token tree mask over the last mask_k keys
+    int mask_k = 0;
+    int window = 0;                   // >0: block-granular sliding window (tokens)
+    float scale = 0.f;
+    bf16* out = nullptr;              // token t, head h at out + t*out_ld + h*d
+    int out_ld = 0;
+    float* ws_o = nullptr;            // [splits, tq*hq, d]
+    float* ws_ml = nullptr;           // [splits, tq*hq, 2]
+};
+size_t attn_workspace_bytes(int tq, int hq, int d, int splits);
+AttnPlan make_attn_plan(const bf16* q, int q_ld_tokens, const bf16* k_cache, const bf16* v_cache, int budget,
+                        int tq, int hq, int hkv, int d, int splits, bf16* out, int out_ld, float* ws_o,
+                        float* ws_ml);
+void launch_tree_attention(const AttnPlan& plan, cudaStream_t s);

@@ -1,0 +1,378 @@
+// EAGLE draft-tree kernels: log-softmax + per-row top-k over the draft
+// vocabulary, frontier expansion with cumulative log-probabilities, final
+// selection of the tree nodes and construction of positions / parents / packed
+// ancestor masks.
+//
+// Replaces, with identical integer results given identical bf16 inputs:
+//   log_softmax_kernel                      src/model/eagle.cuh:29-89
+//   bitonic top-k (value desc, index asc)   src/model/topk.cuh:7-42,159-213,273-286
+//   add/repeat/init_tree/set_parent/update_tree/cumsum/remap_* kernels
+//                                           src/model/eagle.cuh:11-127
+//   build_dynamic_tree_kernel               src/model/eagle.cuh:188-218
+// The reference runs ~12 tiny launches and three device copies per level plus a
+// host round trip for the tree; here a level is three launches and the tree one.
+#include "common.cuh"
+#include "draft_tree.cuh"
+
+namespace {
+
+constexpr int SEG = 2048;          // vocabulary entries per CTA in the scan kernels
+constexpr int SCAN_THREADS = 256;  // SEG / 8 entries per thread
+
+// Order-preserving key: larger key == earlier in (value desc, index asc) order.
+__device__ __forceinline__ uint32_t bf16_orderable(bf16 v) {
+    const uint16_t b = __bfloat16_as_ushort(v);
+    if ((b & 0x7F80) == 0x7F80 && (b & 0x007F) != 0) return 0;  // NaN sorts last
+    return (b & 0x8000) ? static_cast<uint16_t>(~b) : static_cast<uint16_t>(b | 0x8000);
+}
+__device__ __forceinline__ unsigned long long make_key(bf16 v, int idx) {
+    return (static_cast<unsigned long long>(bf16_orderable(v)) << 32) |
+           static_cast<unsigned long long>(0xFFFFFFFFu - static_cast<uint32_t>(idx));
+}
+__device__ __forceinline__ int key_index(unsigned long long k) {
+    return static_cast<int>(0xFFFFFFFFu - static_cast<uint32_t>(k & 0xFFFFFFFFull));
+}
+
+__device__ __forceinline__ unsigned long long warp_max_u64(unsigned long long v) {
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) {
+        const unsigned long long other = __shfl_xor_sync(0xffffffffu, v, o);
+        v = (other > v) ? other : v;
+    }
+    return v;
+}
+
+// ---- pass 1: per (row, segment) running max and sum of exp over bf16 logits
+__global__ void lsm_stats_kernel(const bf16* __restrict__ logits, int ld, int vocab, float2* __restrict__ stats,
+                                 int nseg, const int32_t* __restrict__ row0) {
+    __shared__ float sh_m[SCAN_THREADS / 32];
+    __shared__ float sh_s[SCAN_THREADS / 32];
+    const int row = blockIdx.y, seg = blockIdx.x;
+    const bf16* x = logits + static_cast<size_t>(row + (row0 ? *row0 : 0)) * ld;
+    const int begin = seg * SEG;
+    const int end = min(begin + SEG, vocab);
+    float v[SEG / SCAN_THREADS];
+    float m = -INFINITY;
+#pragma unroll
+    for (int j = 0; j < SEG / SCAN_THREADS; ++j) {
+        const int i = begin + j * SCAN_THREADS + threadIdx.x;
+        v[j] = (i < end) ? __bfloat162float(x[i]) : -INFINITY;
+        m = fmaxf(m, v[j]);
+    }
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) m = fmaxf(m, __shfl_xor_sync(0xffffffffu, m, o));
+    if ((threadIdx.x & 31) == 0) sh_m[threadIdx.x >> 5] = m;
+    __syncthreads();
+    m = sh_m[0];
+#pragma unroll
+    for (int w = 1; w < SCAN_THREADS / 32; ++w) m = fmaxf(m, sh_m[w]);
+    float s = 0.f;
+    if (m > -INFINITY) {
+#pragma unroll
+        for (int j = 0; j < SEG / SCAN_THREADS; ++j) s += expf(v[j] - m);  // exp(-inf) = 0 for padding
+    }
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) s += __shfl_xor_sync(0xffffffffu, s, o);
+    if ((threadIdx.x & 31) == 0) sh_s[threadIdx.x >> 5] = s;
+    __syncthreads();
+    if (threadIdx.x == 0) {
+        float t = 0.f;
+#pragma unroll
+        for (int w = 0; w < SCAN_THREADS / 32; ++w) t += sh_s[w];
+        stats[static_cast<size_t>(row) * nseg + seg] = make_float2(m, t);
+    }
+}
+
+// Row-wide log-sum-exp offset from the segment partials (fixed order => deterministic).
+__device__ __forceinline__ void row_offset(const float2* __restrict__ st, int nseg, float& mx, float& logsum) {
+    float m = -INFINITY;
+    for (int s = 0; s < nseg; ++s) m = fmaxf(m, st[s].x);
+    float sum = 0.f;
+    for (int s = 0; s < nseg; ++s) sum += st[s].y * expf(st[s].x - m);
+    mx = m;
+    logsum = logf(sum);
+}
+
+// ---- pass 2: lp = bf16(x - max - log(sum)); segment-local top-k by (lp desc, index asc)
+__global__ void lsm_local_topk_kernel(const bf16* __restrict__ logits, int ld, int vocab,
+                                      const float2* __restrict__ stats, int nseg, int k,
+                                      unsigned long long* __restrict__ cand, const int32_t* __restrict__ row0) {
+    __shared__ unsigned long long sh_best[SCAN_THREADS / 32];
+    __shared__ float sh_off[2];
+    const int row = blockIdx.y, seg = blockIdx.x;
+    if (threadIdx.x == 0) {
+        float mx, ls;
+        row_offset(stats + static_cast<size_t>(row) * nseg, nseg, mx, ls);
+        sh_off[0] = mx;
+        sh_off[1] = ls;
+    }
+    __syncthreads();
+    const float mx = sh_off[0], ls = sh_off[1];
+    const bf16* x = logits + static_cast<size_t>(row + (row0 ? *row0 : 0)) * ld;
+    const int begin = seg * SEG;
+    const int end = min(begin + SEG, vocab);
+    unsigned long long keys[SEG / SCAN_THREADS];
+#pragma unroll
+    for (int j = 0; j < SEG / SCAN_THREADS; ++j) {
+        const int i = begin + j * SCAN_THREADS + threadIdx.x;
+        if (i < end) {
+            const bf16 lp = __float2bfloat16(__bfloat162float(x[i]) - mx - ls);
+            keys[j] = make_key(lp, i);
+        } else {
+            keys[j] = 0ull;
+        }
+    }
+    unsigned long long* out = cand + (static_cast<size_t>(row) * nseg + seg) * k;
+    for (int round = 0; round < k; ++round) {
+        unsigned long long best = 0ull;
+#pragma unroll
+        for (int j = 0; j < SEG / SCAN_THREADS; ++j) best = (keys[j] > best) ? keys[j] : best;
+        best = warp_max_u64(best);
+        if ((threadIdx.x & 31) == 0) sh_best[threadIdx.x >> 5] = best;
+        __syncthreads();
+        best = sh_best[0];
+#pragma unroll
+        for (int w = 1; w < SCAN_THREADS / 32; ++w) best = (sh_best[w] > best) ? sh_best[w] : best;
+        __syncthreads();
+        if (threadIdx.x == 0) out[round] = best;
+#pragma unroll
+        for (int j = 0; j < SEG / SCAN_THREADS; ++j) {
+            if (keys[j] == best) keys[j] = 0ull;  // keys are unique (index is part of the key)
+        }
+    }
+}
+
+// Select the `k` largest of `n` unique keys held in shared memory by one warp;
+// result r (0 = largest) is returned to lane r.
+__device__ unsigned long long warp_select(unsigned long long* keys, int n, int k, int lane) {
+    unsigned long long mine = 0ull;
+    for (int round = 0; round < k; ++round) {
+        unsigned long long best = 0ull;
+        for (int i = lane; i < n; i += 32) best = (keys[i] > best) ? keys[i] : best;
+        best = warp_max_u64(best);
+        if (lane == round) mine = best;
+        for (int i = lane; i < n; i += 32) {
+            if (keys[i] == best) keys[i] = 0ull;
+        }
+        __syncwarp();
+    }
+    return mine;
+}
+
+// ---- pass 3 + frontier expansion.  One CTA, one warp per frontier row.
+// level 0: rows = 1; seeds the frontier from the single row's top-k.
+// level d >= 1: rows = k; cumulative scores, history append, top-k of k*k,
+//               parent / mask / hidden / token bookkeeping for the next level.
+__global__ void draft_expand_kernel(DraftTreeState st, const unsigned long long* __restrict__ cand, int nseg,
+                                    const bf16* __restrict__ logits, int ld, const float2* __restrict__ stats,
+                                    int level, const bf16* __restrict__ h_rows, int h_ld,
+                                    const int32_t* __restrict__ last_row_ptr, bf16* __restrict__ hid_out,
+                                    int hid_ld, int hidden) {
+    extern __shared__ unsigned long long sh_keys[];  // rows * nseg * k candidate keys, then scratch
+    const int k = st.k;
+    const int rows = (level == 0) ? 1 : k;
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int per_row = nseg * k;
+    __shared__ bf16 s_val[32 * 32];
+    __shared__ int s_pos[32 * 32];
+    __shared__ unsigned long long s_ckey[32 * 32];
+    __shared__ int s_sel[32];
+    __shared__ uint64_t s_oldmask[32];
+
+    if (warp < rows) {
+        unsigned long long* mykeys = sh_keys + static_cast<size_t>(warp) * per_row;
+        for (int i = lane; i < per_row; i += 32) mykeys[i] = cand[static_cast<size_t>(warp) * per_row + i];
+        __syncwarp();
+        const unsigned long long got = warp_select(mykeys, per_row, k, lane);
+        if (lane < k) {
+            const int idx = key_index(got);
+            float mx, ls;
+            row_offset(stats + static_cast<size_t>(warp) * nseg, nseg, mx, ls);
+            const int lrow = warp + ((level == 0 && last_row_ptr) ? *last_row_ptr : 0);
+            const bf16 lp = __float2bfloat16(__bfloat162float(logits[static_cast<size_t>(lrow) * ld + idx]) - mx - ls);
+            s_val[warp * k + lane] = lp;
+            s_pos[warp * k + lane] = idx;
+        }
+    }
+    __syncthreads();
+
+    if (level == 0) {
+        if (threadIdx.x < k) {
+            const int i = threadIdx.x;
+            st.tried_val[i] = s_val[i];
+            st.tried_pos[i] = s_pos[i];
+            st.fr_score[i] = s_val[i];
+            st.fr_id[i] = st.token_id_remap ? st.token_id_remap[s_pos[i]] : s_pos[i];
+            st.fr_mask[i] = 1ull << i;
+        }
+        // frontier hidden state: the last valid row of the catch-up pass, repeated k times
+        const int src = last_row_ptr ? *last_row_ptr : 0;
+        const uint4* s4 = reinterpret_cast<const uint4*>(h_rows + static_cast<size_t>(src) * h_ld);
+        for (int i = threadIdx.x; i < k * (hidden / 8); i += blockDim.x) {
+            const int r = i / (hidden / 8), c = i - r * (hidden / 8);
+            reinterpret_cast<uint4*>(hid_out + static_cast<size_t>(r) * hid_ld)[c] = s4[c];
+        }
+        return;
+    }
+
+    // cumulative log-prob in bf16 (reference cumsum_kernel: value += frontier score, rounded to bf16)
+    const int kk = k * k;
+    const int base = k + (level - 1) * kk;
+    for (int i = threadIdx.x; i < kk; i += blockDim.x) {
+        const int r = i / k;
+        const bf16 v = __float2bfloat16(__bfloat162float(s_val[i]) + __bfloat162float(st.fr_score[r]));
+        s_val[i] = v;
+        st.tried_val[base + i] = v;
+        st.tried_pos[base + i] = s_pos[i];
+        s_ckey[i] = make_key(v, i);
+    }
+    if (threadIdx.x < k) s_oldmask[threadIdx.x] = st.fr_mask[threadIdx.x];
+    __syncthreads();
+    if (warp == 0) {
+        const unsigned long long got = warp_select(s_ckey, kk, k, lane);
+        if (lane < k) s_sel[lane] = key_index(got);
+    }
+    __syncthreads();
+    if (threadIdx.x < k) {
+        const int i = threadIdx.x;
+        const int sel = s_sel[i];
+        st.tried_parent[(level - 1) * k + i] = sel + base;
+        st.fr_mask[i] = s_oldmask[sel / k] | (1ull << (k * level + i));
+        st.fr_score[i] = s_val[sel];
+        st.fr_id[i] = st.token_id_remap ? st.token_id_remap[s_pos[sel]] : s_pos[sel];
+    }
+    for (int i = threadIdx.x; i < k * (hidden / 8); i += blockDim.x) {
+        const int r = i / (hidden / 8), c = i - r * (hidden / 8);
+        const int src = s_sel[r] / k;
+        reinterpret_cast<uint4*>(hid_out + static_cast<size_t>(r) * hid_ld)[c] =
+            reinterpret_cast<const uint4*>(h_rows + static_cast<size_t>(src) * h_ld)[c];
+    }
+}
+
+// ---- final selection of tree_size-1 candidates + tree arrays.  One CTA.
+__global__ void tree_finalize_kernel(DraftTreeState st, const int32_t* __restrict__ cache_length,
+                                     int32_t* __restrict__ tree_draft_ids, int32_t* __restrict__ tree_pos,
+                                     uint64_t* __restrict__ tree_mask, int32_t* __restrict__ tree_parent,
+                                     int* __restrict__ error) {
+    __shared__ unsigned long long s_key[2048];
+    __shared__ int s_sel[64];       // node i (1-based) <-> tried index s_sel[i-1]
+    __shared__ int s_rank[2048];    // tried index -> node id (0 if not selected)
+    __shared__ int s_par[64];
+    const int k = st.k, T = st.tree_size, TT = st.total_tried;
+    const int L = cache_length[0];
+    for (int i = threadIdx.x; i < TT; i += blockDim.x) {
+        s_key[i] = make_key(st.tried_val[i], i);
+        s_rank[i] = 0;
+    }
+    __syncthreads();
+    // rank by counting: position in (value desc, index asc) order
+    for (int i = threadIdx.x; i < TT; i += blockDim.x) {
+        const unsigned long long mine = s_key[i];
+        int r = 0;
+        for (int j = 0; j < TT; ++j) r += (s_key[j] > mine) ? 1 : 0;
+        if (r < T - 1) {
+            s_sel[r] = i;
+            s_rank[i] = r + 1;
+        }
+    }
+    __syncthreads();
+    const int kk = k * k;
+    if (threadIdx.x < T) {
+        const int i = threadIdx.x;
+        if (i == 0) {
+            tree_pos[0] = L;
+            s_par[0] = 0;
+        } else {
+            int p = s_sel[i - 1];
+            st.sel_pos[i - 1] = p;
+            const int depth = (p < k) ? 1 : (p - k) / kk + 2;
+            tree_pos[i] = L + depth;
+            int q;
+            if (p < k) {
+                q = -1;
+            } else if (p - k < kk) {
+                q = (p - k) / k;
+            } else {
+                q = st.tried_parent[(p - k - kk) / k];
+            }
+            int par = (q < 0) ? 0 : s_rank[q];
+            if (q >= 0 && par == 0) {  // parent not selected: scores were not monotone (NaN/Inf input)
+                atomicOr(error, ERR_BAD_TREE);
+            }
+            if (par >= i) {
+                atomicOr(error, ERR_BAD_TREE);
+                par = 0;
+            }
+            s_par[i] = par;
+            tree_parent[i] = par;
+            const int tok = st.tried_pos[p];
+            tree_draft_ids[i] = st.token_id_remap ? st.token_id_remap[tok] : tok;
+        }
+    }
+    __syncthreads();
+    if (threadIdx.x < T) {
+        const int i = threadIdx.x;
+        uint64_t m = (1ull << i) | 1ull;
+        int q = s_par[i];
+        int guard = 0;
+        while (q > 0 && guard++ < 64) {
+            m |= 1ull << q;
+            q = s_par[q];
+        }
+        tree_mask[i] = m;
+    }
+}
+
+}  // namespace
+
+int draft_num_segments(int vocab) { return ceil_div(vocab, SEG); }
+
+size_t draft_scan_workspace_bytes(int rows, int vocab, int k) {
+    const int nseg = draft_num_segments(vocab);
+    return static_cast<size_t>(rows) * nseg * (sizeof(float2) + static_cast<size_t>(k) * sizeof(unsigned long long)) +
+           256;
+}
+
+void launch_draft_topk_expand(const DraftTreeState& st, const bf16* logits, int ld, int vocab, int level,
+                              void* scan_ws, const bf16* h_rows, int h_ld, const int32_t* last_row_ptr, bf16* hid_out,
+                              int hid_ld, int hidden, cudaStream_t s) {
+    const int k = st.k;
+    const int rows = (level == 0) ? 1 : k;
+    const int nseg = draft_num_segments(vocab);
+    CPM_REQUIRE(k >= 1 && k <= 32, "draft: topk_per_iter must be in [1,32]");
+    CPM_REQUIRE(hidden % 8 == 0, "draft: hidden size must be a multiple of 8");
+    float2* stats = reinterpret_cast<float2*>(scan_ws);
+    unsigned long long* cand = reinterpret_cast<unsigned long long*>(
+        reinterpret_cast<uint8_t*>(scan_ws) + align_up(static_cast<int64_t>(k) * nseg * sizeof(float2), 256));
+    dim3 grid(nseg, rows);
+    lsm_stats_kernel<<<grid, SCAN_THREADS, 0, s>>>(logits, ld, vocab, stats, nseg, level == 0 ? last_row_ptr : nullptr);
+    CUDA_CHECK(cudaGetLastError());
+    runtime().launches++;
+    lsm_local_topk_kernel<<<grid, SCAN_THREADS, 0, s>>>(logits, ld, vocab, stats, nseg, k, cand,
+                                                        level == 0 ? last_row_ptr : nullptr);
+    CUDA_CHECK(cudaGetLastError());
+    runtime().launches++;
+    const size_t shmem = static_cast<size_t>(rows) * nseg * k * sizeof(unsigned long long);
+    static size_t configured = 0;
+    if (shmem > 48 * 1024 && shmem > configured) {
+        CPM_REQUIRE(shmem <= 200 * 1024, "draft: candidate list too large for one CTA");
+        CUDA_CHECK(cudaFuncSetAttribute(draft_expand_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                        static_cast<int>(shmem)));
+        configured = shmem;
+    }
+    draft_expand_kernel<<<1, 32 * (k < 4 ? 4 : k), shmem, s>>>(st, cand, nseg, logits, ld, stats, level, h_rows, h_ld,
+                                                               last_row_ptr, hid_out, hid_ld, hidden);
+    CUDA_CHECK(cudaGetLastError());
+    runtime().launches++;
+}
+
+void launch_tree_finalize(const DraftTreeState& st, const int32_t* cache_length, int32_t* tree_draft_ids,
+                          int32_t* tree_pos, uint64_t* tree_mask, int32_t* tree_parent, cudaStream_t s) {
+    CPM_REQUIRE(st.total_tried <= 2048, "draft: total tried candidates exceed 2048");
+    CPM_REQUIRE(st.tree_size >= 2 && st.tree_size <= 64, "draft: tree_size must be in [2,64]");
+    CPM_REQUIRE(st.tree_size - 1 <= st.total_tried, "draft: tree larger than the candidate set");
+    tree_finalize_kernel<<<1, 512, 0, s>>>(st, cache_length, tree_draft_ids, tree_pos, tree_mask, tree_parent,
+                                           runtime().d_error);
+    CUDA_CHECK(cudaGetLastError());
+    runtime().launches++;
+}

@@ -1,0 +1,796 @@
+// Engine: storage layout, weight loading, prefill, tree-verify forward, EAGLE
+// draft loop, acceptance and the captured speculative step.  See engine.cuh for
+// the reference interfaces this mirrors.
+#include "engine.cuh"
+
+#include <algorithm>
+#include <cmath>
+#include <cstring>
+#include <regex>
+
+namespace {
+
+__global__ void state_sync_kernel(int32_t* st, const int32_t* cache_length, int32_t* tree_ids, int fused) {
+    // S_L=0, S_NPREV=1, S_BASE=2, S_LASTROW=3, S_ACCEPT=4
+    const int n = st[4];
+    int L;
+    if (fused) {
+        L = st[0] + n;
+        if (n > 0) tree_ids[0] = tree_ids[n - 1];  // new root = bonus token of the previous step
+    } else {
+        L = cache_length[0];
+    }
+    st[0] = L;
+    st[1] = n;
+    st[2] = L - n;
+    st[3] = (n > 0) ? n - 1 : 0;
+}
+
+__global__ void publish_kernel(const int32_t* result, const int32_t* tokens, const int* error, int32_t* st,
+                               int32_t* out) {
+    const int n = result[0];
+    if (threadIdx.x == 0) {
+        st[4] = n;
+        out[0] = n;
+        out[31] = *error;
+    }
+    if (threadIdx.x < 16) out[1 + threadIdx.x] = (threadIdx.x < n) ? tokens[threadIdx.x] : -1;
+}
+
+__global__ void gather_rows_kernel(const bf16* __restrict__ src, const int32_t* __restrict__ idx, bf16* __restrict__ dst,
+                                   int dim) {
+    const size_t s = static_cast<size_t>(idx[blockIdx.x]) * dim, d = static_cast<size_t>(blockIdx.x) * dim;
+    for (int i = threadIdx.x * 8; i < dim; i += blockDim.x * 8) {
+        *reinterpret_cast<uint4*>(dst + d + i) = *reinterpret_cast<const uint4*>(src + s + i);
+    }
+}
+
+void copy_rows(bf16* dst, int ld_dst, const bf16* src, int ld_src, int rows, int dim, cudaStream_t s) {
+    if (rows <= 0) return;
+    CUDA_CHECK(cudaMemcpy2DAsync(dst, static_cast<size_t>(ld_dst) * 2, src, static_cast<size_t>(ld_src) * 2,
+                                 static_cast<size_t>(dim) * 2, rows, cudaMemcpyDeviceToDevice, s));
+}
+
+}  // namespace
+
+// ------------------------------------------------------------------ memory
+void* Engine::Pool::take(size_t bytes) {
+    const size_t off = (used + 255) & ~size_t(255);
+    used = off + bytes;
+    if (counting) return nullptr;
+    if (used > cap) throw std::runtime_error("cpmcu_b200: device pool overflow");
+    return base + off;
+}
+
+Engine::Engine(const ModelConfig& mc) : mc_(mc) {
+    CPM_REQUIRE(mc.head_dim == 128, "only head_dim 128 is supported");
+    CPM_REQUIRE(mc.hidden % 64 == 0 && mc.inter % 64 == 0, "hidden and intermediate sizes must be multiples of 64");
+    CPM_REQUIRE(mc.hq % mc.hkv == 0, "num_attention_heads must be a multiple of num_key_value_heads");
+    CPM_REQUIRE((mc.hq * mc.head_dim) % 64 == 0, "attention width must be a multiple of 64");
+    qkv_dim_ = (mc.hq + 2 * mc.hkv) * mc.head_dim;
+    layers_.resize(mc.layers);
+    kv_.resize(mc.layers);
+    runtime();
+}
+
+Engine::~Engine() {
+    if (step_graph_) cudaGraphExecDestroy(step_graph_);
+    if (ev0_) cudaEventDestroy(ev0_);
+    if (ev1_) cudaEventDestroy(ev1_);
+    if (pool_.base) cudaFree(pool_.base);
+    if (h_result_) cudaFreeHost(h_result_);
+}
+
+void Engine::attach_eagle(const EagleConfig& ec) {
+    CPM_REQUIRE(!storage_ready_, "attach the drafter before init_storage");
+    CPM_REQUIRE(ec.num_layers == 1, "only a 1-layer EAGLE drafter is supported");
+    CPM_REQUIRE(ec.tree_size >= 2 && ec.tree_size <= 64, "tree_size must be in [2,64]");
+    CPM_REQUIRE(ec.topk >= 1 && ec.topk <= 32 && ec.topk <= ec.tree_size - 1, "topk_per_iter out of range");
+    CPM_REQUIRE(ec.num_iter >= 1 && ec.num_iter <= 15, "num_iter out of range");
+    CPM_REQUIRE(ec.topk * ec.num_iter <= 64, "draft keys (topk * num_iter) exceed the 64-bit mask");
+    ec_ = ec;
+    has_eagle_ = true;
+    draft_vocab_ = (ec.frspec_vocab > 0 && ec.frspec_vocab != mc_.vocab) ? ec.frspec_vocab : mc_.vocab;
+    tree_.k = ec.topk;
+    tree_.num_iter = ec.num_iter;
+    tree_.tree_size = ec.tree_size;
+    tree_.total_tried = ec.topk + ec.topk * ec.topk * (ec.num_iter - 1);
+    CPM_REQUIRE(tree_.total_tried <= 2048, "too many draft candidates");
+    catchup_rows_ = ec.num_iter + 1;
+}
+
+int Engine::attn_splits_for(int rows) const {
+    const int grp = mc_.hq / mc_.hkv;
+    const int mtiles = ceil_div(rows, 128 / grp) * mc_.hkv;
+    int s = runtime().num_sms / mtiles;
+    return std::max(1, std::min(s, 32));
+}
+
+void Engine::lay_out(Pool& p) {
+    const int H = mc_.hidden, I = mc_.inter, V = mc_.vocab, d = mc_.head_dim;
+    const int kvd = mc_.hkv * d;
+    const size_t R = max_rows_;
+    // weights
+    embed_ = take<bf16>(p, static_cast<size_t>(V) * H);
+    lm_head_ = take<bf16>(p, static_cast<size_t>(V) * H);
+    final_norm_ = take<bf16>(p, H);
+    inv_freq_ = take<float>(p, d / 2);
+    for (auto& w : layers_) {
+        w.qkv = take<bf16>(p, static_cast<size_t>(qkv_dim_) * H);
+        w.o = take<bf16>(p, static_cast<size_t>(H) * mc_.hq * d);
+        w.gate_up = take<bf16>(p, static_cast<size_t>(2) * I * H);
+        w.down = take<bf16>(p, static_cast<size_t>(H) * I);
+        w.ln_attn = take<bf16>(p, H);
+        w.ln_ffn = take<bf16>(p, H);
+    }
+    if (has_eagle_) {
+        fc_ = take<bf16>(p, static_cast<size_t>(H) * 2 * H);
+        fc_bias_ = take<bf16>(p, H);
+        in_norm1_ = take<bf16>(p, H);
+        in_norm2_ = take<bf16>(p, H);
+        elayer_.qkv = take<bf16>(p, static_cast<size_t>(qkv_dim_) * H);
+        elayer_.o = take<bf16>(p, static_cast<size_t>(H) * mc_.hq * d);
+        elayer_.gate_up = take<bf16>(p, static_cast<size_t>(2) * I * H);
+        elayer_.down = take<bf16>(p, static_cast<size_t>(H) * I);
+        elayer_.ln_attn = take<bf16>(p, H);
+        elayer_.ln_ffn = take<bf16>(p, H);
+        token_id_remap_ = take<int32_t>(p, draft_vocab_);
+        bf16* dl = (draft_vocab_ != V) ? take<bf16>(p, static_cast<size_t>(draft_vocab_) * H) : lm_head_;
+        draft_lm_head_ = dl;
+    }
+    // activations
+    x_ = take<bf16>(p, R * H);
+    normed_ = take<bf16>(p, R * H);
+    qkv_ = take<bf16>(p, R * qkv_dim_);
+    attn_out_ = take<bf16>(p, R * mc_.hq * d);
+    delta_ = take<bf16>(p, R * H);
+    gate_up_ = take<bf16>(p, R * 2 * I);
+    act_ = take<bf16>(p, R * I);
+    norm_out_ = take<bf16>(p, R * H);
+    lm_in_ = take<bf16>(p, static_cast<size_t>(64) * H);
+    logits_ = take<bf16>(p, static_cast<size_t>(64) * V);
+    gemm_ws_ = reinterpret_cast<float*>(p.take(linear_workspace_bytes(256, runtime().num_sms)));
+    tickets_ = take<int>(p, 1 << 16);
+    {
+        size_t a = 0;
+        for (int rows = 1; rows <= 64; ++rows) {
+            a = std::max(a, attn_workspace_bytes(rows, mc_.hq, d, attn_splits_for(rows)));
+        }
+        attn_ws_o_ = reinterpret_cast<float*>(p.take(a));
+        attn_ws_ml_ = reinterpret_cast<float*>(p.take(a / 32 + 1024));
+    }
+    st_ = take<int32_t>(p, S_COUNT);
+    d_cache_ptrs_ = reinterpret_cast<bf16**>(p.take(sizeof(bf16*) * 2 * mc_.layers));
+    t_ids_ = take<int32_t>(p, 64);
+    t_pos_ = take<int32_t>(p, 64);
+    t_parent_ = take<int32_t>(p, 64);
+    t_gt_ = take<int32_t>(p, 64);
+    t_mask_ = take<uint64_t>(p, 64);
+    accept_result_ = take<int32_t>(p, 32);
+    d_publish_ = take<int32_t>(p, 32);
+    if (has_eagle_) {
+        e_in_ = take<bf16>(p, R * 2 * H);
+        e_x_ = take<bf16>(p, R * H);
+        e_h_ = take<bf16>(p, R * H);
+        e_hid_ = take<bf16>(p, static_cast<size_t>(32) * H);
+        e_emb_ = take<bf16>(p, static_cast<size_t>(32) * H);
+        prev_embed_ = take<bf16>(p, R * H);
+        prev_hidden_ = take<bf16>(p, R * H);
+        e_logits_ = take<bf16>(p, static_cast<size_t>(32) * draft_vocab_);
+        eagle_pos_ = take<int32_t>(p, R);
+        scan_ws_ = p.take(draft_scan_workspace_bytes(32, draft_vocab_, 32));
+        tree_.tried_val = take<bf16>(p, tree_.total_tried + 64);
+        tree_.tried_pos = take<int32_t>(p, tree_.total_tried + 64);
+        tree_.tried_parent = take<int32_t>(p, ec_.topk * ec_.num_iter + 64);
+        tree_.fr_score = take<bf16>(p, 64);
+        tree_.fr_id = take<int32_t>(p, 64);
+        tree_.fr_mask = take<uint64_t>(p, 64);
+        tree_.sel_pos = take<int32_t>(p, 64);
+    }
+    // KV caches last: everything that is left up to the budget
+    for (auto& c : kv_) {
+        c.k = take<bf16>(p, static_cast<size_t>(budget_) * kvd);
+        c.v = take<bf16>(p, static_cast<size_t>(budget_) * kvd);
+    }
+    if (has_eagle_) {
+        ekv_.k = take<bf16>(p, static_cast<size_t>(budget_) * kvd);
+        ekv_.v = take<bf16>(p, static_cast<size_t>(budget_) * kvd);
+    }
+}
+
+int Engine::init_storage() {
+    CPM_REQUIRE(!storage_ready_, "init_storage called twice");
+    Runtime& rt = runtime();
+    max_rows_ = std::max(mc_.chunk_length, 64);
+    size_t free_b = 0, total_b = 0;
+    CUDA_CHECK(cudaMemGetInfo(&free_b, &total_b));
+    const size_t limit = std::min(static_cast<size_t>(static_cast<double>(total_b) * mc_.memory_limit), free_b);
+    // size of everything except the KV caches
+    budget_ = 0;
+    Pool count;
+    lay_out(count);
+    const size_t fixed = count.used + (1 << 20);
+    const size_t per_token = static_cast<size_t>(mc_.layers + (has_eagle_ ? 1 : 0)) * 2 * mc_.hkv * mc_.head_dim * 2;
+    if (fixed + per_token * 256 > limit) {
+        throw std::runtime_error("cpmcu_b200: memory_limit too small for the model (" + std::to_string(fixed >> 20) +
+                                 " MiB needed before any KV cache)");
+    }
+    size_t tokens = (limit - fixed) / per_token;
+    const char* cap_env = getenv("CPMCU_MAX_TOKENS");
+    const size_t cap = cap_env ? static_cast<size_t>(atoll(cap_env)) : (size_t(1) << 20);
+    tokens = std::min(tokens, cap);
+    tokens = tokens / 128 * 128;
+    budget_ = static_cast<int>(tokens);
+    Pool measure;
+    lay_out(measure);
+    pool_.cap = measure.used + 4096;
+    CUDA_CHECK(cudaMalloc(&pool_.base, pool_.cap));
+    pool_.counting = false;
+    pool_.used = 0;
+    lay_out(pool_);
+    // KV rows past the valid length are multiplied by zero probabilities, so they
+    // must hold finite values: clear the caches (and everything else) once.
+    CUDA_CHECK(cudaMemsetAsync(pool_.base, 0, pool_.cap, rt.stream));
+    std::vector<bf16*> ptrs;
+    for (auto& c : kv_) { ptrs.push_back(c.k); ptrs.push_back(c.v); }
+    CUDA_CHECK(cudaMemcpyAsync(d_cache_ptrs_, ptrs.data(), ptrs.size() * sizeof(bf16*), cudaMemcpyHostToDevice,
+                               rt.stream));
+    CUDA_CHECK(cudaStreamSynchronize(rt.stream));
+    CUDA_CHECK(cudaMallocHost(&h_result_, 32 * sizeof(int32_t)));
+    memset(h_result_, 0, 32 * sizeof(int32_t));
+    CUDA_CHECK(cudaEventCreate(&ev0_));
+    CUDA_CHECK(cudaEventCreate(&ev1_));
+    storage_ready_ = true;
+
+    if (has_eagle_) {
+        tree_.token_id_remap = (draft_vocab_ != mc_.vocab) ? token_id_remap_ : nullptr;
+        const int H = mc_.hidden, k = ec_.topk, rc = catchup_rows_;
+        build_layer_plans(eplan_level_, elayer_, ekv_, k, attn_splits_for(k));
+        build_layer_plans(eplan_catchup_, elayer_, ekv_, rc, attn_splits_for(rc));
+        eplan_level_.attn.window = ec_.window;
+        eplan_catchup_.attn.window = ec_.window;
+        fc_plan_level_ = make_linear_plan(e_in_, k, fc_, k, H, 2 * H, e_x_, H, fc_bias_, gemm_ws_, tickets_, rt.num_sms);
+        fc_plan_catchup_ = make_linear_plan(e_in_, rc, fc_, rc, H, 2 * H, e_x_, H, fc_bias_, gemm_ws_, tickets_, rt.num_sms);
+        const bool scale_in = (!ec_.minicpm4_variant && mc_.scale_lmhead != 1.0f);
+        const bf16* lm_x = scale_in ? lm_in_ : e_h_;
+        dlm_plan_level_ = make_linear_plan(lm_x, k, draft_lm_head_, k, draft_vocab_, H, e_logits_, draft_vocab_, nullptr,
+                                           gemm_ws_, tickets_, rt.num_sms);
+        dlm_plan_catchup_ = make_linear_plan(lm_x, rc, draft_lm_head_, rc, draft_vocab_, H, e_logits_, draft_vocab_,
+                                             nullptr, gemm_ws_, tickets_, rt.num_sms);
+    }
+    return budget_;
+}
+
+// ------------------------------------------------------------------ loading
+void Engine::load(const std::string& name, const void* src) {
+    CPM_REQUIRE(storage_ready_, "load_model before init_storage");
+    Runtime& rt = runtime();
+    const int H = mc_.hidden, I = mc_.inter, d = mc_.head_dim;
+    auto copy = [&](void* dst, size_t bytes) {
+        CUDA_CHECK(cudaMemcpyAsync(dst, src, bytes, cudaMemcpyDefault, rt.stream));
+        CUDA_CHECK(cudaStreamSynchronize(rt.stream));
+    };
+    auto load_layer = [&](LayerWeights& w, const std::string& sub) {
+        const size_t qn = static_cast<size_t>(mc_.hq) * d * H, kn = static_cast<size_t>(mc_.hkv) * d * H;
+        if (sub.find("q_proj") != std::string::npos) copy(w.qkv, qn * 2);
+        else if (sub.find("k_proj") != std::string::npos) copy(w.qkv + qn, kn * 2);
+        else if (sub.find("v_proj") != std::string::npos) copy(w.qkv + qn + kn, kn * 2);
+        else if (sub.find("o_proj") != std::string::npos) copy(w.o, static_cast<size_t>(H) * mc_.hq * d * 2);
+        else if (sub.find("gate_proj") != std::string::npos) copy(w.gate_up, static_cast<size_t>(I) * H * 2);
+        else if (sub.find("up_proj") != std::string::npos) copy(w.gate_up + static_cast<size_t>(I) * H, static_cast<size_t>(I) * H * 2);
+        else if (sub.find("down_proj") != std::string::npos) copy(w.down, static_cast<size_t>(H) * I * 2);
+        else if (sub.find("input_layernorm") != std::string::npos) copy(w.ln_attn, static_cast<size_t>(H) * 2);
+        else if (sub.find("post_attention_layernorm") != std::string::npos) copy(w.ln_ffn, static_cast<size_t>(H) * 2);
+        else throw std::invalid_argument("Unsupported name " + sub);
+    };
+    static const std::regex layer_re("layers\\.(\\d+)\\.(.*)");
+    std::smatch m;
+    if (name.rfind("eagle", 0) == 0) {
+        CPM_REQUIRE(has_eagle_, "eagle weight given but no drafter was initialised");
+        if (name.rfind("eagle.fc1", 0) == 0) {
+            if (name.find("weight") != std::string::npos) {
+                CUDA_CHECK(cudaMemcpy2DAsync(fc_, static_cast<size_t>(2) * H * 2, src, static_cast<size_t>(H) * 2,
+                                             static_cast<size_t>(H) * 2, H, cudaMemcpyDefault, rt.stream));
+                CUDA_CHECK(cudaStreamSynchronize(rt.stream));
+            } else if (name.find("bias") != std::string::npos) {
+                copy(fc_bias_, static_cast<size_t>(H) * 2);
+            } else throw std::invalid_argument("Unsupported name " + name);
+        } else if (name.rfind("eagle.fc2", 0) == 0) {
+            CPM_REQUIRE(name.find("weight") != std::string::npos, "Unsupported name " + name);
+            CUDA_CHECK(cudaMemcpy2DAsync(fc_ + H, static_cast<size_t>(2) * H * 2, src, static_cast<size_t>(H) * 2,
+                                         static_cast<size_t>(H) * 2, H, cudaMemcpyDefault, rt.stream));
+            CUDA_CHECK(cudaStreamSynchronize(rt.stream));
+        } else if (name.rfind("eagle.token_id_remap", 0) == 0) {
+            copy(token_id_remap_, static_cast<size_t>(draft_vocab_) * 4);
+            remap_loaded_ = true;
+        } else if (name.find("eagle.input_norm1") != std::string::npos) {
+            CPM_REQUIRE(ec_.use_input_norm, "norm is not used, but input_norm1 is found");
+            copy(in_norm1_, static_cast<size_t>(H) * 2);
+        } else if (name.find("eagle.input_norm2") != std::string::npos) {
+            CPM_REQUIRE(ec_.use_input_norm, "norm is not used, but input_norm2 is found");
+            copy(in_norm2_, static_cast<size_t>(H) * 2);
+        } else if (name.find("eagle.rotary_emb") != std::string::npos) {
+            copy(inv_freq_, static_cast<size_t>(d / 2) * 4);
+        } else if (std::regex_search(name, m, layer_re)) {
+            CPM_REQUIRE(std::stoi(m[1]) == 0, "drafter has a single layer");
+            load_layer(elayer_, m[2]);
+        } else {
+            throw std::invalid_argument("Unsupported name (layer_idx not found): " + name);
+        }
+        return;
+    }
+    if (name.rfind("model.embed_tokens", 0) == 0) {
+        copy(embed_, static_cast<size_t>(mc_.vocab) * H * 2);
+    } else if (name.rfind("model.norm", 0) == 0) {
+        copy(final_norm_, static_cast<size_t>(H) * 2);
+    } else if (name.rfind("lm_head", 0) == 0) {
+        copy(lm_head_, static_cast<size_t>(mc_.vocab) * H * 2);
+        if (has_eagle_ && draft_vocab_ != mc_.vocab) {
+            // FR-Spec: the draft head is the rows of the full head picked by token_id_remap,
+            // which therefore has to be loaded first (reference minicpm4_eagle.cuh:215-218)
+            CPM_REQUIRE(remap_loaded_, "eagle.token_id_remap must be loaded before lm_head");
+            gather_rows_kernel<<<draft_vocab_, 128, 0, rt.stream>>>(lm_head_, token_id_remap_, draft_lm_head_, H);
+            CUDA_CHECK(cudaGetLastError());
+            CUDA_CHECK(cudaStreamSynchronize(rt.stream));
+        }
+    } else if (name.find("rotary_emb") != std::string::npos) {
+        copy(inv_freq_, static_cast<size_t>(d / 2) * 4);
+    } else if (name.rfind("model.layers", 0) == 0 && std::regex_search(name, m, layer_re)) {
+        const int li = std::stoi(m[1]);
+        CPM_REQUIRE(li >= 0 && li < mc_.layers, "layer index out of range: " + name);
+        load_layer(layers_[li], m[2]);
+    } else {
+        throw std::invalid_argument("Unsupported name " + name);
+    }
+}
+
+// ------------------------------------------------------------------ plans
+void Engine::build_layer_plans(LayerPlans& lp, const LayerWeights& w, const KVLayer& kv, int rows, int attn_splits) {
+    const int H = mc_.hidden, I = mc_.inter, d = mc_.head_dim;
+    const int sms = runtime().num_sms;
+    lp.qkv = make_linear_plan(normed_, rows, w.qkv, rows, qkv_dim_, H, qkv_, qkv_dim_, nullptr, gemm_ws_, tickets_, sms);
+    lp.o = make_linear_plan(attn_out_, rows, w.o, rows, H, mc_.hq * d, delta_, H, nullptr, gemm_ws_, tickets_, sms);
+    lp.gate_up = make_linear_plan(normed_, rows, w.gate_up, rows, 2 * I, H, gate_up_, 2 * I, nullptr, gemm_ws_, tickets_, sms);
+    lp.down = make_linear_plan(act_, rows, w.down, rows, H, I, delta_, H, nullptr, gemm_ws_, tickets_, sms);
+    lp.attn = make_attn_plan(qkv_, qkv_dim_, kv.k, kv.v, budget_, rows, mc_.hq, mc_.hkv, d, attn_splits, attn_out_,
+                             mc_.hq * d, attn_ws_o_, attn_ws_ml_);
+}
+
+ForwardPlans& Engine::target_plans(int rows) {
+    auto it = plans_.find(rows);
+    if (it != plans_.end()) return *it->second;
+    auto fp = std::make_unique<ForwardPlans>();
+    fp->rows = rows;
+    fp->layers.resize(mc_.layers);
+    const int splits = (rows <= 64) ? attn_splits_for(rows) : 1;
+    for (int l = 0; l < mc_.layers; ++l) build_layer_plans(fp->layers[l], layers_[l], kv_[l], rows, splits);
+    ForwardPlans& ref = *fp;
+    plans_[rows] = std::move(fp);
+    return ref;
+}
+
+// ------------------------------------------------------------------ forward pieces
+void Engine::layer_forward(LayerPlans& lp, const LayerWeights& w, const KVLayer& kv, const RowCtx& c, bf16* x,
+                           const bf16* pending, float pending_scale, bool first_norm, float res_scale,
+                           cudaStream_t s) {
+    const int H = mc_.hidden, rows = c.rows;
+    if (first_norm) {
+        if (pending) launch_add_rms_norm(x, pending, pending_scale, w.ln_attn, normed_, rows, H, mc_.eps, s);
+        else launch_rms_norm(x, H, w.ln_attn, normed_, H, rows, H, mc_.eps, s);
+    } else {
+        if (pending) launch_add_scaled(x, x, pending, pending_scale, rows, H, s);
+        copy_rows(normed_, H, x, H, rows, H, s);
+    }
+    launch_linear(lp.qkv, s);
+    launch_rope_append(qkv_, rows, mc_.hq, mc_.hkv, mc_.head_dim, inv_freq_, c.pos, c.pos_base, c.pos_off, c.pos_step,
+                       kv.k, kv.v, c.kv_len, c.kv_append_off, c.n_valid, s);
+    lp.attn.kv_len = c.kv_len;
+    lp.attn.kv_len_add = c.attn_kv_add;
+    lp.attn.n_valid = c.n_valid;
+    lp.attn.mask = c.mask;
+    lp.attn.mask_k = c.mask_k;
+    lp.attn.window = c.window;
+    launch_tree_attention(lp.attn, s);
+    launch_linear(lp.o, s);
+    launch_add_rms_norm(x, delta_, res_scale, w.ln_ffn, normed_, rows, H, mc_.eps, s);
+    launch_linear(lp.gate_up, s);
+    launch_silu_gate(gate_up_, act_, rows, mc_.inter, s);
+    launch_linear(lp.down, s);
+}
+
+void Engine::lm_head_rows(const bf16* x, int x_rows, int rows, bf16* logits_out, int ld, cudaStream_t s) {
+    const bf16* in = x;
+    if (mc_.scale_lmhead != 1.0f) {
+        CPM_REQUIRE(rows <= 64, "lm head: at most 64 rows");
+        launch_scale(lm_in_, x, mc_.scale_lmhead, static_cast<size_t>(rows) * mc_.hidden, s);
+        in = lm_in_;
+        x_rows = rows;
+    }
+    LinearPlan p = make_linear_plan(in, x_rows, lm_head_, rows, mc_.vocab, mc_.hidden, logits_out, ld, nullptr,
+                                    gemm_ws_, tickets_, runtime().num_sms);
+    launch_linear(p, s);
+}
+
+void Engine::target_forward(ForwardPlans& fp, const RowCtx& c, const int32_t* ids, bool all_logits,
+                            bf16* logits_out, int logits_ld, cudaStream_t s) {
+    const int H = mc_.hidden, rows = c.rows;
+    launch_embedding(ids, embed_, x_, H, rows, H, mc_.scale_embed, s);
+    const bf16* pending = nullptr;
+    for (int l = 0; l < mc_.layers; ++l) {
+        layer_forward(fp.layers[l], layers_[l], kv_[l], c, x_, pending, mc_.scale_residual, true, mc_.scale_residual, s);
+        pending = delta_;
+    }
+    launch_add_rms_norm(x_, pending, mc_.scale_residual, final_norm_, norm_out_, rows, H, mc_.eps, s);
+    if (all_logits) lm_head_rows(norm_out_, rows, rows, logits_out, logits_ld, s);
+    else lm_head_rows(norm_out_ + static_cast<size_t>(rows - 1) * H, 1, 1, logits_out, logits_ld, s);
+}
+
+// ------------------------------------------------------------------ prefill / decode (reference API)
+void Engine::prefill(int n, int history, const int32_t* ids, const int32_t* pos, bf16* logits_out) {
+    CPM_REQUIRE(storage_ready_, "prefill before init_storage");
+    CPM_REQUIRE(n >= 1 && n <= max_rows_, "prefill chunk larger than chunk_length");
+    CPM_REQUIRE(history >= 0 && history + n <= budget_, "prefill exceeds the KV budget");
+    Runtime& rt = runtime();
+    cudaStream_t s = rt.stream;
+    const int H = mc_.hidden;
+    if (has_eagle_ && history > 0) {
+        // deferred draft prefill of the previous chunk; its last "next token" is this chunk's first token
+        launch_embedding(ids, embed_, prev_embed_ + static_cast<size_t>(num_prev_ - 1) * H, H, 1, H, mc_.scale_embed, s);
+        draft_first(num_history_, s);
+    }
+    CUDA_CHECK(cudaMemcpyAsync(st_ + 6, &history, sizeof(int), cudaMemcpyHostToDevice, s));
+    RowCtx c;
+    c.rows = n;
+    c.pos = pos;
+    c.kv_len = st_ + 6;
+    c.kv_append_off = 0;
+    c.attn_kv_add = n;
+    ForwardPlans fp;  // chunk-sized plans are built per call
+    fp.rows = n;
+    fp.layers.resize(mc_.layers);
+    for (int l = 0; l < mc_.layers; ++l) build_layer_plans(fp.layers[l], layers_[l], kv_[l], n, 1);
+    target_forward(fp, c, ids, false, logits_out, mc_.vocab, s);
+    if (has_eagle_) {
+        if (n > 1) launch_embedding(ids + 1, embed_, prev_embed_, H, n - 1, H, mc_.scale_embed, s);
+        copy_rows(prev_hidden_, H, norm_out_, H, n, H, s);
+        CUDA_CHECK(cudaMemcpyAsync(eagle_pos_, pos, static_cast<size_t>(n) * 4, cudaMemcpyDeviceToDevice, s));
+        num_prev_ = n;
+        num_history_ = history;
+        first_draft_ = true;
+    }
+    CUDA_CHECK(cudaStreamSynchronize(s));
+    check_errors("prefill");
+}
+
+void Engine::decode(int n, int padded_len, const int32_t* ids, const int32_t* pos, const int32_t* cache_length,
+                    const uint64_t* mask, bf16* logits_out, bool cuda_graph) {
+    (void)padded_len;
+    (void)cuda_graph;
+    CPM_REQUIRE(storage_ready_, "decode before init_storage");
+    CPM_REQUIRE(n >= 1 && n <= 64, "decode supports 1..64 tokens");
+    cudaStream_t s = runtime().stream;
+    RowCtx c;
+    c.rows = n;
+    c.pos = pos;
+    c.kv_len = cache_length;  // the caller has already added n (reference cpmcu/llm.py:263-283)
+    c.kv_append_off = -n;
+    c.attn_kv_add = 0;
+    c.mask = mask;
+    c.mask_k = mask ? n : 0;
+    target_forward(target_plans(n), c, ids, true, logits_out, mc_.vocab, s);
+    CUDA_CHECK(cudaStreamSynchronize(s));
+    check_errors("decode");
+}
+
+// ------------------------------------------------------------------ draft
+// x = fc([n1(embed) | n2(hidden)]) + b ; h = x + s * DecoderLayer(x).  e_in_ must hold the concatenated input rows.
+void Engine::draft_forward(const RowCtx& c, int rows, LayerPlans& lp, cudaStream_t s) {
+    (void)rows;
+    layer_forward(lp, elayer_, ekv_, c, e_x_, nullptr, 1.f, ec_.use_attn_norm, ec_.residual_scale, s);
+    launch_add_scaled(e_h_, e_x_, delta_, ec_.residual_scale, c.rows, mc_.hidden, s);
+}
+
+// Draft pass over the num_prev_ rows left by prefill (reference eagle_prefill).
+void Engine::draft_first(int history, cudaStream_t s) {
+    const int H = mc_.hidden, P = num_prev_;
+    Runtime& rt = runtime();
+    if (ec_.use_input_norm) {
+        launch_rms_norm(prev_embed_, H, in_norm1_, e_in_, 2 * H, P, H, mc_.eps, s);
+        launch_rms_norm(prev_hidden_, H, in_norm2_, e_in_ + H, 2 * H, P, H, mc_.eps, s);
+    } else {
+        copy_rows(e_in_, 2 * H, prev_embed_, H, P, H, s);
+        copy_rows(e_in_ + H, 2 * H, prev_hidden_, H, P, H, s);
+    }
+    LinearPlan fc = make_linear_plan(e_in_, P, fc_, P, H, 2 * H, e_x_, H, fc_bias_, gemm_ws_, tickets_, rt.num_sms);
+    launch_linear(fc, s);
+    CUDA_CHECK(cudaMemcpyAsync(st_ + 7, &history, sizeof(int), cudaMemcpyHostToDevice, s));
+    LayerPlans lp;
+    build_layer_plans(lp, elayer_, ekv_, P, 1);
+    RowCtx c;
+    c.rows = P;
+    c.pos = eagle_pos_;
+    c.kv_len = st_ + 7;
+    c.kv_append_off = 0;
+    c.attn_kv_add = P;
+    c.window = ec_.window;
+    draft_forward(c, P, lp, s);
+}
+
+// Draft pass over the tokens accepted by the previous step (reference eagle_decode);
+// fixed launch shape, the valid row count lives on the device.
+void Engine::draft_catchup(cudaStream_t s) {
+    const int H = mc_.hidden, rc = catchup_rows_;
+    if (ec_.use_input_norm) {
+        launch_rms_norm(prev_embed_, H, in_norm1_, e_in_, 2 * H, rc, H, mc_.eps, s);
+        launch_rms_norm(prev_hidden_, H, in_norm2_, e_in_ + H, 2 * H, rc, H, mc_.eps, s);
+    } else {
+        copy_rows(e_in_, 2 * H, prev_embed_, H, rc, H, s);
+        copy_rows(e_in_ + H, 2 * H, prev_hidden_, H, rc, H, s);
+    }
+    launch_linear(fc_plan_catchup_, s);
+    // layer_forward takes kv_len for both append and attention; the catch-up needs
+    // different bases (append at L-n, attend over L), so split it here.
+    {
+        LayerPlans& lp = eplan_catchup_;
+        const LayerWeights& w = elayer_;
+        if (ec_.use_attn_norm) launch_rms_norm(e_x_, H, w.ln_attn, normed_, H, rc, H, mc_.eps, s);
+        else copy_rows(normed_, H, e_x_, H, rc, H, s);
+        launch_linear(lp.qkv, s);
+        launch_rope_append(qkv_, rc, mc_.hq, mc_.hkv, mc_.head_dim, inv_freq_, eagle_pos_, nullptr, 0, 0, ekv_.k, ekv_.v,
+                           st_ + S_BASE, 0, st_ + S_NPREV, s);
+        lp.attn.kv_len = st_ + S_L;
+        lp.attn.kv_len_add = 0;
+        lp.attn.n_valid = st_ + S_NPREV;
+        lp.attn.mask = nullptr;
+        lp.attn.mask_k = 0;
+        lp.attn.window = ec_.window;
+        launch_tree_attention(lp.attn, s);
+        launch_linear(lp.o, s);
+        launch_add_rms_norm(e_x_, delta_, ec_.residual_scale, w.ln_ffn, normed_, rc, H, mc_.eps, s);
+        launch_linear(lp.gate_up, s);
+        launch_silu_gate(gate_up_, act_, rc, mc_.inter, s);
+        launch_linear(lp.down, s);
+        launch_add_scaled(e_h_, e_x_, delta_, ec_.residual_scale, rc, H, s);
+    }
+}
+
+void Engine::draft_levels(int32_t* tree_ids, int32_t* tree_pos, const int32_t* cache_length, uint64_t* tree_mask,
+                          int32_t* tree_parent, bool first, cudaStream_t s) {
+    const int H = mc_.hidden, k = ec_.topk;
+    Runtime& rt = runtime();
+    const bool scale_in = (!ec_.minicpm4_variant && mc_.scale_lmhead != 1.0f);
+    bf16* hid_dst = ec_.use_input_norm ? e_hid_ : e_in_ + H;
+    const int hid_ld = ec_.use_input_norm ? H : 2 * H;
+    // level 0: logits of the last pending row
+    if (first) {
+        const bf16* last = e_h_ + static_cast<size_t>(num_prev_ - 1) * H;
+        const bf16* in = last;
+        if (scale_in) {
+            launch_scale(lm_in_, last, mc_.scale_lmhead, H, s);
+            in = lm_in_;
+        }
+        LinearPlan p = make_linear_plan(in, 1, draft_lm_head_, 1, draft_vocab_, H, e_logits_, draft_vocab_, nullptr,
+                                        gemm_ws_, tickets_, rt.num_sms);
+        launch_linear(p, s);
+        launch_draft_topk_expand(tree_, e_logits_, draft_vocab_, draft_vocab_, 0, scan_ws_, last, H, nullptr, hid_dst,
+                                 hid_ld, H, s);
+    } else {
+        if (scale_in) launch_scale(lm_in_, e_h_, mc_.scale_lmhead, static_cast<size_t>(catchup_rows_) * H, s);
+        launch_linear(dlm_plan_catchup_, s);
+        launch_draft_topk_expand(tree_, e_logits_, draft_vocab_, draft_vocab_, 0, scan_ws_, e_h_, H, st_ + S_LASTROW,
+                                 hid_dst, hid_ld, H, s);
+    }
+    for (int d = 1; d < ec_.num_iter; ++d) {
+        if (ec_.use_input_norm) {
+            launch_embedding(tree_.fr_id, embed_, e_emb_, H, k, H, mc_.scale_embed, s);
+            launch_rms_norm(e_emb_, H, in_norm1_, e_in_, 2 * H, k, H, mc_.eps, s);
+            launch_rms_norm(e_hid_, H, in_norm2_, e_in_ + H, 2 * H, k, H, mc_.eps, s);
+        } else {
+            launch_embedding(tree_.fr_id, embed_, e_in_, 2 * H, k, H, mc_.scale_embed, s);
+        }
+        launch_linear(fc_plan_level_, s);
+        RowCtx c;
+        c.rows = k;
+        c.pos_base = cache_length;
+        c.pos_off = d - 1;
+        c.pos_step = 0;
+        c.kv_len = cache_length;
+        c.kv_append_off = k * (d - 1);
+        c.attn_kv_add = k * d;
+        c.mask = tree_.fr_mask;
+        c.mask_k = k * d;
+        c.window = ec_.window;
+        draft_forward(c, k, eplan_level_, s);
+        if (scale_in) launch_scale(lm_in_, e_h_, mc_.scale_lmhead, static_cast<size_t>(k) * H, s);
+        launch_linear(dlm_plan_level_, s);
+        launch_draft_topk_expand(tree_, e_logits_, draft_vocab_, draft_vocab_, d, scan_ws_, e_h_, H, nullptr, hid_dst,
+                                 hid_ld, H, s);
+    }
+    launch_tree_finalize(tree_, cache_length, tree_ids, tree_pos, tree_mask, tree_parent, s);
+}
+
+void Engine::draft(int32_t* tree_ids, int32_t* tree_pos, const int32_t* cache_length, uint64_t* tree_mask,
+                   int32_t* tree_parent) {
+    CPM_REQUIRE(has_eagle_ && storage_ready_, "draft needs an initialised drafter");
+    cudaStream_t s = runtime().stream;
+    const int H = mc_.hidden;
+    if (first_draft_) {
+        // the root token's embedding is the last "next token" input of the prompt rows
+        launch_embedding(tree_ids, embed_, prev_embed_ + static_cast<size_t>(num_prev_ - 1) * H, H, 1, H,
+                         mc_.scale_embed, s);
+        draft_first(num_history_, s);
+    } else {
+        state_sync_kernel<<<1, 1, 0, s>>>(st_, cache_length, tree_ids, 0);
+        CUDA_CHECK(cudaGetLastError());
+        runtime().launches++;
+        draft_catchup(s);
+    }
+    draft_levels(tree_ids, tree_pos, cache_length, tree_mask, tree_parent, first_draft_, s);
+    first_draft_ = false;
+    CUDA_CHECK(cudaStreamSynchronize(s));
+    check_errors("draft");
+}
+
+// ------------------------------------------------------------------ accept
+void Engine::accept_and_fix(int T, int32_t* pred, const int32_t* gt, const int32_t* pos, const int32_t* cache_length,
+                            const uint64_t* mask, const int32_t* parent, cudaStream_t s) {
+    AcceptIO io;
+    io.tree_size = T;
+    io.pred = pred;
+    io.gt = gt;
+    io.position_ids = pos;
+    io.cache_length = cache_length;
+    io.attn_mask = mask;
+    io.tree_parent = parent;
+    io.result = accept_result_;
+    launch_verify_accept(io, s);
+    FixupArgs f;
+    f.result = accept_result_;
+    f.cache_length = cache_length;
+    f.caches = d_cache_ptrs_;
+    f.num_caches = 2 * mc_.layers;
+    f.kv_dim = mc_.hkv * mc_.head_dim;
+    f.max_accept = has_eagle_ ? catchup_rows_ : 1;
+    f.norm_out = norm_out_;
+    f.prev_hidden = prev_hidden_;
+    f.tokens = pred;
+    f.embed_table = embed_;
+    f.embed_scale = mc_.scale_embed;
+    f.prev_embed = prev_embed_;
+    f.eagle_pos = eagle_pos_;
+    f.hidden = mc_.hidden;
+    launch_accept_fixup(f, s);
+    publish_kernel<<<1, 32, 0, s>>>(accept_result_, pred, runtime().d_error, st_, d_publish_);
+    CUDA_CHECK(cudaGetLastError());
+    runtime().launches++;
+}
+
+int Engine::verify_and_fix(int T, int32_t* pred, const int32_t* gt, const int32_t* pos, const int32_t* cache_length,
+                           const uint64_t* mask, const int32_t* parent) {
+    CPM_REQUIRE(has_eagle_ && storage_ready_, "verify needs an initialised drafter");
+    CPM_REQUIRE(T == ec_.tree_size, "verify: tree size differs from the drafter's");
+    cudaStream_t s = runtime().stream;
+    accept_and_fix(T, pred, gt, pos, cache_length, mask, parent, s);
+    CUDA_CHECK(cudaMemcpyAsync(h_result_, d_publish_, 32 * sizeof(int32_t), cudaMemcpyDeviceToHost, s));
+    CUDA_CHECK(cudaStreamSynchronize(s));
+    if (h_result_[31] != 0) check_errors("verify_and_fix");
+    num_prev_ = h_result_[0];
+    return h_result_[0];
+}
+
+void Engine::check_errors(const char* where) {
+    const int e = read_and_clear_error();
+    if (e != 0) {
+        throw std::runtime_error(std::string("cpmcu_b200: kernel error flags ") + std::to_string(e) + " raised in " +
+                                 where + " (1 = GEMM pipeline timeout, 2 = attention pipeline timeout, 4 = malformed draft tree)");
+    }
+}
+
+// ------------------------------------------------------------------ fused step
+void Engine::begin_generation(int prefix_length, int32_t root_token) {
+    CPM_REQUIRE(has_eagle_ && storage_ready_, "begin_generation needs an initialised drafter");
+    CPM_REQUIRE(first_draft_, "begin_generation must follow prefill");
+    cudaStream_t s = runtime().stream;
+    int32_t init[S_COUNT] = {0};
+    init[S_L] = prefix_length;
+    CUDA_CHECK(cudaMemcpyAsync(st_, init, 6 * sizeof(int32_t), cudaMemcpyHostToDevice, s));
+    CUDA_CHECK(cudaMemcpyAsync(t_ids_, &root_token, sizeof(int32_t), cudaMemcpyHostToDevice, s));
+    CUDA_CHECK(cudaStreamSynchronize(s));
+}
+
+// One speculative step on engine-owned buffers: state advance, draft, tree,
+// target verify forward, argmax, acceptance, fix-up, publish.
+void Engine::enqueue_step(bool first, cudaStream_t s) {
+    const int T = ec_.tree_size, H = mc_.hidden;
+    state_sync_kernel<<<1, 1, 0, s>>>(st_, nullptr, t_ids_, 1);
+    CUDA_CHECK(cudaGetLastError());
+    runtime().launches++;
+    if (first) {
+        launch_embedding(t_ids_, embed_, prev_embed_ + static_cast<size_t>(num_prev_ - 1) * H, H, 1, H, mc_.scale_embed, s);
+        draft_first(num_history_, s);
+    } else {
+        draft_catchup(s);
+    }
+    draft_levels(t_ids_, t_pos_, st_ + S_L, t_mask_, t_parent_, first, s);
+    RowCtx c;
+    c.rows = T;
+    c.pos = t_pos_;
+    c.kv_len = st_ + S_L;
+    c.kv_append_off = 0;
+    c.attn_kv_add = T;
+    c.mask = t_mask_;
+    c.mask_k = T;
+    ForwardPlans& fp = target_plans(T);
+    const int V = mc_.vocab;
+    // target forward; the LM-head plan is cached because its output buffer is engine-owned
+    launch_embedding(t_ids_, embed_, x_, H, T, H, mc_.scale_embed, s);
+    const bf16* pending = nullptr;
+    for (int l = 0; l < mc_.layers; ++l) {
+        layer_forward(fp.layers[l], layers_[l], kv_[l], c, x_, pending, mc_.scale_residual, true, mc_.scale_residual, s);
+        pending = delta_;
+    }
+    launch_add_rms_norm(x_, pending, mc_.scale_residual, final_norm_, norm_out_, T, H, mc_.eps, s);
+    if (mc_.scale_lmhead != 1.0f) launch_scale(lm_in_, norm_out_, mc_.scale_lmhead, static_cast<size_t>(T) * H, s);
+    if (lm_plan_tree_.grid == 0) {
+        lm_plan_tree_ = make_linear_plan(mc_.scale_lmhead != 1.0f ? lm_in_ : norm_out_, T, lm_head_, T, V, H, logits_, V,
+                                         nullptr, gemm_ws_, tickets_, runtime().num_sms);
+    }
+    launch_linear(lm_plan_tree_, s);
+    launch_argmax(logits_, T, V, V, t_gt_, s);
+    accept_and_fix(T, t_ids_, t_gt_, t_pos_, st_ + S_L, t_mask_, t_parent_, s);
+    CUDA_CHECK(cudaMemcpyAsync(h_result_, d_publish_, 32 * sizeof(int32_t), cudaMemcpyDeviceToHost, s));
+}
+
+int Engine::spec_step(int32_t* out_tokens, int max_tokens) {
+    CPM_REQUIRE(has_eagle_ && storage_ready_, "spec_step needs an initialised drafter");
+    Runtime& rt = runtime();
+    cudaStream_t s = rt.stream;
+    if (first_draft_) {
+        CUDA_CHECK(cudaEventRecord(ev0_, s));
+        enqueue_step(true, s);
+        CUDA_CHECK(cudaEventRecord(ev1_, s));
+        first_draft_ = false;
+    } else {
+        if (step_graph_ == nullptr) {
+            const long before = rt.launches;
+            cudaGraph_t graph = nullptr;
+            CUDA_CHECK(cudaStreamBeginCapture(s, cudaStreamCaptureModeRelaxed));
+            try {
+                enqueue_step(false, s);
+            } catch (...) {
+                cudaStreamEndCapture(s, &graph);
+                if (graph) cudaGraphDestroy(graph);
+                throw;
+            }
+            CUDA_CHECK(cudaStreamEndCapture(s, &graph));
+            CUDA_CHECK(cudaGraphInstantiate(&step_graph_, graph, 0));
+            CUDA_CHECK(cudaGraphDestroy(graph));
+            launches_per_step_ = rt.launches - before;
+        }
+        CUDA_CHECK(cudaEventRecord(ev0_, s));
+        CUDA_CHECK(cudaGraphLaunch(step_graph_, s));
+        CUDA_CHECK(cudaEventRecord(ev1_, s));
+        rt.launches += launches_per_step_;
+    }
+    CUDA_CHECK(cudaStreamSynchronize(s));
+    float ms = 0.f;
+    CUDA_CHECK(cudaEventElapsedTime(&ms, ev0_, ev1_));
+    last_step_ms_ = ms;
+    if (h_result_[31] != 0) check_errors("spec_step");
+    const int n = h_result_[0];
+    num_prev_ = n;
+    for (int i = 0; i < n && i < max_tokens; ++i) out_tokens[i] = h_result_[1 + i];
+    return n;
+}
+
+const int32_t* Engine::tree_buffers(int which) const {
+    switch (which) {
+        case 0: return t_ids_;
+        case 1: return t_pos_;
+        case 2: return t_parent_;
+        case 3: return t_gt_;
+        case 4: return reinterpret_cast<const int32_t*>(t_mask_);
+        case 5: return st_;
+        default: return nullptr;
+    }
+}

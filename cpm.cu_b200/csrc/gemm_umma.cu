@@ -1,0 +1,347 @@
+// Weight-streaming linear layer for the speculative step, sm_100a.
+//
+//   Y[M,N] = X[M,K] * W[N,K]^T (+ bias)      bf16 in, fp32 accumulate, bf16 out
+//
+// Replaces the reference's cuBLAS call `linear<T>` (src/model/linear.cuh:8-37)
+// for every GEMM of the draft loop (M = 1..16) and of the tree-verify pass
+// (M = tree size <= 64), where the op is bound by reading W once from HBM.
+//
+// Mapping.  The weight tile is the UMMA "A" operand (128 rows of N, full-rate
+// M=128 MMA) and the token tile is the "B" operand (UMMA N = MT = 16..256), so
+// the accumulator in TMEM is Y^T: lane = output feature, column = token.  Both
+// operands are K-major and arrive through TMA with 128-byte swizzle into a
+// multi-stage shared-memory ring; one thread issues tcgen05.mma; four epilogue
+// warps read TMEM back with tcgen05.ld.
+//
+// Scheduling.  The (tile, k-block) work units are laid out in one line and cut
+// into gridDim.x equal pieces (stream-K), so every SM streams the same number
+// of weight bytes whatever N and K are.  A piece that covers only part of a
+// tile's K range writes its fp32 partial to a workspace slot and bumps the
+// tile's ticket; the last piece to arrive sums the slots in a fixed order
+// (deterministic) and writes the bf16 result.  No CTA ever waits on another.
+#include "common.cuh"
+#include "ptx.cuh"
+
+namespace {
+
+constexpr int BLOCK_N = 128;  // weight rows per tile (UMMA M)
+constexpr int BLOCK_K = 64;   // bf16 elements per 128-byte swizzle row
+constexpr int UMMA_K = 16;
+constexpr int W_TILE_BYTES = BLOCK_N * BLOCK_K * 2;
+constexpr int NUM_THREADS = 192;  // warp 0 TMA, warp 1 MMA + TMEM, warps 2-5 epilogue
+
+template <int MT>
+struct Cfg {
+    static constexpr int X_TILE_BYTES = MT * BLOCK_K * 2;
+    static constexpr int STAGE_BYTES = W_TILE_BYTES + X_TILE_BYTES;
+    static constexpr int STAGES = (MT <= 16) ? 10 : (MT <= 32) ? 9 : (MT <= 64) ? 8 : (MT <= 128) ? 6 : 4;
+    static constexpr int TMEM_COLS = (2 * MT < 32) ? 32 : 2 * MT;
+    static constexpr int CTRL_BYTES = 256;
+    static constexpr int SMEM_BYTES = STAGES * STAGE_BYTES + CTRL_BYTES + 1024;
+};
+
+struct LinearArgs {
+    int M, N, K;
+    int n_tiles, m_tiles, kblocks;
+    long long total_units;
+    bf16* y;
+    int ldy;
+    const bf16* bias;
+    float* workspace;
+    int* tickets;
+    int* error;
+};
+
+struct SegIter {
+    long long u, u_end;
+    int kblocks;
+    __device__ bool next(int& tile, int& kb0, int& kb1) {
+        if (u >= u_end) return false;
+        tile = static_cast<int>(u / kblocks);
+        kb0 = static_cast<int>(u - static_cast<long long>(tile) * kblocks);
+        long long rem = u_end - u;
+        kb1 = (kb0 + rem < kblocks) ? static_cast<int>(kb0 + rem) : kblocks;
+        u += kb1 - kb0;
+        return true;
+    }
+};
+
+// CTA that owns work unit u when [0,U) is cut into G pieces starting at floor(g*U/G).
+__device__ __forceinline__ int unit_owner(long long u, long long U, int G) {
+    return static_cast<int>(((u + 1) * G - 1) / U);
+}
+
+template <int MT>
+__global__ void __launch_bounds__(NUM_THREADS, 1)
+linear_umma_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_constant__ CUtensorMap tm_x,
+                   const LinearArgs a) {
+    using C = Cfg<MT>;
+    extern __shared__ uint8_t smem_raw[];
+    uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+    uint8_t* tiles = smem;
+    uint64_t* full = reinterpret_cast<uint64_t*>(smem + C::STAGES * C::STAGE_BYTES);
+    uint64_t* empty = full + C::STAGES;
+    uint64_t* acc_full = empty + C::STAGES;
+    uint64_t* acc_empty = acc_full + 2;
+    uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(acc_empty + 2);
+    volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
+    volatile int* s_last = abort_flag + 1;
+
+    const int warp = threadIdx.x >> 5;
+    const int lane = threadIdx.x & 31;
+    const int G = gridDim.x;
+    const int g = blockIdx.x;
+
+    if (threadIdx.x == 0) {
+        for (int s = 0; s < C::STAGES; ++s) {
+            ptx::mbar_init(&full[s], 1);
+            ptx::mbar_init(&empty[s], 1);
+        }
+        for (int s = 0; s < 2; ++s) {
+            ptx::mbar_init(&acc_full[s], 1);
+            ptx::mbar_init(&acc_empty[s], 128);
+        }
+        *abort_flag = 0;
+        *s_last = 0;
+        ptx::mbar_fence_init();
+        ptx::prefetch_tensormap(&tm_w);
+        ptx::prefetch_tensormap(&tm_x);
+    }
+    if (warp == 1) {
+        ptx::tmem_alloc(tmem_slot, C::TMEM_COLS);
+        ptx::tmem_relinquish();
+    }
+    ptx::tc_fence_before();
+    __syncthreads();
+    ptx::tc_fence_after();
+    const uint32_t tmem_base = *tmem_slot;
+
+    SegIter it;
+    it.u = (a.total_units * g) / G;
+    it.u_end = (a.total_units * (g + 1)) / G;
+    it.kblocks = a.kblocks;
+
+    if (warp == 0) {
+        // ------------------------------------------------ TMA producer
+        if (lane == 0) {
+            int stage = 0;
+            uint32_t phase = 0;
+            int tile, kb0, kb1;
+            bool ok = true;
+            while (ok && it.next(tile, kb0, kb1)) {
+                const int m_tile = tile / a.n_tiles;
+                const int n_tile = tile - m_tile * a.n_tiles;
+                for (int kb = kb0; kb < kb1; ++kb) {
+                    if (!ptx::mbar_wait(&empty[stage], phase ^ 1, abort_flag)) { ok = false; break; }
+                    uint8_t* dst = tiles + stage * C::STAGE_BYTES;
+                    ptx::mbar_arrive_expect_tx(&full[stage], C::STAGE_BYTES);
+                    ptx::tma_load_2d(dst, &tm_w, &full[stage], kb * BLOCK_K, n_tile * BLOCK_N);
+                    ptx::tma_load_2d(dst + W_TILE_BYTES, &tm_x, &full[stage], kb * BLOCK_K, m_tile * MT);
+                    if (++stage == C::STAGES) { stage = 0; phase ^= 1; }
+                }
+            }
+            if (!ok) {
+                // give copies already in flight time to land before the CTA retires
+                const long long t0 = clock64();
+                while (clock64() - t0 < 2000000LL) {}
+            }
+        }
+    } else if (warp == 1) {
+        // ------------------------------------------------ MMA issuer
+        if (lane == 0) {
+            constexpr uint32_t idesc = ptx::umma_idesc_bf16(BLOCK_N, MT, 0, 0);
+            int stage = 0;
+            uint32_t phase = 0;
+            int acc = 0;
+            uint32_t acc_phase = 0;
+            int tile, kb0, kb1;
+            bool ok = true;
+            while (ok && it.next(tile, kb0, kb1)) {
+                if (!ptx::mbar_wait(&acc_empty[acc], acc_phase ^ 1, abort_flag)) break;
+                ptx::tc_fence_after();
+                const uint32_t d_tmem = tmem_base + acc * MT;
+                for (int kb = kb0; kb < kb1; ++kb) {
+                    if (!ptx::mbar_wait(&full[stage], phase, abort_flag)) { ok = false; break; }
+                    ptx::tc_fence_after();
+                    const uint32_t wa = ptx::smem_u32(tiles + stage * C::STAGE_BYTES);
+                    const uint32_t xa = wa + W_TILE_BYTES;
+#pragma unroll
+                    for (int j = 0; j < BLOCK_K / UMMA_K; ++j) {
+                        const uint64_t da = ptx::umma_desc_sw128(wa + j * UMMA_K * 2, 16, 1024);
+                        const uint64_t db = ptx::umma_desc_sw128(xa + j * UMMA_K * 2, 16, 1024);
+                        ptx::umma_ss(d_tmem, da, db, idesc, (kb > kb0 || j > 0) ? 1u : 0u);
+                    }
+                    ptx::umma_commit(&empty[stage]);
+                    if (++stage == C::STAGES) { stage = 0; phase ^= 1; }
+                }
+                if (!ok) break;
+                ptx::umma_commit(&acc_full[acc]);
+                acc ^= 1;
+                if (acc == 0) acc_phase ^= 1;
+            }
+        }
+    } else {
+        // ------------------------------------------------ epilogue (128 threads)
+        const int q = warp & 3;                 // TMEM lane quarter this warp may read
+        const int row = q * 32 + lane;          // output feature within the tile
+        const int epi_tid = threadIdx.x - 64;
+        int acc = 0;
+        uint32_t acc_phase = 0;
+        int tile, kb0, kb1;
+        while (it.next(tile, kb0, kb1)) {
+            const int m_tile = tile / a.n_tiles;
+            const int n_tile = tile - m_tile * a.n_tiles;
+            const int m_base = m_tile * MT;
+            const int n = n_tile * BLOCK_N + row;
+            int m_cnt = a.M - m_base;
+            if (m_cnt > MT) m_cnt = MT;
+            const bool complete = (kb0 == 0 && kb1 == a.kblocks);
+            // partial slot: pieces that start mid-tile use slot 0 of this CTA, the
+            // piece that starts a tile but does not finish it uses slot 1
+            float* my_ws = a.workspace + (static_cast<size_t>(g) * 2 + (kb0 == 0 ? 1 : 0)) * (MT * BLOCK_N);
+            const float bias_v = (a.bias != nullptr && n < a.N) ? __bfloat162float(a.bias[n]) : 0.f;
+
+            if (!ptx::mbar_wait(&acc_full[acc], acc_phase, abort_flag)) break;
+            ptx::tc_fence_after();
+            const uint32_t t_addr = tmem_base + (static_cast<uint32_t>(q * 32) << 16) + acc * MT;
+#pragma unroll 1
+            for (int c0 = 0; c0 < MT; c0 += 16) {
+                if (c0 >= m_cnt) break;  // uniform across the CTA
+                uint32_t r[16];
+                ptx::tmem_ld16(t_addr + c0, r);
+                ptx::tmem_wait_ld();
+                if (complete) {
+                    if (n < a.N) {
+#pragma unroll
+                        for (int c = 0; c < 16; ++c) {
+                            if (c0 + c < m_cnt) {
+                                a.y[static_cast<size_t>(m_base + c0 + c) * a.ldy + n] =
+                                    __float2bfloat16(__uint_as_float(r[c]) + bias_v);
+                            }
+                        }
+                    }
+                } else {
+#pragma unroll
+                    for (int c = 0; c < 16; ++c) {
+                        if (c0 + c < m_cnt) my_ws[(c0 + c) * BLOCK_N + row] = __uint_as_float(r[c]);
+                    }
+                }
+            }
+            ptx::tc_fence_before();
+            ptx::mbar_arrive(&acc_empty[acc]);
+            acc ^= 1;
+            if (acc == 0) acc_phase ^= 1;
+
+            if (!complete) {
+                const long long tile_u0 = static_cast<long long>(tile) * a.kblocks;
+                const int g_first = unit_owner(tile_u0, a.total_units, G);
+                const int g_last = unit_owner(tile_u0 + a.kblocks - 1, a.total_units, G);
+                const int nseg = g_last - g_first + 1;
+                __threadfence();
+                ptx::named_bar_sync(1, 128);
+                if (epi_tid == 0) {
+                    const int old = atomicAdd(&a.tickets[tile], 1);
+                    const int last = (old == nseg - 1) ? 1 : 0;
+                    if (last) a.tickets[tile] = 0;  // ready for the next launch
+                    *s_last = last;
+                }
+                ptx::named_bar_sync(1, 128);
+                const bool is_last = (*s_last != 0);
+                ptx::named_bar_sync(1, 128);  // everyone has read s_last before it can change
+                if (is_last) {
+                    __threadfence();
+                    if (n < a.N) {
+                        for (int c = 0; c < m_cnt; ++c) {
+                            float sum = 0.f;
+                            for (int gg = g_first; gg <= g_last; ++gg) {
+                                const float* ws = a.workspace +
+                                                  (static_cast<size_t>(gg) * 2 + (gg == g_first ? 1 : 0)) * (MT * BLOCK_N);
+                                sum += __ldcg(ws + c * BLOCK_N + row);
+                            }
+                            a.y[static_cast<size_t>(m_base + c) * a.ldy + n] = __float2bfloat16(sum + bias_v);
+                        }
+                    }
+                }
+            }
+        }
+    }
+
+    ptx::tc_fence_before();
+    __syncthreads();
+    if (warp == 1) {
+        ptx::tc_fence_after();
+        ptx::tmem_dealloc(tmem_base, C::TMEM_COLS);
+    }
+    if (threadIdx.x == 0 && *abort_flag) atomicOr(a.error, ERR_GEMM_TIMEOUT);
+}
+
+template <int MT>
+void launch_mt(const LinearPlan& p, const LinearArgs& args, cudaStream_t stream) {
+    using C = Cfg<MT>;
+    static bool configured = false;
+    if (!configured) {
+        CUDA_CHECK(cudaFuncSetAttribute(linear_umma_kernel<MT>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                        C::SMEM_BYTES));
+        configured = true;
+    }
+    linear_umma_kernel<MT><<<p.grid, NUM_THREADS, C::SMEM_BYTES, stream>>>(p.tm_w, p.tm_x, args);
+    CUDA_CHECK(cudaGetLastError());
+    runtime().launches++;
+}
+
+}  // namespace
+
+int linear_pick_mt(int M) {
+    if (M <= 16) return 16;
+    if (M <= 32) return 32;
+    if (M <= 64) return 64;
+    if (M <= 128) return 128;
+    return 256;
+}
+
+size_t linear_workspace_bytes(int mt, int grid) {
+    return static_cast<size_t>(grid) * 2 * mt * BLOCK_N * sizeof(float);
+}
+
+LinearPlan make_linear_plan(const bf16* x, int x_rows, const bf16* w, int M, int N, int K, bf16* y, int ldy,
+                            const bf16* bias, float* workspace, int* tickets, int grid_limit) {
+    CPM_REQUIRE(M >= 1 && N >= 1 && K >= BLOCK_K, "linear: empty problem");
+    CPM_REQUIRE(K % BLOCK_K == 0, "linear: K must be a multiple of 64");
+    CPM_REQUIRE(x_rows >= 1, "linear: x_rows must be positive");
+    CPM_REQUIRE((reinterpret_cast<uintptr_t>(x) & 15) == 0 && (reinterpret_cast<uintptr_t>(w) & 15) == 0,
+                "linear: operands must be 16-byte aligned");
+    LinearPlan p;
+    p.M = M; p.N = N; p.K = K;
+    p.mt = linear_pick_mt(M);
+    p.y = y; p.ldy = ldy; p.bias = bias;
+    p.workspace = workspace; p.tickets = tickets;
+    const int n_tiles = ceil_div(N, BLOCK_N), m_tiles = ceil_div(M, p.mt), kblocks = K / BLOCK_K;
+    const long long units = static_cast<long long>(n_tiles) * m_tiles * kblocks;
+    long long grid = units / 4;  // at least four k-blocks per CTA
+    if (grid < 1) grid = 1;
+    if (grid > grid_limit) grid = grid_limit;
+    p.grid = static_cast<int>(grid);
+    p.tm_w = make_tmap_2d(w, K, N, static_cast<uint64_t>(K) * 2, BLOCK_K, BLOCK_N);
+    p.tm_x = make_tmap_2d(x, K, x_rows, static_cast<uint64_t>(K) * 2, BLOCK_K, p.mt);
+    return p;
+}
+
+void launch_linear(const LinearPlan& p, cudaStream_t stream) {
+    LinearArgs a;
+    a.M = p.M; a.N = p.N; a.K = p.K;
+    a.n_tiles = ceil_div(p.N, BLOCK_N);
+    a.m_tiles = ceil_div(p.M, p.mt);
+    a.kblocks = p.K / BLOCK_K;
+    a.total_units = static_cast<long long>(a.n_tiles) * a.m_tiles * a.kblocks;
+    a.y = p.y; a.ldy = p.ldy; a.bias = p.bias;
+    a.workspace = p.workspace; a.tickets = p.tickets;
+    a.error = runtime().d_error;
+    switch (p.mt) {
+        case 16: launch_mt<16>(p, a, stream); break;
+        case 32: launch_mt<32>(p, a, stream); break;
+        case 64: launch_mt<64>(p, a, stream); break;
+        case 128: launch_mt<128>(p, a, stream); break;
+        case 256: launch_mt<256>(p, a, stream); break;
+        default: throw std::invalid_argument("cpmcu_b200: bad token tile");
+    }
+}

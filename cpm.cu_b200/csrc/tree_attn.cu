@@ -1,0 +1,454 @@
+// Tree-verification attention over the contiguous bf16 KV cache, sm_100a.
+//
+// Replaces the reference's FlashAttention fork entry `mha_fwd_kvcache`
+// (src/flash_attn/flash_api.hpp:292-392: split-KV kernel + combine) for the
+// verify pass (tree rows), the draft levels, the draft's catch-up pass and the
+// causal prefill.  Visibility of key c for query token t follows the reference
+// (src/flash_attn/src/mask.h:182-222): c < kv_total - tq + t + 1 (causal), and
+// for the last `mask_k` keys additionally bit (c - (kv_total - mask_k)) of the
+// token's 64-bit tree mask.
+//
+// Mapping.  All `grp = hq / hkv` query heads that share a KV head are packed
+// with 128 / grp consecutive tokens into one 128-row tile, so a K/V tile is
+// read once per KV head and tile instead of once per query head.  Per CTA:
+//   S = Q K^T   tcgen05.mma, A = Q (K-major), B = K tile (K-major), S in TMEM
+//   softmax     one thread per row reads S with tcgen05.ld, online max/sum,
+//               writes bf16 P into 128-byte-swizzled shared memory
+//   O += P V    tcgen05.mma, A = P (K-major), B = V tile (N-major), O in TMEM
+// K/V tiles of 128 keys arrive by TMA (no multicast) into a two-stage ring.
+// gridDim.y key splits each write an unnormalised partial (O, max, sum); a
+// small second kernel merges them.  With one split the kernel normalises and
+// stores bf16 directly.
+#include "common.cuh"
+#include "ptx.cuh"
+
+namespace {
+
+constexpr int D = 128;          // head dim
+constexpr int ROWS = 128;       // query rows per tile (UMMA M)
+constexpr int KEYS = 128;       // keys per tile
+constexpr int HALF_BYTES = ROWS * 128;        // one 64-column half: 128 rows x 128 B
+constexpr int TILE_BYTES = 2 * HALF_BYTES;    // 32 KB
+constexpr int SMEM_Q = 0;
+constexpr int SMEM_K = SMEM_Q + TILE_BYTES;          // 2 stages
+constexpr int SMEM_V = SMEM_K + 2 * TILE_BYTES;      // 2 stages
+constexpr int SMEM_P = SMEM_V + 2 * TILE_BYTES;
+constexpr int SMEM_CTRL = SMEM_P + TILE_BYTES;
+constexpr int SMEM_TOTAL = SMEM_CTRL + 256 + 1024;
+constexpr int TMEM_COLS = 256;  // S: columns [0,128), O: columns [128,256)
+constexpr int NTHREADS = 128;
+
+struct AttnArgs {
+    int tq, hq, hkv, grp, tok_per_tile, num_mtiles;
+    const int32_t* kv_len;
+    int kv_len_add;
+    const int32_t* n_valid;
+    const uint64_t* mask;
+    int mask_k;
+    int window;
+    float scale_log2;
+    bf16* out;
+    int out_ld;
+    float* ws_o;
+    float* ws_ml;
+    int* error;
+};
+
+__global__ void __launch_bounds__(NTHREADS, 1)
+tree_attn_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CUtensorMap tm_k,
+                 const __grid_constant__ CUtensorMap tm_v, const AttnArgs a) {
+    extern __shared__ uint8_t smem_raw[];
+    uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+    uint64_t* bars = reinterpret_cast<uint64_t*>(smem + SMEM_CTRL);
+    uint64_t* q_bar = bars;
+    uint64_t* k_full = bars + 1;  // [2]
+    uint64_t* v_full = bars + 3;  // [2]
+    uint64_t* s_bar = bars + 5;
+    uint64_t* o_bar = bars + 6;
+    uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 7);
+    volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
+
+    const int tid = threadIdx.x;
+    const int warp = tid >> 5;
+    const bool leader = (tid == 0);
+    const int mt = blockIdx.x % a.num_mtiles;
+    const int h = blockIdx.x / a.num_mtiles;  // kv head
+    const int split = blockIdx.y;
+    const int nsplit = gridDim.y;
+
+    if (leader) {
+        ptx::mbar_init(q_bar, 1);
+        for (int i = 0; i < 2; ++i) {
+            ptx::mbar_init(&k_full[i], 1);
+            ptx::mbar_init(&v_full[i], 1);
+        }
+        ptx::mbar_init(s_bar, 1);
+        ptx::mbar_init(o_bar, 1);
+        *abort_flag = 0;
+        ptx::mbar_fence_init();
+        ptx::prefetch_tensormap(&tm_q);
+        ptx::prefetch_tensormap(&tm_k);
+        ptx::prefetch_tensormap(&tm_v);
+    }
+    if (warp == 0) {
+        ptx::tmem_alloc(tmem_slot, TMEM_COLS);
+        ptx::tmem_relinquish();
+    }
+    ptx::tc_fence_before();
+    __syncthreads();
+    ptx::tc_fence_after();
+    const uint32_t tmem_base = *tmem_slot;
+    const uint32_t tmem_s = tmem_base;
+    const uint32_t tmem_o = tmem_base + KEYS;
+    const uint32_t lane_sel = static_cast<uint32_t>(warp * 32) << 16;
+
+    // ---- geometry of this tile
+    const int kv_total = *a.kv_len + a.kv_len_add;
+    const int tq_eff = (a.n_valid != nullptr) ? min(*a.n_valid, a.tq) : a.tq;
+    const int t0 = mt * a.tok_per_tile;
+    const int t = t0 + tid / a.grp;          // query token of this thread's row
+    const int qh = h * a.grp + tid % a.grp;  // query head of this thread's row
+    const bool row_valid = (t < tq_eff);
+    const int causal_base = kv_total - tq_eff;  // token t sees keys < causal_base + t + 1
+    int limit = row_valid ? min(kv_total, causal_base + t + 1) : 0;
+    if (limit < 0) limit = 0;
+    const int mbeg = (a.mask != nullptr) ? (kv_total - a.mask_k) : 0x7fffffff;
+    const uint64_t mword = (a.mask != nullptr && row_valid) ? a.mask[t] : ~0ull;
+    // keys any row of this tile may see: [key_lo, key_hi)
+    const int t_last = min(t0 + a.tok_per_tile, tq_eff) - 1;
+    int key_hi = (t_last >= t0) ? min(kv_total, causal_base + t_last + 1) : 0;
+    if (key_hi < 0) key_hi = 0;
+    int key_lo = 0;
+    if (a.window > 0) {
+        // block-granular sliding window of the draft layer (reference
+        // src/flash_attn/src/flash_blockmask.h:29-33, 128-key blocks)
+        const int q0 = causal_base + t0;
+        const int lo_blk = (q0 + KEYS - 1) / KEYS - a.window / KEYS;
+        if (lo_blk > 0) key_lo = lo_blk * KEYS;
+    }
+    const int kt_lo = key_lo / KEYS;
+    const int kt_hi = (key_hi + KEYS - 1) / KEYS;
+    const int n_kt = max(kt_hi - kt_lo, 0);
+    const int kt_begin = kt_lo + static_cast<int>((static_cast<long long>(n_kt) * split) / nsplit);
+    const int kt_end = kt_lo + static_cast<int>((static_cast<long long>(n_kt) * (split + 1)) / nsplit);
+    const int n_it = kt_end - kt_begin;
+
+    const uint32_t q_addr = ptx::smem_u32(smem + SMEM_Q);
+    const uint32_t p_addr = ptx::smem_u32(smem + SMEM_P);
+    constexpr uint32_t idesc_s = ptx::umma_idesc_bf16(ROWS, KEYS, 0, 0);
+    constexpr uint32_t idesc_o = ptx::umma_idesc_bf16(ROWS, D, 0, 1);
+
+    bool ok = true;
+    if (leader && n_it > 0) {
+        ptx::mbar_arrive_expect_tx(q_bar, TILE_BYTES);
+        ptx::tma_load_3d(smem + SMEM_Q, &tm_q, q_bar, 0, h * a.grp, t0);
+        ptx::tma_load_3d(smem + SMEM_Q + HALF_BYTES, &tm_q, q_bar, 64, h * a.grp, t0);
+        for (int i = 0; i < 2 && i < n_it; ++i) {
+            const int key0 = (kt_begin + i) * KEYS;
+            ptx::mbar_arrive_expect_tx(&k_full[i], TILE_BYTES);
+            ptx::tma_load_2d(smem + SMEM_K + i * TILE_BYTES, &tm_k, &k_full[i], h * D, key0);
+            ptx::tma_load_2d(smem + SMEM_K + i * TILE_BYTES + HALF_BYTES, &tm_k, &k_full[i], h * D + 64, key0);
+            ptx::mbar_arrive_expect_tx(&v_full[i], TILE_BYTES);
+            ptx::tma_load_2d(smem + SMEM_V + i * TILE_BYTES, &tm_v, &v_full[i], h * D, key0);
+            ptx::tma_load_2d(smem + SMEM_V + i * TILE_BYTES + HALF_BYTES, &tm_v, &v_full[i], h * D + 64, key0);
+        }
+    }
+
+    float m_run = -INFINITY;  // running max of raw scores
+    float l_run = 0.f;
+
+    for (int i = 0; i < n_it && ok; ++i) {
+        const int st = i & 1;
+        const uint32_t ph = (i >> 1) & 1;
+        const int key0 = (kt_begin + i) * KEYS;
+
+        if (leader) {
+            bool w = true;
+            if (i == 0) w = ptx::mbar_wait(q_bar, 0, abort_flag);
+            w = w && ptx::mbar_wait(&k_full[st], ph, abort_flag);
+            if (w) {
+                ptx::tc_fence_after();
+                const uint32_t k_addr = ptx::smem_u32(smem + SMEM_K + st * TILE_BYTES);
+#pragma unroll
+                for (int dh = 0; dh < 2; ++dh) {
+#pragma unroll
+                    for (int j = 0; j < 4; ++j) {
+                        const uint64_t da = ptx::umma_desc_sw128(q_addr + dh * HALF_BYTES + j * 32, 16, 1024);
+                        const uint64_t db = ptx::umma_desc_sw128(k_addr + dh * HALF_BYTES + j * 32, 16, 1024);
+                        ptx::umma_ss(tmem_s, da, db, idesc_s, (dh | j) ? 1u : 0u);
+                    }
+                }
+                ptx::umma_commit(s_bar);
+            }
+        }
+        if (!ptx::mbar_wait(s_bar, i & 1, abort_flag)) { ok = false; break; }
+        ptx::tc_fence_after();
+
+        if (leader && i + 2 < n_it) {  // K stage is free again: prefetch two tiles ahead
+            const int keyn = (kt_begin + i + 2) * KEYS;
+            ptx::mbar_arrive_expect_tx(&k_full[st], TILE_BYTES);
+            ptx::tma_load_2d(smem + SMEM_K + st * TILE_BYTES, &tm_k, &k_full[st], h * D, keyn);
+            ptx::tma_load_2d(smem + SMEM_K + st * TILE_BYTES + HALF_BYTES, &tm_k, &k_full[st], h * D + 64, keyn);
+        }
+
+        // ---- pass 1: row maximum over visible keys
+        const bool need_mask = (key0 + KEYS > limit) || (key0 + KEYS > mbeg) || (key0 < key_lo);
+        float m_tile = -INFINITY;
+#pragma unroll 1
+        for (int c0 = 0; c0 < KEYS; c0 += 32) {
+            uint32_t r[32];
+            ptx::tmem_ld32(tmem_s + lane_sel + c0, r);
+            ptx::tmem_wait_ld();
+            if (!need_mask) {
+#pragma unroll
+                for (int c = 0; c < 32; ++c) m_tile = fmaxf(m_tile, __uint_as_float(r[c]));
+            } else {
+#pragma unroll
+                for (int c = 0; c < 32; ++c) {
+                    const int key = key0 + c0 + c;
+                    bool vis = key < limit && key >= key_lo;
+                    if (key >= mbeg) vis = vis && ((mword >> (key - mbeg)) & 1ull);
+                    if (vis) m_tile = fmaxf(m_tile, __uint_as_float(r[c]));
+                }
+            }
+        }
+        const float m_new = fmaxf(m_run, m_tile);
+        const float m_use = (m_new == -INFINITY) ? 0.f : m_new;
+        const float alpha = (m_run == -INFINITY) ? ((l_run == 0.f) ? 1.f : 0.f)
+                                                 : exp2f((m_run - m_use) * a.scale_log2);
+        const bool rescale = (i > 0) && __any_sync(0xffffffffu, alpha != 1.f);
+
+        if (i > 0) {  // P buffer, the other V stage and O are in use until PV(i-1) has finished
+            if (!ptx::mbar_wait(o_bar, (i - 1) & 1, abort_flag)) { ok = false; break; }
+            ptx::tc_fence_after();
+            if (leader && i + 1 < n_it) {
+                const int sv = (i + 1) & 1;
+                const int keyn = (kt_begin + i + 1) * KEYS;
+                ptx::mbar_arrive_expect_tx(&v_full[sv], TILE_BYTES);
+                ptx::tma_load_2d(smem + SMEM_V + sv * TILE_BYTES, &tm_v, &v_full[sv], h * D, keyn);
+                ptx::tma_load_2d(smem + SMEM_V + sv * TILE_BYTES + HALF_BYTES, &tm_v, &v_full[sv], h * D + 64, keyn);
+            }
+        }
+        if (rescale) {
+#pragma unroll 1
+            for (int c0 = 0; c0 < D; c0 += 32) {
+                uint32_t r[32];
+                ptx::tmem_ld32(tmem_o + lane_sel + c0, r);
+                ptx::tmem_wait_ld();
+#pragma unroll
+                for (int c = 0; c < 32; ++c) r[c] = __float_as_uint(__uint_as_float(r[c]) * alpha);
+                ptx::tmem_st32(tmem_o + lane_sel + c0, r);
+            }
+            ptx::tmem_wait_st();
+        }
+        l_run *= alpha;
+        m_run = m_new;
+
+        // ---- pass 2: P = exp2((s - m) * scale), bf16, into swizzled smem
+        float l_add = 0.f;
+        const float m_off = m_use * a.scale_log2;
+        uint8_t* p_row = smem + SMEM_P + tid * 128;
+#pragma unroll 1
+        for (int c0 = 0; c0 < KEYS; c0 += 32) {
+            uint32_t r[32];
+            ptx::tmem_ld32(tmem_s + lane_sel + c0, r);
+            ptx::tmem_wait_ld();
+            float p[32];
+#pragma unroll
+            for (int c = 0; c < 32; ++c) {
+                float v = exp2f(__uint_as_float(r[c]) * a.scale_log2 - m_off);
+                if (need_mask) {
+                    const int key = key0 + c0 + c;
+                    bool vis = key < limit && key >= key_lo;
+                    if (key >= mbeg) vis = vis && ((mword >> (key - mbeg)) & 1ull);
+                    if (!vis) v = 0.f;
+                }
+                p[c] = v;
+                l_add += v;
+            }
+            // 32 keys = 4 chunks of 16 B inside the 64-key half (c0 / 64)
+            uint8_t* half = p_row + (c0 >> 6) * HALF_BYTES;
+#pragma unroll
+            for (int ch = 0; ch < 4; ++ch) {
+                uint4 pk;
+                uint32_t* w = reinterpret_cast<uint32_t*>(&pk);
+#pragma unroll
+                for (int e = 0; e < 4; ++e) {
+                    __nv_bfloat162 b2 = __floats2bfloat162_rn(p[ch * 8 + e * 2], p[ch * 8 + e * 2 + 1]);
+                    w[e] = *reinterpret_cast<uint32_t*>(&b2);
+                }
+                const int chunk = ((c0 & 63) >> 3) + ch;  // 16-byte chunk index within the 128-byte row
+                *reinterpret_cast<uint4*>(half + ((chunk ^ (tid & 7)) << 4)) = pk;
+            }
+        }
+        l_run += l_add;
+
+        ptx::fence_proxy_async_smem();
+        ptx::tc_fence_before();
+        __syncthreads();
+
+        if (leader) {
+            ptx::tc_fence_after();
+            if (ptx::mbar_wait(&v_full[st], ph, abort_flag)) {
+                ptx::tc_fence_after();
+                const uint32_t v_addr = ptx::smem_u32(smem + SMEM_V + st * TILE_BYTES);
+#pragma unroll
+                for (int kk = 0; kk < KEYS / 16; ++kk) {
+                    // A: P, K-major: 64-key half (kk / 4), 32 B per 16-key step inside it
+                    const uint64_t da =
+                        ptx::umma_desc_sw128(p_addr + (kk >> 2) * HALF_BYTES + (kk & 3) * 32, 16, 1024);
+                    // B: V, N-major: 16 key rows of 128 B per step; 64-wide d halves HALF_BYTES apart
+                    const uint64_t db = ptx::umma_desc_sw128(v_addr + kk * 16 * 128, HALF_BYTES, 1024);
+                    ptx::umma_ss(tmem_o, da, db, idesc_o, (i > 0 || kk > 0) ? 1u : 0u);
+                }
+                ptx::umma_commit(o_bar);
+            }
+        }
+    }
+
+    if (ok && n_it > 0) {
+        if (!ptx::mbar_wait(o_bar, (n_it - 1) & 1, abort_flag)) ok = false;
+        ptx::tc_fence_after();
+    }
+
+    // ---- write-out.  TMEM reads are warp-collective, so every thread runs them
+    // and only the global stores depend on whether the row exists.
+    if (ok) {
+        const bool store = (t < a.tq);
+        const size_t grow = static_cast<size_t>(store ? t : 0) * a.hq + qh;
+        const float inv = (nsplit == 1) ? ((l_run > 0.f) ? 1.f / l_run : 0.f) : 1.f;
+        bf16* dst_b = a.out + static_cast<size_t>(store ? t : 0) * a.out_ld + qh * D;
+        float* dst_f = (nsplit > 1) ? a.ws_o + (static_cast<size_t>(split) * a.tq * a.hq + grow) * D : nullptr;
+#pragma unroll 1
+        for (int c0 = 0; c0 < D; c0 += 32) {
+            uint32_t r[32];
+            if (n_it > 0) {  // uniform across the CTA
+                ptx::tmem_ld32(tmem_o + lane_sel + c0, r);
+                ptx::tmem_wait_ld();
+            } else {
+#pragma unroll
+                for (int c = 0; c < 32; ++c) r[c] = 0;
+            }
+            if (store) {
+                if (nsplit == 1) {
+#pragma unroll
+                    for (int c = 0; c < 32; c += 8) {
+                        uint4 pk;
+                        uint32_t* w = reinterpret_cast<uint32_t*>(&pk);
+#pragma unroll
+                        for (int e = 0; e < 4; ++e) {
+                            __nv_bfloat162 b2 = __floats2bfloat162_rn(__uint_as_float(r[c + e * 2]) * inv,
+                                                                      __uint_as_float(r[c + e * 2 + 1]) * inv);
+                            w[e] = *reinterpret_cast<uint32_t*>(&b2);
+                        }
+                        *reinterpret_cast<uint4*>(dst_b + c0 + c) = pk;
+                    }
+                } else {
+#pragma unroll
+                    for (int c = 0; c < 32; c += 4) {
+                        *reinterpret_cast<uint4*>(dst_f + c0 + c) = make_uint4(r[c], r[c + 1], r[c + 2], r[c + 3]);
+                    }
+                }
+            }
+        }
+        if (store && nsplit > 1) {
+            float* ml = a.ws_ml + (static_cast<size_t>(split) * a.tq * a.hq + grow) * 2;
+            ml[0] = m_run;
+            ml[1] = l_run;
+        }
+    }
+
+    ptx::tc_fence_before();
+    __syncthreads();
+    if (warp == 0) {
+        ptx::tc_fence_after();
+        ptx::tmem_dealloc(tmem_base, TMEM_COLS);
+    }
+    if (leader && *abort_flag) atomicOr(a.error, ERR_ATTN_TIMEOUT);
+}
+
+// Merge split partials: out = sum_s 2^((m_s - M) c) O_s / sum_s 2^((m_s - M) c) l_s.
+__global__ void attn_combine_kernel(const float* __restrict__ ws_o, const float* __restrict__ ws_ml, int nsplit,
+                                    int rows, int hq, float scale_log2, bf16* __restrict__ out, int out_ld) {
+    const int row = blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
+    const int lane = threadIdx.x & 31;
+    if (row >= rows) return;
+    float M = -INFINITY;
+    for (int s = 0; s < nsplit; ++s) M = fmaxf(M, ws_ml[(static_cast<size_t>(s) * rows + row) * 2]);
+    float acc[4] = {0.f, 0.f, 0.f, 0.f};
+    float l = 0.f;
+    for (int s = 0; s < nsplit; ++s) {
+        const float* ml = ws_ml + (static_cast<size_t>(s) * rows + row) * 2;
+        const float ms = ml[0];
+        if (ms == -INFINITY) continue;
+        const float w = exp2f((ms - M) * scale_log2);
+        l += w * ml[1];
+        const float4 o = *reinterpret_cast<const float4*>(ws_o + (static_cast<size_t>(s) * rows + row) * D + lane * 4);
+        acc[0] += w * o.x; acc[1] += w * o.y; acc[2] += w * o.z; acc[3] += w * o.w;
+    }
+    const float inv = (l > 0.f) ? 1.f / l : 0.f;
+    const int t = row / hq, qh = row - t * hq;
+    __nv_bfloat162 a0 = __floats2bfloat162_rn(acc[0] * inv, acc[1] * inv);
+    __nv_bfloat162 a1 = __floats2bfloat162_rn(acc[2] * inv, acc[3] * inv);
+    uint2 pk;
+    pk.x = *reinterpret_cast<uint32_t*>(&a0);
+    pk.y = *reinterpret_cast<uint32_t*>(&a1);
+    *reinterpret_cast<uint2*>(out + static_cast<size_t>(t) * out_ld + qh * D + lane * 4) = pk;
+}
+
+}  // namespace
+
+size_t attn_workspace_bytes(int tq, int hq, int d, int splits) {
+    return static_cast<size_t>(splits) * tq * hq * (d + 2) * sizeof(float);
+}
+
+AttnPlan make_attn_plan(const bf16* q, int q_ld_tokens, const bf16* k_cache, const bf16* v_cache, int budget, int tq,
+                        int hq, int hkv, int d, int splits, bf16* out, int out_ld, float* ws_o, float* ws_ml) {
+    CPM_REQUIRE(d == D, "attention: head_dim must be 128");
+    CPM_REQUIRE(hq % hkv == 0, "attention: query heads must be a multiple of kv heads");
+    const int grp = hq / hkv;
+    CPM_REQUIRE(grp <= ROWS && ROWS % grp == 0, "attention: unsupported GQA ratio");
+    CPM_REQUIRE(tq >= 1 && splits >= 1, "attention: empty problem");
+    AttnPlan p;
+    p.tq = tq; p.hq = hq; p.hkv = hkv; p.d = d; p.splits = splits;
+    p.out = out; p.out_ld = out_ld; p.ws_o = ws_o; p.ws_ml = ws_ml;
+    p.scale = 1.0f / sqrtf(static_cast<float>(d));
+    p.tm_q = make_tmap_3d(q, d, hq, tq, static_cast<uint64_t>(d) * 2, static_cast<uint64_t>(q_ld_tokens) * 2, 64, grp,
+                          ROWS / grp);
+    p.tm_k = make_tmap_2d(k_cache, static_cast<uint64_t>(hkv) * d, budget, static_cast<uint64_t>(hkv) * d * 2, 64, KEYS);
+    p.tm_v = make_tmap_2d(v_cache, static_cast<uint64_t>(hkv) * d, budget, static_cast<uint64_t>(hkv) * d * 2, 64, KEYS);
+    return p;
+}
+
+void launch_tree_attention(const AttnPlan& p, cudaStream_t s) {
+    static bool configured = false;
+    if (!configured) {
+        CUDA_CHECK(cudaFuncSetAttribute(tree_attn_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_TOTAL));
+        configured = true;
+    }
+    AttnArgs a;
+    a.tq = p.tq; a.hq = p.hq; a.hkv = p.hkv;
+    a.grp = p.hq / p.hkv;
+    a.tok_per_tile = ROWS / a.grp;
+    a.num_mtiles = ceil_div(p.tq, a.tok_per_tile);
+    a.kv_len = p.kv_len; a.kv_len_add = p.kv_len_add;
+    a.n_valid = p.n_valid;
+    a.mask = p.mask; a.mask_k = p.mask_k;
+    a.window = p.window;
+    a.scale_log2 = p.scale * 1.4426950408889634f;
+    a.out = p.out; a.out_ld = p.out_ld;
+    a.ws_o = p.ws_o; a.ws_ml = p.ws_ml;
+    a.error = runtime().d_error;
+    CPM_REQUIRE(p.splits == 1 || (p.ws_o != nullptr && p.ws_ml != nullptr), "attention: split-KV needs a workspace");
+    dim3 grid(a.num_mtiles * p.hkv, p.splits);
+    tree_attn_kernel<<<grid, NTHREADS, SMEM_TOTAL, s>>>(p.tm_q, p.tm_k, p.tm_v, a);
+    CUDA_CHECK(cudaGetLastError());
+    runtime().launches++;
+    if (p.splits > 1) {
+        const int rows = p.tq * p.hq;
+        attn_combine_kernel<<<ceil_div(rows, 4), 128, 0, s>>>(p.ws_o, p.ws_ml, p.splits, rows, p.hq, a.scale_log2, p.out,
+                                                             p.out_ld);
+        CUDA_CHECK(cudaGetLastError());
+    runtime().launches++;
+    }
+}

@@ -1,0 +1,196 @@
+/* C ABI of libcpmcu_b200.so: the speculative-decoding hot path of CPM.cu
+ * (EAGLE draft loop -> tree build -> tree-verify forward -> greedy acceptance
+ * with KV compaction) as sm_100a CUDA.
+ *
+ * Part 1 declares, one for one, the functions the reference binds into its
+ * `cpmcu.C` Python module (src/entry.cu:510-535).  Arguments keep the
+ * reference's order and meaning; pointers that the reference passes as
+ * uintptr_t are plain pointers here.  Unless stated otherwise pointers are
+ * DEVICE memory.  Functions that return void in the reference return 0 on
+ * success and -1 on failure here (message via cpmcu_last_error()).
+ *
+ * Part 2 is the fused step (one CUDA graph per speculative step, no host
+ * round trips inside the step).  Part 3 exposes the individual kernels so each
+ * can be checked in isolation against the CPU oracle.
+ *
+ * bf16 values are passed as void* (16-bit storage, row-major).
+ * There is no CPU path: every call fails with an error if no sm_100 device is
+ * visible.
+ */
+#ifndef CPMCU_B200_H
+#define CPMCU_B200_H
+
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+/* ------------------------------------------------------------------ part 1 */
+
+/* Message of the last failure on the calling thread ("" if none). */
+const char* cpmcu_last_error(void);
+
+/* reference: init_base_model, src/entry.cu:100-136.  torch_dtype: 1 = bf16
+ * (0 = fp16 is rejected: this library computes in bf16 only). */
+int cpmcu_init_base_model(float memory_limit, int vocab_size, int num_hidden_layers, int hidden_size,
+                          int intermediate_size, int num_attention_heads, int num_key_value_heads, int head_dim,
+                          float rms_norm_eps, int torch_dtype, int chunk_length, float scale_embed,
+                          float scale_lmhead, float scale_residual);
+
+/* reference: init_minicpm4_model, src/entry.cu:138-184 (InfLLM-v2 sparse target).
+ * Accepted only when the sparse path can never trigger (sparse_switch beyond
+ * the context budget); otherwise fails: block-sparse attention is not built. */
+int cpmcu_init_minicpm4_model(float memory_limit, int vocab_size, int num_hidden_layers, int hidden_size,
+                              int intermediate_size, int num_attention_heads, int num_key_value_heads,
+                              int head_dim, float rms_norm_eps, int torch_dtype, int chunk_length,
+                              float scale_embed, float scale_lmhead, float scale_residual, int sink_window_size,
+                              int block_window_size, int sparse_topk_k, int sparse_switch, int apply_compress_lse);
+
+/* reference: init_w4a16_gptq_marlin_base_model, src/entry.cu:186-225, and
+ * init_w4a16_gptq_marlin_minicpm4_model, :227-275.  Not built: always fail. */
+int cpmcu_init_w4a16_gptq_marlin_base_model(float memory_limit, int vocab_size, int num_hidden_layers,
+                                            int hidden_size, int intermediate_size, int num_attention_heads,
+                                            int num_key_value_heads, int head_dim, float rms_norm_eps,
+                                            int group_size, int torch_dtype, int chunk_length, float scale_embed,
+                                            float scale_lmhead, float scale_residual);
+int cpmcu_init_w4a16_gptq_marlin_minicpm4_model(float memory_limit, int vocab_size, int num_hidden_layers,
+                                                int hidden_size, int intermediate_size, int num_attention_heads,
+                                                int num_key_value_heads, int head_dim, float rms_norm_eps,
+                                                int group_size, int torch_dtype, int chunk_length,
+                                                float scale_embed, float scale_lmhead, float scale_residual,
+                                                int sink_window_size, int block_window_size, int sparse_topk_k,
+                                                int sparse_switch, int apply_compress_lse);
+
+/* reference: init_eagle_model, src/entry.cu:278-301 (plain EAGLE head: no input
+ * norms, no attention norm in the draft layer, fc bias, full-vocabulary head). */
+int cpmcu_init_eagle_model(int num_layers, int num_iter, int topk_per_iter, int tree_size, int torch_dtype);
+
+/* reference: init_minicpm4_eagle_model, src/entry.cu:303-341 (optional input
+ * norms / attention norm, FR-Spec reduced draft vocabulary, draft sliding
+ * window, residual scale).  apply_eagle_quant must be 0. */
+int cpmcu_init_minicpm4_eagle_model(int num_layers, int num_iter, int topk_per_iter, int tree_size, int torch_dtype,
+                                    int apply_eagle_quant, int group_size, int eagle_window_size,
+                                    int frspec_vocab_size, float residual_scale, int use_input_norm,
+                                    int use_attn_norm);
+
+/* reference: the three spec / hierarchical initialisers, src/entry.cu:344-459.
+ * Out of scope for this library: always fail. */
+int cpmcu_init_w4a16_gm_spec_w4a16_gm_model(void);
+int cpmcu_init_hier_eagle_w4a16_gm_spec_w4a16_gm_model(void);
+int cpmcu_init_hier_eagle_w4a16_gm_rot_spec_w4a16_gm_model(void);
+
+/* reference: init_storage, src/entry.cu:462.  Allocates the device pool and
+ * returns the number of tokens the KV caches hold, or -1. */
+int cpmcu_init_storage(void);
+
+/* reference: load_model, src/entry.cu:466.  `param` may be host or device
+ * memory holding the tensor in the model dtype (fp32 for *rotary_emb.inv_freq,
+ * int32 for eagle.token_id_remap).  Names as in the reference
+ * (src/model/model.cuh:116-137, src/model/minicpm4/minicpm4_eagle.cuh:187-221). */
+int cpmcu_load_model(const char* name, const void* param);
+
+/* reference: prefill, src/entry.cu:470.  `output` receives the logits of the
+ * last token (row 0 of a [>=1, vocab] bf16 buffer). */
+int cpmcu_prefill(int input_length, int history_length, const int32_t* input, const int32_t* position_ids,
+                  void* output);
+
+/* reference: decode, src/entry.cu:474-496.  *cache_length must already include
+ * input_length (reference cpmcu/llm.py:263-283); mask_2d may be NULL (causal).
+ * `output` is [input_length, vocab] bf16.  padded_length and cuda_graph are
+ * accepted for compatibility and ignored. */
+int cpmcu_decode(int input_length, int padded_length, const int32_t* input, const int32_t* position_ids,
+                 const int32_t* cache_length, const uint64_t* mask_2d, void* output, int cuda_graph);
+
+/* reference: draft, src/entry.cu:498.  Reads tree_draft_ids[0] (root) and
+ * *cache_length; writes tree_draft_ids[1:], positions, masks, parents. */
+int cpmcu_draft(int32_t* tree_draft_ids, int32_t* tree_position_ids, const int32_t* cache_length,
+                uint64_t* attn_mask, int32_t* tree_parent);
+
+/* reference: verify_and_fix, src/entry.cu:502.  Returns the accept length n
+ * (>= 1) or -1; pred[0:n] then holds the emitted tokens. */
+int cpmcu_verify_and_fix(int num_tokens, int32_t* pred, const int32_t* gt, const int32_t* position_ids,
+                         const int32_t* cache_length, const uint64_t* attn_mask, const int32_t* tree_parent);
+
+/* reference: print_perf_summary, src/entry.cu:506.  Prints launch counts. */
+void cpmcu_print_perf_summary(void);
+
+/* ------------------------------------------------------------------ part 2 */
+
+/* Start fused generation after prefill: prefix_length tokens are cached and
+ * root_token is the first generated token.  No counterpart in the reference
+ * (its loop lives in cpmcu/speculative/tree_drafter.py:215-252). */
+int cpmcu_begin_generation(int prefix_length, int32_t root_token);
+
+/* One speculative step on engine-owned buffers.  Writes the n emitted tokens
+ * to out_tokens (HOST memory, at most max_tokens) and returns n, or -1. */
+int cpmcu_spec_step(int32_t* out_tokens, int max_tokens);
+
+/* Device time of the last cpmcu_spec_step in milliseconds (CUDA events). */
+double cpmcu_last_step_ms(void);
+/* Kernels in one captured step / launched by this library so far. */
+long cpmcu_launches_per_step(void);
+long cpmcu_total_launches(void);
+/* Copies the engine-owned tree of the last step to HOST arrays of 64 entries
+ * (any pointer may be NULL). */
+int cpmcu_get_tree(int32_t* ids, int32_t* pos, int32_t* parent, int32_t* gt, uint64_t* mask, int32_t* state);
+/* Drops the current model (frees the device pool). */
+void cpmcu_release(void);
+
+/* ------------------------------------------------------------------ part 3 */
+
+/* Y[M,N] = X[M,K] W[N,K]^T (+ bias[N]).  reference: linear<T>,
+ * src/model/linear.cuh:8-37 (cuBLAS).  K % 64 == 0.  grid_limit <= 0 uses one
+ * CTA per SM; smaller values force split-K pieces (tests). */
+int cpmcu_linear_bf16(const void* x, const void* w, const void* bias, void* y, int M, int N, int K,
+                      int grid_limit);
+
+/* reference: mha_fwd_kvcache, src/flash_attn/flash_api.hpp:292-392.
+ * q: token t, head h at q + t*q_ld + h*128; caches [budget, hkv*128]; keys
+ * visible = *kv_len + kv_len_add; n_valid (device, may be NULL) = number of
+ * real query rows; mask (may be NULL) covers the last mask_k keys. */
+int cpmcu_tree_attention(const void* q, int q_ld, const void* k_cache, const void* v_cache, int budget, int tq,
+                         int hq, int hkv, const int32_t* kv_len, int kv_len_add, const int32_t* n_valid,
+                         const uint64_t* mask, int mask_k, int window, int splits, void* out, int out_ld);
+
+/* reference: rms_norm / add_and_rms_norm, src/model/norm.cuh:8-99.
+ * delta may be NULL; otherwise x += round(delta * delta_scale) in place first. */
+int cpmcu_rms_norm(void* x, const void* delta, float delta_scale, const void* weight, void* y, int rows, int dim,
+                   float eps);
+
+/* reference: rotary_embedding + copy_to_kvcache, src/model/rotary.cuh:7-34,
+ * src/model/attn.cuh:14-21.  qkv [rows, (hq+2hkv)*128] is rotated in place
+ * (q part); k (rotated) and v go to cache row *kv_len + kv_off + r. */
+int cpmcu_rope_append(void* qkv, int rows, int hq, int hkv, const float* inv_freq, const int32_t* pos,
+                      void* k_cache, void* v_cache, const int32_t* kv_len, int kv_off);
+
+/* reference: gated_silu_interleaved, src/model/activation.cuh:7-18. */
+int cpmcu_silu_gate(const void* gate_up, void* out, int rows, int inter);
+
+/* Row argmax (lowest index wins ties); reference: torch argmax in
+ * cpmcu/speculative/tree_drafter.py:233. */
+int cpmcu_argmax(const void* logits, int rows, int vocab, int32_t* out);
+
+/* Draft tree from given logits: level 0 uses row 0 of `logits`, level d >= 1
+ * rows 1 + (d-1)*k .. (k rows).  logits: [1 + (num_iter-1)*k, vocab] bf16.
+ * Runs log-softmax, top-k, frontier expansion and the final tree build exactly
+ * as the draft loop does (reference src/model/eagle.cuh:436-498, 188-218).
+ * Outputs (device): tree ids[1:], positions, masks, parents (tree_size
+ * entries each; ids[0] is left untouched) and, if not NULL, the candidate
+ * history tried_val (bf16) / tried_pos / tried_parent. */
+int cpmcu_draft_tree_from_logits(const void* logits, int vocab, int k, int num_iter, int tree_size,
+                                 const int32_t* token_id_remap, const int32_t* cache_length, int32_t* tree_ids,
+                                 int32_t* tree_pos, uint64_t* tree_mask, int32_t* tree_parent, void* tried_val,
+                                 int32_t* tried_pos, int32_t* tried_parent);
+
+/* reference: verify_kernel + fix_kvcache_kernel_1/2, src/model/tree_drafter.cuh:5-101.
+ * caches: device array of num_caches row-major [rows, kv_dim] bf16 buffers.
+ * result (device, 18 ints): [0] accept length, [1] best node, [2..] path. */
+int cpmcu_verify_and_compact(int tree_size, int32_t* pred, const int32_t* gt, const int32_t* position_ids,
+                             const int32_t* cache_length, const uint64_t* attn_mask, const int32_t* tree_parent,
+                             void* const* caches, int num_caches, int kv_dim, int max_accept, int32_t* result);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* CPMCU_B200_H */
