@@ -203,6 +203,7 @@ linear_umma_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_consta
 
             if (!ptx::mbar_wait(&acc_full[acc], acc_phase, abort_flag)) break;
             ptx::tc_fence_after();
+            __syncwarp();  // TMEM loads below are warp-collective
             const uint32_t t_addr = tmem_base + (static_cast<uint32_t>(q * 32) << 16) + acc * MT;
 #pragma unroll 1
             for (int c0 = 0; c0 < MT; c0 += 16) {

@@ -183,6 +183,7 @@ tree_attn_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant
         }
         if (!ptx::mbar_wait(s_bar, i & 1, abort_flag)) { ok = false; break; }
         ptx::tc_fence_after();
+        __syncwarp();  // TMEM loads below are warp-collective
 
         if (leader && i + 2 < n_it) {  // K stage is free again: prefetch two tiles ahead
             const int keyn = (kt_begin + i + 2) * KEYS;
@@ -221,6 +222,7 @@ tree_attn_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant
         if (i > 0) {  // P buffer, the other V stage and O are in use until PV(i-1) has finished
             if (!ptx::mbar_wait(o_bar, (i - 1) & 1, abort_flag)) { ok = false; break; }
             ptx::tc_fence_after();
+            __syncwarp();
             if (leader && i + 1 < n_it) {
                 const int sv = (i + 1) & 1;
                 const int keyn = (kt_begin + i + 1) * KEYS;
@@ -243,6 +245,7 @@ tree_attn_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant
         }
         l_run *= alpha;
         m_run = m_new;
+        __syncwarp();
 
         // ---- pass 2: P = exp2((s - m) * scale), bf16, into swizzled smem
         float l_add = 0.f;
@@ -310,6 +313,7 @@ tree_attn_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant
         if (!ptx::mbar_wait(o_bar, (n_it - 1) & 1, abort_flag)) ok = false;
         ptx::tc_fence_after();
     }
+    ok = __all_sync(0xffffffffu, ok);  // keep each warp together for the collective TMEM reads
 
     // ---- write-out.  TMEM reads are warp-collective, so every thread runs them
     // and only the global stores depend on whether the row exists.
