@@ -1,0 +1,361 @@
+"""Benchmark of the speculative-decoding step (draft -> tree -> verify -> accept).
+
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--impl ours|reference]
+
+Workload (BASELINE.json configs[1]): MiniCPM4-8B-shaped bf16 target (32 layers,
+hidden 4096, 32 q / 2 kv heads, head_dim 128, FFN 16384, vocab 73448), random
+N(0, 0.02) weights (seed 1), 1-layer EAGLE drafter copied from the target's last
+layer, tree of 60 nodes (6 iterations, top-k 10), a 4096-token Zipf(1.1) prompt,
+batch 1, greedy.  A "step" is one speculative step.  Synthetic data throughout.
+
+Ours: `value` = tokens emitted by the K timed steps / their summed device time
+(CUDA events around each captured step, inputs resident in HBM); `e2e` = the
+same K steps timed by the host clock around the public `C.spec_step()` calls,
+which includes the per-step device->host read of the accepted tokens.  With
+N > 1 every rank runs an independent replica on its own GPU (no collective on
+the data path); value = all ranks' tokens / the slowest rank's time.
+
+--impl reference: the reference has no CPU implementation of this path and its
+CUDA build is not part of this repository, so this arm times the CPU oracle
+(oracle/, a restatement of the reference's step) on the host cores over a
+bounded sample and reports the same metric.
+"""
+import argparse
+import json
+import os
+import statistics
+import subprocess
+import sys
+import threading
+import time
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+for p in (ROOT, os.path.join(ROOT, "cpm.cu_b200")):
+    if p not in sys.path:
+        sys.path.insert(0, p)
+
+CFG = dict(vocab=73448, layers=32, hidden=4096, inter=16384, hq=32, hkv=2, head_dim=128, eps=1e-5, rope_theta=10000.0)
+TREE = dict(num_iter=6, topk=10, tree_size=60)
+PROMPT_LEN = 4096
+METRIC = "spec_decode_tokens_per_s"
+UNIT = "tokens/s"
+
+
+def zipf_prompt(n, vocab, seed, s=1.1):
+    import numpy as np
+    rng = np.random.default_rng(seed)
+    p = 1.0 / np.arange(1, vocab + 1, dtype=np.float64) ** s
+    p /= p.sum()
+    return rng.choice(vocab, size=n, p=p).astype(np.int32)
+
+
+def algorithmic_bytes():
+    """Weight bytes one speculative step has to stream (bf16), per SURVEY 8(d) arithmetic:
+    every target linear once (M = 60), the draft fc + layer + LM head six times."""
+    H, I, V = CFG["hidden"], CFG["inter"], CFG["vocab"]
+    qkv = (CFG["hq"] + 2 * CFG["hkv"]) * CFG["head_dim"]
+    layer = qkv * H + H * CFG["hq"] * CFG["head_dim"] + 2 * I * H + H * I
+    target = (CFG["layers"] * layer + V * H) * 2
+    draft_pass = (2 * H * H + layer + V * H) * 2
+    return target, TREE["num_iter"] * draft_pass
+
+
+class ClockSampler(threading.Thread):
+    """Samples nvidia-smi clocks and throttle reasons while the timed region runs."""
+
+    def __init__(self, index):
+        super().__init__(daemon=True)
+        self.index, self.samples, self.stop_flag = index, [], threading.Event()
+
+    def run(self):
+        q = ("clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.hw_slowdown,"
+             "clocks_event_reasons.hw_thermal_slowdown,clocks_event_reasons.sw_thermal_slowdown,"
+             "clocks_event_reasons.sw_power_cap")
+        while not self.stop_flag.is_set():
+            try:
+                out = subprocess.run(["nvidia-smi", "-i", str(self.index), "--query-gpu=" + q,
+                                      "--format=csv,noheader,nounits"], capture_output=True, text=True, timeout=5).stdout
+                parts = [x.strip() for x in out.strip().split(",")]
+                if len(parts) >= 7:
+                    self.samples.append(parts)
+            except Exception:
+                pass
+            self.stop_flag.wait(0.1)
+
+    def summary(self):
+        if not self.samples:
+            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": [], "samples": 0}
+        sm = [float(s[0]) for s in self.samples if s[0].replace(".", "").isdigit()]
+        mx = [float(s[1]) for s in self.samples if s[1].replace(".", "").isdigit()]
+        names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
+        reasons = [n for i, n in enumerate(names) if any(s[3 + i].lower().startswith("active") for s in self.samples)]
+        return {"sm_mhz": statistics.median(sm) if sm else None, "sm_max_mhz": max(mx) if mx else None,
+                "reasons": reasons, "samples": len(self.samples)}
+
+
+# ---------------------------------------------------------------------------- ours
+def build_model(device_index, seed=1):
+    """Random-init config-2 model, generated on the GPU tensor by tensor and loaded through the
+    reference-shaped Python classes (C.load_model accepts device pointers)."""
+    import types
+
+    import torch
+    from cpmcu.speculative.eagle import LLM_with_eagle
+    torch.cuda.set_device(device_index)
+    os.environ.setdefault("CPMCU_MAX_TOKENS", "8192")
+    hf = types.SimpleNamespace(vocab_size=CFG["vocab"], num_hidden_layers=CFG["layers"], hidden_size=CFG["hidden"],
+                               intermediate_size=CFG["inter"], num_attention_heads=CFG["hq"],
+                               num_key_value_heads=CFG["hkv"], head_dim=CFG["head_dim"], rms_norm_eps=CFG["eps"],
+                               rope_theta=CFG["rope_theta"], torch_dtype=torch.bfloat16)
+    llm = LLM_with_eagle(None, None, num_iter=TREE["num_iter"], topk_per_iter=TREE["topk"],
+                         tree_size=TREE["tree_size"], eagle_config={"num_hidden_layers": 1}, config=hf,
+                         dtype=torch.bfloat16, chunk_length=PROMPT_LEN, memory_limit=0.8, fused_step=True)
+    llm.init_storage()
+    g = torch.Generator(device="cuda").manual_seed(seed)
+    H, I, d = CFG["hidden"], CFG["inter"], CFG["head_dim"]
+
+    def rnd(*shape):
+        return (torch.randn(*shape, device="cuda", generator=g, dtype=torch.float32) * 0.02).to(torch.bfloat16)
+
+    ones = torch.ones(H, device="cuda", dtype=torch.bfloat16)
+    llm._load("model.embed_tokens.weight", rnd(CFG["vocab"], H))
+    llm._load("lm_head.weight", rnd(CFG["vocab"], H))
+    llm._load("model.norm.weight", ones)
+    last = {}
+    for l in range(CFG["layers"]):
+        p = "model.layers.%d." % l
+        tensors = {"self_attn.q_proj": rnd(CFG["hq"] * d, H), "self_attn.k_proj": rnd(CFG["hkv"] * d, H),
+                   "self_attn.v_proj": rnd(CFG["hkv"] * d, H), "self_attn.o_proj": rnd(H, CFG["hq"] * d),
+                   "mlp.gate_proj": rnd(I, H), "mlp.up_proj": rnd(I, H), "mlp.down_proj": rnd(H, I),
+                   "input_layernorm": ones, "post_attention_layernorm": ones}
+        for name, t in tensors.items():
+            llm._load(p + name + ".weight", t)
+        if l == CFG["layers"] - 1:
+            last = tensors
+    # drafter: the target's last layer; fc passes the hidden state through (fc1 = 0, fc2 = I, bias 0)
+    for name, t in last.items():
+        llm._load("layers.0." + name + ".weight", t, cls="eagle")
+    fc = torch.cat([torch.zeros(H, H, device="cuda"), torch.eye(H, device="cuda")], dim=1).to(torch.bfloat16)
+    llm._load("fc.weight", fc, cls="eagle")
+    llm._load("fc.bias", torch.zeros(H, device="cuda", dtype=torch.bfloat16), cls="eagle")
+    llm._load("model.rotary_emb.inv_freq", llm._rope_inv_freq(), dtype=torch.float32)
+    del last, fc
+    torch.cuda.empty_cache()
+    return llm
+
+
+def run_ours(args):
+    import torch
+    import cpmcu.C as C
+    rank = int(os.environ.get("RANK", "0"))
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    local = int(os.environ.get("LOCAL_RANK", "0"))
+    dist = None
+    if world > 1:
+        import torch.distributed as dist
+        torch.cuda.set_device(local)
+        dist.init_process_group("nccl", device_id=torch.device("cuda", local))
+    C.load()  # fails loudly if the CUDA library is missing
+    llm = build_model(local, seed=1)
+    prompt = torch.tensor(zipf_prompt(PROMPT_LEN, CFG["vocab"], 100 + rank), device="cuda")
+    pos = torch.arange(PROMPT_LEN, dtype=torch.int32, device="cuda")
+    torch.cuda.synchronize()
+    t0 = time.time()
+    logits = llm.prefill(prompt, pos)
+    torch.cuda.synchronize()
+    prefill_s = time.time() - t0
+    root = int(logits[0].argmax())
+    C.begin_generation(PROMPT_LEN, root)
+    for _ in range(args.warmup):
+        C.spec_step(16)
+
+    def barrier():
+        if dist is not None:
+            dist.barrier()
+        torch.cuda.synchronize()
+
+    sampler = ClockSampler(local)
+    sampler.start()
+    barrier()
+    wall0 = time.perf_counter()
+    tokens, dev_ms, accept = 0, [], []
+    for _ in range(args.steps):
+        out = C.spec_step(16)
+        tokens += len(out)
+        accept.append(len(out))
+        dev_ms.append(C.last_step_ms())
+    torch.cuda.synchronize()
+    wall = time.perf_counter() - wall0
+    barrier()
+    sampler.stop_flag.set()
+    sampler.join(timeout=2)
+    launches = C.launches_per_step()
+
+    # per-class device time of a few uncaptured steps (CUDA events around every launch)
+    lin_ms, att_ms, lin_n, prof_total = [], [], 0, []
+    for _ in range(3):
+        cls, total = C.profile_step()
+        lin_ms.append(cls["linear"][0])
+        att_ms.append(cls["attention"][0])
+        lin_n = cls["linear"][1]
+        prof_total.append(total)
+
+    dev_s = sum(dev_ms) / 1e3
+    stats = torch.tensor([float(tokens), dev_s, wall], dtype=torch.float64, device="cuda")
+    if dist is not None:
+        tok_all = stats[0:1].clone()
+        dist.all_reduce(tok_all, op=dist.ReduceOp.SUM)
+        t_all = stats[1:3].clone()
+        dist.all_reduce(t_all, op=dist.ReduceOp.MAX)
+        tokens_all, dev_max, wall_max = float(tok_all[0]), float(t_all[0]), float(t_all[1])
+    else:
+        tokens_all, dev_max, wall_max = float(tokens), dev_s, wall
+
+    if rank == 0:
+        peaks = {}
+        try:
+            with open(os.path.join(ROOT, "MEASURED_PEAKS.json")) as f:
+                peaks = json.load(f)
+        except Exception:
+            pass
+        peak = float(peaks.get("hbm_gbs", 6650.0))
+        peak_src = "measured" if "hbm_gbs" in peaks else "fallback"
+        tgt_b, draft_b = algorithmic_bytes()
+        lin_s = statistics.median(lin_ms) / 1e3
+        achieved = (tgt_b + draft_b) / 1e9 / lin_s
+        line = {
+            "metric": METRIC, "value": tokens_all / dev_max, "unit": UNIT, "n_gpus": world, "steps": args.steps,
+            "warmup": args.warmup, "ms_per_step": 1e3 * dev_max / args.steps, "higher_is_better": True,
+            "scaling": "weak", "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
+            "config": {"workload": "configs[1]: 8B-shaped bf16 target + 1-layer EAGLE, tree 60 (6 iters x top-10), "
+                                   "4096-token Zipf(1.1) prompt, batch 1, greedy",
+                       "replicas": world, "l2": "inputs larger than L2 (22.6 GB of weights streamed per step)"},
+            "e2e": {"value": tokens_all / wall_max, "unit": UNIT, "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 128},
+            "gpu_launches": int(launches) * args.steps,
+            "launches_per_step": int(launches),
+            "mean_accept_length": statistics.mean(accept),
+            "step_device_ms_median": statistics.median(dev_ms),
+            "prefill_tokens_per_s": PROMPT_LEN / prefill_s,
+            "profile_eager_step_ms": {"total": statistics.median(prof_total), "linear": statistics.median(lin_ms),
+                                      "attention": statistics.median(att_ms), "linear_launches": lin_n},
+            "roofline": {"bound": "hbm", "kernel": "linear_umma_kernel (all %d launches of a step)" % lin_n,
+                         "achieved": achieved, "peak": peak, "unit": "GB/s", "frac": achieved / peak,
+                         "peak_source": peak_src, "traffic": None,
+                         "algorithmic_bytes_per_step": tgt_b + draft_b},
+            "step_roofline_frac": ((tgt_b + draft_b) / 1e9 / peak) / (statistics.median(dev_ms) / 1e3),
+            "clocks": sampler.summary(),
+        }
+        if world == 1 and not args.no_cpu_baseline:
+            line["cpu_baseline"] = cpu_step_baseline(statistics.mean(accept))
+        print(json.dumps(line), flush=True)
+    if dist is not None:
+        dist.barrier()
+        dist.destroy_process_group()
+    C.release()
+
+
+# ---------------------------------------------------------------------------- CPU oracle arm
+def cpu_step_baseline(mean_accept, budget_s=25.0):
+    """Times the CPU oracle on the host cores over a bounded sample of the step and scales it:
+    one target layer at M = 60 over a 4096-token KV cache, the target LM head at M = 60, one draft
+    level (fc + layer at M = 10 + LM head + log-softmax/top-k); step = 32 layers + head + 6 draft levels."""
+    import numpy as np
+    import torch
+    from oracle import tree as otree
+    from oracle.model import EagleOracleConfig, OracleConfig, OracleModel
+    cores = os.cpu_count() or 1
+    torch.set_num_threads(cores)
+    cfg = OracleConfig(vocab=CFG["vocab"], layers=1, hidden=CFG["hidden"], inter=CFG["inter"], hq=CFG["hq"],
+                       hkv=CFG["hkv"], head_dim=CFG["head_dim"], dtype="bf16")
+    eagle = EagleOracleConfig(**TREE)
+    g = torch.Generator().manual_seed(1)
+    H, I, d, V = CFG["hidden"], CFG["inter"], CFG["head_dim"], CFG["vocab"]
+
+    def rnd(*shape):
+        return (torch.randn(*shape, generator=g) * 0.02).to(torch.bfloat16).to(torch.float32)
+
+    p = "model.layers.0."
+    w = {"model.embed_tokens.weight": rnd(1024, H), "lm_head.weight": rnd(V, H), "model.norm.weight": torch.ones(H),
+         p + "self_attn.q_proj.weight": rnd(CFG["hq"] * d, H), p + "self_attn.k_proj.weight": rnd(CFG["hkv"] * d, H),
+         p + "self_attn.v_proj.weight": rnd(CFG["hkv"] * d, H), p + "self_attn.o_proj.weight": rnd(H, CFG["hq"] * d),
+         p + "mlp.gate_proj.weight": rnd(I, H), p + "mlp.up_proj.weight": rnd(I, H), p + "mlp.down_proj.weight": rnd(H, I),
+         p + "input_layernorm.weight": torch.ones(H), p + "post_attention_layernorm.weight": torch.ones(H)}
+    ew = {k.replace("model.layers.0.", "layers.0."): v for k, v in w.items() if k.startswith(p)}
+    ew["fc.weight"] = torch.cat([torch.zeros(H, H), torch.eye(H)], dim=1)
+    ew["fc.bias"] = torch.zeros(H)
+    L, T, k = PROMPT_LEN, TREE["tree_size"], TREE["topk"]
+    m = OracleModel(cfg, w, eagle, ew, budget=L + 128)
+    m.k_cache.normal_(generator=g)
+    m.v_cache.normal_(generator=g)
+    m.ek_cache.normal_(generator=g)
+    m.ev_cache.normal_(generator=g)
+    x = rnd(T, H) * 50
+    masks = [(1 << i) | 1 for i in range(T)]
+    pos = torch.full((T,), L, dtype=torch.long)
+    t_start = time.perf_counter()
+
+    def timed(fn, reps):
+        fn()
+        t0 = time.perf_counter()
+        for _ in range(reps):
+            fn()
+        return (time.perf_counter() - t0) / reps
+
+    t_layer = timed(lambda: m.layer(p, w, x, None, 1.0, 1.0, pos, m.k_cache[0], m.v_cache[0], L, L + T, None, masks, T,
+                                    0), 30)
+    t_head = timed(lambda: m.lm_head(x), 10)
+    xd = rnd(k, H) * 50
+
+    def draft_level():
+        h = m._draft_core(xd, xd, pos[:k], L, L + k, None, [(1 << i) for i in range(k)], k)
+        lg = m.lm_head(h, m.draft_head, True)
+        for r in range(k):
+            otree.topk_desc(otree.log_softmax_bf16(lg[r].numpy()), k)
+
+    t_draft = timed(draft_level, 10)
+    step_s = CFG["layers"] * t_layer + t_head + TREE["num_iter"] * t_draft
+    return {"value": mean_accept / step_s, "unit": UNIT, "cores": cores, "kind": "port",
+            "step_seconds": step_s,
+            "sample": "1 of 32 target layers at M=60 over a 4096-token KV (%.2f s), target LM head at M=60 (%.2f s), "
+                      "1 of 6 draft levels incl. log-softmax/top-k (%.2f s), scaled by op counts; %.0f s of CPU work"
+                      % (t_layer, t_head, t_draft, time.perf_counter() - t_start)}
+
+
+def run_reference(args):
+    rank = int(os.environ.get("RANK", "0"))
+    if rank != 0:
+        return
+    # the oracle is not driven by random acceptance here: accept length 1 (bonus token only) is what
+    # the random-weight config yields; the GPU arm reports its measured mean next to its own number
+    base = cpu_step_baseline(1.0)
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    line = {"impl": "reference", "metric": METRIC, "value": base["value"], "unit": UNIT, "n_gpus": world,
+            "steps": args.steps, "warmup": args.warmup, "ms_per_step": 1e3 * base["step_seconds"],
+            "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
+            "config": {"workload": "configs[1]: 8B-shaped bf16 target + 1-layer EAGLE, tree 60 (6 iters x top-10), "
+                                   "4096-token context, batch 1, greedy; CPU oracle of the reference step"},
+            "cpu_baseline": base,
+            "e2e": {"value": base["value"], "unit": UNIT, "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
+            "note": "the reference has no CPU implementation; its CUDA build is not run here, so this arm times "
+                    "the CPU restatement (oracle/) on the host cores"}
+    print(json.dumps(line), flush=True)
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=128)
+    ap.add_argument("--warmup", type=int, default=5)
+    ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    ap.add_argument("--no-cpu-baseline", action="store_true")
+    args = ap.parse_args()
+    if args.warmup < 3:
+        args.warmup = 3
+    if args.impl == "reference":
+        run_reference(args)
+    else:
+        run_ours(args)
+
+
+if __name__ == "__main__":
+    main()

@@ -34,6 +34,7 @@ _SIGNATURES = {
     "cpmcu_print_perf_summary": (None, []),
     "cpmcu_begin_generation": (_c_int, [_c_int, _c_int]),
     "cpmcu_spec_step": (_c_int, [_c_void_p, _c_int]),
+    "cpmcu_profile_step": (_c_int, [_c_void_p] * 3),
     "cpmcu_last_step_ms": (ctypes.c_double, []),
     "cpmcu_launches_per_step": (ctypes.c_long, []),
     "cpmcu_total_launches": (ctypes.c_long, []),
@@ -192,6 +193,16 @@ def spec_step(max_tokens=16):
     buf = (ctypes.c_int32 * max_tokens)()
     n = call("cpmcu_spec_step", ctypes.cast(buf, _c_void_p), max_tokens)
     return list(buf[: min(n, max_tokens)])
+
+
+def profile_step():
+    """One eager step with per-launch CUDA events: returns ({class: (ms, launches)}, total_ms)."""
+    ms = (ctypes.c_float * 3)()
+    cnt = (ctypes.c_int * 3)()
+    total = ctypes.c_float()
+    call("cpmcu_profile_step", ctypes.cast(ms, _c_void_p), ctypes.cast(cnt, _c_void_p),
+         ctypes.cast(ctypes.pointer(total), _c_void_p))
+    return {"linear": (ms[0], cnt[0]), "attention": (ms[1], cnt[1])}, total.value
 
 
 def last_step_ms():

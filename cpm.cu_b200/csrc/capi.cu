@@ -215,6 +215,13 @@ int cpmcu_spec_step(int32_t* out_tokens, int max_tokens) {
     return guarded([&] { return engine().spec_step(out_tokens, max_tokens); });
 }
 
+int cpmcu_profile_step(float* class_ms, int* class_launches, float* total_ms) {
+    return guarded([&] {
+        engine().profile_step(class_ms, class_launches, total_ms);
+        return 0;
+    });
+}
+
 double cpmcu_last_step_ms(void) { return g_engine ? g_engine->last_step_device_ms() : 0.0; }
 long cpmcu_launches_per_step(void) { return g_engine ? g_engine->launches_per_step() : 0; }
 long cpmcu_total_launches(void) {

@@ -8,6 +8,8 @@
 #include <stdint.h>
 #include <stdexcept>
 #include <string>
+#include <utility>
+#include <vector>
 
 typedef __nv_bfloat16 bf16;
 
@@ -37,12 +39,27 @@ enum KernelError : int {
     ERR_BAD_TREE = 4,
 };
 
+enum KernelClass : int { KC_LINEAR = 0, KC_ATTENTION = 1, KC_OTHER = 2, KC_COUNT = 3 };
+
 struct Runtime {
     cudaStream_t stream = nullptr;
     int* d_error = nullptr;  // device error word, or-ed into by kernels
     int num_sms = 148;
     int device = 0;
     long launches = 0;  // kernels launched (or captured) so far by this library
+    // Optional per-launch timing (eager runs only): event pairs per kernel class.
+    bool profile = false;
+    std::vector<std::pair<cudaEvent_t, cudaEvent_t>> prof[KC_COUNT];
+};
+
+// Brackets one launch with CUDA events on its stream while Runtime::profile is set.
+struct ProfileScope {
+    cudaStream_t s;
+    int kind;
+    bool on;
+    cudaEvent_t e1 = nullptr;
+    ProfileScope(int kind_, cudaStream_t s_);
+    ~ProfileScope();
 };
 Runtime& runtime();          // lazily initialised, one per process
 int read_and_clear_error();  // synchronises the stream

@@ -794,3 +794,41 @@ const int32_t* Engine::tree_buffers(int which) const {
         default: return nullptr;
     }
 }
+
+// One eager (uncaptured) step with every linear / attention launch bracketed by
+// CUDA events; returns summed device milliseconds and launch counts per class.
+void Engine::profile_step(float* ms, int* counts, float* total_ms) {
+    CPM_REQUIRE(has_eagle_ && storage_ready_ && !first_draft_, "profile_step needs a generation in progress");
+    Runtime& rt = runtime();
+    cudaStream_t s = rt.stream;
+    for (int c = 0; c < KC_COUNT; ++c) rt.prof[c].clear();
+    rt.profile = true;
+    CUDA_CHECK(cudaEventRecord(ev0_, s));
+    try {
+        enqueue_step(false, s);
+    } catch (...) {
+        rt.profile = false;
+        throw;
+    }
+    rt.profile = false;
+    CUDA_CHECK(cudaEventRecord(ev1_, s));
+    CUDA_CHECK(cudaStreamSynchronize(s));
+    float t = 0.f;
+    CUDA_CHECK(cudaEventElapsedTime(&t, ev0_, ev1_));
+    *total_ms = t;
+    for (int c = 0; c < KC_COUNT; ++c) {
+        double sum = 0.0;
+        for (auto& pr : rt.prof[c]) {
+            float x = 0.f;
+            cudaEventElapsedTime(&x, pr.first, pr.second);
+            sum += x;
+            cudaEventDestroy(pr.first);
+            cudaEventDestroy(pr.second);
+        }
+        ms[c] = static_cast<float>(sum);
+        counts[c] = static_cast<int>(rt.prof[c].size());
+        rt.prof[c].clear();
+    }
+    if (h_result_[31] != 0) check_errors("profile_step");
+    num_prev_ = h_result_[0];
+}

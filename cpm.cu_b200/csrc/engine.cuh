@@ -89,6 +89,7 @@ public:
     // begin_generation() is called once after prefill with the first root token.
     void begin_generation(int prefix_length, int32_t root_token);
     int spec_step(int32_t* out_tokens, int max_tokens);  // returns accept length n; out_tokens[0:n]
+    void profile_step(float* ms, int* counts, float* total_ms);
     double last_step_device_ms() const { return last_step_ms_; }
     long launches_per_step() const { return launches_per_step_; }
 

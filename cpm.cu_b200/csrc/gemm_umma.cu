@@ -328,6 +328,7 @@ LinearPlan make_linear_plan(const bf16* x, int x_rows, const bf16* w, int M, int
 }
 
 void launch_linear(const LinearPlan& p, cudaStream_t stream) {
+    ProfileScope prof(KC_LINEAR, stream);
     LinearArgs a;
     a.M = p.M; a.N = p.N; a.K = p.K;
     a.n_tiles = ceil_div(p.N, BLOCK_N);

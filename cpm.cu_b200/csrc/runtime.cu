@@ -99,3 +99,18 @@ CUtensorMap make_tmap_3d(const void* base, uint64_t d0, uint64_t d1, uint64_t d2
     if (r != CUDA_SUCCESS) throw std::runtime_error("cpmcu_b200: cuTensorMapEncodeTiled (3-D) failed: " + std::to_string(r));
     return tm;
 }
+
+ProfileScope::ProfileScope(int kind_, cudaStream_t s_) : s(s_), kind(kind_), on(false) {
+    Runtime& rt = runtime();
+    if (!rt.profile) return;
+    on = true;
+    cudaEvent_t e0;
+    cudaEventCreate(&e0);
+    cudaEventCreate(&e1);
+    cudaEventRecord(e0, s);
+    rt.prof[kind].push_back(std::make_pair(e0, e1));
+}
+
+ProfileScope::~ProfileScope() {
+    if (on) cudaEventRecord(e1, s);
+}

@@ -425,6 +425,7 @@ AttnPlan make_attn_plan(const bf16* q, int q_ld_tokens, const bf16* k_cache, con
 }
 
 void launch_tree_attention(const AttnPlan& p, cudaStream_t s) {
+    ProfileScope prof(KC_ATTENTION, s);
     static bool configured = false;
     if (!configured) {
         CUDA_CHECK(cudaFuncSetAttribute(tree_attn_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_TOTAL));

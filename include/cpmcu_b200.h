@@ -126,6 +126,12 @@ int cpmcu_begin_generation(int prefix_length, int32_t root_token);
  * to out_tokens (HOST memory, at most max_tokens) and returns n, or -1. */
 int cpmcu_spec_step(int32_t* out_tokens, int max_tokens);
 
+/* Runs one more speculative step eagerly (not from the graph) with every launch
+ * bracketed by CUDA events on its stream.  class_ms / class_launches receive 3
+ * entries (HOST memory): [0] linear layers, [1] attention, [2] unused; total_ms
+ * the whole step.  The step's tokens are consumed (generation advances). */
+int cpmcu_profile_step(float* class_ms, int* class_launches, float* total_ms);
+
 /* Device time of the last cpmcu_spec_step in milliseconds (CUDA events). */
 double cpmcu_last_step_ms(void);
 /* Kernels in one captured step / launched by this library so far. */
