@@ -156,7 +156,9 @@ def run_ours(args):
         torch.cuda.set_device(local)
         dist.init_process_group("nccl", device_id=torch.device("cuda", local))
     C.load()  # fails loudly if the CUDA library is missing
-    llm = build_model(local, seed=1)
+    import contextlib
+    with contextlib.redirect_stdout(sys.stderr):  # keep stdout for the single JSON line
+        llm = build_model(local, seed=1)
     prompt = torch.tensor(zipf_prompt(PROMPT_LEN, CFG["vocab"], 100 + rank), device="cuda")
     pos = torch.arange(PROMPT_LEN, dtype=torch.int32, device="cuda")
     torch.cuda.synchronize()

@@ -267,12 +267,54 @@ int cpmcu_linear_bf16(const void* x, const void* w, const void* bias, void* y, i
     });
 }
 
+int cpmcu_bench_linear(int M, int N, int K, int copies, int iters, int grid_limit, float* avg_us) {
+    return guarded([&] {
+        Runtime& rt = runtime();
+        cudaStream_t s = rt.stream;
+        CPM_REQUIRE(copies >= 1 && copies <= 64 && iters >= 1, "bench_linear: bad repetition counts");
+        const int limit = (grid_limit > 0) ? grid_limit : rt.num_sms;
+        const int mt = linear_pick_mt(M);
+        const size_t wbytes = static_cast<size_t>(N) * K * 2;
+        DeviceBuf w(wbytes * copies), x(static_cast<size_t>(M) * K * 2), y(static_cast<size_t>(M) * N * 2);
+        DeviceBuf ws(linear_workspace_bytes(mt, limit));
+        const size_t tiles = static_cast<size_t>(ceil_div(N, 128)) * ceil_div(M, mt);
+        DeviceBuf tickets(tiles * sizeof(int));
+        CUDA_CHECK(cudaMemsetAsync(tickets.p, 0, tiles * sizeof(int), s));
+        CUDA_CHECK(cudaMemsetAsync(w.p, 0x3c, wbytes * copies, s));
+        CUDA_CHECK(cudaMemsetAsync(x.p, 0x3c, static_cast<size_t>(M) * K * 2, s));
+        std::vector<LinearPlan> plans;
+        for (int c = 0; c < copies; ++c) {
+            plans.push_back(make_linear_plan(static_cast<const bf16*>(x.p), M,
+                                             reinterpret_cast<const bf16*>(static_cast<uint8_t*>(w.p) + wbytes * c), M, N, K,
+                                             static_cast<bf16*>(y.p), N, nullptr, static_cast<float*>(ws.p),
+                                             static_cast<int*>(tickets.p), limit));
+            const char* dbg = getenv("CPMCU_LINEAR_DEBUG");
+            if (dbg) plans.back().debug = atoi(dbg);
+        }
+        for (int c = 0; c < copies && c < 3; ++c) launch_linear(plans[c], s);
+        cudaEvent_t e0, e1;
+        CUDA_CHECK(cudaEventCreate(&e0));
+        CUDA_CHECK(cudaEventCreate(&e1));
+        CUDA_CHECK(cudaEventRecord(e0, s));
+        for (int i = 0; i < iters; ++i) launch_linear(plans[i % copies], s);
+        CUDA_CHECK(cudaEventRecord(e1, s));
+        CUDA_CHECK(cudaStreamSynchronize(s));
+        float ms = 0.f;
+        CUDA_CHECK(cudaEventElapsedTime(&ms, e0, e1));
+        cudaEventDestroy(e0);
+        cudaEventDestroy(e1);
+        *avg_us = ms * 1000.f / iters;
+        sync_and_check("bench_linear");
+        return 0;
+    });
+}
+
 int cpmcu_tree_attention(const void* q, int q_ld, const void* k_cache, const void* v_cache, int budget, int tq,
                          int hq, int hkv, const int32_t* kv_len, int kv_len_add, const int32_t* n_valid,
                          const uint64_t* mask, int mask_k, int window, int splits, void* out, int out_ld) {
     return guarded([&] {
         Runtime& rt = runtime();
-        CPM_REQUIRE(splits >= 1 && splits <= 64, "attention: splits must be in [1,64]");
+        CPM_REQUIRE(splits >= 1 && splits <= 32, "attention: splits must be in [1,32]");
         const size_t rows = static_cast<size_t>(tq) * hq;
         DeviceBuf ws_o(splits > 1 ? rows * splits * 128 * sizeof(float) : 0);
         DeviceBuf ws_ml(splits > 1 ? rows * splits * 2 * sizeof(float) : 0);
@@ -288,6 +330,57 @@ int cpmcu_tree_attention(const void* q, int q_ld, const void* k_cache, const voi
         p.window = window;
         launch_tree_attention(p, rt.stream);
         sync_and_check("tree_attention");
+        return 0;
+    });
+}
+
+int cpmcu_bench_attention(int tq, int hq, int hkv, int kv_total, int splits, int with_mask, int iters, float* avg_us) {
+    return guarded([&] {
+        Runtime& rt = runtime();
+        cudaStream_t s = rt.stream;
+        const int budget = (kv_total + 255) / 128 * 128;
+        const int q_ld = (hq + 2 * hkv) * 128;
+        const size_t kv_bytes = static_cast<size_t>(budget) * hkv * 128 * 2;
+        const int layers = 8;  // rotate over several caches like consecutive layers do
+        DeviceBuf q(static_cast<size_t>(tq) * q_ld * 2), k(kv_bytes * layers), v(kv_bytes * layers);
+        DeviceBuf out(static_cast<size_t>(tq) * hq * 128 * 2), len(4), mask(64 * 8);
+        const size_t rows = static_cast<size_t>(tq) * hq;
+        DeviceBuf ws_o(rows * splits * 128 * 4), ws_ml(rows * splits * 2 * 4);
+        CUDA_CHECK(cudaMemsetAsync(q.p, 0x3c, static_cast<size_t>(tq) * q_ld * 2, s));
+        CUDA_CHECK(cudaMemsetAsync(k.p, 0x3c, kv_bytes * layers, s));
+        CUDA_CHECK(cudaMemsetAsync(v.p, 0x3c, kv_bytes * layers, s));
+        CUDA_CHECK(cudaMemcpyAsync(len.p, &kv_total, 4, cudaMemcpyHostToDevice, s));
+        uint64_t hm[64];
+        for (int i = 0; i < 64; ++i) hm[i] = (1ull << i) | 1ull;
+        CUDA_CHECK(cudaMemcpyAsync(mask.p, hm, sizeof(hm), cudaMemcpyHostToDevice, s));
+        std::vector<AttnPlan> plans;
+        for (int l = 0; l < layers; ++l) {
+            AttnPlan p = make_attn_plan(static_cast<const bf16*>(q.p), q_ld,
+                                        reinterpret_cast<const bf16*>(static_cast<uint8_t*>(k.p) + kv_bytes * l),
+                                        reinterpret_cast<const bf16*>(static_cast<uint8_t*>(v.p) + kv_bytes * l), budget, tq,
+                                        hq, hkv, 128, splits, static_cast<bf16*>(out.p), hq * 128,
+                                        static_cast<float*>(ws_o.p), static_cast<float*>(ws_ml.p));
+            p.kv_len = static_cast<const int32_t*>(len.p);
+            if (with_mask) {
+                p.mask = static_cast<const uint64_t*>(mask.p);
+                p.mask_k = tq;
+            }
+            plans.push_back(p);
+        }
+        for (int l = 0; l < 3; ++l) launch_tree_attention(plans[l], s);
+        cudaEvent_t e0, e1;
+        CUDA_CHECK(cudaEventCreate(&e0));
+        CUDA_CHECK(cudaEventCreate(&e1));
+        CUDA_CHECK(cudaEventRecord(e0, s));
+        for (int i = 0; i < iters; ++i) launch_tree_attention(plans[i % layers], s);
+        CUDA_CHECK(cudaEventRecord(e1, s));
+        CUDA_CHECK(cudaStreamSynchronize(s));
+        float ms = 0.f;
+        CUDA_CHECK(cudaEventElapsedTime(&ms, e0, e1));
+        cudaEventDestroy(e0);
+        cudaEventDestroy(e1);
+        *avg_us = ms * 1000.f / iters;
+        sync_and_check("bench_attention");
         return 0;
     });
 }

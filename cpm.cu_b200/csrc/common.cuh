@@ -84,6 +84,7 @@ struct LinearPlan {
     const bf16* bias = nullptr;
     float* workspace = nullptr;  // split-K partials: grid * 2 * mt * 128 floats
     int* tickets = nullptr;      // one counter per output tile, zero between launches
+    int debug = 0;               // bench-only switches, see gemm_umma.cu
     // Optional fused epilogue: y = silu(gate) * up where gate/up rows alternate
     // in 64-row halves of each 128-row weight tile (see make_linear_plan).
     int epilogue = 0;

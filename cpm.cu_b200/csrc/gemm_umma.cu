@@ -50,6 +50,7 @@ struct LinearArgs {
     float* workspace;
     int* tickets;
     int* error;
+    int debug;  // bench-only switches: 1 = skip the X loads, 2 = skip epilogue stores and the split-K fix-up
 };
 
 struct SegIter {
@@ -134,9 +135,14 @@ linear_umma_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_consta
                 for (int kb = kb0; kb < kb1; ++kb) {
                     if (!ptx::mbar_wait(&empty[stage], phase ^ 1, abort_flag)) { ok = false; break; }
                     uint8_t* dst = tiles + stage * C::STAGE_BYTES;
-                    ptx::mbar_arrive_expect_tx(&full[stage], C::STAGE_BYTES);
-                    ptx::tma_load_2d(dst, &tm_w, &full[stage], kb * BLOCK_K, n_tile * BLOCK_N);
-                    ptx::tma_load_2d(dst + W_TILE_BYTES, &tm_x, &full[stage], kb * BLOCK_K, m_tile * MT);
+                    if (a.debug & 1) {
+                        ptx::mbar_arrive_expect_tx(&full[stage], W_TILE_BYTES);
+                        ptx::tma_load_2d(dst, &tm_w, &full[stage], kb * BLOCK_K, n_tile * BLOCK_N);
+                    } else {
+                        ptx::mbar_arrive_expect_tx(&full[stage], C::STAGE_BYTES);
+                        ptx::tma_load_2d(dst, &tm_w, &full[stage], kb * BLOCK_K, n_tile * BLOCK_N);
+                        ptx::tma_load_2d(dst + W_TILE_BYTES, &tm_x, &full[stage], kb * BLOCK_K, m_tile * MT);
+                    }
                     if (++stage == C::STAGES) { stage = 0; phase ^= 1; }
                 }
             }
@@ -205,9 +211,11 @@ linear_umma_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_consta
             ptx::tc_fence_after();
             __syncwarp();  // TMEM loads below are warp-collective
             const uint32_t t_addr = tmem_base + (static_cast<uint32_t>(q * 32) << 16) + acc * MT;
+            // partial slot layout: [128 features][MT tokens] fp32, so a thread owns one contiguous row
+            float* my_row = my_ws + row * MT;
 #pragma unroll 1
             for (int c0 = 0; c0 < MT; c0 += 16) {
-                if (c0 >= m_cnt) break;  // uniform across the CTA
+                if (c0 >= m_cnt || (a.debug & 2)) break;  // uniform across the CTA
                 uint32_t r[16];
                 ptx::tmem_ld16(t_addr + c0, r);
                 ptx::tmem_wait_ld();
@@ -223,8 +231,8 @@ linear_umma_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_consta
                     }
                 } else {
 #pragma unroll
-                    for (int c = 0; c < 16; ++c) {
-                        if (c0 + c < m_cnt) my_ws[(c0 + c) * BLOCK_N + row] = __uint_as_float(r[c]);
+                    for (int c = 0; c < 16; c += 4) {
+                        *reinterpret_cast<uint4*>(my_row + c0 + c) = make_uint4(r[c], r[c + 1], r[c + 2], r[c + 3]);
                     }
                 }
             }
@@ -233,7 +241,7 @@ linear_umma_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_consta
             acc ^= 1;
             if (acc == 0) acc_phase ^= 1;
 
-            if (!complete) {
+            if (!complete && !(a.debug & 2)) {
                 const long long tile_u0 = static_cast<long long>(tile) * a.kblocks;
                 const int g_first = unit_owner(tile_u0, a.total_units, G);
                 const int g_last = unit_owner(tile_u0 + a.kblocks - 1, a.total_units, G);
@@ -251,15 +259,37 @@ linear_umma_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_consta
                 ptx::named_bar_sync(1, 128);  // everyone has read s_last before it can change
                 if (is_last) {
                     __threadfence();
-                    if (n < a.N) {
-                        for (int c = 0; c < m_cnt; ++c) {
-                            float sum = 0.f;
-                            for (int gg = g_first; gg <= g_last; ++gg) {
-                                const float* ws = a.workspace +
-                                                  (static_cast<size_t>(gg) * 2 + (gg == g_first ? 1 : 0)) * (MT * BLOCK_N);
-                                sum += __ldcg(ws + c * BLOCK_N + row);
+                    // sum the pieces in CTA order (deterministic); 16 tokens at a time, four
+                    // independent 16-byte loads per piece in flight
+#pragma unroll 1
+                    for (int c0 = 0; c0 < m_cnt; c0 += 16) {
+                        float sum[16];
+#pragma unroll
+                        for (int c = 0; c < 16; ++c) sum[c] = 0.f;
+#pragma unroll 2
+                        for (int gg = g_first; gg <= g_last; ++gg) {
+                            const float* ws = a.workspace +
+                                              (static_cast<size_t>(gg) * 2 + (gg == g_first ? 1 : 0)) * (MT * BLOCK_N) +
+                                              row * MT + c0;
+                            float4 v[4];
+#pragma unroll
+                            for (int j = 0; j < 4; ++j) v[j] = __ldcg(reinterpret_cast<const float4*>(ws) + j);
+#pragma unroll
+                            for (int j = 0; j < 4; ++j) {
+                                sum[4 * j + 0] += v[j].x;
+                                sum[4 * j + 1] += v[j].y;
+                                sum[4 * j + 2] += v[j].z;
+                                sum[4 * j + 3] += v[j].w;
                             }
-                            a.y[static_cast<size_t>(m_base + c) * a.ldy + n] = __float2bfloat16(sum + bias_v);
+                        }
+                        if (n < a.N) {
+#pragma unroll
+                            for (int c = 0; c < 16; ++c) {
+                                if (c0 + c < m_cnt) {
+                                    a.y[static_cast<size_t>(m_base + c0 + c) * a.ldy + n] =
+                                        __float2bfloat16(sum[c] + bias_v);
+                                }
+                            }
                         }
                     }
                 }
@@ -338,6 +368,7 @@ void launch_linear(const LinearPlan& p, cudaStream_t stream) {
     a.y = p.y; a.ldy = p.ldy; a.bias = p.bias;
     a.workspace = p.workspace; a.tickets = p.tickets;
     a.error = runtime().d_error;
+    a.debug = p.debug;
     switch (p.mt) {
         case 16: launch_mt<16>(p, a, stream); break;
         case 32: launch_mt<32>(p, a, stream); break;

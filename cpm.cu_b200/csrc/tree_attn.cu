@@ -34,9 +34,10 @@ constexpr int SMEM_K = SMEM_Q + TILE_BYTES;          // 2 stages
 constexpr int SMEM_V = SMEM_K + 2 * TILE_BYTES;      // 2 stages
 constexpr int SMEM_P = SMEM_V + 2 * TILE_BYTES;
 constexpr int SMEM_CTRL = SMEM_P + TILE_BYTES;
-constexpr int SMEM_TOTAL = SMEM_CTRL + 256 + 1024;
+constexpr int SMEM_XCH = SMEM_CTRL + 256;   // 2 x 128 floats
+constexpr int SMEM_TOTAL = SMEM_XCH + 1024 + 1024;
 constexpr int TMEM_COLS = 256;  // S: columns [0,128), O: columns [128,256)
-constexpr int NTHREADS = 128;
+constexpr int NTHREADS = 256;   // two threads per query row: warps 0-3 take keys 0-63 of a tile, warps 4-7 keys 64-127
 
 struct AttnArgs {
     int tq, hq, hkv, grp, tok_per_tile, num_mtiles;
@@ -54,6 +55,12 @@ struct AttnArgs {
     int* error;
 };
 
+__device__ __forceinline__ float fast_exp2(float x) {
+    float y;
+    asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
+    return y;
+}
+
 __global__ void __launch_bounds__(NTHREADS, 1)
 tree_attn_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CUtensorMap tm_k,
                  const __grid_constant__ CUtensorMap tm_v, const AttnArgs a) {
@@ -67,9 +74,13 @@ tree_attn_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant
     uint64_t* o_bar = bars + 6;
     uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 7);
     volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
+    float* xch = reinterpret_cast<float*>(smem + SMEM_XCH);  // [2][128] row maxima / sums of the two column halves
 
     const int tid = threadIdx.x;
     const int warp = tid >> 5;
+    const int lane = tid & 31;
+    const int ch = warp >> 2;                    // column half of the key tile
+    const int row = (warp & 3) * 32 + lane;      // query row of the tile == TMEM lane
     const bool leader = (tid == 0);
     const int mt = blockIdx.x % a.num_mtiles;
     const int h = blockIdx.x / a.num_mtiles;  // kv head
@@ -98,16 +109,16 @@ tree_attn_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant
     __syncthreads();
     ptx::tc_fence_after();
     const uint32_t tmem_base = *tmem_slot;
-    const uint32_t tmem_s = tmem_base;
-    const uint32_t tmem_o = tmem_base + KEYS;
-    const uint32_t lane_sel = static_cast<uint32_t>(warp * 32) << 16;
+    const uint32_t lane_sel = static_cast<uint32_t>((warp & 3) * 32) << 16;
+    const uint32_t tmem_s = tmem_base + lane_sel + ch * 64;         // this thread's 64 score columns
+    const uint32_t tmem_o = tmem_base + lane_sel + KEYS + ch * 64;  // this thread's 64 output columns
 
     // ---- geometry of this tile
     const int kv_total = *a.kv_len + a.kv_len_add;
     const int tq_eff = (a.n_valid != nullptr) ? min(*a.n_valid, a.tq) : a.tq;
     const int t0 = mt * a.tok_per_tile;
-    const int t = t0 + tid / a.grp;          // query token of this thread's row
-    const int qh = h * a.grp + tid % a.grp;  // query head of this thread's row
+    const int t = t0 + row / a.grp;          // query token of this thread's row
+    const int qh = h * a.grp + row % a.grp;  // query head of this thread's row
     const bool row_valid = (t < tq_eff);
     const int causal_base = kv_total - tq_eff;  // token t sees keys < causal_base + t + 1
     int limit = row_valid ? min(kv_total, causal_base + t + 1) : 0;
@@ -154,13 +165,13 @@ tree_attn_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant
         }
     }
 
-    float m_run = -INFINITY;  // running max of raw scores
-    float l_run = 0.f;
+    float m_run = -INFINITY;  // running max of raw scores (same in both threads of a row)
+    float l_run = 0.f;        // this thread's share of the running sum
 
     for (int i = 0; i < n_it && ok; ++i) {
         const int st = i & 1;
         const uint32_t ph = (i >> 1) & 1;
-        const int key0 = (kt_begin + i) * KEYS;
+        const int key0 = (kt_begin + i) * KEYS + ch * 64;  // first key of this thread's 64 columns
 
         if (leader) {
             bool w = true;
@@ -175,7 +186,7 @@ tree_attn_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant
                     for (int j = 0; j < 4; ++j) {
                         const uint64_t da = ptx::umma_desc_sw128(q_addr + dh * HALF_BYTES + j * 32, 16, 1024);
                         const uint64_t db = ptx::umma_desc_sw128(k_addr + dh * HALF_BYTES + j * 32, 16, 1024);
-                        ptx::umma_ss(tmem_s, da, db, idesc_s, (dh | j) ? 1u : 0u);
+                        ptx::umma_ss(tmem_base, da, db, idesc_s, (dh | j) ? 1u : 0u);
                     }
                 }
                 ptx::umma_commit(s_bar);
@@ -192,31 +203,36 @@ tree_attn_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant
             ptx::tma_load_2d(smem + SMEM_K + st * TILE_BYTES + HALF_BYTES, &tm_k, &k_full[st], h * D + 64, keyn);
         }
 
-        // ---- pass 1: row maximum over visible keys
-        const bool need_mask = (key0 + KEYS > limit) || (key0 + KEYS > mbeg) || (key0 < key_lo);
-        float m_tile = -INFINITY;
-#pragma unroll 1
-        for (int c0 = 0; c0 < KEYS; c0 += 32) {
-            uint32_t r[32];
-            ptx::tmem_ld32(tmem_s + lane_sel + c0, r);
-            ptx::tmem_wait_ld();
-            if (!need_mask) {
+        // ---- scores of this thread: 64 columns, kept in registers for both passes
+        uint32_t sc[64];
+        ptx::tmem_ld32(tmem_s, sc);
+        ptx::tmem_ld32(tmem_s + 32, sc + 32);
+        ptx::tmem_wait_ld();
+        const bool need_mask = (key0 + 64 > limit) || (key0 + 64 > mbeg) || (key0 < key_lo);
+        if (need_mask) {
 #pragma unroll
-                for (int c = 0; c < 32; ++c) m_tile = fmaxf(m_tile, __uint_as_float(r[c]));
-            } else {
-#pragma unroll
-                for (int c = 0; c < 32; ++c) {
-                    const int key = key0 + c0 + c;
-                    bool vis = key < limit && key >= key_lo;
-                    if (key >= mbeg) vis = vis && ((mword >> (key - mbeg)) & 1ull);
-                    if (vis) m_tile = fmaxf(m_tile, __uint_as_float(r[c]));
-                }
+            for (int c = 0; c < 64; ++c) {
+                const int key = key0 + c;
+                bool vis = key < limit && key >= key_lo;
+                if (key >= mbeg) vis = vis && ((mword >> (key - mbeg)) & 1ull);
+                if (!vis) sc[c] = 0xff800000u;  // -inf
             }
         }
+        float mx[4] = {-INFINITY, -INFINITY, -INFINITY, -INFINITY};
+#pragma unroll
+        for (int c = 0; c < 64; c += 4) {
+            mx[0] = fmaxf(mx[0], __uint_as_float(sc[c]));
+            mx[1] = fmaxf(mx[1], __uint_as_float(sc[c + 1]));
+            mx[2] = fmaxf(mx[2], __uint_as_float(sc[c + 2]));
+            mx[3] = fmaxf(mx[3], __uint_as_float(sc[c + 3]));
+        }
+        const float m_half = fmaxf(fmaxf(mx[0], mx[1]), fmaxf(mx[2], mx[3]));
+        xch[ch * ROWS + row] = m_half;
+        __syncthreads();
+        const float m_tile = fmaxf(m_half, xch[(ch ^ 1) * ROWS + row]);
         const float m_new = fmaxf(m_run, m_tile);
         const float m_use = (m_new == -INFINITY) ? 0.f : m_new;
-        const float alpha = (m_run == -INFINITY) ? ((l_run == 0.f) ? 1.f : 0.f)
-                                                 : exp2f((m_run - m_use) * a.scale_log2);
+        const float alpha = (m_run == -INFINITY) ? 1.f : fast_exp2((m_run - m_use) * a.scale_log2);
         const bool rescale = (i > 0) && __any_sync(0xffffffffu, alpha != 1.f);
 
         if (i > 0) {  // P buffer, the other V stage and O are in use until PV(i-1) has finished
@@ -230,61 +246,44 @@ tree_attn_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant
                 ptx::tma_load_2d(smem + SMEM_V + sv * TILE_BYTES, &tm_v, &v_full[sv], h * D, keyn);
                 ptx::tma_load_2d(smem + SMEM_V + sv * TILE_BYTES + HALF_BYTES, &tm_v, &v_full[sv], h * D + 64, keyn);
             }
+            __syncwarp();
         }
         if (rescale) {
 #pragma unroll 1
-            for (int c0 = 0; c0 < D; c0 += 32) {
+            for (int c0 = 0; c0 < 64; c0 += 32) {
                 uint32_t r[32];
-                ptx::tmem_ld32(tmem_o + lane_sel + c0, r);
+                ptx::tmem_ld32(tmem_o + c0, r);
                 ptx::tmem_wait_ld();
 #pragma unroll
                 for (int c = 0; c < 32; ++c) r[c] = __float_as_uint(__uint_as_float(r[c]) * alpha);
-                ptx::tmem_st32(tmem_o + lane_sel + c0, r);
+                ptx::tmem_st32(tmem_o + c0, r);
             }
             ptx::tmem_wait_st();
         }
-        l_run *= alpha;
         m_run = m_new;
-        __syncwarp();
 
-        // ---- pass 2: P = exp2((s - m) * scale), bf16, into swizzled smem
-        float l_add = 0.f;
+        // ---- P = 2^((s - m) * scale) in bf16 into the swizzled A-operand tile; row sums in fp32
         const float m_off = m_use * a.scale_log2;
-        uint8_t* p_row = smem + SMEM_P + tid * 128;
-#pragma unroll 1
-        for (int c0 = 0; c0 < KEYS; c0 += 32) {
-            uint32_t r[32];
-            ptx::tmem_ld32(tmem_s + lane_sel + c0, r);
-            ptx::tmem_wait_ld();
-            float p[32];
+        float ls[4] = {0.f, 0.f, 0.f, 0.f};
+        uint8_t* p_half = smem + SMEM_P + ch * HALF_BYTES + row * 128;
 #pragma unroll
-            for (int c = 0; c < 32; ++c) {
-                float v = exp2f(__uint_as_float(r[c]) * a.scale_log2 - m_off);
-                if (need_mask) {
-                    const int key = key0 + c0 + c;
-                    bool vis = key < limit && key >= key_lo;
-                    if (key >= mbeg) vis = vis && ((mword >> (key - mbeg)) & 1ull);
-                    if (!vis) v = 0.f;
-                }
-                p[c] = v;
-                l_add += v;
+        for (int c8 = 0; c8 < 8; ++c8) {
+            float p[8];
+#pragma unroll
+            for (int e = 0; e < 8; ++e) {
+                p[e] = fast_exp2(fmaf(__uint_as_float(sc[c8 * 8 + e]), a.scale_log2, -m_off));
+                ls[e & 3] += p[e];
             }
-            // 32 keys = 4 chunks of 16 B inside the 64-key half (c0 / 64)
-            uint8_t* half = p_row + (c0 >> 6) * HALF_BYTES;
+            uint4 pk;
+            uint32_t* w = reinterpret_cast<uint32_t*>(&pk);
 #pragma unroll
-            for (int ch = 0; ch < 4; ++ch) {
-                uint4 pk;
-                uint32_t* w = reinterpret_cast<uint32_t*>(&pk);
-#pragma unroll
-                for (int e = 0; e < 4; ++e) {
-                    __nv_bfloat162 b2 = __floats2bfloat162_rn(p[ch * 8 + e * 2], p[ch * 8 + e * 2 + 1]);
-                    w[e] = *reinterpret_cast<uint32_t*>(&b2);
-                }
-                const int chunk = ((c0 & 63) >> 3) + ch;  // 16-byte chunk index within the 128-byte row
-                *reinterpret_cast<uint4*>(half + ((chunk ^ (tid & 7)) << 4)) = pk;
+            for (int e = 0; e < 4; ++e) {
+                __nv_bfloat162 b2 = __floats2bfloat162_rn(p[e * 2], p[e * 2 + 1]);
+                w[e] = *reinterpret_cast<uint32_t*>(&b2);
             }
+            *reinterpret_cast<uint4*>(p_half + ((c8 ^ (row & 7)) << 4)) = pk;
         }
-        l_run += l_add;
+        l_run = l_run * alpha + ((ls[0] + ls[1]) + (ls[2] + ls[3]));
 
         ptx::fence_proxy_async_smem();
         ptx::tc_fence_before();
@@ -302,11 +301,12 @@ tree_attn_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant
                         ptx::umma_desc_sw128(p_addr + (kk >> 2) * HALF_BYTES + (kk & 3) * 32, 16, 1024);
                     // B: V, N-major: 16 key rows of 128 B per step; 64-wide d halves HALF_BYTES apart
                     const uint64_t db = ptx::umma_desc_sw128(v_addr + kk * 16 * 128, HALF_BYTES, 1024);
-                    ptx::umma_ss(tmem_o, da, db, idesc_o, (i > 0 || kk > 0) ? 1u : 0u);
+                    ptx::umma_ss(tmem_base + KEYS, da, db, idesc_o, (i > 0 || kk > 0) ? 1u : 0u);
                 }
                 ptx::umma_commit(o_bar);
             }
         }
+        __syncwarp();
     }
 
     if (ok && n_it > 0) {
@@ -317,17 +317,20 @@ tree_attn_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant
 
     // ---- write-out.  TMEM reads are warp-collective, so every thread runs them
     // and only the global stores depend on whether the row exists.
+    xch[ch * ROWS + row] = l_run;
+    __syncthreads();
+    const float l_row = l_run + xch[(ch ^ 1) * ROWS + row];
     if (ok) {
         const bool store = (t < a.tq);
         const size_t grow = static_cast<size_t>(store ? t : 0) * a.hq + qh;
-        const float inv = (nsplit == 1) ? ((l_run > 0.f) ? 1.f / l_run : 0.f) : 1.f;
-        bf16* dst_b = a.out + static_cast<size_t>(store ? t : 0) * a.out_ld + qh * D;
-        float* dst_f = (nsplit > 1) ? a.ws_o + (static_cast<size_t>(split) * a.tq * a.hq + grow) * D : nullptr;
+        const float inv = (nsplit == 1) ? ((l_row > 0.f) ? 1.f / l_row : 0.f) : 1.f;
+        bf16* dst_b = a.out + static_cast<size_t>(store ? t : 0) * a.out_ld + qh * D + ch * 64;
+        float* dst_f = (nsplit > 1) ? a.ws_o + (static_cast<size_t>(split) * a.tq * a.hq + grow) * D + ch * 64 : nullptr;
 #pragma unroll 1
-        for (int c0 = 0; c0 < D; c0 += 32) {
+        for (int c0 = 0; c0 < 64; c0 += 32) {
             uint32_t r[32];
             if (n_it > 0) {  // uniform across the CTA
-                ptx::tmem_ld32(tmem_o + lane_sel + c0, r);
+                ptx::tmem_ld32(tmem_o + c0, r);
                 ptx::tmem_wait_ld();
             } else {
 #pragma unroll
@@ -355,10 +358,10 @@ tree_attn_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant
                 }
             }
         }
-        if (store && nsplit > 1) {
+        if (store && nsplit > 1 && ch == 0) {
             float* ml = a.ws_ml + (static_cast<size_t>(split) * a.tq * a.hq + grow) * 2;
             ml[0] = m_run;
-            ml[1] = l_run;
+            ml[1] = l_row;
         }
     }
 
@@ -372,28 +375,51 @@ tree_attn_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant
 }
 
 // Merge split partials: out = sum_s 2^((m_s - M) c) O_s / sum_s 2^((m_s - M) c) l_s.
+// One warp per (token, head) row; lane s first owns split s's (max, sum) pair, then
+// every lane accumulates four output columns with independent loads in flight.
 __global__ void attn_combine_kernel(const float* __restrict__ ws_o, const float* __restrict__ ws_ml, int nsplit,
                                     int rows, int hq, float scale_log2, bf16* __restrict__ out, int out_ld) {
     const int row = blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
     const int lane = threadIdx.x & 31;
     if (row >= rows) return;
-    float M = -INFINITY;
-    for (int s = 0; s < nsplit; ++s) M = fmaxf(M, ws_ml[(static_cast<size_t>(s) * rows + row) * 2]);
-    float acc[4] = {0.f, 0.f, 0.f, 0.f};
-    float l = 0.f;
-    for (int s = 0; s < nsplit; ++s) {
-        const float* ml = ws_ml + (static_cast<size_t>(s) * rows + row) * 2;
-        const float ms = ml[0];
-        if (ms == -INFINITY) continue;
-        const float w = exp2f((ms - M) * scale_log2);
-        l += w * ml[1];
-        const float4 o = *reinterpret_cast<const float4*>(ws_o + (static_cast<size_t>(s) * rows + row) * D + lane * 4);
-        acc[0] += w * o.x; acc[1] += w * o.y; acc[2] += w * o.z; acc[3] += w * o.w;
+    float m_s = -INFINITY, l_s = 0.f;
+    if (lane < nsplit) {
+        const float2 ml = *reinterpret_cast<const float2*>(ws_ml + (static_cast<size_t>(lane) * rows + row) * 2);
+        m_s = ml.x;
+        l_s = ml.y;
+    }
+    float M = m_s;
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) M = fmaxf(M, __shfl_xor_sync(0xffffffffu, M, o));
+    const float w_s = (m_s == -INFINITY) ? 0.f : exp2f((m_s - M) * scale_log2);
+    float l = w_s * l_s;
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) l += __shfl_xor_sync(0xffffffffu, l, o);
+    float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
+    const float* base = ws_o + static_cast<size_t>(row) * D + lane * 4;
+    const size_t stride = static_cast<size_t>(rows) * D;
+    for (int s0 = 0; s0 < nsplit; s0 += 4) {
+        float4 o[4];
+        float w[4];
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+            const int s = s0 + j;
+            w[j] = __shfl_sync(0xffffffffu, w_s, s & 31);
+            o[j] = (s < nsplit) ? __ldcg(reinterpret_cast<const float4*>(base + s * stride)) : make_float4(0.f, 0.f, 0.f, 0.f);
+            if (s >= nsplit) w[j] = 0.f;
+        }
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+            acc.x += w[j] * o[j].x;
+            acc.y += w[j] * o[j].y;
+            acc.z += w[j] * o[j].z;
+            acc.w += w[j] * o[j].w;
+        }
     }
     const float inv = (l > 0.f) ? 1.f / l : 0.f;
     const int t = row / hq, qh = row - t * hq;
-    __nv_bfloat162 a0 = __floats2bfloat162_rn(acc[0] * inv, acc[1] * inv);
-    __nv_bfloat162 a1 = __floats2bfloat162_rn(acc[2] * inv, acc[3] * inv);
+    __nv_bfloat162 a0 = __floats2bfloat162_rn(acc.x * inv, acc.y * inv);
+    __nv_bfloat162 a1 = __floats2bfloat162_rn(acc.z * inv, acc.w * inv);
     uint2 pk;
     pk.x = *reinterpret_cast<uint32_t*>(&a0);
     pk.y = *reinterpret_cast<uint32_t*>(&a1);
@@ -412,7 +438,7 @@ AttnPlan make_attn_plan(const bf16* q, int q_ld_tokens, const bf16* k_cache, con
     CPM_REQUIRE(hq % hkv == 0, "attention: query heads must be a multiple of kv heads");
     const int grp = hq / hkv;
     CPM_REQUIRE(grp <= ROWS && ROWS % grp == 0, "attention: unsupported GQA ratio");
-    CPM_REQUIRE(tq >= 1 && splits >= 1, "attention: empty problem");
+    CPM_REQUIRE(tq >= 1 && splits >= 1 && splits <= 32, "attention: splits must be in [1,32]");
     AttnPlan p;
     p.tq = tq; p.hq = hq; p.hkv = hkv; p.d = d; p.splits = splits;
     p.out = out; p.out_ld = out_ld; p.ws_o = ws_o; p.ws_ml = ws_ml;

@@ -151,6 +151,11 @@ void cpmcu_release(void);
 int cpmcu_linear_bf16(const void* x, const void* w, const void* bias, void* y, int M, int N, int K,
                       int grid_limit);
 
+/* Times `iters` back-to-back launches of the linear kernel on the library's
+ * stream with CUDA events, cycling through `copies` separate weight buffers so
+ * that the weights come from HBM and not from L2.  avg_us: HOST float. */
+int cpmcu_bench_linear(int M, int N, int K, int copies, int iters, int grid_limit, float* avg_us);
+
 /* reference: mha_fwd_kvcache, src/flash_attn/flash_api.hpp:292-392.
  * q: token t, head h at q + t*q_ld + h*128; caches [budget, hkv*128]; keys
  * visible = *kv_len + kv_len_add; n_valid (device, may be NULL) = number of
@@ -158,6 +163,11 @@ int cpmcu_linear_bf16(const void* x, const void* w, const void* bias, void* y, i
 int cpmcu_tree_attention(const void* q, int q_ld, const void* k_cache, const void* v_cache, int budget, int tq,
                          int hq, int hkv, const int32_t* kv_len, int kv_len_add, const int32_t* n_valid,
                          const uint64_t* mask, int mask_k, int window, int splits, void* out, int out_ld);
+
+/* Times `iters` back-to-back tree-attention launches (split kernel + merge) with
+ * CUDA events on the library's stream, rotating over 8 separate KV caches. */
+int cpmcu_bench_attention(int tq, int hq, int hkv, int kv_total, int splits, int with_mask, int iters,
+                          float* avg_us);
 
 /* reference: rms_norm / add_and_rms_norm, src/model/norm.cuh:8-99.
  * delta may be NULL; otherwise x += round(delta * delta_scale) in place first. */
