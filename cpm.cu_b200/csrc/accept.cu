@@ -23,6 +23,7 @@ namespace {
 constexpr int MAX_PATH = 16;
 
 __global__ void verify_accept_kernel(AcceptIO io) {
+    grid_dependency_sync();
     __shared__ unsigned long long s_correct[2];
     __shared__ unsigned long long s_best[2];
     const int i = threadIdx.x;  // 64 threads
@@ -71,6 +72,7 @@ __global__ void verify_accept_kernel(AcceptIO io) {
 }
 
 __global__ void accept_fixup_kernel(FixupArgs a) {
+    grid_dependency_sync();
     const int n = min(a.result[0], a.max_accept);
     const int L = a.cache_length[0];
     const int vec_per_row = a.kv_dim / 8;
@@ -121,9 +123,7 @@ __global__ void accept_fixup_kernel(FixupArgs a) {
 
 void launch_verify_accept(const AcceptIO& io, cudaStream_t s) {
     CPM_REQUIRE(io.tree_size >= 1 && io.tree_size <= 64, "verify: tree_size must be in [1,64]");
-    verify_accept_kernel<<<1, 64, 0, s>>>(io);
-    CUDA_CHECK(cudaGetLastError());
-    runtime().launches++;
+    launch_kernel(verify_accept_kernel, dim3(1), dim3(64), 0, s, io);
 }
 
 void launch_accept_fixup(const FixupArgs& a, cudaStream_t s) {
@@ -131,7 +131,5 @@ void launch_accept_fixup(const FixupArgs& a, cudaStream_t s) {
     CPM_REQUIRE(a.kv_dim % 8 == 0 && a.hidden % 8 == 0, "fixup: row sizes must be multiples of 8 elements");
     const long long threads = static_cast<long long>(a.num_caches) * (a.kv_dim / 8) +
                               2LL * a.max_accept * (a.hidden / 8);
-    accept_fixup_kernel<<<static_cast<unsigned>((threads + 255) / 256), 256, 0, s>>>(a);
-    CUDA_CHECK(cudaGetLastError());
-    runtime().launches++;
+    launch_kernel(accept_fixup_kernel, dim3(static_cast<unsigned>((threads + 255) / 256)), dim3(256), 0, s, a);
 }

@@ -47,6 +47,7 @@ struct Runtime {
     int num_sms = 148;
     int device = 0;
     long launches = 0;  // kernels launched (or captured) so far by this library
+    bool pdl = true;  // launch kernels with programmatic stream serialization (prologue overlap)
     // Optional per-launch timing (eager runs only): event pairs per kernel class.
     bool profile = false;
     std::vector<std::pair<cudaEvent_t, cudaEvent_t>> prof[KC_COUNT];
@@ -63,6 +64,39 @@ struct ProfileScope {
 };
 Runtime& runtime();          // lazily initialised, one per process
 int read_and_clear_error();  // synchronises the stream
+
+// Kernel launch with programmatic dependent launch enabled: the grid may start
+// while its predecessor in the stream drains; every kernel here executes
+// griddepcontrol.wait before touching global memory, which restores the order.
+template <typename... KArgs, typename... Args>
+void launch_kernel(void (*kernel)(KArgs...), dim3 grid, dim3 block, size_t smem, cudaStream_t s, Args&&... args) {
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = grid;
+    cfg.blockDim = block;
+    cfg.dynamicSmemBytes = smem;
+    cfg.stream = s;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[0].val.programmaticStreamSerializationAllowed = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = runtime().pdl ? 1 : 0;
+    CUDA_CHECK(cudaLaunchKernelEx(&cfg, kernel, KArgs(args)...));
+    runtime().launches++;
+}
+
+// Device side of the above.  Every kernel lets its successor start launching at once
+// (the successor can only set up and read constant data until its own wait returns) and
+// waits for its predecessor before it touches anything a previous kernel may have written.
+__device__ __forceinline__ void grid_dep_trigger() {
+    asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
+}
+__device__ __forceinline__ void grid_dep_wait() {
+    asm volatile("griddepcontrol.wait;" ::: "memory");
+}
+__device__ __forceinline__ void grid_dependency_sync() {
+    grid_dep_trigger();
+    grid_dep_wait();
+}
 
 // 2-D / 3-D bf16 tensor maps with 128-byte swizzle; inner box extent is 64
 // elements (128 B).  Strides are in bytes and must be multiples of 16.

@@ -45,6 +45,7 @@ __device__ __forceinline__ unsigned long long warp_max_u64(unsigned long long v)
 // ---- pass 1: per (row, segment) running max and sum of exp over bf16 logits
 __global__ void lsm_stats_kernel(const bf16* __restrict__ logits, int ld, int vocab, float2* __restrict__ stats,
                                  int nseg, const int32_t* __restrict__ row0) {
+    grid_dependency_sync();
     __shared__ float sh_m[SCAN_THREADS / 32];
     __shared__ float sh_s[SCAN_THREADS / 32];
     const int row = blockIdx.y, seg = blockIdx.x;
@@ -97,6 +98,7 @@ __device__ __forceinline__ void row_offset(const float2* __restrict__ st, int ns
 __global__ void lsm_local_topk_kernel(const bf16* __restrict__ logits, int ld, int vocab,
                                       const float2* __restrict__ stats, int nseg, int k,
                                       unsigned long long* __restrict__ cand, const int32_t* __restrict__ row0) {
+    grid_dependency_sync();
     __shared__ unsigned long long sh_best[SCAN_THREADS / 32];
     __shared__ float sh_off[2];
     const int row = blockIdx.y, seg = blockIdx.x;
@@ -168,6 +170,7 @@ __global__ void draft_expand_kernel(DraftTreeState st, const unsigned long long*
                                     int level, const bf16* __restrict__ h_rows, int h_ld,
                                     const int32_t* __restrict__ last_row_ptr, bf16* __restrict__ hid_out,
                                     int hid_ld, int hidden) {
+    grid_dependency_sync();
     extern __shared__ unsigned long long sh_keys[];  // rows * nseg * k candidate keys, then scratch
     const int k = st.k;
     const int rows = (level == 0) ? 1 : k;
@@ -254,6 +257,7 @@ __global__ void tree_finalize_kernel(DraftTreeState st, const int32_t* __restric
                                      int32_t* __restrict__ tree_draft_ids, int32_t* __restrict__ tree_pos,
                                      uint64_t* __restrict__ tree_mask, int32_t* __restrict__ tree_parent,
                                      int* __restrict__ error) {
+    grid_dependency_sync();
     __shared__ unsigned long long s_key[2048];
     __shared__ int s_sel[64];       // node i (1-based) <-> tried index s_sel[i-1]
     __shared__ int s_rank[2048];    // tried index -> node id (0 if not selected)
@@ -345,13 +349,10 @@ void launch_draft_topk_expand(const DraftTreeState& st, const bf16* logits, int 
     unsigned long long* cand = reinterpret_cast<unsigned long long*>(
         reinterpret_cast<uint8_t*>(scan_ws) + align_up(static_cast<int64_t>(k) * nseg * sizeof(float2), 256));
     dim3 grid(nseg, rows);
-    lsm_stats_kernel<<<grid, SCAN_THREADS, 0, s>>>(logits, ld, vocab, stats, nseg, level == 0 ? last_row_ptr : nullptr);
-    CUDA_CHECK(cudaGetLastError());
-    runtime().launches++;
-    lsm_local_topk_kernel<<<grid, SCAN_THREADS, 0, s>>>(logits, ld, vocab, stats, nseg, k, cand,
-                                                        level == 0 ? last_row_ptr : nullptr);
-    CUDA_CHECK(cudaGetLastError());
-    runtime().launches++;
+    launch_kernel(lsm_stats_kernel, grid, dim3(SCAN_THREADS), 0, s, logits, ld, vocab, stats, nseg,
+                  level == 0 ? last_row_ptr : nullptr);
+    launch_kernel(lsm_local_topk_kernel, grid, dim3(SCAN_THREADS), 0, s, logits, ld, vocab, stats, nseg, k, cand,
+                  level == 0 ? last_row_ptr : nullptr);
     const size_t shmem = static_cast<size_t>(rows) * nseg * k * sizeof(unsigned long long);
     static size_t configured = 0;
     if (shmem > 48 * 1024 && shmem > configured) {
@@ -360,10 +361,8 @@ void launch_draft_topk_expand(const DraftTreeState& st, const bf16* logits, int 
                                         static_cast<int>(shmem)));
         configured = shmem;
     }
-    draft_expand_kernel<<<1, 32 * (k < 4 ? 4 : k), shmem, s>>>(st, cand, nseg, logits, ld, stats, level, h_rows, h_ld,
-                                                               last_row_ptr, hid_out, hid_ld, hidden);
-    CUDA_CHECK(cudaGetLastError());
-    runtime().launches++;
+    launch_kernel(draft_expand_kernel, dim3(1), dim3(32 * (k < 4 ? 4 : k)), shmem, s, st, cand, nseg, logits, ld, stats,
+                  level, h_rows, h_ld, last_row_ptr, hid_out, hid_ld, hidden);
 }
 
 void launch_tree_finalize(const DraftTreeState& st, const int32_t* cache_length, int32_t* tree_draft_ids,
@@ -371,8 +370,6 @@ void launch_tree_finalize(const DraftTreeState& st, const int32_t* cache_length,
     CPM_REQUIRE(st.total_tried <= 2048, "draft: total tried candidates exceed 2048");
     CPM_REQUIRE(st.tree_size >= 2 && st.tree_size <= 64, "draft: tree_size must be in [2,64]");
     CPM_REQUIRE(st.tree_size - 1 <= st.total_tried, "draft: tree larger than the candidate set");
-    tree_finalize_kernel<<<1, 512, 0, s>>>(st, cache_length, tree_draft_ids, tree_pos, tree_mask, tree_parent,
-                                           runtime().d_error);
-    CUDA_CHECK(cudaGetLastError());
-    runtime().launches++;
+    launch_kernel(tree_finalize_kernel, dim3(1), dim3(512), 0, s, st, cache_length, tree_draft_ids, tree_pos, tree_mask,
+                  tree_parent, runtime().d_error);
 }

@@ -37,6 +37,7 @@ __device__ __forceinline__ float block_sum(float v, float* sh) {
 template <bool ADD>
 __global__ void rms_norm_kernel(bf16* __restrict__ x, int ldx, const bf16* __restrict__ delta, float delta_scale,
                                 const bf16* __restrict__ w, bf16* __restrict__ y, int ldy, int dim, float eps) {
+    grid_dependency_sync();
     __shared__ float sh[32];
     const size_t base = static_cast<size_t>(blockIdx.x) * ldx;
     const size_t dbase = static_cast<size_t>(blockIdx.x) * dim;
@@ -71,6 +72,7 @@ __global__ void rms_norm_kernel(bf16* __restrict__ x, int ldx, const bf16* __res
 
 __global__ void embedding_kernel(const int32_t* __restrict__ ids, const bf16* __restrict__ table,
                                  bf16* __restrict__ out, int ld_out, int dim, float scale) {
+    grid_dependency_sync();
     const int row = blockIdx.x;
     const size_t src = static_cast<size_t>(ids[row]) * dim;
     const size_t dst = static_cast<size_t>(row) * ld_out;
@@ -92,6 +94,7 @@ __global__ void rope_append_kernel(bf16* __restrict__ qkv, int hq, int hkv, int 
                                    int pos_step, bf16* __restrict__ k_cache, bf16* __restrict__ v_cache,
                                    const int32_t* __restrict__ kv_len, int kv_off,
                                    const int32_t* __restrict__ n_valid) {
+    grid_dependency_sync();
     const int r = blockIdx.x;
     const int half = d >> 1;
     const int ld = (hq + 2 * hkv) * d;
@@ -129,6 +132,7 @@ __global__ void rope_append_kernel(bf16* __restrict__ qkv, int hq, int hkv, int 
 }
 
 __global__ void silu_gate_kernel(const bf16* __restrict__ gate_up, bf16* __restrict__ out, int inter) {
+    grid_dependency_sync();
     const int r = blockIdx.y;
     const int c = (blockIdx.x * blockDim.x + threadIdx.x) * 2;
     if (c >= inter) return;
@@ -149,6 +153,7 @@ __global__ void silu_gate_kernel(const bf16* __restrict__ gate_up, bf16* __restr
 
 __global__ void add_scaled_kernel(bf16* __restrict__ x, const bf16* __restrict__ a, const bf16* __restrict__ b,
                                   float scale_b, size_t n) {
+    grid_dependency_sync();
     const size_t i = (static_cast<size_t>(blockIdx.x) * blockDim.x + threadIdx.x) * 2;
     if (i >= n) return;
     const __nv_bfloat162 av = *reinterpret_cast<const __nv_bfloat162*>(a + i);
@@ -164,12 +169,14 @@ __global__ void add_scaled_kernel(bf16* __restrict__ x, const bf16* __restrict__
 }
 
 __global__ void scale_kernel(bf16* __restrict__ out, const bf16* __restrict__ in, float scale, size_t n) {
+    grid_dependency_sync();
     const size_t i = static_cast<size_t>(blockIdx.x) * blockDim.x + threadIdx.x;
     if (i < n) out[i] = __float2bfloat16(__bfloat162float(in[i]) * scale);
 }
 
 // Row argmax over bf16 logits, lowest index wins ties.
 __global__ void argmax_kernel(const bf16* __restrict__ logits, int vocab, int ld, int32_t* __restrict__ out) {
+    grid_dependency_sync();
     __shared__ float sv[32];
     __shared__ int si[32];
     const bf16* row = logits + static_cast<size_t>(blockIdx.x) * ld;
@@ -208,27 +215,21 @@ void launch_rms_norm(const bf16* x, int ldx, const bf16* w, bf16* y, int ldy, in
                      cudaStream_t s) {
     if (rows <= 0) return;
     CPM_REQUIRE(dim % 2 == 0 && ldx % 2 == 0 && ldy % 2 == 0, "rms_norm: dims must be even");
-    rms_norm_kernel<false><<<rows, 256, 0, s>>>(const_cast<bf16*>(x), ldx, nullptr, 1.f, w, y, ldy, dim, eps);
-    CUDA_CHECK(cudaGetLastError());
-    runtime().launches++;
+    launch_kernel(rms_norm_kernel<false>, dim3(rows), dim3(256), 0, s, const_cast<bf16*>(x), ldx, nullptr, 1.f, w, y, ldy, dim, eps);
 }
 
 void launch_add_rms_norm(bf16* x, const bf16* delta, float delta_scale, const bf16* w, bf16* y, int rows, int dim,
                          float eps, cudaStream_t s) {
     if (rows <= 0) return;
     CPM_REQUIRE(dim % 2 == 0, "rms_norm: dim must be even");
-    rms_norm_kernel<true><<<rows, 256, 0, s>>>(x, dim, delta, delta_scale, w, y, dim, dim, eps);
-    CUDA_CHECK(cudaGetLastError());
-    runtime().launches++;
+    launch_kernel(rms_norm_kernel<true>, dim3(rows), dim3(256), 0, s, x, dim, delta, delta_scale, w, y, dim, dim, eps);
 }
 
 void launch_embedding(const int32_t* ids, const bf16* table, bf16* out, int ld_out, int rows, int dim, float scale,
                       cudaStream_t s) {
     if (rows <= 0) return;
     CPM_REQUIRE(dim % 8 == 0 && ld_out % 8 == 0, "embedding: dim must be a multiple of 8");
-    embedding_kernel<<<rows, 128, 0, s>>>(ids, table, out, ld_out, dim, scale);
-    CUDA_CHECK(cudaGetLastError());
-    runtime().launches++;
+    launch_kernel(embedding_kernel, dim3(rows), dim3(128), 0, s, ids, table, out, ld_out, dim, scale);
 }
 
 void launch_rope_append(bf16* qkv, int rows, int hq, int hkv, int d, const float* inv_freq, const int32_t* pos,
@@ -236,39 +237,29 @@ void launch_rope_append(bf16* qkv, int rows, int hq, int hkv, int d, const float
                         const int32_t* kv_len, int kv_off, const int32_t* n_valid, cudaStream_t s) {
     if (rows <= 0) return;
     CPM_REQUIRE(pos != nullptr || pos_base != nullptr, "rope: no positions given");
-    rope_append_kernel<<<rows, 256, 0, s>>>(qkv, hq, hkv, d, inv_freq, pos, pos_base, pos_off, pos_step, k_cache,
-                                           v_cache, kv_len, kv_off, n_valid);
-    CUDA_CHECK(cudaGetLastError());
-    runtime().launches++;
+    launch_kernel(rope_append_kernel, dim3(rows), dim3(256), 0, s, qkv, hq, hkv, d, inv_freq, pos, pos_base, pos_off,
+                  pos_step, k_cache, v_cache, kv_len, kv_off, n_valid);
 }
 
 void launch_silu_gate(const bf16* gate_up, bf16* out, int rows, int inter, cudaStream_t s) {
     if (rows <= 0) return;
     CPM_REQUIRE(inter % 2 == 0, "silu_gate: width must be even");
     dim3 grid(ceil_div(inter / 2, 256), rows);
-    silu_gate_kernel<<<grid, 256, 0, s>>>(gate_up, out, inter);
-    CUDA_CHECK(cudaGetLastError());
-    runtime().launches++;
+    launch_kernel(silu_gate_kernel, grid, dim3(256), 0, s, gate_up, out, inter);
 }
 
 void launch_add_scaled(bf16* x, const bf16* a, const bf16* b, float scale_b, int rows, int dim, cudaStream_t s) {
     if (rows <= 0) return;
     const size_t n = static_cast<size_t>(rows) * dim;
-    add_scaled_kernel<<<static_cast<unsigned>((n / 2 + 255) / 256), 256, 0, s>>>(x, a, b, scale_b, n);
-    CUDA_CHECK(cudaGetLastError());
-    runtime().launches++;
+    launch_kernel(add_scaled_kernel, dim3(static_cast<unsigned>((n / 2 + 255) / 256)), dim3(256), 0, s, x, a, b, scale_b, n);
 }
 
 void launch_scale(bf16* out, const bf16* in, float scale, size_t n, cudaStream_t s) {
     if (n == 0) return;
-    scale_kernel<<<static_cast<unsigned>((n + 255) / 256), 256, 0, s>>>(out, in, scale, n);
-    CUDA_CHECK(cudaGetLastError());
-    runtime().launches++;
+    launch_kernel(scale_kernel, dim3(static_cast<unsigned>((n + 255) / 256)), dim3(256), 0, s, out, in, scale, n);
 }
 
 void launch_argmax(const bf16* logits, int rows, int vocab, int ld, int32_t* out, cudaStream_t s) {
     if (rows <= 0) return;
-    argmax_kernel<<<rows, 1024, 0, s>>>(logits, vocab, ld, out);
-    CUDA_CHECK(cudaGetLastError());
-    runtime().launches++;
+    launch_kernel(argmax_kernel, dim3(rows), dim3(1024), 0, s, logits, vocab, ld, out);
 }

@@ -11,6 +11,7 @@
 namespace {
 
 __global__ void state_sync_kernel(int32_t* st, const int32_t* cache_length, int32_t* tree_ids, int fused) {
+    grid_dependency_sync();
     // S_L=0, S_NPREV=1, S_BASE=2, S_LASTROW=3, S_ACCEPT=4
     const int n = st[4];
     int L;
@@ -28,6 +29,7 @@ __global__ void state_sync_kernel(int32_t* st, const int32_t* cache_length, int3
 
 __global__ void publish_kernel(const int32_t* result, const int32_t* tokens, const int* error, int32_t* st,
                                int32_t* out) {
+    grid_dependency_sync();
     const int n = result[0];
     if (threadIdx.x == 0) {
         st[4] = n;
@@ -620,9 +622,7 @@ void Engine::draft(int32_t* tree_ids, int32_t* tree_pos, const int32_t* cache_le
                          mc_.scale_embed, s);
         draft_first(num_history_, s);
     } else {
-        state_sync_kernel<<<1, 1, 0, s>>>(st_, cache_length, tree_ids, 0);
-        CUDA_CHECK(cudaGetLastError());
-        runtime().launches++;
+        launch_kernel(state_sync_kernel, dim3(1), dim3(1), 0, s, st_, cache_length, tree_ids, 0);
         draft_catchup(s);
     }
     draft_levels(tree_ids, tree_pos, cache_length, tree_mask, tree_parent, first_draft_, s);
@@ -660,9 +660,7 @@ void Engine::accept_and_fix(int T, int32_t* pred, const int32_t* gt, const int32
     f.eagle_pos = eagle_pos_;
     f.hidden = mc_.hidden;
     launch_accept_fixup(f, s);
-    publish_kernel<<<1, 32, 0, s>>>(accept_result_, pred, runtime().d_error, st_, d_publish_);
-    CUDA_CHECK(cudaGetLastError());
-    runtime().launches++;
+    launch_kernel(publish_kernel, dim3(1), dim3(32), 0, s, accept_result_, pred, runtime().d_error, st_, d_publish_);
 }
 
 int Engine::verify_and_fix(int T, int32_t* pred, const int32_t* gt, const int32_t* pos, const int32_t* cache_length,
@@ -702,9 +700,7 @@ void Engine::begin_generation(int prefix_length, int32_t root_token) {
 // target verify forward, argmax, acceptance, fix-up, publish.
 void Engine::enqueue_step(bool first, cudaStream_t s) {
     const int T = ec_.tree_size, H = mc_.hidden;
-    state_sync_kernel<<<1, 1, 0, s>>>(st_, nullptr, t_ids_, 1);
-    CUDA_CHECK(cudaGetLastError());
-    runtime().launches++;
+    launch_kernel(state_sync_kernel, dim3(1), dim3(1), 0, s, st_, static_cast<const int32_t*>(nullptr), t_ids_, 1);
     if (first) {
         launch_embedding(t_ids_, embed_, prev_embed_ + static_cast<size_t>(num_prev_ - 1) * H, H, 1, H, mc_.scale_embed, s);
         draft_first(num_history_, s);

@@ -19,6 +19,8 @@
 // tile's K range writes its fp32 partial to a workspace slot and bumps the
 // tile's ticket; the last piece to arrive sums the slots in a fixed order
 // (deterministic) and writes the bf16 result.  No CTA ever waits on another.
+#include <algorithm>
+
 #include "common.cuh"
 #include "ptx.cuh"
 
@@ -92,6 +94,7 @@ linear_umma_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_consta
     const int lane = threadIdx.x & 31;
     const int G = gridDim.x;
     const int g = blockIdx.x;
+    grid_dep_trigger();
 
     if (threadIdx.x == 0) {
         for (int s = 0; s < C::STAGES; ++s) {
@@ -121,6 +124,9 @@ linear_umma_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_consta
     it.u = (a.total_units * g) / G;
     it.u_end = (a.total_units * (g + 1)) / G;
     it.kblocks = a.kblocks;
+    // Weights never depend on the previous kernel: the producer fills the ring with W tiles
+    // first, and only then does the CTA wait for the predecessor grid (activations, workspace).
+    if (warp != 0) grid_dep_wait();
 
     if (warp == 0) {
         // ------------------------------------------------ TMA producer
@@ -129,19 +135,40 @@ linear_umma_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_consta
             uint32_t phase = 0;
             int tile, kb0, kb1;
             bool ok = true;
+            // ---- phase 1: W tiles of the first STAGES k-blocks, before the dependency wait
+            int pre = 0;
+            {
+                SegIter pit = it;
+                while (pre < C::STAGES && pit.next(tile, kb0, kb1)) {
+                    const int n_tile = tile % a.n_tiles;
+                    for (int kb = kb0; kb < kb1 && pre < C::STAGES; ++kb, ++pre) {
+                        ptx::mbar_arrive_expect_tx(&full[pre], (a.debug & 1) ? W_TILE_BYTES : C::STAGE_BYTES);
+                        ptx::tma_load_2d(tiles + pre * C::STAGE_BYTES, &tm_w, &full[pre], kb * BLOCK_K, n_tile * BLOCK_N);
+                    }
+                }
+            }
+            grid_dep_wait();
+            // ---- phase 2: the matching X tiles, then the steady-state ring
+            int issued = 0;
             while (ok && it.next(tile, kb0, kb1)) {
                 const int m_tile = tile / a.n_tiles;
                 const int n_tile = tile - m_tile * a.n_tiles;
-                for (int kb = kb0; kb < kb1; ++kb) {
-                    if (!ptx::mbar_wait(&empty[stage], phase ^ 1, abort_flag)) { ok = false; break; }
+                for (int kb = kb0; kb < kb1; ++kb, ++issued) {
                     uint8_t* dst = tiles + stage * C::STAGE_BYTES;
-                    if (a.debug & 1) {
-                        ptx::mbar_arrive_expect_tx(&full[stage], W_TILE_BYTES);
-                        ptx::tma_load_2d(dst, &tm_w, &full[stage], kb * BLOCK_K, n_tile * BLOCK_N);
+                    if (issued < pre) {
+                        if (!(a.debug & 1)) {
+                            ptx::tma_load_2d(dst + W_TILE_BYTES, &tm_x, &full[stage], kb * BLOCK_K, m_tile * MT);
+                        }
                     } else {
-                        ptx::mbar_arrive_expect_tx(&full[stage], C::STAGE_BYTES);
-                        ptx::tma_load_2d(dst, &tm_w, &full[stage], kb * BLOCK_K, n_tile * BLOCK_N);
-                        ptx::tma_load_2d(dst + W_TILE_BYTES, &tm_x, &full[stage], kb * BLOCK_K, m_tile * MT);
+                        if (!ptx::mbar_wait(&empty[stage], phase ^ 1, abort_flag)) { ok = false; break; }
+                        if (a.debug & 1) {
+                            ptx::mbar_arrive_expect_tx(&full[stage], W_TILE_BYTES);
+                            ptx::tma_load_2d(dst, &tm_w, &full[stage], kb * BLOCK_K, n_tile * BLOCK_N);
+                        } else {
+                            ptx::mbar_arrive_expect_tx(&full[stage], C::STAGE_BYTES);
+                            ptx::tma_load_2d(dst, &tm_w, &full[stage], kb * BLOCK_K, n_tile * BLOCK_N);
+                            ptx::tma_load_2d(dst + W_TILE_BYTES, &tm_x, &full[stage], kb * BLOCK_K, m_tile * MT);
+                        }
                     }
                     if (++stage == C::STAGES) { stage = 0; phase ^= 1; }
                 }
@@ -151,6 +178,9 @@ linear_umma_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_consta
                 const long long t0 = clock64();
                 while (clock64() - t0 < 2000000LL) {}
             }
+        }
+        else {
+            grid_dep_wait();  // the other lanes of the producer warp
         }
     } else if (warp == 1) {
         // ------------------------------------------------ MMA issuer
@@ -211,8 +241,7 @@ linear_umma_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_consta
             ptx::tc_fence_after();
             __syncwarp();  // TMEM loads below are warp-collective
             const uint32_t t_addr = tmem_base + (static_cast<uint32_t>(q * 32) << 16) + acc * MT;
-            // partial slot layout: [128 features][MT tokens] fp32, so a thread owns one contiguous row
-            float* my_row = my_ws + row * MT;
+            // partial slot layout: [MT tokens][128 features] fp32: a warp touches one 128-byte line per token
 #pragma unroll 1
             for (int c0 = 0; c0 < MT; c0 += 16) {
                 if (c0 >= m_cnt || (a.debug & 2)) break;  // uniform across the CTA
@@ -229,10 +258,10 @@ linear_umma_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_consta
                             }
                         }
                     }
-                } else {
+                } else if (!(a.debug & 4)) {
 #pragma unroll
-                    for (int c = 0; c < 16; c += 4) {
-                        *reinterpret_cast<uint4*>(my_row + c0 + c) = make_uint4(r[c], r[c + 1], r[c + 2], r[c + 3]);
+                    for (int c = 0; c < 16; ++c) {
+                        if (c0 + c < m_cnt) my_ws[(c0 + c) * BLOCK_N + row] = __uint_as_float(r[c]);
                     }
                 }
             }
@@ -241,7 +270,7 @@ linear_umma_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_consta
             acc ^= 1;
             if (acc == 0) acc_phase ^= 1;
 
-            if (!complete && !(a.debug & 2)) {
+            if (!complete && !(a.debug & (2 | 8))) {
                 const long long tile_u0 = static_cast<long long>(tile) * a.kblocks;
                 const int g_first = unit_owner(tile_u0, a.total_units, G);
                 const int g_last = unit_owner(tile_u0 + a.kblocks - 1, a.total_units, G);
@@ -257,34 +286,39 @@ linear_umma_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_consta
                 ptx::named_bar_sync(1, 128);
                 const bool is_last = (*s_last != 0);
                 ptx::named_bar_sync(1, 128);  // everyone has read s_last before it can change
-                if (is_last) {
+                if (is_last && !(a.debug & 16)) {
                     __threadfence();
-                    // sum the pieces in CTA order (deterministic); 16 tokens at a time, four
-                    // independent 16-byte loads per piece in flight
+                    // sum the pieces in CTA order (deterministic): CH tokens per pass, the coalesced
+                    // loads of up to four pieces (4 * CH per thread) in flight before the first add
+                    constexpr int CH = (MT < 32) ? MT : 32;
 #pragma unroll 1
-                    for (int c0 = 0; c0 < m_cnt; c0 += 16) {
-                        float sum[16];
+                    for (int c0 = 0; c0 < m_cnt; c0 += CH) {
+                        float sum[CH];
 #pragma unroll
-                        for (int c = 0; c < 16; ++c) sum[c] = 0.f;
-#pragma unroll 2
-                        for (int gg = g_first; gg <= g_last; ++gg) {
-                            const float* ws = a.workspace +
-                                              (static_cast<size_t>(gg) * 2 + (gg == g_first ? 1 : 0)) * (MT * BLOCK_N) +
-                                              row * MT + c0;
-                            float4 v[4];
+                        for (int c = 0; c < CH; ++c) sum[c] = 0.f;
+#pragma unroll 1
+                        for (int g0 = g_first; g0 <= g_last; g0 += 4) {
+                            float v[4][CH];
 #pragma unroll
-                            for (int j = 0; j < 4; ++j) v[j] = __ldcg(reinterpret_cast<const float4*>(ws) + j);
+                            for (int s = 0; s < 4; ++s) {
+                                const int gg = g0 + s;
+                                const float* ws = a.workspace +
+                                                  (static_cast<size_t>(gg) * 2 + (gg == g_first ? 1 : 0)) * (MT * BLOCK_N) +
+                                                  static_cast<size_t>(c0) * BLOCK_N + row;
 #pragma unroll
-                            for (int j = 0; j < 4; ++j) {
-                                sum[4 * j + 0] += v[j].x;
-                                sum[4 * j + 1] += v[j].y;
-                                sum[4 * j + 2] += v[j].z;
-                                sum[4 * j + 3] += v[j].w;
+                                for (int c = 0; c < CH; ++c) {
+                                    v[s][c] = (gg <= g_last && c0 + c < m_cnt) ? __ldcg(ws + c * BLOCK_N) : 0.f;
+                                }
+                            }
+#pragma unroll
+                            for (int s = 0; s < 4; ++s) {
+#pragma unroll
+                                for (int c = 0; c < CH; ++c) sum[c] += v[s][c];
                             }
                         }
                         if (n < a.N) {
 #pragma unroll
-                            for (int c = 0; c < 16; ++c) {
+                            for (int c = 0; c < CH; ++c) {
                                 if (c0 + c < m_cnt) {
                                     a.y[static_cast<size_t>(m_base + c0 + c) * a.ldy + n] =
                                         __float2bfloat16(sum[c] + bias_v);
@@ -315,9 +349,7 @@ void launch_mt(const LinearPlan& p, const LinearArgs& args, cudaStream_t stream)
                                         C::SMEM_BYTES));
         configured = true;
     }
-    linear_umma_kernel<MT><<<p.grid, NUM_THREADS, C::SMEM_BYTES, stream>>>(p.tm_w, p.tm_x, args);
-    CUDA_CHECK(cudaGetLastError());
-    runtime().launches++;
+    launch_kernel(linear_umma_kernel<MT>, dim3(p.grid), dim3(NUM_THREADS), C::SMEM_BYTES, stream, p.tm_w, p.tm_x, args);
 }
 
 }  // namespace
@@ -332,6 +364,36 @@ int linear_pick_mt(int M) {
 
 size_t linear_workspace_bytes(int mt, int grid) {
     return static_cast<size_t>(grid) * 2 * mt * BLOCK_N * sizeof(float);
+}
+
+// Number of CTAs for a decode-shaped launch (one token tile).  Every CTA gets the same
+// share of the (tile, k-block) line; the model below trades streaming time (per-SM and
+// HBM limits as measured on B200) against the cost of split-K fix-ups, which vanish when
+// the shares line up with tile boundaries.
+static int pick_grid(int n_tiles, int kblocks, int m_valid, int limit) {
+    const long long units = static_cast<long long>(n_tiles) * kblocks;
+    const double tile_bytes = 16384.0;        // one W k-block
+    const double sm_rate = 55e9, hbm_rate = 6.3e12;
+    double best_t = 1e30;
+    int best_g = 1;
+    for (int g = 1; g <= limit && g <= units; ++g) {
+        const long long per = (units + g - 1) / g;
+        const double rate = std::min(sm_rate, hbm_rate / g);
+        double t = per * tile_bytes / rate;
+        const bool aligned_whole = (units % g == 0) && ((units / g) % kblocks == 0);
+        if (!aligned_whole) {
+            const double share = static_cast<double>(units) / g;
+            int nseg;
+            if (units % g == 0 && kblocks % (units / g) == 0) nseg = static_cast<int>(kblocks / (units / g));
+            else nseg = static_cast<int>(kblocks / share) + 2;
+            t += 4.5e-6 + 1.0e-6 * ((m_valid + 31) / 32) * ((nseg + 3) / 4);
+        }
+        if (t < best_t - 1e-9) {
+            best_t = t;
+            best_g = g;
+        }
+    }
+    return best_g;
 }
 
 LinearPlan make_linear_plan(const bf16* x, int x_rows, const bf16* w, int M, int N, int K, bf16* y, int ldy,
@@ -351,6 +413,7 @@ LinearPlan make_linear_plan(const bf16* x, int x_rows, const bf16* w, int M, int
     long long grid = units / 4;  // at least four k-blocks per CTA
     if (grid < 1) grid = 1;
     if (grid > grid_limit) grid = grid_limit;
+    if (m_tiles == 1 && grid_limit >= 64) grid = pick_grid(n_tiles, kblocks, M, static_cast<int>(grid));
     p.grid = static_cast<int>(grid);
     p.tm_w = make_tmap_2d(w, K, N, static_cast<uint64_t>(K) * 2, BLOCK_K, BLOCK_N);
     p.tm_x = make_tmap_2d(x, K, x_rows, static_cast<uint64_t>(K) * 2, BLOCK_K, p.mt);

@@ -46,6 +46,7 @@ Runtime& runtime() {
                                      std::to_string(prop.major * 10 + prop.minor) + ")");
         }
         rt.num_sms = prop.multiProcessorCount;
+        rt.pdl = (getenv("CPMCU_NO_PDL") == nullptr);
         CUDA_CHECK(cudaStreamCreate(&rt.stream));
         CUDA_CHECK(cudaMalloc(&rt.d_error, sizeof(int)));
         CUDA_CHECK(cudaMemset(rt.d_error, 0, sizeof(int)));

@@ -82,6 +82,7 @@ tree_attn_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant
     const int ch = warp >> 2;                    // column half of the key tile
     const int row = (warp & 3) * 32 + lane;      // query row of the tile == TMEM lane
     const bool leader = (tid == 0);
+    grid_dep_trigger();
     const int mt = blockIdx.x % a.num_mtiles;
     const int h = blockIdx.x / a.num_mtiles;  // kv head
     const int split = blockIdx.y;
@@ -112,6 +113,7 @@ tree_attn_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant
     const uint32_t lane_sel = static_cast<uint32_t>((warp & 3) * 32) << 16;
     const uint32_t tmem_s = tmem_base + lane_sel + ch * 64;         // this thread's 64 score columns
     const uint32_t tmem_o = tmem_base + lane_sel + KEYS + ch * 64;  // this thread's 64 output columns
+    grid_dep_wait();  // everything above overlaps the previous kernel's tail
 
     // ---- geometry of this tile
     const int kv_total = *a.kv_len + a.kv_len_add;
@@ -379,6 +381,7 @@ tree_attn_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant
 // every lane accumulates four output columns with independent loads in flight.
 __global__ void attn_combine_kernel(const float* __restrict__ ws_o, const float* __restrict__ ws_ml, int nsplit,
                                     int rows, int hq, float scale_log2, bf16* __restrict__ out, int out_ld) {
+    grid_dependency_sync();
     const int row = blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
     const int lane = threadIdx.x & 31;
     if (row >= rows) return;
@@ -472,14 +475,10 @@ void launch_tree_attention(const AttnPlan& p, cudaStream_t s) {
     a.error = runtime().d_error;
     CPM_REQUIRE(p.splits == 1 || (p.ws_o != nullptr && p.ws_ml != nullptr), "attention: split-KV needs a workspace");
     dim3 grid(a.num_mtiles * p.hkv, p.splits);
-    tree_attn_kernel<<<grid, NTHREADS, SMEM_TOTAL, s>>>(p.tm_q, p.tm_k, p.tm_v, a);
-    CUDA_CHECK(cudaGetLastError());
-    runtime().launches++;
+    launch_kernel(tree_attn_kernel, grid, dim3(NTHREADS), SMEM_TOTAL, s, p.tm_q, p.tm_k, p.tm_v, a);
     if (p.splits > 1) {
         const int rows = p.tq * p.hq;
-        attn_combine_kernel<<<ceil_div(rows, 4), 128, 0, s>>>(p.ws_o, p.ws_ml, p.splits, rows, p.hq, a.scale_log2, p.out,
-                                                             p.out_ld);
-        CUDA_CHECK(cudaGetLastError());
-    runtime().launches++;
+        launch_kernel(attn_combine_kernel, dim3(ceil_div(rows, 4)), dim3(128), 0, s, p.ws_o, p.ws_ml, p.splits, rows, p.hq,
+                      a.scale_log2, p.out, p.out_ld);
     }
 }
