@@ -419,7 +419,8 @@ int cpmcu_silu_gate(const void* gate_up, void* out, int rows, int inter) {
 
 int cpmcu_argmax(const void* logits, int rows, int vocab, int32_t* out) {
     return guarded([&] {
-        launch_argmax(static_cast<const bf16*>(logits), rows, vocab, vocab, out, runtime().stream);
+        DeviceBuf ws(argmax_workspace_bytes(rows, vocab));
+        launch_argmax(static_cast<const bf16*>(logits), rows, vocab, vocab, out, ws.p, runtime().stream);
         sync_and_check("argmax");
         return 0;
     });

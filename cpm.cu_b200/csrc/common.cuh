@@ -153,7 +153,8 @@ void launch_silu_gate(const bf16* gate_up, bf16* out, int rows, int inter, cudaS
 void launch_add_scaled(bf16* x, const bf16* a, const bf16* b, float scale_b, int rows, int dim,
                        cudaStream_t s);  // x = a + b*scale
 void launch_scale(bf16* out, const bf16* in, float scale, size_t n, cudaStream_t s);
-void launch_argmax(const bf16* logits, int rows, int vocab, int ld, int32_t* out, cudaStream_t s);
+size_t argmax_workspace_bytes(int rows, int vocab);
+void launch_argmax(const bf16* logits, int rows, int vocab, int ld, int32_t* out, void* workspace, cudaStream_t s);
 
 // ---------------------------------------------------------------- attention
 struct AttnPlan {

@@ -84,32 +84,46 @@ __global__ void lsm_stats_kernel(const bf16* __restrict__ logits, int ld, int vo
     }
 }
 
-// Row-wide log-sum-exp offset from the segment partials (fixed order => deterministic).
-__device__ __forceinline__ void row_offset(const float2* __restrict__ st, int nseg, float& mx, float& logsum) {
+// Row-wide log-sum-exp offset from the segment partials, computed by one CTA with a
+// fixed reduction tree (deterministic): returns (max, log(sum exp(x - max))) to all threads.
+__device__ __forceinline__ float2 row_offset_block(const float2* __restrict__ st, int nseg, float* sh) {
     float m = -INFINITY;
-    for (int s = 0; s < nseg; ++s) m = fmaxf(m, st[s].x);
+    for (int s = threadIdx.x; s < nseg; s += blockDim.x) m = fmaxf(m, st[s].x);
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) m = fmaxf(m, __shfl_xor_sync(0xffffffffu, m, o));
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, nw = blockDim.x >> 5;
+    if (lane == 0) sh[warp] = m;
+    __syncthreads();
+    m = sh[0];
+    for (int w = 1; w < nw; ++w) m = fmaxf(m, sh[w]);
+    __syncthreads();
     float sum = 0.f;
-    for (int s = 0; s < nseg; ++s) sum += st[s].y * expf(st[s].x - m);
-    mx = m;
-    logsum = logf(sum);
+    for (int s = threadIdx.x; s < nseg; s += blockDim.x) {
+        const float2 v = st[s];
+        sum += v.y * expf(v.x - m);
+    }
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) sum += __shfl_xor_sync(0xffffffffu, sum, o);
+    if (lane == 0) sh[warp] = sum;
+    __syncthreads();
+    sum = sh[0];
+    for (int w = 1; w < nw; ++w) sum += sh[w];
+    __syncthreads();
+    return make_float2(m, logf(sum));
 }
 
 // ---- pass 2: lp = bf16(x - max - log(sum)); segment-local top-k by (lp desc, index asc)
 __global__ void lsm_local_topk_kernel(const bf16* __restrict__ logits, int ld, int vocab,
                                       const float2* __restrict__ stats, int nseg, int k,
-                                      unsigned long long* __restrict__ cand, const int32_t* __restrict__ row0) {
+                                      unsigned long long* __restrict__ cand, const int32_t* __restrict__ row0,
+                                      float2* __restrict__ rowoff) {
     grid_dependency_sync();
     __shared__ unsigned long long sh_best[SCAN_THREADS / 32];
-    __shared__ float sh_off[2];
+    __shared__ float sh_red[SCAN_THREADS / 32];
     const int row = blockIdx.y, seg = blockIdx.x;
-    if (threadIdx.x == 0) {
-        float mx, ls;
-        row_offset(stats + static_cast<size_t>(row) * nseg, nseg, mx, ls);
-        sh_off[0] = mx;
-        sh_off[1] = ls;
-    }
-    __syncthreads();
-    const float mx = sh_off[0], ls = sh_off[1];
+    const float2 off = row_offset_block(stats + static_cast<size_t>(row) * nseg, nseg, sh_red);
+    if (seg == 0 && threadIdx.x == 0) rowoff[row] = off;  // the expansion kernel reuses the exact values
+    const float mx = off.x, ls = off.y;
     const bf16* x = logits + static_cast<size_t>(row + (row0 ? *row0 : 0)) * ld;
     const int begin = seg * SEG;
     const int end = min(begin + SEG, vocab);
@@ -166,7 +180,7 @@ __device__ unsigned long long warp_select(unsigned long long* keys, int n, int k
 // level d >= 1: rows = k; cumulative scores, history append, top-k of k*k,
 //               parent / mask / hidden / token bookkeeping for the next level.
 __global__ void draft_expand_kernel(DraftTreeState st, const unsigned long long* __restrict__ cand, int nseg,
-                                    const bf16* __restrict__ logits, int ld, const float2* __restrict__ stats,
+                                    const bf16* __restrict__ logits, int ld, const float2* __restrict__ rowoff,
                                     int level, const bf16* __restrict__ h_rows, int h_ld,
                                     const int32_t* __restrict__ last_row_ptr, bf16* __restrict__ hid_out,
                                     int hid_ld, int hidden) {
@@ -189,8 +203,7 @@ __global__ void draft_expand_kernel(DraftTreeState st, const unsigned long long*
         const unsigned long long got = warp_select(mykeys, per_row, k, lane);
         if (lane < k) {
             const int idx = key_index(got);
-            float mx, ls;
-            row_offset(stats + static_cast<size_t>(warp) * nseg, nseg, mx, ls);
+            const float mx = rowoff[warp].x, ls = rowoff[warp].y;
             const int lrow = warp + ((level == 0 && last_row_ptr) ? *last_row_ptr : 0);
             const bf16 lp = __float2bfloat16(__bfloat162float(logits[static_cast<size_t>(lrow) * ld + idx]) - mx - ls);
             s_val[warp * k + lane] = lp;
@@ -333,8 +346,8 @@ int draft_num_segments(int vocab) { return ceil_div(vocab, SEG); }
 
 size_t draft_scan_workspace_bytes(int rows, int vocab, int k) {
     const int nseg = draft_num_segments(vocab);
-    return static_cast<size_t>(rows) * nseg * (sizeof(float2) + static_cast<size_t>(k) * sizeof(unsigned long long)) +
-           256;
+    (void)rows;
+    return static_cast<size_t>(32) * nseg * (sizeof(float2) + static_cast<size_t>(k) * sizeof(unsigned long long)) + 1024;
 }
 
 void launch_draft_topk_expand(const DraftTreeState& st, const bf16* logits, int ld, int vocab, int level,
@@ -346,13 +359,14 @@ void launch_draft_topk_expand(const DraftTreeState& st, const bf16* logits, int 
     CPM_REQUIRE(k >= 1 && k <= 32, "draft: topk_per_iter must be in [1,32]");
     CPM_REQUIRE(hidden % 8 == 0, "draft: hidden size must be a multiple of 8");
     float2* stats = reinterpret_cast<float2*>(scan_ws);
-    unsigned long long* cand = reinterpret_cast<unsigned long long*>(
-        reinterpret_cast<uint8_t*>(scan_ws) + align_up(static_cast<int64_t>(k) * nseg * sizeof(float2), 256));
+    float2* rowoff = reinterpret_cast<float2*>(reinterpret_cast<uint8_t*>(scan_ws) +
+                                               align_up(static_cast<int64_t>(32) * nseg * sizeof(float2), 256));
+    unsigned long long* cand = reinterpret_cast<unsigned long long*>(reinterpret_cast<uint8_t*>(rowoff) + 256);
     dim3 grid(nseg, rows);
     launch_kernel(lsm_stats_kernel, grid, dim3(SCAN_THREADS), 0, s, logits, ld, vocab, stats, nseg,
                   level == 0 ? last_row_ptr : nullptr);
-    launch_kernel(lsm_local_topk_kernel, grid, dim3(SCAN_THREADS), 0, s, logits, ld, vocab, stats, nseg, k, cand,
-                  level == 0 ? last_row_ptr : nullptr);
+    launch_kernel(lsm_local_topk_kernel, grid, dim3(SCAN_THREADS), 0, s, logits, ld, vocab, static_cast<const float2*>(stats),
+                  nseg, k, cand, level == 0 ? last_row_ptr : nullptr, rowoff);
     const size_t shmem = static_cast<size_t>(rows) * nseg * k * sizeof(unsigned long long);
     static size_t configured = 0;
     if (shmem > 48 * 1024 && shmem > configured) {
@@ -361,8 +375,9 @@ void launch_draft_topk_expand(const DraftTreeState& st, const bf16* logits, int 
                                         static_cast<int>(shmem)));
         configured = shmem;
     }
-    launch_kernel(draft_expand_kernel, dim3(1), dim3(32 * (k < 4 ? 4 : k)), shmem, s, st, cand, nseg, logits, ld, stats,
-                  level, h_rows, h_ld, last_row_ptr, hid_out, hid_ld, hidden);
+    launch_kernel(draft_expand_kernel, dim3(1), dim3(32 * (k < 4 ? 4 : k)), shmem, s, st,
+                  static_cast<const unsigned long long*>(cand), nseg, logits, ld, static_cast<const float2*>(rowoff), level,
+                  h_rows, h_ld, last_row_ptr, hid_out, hid_ld, hidden);
 }
 
 void launch_tree_finalize(const DraftTreeState& st, const int32_t* cache_length, int32_t* tree_draft_ids,

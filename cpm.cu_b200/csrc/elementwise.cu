@@ -34,7 +34,9 @@ __device__ __forceinline__ float block_sum(float v, float* sh) {
 }
 
 // y = x * rsqrt(mean(x^2) + eps) * w, optionally after x += round(delta * scale).
-template <bool ADD>
+// One CTA per row; every thread owns up to VPT 16-byte vectors of the row, loads them
+// all up front and keeps them in registers between the two passes.
+template <bool ADD, int VPT>
 __global__ void rms_norm_kernel(bf16* __restrict__ x, int ldx, const bf16* __restrict__ delta, float delta_scale,
                                 const bf16* __restrict__ w, bf16* __restrict__ y, int ldy, int dim, float eps) {
     grid_dependency_sync();
@@ -42,31 +44,54 @@ __global__ void rms_norm_kernel(bf16* __restrict__ x, int ldx, const bf16* __res
     const size_t base = static_cast<size_t>(blockIdx.x) * ldx;
     const size_t dbase = static_cast<size_t>(blockIdx.x) * dim;
     const size_t ybase = static_cast<size_t>(blockIdx.x) * ldy;
-    float ss = 0.f;
-    for (int i = threadIdx.x * 2; i < dim; i += blockDim.x * 2) {
-        __nv_bfloat162 v = *reinterpret_cast<const __nv_bfloat162*>(x + base + i);
-        if (ADD) {
-            __nv_bfloat162 dl = *reinterpret_cast<const __nv_bfloat162*>(delta + dbase + i);
-            if (delta_scale != 1.0f) {
-                dl.x = __float2bfloat16(__bfloat162float(dl.x) * delta_scale);
-                dl.y = __float2bfloat16(__bfloat162float(dl.y) * delta_scale);
-            }
-            v.x = __float2bfloat16(__bfloat162float(v.x) + __bfloat162float(dl.x));
-            v.y = __float2bfloat16(__bfloat162float(v.y) + __bfloat162float(dl.y));
-            *reinterpret_cast<__nv_bfloat162*>(x + base + i) = v;
+    const int nvec = dim >> 3;
+    uint4 xv[VPT], dv[VPT];
+#pragma unroll
+    for (int j = 0; j < VPT; ++j) {
+        const int v = threadIdx.x + j * blockDim.x;
+        if (v < nvec) {
+            xv[j] = *reinterpret_cast<const uint4*>(x + base + v * 8);
+            if (ADD) dv[j] = *reinterpret_cast<const uint4*>(delta + dbase + v * 8);
         }
-        const float a = __bfloat162float(v.x), b = __bfloat162float(v.y);
-        ss += a * a + b * b;
+    }
+    float ss = 0.f;
+#pragma unroll
+    for (int j = 0; j < VPT; ++j) {
+        const int v = threadIdx.x + j * blockDim.x;
+        if (v < nvec) {
+            bf16* xe = reinterpret_cast<bf16*>(&xv[j]);
+            if (ADD) {
+                const bf16* de = reinterpret_cast<const bf16*>(&dv[j]);
+#pragma unroll
+                for (int e = 0; e < 8; ++e) {
+                    bf16 dl = de[e];
+                    if (delta_scale != 1.0f) dl = __float2bfloat16(__bfloat162float(dl) * delta_scale);
+                    xe[e] = __float2bfloat16(__bfloat162float(xe[e]) + __bfloat162float(dl));
+                }
+                *reinterpret_cast<uint4*>(x + base + v * 8) = xv[j];
+            }
+#pragma unroll
+            for (int e = 0; e < 8; ++e) {
+                const float f = __bfloat162float(xe[e]);
+                ss += f * f;
+            }
+        }
     }
     ss = block_sum(ss, sh);
     const float rs = rsqrtf(ss / dim + eps);
-    for (int i = threadIdx.x * 2; i < dim; i += blockDim.x * 2) {
-        const __nv_bfloat162 v = *reinterpret_cast<const __nv_bfloat162*>(x + base + i);
-        const __nv_bfloat162 ww = *reinterpret_cast<const __nv_bfloat162*>(w + i);
-        __nv_bfloat162 o;
-        o.x = __float2bfloat16(rs * __bfloat162float(v.x) * __bfloat162float(ww.x));
-        o.y = __float2bfloat16(rs * __bfloat162float(v.y) * __bfloat162float(ww.y));
-        *reinterpret_cast<__nv_bfloat162*>(y + ybase + i) = o;
+#pragma unroll
+    for (int j = 0; j < VPT; ++j) {
+        const int v = threadIdx.x + j * blockDim.x;
+        if (v < nvec) {
+            const uint4 wv = *reinterpret_cast<const uint4*>(w + v * 8);
+            const bf16* xe = reinterpret_cast<const bf16*>(&xv[j]);
+            const bf16* we = reinterpret_cast<const bf16*>(&wv);
+            uint4 ov;
+            bf16* oe = reinterpret_cast<bf16*>(&ov);
+#pragma unroll
+            for (int e = 0; e < 8; ++e) oe[e] = __float2bfloat16(rs * __bfloat162float(xe[e]) * __bfloat162float(we[e]));
+            *reinterpret_cast<uint4*>(y + ybase + v * 8) = ov;
+        }
     }
 }
 
@@ -88,13 +113,16 @@ __global__ void embedding_kernel(const int32_t* __restrict__ ids, const bf16* __
 }
 
 // One CTA per token row.  q heads rotate in place; k heads rotate into the
-// cache; v heads are copied into the cache.
+// cache; v heads are copied into the cache.  The d/2 sines and cosines of the row's
+// position are computed once per CTA; each thread then rotates element pairs
+// (c, c+1) and (c + d/2, c + d/2 + 1) with 4-byte accesses.
 __global__ void rope_append_kernel(bf16* __restrict__ qkv, int hq, int hkv, int d, const float* __restrict__ inv_freq,
                                    const int32_t* __restrict__ pos, const int32_t* __restrict__ pos_base, int pos_off,
                                    int pos_step, bf16* __restrict__ k_cache, bf16* __restrict__ v_cache,
                                    const int32_t* __restrict__ kv_len, int kv_off,
                                    const int32_t* __restrict__ n_valid) {
     grid_dependency_sync();
+    __shared__ float s_cos[128], s_sin[128];
     const int r = blockIdx.x;
     const int half = d >> 1;
     const int ld = (hq + 2 * hkv) * d;
@@ -103,23 +131,33 @@ __global__ void rope_append_kernel(bf16* __restrict__ qkv, int hq, int hkv, int 
     const bool store_kv = (n_valid == nullptr) || (r < *n_valid);
     const long long kv_row = static_cast<long long>(*kv_len) + kv_off + r;
     const int kv_dim = hkv * d;
-    for (int i = threadIdx.x; i < (hq + hkv) * half; i += blockDim.x) {
-        const int h = i / half, c = i - h * half;
-        const float freq = p * inv_freq[c];
+    if (threadIdx.x < half) {
         float sn, cs;
-        sincosf(freq, &sn, &cs);
+        sincosf(p * inv_freq[threadIdx.x], &sn, &cs);
+        s_cos[threadIdx.x] = cs;
+        s_sin[threadIdx.x] = sn;
+    }
+    __syncthreads();
+    const int pairs = half >> 1;  // bf16x2 pairs per half head
+    for (int i = threadIdx.x; i < (hq + hkv) * pairs; i += blockDim.x) {
+        const int h = i / pairs, c = (i - h * pairs) * 2;
         bf16* hp = row + h * d;
-        const float a = __bfloat162float(hp[c]);
-        const float b = __bfloat162float(hp[c + half]);
-        const bf16 o1 = __float2bfloat16(a * cs - b * sn);
-        const bf16 o2 = __float2bfloat16(a * sn + b * cs);
+        const __nv_bfloat162 lo = *reinterpret_cast<const __nv_bfloat162*>(hp + c);
+        const __nv_bfloat162 hi = *reinterpret_cast<const __nv_bfloat162*>(hp + c + half);
+        const float a0 = __bfloat162float(lo.x), a1 = __bfloat162float(lo.y);
+        const float b0 = __bfloat162float(hi.x), b1 = __bfloat162float(hi.y);
+        __nv_bfloat162 o_lo, o_hi;
+        o_lo.x = __float2bfloat16(a0 * s_cos[c] - b0 * s_sin[c]);
+        o_lo.y = __float2bfloat16(a1 * s_cos[c + 1] - b1 * s_sin[c + 1]);
+        o_hi.x = __float2bfloat16(a0 * s_sin[c] + b0 * s_cos[c]);
+        o_hi.y = __float2bfloat16(a1 * s_sin[c + 1] + b1 * s_cos[c + 1]);
         if (h < hq) {
-            hp[c] = o1;
-            hp[c + half] = o2;
+            *reinterpret_cast<__nv_bfloat162*>(hp + c) = o_lo;
+            *reinterpret_cast<__nv_bfloat162*>(hp + c + half) = o_hi;
         } else if (store_kv && kv_row >= 0) {
             bf16* kd = k_cache + kv_row * kv_dim + (h - hq) * d;
-            kd[c] = o1;
-            kd[c + half] = o2;
+            *reinterpret_cast<__nv_bfloat162*>(kd + c) = o_lo;
+            *reinterpret_cast<__nv_bfloat162*>(kd + c + half) = o_hi;
         }
     }
     if (store_kv && kv_row >= 0) {
@@ -134,21 +172,21 @@ __global__ void rope_append_kernel(bf16* __restrict__ qkv, int hq, int hkv, int 
 __global__ void silu_gate_kernel(const bf16* __restrict__ gate_up, bf16* __restrict__ out, int inter) {
     grid_dependency_sync();
     const int r = blockIdx.y;
-    const int c = (blockIdx.x * blockDim.x + threadIdx.x) * 2;
+    const int c = (blockIdx.x * blockDim.x + threadIdx.x) * 8;
     if (c >= inter) return;
     const bf16* g = gate_up + static_cast<size_t>(r) * 2 * inter;
-    const __nv_bfloat162 gv = *reinterpret_cast<const __nv_bfloat162*>(g + c);
-    const __nv_bfloat162 uv = *reinterpret_cast<const __nv_bfloat162*>(g + inter + c);
-    __nv_bfloat162 o;
-    {
-        const float x = __bfloat162float(gv.x);
-        o.x = __float2bfloat16(x * (1.0f / (1.0f + expf(-x))) * __bfloat162float(uv.x));
+    const uint4 gv = *reinterpret_cast<const uint4*>(g + c);
+    const uint4 uv = *reinterpret_cast<const uint4*>(g + inter + c);
+    const bf16* ge = reinterpret_cast<const bf16*>(&gv);
+    const bf16* ue = reinterpret_cast<const bf16*>(&uv);
+    uint4 ov;
+    bf16* oe = reinterpret_cast<bf16*>(&ov);
+#pragma unroll
+    for (int e = 0; e < 8; ++e) {
+        const float x = __bfloat162float(ge[e]);
+        oe[e] = __float2bfloat16(x * (1.0f / (1.0f + expf(-x))) * __bfloat162float(ue[e]));
     }
-    {
-        const float x = __bfloat162float(gv.y);
-        o.y = __float2bfloat16(x * (1.0f / (1.0f + expf(-x))) * __bfloat162float(uv.y));
-    }
-    *reinterpret_cast<__nv_bfloat162*>(out + static_cast<size_t>(r) * inter + c) = o;
+    *reinterpret_cast<uint4*>(out + static_cast<size_t>(r) * inter + c) = ov;
 }
 
 __global__ void add_scaled_kernel(bf16* __restrict__ x, const bf16* __restrict__ a, const bf16* __restrict__ b,
@@ -174,23 +212,44 @@ __global__ void scale_kernel(bf16* __restrict__ out, const bf16* __restrict__ in
     if (i < n) out[i] = __float2bfloat16(__bfloat162float(in[i]) * scale);
 }
 
-// Row argmax over bf16 logits, lowest index wins ties.
-__global__ void argmax_kernel(const bf16* __restrict__ logits, int vocab, int ld, int32_t* __restrict__ out) {
+// Row argmax over bf16 logits, lowest index wins ties.  Stage 1: each CTA scans one
+// 8192-entry chunk of a row with 16-byte loads; stage 2: one warp per row merges.
+constexpr int AM_CHUNK = 8192;
+
+__device__ __forceinline__ void am_better(float& best, int& bi, float v, int i) {
+    if (v > best || (v == best && i < bi)) { best = v; bi = i; }
+}
+
+__global__ void argmax_partial_kernel(const bf16* __restrict__ logits, int vocab, int ld, int nchunk,
+                                      float* __restrict__ pval, int* __restrict__ pidx) {
     grid_dependency_sync();
     __shared__ float sv[32];
     __shared__ int si[32];
-    const bf16* row = logits + static_cast<size_t>(blockIdx.x) * ld;
+    const int row = blockIdx.y, chunk = blockIdx.x;
+    const bf16* x = logits + static_cast<size_t>(row) * ld;
+    const int begin = chunk * AM_CHUNK, end = min(begin + AM_CHUNK, vocab);
     float best = -INFINITY;
     int bi = 0x7fffffff;
-    for (int i = threadIdx.x; i < vocab; i += blockDim.x) {
-        const float v = __bfloat162float(row[i]);
-        if (v > best || (v == best && i < bi)) { best = v; bi = i; }
+    const bool aligned = ((reinterpret_cast<uintptr_t>(x + begin) & 15) == 0);
+    if (aligned) {
+        for (int i = begin + threadIdx.x * 8; i < end; i += blockDim.x * 8) {
+            if (i + 8 <= end) {
+                const uint4 v = *reinterpret_cast<const uint4*>(x + i);
+                const bf16* e = reinterpret_cast<const bf16*>(&v);
+#pragma unroll
+                for (int j = 0; j < 8; ++j) am_better(best, bi, __bfloat162float(e[j]), i + j);
+            } else {
+                for (int j = i; j < end; ++j) am_better(best, bi, __bfloat162float(x[j]), j);
+            }
+        }
+    } else {
+        for (int i = begin + threadIdx.x; i < end; i += blockDim.x) am_better(best, bi, __bfloat162float(x[i]), i);
     }
 #pragma unroll
     for (int o = 16; o > 0; o >>= 1) {
         const float ov = __shfl_xor_sync(0xffffffffu, best, o);
         const int oi = __shfl_xor_sync(0xffffffffu, bi, o);
-        if (ov > best || (ov == best && oi < bi)) { best = ov; bi = oi; }
+        am_better(best, bi, ov, oi);
     }
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     if (lane == 0) { sv[warp] = best; si[warp] = bi; }
@@ -203,10 +262,29 @@ __global__ void argmax_kernel(const bf16* __restrict__ logits, int vocab, int ld
         for (int o = 16; o > 0; o >>= 1) {
             const float ov = __shfl_xor_sync(0xffffffffu, best, o);
             const int oi = __shfl_xor_sync(0xffffffffu, bi, o);
-            if (ov > best || (ov == best && oi < bi)) { best = ov; bi = oi; }
+            am_better(best, bi, ov, oi);
         }
-        if (lane == 0) out[blockIdx.x] = (bi == 0x7fffffff) ? 0 : bi;
+        if (lane == 0) {
+            pval[row * nchunk + chunk] = best;
+            pidx[row * nchunk + chunk] = bi;
+        }
     }
+}
+
+__global__ void argmax_merge_kernel(const float* __restrict__ pval, const int* __restrict__ pidx, int nchunk,
+                                    int32_t* __restrict__ out) {
+    grid_dependency_sync();
+    const int row = blockIdx.x, lane = threadIdx.x;
+    float best = -INFINITY;
+    int bi = 0x7fffffff;
+    for (int c = lane; c < nchunk; c += 32) am_better(best, bi, pval[row * nchunk + c], pidx[row * nchunk + c]);
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) {
+        const float ov = __shfl_xor_sync(0xffffffffu, best, o);
+        const int oi = __shfl_xor_sync(0xffffffffu, bi, o);
+        am_better(best, bi, ov, oi);
+    }
+    if (lane == 0) out[row] = (bi == 0x7fffffff) ? 0 : bi;
 }
 
 }  // namespace
@@ -214,15 +292,27 @@ __global__ void argmax_kernel(const bf16* __restrict__ logits, int vocab, int ld
 void launch_rms_norm(const bf16* x, int ldx, const bf16* w, bf16* y, int ldy, int rows, int dim, float eps,
                      cudaStream_t s) {
     if (rows <= 0) return;
-    CPM_REQUIRE(dim % 2 == 0 && ldx % 2 == 0 && ldy % 2 == 0, "rms_norm: dims must be even");
-    launch_kernel(rms_norm_kernel<false>, dim3(rows), dim3(256), 0, s, const_cast<bf16*>(x), ldx, nullptr, 1.f, w, y, ldy, dim, eps);
+    CPM_REQUIRE(dim % 8 == 0 && ldx % 8 == 0 && ldy % 8 == 0, "rms_norm: dims must be multiples of 8");
+    CPM_REQUIRE(dim <= 256 * 8 * 8, "rms_norm: hidden size above 16384 is not supported");
+    if (dim <= 256 * 8 * 2) {
+        launch_kernel(rms_norm_kernel<false, 2>, dim3(rows), dim3(256), 0, s, const_cast<bf16*>(x), ldx,
+                      static_cast<const bf16*>(nullptr), 1.f, w, y, ldy, dim, eps);
+    } else {
+        launch_kernel(rms_norm_kernel<false, 8>, dim3(rows), dim3(256), 0, s, const_cast<bf16*>(x), ldx,
+                      static_cast<const bf16*>(nullptr), 1.f, w, y, ldy, dim, eps);
+    }
 }
 
 void launch_add_rms_norm(bf16* x, const bf16* delta, float delta_scale, const bf16* w, bf16* y, int rows, int dim,
                          float eps, cudaStream_t s) {
     if (rows <= 0) return;
-    CPM_REQUIRE(dim % 2 == 0, "rms_norm: dim must be even");
-    launch_kernel(rms_norm_kernel<true>, dim3(rows), dim3(256), 0, s, x, dim, delta, delta_scale, w, y, dim, dim, eps);
+    CPM_REQUIRE(dim % 8 == 0, "rms_norm: dim must be a multiple of 8");
+    CPM_REQUIRE(dim <= 256 * 8 * 8, "rms_norm: hidden size above 16384 is not supported");
+    if (dim <= 256 * 8 * 2) {
+        launch_kernel(rms_norm_kernel<true, 2>, dim3(rows), dim3(256), 0, s, x, dim, delta, delta_scale, w, y, dim, dim, eps);
+    } else {
+        launch_kernel(rms_norm_kernel<true, 8>, dim3(rows), dim3(256), 0, s, x, dim, delta, delta_scale, w, y, dim, dim, eps);
+    }
 }
 
 void launch_embedding(const int32_t* ids, const bf16* table, bf16* out, int ld_out, int rows, int dim, float scale,
@@ -237,14 +327,15 @@ void launch_rope_append(bf16* qkv, int rows, int hq, int hkv, int d, const float
                         const int32_t* kv_len, int kv_off, const int32_t* n_valid, cudaStream_t s) {
     if (rows <= 0) return;
     CPM_REQUIRE(pos != nullptr || pos_base != nullptr, "rope: no positions given");
+    CPM_REQUIRE(d % 4 == 0 && d <= 256, "rope: head_dim must be a multiple of 4 and at most 256");
     launch_kernel(rope_append_kernel, dim3(rows), dim3(256), 0, s, qkv, hq, hkv, d, inv_freq, pos, pos_base, pos_off,
                   pos_step, k_cache, v_cache, kv_len, kv_off, n_valid);
 }
 
 void launch_silu_gate(const bf16* gate_up, bf16* out, int rows, int inter, cudaStream_t s) {
     if (rows <= 0) return;
-    CPM_REQUIRE(inter % 2 == 0, "silu_gate: width must be even");
-    dim3 grid(ceil_div(inter / 2, 256), rows);
+    CPM_REQUIRE(inter % 8 == 0, "silu_gate: width must be a multiple of 8");
+    dim3 grid(ceil_div(inter / 8, 256), rows);
     launch_kernel(silu_gate_kernel, grid, dim3(256), 0, s, gate_up, out, inter);
 }
 
@@ -259,7 +350,16 @@ void launch_scale(bf16* out, const bf16* in, float scale, size_t n, cudaStream_t
     launch_kernel(scale_kernel, dim3(static_cast<unsigned>((n + 255) / 256)), dim3(256), 0, s, out, in, scale, n);
 }
 
-void launch_argmax(const bf16* logits, int rows, int vocab, int ld, int32_t* out, cudaStream_t s) {
+size_t argmax_workspace_bytes(int rows, int vocab) {
+    return static_cast<size_t>(rows) * ceil_div(vocab, AM_CHUNK) * 8 + 256;
+}
+
+void launch_argmax(const bf16* logits, int rows, int vocab, int ld, int32_t* out, void* workspace, cudaStream_t s) {
     if (rows <= 0) return;
-    launch_kernel(argmax_kernel, dim3(rows), dim3(1024), 0, s, logits, vocab, ld, out);
+    const int nchunk = ceil_div(vocab, AM_CHUNK);
+    float* pval = static_cast<float*>(workspace);
+    int* pidx = reinterpret_cast<int*>(pval + static_cast<size_t>(rows) * nchunk);
+    launch_kernel(argmax_partial_kernel, dim3(nchunk, rows), dim3(256), 0, s, logits, vocab, ld, nchunk, pval, pidx);
+    launch_kernel(argmax_merge_kernel, dim3(rows), dim3(32), 0, s, static_cast<const float*>(pval),
+                  static_cast<const int*>(pidx), nchunk, out);
 }

@@ -169,6 +169,7 @@ void Engine::lay_out(Pool& p) {
     t_gt_ = take<int32_t>(p, 64);
     t_mask_ = take<uint64_t>(p, 64);
     accept_result_ = take<int32_t>(p, 32);
+    argmax_ws_ = p.take(argmax_workspace_bytes(64, V));
     d_publish_ = take<int32_t>(p, 32);
     if (has_eagle_) {
         e_in_ = take<bf16>(p, R * 2 * H);
@@ -732,7 +733,7 @@ void Engine::enqueue_step(bool first, cudaStream_t s) {
                                          nullptr, gemm_ws_, tickets_, runtime().num_sms);
     }
     launch_linear(lm_plan_tree_, s);
-    launch_argmax(logits_, T, V, V, t_gt_, s);
+    launch_argmax(logits_, T, V, V, t_gt_, argmax_ws_, s);
     accept_and_fix(T, t_ids_, t_gt_, t_pos_, st_ + S_L, t_mask_, t_parent_, s);
     CUDA_CHECK(cudaMemcpyAsync(h_result_, d_publish_, 32 * sizeof(int32_t), cudaMemcpyDeviceToHost, s));
 }

@@ -169,6 +169,7 @@ private:
     int* tickets_ = nullptr;
     float *attn_ws_o_ = nullptr, *attn_ws_ml_ = nullptr;
     void* scan_ws_ = nullptr;
+    void* argmax_ws_ = nullptr;
     bf16** d_cache_ptrs_ = nullptr;
     // device state words
     int32_t* st_ = nullptr;
