@@ -56,6 +56,8 @@ void sync_and_check(const char* where) {
 
 }  // namespace
 
+void cpm_set_error(const char* msg) { g_error = msg ? msg : ""; }
+
 extern "C" {
 
 const char* cpmcu_last_error(void) { return g_error.c_str(); }

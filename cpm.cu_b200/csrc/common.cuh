@@ -27,6 +27,9 @@ typedef __nv_bfloat16 bf16;
         if (!(cond)) throw std::invalid_argument(std::string("cpmcu_b200: ") + (msg)); \
     } while (0)
 
+// Records the message cpmcu_last_error() returns on this thread (capi.cu).
+void cpm_set_error(const char* msg);
+
 static inline int ceil_div(int a, int b) { return (a + b - 1) / b; }
 static inline int64_t align_up(int64_t x, int64_t a) { return (x + a - 1) / a * a; }
 

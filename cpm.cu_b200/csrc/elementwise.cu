@@ -363,3 +363,55 @@ void launch_argmax(const bf16* logits, int rows, int vocab, int ld, int32_t* out
     launch_kernel(argmax_merge_kernel, dim3(rows), dim3(32), 0, s, static_cast<const float*>(pval),
                   static_cast<const int*>(pidx), nchunk, out);
 }
+
+// ------------------------------------------------------------------ allocation-free argmax
+// Scratch of cpmcu_argmax_noalloc(): the stage-1 (value, index) partials.  It lives in the
+// library image, so every GPU that loads the library holds these 16 KB until the process exits.
+constexpr int NOALLOC_MAX_ROWS = 64;
+constexpr int NOALLOC_MAX_VOCAB = 32 * AM_CHUNK;  // 262144
+constexpr size_t NOALLOC_SCRATCH_BYTES = static_cast<size_t>(NOALLOC_MAX_ROWS) * 32 * 8;
+static __device__ __align__(256) unsigned char g_argmax_scratch[NOALLOC_SCRATCH_BYTES];
+
+extern "C" int cpmcu_argmax_noalloc(const void* logits, int rows, int vocab, int32_t* out) {
+    // In host code `g_argmax_scratch` is only a handle for the symbol, not a device pointer:
+    // the address the kernels need is looked up once per device, with that device current.
+    static void* scratch_addr[64] = {nullptr};
+    if (logits == nullptr || out == nullptr) {
+        cpm_set_error("cpmcu_argmax_noalloc: null pointer");
+        return -1;
+    }
+    if (rows < 1 || rows > NOALLOC_MAX_ROWS || vocab < 1 || vocab > NOALLOC_MAX_VOCAB) {
+        cpm_set_error("cpmcu_argmax_noalloc: at most 64 rows and 262144 columns fit the built-in scratch; "
+                      "use cpmcu_argmax for larger inputs");
+        return -1;
+    }
+    int dev = 0;
+    cudaError_t e = cudaGetDevice(&dev);
+    if (e != cudaSuccess || dev < 0 || dev >= 64) {
+        cpm_set_error("cpmcu_argmax_noalloc: no usable CUDA device is current");
+        return -1;
+    }
+    if (scratch_addr[dev] == nullptr) {
+        void* p = nullptr;
+        e = cudaGetSymbolAddress(&p, g_argmax_scratch);
+        if (e != cudaSuccess || p == nullptr) {
+            cpm_set_error((std::string("cpmcu_argmax_noalloc: cudaGetSymbolAddress failed: ") + cudaGetErrorString(e)).c_str());
+            return -1;
+        }
+        scratch_addr[dev] = p;
+    }
+    const int nchunk = ceil_div(vocab, AM_CHUNK);
+    float* pval = static_cast<float*>(scratch_addr[dev]);
+    int* pidx = reinterpret_cast<int*>(pval + static_cast<size_t>(rows) * nchunk);
+    // Both stages overwrite every scratch word they later read, so nothing has to be cleared.
+    argmax_partial_kernel<<<dim3(nchunk, rows), 256, 0, cudaStreamLegacy>>>(static_cast<const bf16*>(logits), vocab, vocab,
+                                                                            nchunk, pval, pidx);
+    argmax_merge_kernel<<<rows, 32, 0, cudaStreamLegacy>>>(pval, pidx, nchunk, out);
+    e = cudaGetLastError();
+    if (e == cudaSuccess) e = cudaStreamSynchronize(cudaStreamLegacy);
+    if (e != cudaSuccess) {
+        cpm_set_error((std::string("cpmcu_argmax_noalloc: ") + cudaGetErrorString(e)).c_str());
+        return -1;
+    }
+    return 0;
+}

@@ -187,6 +187,26 @@ int cpmcu_silu_gate(const void* gate_up, void* out, int rows, int inter);
  * cpmcu/speculative/tree_drafter.py:233. */
 int cpmcu_argmax(const void* logits, int rows, int vocab, int32_t* out);
 
+/* Row argmax like cpmcu_argmax, but without any device allocation.  It has no
+ * counterpart in the reference.  cpmcu_argmax takes its two-stage scratch from
+ * cudaMalloc on every call; once cpmcu_init_storage has handed memory_limit of
+ * the device to the model pool that allocation can fail, and even when it fits,
+ * cudaMalloc and cudaFree synchronise the whole device and so stall a
+ * speculative step in flight on the library's stream.  A caller in that
+ * position (a serving loop that picks tokens from logits it owns while the
+ * engine is live) uses this variant: the scratch is a 16 KB array inside the
+ * library image, which every GPU that loads the library keeps until exit.
+ *   - rows <= 64 and vocab <= 262144, otherwise -1 with a message.
+ *   - The first call on each device looks up the array's device address
+ *     (cudaGetSymbolAddress, with that device current); make that first call
+ *     before opening any stream capture.
+ *   - Runs on the legacy default stream and returns after it has drained.
+ *   - All calls share the one array, which keeps the previous call's partials
+ *     (each call overwrites what it reads, nothing needs clearing); two calls
+ *     that overlap on the GPU, from different host threads or processes sharing
+ *     a context, race on it. */
+int cpmcu_argmax_noalloc(const void* logits, int rows, int vocab, int32_t* out);
+
 /* Draft tree from given logits: level 0 uses row 0 of `logits`, level d >= 1
  * rows 1 + (d-1)*k .. (k rows).  logits: [1 + (num_iter-1)*k, vocab] bf16.
  * Runs log-softmax, top-k, frontier expansion and the final tree build exactly
