@@ -159,7 +159,8 @@ def run_ours(args):
     import contextlib
     with contextlib.redirect_stdout(sys.stderr):  # keep stdout for the single JSON line
         llm = build_model(local, seed=1)
-    prompt = torch.tensor(zipf_prompt(PROMPT_LEN, CFG["vocab"], 100 + rank), device="cuda")
+    from cpmcu.replicas import replica_seed
+    prompt = torch.tensor(zipf_prompt(PROMPT_LEN, CFG["vocab"], replica_seed(100, rank)), device="cuda")
     pos = torch.arange(PROMPT_LEN, dtype=torch.int32, device="cuda")
     torch.cuda.synchronize()
     t0 = time.time()
@@ -203,15 +204,8 @@ def run_ours(args):
         prof_total.append(total)
 
     dev_s = sum(dev_ms) / 1e3
-    stats = torch.tensor([float(tokens), dev_s, wall], dtype=torch.float64, device="cuda")
-    if dist is not None:
-        tok_all = stats[0:1].clone()
-        dist.all_reduce(tok_all, op=dist.ReduceOp.SUM)
-        t_all = stats[1:3].clone()
-        dist.all_reduce(t_all, op=dist.ReduceOp.MAX)
-        tokens_all, dev_max, wall_max = float(tok_all[0]), float(t_all[0]), float(t_all[1])
-    else:
-        tokens_all, dev_max, wall_max = float(tokens), dev_s, wall
+    from cpmcu.replicas import combine_ranks
+    tokens_all, dev_max, wall_max = combine_ranks(tokens, dev_s, wall, dist, "cuda")
 
     if rank == 0:
         peaks = {}
