@@ -432,6 +432,10 @@ void launch_linear(const LinearPlan& p, cudaStream_t stream) {
     a.workspace = p.workspace; a.tickets = p.tickets;
     a.error = runtime().d_error;
     a.debug = p.debug;
+    {
+        static const char* dbg = getenv("CPMCU_LINEAR_DEBUG_ALL");
+        if (dbg) a.debug = atoi(dbg);
+    }
     switch (p.mt) {
         case 16: launch_mt<16>(p, a, stream); break;
         case 32: launch_mt<32>(p, a, stream); break;

@@ -32,12 +32,14 @@ constexpr int TILE_BYTES = 2 * HALF_BYTES;    // 32 KB
 constexpr int SMEM_Q = 0;
 constexpr int SMEM_K = SMEM_Q + TILE_BYTES;          // 2 stages
 constexpr int SMEM_V = SMEM_K + 2 * TILE_BYTES;      // 2 stages
-constexpr int SMEM_P = SMEM_V + 2 * TILE_BYTES;
-constexpr int SMEM_CTRL = SMEM_P + TILE_BYTES;
+constexpr int SMEM_P = SMEM_V + 2 * TILE_BYTES;      // 2 stages
+constexpr int SMEM_CTRL = SMEM_P + 2 * TILE_BYTES;
 constexpr int SMEM_XCH = SMEM_CTRL + 256;   // 2 x 128 floats
 constexpr int SMEM_TOTAL = SMEM_XCH + 1024 + 1024;
-constexpr int TMEM_COLS = 256;  // S: columns [0,128), O: columns [128,256)
-constexpr int NTHREADS = 256;   // two threads per query row: warps 0-3 take keys 0-63 of a tile, warps 4-7 keys 64-127
+constexpr int TMEM_COLS = 512;  // S stage 0: [0,128), S stage 1: [128,256), O: [256,384)
+constexpr int TMEM_O = 256;
+constexpr int SOFTMAX_THREADS = 256;  // two threads per query row: warps 0-3 keys 0-63 of a tile, warps 4-7 keys 64-127
+constexpr int NTHREADS = SOFTMAX_THREADS + 32;  // + one control warp (TMA and MMA issue)
 
 struct AttnArgs {
     int tq, hq, hkv, grp, tok_per_tile, num_mtiles;
@@ -61,6 +63,10 @@ __device__ __forceinline__ float fast_exp2(float x) {
     return y;
 }
 
+// Software pipeline over 128-key tiles.  The control warp keeps the tensor pipe one tile
+// ahead: S(i+1) = Q K(i+1)^T is already in TMEM (two S stages) while the softmax warps work
+// on tile i, and O += P(i) V(i) is issued as soon as P(i) is in shared memory (two P stages),
+// so in steady state an iteration costs one softmax pass.
 __global__ void __launch_bounds__(NTHREADS, 1)
 tree_attn_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant__ CUtensorMap tm_k,
                  const __grid_constant__ CUtensorMap tm_v, const AttnArgs a) {
@@ -68,34 +74,36 @@ tree_attn_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant
     uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
     uint64_t* bars = reinterpret_cast<uint64_t*>(smem + SMEM_CTRL);
     uint64_t* q_bar = bars;
-    uint64_t* k_full = bars + 1;  // [2]
-    uint64_t* v_full = bars + 3;  // [2]
-    uint64_t* s_bar = bars + 5;
-    uint64_t* o_bar = bars + 6;
-    uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 7);
+    uint64_t* k_full = bars + 1;   // [2]
+    uint64_t* v_full = bars + 3;   // [2]
+    uint64_t* s_bar = bars + 5;    // [2]  S(i) is in TMEM
+    uint64_t* o_bar = bars + 7;    // [2]  PV(i) has finished (P stage, V stage and O are free / stable)
+    uint64_t* p_ready = bars + 9;  // [2]  P(i) is in shared memory (256 arrivals)
+    uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 11);
     volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
     float* xch = reinterpret_cast<float*>(smem + SMEM_XCH);  // [2][128] row maxima / sums of the two column halves
 
     const int tid = threadIdx.x;
     const int warp = tid >> 5;
     const int lane = tid & 31;
-    const int ch = warp >> 2;                    // column half of the key tile
+    const bool is_control = (warp == SOFTMAX_THREADS / 32);
+    const int ch = (warp >> 2) & 1;              // column half of the key tile
     const int row = (warp & 3) * 32 + lane;      // query row of the tile == TMEM lane
-    const bool leader = (tid == 0);
     grid_dep_trigger();
     const int mt = blockIdx.x % a.num_mtiles;
     const int h = blockIdx.x / a.num_mtiles;  // kv head
     const int split = blockIdx.y;
     const int nsplit = gridDim.y;
 
-    if (leader) {
+    if (tid == 0) {
         ptx::mbar_init(q_bar, 1);
         for (int i = 0; i < 2; ++i) {
             ptx::mbar_init(&k_full[i], 1);
             ptx::mbar_init(&v_full[i], 1);
+            ptx::mbar_init(&s_bar[i], 1);
+            ptx::mbar_init(&o_bar[i], 1);
+            ptx::mbar_init(&p_ready[i], SOFTMAX_THREADS);
         }
-        ptx::mbar_init(s_bar, 1);
-        ptx::mbar_init(o_bar, 1);
         *abort_flag = 0;
         ptx::mbar_fence_init();
         ptx::prefetch_tensormap(&tm_q);
@@ -111,8 +119,7 @@ tree_attn_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant
     ptx::tc_fence_after();
     const uint32_t tmem_base = *tmem_slot;
     const uint32_t lane_sel = static_cast<uint32_t>((warp & 3) * 32) << 16;
-    const uint32_t tmem_s = tmem_base + lane_sel + ch * 64;         // this thread's 64 score columns
-    const uint32_t tmem_o = tmem_base + lane_sel + KEYS + ch * 64;  // this thread's 64 output columns
+    const uint32_t tmem_o = tmem_base + lane_sel + TMEM_O + ch * 64;  // this thread's 64 output columns
     grid_dep_wait();  // everything above overlaps the previous kernel's tail
 
     // ---- geometry of this tile
@@ -146,40 +153,32 @@ tree_attn_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant
     const int kt_end = kt_lo + static_cast<int>((static_cast<long long>(n_kt) * (split + 1)) / nsplit);
     const int n_it = kt_end - kt_begin;
 
-    const uint32_t q_addr = ptx::smem_u32(smem + SMEM_Q);
-    const uint32_t p_addr = ptx::smem_u32(smem + SMEM_P);
-    constexpr uint32_t idesc_s = ptx::umma_idesc_bf16(ROWS, KEYS, 0, 0);
-    constexpr uint32_t idesc_o = ptx::umma_idesc_bf16(ROWS, D, 0, 1);
-
-    bool ok = true;
-    if (leader && n_it > 0) {
-        ptx::mbar_arrive_expect_tx(q_bar, TILE_BYTES);
-        ptx::tma_load_3d(smem + SMEM_Q, &tm_q, q_bar, 0, h * a.grp, t0);
-        ptx::tma_load_3d(smem + SMEM_Q + HALF_BYTES, &tm_q, q_bar, 64, h * a.grp, t0);
-        for (int i = 0; i < 2 && i < n_it; ++i) {
-            const int key0 = (kt_begin + i) * KEYS;
-            ptx::mbar_arrive_expect_tx(&k_full[i], TILE_BYTES);
-            ptx::tma_load_2d(smem + SMEM_K + i * TILE_BYTES, &tm_k, &k_full[i], h * D, key0);
-            ptx::tma_load_2d(smem + SMEM_K + i * TILE_BYTES + HALF_BYTES, &tm_k, &k_full[i], h * D + 64, key0);
-            ptx::mbar_arrive_expect_tx(&v_full[i], TILE_BYTES);
-            ptx::tma_load_2d(smem + SMEM_V + i * TILE_BYTES, &tm_v, &v_full[i], h * D, key0);
-            ptx::tma_load_2d(smem + SMEM_V + i * TILE_BYTES + HALF_BYTES, &tm_v, &v_full[i], h * D + 64, key0);
-        }
-    }
-
     float m_run = -INFINITY;  // running max of raw scores (same in both threads of a row)
     float l_run = 0.f;        // this thread's share of the running sum
+    bool ok = true;
 
-    for (int i = 0; i < n_it && ok; ++i) {
-        const int st = i & 1;
-        const uint32_t ph = (i >> 1) & 1;
-        const int key0 = (kt_begin + i) * KEYS + ch * 64;  // first key of this thread's 64 columns
-
-        if (leader) {
-            bool w = true;
-            if (i == 0) w = ptx::mbar_wait(q_bar, 0, abort_flag);
-            w = w && ptx::mbar_wait(&k_full[st], ph, abort_flag);
-            if (w) {
+    if (is_control) {
+        // ================================================= control warp: TMA + MMA issue
+        if (lane == 0 && n_it > 0) {
+            const uint32_t q_addr = ptx::smem_u32(smem + SMEM_Q);
+            const uint32_t p_addr = ptx::smem_u32(smem + SMEM_P);
+            constexpr uint32_t idesc_s = ptx::umma_idesc_bf16(ROWS, KEYS, 0, 0);
+            constexpr uint32_t idesc_o = ptx::umma_idesc_bf16(ROWS, D, 0, 1);
+            auto load_k = [&](int i) {
+                const int st = i & 1, key0 = (kt_begin + i) * KEYS;
+                ptx::mbar_arrive_expect_tx(&k_full[st], TILE_BYTES);
+                ptx::tma_load_2d(smem + SMEM_K + st * TILE_BYTES, &tm_k, &k_full[st], h * D, key0);
+                ptx::tma_load_2d(smem + SMEM_K + st * TILE_BYTES + HALF_BYTES, &tm_k, &k_full[st], h * D + 64, key0);
+            };
+            auto load_v = [&](int i) {
+                const int st = i & 1, key0 = (kt_begin + i) * KEYS;
+                ptx::mbar_arrive_expect_tx(&v_full[st], TILE_BYTES);
+                ptx::tma_load_2d(smem + SMEM_V + st * TILE_BYTES, &tm_v, &v_full[st], h * D, key0);
+                ptx::tma_load_2d(smem + SMEM_V + st * TILE_BYTES + HALF_BYTES, &tm_v, &v_full[st], h * D + 64, key0);
+            };
+            auto issue_s = [&](int i) -> bool {  // S(i) = Q K(i)^T into S stage i & 1
+                const int st = i & 1;
+                if (!ptx::mbar_wait(&k_full[st], (i >> 1) & 1, abort_flag)) return false;
                 ptx::tc_fence_after();
                 const uint32_t k_addr = ptx::smem_u32(smem + SMEM_K + st * TILE_BYTES);
 #pragma unroll
@@ -188,182 +187,197 @@ tree_attn_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant
                     for (int j = 0; j < 4; ++j) {
                         const uint64_t da = ptx::umma_desc_sw128(q_addr + dh * HALF_BYTES + j * 32, 16, 1024);
                         const uint64_t db = ptx::umma_desc_sw128(k_addr + dh * HALF_BYTES + j * 32, 16, 1024);
-                        ptx::umma_ss(tmem_base, da, db, idesc_s, (dh | j) ? 1u : 0u);
+                        ptx::umma_ss(tmem_base + st * KEYS, da, db, idesc_s, (dh | j) ? 1u : 0u);
                     }
                 }
-                ptx::umma_commit(s_bar);
+                ptx::umma_commit(&s_bar[st]);
+                return true;
+            };
+            ptx::mbar_arrive_expect_tx(q_bar, TILE_BYTES);
+            ptx::tma_load_3d(smem + SMEM_Q, &tm_q, q_bar, 0, h * a.grp, t0);
+            ptx::tma_load_3d(smem + SMEM_Q + HALF_BYTES, &tm_q, q_bar, 64, h * a.grp, t0);
+            for (int i = 0; i < 2 && i < n_it; ++i) {
+                load_k(i);
+                load_v(i);
             }
-        }
-        if (!ptx::mbar_wait(s_bar, i & 1, abort_flag)) { ok = false; break; }
-        ptx::tc_fence_after();
-        __syncwarp();  // TMEM loads below are warp-collective
-
-        if (leader && i + 2 < n_it) {  // K stage is free again: prefetch two tiles ahead
-            const int keyn = (kt_begin + i + 2) * KEYS;
-            ptx::mbar_arrive_expect_tx(&k_full[st], TILE_BYTES);
-            ptx::tma_load_2d(smem + SMEM_K + st * TILE_BYTES, &tm_k, &k_full[st], h * D, keyn);
-            ptx::tma_load_2d(smem + SMEM_K + st * TILE_BYTES + HALF_BYTES, &tm_k, &k_full[st], h * D + 64, keyn);
-        }
-
-        // ---- scores of this thread: 64 columns, kept in registers for both passes
-        uint32_t sc[64];
-        ptx::tmem_ld32(tmem_s, sc);
-        ptx::tmem_ld32(tmem_s + 32, sc + 32);
-        ptx::tmem_wait_ld();
-        const bool need_mask = (key0 + 64 > limit) || (key0 + 64 > mbeg) || (key0 < key_lo);
-        if (need_mask) {
-#pragma unroll
-            for (int c = 0; c < 64; ++c) {
-                const int key = key0 + c;
-                bool vis = key < limit && key >= key_lo;
-                if (key >= mbeg) vis = vis && ((mword >> (key - mbeg)) & 1ull);
-                if (!vis) sc[c] = 0xff800000u;  // -inf
-            }
-        }
-        float mx[4] = {-INFINITY, -INFINITY, -INFINITY, -INFINITY};
-#pragma unroll
-        for (int c = 0; c < 64; c += 4) {
-            mx[0] = fmaxf(mx[0], __uint_as_float(sc[c]));
-            mx[1] = fmaxf(mx[1], __uint_as_float(sc[c + 1]));
-            mx[2] = fmaxf(mx[2], __uint_as_float(sc[c + 2]));
-            mx[3] = fmaxf(mx[3], __uint_as_float(sc[c + 3]));
-        }
-        const float m_half = fmaxf(fmaxf(mx[0], mx[1]), fmaxf(mx[2], mx[3]));
-        xch[ch * ROWS + row] = m_half;
-        __syncthreads();
-        const float m_tile = fmaxf(m_half, xch[(ch ^ 1) * ROWS + row]);
-        const float m_new = fmaxf(m_run, m_tile);
-        const float m_use = (m_new == -INFINITY) ? 0.f : m_new;
-        const float alpha = (m_run == -INFINITY) ? 1.f : fast_exp2((m_run - m_use) * a.scale_log2);
-        const bool rescale = (i > 0) && __any_sync(0xffffffffu, alpha != 1.f);
-
-        if (i > 0) {  // P buffer, the other V stage and O are in use until PV(i-1) has finished
-            if (!ptx::mbar_wait(o_bar, (i - 1) & 1, abort_flag)) { ok = false; break; }
-            ptx::tc_fence_after();
-            __syncwarp();
-            if (leader && i + 1 < n_it) {
-                const int sv = (i + 1) & 1;
-                const int keyn = (kt_begin + i + 1) * KEYS;
-                ptx::mbar_arrive_expect_tx(&v_full[sv], TILE_BYTES);
-                ptx::tma_load_2d(smem + SMEM_V + sv * TILE_BYTES, &tm_v, &v_full[sv], h * D, keyn);
-                ptx::tma_load_2d(smem + SMEM_V + sv * TILE_BYTES + HALF_BYTES, &tm_v, &v_full[sv], h * D + 64, keyn);
-            }
-            __syncwarp();
-        }
-        if (rescale) {
-#pragma unroll 1
-            for (int c0 = 0; c0 < 64; c0 += 32) {
-                uint32_t r[32];
-                ptx::tmem_ld32(tmem_o + c0, r);
-                ptx::tmem_wait_ld();
-#pragma unroll
-                for (int c = 0; c < 32; ++c) r[c] = __float_as_uint(__uint_as_float(r[c]) * alpha);
-                ptx::tmem_st32(tmem_o + c0, r);
-            }
-            ptx::tmem_wait_st();
-        }
-        m_run = m_new;
-
-        // ---- P = 2^((s - m) * scale) in bf16 into the swizzled A-operand tile; row sums in fp32
-        const float m_off = m_use * a.scale_log2;
-        float ls[4] = {0.f, 0.f, 0.f, 0.f};
-        uint8_t* p_half = smem + SMEM_P + ch * HALF_BYTES + row * 128;
-#pragma unroll
-        for (int c8 = 0; c8 < 8; ++c8) {
-            float p[8];
-#pragma unroll
-            for (int e = 0; e < 8; ++e) {
-                p[e] = fast_exp2(fmaf(__uint_as_float(sc[c8 * 8 + e]), a.scale_log2, -m_off));
-                ls[e & 3] += p[e];
-            }
-            uint4 pk;
-            uint32_t* w = reinterpret_cast<uint32_t*>(&pk);
-#pragma unroll
-            for (int e = 0; e < 4; ++e) {
-                __nv_bfloat162 b2 = __floats2bfloat162_rn(p[e * 2], p[e * 2 + 1]);
-                w[e] = *reinterpret_cast<uint32_t*>(&b2);
-            }
-            *reinterpret_cast<uint4*>(p_half + ((c8 ^ (row & 7)) << 4)) = pk;
-        }
-        l_run = l_run * alpha + ((ls[0] + ls[1]) + (ls[2] + ls[3]));
-
-        ptx::fence_proxy_async_smem();
-        ptx::tc_fence_before();
-        __syncthreads();
-
-        if (leader) {
-            ptx::tc_fence_after();
-            if (ptx::mbar_wait(&v_full[st], ph, abort_flag)) {
+            bool w = ptx::mbar_wait(q_bar, 0, abort_flag);
+            for (int i = 0; w && i < 2 && i < n_it; ++i) w = issue_s(i);
+            for (int i = 0; w && i < n_it; ++i) {
+                const int st = i & 1;
+                const uint32_t ph = (i >> 1) & 1;
+                // K stage st is free once S(i) has been computed: fetch K(i+2)
+                if (i + 2 < n_it) {
+                    if (!ptx::mbar_wait(&s_bar[st], ph, abort_flag)) { w = false; break; }
+                    load_k(i + 2);
+                }
+                // O += P(i) V(i)
+                if (!ptx::mbar_wait(&p_ready[st], ph, abort_flag)) { w = false; break; }
+                if (!ptx::mbar_wait(&v_full[st], ph, abort_flag)) { w = false; break; }
                 ptx::tc_fence_after();
                 const uint32_t v_addr = ptx::smem_u32(smem + SMEM_V + st * TILE_BYTES);
+                const uint32_t pa = p_addr + st * TILE_BYTES;
 #pragma unroll
                 for (int kk = 0; kk < KEYS / 16; ++kk) {
                     // A: P, K-major: 64-key half (kk / 4), 32 B per 16-key step inside it
-                    const uint64_t da =
-                        ptx::umma_desc_sw128(p_addr + (kk >> 2) * HALF_BYTES + (kk & 3) * 32, 16, 1024);
+                    const uint64_t da = ptx::umma_desc_sw128(pa + (kk >> 2) * HALF_BYTES + (kk & 3) * 32, 16, 1024);
                     // B: V, N-major: 16 key rows of 128 B per step; 64-wide d halves HALF_BYTES apart
                     const uint64_t db = ptx::umma_desc_sw128(v_addr + kk * 16 * 128, HALF_BYTES, 1024);
-                    ptx::umma_ss(tmem_base + KEYS, da, db, idesc_o, (i > 0 || kk > 0) ? 1u : 0u);
+                    ptx::umma_ss(tmem_base + TMEM_O, da, db, idesc_o, (i > 0 || kk > 0) ? 1u : 0u);
                 }
-                ptx::umma_commit(o_bar);
+                ptx::umma_commit(&o_bar[st]);
+                // S(i+2) reuses S stage st: softmax(i) has read it (p_ready) and K(i+2) is on its way
+                if (i + 2 < n_it) {
+                    if (!issue_s(i + 2)) { w = false; break; }
+                    // V stage st is free once PV(i) has finished
+                    if (!ptx::mbar_wait(&o_bar[st], ph, abort_flag)) { w = false; break; }
+                    load_v(i + 2);
+                }
             }
         }
-        __syncwarp();
-    }
+    } else {
+        // ================================================= softmax warps
+        for (int i = 0; i < n_it && ok; ++i) {
+            const int st = i & 1;
+            const uint32_t ph = (i >> 1) & 1;
+            const int key0 = (kt_begin + i) * KEYS + ch * 64;  // first key of this thread's 64 columns
+            if (!ptx::mbar_wait(&s_bar[st], ph, abort_flag)) { ok = false; break; }
+            ptx::tc_fence_after();
+            __syncwarp();  // TMEM loads below are warp-collective
 
-    if (ok && n_it > 0) {
-        if (!ptx::mbar_wait(o_bar, (n_it - 1) & 1, abort_flag)) ok = false;
-        ptx::tc_fence_after();
-    }
-    ok = __all_sync(0xffffffffu, ok);  // keep each warp together for the collective TMEM reads
-
-    // ---- write-out.  TMEM reads are warp-collective, so every thread runs them
-    // and only the global stores depend on whether the row exists.
-    xch[ch * ROWS + row] = l_run;
-    __syncthreads();
-    const float l_row = l_run + xch[(ch ^ 1) * ROWS + row];
-    if (ok) {
-        const bool store = (t < a.tq);
-        const size_t grow = static_cast<size_t>(store ? t : 0) * a.hq + qh;
-        const float inv = (nsplit == 1) ? ((l_row > 0.f) ? 1.f / l_row : 0.f) : 1.f;
-        bf16* dst_b = a.out + static_cast<size_t>(store ? t : 0) * a.out_ld + qh * D + ch * 64;
-        float* dst_f = (nsplit > 1) ? a.ws_o + (static_cast<size_t>(split) * a.tq * a.hq + grow) * D + ch * 64 : nullptr;
-#pragma unroll 1
-        for (int c0 = 0; c0 < 64; c0 += 32) {
-            uint32_t r[32];
-            if (n_it > 0) {  // uniform across the CTA
-                ptx::tmem_ld32(tmem_o + c0, r);
-                ptx::tmem_wait_ld();
-            } else {
+            // ---- scores of this thread: 64 columns, kept in registers for both passes
+            uint32_t sc[64];
+            const uint32_t tmem_s = tmem_base + lane_sel + st * KEYS + ch * 64;
+            ptx::tmem_ld32(tmem_s, sc);
+            ptx::tmem_ld32(tmem_s + 32, sc + 32);
+            ptx::tmem_wait_ld();
+            const bool need_mask = (key0 + 64 > limit) || (key0 + 64 > mbeg) || (key0 < key_lo);
+            if (need_mask) {
 #pragma unroll
-                for (int c = 0; c < 32; ++c) r[c] = 0;
+                for (int c = 0; c < 64; ++c) {
+                    const int key = key0 + c;
+                    bool vis = key < limit && key >= key_lo;
+                    if (key >= mbeg) vis = vis && ((mword >> (key - mbeg)) & 1ull);
+                    if (!vis) sc[c] = 0xff800000u;  // -inf
+                }
             }
-            if (store) {
-                if (nsplit == 1) {
+            float mx[4] = {-INFINITY, -INFINITY, -INFINITY, -INFINITY};
 #pragma unroll
-                    for (int c = 0; c < 32; c += 8) {
-                        uint4 pk;
-                        uint32_t* w = reinterpret_cast<uint32_t*>(&pk);
+            for (int c = 0; c < 64; c += 4) {
+                mx[0] = fmaxf(mx[0], __uint_as_float(sc[c]));
+                mx[1] = fmaxf(mx[1], __uint_as_float(sc[c + 1]));
+                mx[2] = fmaxf(mx[2], __uint_as_float(sc[c + 2]));
+                mx[3] = fmaxf(mx[3], __uint_as_float(sc[c + 3]));
+            }
+            const float m_half = fmaxf(fmaxf(mx[0], mx[1]), fmaxf(mx[2], mx[3]));
+            xch[ch * ROWS + row] = m_half;
+            ptx::named_bar_sync(1, SOFTMAX_THREADS);
+            const float m_tile = fmaxf(m_half, xch[(ch ^ 1) * ROWS + row]);
+            ptx::named_bar_sync(2, SOFTMAX_THREADS);  // xch is rewritten by the next iteration
+            const float m_new = fmaxf(m_run, m_tile);
+            const float m_use = (m_new == -INFINITY) ? 0.f : m_new;
+            const float alpha = (m_run == -INFINITY) ? 1.f : fast_exp2((m_run - m_use) * a.scale_log2);
+            const bool rescale = (i > 0) && __any_sync(0xffffffffu, alpha != 1.f);
+            if (rescale) {  // O must hold every product issued so far: wait for PV(i-1)
+                if (!ptx::mbar_wait(&o_bar[(i - 1) & 1], ((i - 1) >> 1) & 1, abort_flag)) { ok = false; break; }
+                ptx::tc_fence_after();
+                __syncwarp();
+#pragma unroll 1
+                for (int c0 = 0; c0 < 64; c0 += 32) {
+                    uint32_t r[32];
+                    ptx::tmem_ld32(tmem_o + c0, r);
+                    ptx::tmem_wait_ld();
 #pragma unroll
-                        for (int e = 0; e < 4; ++e) {
-                            __nv_bfloat162 b2 = __floats2bfloat162_rn(__uint_as_float(r[c + e * 2]) * inv,
-                                                                      __uint_as_float(r[c + e * 2 + 1]) * inv);
-                            w[e] = *reinterpret_cast<uint32_t*>(&b2);
-                        }
-                        *reinterpret_cast<uint4*>(dst_b + c0 + c) = pk;
-                    }
+                    for (int c = 0; c < 32; ++c) r[c] = __float_as_uint(__uint_as_float(r[c]) * alpha);
+                    ptx::tmem_st32(tmem_o + c0, r);
+                }
+                ptx::tmem_wait_st();
+            }
+            m_run = m_new;
+            if (i >= 2) {  // P stage st was last read by PV(i-2)
+                if (!ptx::mbar_wait(&o_bar[st], ((i - 2) >> 1) & 1, abort_flag)) { ok = false; break; }
+            }
+
+            // ---- P = 2^((s - m) * scale) in bf16 into the swizzled A-operand tile; row sums in fp32
+            const float m_off = m_use * a.scale_log2;
+            float ls[4] = {0.f, 0.f, 0.f, 0.f};
+            uint8_t* p_half = smem + SMEM_P + st * TILE_BYTES + ch * HALF_BYTES + row * 128;
+#pragma unroll
+            for (int c8 = 0; c8 < 8; ++c8) {
+                float p[8];
+#pragma unroll
+                for (int e = 0; e < 8; ++e) {
+                    p[e] = fast_exp2(fmaf(__uint_as_float(sc[c8 * 8 + e]), a.scale_log2, -m_off));
+                    ls[e & 3] += p[e];
+                }
+                uint4 pk;
+                uint32_t* w = reinterpret_cast<uint32_t*>(&pk);
+#pragma unroll
+                for (int e = 0; e < 4; ++e) {
+                    __nv_bfloat162 b2 = __floats2bfloat162_rn(p[e * 2], p[e * 2 + 1]);
+                    w[e] = *reinterpret_cast<uint32_t*>(&b2);
+                }
+                *reinterpret_cast<uint4*>(p_half + ((c8 ^ (row & 7)) << 4)) = pk;
+            }
+            l_run = l_run * alpha + ((ls[0] + ls[1]) + (ls[2] + ls[3]));
+            ptx::fence_proxy_async_smem();  // P stores -> visible to the tensor core's async proxy
+            ptx::tc_fence_before();         // TMEM reads / rescale ordered before the control warp's next MMA
+            ptx::mbar_arrive(&p_ready[st]);
+        }
+        if (ok && n_it > 0) {
+            if (!ptx::mbar_wait(&o_bar[(n_it - 1) & 1], ((n_it - 1) >> 1) & 1, abort_flag)) ok = false;
+            ptx::tc_fence_after();
+        }
+        ok = __all_sync(0xffffffffu, ok);  // keep each warp together for the collective TMEM reads
+
+        // ---- write-out.  TMEM reads are warp-collective, so every thread runs them
+        // and only the global stores depend on whether the row exists.
+        xch[ch * ROWS + row] = l_run;
+        ptx::named_bar_sync(1, SOFTMAX_THREADS);
+        const float l_row = l_run + xch[(ch ^ 1) * ROWS + row];
+        if (ok) {
+            const bool store = (t < a.tq);
+            const size_t grow = static_cast<size_t>(store ? t : 0) * a.hq + qh;
+            const float inv = (nsplit == 1) ? ((l_row > 0.f) ? 1.f / l_row : 0.f) : 1.f;
+            bf16* dst_b = a.out + static_cast<size_t>(store ? t : 0) * a.out_ld + qh * D + ch * 64;
+            float* dst_f =
+                (nsplit > 1) ? a.ws_o + (static_cast<size_t>(split) * a.tq * a.hq + grow) * D + ch * 64 : nullptr;
+#pragma unroll 1
+            for (int c0 = 0; c0 < 64; c0 += 32) {
+                uint32_t r[32];
+                if (n_it > 0) {  // uniform across the CTA
+                    ptx::tmem_ld32(tmem_o + c0, r);
+                    ptx::tmem_wait_ld();
                 } else {
 #pragma unroll
-                    for (int c = 0; c < 32; c += 4) {
-                        *reinterpret_cast<uint4*>(dst_f + c0 + c) = make_uint4(r[c], r[c + 1], r[c + 2], r[c + 3]);
+                    for (int c = 0; c < 32; ++c) r[c] = 0;
+                }
+                if (store) {
+                    if (nsplit == 1) {
+#pragma unroll
+                        for (int c = 0; c < 32; c += 8) {
+                            uint4 pk;
+                            uint32_t* w = reinterpret_cast<uint32_t*>(&pk);
+#pragma unroll
+                            for (int e = 0; e < 4; ++e) {
+                                __nv_bfloat162 b2 = __floats2bfloat162_rn(__uint_as_float(r[c + e * 2]) * inv,
+                                                                          __uint_as_float(r[c + e * 2 + 1]) * inv);
+                                w[e] = *reinterpret_cast<uint32_t*>(&b2);
+                            }
+                            *reinterpret_cast<uint4*>(dst_b + c0 + c) = pk;
+                        }
+                    } else {
+#pragma unroll
+                        for (int c = 0; c < 32; c += 4) {
+                            *reinterpret_cast<uint4*>(dst_f + c0 + c) = make_uint4(r[c], r[c + 1], r[c + 2], r[c + 3]);
+                        }
                     }
                 }
             }
-        }
-        if (store && nsplit > 1 && ch == 0) {
-            float* ml = a.ws_ml + (static_cast<size_t>(split) * a.tq * a.hq + grow) * 2;
-            ml[0] = m_run;
-            ml[1] = l_row;
+            if (store && nsplit > 1 && ch == 0) {
+                float* ml = a.ws_ml + (static_cast<size_t>(split) * a.tq * a.hq + grow) * 2;
+                ml[0] = m_run;
+                ml[1] = l_row;
+            }
         }
     }
 
@@ -373,7 +387,7 @@ tree_attn_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant
         ptx::tc_fence_after();
         ptx::tmem_dealloc(tmem_base, TMEM_COLS);
     }
-    if (leader && *abort_flag) atomicOr(a.error, ERR_ATTN_TIMEOUT);
+    if (tid == 0 && *abort_flag) atomicOr(a.error, ERR_ATTN_TIMEOUT);
 }
 
 // Merge split partials: out = sum_s 2^((m_s - M) c) O_s / sum_s 2^((m_s - M) c) l_s.
