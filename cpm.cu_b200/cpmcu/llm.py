@@ -70,16 +70,21 @@ class LLM(torch.nn.Module):
         scale_embed = getattr(cfg, "scale_emb", 1.0)
         scale_lmhead = (cfg.dim_model_base / cfg.hidden_size) if hasattr(cfg, "dim_model_base") else 1.0
         scale_residual = cfg.scale_depth / math.sqrt(cfg.num_hidden_layers) if hasattr(cfg, "scale_depth") else 1.0
+        self._init_native(memory_limit, scale_embed, scale_lmhead, scale_residual, apply_sparse,
+                          (sink_window_size, block_window_size, sparse_topk_k, sparse_switch, apply_compress_lse))
+        self.logits = torch.empty((64, cfg.vocab_size), dtype=self.dtype, device="cuda")
+        self.max_total_length = 0
+
+    def _init_native(self, memory_limit, scale_embed, scale_lmhead, scale_residual, apply_sparse, sparse_args):
+        """Create the native model (bf16 target).  Quantised subclasses override this."""
+        cfg = self.config
         common = (memory_limit, cfg.vocab_size, cfg.num_hidden_layers, cfg.hidden_size, cfg.intermediate_size,
                   cfg.num_attention_heads, cfg.num_key_value_heads, cfg.head_dim, cfg.rms_norm_eps, self.dtype_int,
                   self.chunk_length, scale_embed, scale_lmhead, scale_residual)
         if apply_sparse:
-            C.init_minicpm4_model(*common, sink_window_size, block_window_size, sparse_topk_k, sparse_switch,
-                                  apply_compress_lse)
+            C.init_minicpm4_model(*common, *sparse_args)
         else:
             C.init_base_model(*common)
-        self.logits = torch.empty((64, cfg.vocab_size), dtype=self.dtype, device="cuda")
-        self.max_total_length = 0
 
     # ------------------------------------------------------------------ storage / weights
     def init_storage(self):

@@ -100,9 +100,33 @@ int cpmcu_init_minicpm4_model(float memory_limit, int vocab_size, int num_hidden
                                  chunk_length, scale_embed, scale_lmhead, scale_residual);
 }
 
-int cpmcu_init_w4a16_gptq_marlin_base_model(float, int, int, int, int, int, int, int, float, int, int, int, float, float,
-                                            float) {
-    return not_built("the W4A16 GPTQ-Marlin target");
+int cpmcu_init_w4a16_gptq_marlin_base_model(float memory_limit, int vocab_size, int num_hidden_layers,
+                                            int hidden_size, int intermediate_size, int num_attention_heads,
+                                            int num_key_value_heads, int head_dim, float rms_norm_eps,
+                                            int group_size, int torch_dtype, int chunk_length, float scale_embed,
+                                            float scale_lmhead, float scale_residual) {
+    return guarded([&] {
+        require_bf16(torch_dtype);
+        ModelConfig mc;
+        mc.memory_limit = memory_limit;
+        mc.vocab = vocab_size;
+        mc.layers = num_hidden_layers;
+        mc.hidden = hidden_size;
+        mc.inter = intermediate_size;
+        mc.hq = num_attention_heads;
+        mc.hkv = num_key_value_heads;
+        mc.head_dim = head_dim;
+        mc.eps = rms_norm_eps;
+        mc.chunk_length = chunk_length;
+        mc.scale_embed = scale_embed;
+        mc.scale_lmhead = scale_lmhead;
+        mc.scale_residual = scale_residual;
+        mc.w4a16 = true;
+        mc.group_size = group_size;
+        g_engine.reset();
+        g_engine = std::make_unique<Engine>(mc);
+        return 0;
+    });
 }
 int cpmcu_init_w4a16_gptq_marlin_minicpm4_model(float, int, int, int, int, int, int, int, float, int, int, int, float,
                                                 float, float, int, int, int, int, int) {

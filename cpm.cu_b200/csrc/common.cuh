@@ -137,6 +137,10 @@ LinearPlan make_linear_plan(const bf16* x, int x_rows, const bf16* w, int M, int
                             const bf16* bias, float* workspace, int* tickets, int grid_limit);
 void launch_linear(const LinearPlan& plan, cudaStream_t stream);
 
+// W4A16 GPTQ-Marlin tensor (packed int32 [K/16, 2N] + permuted bf16 scales [K/128, N]) -> bf16 [N, K].
+void marlin_dequant_to_bf16(const void* packed, const void* scales, int K, int N, int group_size, bf16* dst,
+                            cudaStream_t s);
+
 // ---------------------------------------------------------------- small ops
 void launch_rms_norm(const bf16* x, int ldx, const bf16* w, bf16* y, int ldy, int rows, int dim, float eps,
                      cudaStream_t s);

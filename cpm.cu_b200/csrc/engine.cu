@@ -69,6 +69,10 @@ Engine::Engine(const ModelConfig& mc) : mc_(mc) {
     CPM_REQUIRE(mc.hidden % 64 == 0 && mc.inter % 64 == 0, "hidden and intermediate sizes must be multiples of 64");
     CPM_REQUIRE(mc.hq % mc.hkv == 0, "num_attention_heads must be a multiple of num_key_value_heads");
     CPM_REQUIRE((mc.hq * mc.head_dim) % 64 == 0, "attention width must be a multiple of 64");
+    if (mc.w4a16) {
+        CPM_REQUIRE(mc.group_size == 128, "W4A16: only group_size 128 is supported");
+        CPM_REQUIRE(mc.hidden % 128 == 0 && mc.inter % 128 == 0, "W4A16: hidden and intermediate sizes must be multiples of 128");
+    }
     qkv_dim_ = (mc.hq + 2 * mc.hkv) * mc.head_dim;
     layers_.resize(mc.layers);
     kv_.resize(mc.layers);
@@ -273,6 +277,17 @@ void Engine::load(const std::string& name, const void* src) {
         CUDA_CHECK(cudaMemcpyAsync(dst, src, bytes, cudaMemcpyDefault, rt.stream));
         CUDA_CHECK(cudaStreamSynchronize(rt.stream));
     };
+    auto load_quant_layer = [&](LayerWeights& w, const std::string& key, const std::string& sub) -> bool {
+        // fused W4A16 tensors of the reference converter: qkv_proj, o_proj, gate_up_proj, down_proj
+        const bool is_scales = sub.find("scales") != std::string::npos;
+        if (!is_scales && sub.find("qweight") == std::string::npos) return false;
+        if (sub.find("qkv_proj") != std::string::npos) load_quantized(key + ".qkv", is_scales, src, H, qkv_dim_, w.qkv);
+        else if (sub.find("o_proj") != std::string::npos) load_quantized(key + ".o", is_scales, src, mc_.hq * d, H, w.o);
+        else if (sub.find("gate_up_proj") != std::string::npos) load_quantized(key + ".gu", is_scales, src, H, 2 * I, w.gate_up);
+        else if (sub.find("down_proj") != std::string::npos) load_quantized(key + ".down", is_scales, src, I, H, w.down);
+        else throw std::invalid_argument("Unsupported quantized tensor " + sub);
+        return true;
+    };
     auto load_layer = [&](LayerWeights& w, const std::string& sub) {
         const size_t qn = static_cast<size_t>(mc_.hq) * d * H, kn = static_cast<size_t>(mc_.hkv) * d * H;
         if (sub.find("q_proj") != std::string::npos) copy(w.qkv, qn * 2);
@@ -341,9 +356,28 @@ void Engine::load(const std::string& name, const void* src) {
     } else if (name.rfind("model.layers", 0) == 0 && std::regex_search(name, m, layer_re)) {
         const int li = std::stoi(m[1]);
         CPM_REQUIRE(li >= 0 && li < mc_.layers, "layer index out of range: " + name);
+        if (mc_.w4a16 && load_quant_layer(layers_[li], "L" + std::to_string(li), m[2])) return;
         load_layer(layers_[li], m[2]);
     } else {
         throw std::invalid_argument("Unsupported name " + name);
+    }
+}
+
+void Engine::load_quantized(const std::string& key, bool is_scales, const void* src, int K, int N, bf16* dst) {
+    Runtime& rt = runtime();
+    PendingQuant& p = pending_quant_[key];
+    const size_t bytes = is_scales ? static_cast<size_t>(K / mc_.group_size) * N * 2 : static_cast<size_t>(K) * N / 2;
+    void*& slot = is_scales ? p.scales : p.qweight;
+    CPM_REQUIRE(slot == nullptr, "quantized tensor loaded twice: " + key);
+    CUDA_CHECK(cudaMalloc(&slot, bytes));
+    CUDA_CHECK(cudaMemcpyAsync(slot, src, bytes, cudaMemcpyDefault, rt.stream));
+    CUDA_CHECK(cudaStreamSynchronize(rt.stream));
+    if (p.qweight != nullptr && p.scales != nullptr) {
+        marlin_dequant_to_bf16(p.qweight, p.scales, K, N, mc_.group_size, dst, rt.stream);
+        CUDA_CHECK(cudaStreamSynchronize(rt.stream));
+        cudaFree(p.qweight);
+        cudaFree(p.scales);
+        pending_quant_.erase(key);
     }
 }
 

@@ -20,6 +20,8 @@ struct ModelConfig {
     float eps = 1e-5f;
     int chunk_length = 1024;
     float scale_embed = 1.f, scale_lmhead = 1.f, scale_residual = 1.f;
+    bool w4a16 = false;  // target linears arrive as GPTQ-Marlin int4 + scales (embeddings / LM head stay bf16)
+    int group_size = 128;
 };
 
 struct EagleConfig {
@@ -157,6 +159,13 @@ private:
     int32_t* token_id_remap_ = nullptr;
     int draft_vocab_ = 0;
     bool remap_loaded_ = false;
+    // W4A16 loading: whichever of (qweight, scales) arrives first waits here for the other
+    struct PendingQuant {
+        void* qweight = nullptr;
+        void* scales = nullptr;
+    };
+    std::map<std::string, PendingQuant> pending_quant_;
+    void load_quantized(const std::string& key, bool is_scales, const void* src, int K, int N, bf16* dst);
 
     // activations
     bf16 *x_ = nullptr, *normed_ = nullptr, *qkv_ = nullptr, *attn_out_ = nullptr, *delta_ = nullptr,

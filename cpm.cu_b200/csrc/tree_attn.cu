@@ -140,9 +140,10 @@ tree_attn_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant
     if (key_hi < 0) key_hi = 0;
     int key_lo = 0;
     if (a.window > 0) {
-        // block-granular sliding window of the draft layer (reference
+        // block-granular sliding window of the draft layer: the reference derives the bound per
+        // 64-row query block (src/flash_attn/src/flash_fwd_kernel.h:1517 passes m_block * 64 to
         // src/flash_attn/src/flash_blockmask.h:29-33, 128-key blocks)
-        const int q0 = causal_base + t0;
+        const int q0 = causal_base + (t0 / 64) * 64;
         const int lo_blk = (q0 + KEYS - 1) / KEYS - a.window / KEYS;
         if (lo_blk > 0) key_lo = lo_blk * KEYS;
     }

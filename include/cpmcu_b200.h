@@ -47,8 +47,11 @@ int cpmcu_init_minicpm4_model(float memory_limit, int vocab_size, int num_hidden
                               float scale_embed, float scale_lmhead, float scale_residual, int sink_window_size,
                               int block_window_size, int sparse_topk_k, int sparse_switch, int apply_compress_lse);
 
-/* reference: init_w4a16_gptq_marlin_base_model, src/entry.cu:186-225, and
- * init_w4a16_gptq_marlin_minicpm4_model, :227-275.  Not built: always fail. */
+/* reference: init_w4a16_gptq_marlin_base_model, src/entry.cu:186-225.  Target whose linears
+ * arrive as GPTQ-Marlin tensors (`...qkv_proj|o_proj|gate_up_proj|down_proj.{qweight,scales}`,
+ * int32 in Marlin tile order + model-dtype scales, group_size 128).  They are unpacked and
+ * dequantised, w = (q - 8) * scale, when loaded; the forward pass then runs the bf16 GEMM.
+ * init_w4a16_gptq_marlin_minicpm4_model (:227-275, sparse + W4A16) is not built: always fails. */
 int cpmcu_init_w4a16_gptq_marlin_base_model(float memory_limit, int vocab_size, int num_hidden_layers,
                                             int hidden_size, int intermediate_size, int num_attention_heads,
                                             int num_key_value_heads, int head_dim, float rms_norm_eps,

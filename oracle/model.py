@@ -172,10 +172,14 @@ class OracleModel:
                     bits[t, mbeg + c] = (m >> c) & 1
             vis = vis & ((cols[None, :] < mbeg) | bits)
         if window > 0:
-            q0 = kv_total - tq_valid
-            lo_blk = (q0 + 127) // 128 - window // 128
-            if lo_blk > 0:
-                vis = vis & (cols[None, :] >= lo_blk * 128)
+            # block-granular left bound per 64-row query block (flash_blockmask.h:29-33 with the
+            # loop_step_idx = m_block * 64 of flash_fwd_kernel.h:1517): key blocks of 128 below
+            # ceil(q0 / 128) - window / 128 are skipped
+            for blk in range(0, tq, 64):
+                q0 = kv_total - tq_valid + blk
+                lo_blk = (q0 + 127) // 128 - window // 128
+                if lo_blk > 0:
+                    vis[blk:blk + 64] = vis[blk:blk + 64] & (cols[None, :] >= lo_blk * 128)
         out = torch.zeros(tq, cfg.hq, d)
         scale = 1.0 / math.sqrt(d)
         for h in range(cfg.hq):

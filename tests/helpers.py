@@ -52,3 +52,53 @@ def build_pair(cfg, eagle, seed=0, chunk_length=256, layer_scale=0.6, fc_mode="e
 def top2_gap(logits_row):
     v = torch.topk(logits_row.float(), 2).values
     return float(v[0] - v[1])
+
+
+def quantize_target(cfg, w):
+    """W4A16 view of a target: returns (weights with the four linears replaced by their dequantised
+    values, for the oracle) and the Marlin checkpoint tensors the reference converter would produce
+    (fused qkv_proj / gate_up_proj, int32 qweight + bf16 scales)."""
+    from oracle import marlin
+    w = dict(w)
+    ckpt = {}
+    for l in range(cfg.layers):
+        p = "model.layers.%d." % l
+        groups = {"self_attn.qkv_proj": ["self_attn.q_proj", "self_attn.k_proj", "self_attn.v_proj"],
+                  "self_attn.o_proj": ["self_attn.o_proj"], "mlp.gate_up_proj": ["mlp.gate_proj", "mlp.up_proj"],
+                  "mlp.down_proj": ["mlp.down_proj"]}
+        for fused, parts in groups.items():
+            full = torch.cat([w[p + n + ".weight"] for n in parts], dim=0)          # [N, K]
+            q, s = marlin.quantize_sym_int4(full.t().contiguous().numpy())            # [K, N]
+            packed, sperm = marlin.marlin_pack(q, s)
+            deq = torch.from_numpy(marlin.dequantize(q, s)).t().contiguous()          # [N, K]
+            row = 0
+            for n in parts:
+                rows = w[p + n + ".weight"].shape[0]
+                w[p + n + ".weight"] = deq[row:row + rows].clone()
+                row += rows
+            ckpt[p + fused + ".qweight"] = torch.from_numpy(packed.copy())
+            ckpt[p + fused + ".scales"] = torch.from_numpy(sperm.copy()).to(torch.bfloat16)
+    for name in ("model.embed_tokens.weight", "lm_head.weight", "model.norm.weight"):
+        ckpt[name] = w[name].to(torch.bfloat16)
+    for l in range(cfg.layers):
+        for n in ("input_layernorm", "post_attention_layernorm"):
+            ckpt["model.layers.%d.%s.weight" % (l, n)] = w["model.layers.%d.%s.weight" % (l, n)].to(torch.bfloat16)
+    return w, ckpt
+
+
+def build_quant_pair(cfg, eagle, seed=0, chunk_length=256, layer_scale=0.6, fc_gain=200.0, budget=1024):
+    from cpmcu.speculative.eagle_base_quant.eagle_base_w4a16_marlin_gptq import W4A16GPTQMarlinLLM_with_eagle
+    import os
+    w, ew = make_weights(cfg, seed, eagle, layer_scale=layer_scale, fc_mode="embed", fc_gain=fc_gain)
+    wq, ckpt = quantize_target(cfg, w)
+    oracle = OracleModel(cfg, wq, eagle, ew, budget=budget)
+    hf = hf_config(cfg)
+    hf.quantization_config = {"group_size": 128, "bits": 4}
+    llm = W4A16GPTQMarlinLLM_with_eagle(None, None, num_iter=eagle.num_iter, topk_per_iter=eagle.topk,
+                                        tree_size=eagle.tree_size, eagle_config={"num_hidden_layers": 1}, config=hf,
+                                        dtype=torch.bfloat16, chunk_length=chunk_length, memory_limit=0.5)
+    os.environ.setdefault("CPMCU_MAX_TOKENS", "4096")
+    llm.init_storage()
+    llm.load_state_dict_tensors({k: v.to(torch.bfloat16) for k, v in ew.items()}, cls="eagle")
+    llm.load_state_dict_tensors(ckpt)
+    return oracle, llm

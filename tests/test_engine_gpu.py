@@ -5,7 +5,7 @@ import numpy as np
 import pytest
 import torch
 
-from helpers import build_pair, tiny_configs, top2_gap
+from helpers import build_pair, build_quant_pair, tiny_configs, top2_gap
 from oracle.model import EagleOracleConfig
 
 pytestmark = pytest.mark.gpu
@@ -142,14 +142,48 @@ def test_frspec_reduced_vocabulary():
         assert set(st["ids"][1:].tolist()) <= set(remap.tolist())
 
 
+def test_draft_sliding_window():
+    cfg = tiny_configs("a")
+    eagle = EagleOracleConfig(num_iter=3, topk=4, tree_size=12, window=128, minicpm4_variant=True)
+    oracle, llm = build_pair(cfg, eagle, seed=6, chunk_length=512)
+    prompt = prompt_ids(400, cfg.vocab, 6)  # longer than the window: the drafter sees only the last key blocks
+    tokens, acc, _, _ = llm.generate(torch.tensor(prompt, device="cuda"), 24)
+    o_tokens, o_acc, steps = oracle.generate_spec(prompt.tolist(), 24)
+    assert_stream_matches(tokens, o_tokens, steps, "draft window vs oracle")
+    if tokens == o_tokens:
+        assert acc == o_acc
+
+
+def test_w4a16_marlin_target_matches_oracle():
+    from oracle.model import OracleConfig
+    cfg = OracleConfig(vocab=4096, layers=2, hidden=256, inter=768, hq=2, hkv=1, head_dim=128, dtype="bf16")
+    eagle = EagleOracleConfig(num_iter=4, topk=4, tree_size=16)
+    oracle, llm = build_quant_pair(cfg, eagle, seed=8)
+    prompt = prompt_ids(120, cfg.vocab, 8)
+    ids_t = torch.tensor(prompt, device="cuda")
+    pos_t = torch.arange(len(prompt), dtype=torch.int32, device="cuda")
+    logits = llm.prefill(ids_t, pos_t)
+    o_logits = oracle.prefill(prompt.tolist())
+    assert float((logits[0].float().cpu() - o_logits).abs().max()) <= 2e-2 * float(o_logits.abs().max())
+    oracle, llm = build_quant_pair(cfg, eagle, seed=8)
+    tokens, acc, _, _ = llm.generate(ids_t, 30)
+    o_tokens, o_acc, steps = oracle.generate_spec(prompt.tolist(), 30)
+    assert_stream_matches(tokens, o_tokens, steps, "w4a16 vs oracle")
+    if tokens == o_tokens:
+        assert acc == o_acc
+
+
 def test_errors_are_loud():
     import cpmcu.C as C
     with pytest.raises(RuntimeError):
         C.init_base_model(0.5, 1000, 1, 256, 704, 2, 1, 64, 1e-5, 1, 128, 1.0, 1.0, 1.0)  # head_dim 64
     with pytest.raises(RuntimeError):
         C.init_base_model(0.5, 1000, 1, 256, 704, 2, 1, 128, 1e-5, 0, 128, 1.0, 1.0, 1.0)  # fp16
+    with pytest.raises(RuntimeError):  # group size 64 / hidden not a multiple of 128
+        C.init_w4a16_gptq_marlin_base_model(0.5, 1000, 1, 256, 704, 2, 1, 128, 1e-5, 64, 1, 128, 1.0, 1.0, 1.0)
     with pytest.raises(RuntimeError):
-        C.init_w4a16_gptq_marlin_base_model(0.5, 1000, 1, 256, 704, 2, 1, 128, 1e-5, 128, 1, 128, 1.0, 1.0, 1.0)
+        C.init_w4a16_gptq_marlin_minicpm4_model(0.5, 1000, 1, 256, 768, 2, 1, 128, 1e-5, 128, 1, 128, 1.0, 1.0, 1.0,
+                                                1, 32, 32, 8192, False)
     C.init_base_model(0.5, 1000, 1, 256, 704, 2, 1, 128, 1e-5, 1, 128, 1.0, 1.0, 1.0)
     with pytest.raises(RuntimeError):
         C.load_model("model.norm.weight", 0)  # before init_storage

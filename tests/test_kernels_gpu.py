@@ -96,10 +96,11 @@ def ref_attention(q, kc, vc, kv_total, tq_valid, hq, hkv, mask, mask_k, window=0
             for cc in range(mask_k):
                 bits[t, mbeg + cc] = bool((m >> cc) & 1)
         vis = vis & ((cols[None, :] < mbeg) | bits)
-    if window > 0:
-        lo_blk = (kv_total - tq_valid + 127) // 128 - window // 128
-        if lo_blk > 0:
-            vis = vis & (cols[None, :] >= lo_blk * 128)
+    if window > 0:  # block-granular bound per 64-row query block, 128-key blocks
+        for blk in range(0, tq, 64):
+            lo_blk = (kv_total - tq_valid + blk + 127) // 128 - window // 128
+            if lo_blk > 0:
+                vis[blk:blk + 64] = vis[blk:blk + 64] & (cols[None, :] >= lo_blk * 128)
     out = torch.zeros(tq, hq, d, device=q.device)
     qf = q.float().view(tq, hq, d)
     for h in range(hq):
@@ -127,15 +128,18 @@ def random_tree_masks(T, rng, max_depth=7):
 
 
 ATTN_CASES = [
-    # tq, hq, hkv, prefix L, mode, splits
+    # tq, hq, hkv, prefix L, mode, splits[, window]
+    (10, 32, 2, 1500, "tree", 6, 512), (7, 32, 2, 1301, "valid3", 4, 256), (150, 4, 2, 700, "causal", 1, 384),
     (16, 2, 1, 300, "tree", 1), (16, 2, 1, 300, "tree", 3), (60, 32, 2, 1000, "tree", 4), (60, 32, 2, 129, "tree", 9),
     (10, 8, 2, 517, "tree", 5), (200, 4, 2, 0, "causal", 1), (130, 8, 2, 100, "causal", 1),
     (7, 32, 2, 777, "valid3", 6), (1, 32, 2, 400, "causal", 8), (64, 16, 1, 64, "tree", 2),
 ]
 
 
-@pytest.mark.parametrize("tq,hq,hkv,L,mode,splits", ATTN_CASES)
-def test_tree_attention_matches_fp32(tq, hq, hkv, L, mode, splits):
+@pytest.mark.parametrize("case", ATTN_CASES)
+def test_tree_attention_matches_fp32(case):
+    tq, hq, hkv, L, mode, splits = case[:6]
+    window = case[6] if len(case) > 6 else 0
     c = C()
     rng = np.random.default_rng(tq * 7 + hq * 13 + L)
     g = torch.Generator().manual_seed(tq + hq + L)
@@ -162,9 +166,9 @@ def test_tree_attention_matches_fp32(tq, hq, hkv, L, mode, splits):
     kv_len = dev(torch.tensor([kv_total - 5], dtype=torch.int32))  # exercise the host-side addend
     out = torch.full((tq, hq * 128), float("nan"), dtype=torch.bfloat16, device="cuda")
     c.call("cpmcu_tree_attention", ptr(qkv), q_ld, ptr(kc), ptr(vc), budget, tq, hq, hkv, ptr(kv_len), 5,
-           ptr(n_valid), ptr(mask_t), mask_k, 0, splits, ptr(out), hq * 128)
+           ptr(n_valid), ptr(mask_t), mask_k, window, splits, ptr(out), hq * 128)
     q = qkv.view(tq, q_ld)[:, : hq * 128].contiguous().view(tq, hq, 128)
-    ref = ref_attention(q, kc, vc, kv_total, tq_valid, hq, hkv, masks, mask_k)
+    ref = ref_attention(q, kc, vc, kv_total, tq_valid, hq, hkv, masks, mask_k, window)
     got = out.float().view(tq, hq, 128)
     assert torch.isfinite(got).all()
     err = (got[:tq_valid] - ref[:tq_valid]).abs().max().item()
