@@ -105,6 +105,9 @@ __device__ __forceinline__ void grid_dependency_sync() {
 // elements (128 B).  Strides are in bytes and must be multiples of 16.
 CUtensorMap make_tmap_2d(const void* base, uint64_t inner, uint64_t outer, uint64_t outer_stride_bytes,
                          uint32_t box_inner, uint32_t box_outer);
+// Untyped byte matrix without swizzle (packed int4 weights).
+CUtensorMap make_tmap_2d_u8(const void* base, uint64_t inner_bytes, uint64_t outer, uint64_t outer_stride_bytes,
+                            uint32_t box_inner_bytes, uint32_t box_outer);
 CUtensorMap make_tmap_3d(const void* base, uint64_t d0, uint64_t d1, uint64_t d2, uint64_t stride1_bytes,
                          uint64_t stride2_bytes, uint32_t b0, uint32_t b1, uint32_t b2);
 
@@ -122,6 +125,9 @@ struct LinearPlan {
     float* workspace = nullptr;  // split-K partials: grid * 2 * mt * 128 floats
     int* tickets = nullptr;      // one counter per output tile, zero between launches
     int debug = 0;               // bench-only switches, see gemm_umma.cu
+    // W4A16: when wq is set the weights are 4-bit (see gemm_w4_umma.cu); tm_w then maps the packed bytes
+    const uint32_t* wq = nullptr;   // [N][K/8] packed nibbles, k-contiguous
+    const bf16* wscales = nullptr;  // [K/128][N]
     // Optional fused epilogue: y = silu(gate) * up where gate/up rows alternate
     // in 64-row halves of each 128-row weight tile (see make_linear_plan).
     int epilogue = 0;
@@ -136,6 +142,14 @@ int linear_pick_mt(int M);
 LinearPlan make_linear_plan(const bf16* x, int x_rows, const bf16* w, int M, int N, int K, bf16* y, int ldy,
                             const bf16* bias, float* workspace, int* tickets, int grid_limit);
 void launch_linear(const LinearPlan& plan, cudaStream_t stream);
+// Same contract with 4-bit weights: wq [N][K/8] uint32 (nibble order k0 k2 k4 k6 k1 k3 k5 k7 from bit 0),
+// scales [K/128][N] bf16, w = (q - 8) * scale.  K % 256 == 0 and N % 128 == 0.
+LinearPlan make_linear_plan_w4(const bf16* x, int x_rows, const uint32_t* wq, const bf16* wscales, int M, int N, int K,
+                               bf16* y, int ldy, float* workspace, int* tickets, int grid_limit);
+void launch_linear_w4(const LinearPlan& plan, cudaStream_t stream);
+size_t linear_w4_workspace_bytes(int mt, int grid);
+// Marlin tensors (packed int32 [K/16, 2N], permuted scales [K/128, N]) -> the layout above.
+void marlin_retile_for_w4(const void* packed, const void* scales, int K, int N, uint32_t* wq, bf16* wscales, cudaStream_t s);
 
 // W4A16 GPTQ-Marlin tensor (packed int32 [K/16, 2N] + permuted bf16 scales [K/128, N]) -> bf16 [N, K].
 void marlin_dequant_to_bf16(const void* packed, const void* scales, int K, int N, int group_size, bf16* dst,

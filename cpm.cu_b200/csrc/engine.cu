@@ -71,7 +71,8 @@ Engine::Engine(const ModelConfig& mc) : mc_(mc) {
     CPM_REQUIRE((mc.hq * mc.head_dim) % 64 == 0, "attention width must be a multiple of 64");
     if (mc.w4a16) {
         CPM_REQUIRE(mc.group_size == 128, "W4A16: only group_size 128 is supported");
-        CPM_REQUIRE(mc.hidden % 128 == 0 && mc.inter % 128 == 0, "W4A16: hidden and intermediate sizes must be multiples of 128");
+        CPM_REQUIRE(mc.hidden % 256 == 0 && mc.inter % 256 == 0 && (mc.hq * mc.head_dim) % 256 == 0,
+                    "W4A16: hidden, intermediate and attention widths must be multiples of 256");
     }
     qkv_dim_ = (mc.hq + 2 * mc.hkv) * mc.head_dim;
     layers_.resize(mc.layers);
@@ -122,10 +123,21 @@ void Engine::lay_out(Pool& p) {
     final_norm_ = take<bf16>(p, H);
     inv_freq_ = take<float>(p, d / 2);
     for (auto& w : layers_) {
-        w.qkv = take<bf16>(p, static_cast<size_t>(qkv_dim_) * H);
-        w.o = take<bf16>(p, static_cast<size_t>(H) * mc_.hq * d);
-        w.gate_up = take<bf16>(p, static_cast<size_t>(2) * I * H);
-        w.down = take<bf16>(p, static_cast<size_t>(H) * I);
+        if (mc_.w4a16) {
+            auto take_q = [&](uint32_t*& q, bf16*& s, size_t n, size_t k) {
+                q = take<uint32_t>(p, n * k / 8);
+                s = take<bf16>(p, (k / 128) * n);
+            };
+            take_q(w.qkv_q, w.qkv_s, qkv_dim_, H);
+            take_q(w.o_q, w.o_s, H, static_cast<size_t>(mc_.hq) * d);
+            take_q(w.gate_up_q, w.gate_up_s, static_cast<size_t>(2) * I, H);
+            take_q(w.down_q, w.down_s, H, I);
+        } else {
+            w.qkv = take<bf16>(p, static_cast<size_t>(qkv_dim_) * H);
+            w.o = take<bf16>(p, static_cast<size_t>(H) * mc_.hq * d);
+            w.gate_up = take<bf16>(p, static_cast<size_t>(2) * I * H);
+            w.down = take<bf16>(p, static_cast<size_t>(H) * I);
+        }
         w.ln_attn = take<bf16>(p, H);
         w.ln_ffn = take<bf16>(p, H);
     }
@@ -281,10 +293,10 @@ void Engine::load(const std::string& name, const void* src) {
         // fused W4A16 tensors of the reference converter: qkv_proj, o_proj, gate_up_proj, down_proj
         const bool is_scales = sub.find("scales") != std::string::npos;
         if (!is_scales && sub.find("qweight") == std::string::npos) return false;
-        if (sub.find("qkv_proj") != std::string::npos) load_quantized(key + ".qkv", is_scales, src, H, qkv_dim_, w.qkv);
-        else if (sub.find("o_proj") != std::string::npos) load_quantized(key + ".o", is_scales, src, mc_.hq * d, H, w.o);
-        else if (sub.find("gate_up_proj") != std::string::npos) load_quantized(key + ".gu", is_scales, src, H, 2 * I, w.gate_up);
-        else if (sub.find("down_proj") != std::string::npos) load_quantized(key + ".down", is_scales, src, I, H, w.down);
+        if (sub.find("qkv_proj") != std::string::npos) load_quantized(key + ".qkv", is_scales, src, H, qkv_dim_, w.qkv_q, w.qkv_s);
+        else if (sub.find("o_proj") != std::string::npos) load_quantized(key + ".o", is_scales, src, mc_.hq * d, H, w.o_q, w.o_s);
+        else if (sub.find("gate_up_proj") != std::string::npos) load_quantized(key + ".gu", is_scales, src, H, 2 * I, w.gate_up_q, w.gate_up_s);
+        else if (sub.find("down_proj") != std::string::npos) load_quantized(key + ".down", is_scales, src, I, H, w.down_q, w.down_s);
         else throw std::invalid_argument("Unsupported quantized tensor " + sub);
         return true;
     };
@@ -363,7 +375,8 @@ void Engine::load(const std::string& name, const void* src) {
     }
 }
 
-void Engine::load_quantized(const std::string& key, bool is_scales, const void* src, int K, int N, bf16* dst) {
+void Engine::load_quantized(const std::string& key, bool is_scales, const void* src, int K, int N, uint32_t* wq,
+                            bf16* ws) {
     Runtime& rt = runtime();
     PendingQuant& p = pending_quant_[key];
     const size_t bytes = is_scales ? static_cast<size_t>(K / mc_.group_size) * N * 2 : static_cast<size_t>(K) * N / 2;
@@ -373,7 +386,8 @@ void Engine::load_quantized(const std::string& key, bool is_scales, const void* 
     CUDA_CHECK(cudaMemcpyAsync(slot, src, bytes, cudaMemcpyDefault, rt.stream));
     CUDA_CHECK(cudaStreamSynchronize(rt.stream));
     if (p.qweight != nullptr && p.scales != nullptr) {
-        marlin_dequant_to_bf16(p.qweight, p.scales, K, N, mc_.group_size, dst, rt.stream);
+        // Marlin tile order -> row-major k-contiguous nibbles + group-major scales for the streaming kernel
+        marlin_retile_for_w4(p.qweight, p.scales, K, N, wq, ws, rt.stream);
         CUDA_CHECK(cudaStreamSynchronize(rt.stream));
         cudaFree(p.qweight);
         cudaFree(p.scales);
@@ -385,10 +399,17 @@ void Engine::load_quantized(const std::string& key, bool is_scales, const void* 
 void Engine::build_layer_plans(LayerPlans& lp, const LayerWeights& w, const KVLayer& kv, int rows, int attn_splits) {
     const int H = mc_.hidden, I = mc_.inter, d = mc_.head_dim;
     const int sms = runtime().num_sms;
-    lp.qkv = make_linear_plan(normed_, rows, w.qkv, rows, qkv_dim_, H, qkv_, qkv_dim_, nullptr, gemm_ws_, tickets_, sms);
-    lp.o = make_linear_plan(attn_out_, rows, w.o, rows, H, mc_.hq * d, delta_, H, nullptr, gemm_ws_, tickets_, sms);
-    lp.gate_up = make_linear_plan(normed_, rows, w.gate_up, rows, 2 * I, H, gate_up_, 2 * I, nullptr, gemm_ws_, tickets_, sms);
-    lp.down = make_linear_plan(act_, rows, w.down, rows, H, I, delta_, H, nullptr, gemm_ws_, tickets_, sms);
+    if (w.qkv_q != nullptr) {  // W4A16 layer
+        lp.qkv = make_linear_plan_w4(normed_, rows, w.qkv_q, w.qkv_s, rows, qkv_dim_, H, qkv_, qkv_dim_, gemm_ws_, tickets_, sms);
+        lp.o = make_linear_plan_w4(attn_out_, rows, w.o_q, w.o_s, rows, H, mc_.hq * d, delta_, H, gemm_ws_, tickets_, sms);
+        lp.gate_up = make_linear_plan_w4(normed_, rows, w.gate_up_q, w.gate_up_s, rows, 2 * I, H, gate_up_, 2 * I, gemm_ws_, tickets_, sms);
+        lp.down = make_linear_plan_w4(act_, rows, w.down_q, w.down_s, rows, H, I, delta_, H, gemm_ws_, tickets_, sms);
+    } else {
+        lp.qkv = make_linear_plan(normed_, rows, w.qkv, rows, qkv_dim_, H, qkv_, qkv_dim_, nullptr, gemm_ws_, tickets_, sms);
+        lp.o = make_linear_plan(attn_out_, rows, w.o, rows, H, mc_.hq * d, delta_, H, nullptr, gemm_ws_, tickets_, sms);
+        lp.gate_up = make_linear_plan(normed_, rows, w.gate_up, rows, 2 * I, H, gate_up_, 2 * I, nullptr, gemm_ws_, tickets_, sms);
+        lp.down = make_linear_plan(act_, rows, w.down, rows, H, I, delta_, H, nullptr, gemm_ws_, tickets_, sms);
+    }
     lp.attn = make_attn_plan(qkv_, qkv_dim_, kv.k, kv.v, budget_, rows, mc_.hq, mc_.hkv, d, attn_splits, attn_out_,
                              mc_.hq * d, attn_ws_o_, attn_ws_ml_);
 }

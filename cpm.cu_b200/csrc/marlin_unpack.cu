@@ -59,18 +59,71 @@ __global__ void marlin_dequant_kernel(const uint32_t* __restrict__ packed, const
     }
 }
 
+__constant__ int16_t c_marlin_invperm[1024];
+
+// One thread per output word (n, j): gathers q[k = 8j .. 8j+7][n] from the Marlin tensor and packs
+// them k0 k2 k4 k6 k1 k3 k5 k7 from bit 0, so that (word >> 4i) & 0x000f000f yields the pair
+// (k = 2i, k = 2i + 1) in the two bf16 lanes.
+__global__ void marlin_retile_kernel(const uint32_t* __restrict__ packed, int K, int N, uint32_t* __restrict__ wq) {
+    const long long idx = static_cast<long long>(blockIdx.x) * blockDim.x + threadIdx.x;
+    const long long words = static_cast<long long>(N) * (K / 8);
+    if (idx >= words) return;
+    const int n = static_cast<int>(idx / (K / 8));
+    const int j = static_cast<int>(idx - static_cast<long long>(n) * (K / 8));
+    uint32_t out = 0;
+#pragma unroll
+    for (int e = 0; e < 8; ++e) {
+        const int k = j * 8 + e;
+        const int kt = k >> 4;
+        const long long old_col = static_cast<long long>(n >> 4) * 256 + (k & 15) * 16 + (n & 15);
+        const long long col = (old_col & ~1023LL) + c_marlin_invperm[old_col & 1023];
+        const uint32_t word = packed[static_cast<long long>(kt) * 2 * N + (col >> 3)];
+        const uint32_t q = (word >> (4 * (col & 7))) & 0xF;
+        const int slot = (e & 1) ? 4 + (e >> 1) : (e >> 1);
+        out |= q << (4 * slot);
+    }
+    wq[idx] = out;
+}
+
+__global__ void marlin_unpermute_scales_kernel(const bf16* __restrict__ sperm, long long count, bf16* __restrict__ out) {
+    const long long flat = static_cast<long long>(blockIdx.x) * blockDim.x + threadIdx.x;
+    if (flat >= count) return;
+    const int pos = static_cast<int>(flat & 63);
+    out[flat] = sperm[(flat & ~63LL) + (pos & 7) * 8 + (pos >> 3)];
+}
+
+void upload_tables() {
+    static bool ready = false;
+    if (ready) return;
+    const std::vector<int16_t> perm = build_perm();
+    std::vector<int16_t> inv(1024);
+    for (int c = 0; c < 1024; ++c) inv[perm[c]] = static_cast<int16_t>(c);
+    CUDA_CHECK(cudaMemcpyToSymbol(c_marlin_perm, perm.data(), perm.size() * sizeof(int16_t)));
+    CUDA_CHECK(cudaMemcpyToSymbol(c_marlin_invperm, inv.data(), inv.size() * sizeof(int16_t)));
+    ready = true;
+}
+
 }  // namespace
+
+void marlin_retile_for_w4(const void* packed, const void* scales, int K, int N, uint32_t* wq, bf16* wscales,
+                          cudaStream_t s) {
+    CPM_REQUIRE(K % 256 == 0 && N % 128 == 0, "W4A16 GEMM: K must be a multiple of 256 and N a multiple of 128");
+    upload_tables();
+    const long long words = static_cast<long long>(N) * (K / 8);
+    marlin_retile_kernel<<<static_cast<unsigned>((words + 255) / 256), 256, 0, s>>>(static_cast<const uint32_t*>(packed), K,
+                                                                                   N, wq);
+    CUDA_CHECK(cudaGetLastError());
+    const long long count = static_cast<long long>(K / 128) * N;
+    marlin_unpermute_scales_kernel<<<static_cast<unsigned>((count + 255) / 256), 256, 0, s>>>(
+        static_cast<const bf16*>(scales), count, wscales);
+    CUDA_CHECK(cudaGetLastError());
+}
 
 void marlin_dequant_to_bf16(const void* packed, const void* scales, int K, int N, int group_size, bf16* dst,
                             cudaStream_t s) {
     CPM_REQUIRE(group_size == 128, "W4A16: only group_size 128 is supported");
     CPM_REQUIRE(K % 128 == 0 && N % 64 == 0, "W4A16: K must be a multiple of 128 and N a multiple of 64");
-    static bool table_ready = false;
-    if (!table_ready) {
-        const std::vector<int16_t> perm = build_perm();
-        CUDA_CHECK(cudaMemcpyToSymbol(c_marlin_perm, perm.data(), perm.size() * sizeof(int16_t)));
-        table_ready = true;
-    }
+    upload_tables();
     const long long words = static_cast<long long>(K / 16) * N * 2;
     marlin_dequant_kernel<<<static_cast<unsigned>((words + 255) / 256), 256, 0, s>>>(
         static_cast<const uint32_t*>(packed), static_cast<const bf16*>(scales), K, N, dst);

@@ -115,3 +115,20 @@ ProfileScope::ProfileScope(int kind_, cudaStream_t s_) : s(s_), kind(kind_), on(
 ProfileScope::~ProfileScope() {
     if (on) cudaEventRecord(e1, s);
 }
+
+CUtensorMap make_tmap_2d_u8(const void* base, uint64_t inner_bytes, uint64_t outer, uint64_t outer_stride_bytes,
+                            uint32_t box_inner_bytes, uint32_t box_outer) {
+    CPM_REQUIRE((reinterpret_cast<uintptr_t>(base) & 15) == 0, "tensor map base must be 16-byte aligned");
+    CPM_REQUIRE(outer_stride_bytes % 16 == 0 && box_inner_bytes % 16 == 0, "tensor map stride/box must be multiples of 16 bytes");
+    CPM_REQUIRE(box_inner_bytes <= 256 && box_outer >= 1 && box_outer <= 256, "tensor map box out of range");
+    CUtensorMap tm;
+    cuuint64_t dims[2] = {inner_bytes, outer};
+    cuuint64_t strides[1] = {outer_stride_bytes};
+    cuuint32_t box[2] = {box_inner_bytes, box_outer};
+    cuuint32_t estr[2] = {1, 1};
+    CUresult r = encode_fn()(&tm, CU_TENSOR_MAP_DATA_TYPE_UINT8, 2, const_cast<void*>(base), dims, strides, box, estr,
+                             CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_NONE, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                             CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    if (r != CUDA_SUCCESS) throw std::runtime_error("cpmcu_b200: cuTensorMapEncodeTiled (u8) failed: " + std::to_string(r));
+    return tm;
+}

@@ -49,8 +49,9 @@ int cpmcu_init_minicpm4_model(float memory_limit, int vocab_size, int num_hidden
 
 /* reference: init_w4a16_gptq_marlin_base_model, src/entry.cu:186-225.  Target whose linears
  * arrive as GPTQ-Marlin tensors (`...qkv_proj|o_proj|gate_up_proj|down_proj.{qweight,scales}`,
- * int32 in Marlin tile order + model-dtype scales, group_size 128).  They are unpacked and
- * dequantised, w = (q - 8) * scale, when loaded; the forward pass then runs the bf16 GEMM.
+ * int32 in Marlin tile order + model-dtype scales, group_size 128).  They are re-tiled when
+ * loaded (k-contiguous nibbles, group-major scales) and streamed as 4-bit by the W4A16 GEMM,
+ * which dequantises w = (q - 8) * scale on the way into the tensor cores.
  * init_w4a16_gptq_marlin_minicpm4_model (:227-275, sparse + W4A16) is not built: always fails. */
 int cpmcu_init_w4a16_gptq_marlin_base_model(float memory_limit, int vocab_size, int num_hidden_layers,
                                             int hidden_size, int intermediate_size, int num_attention_heads,
@@ -153,6 +154,14 @@ void cpmcu_release(void);
  * CTA per SM; smaller values force split-K pieces (tests). */
 int cpmcu_linear_bf16(const void* x, const void* w, const void* bias, void* y, int M, int N, int K,
                       int grid_limit);
+
+/* W4A16 linear: Y[M,N] = X[M,K] dequant(Wq)^T with w = (q - 8) * scale.  reference:
+ * gptq_marlin_gemm, src/qgemm/gptq_marlin/gptq_marlin.cu:2093-2138.  qweight: int32 [K/16, 2N] in
+ * Marlin tile order, scales: bf16 [K/128, N] in Marlin scale order (both as written by
+ * model_convert/convert_w4a16.py); they are re-tiled for the streaming kernel inside the call.
+ * K % 256 == 0, N % 128 == 0. */
+int cpmcu_linear_w4a16(const void* x, const void* qweight, const void* scales, void* y, int M, int N, int K,
+                       int grid_limit);
 
 /* Times `iters` back-to-back launches of the linear kernel on the library's
  * stream with CUDA events, cycling through `copies` separate weight buffers so

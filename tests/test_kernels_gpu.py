@@ -55,6 +55,40 @@ def test_linear_matches_fp32_matmul(M, N, K, grid):
         assert bool((err <= tol).all()), f"max err {err.max().item()} at M={M} N={N} K={K}"
 
 
+W4_CASES = [
+    # M, N, K, grid_limit
+    (1, 128, 256, 0), (7, 384, 512, 0), (10, 4096, 1024, 0), (16, 1024, 4096, 0), (60, 4608, 4096, 0),
+    (64, 512, 16384, 0), (33, 256, 256, 0), (130, 512, 256, 0), (300, 1024, 512, 0),
+    (60, 1024, 2048, 3), (60, 1024, 2048, 7), (10, 4096, 4096, 5), (257, 640, 1024, 11),
+]
+
+
+@pytest.mark.parametrize("M,N,K,grid", W4_CASES)
+def test_linear_w4a16_matches_dequantised_matmul(M, N, K, grid):
+    """4-bit streaming GEMM against x @ dequant(q)^T, weights in the converter's Marlin layout."""
+    from oracle import marlin
+    c = C()
+    rng = np.random.default_rng(M * 7919 + N * 31 + K)
+    w_kn = (rng.standard_normal((K, N)) * 0.05).astype(np.float32)
+    q, s = marlin.quantize_sym_int4(w_kn)
+    packed, sperm = marlin.marlin_pack(q, s)
+    deq = torch.from_numpy(marlin.dequantize(q, s))                       # [K, N] bf16-valued
+    g = torch.Generator().manual_seed(M + N + K)
+    x = dev(torch.randn(M, K, generator=g).to(torch.bfloat16))
+    qw = dev(torch.from_numpy(packed.copy()))
+    sc = dev(torch.from_numpy(sperm.copy()).to(torch.bfloat16))
+    y = torch.full((M, N), float("nan"), dtype=torch.bfloat16, device="cuda")
+    c.call("cpmcu_linear_w4a16", ptr(x), ptr(qw), ptr(sc), ptr(y), M, N, K, grid)
+    ref = x.float() @ dev(deq)
+    err = (y.float() - ref).abs()
+    tol = 1e-2 * ref.abs() + 2e-2 * ref.abs().mean()   # bf16 store + accumulation order; weights are exact
+    assert torch.isfinite(y.float()).all()
+    assert bool((err <= tol).all()), f"max err {err.max().item()} at M={M} N={N} K={K}"
+    y2 = torch.empty_like(y)
+    c.call("cpmcu_linear_w4a16", ptr(x), ptr(qw), ptr(sc), ptr(y2), M, N, K, grid)
+    assert torch.equal(y, y2)                          # ticketed split-K sums in a fixed order
+
+
 def test_linear_is_deterministic():
     c = C()
     g = torch.Generator().manual_seed(5)
