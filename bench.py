@@ -50,7 +50,7 @@ def zipf_prompt(n, vocab, seed, s=1.1):
 
 
 def algorithmic_bytes():
-    """Weight bytes one speculative step has to stream (bf16), per SURVEY 8(d) arithmetic:
+    """Weight bytes one speculative step has to stream (bf16):
     every target linear once (M = 60), the draft fc + layer + LM head six times."""
     H, I, V = CFG["hidden"], CFG["inter"], CFG["vocab"]
     qkv = (CFG["hq"] + 2 * CFG["hkv"]) * CFG["head_dim"]

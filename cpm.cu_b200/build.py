@@ -19,6 +19,8 @@ SOURCES = ["runtime.cu", "gemm_umma.cu", "gemm_w4_umma.cu", "elementwise.cu", "t
            "marlin_unpack.cu", "engine.cu", "capi.cu"]
 NVCC_FLAGS = ["-gencode", "arch=compute_100a,code=sm_100a", "-lineinfo", "-O3", "-std=c++17",
               "-Xcompiler", "-fPIC", "--threads", "2"]
+# extra defines for instrumented builds, e.g. CPMCU_BUILD_DEFINES="-DCPMCU_W4_PROFILE=1"
+NVCC_FLAGS += os.environ.get("CPMCU_BUILD_DEFINES", "").split()
 
 
 def _nvcc():

@@ -299,15 +299,15 @@ int cpmcu_linear_w4a16(const void* x, const void* qweight, const void* scales, v
         Runtime& rt = runtime();
         cudaStream_t s = rt.stream;
         const int limit = (grid_limit > 0) ? grid_limit : rt.num_sms;
-        const int mt = linear_pick_mt(M);
-        DeviceBuf wq(static_cast<size_t>(N) * K / 2), ws(static_cast<size_t>(K / 128) * N * 2);
-        marlin_retile_for_w4(qweight, scales, K, N, static_cast<uint32_t*>(wq.p), static_cast<bf16*>(ws.p), s);
+        const int mt = std::min(linear_pick_mt(M), 128);  // the 4-bit kernel's largest token tile
+        CPM_REQUIRE(K % 256 == 0 && N % 128 == 0, "linear_w4a16: K must be a multiple of 256 and N of 128");
+        DeviceBuf wq(linear_w4_weight_bytes(N, K));
+        marlin_retile_for_w4(qweight, scales, K, N, wq.p, s);
         DeviceBuf work(linear_w4_workspace_bytes(mt, limit));
         const size_t tiles = static_cast<size_t>(N / 128) * ceil_div(M, mt);
         DeviceBuf tickets(tiles * sizeof(int));
         CUDA_CHECK(cudaMemsetAsync(tickets.p, 0, tiles * sizeof(int), s));
-        LinearPlan p = make_linear_plan_w4(static_cast<const bf16*>(x), M, static_cast<const uint32_t*>(wq.p),
-                                           static_cast<const bf16*>(ws.p), M, N, K, static_cast<bf16*>(y), N,
+        LinearPlan p = make_linear_plan_w4(static_cast<const bf16*>(x), M, wq.p, M, N, K, static_cast<bf16*>(y), N,
                                            static_cast<float*>(work.p), static_cast<int*>(tickets.p), limit);
         launch_linear(p, s);
         sync_and_check("linear_w4a16");
@@ -331,14 +331,12 @@ int cpmcu_bench_linear(int M, int N, int K, int copies, int iters, int grid_limi
         CUDA_CHECK(cudaMemsetAsync(w.p, 0x3c, wbytes * copies, s));
         CUDA_CHECK(cudaMemsetAsync(x.p, 0x3c, static_cast<size_t>(M) * K * 2, s));
         const bool w4 = getenv("CPMCU_BENCH_W4") != nullptr;
-        DeviceBuf w4s(static_cast<size_t>(K / 128 + 1) * N * 2);
-        CUDA_CHECK(cudaMemsetAsync(w4s.p, 0x3c, static_cast<size_t>(K / 128 + 1) * N * 2, s));
         std::vector<LinearPlan> plans;
         for (int c = 0; c < copies; ++c) {
-            if (w4) {  // the same buffer read as packed nibbles: a quarter of the bytes per launch
+            if (w4) {  // the same buffer read as 4-bit blocks: about a quarter of the bytes per launch
                 plans.push_back(make_linear_plan_w4(static_cast<const bf16*>(x.p), M,
-                                                    reinterpret_cast<const uint32_t*>(static_cast<uint8_t*>(w.p) + wbytes * c),
-                                                    static_cast<const bf16*>(w4s.p), M, N, K, static_cast<bf16*>(y.p), N,
+                                                    static_cast<uint8_t*>(w.p) + linear_w4_weight_bytes(N, K) * c,
+                                                    M, N, K, static_cast<bf16*>(y.p), N,
                                                     static_cast<float*>(ws.p), static_cast<int*>(tickets.p), limit));
                 continue;
             }
@@ -362,6 +360,7 @@ int cpmcu_bench_linear(int M, int N, int K, int copies, int iters, int grid_limi
         cudaEventDestroy(e0);
         cudaEventDestroy(e1);
         *avg_us = ms * 1000.f / iters;
+        if (w4) linear_w4_print_prof();
         sync_and_check("bench_linear");
         return 0;
     });

@@ -125,9 +125,8 @@ struct LinearPlan {
     float* workspace = nullptr;  // split-K partials: grid * 2 * mt * 128 floats
     int* tickets = nullptr;      // one counter per output tile, zero between launches
     int debug = 0;               // bench-only switches, see gemm_umma.cu
-    // W4A16: when wq is set the weights are 4-bit (see gemm_w4_umma.cu); tm_w then maps the packed bytes
-    const uint32_t* wq = nullptr;   // [N][K/8] packed nibbles, k-contiguous
-    const bf16* wscales = nullptr;  // [K/128][N]
+    // W4A16: when wq is set the weights are 4-bit blocks in the streaming layout (see gemm_w4_umma.cu)
+    const void* wq = nullptr;
     // Optional fused epilogue: y = silu(gate) * up where gate/up rows alternate
     // in 64-row halves of each 128-row weight tile (see make_linear_plan).
     int epilogue = 0;
@@ -142,14 +141,18 @@ int linear_pick_mt(int M);
 LinearPlan make_linear_plan(const bf16* x, int x_rows, const bf16* w, int M, int N, int K, bf16* y, int ldy,
                             const bf16* bias, float* workspace, int* tickets, int grid_limit);
 void launch_linear(const LinearPlan& plan, cudaStream_t stream);
-// Same contract with 4-bit weights: wq [N][K/8] uint32 (nibble order k0 k2 k4 k6 k1 k3 k5 k7 from bit 0),
-// scales [K/128][N] bf16, w = (q - 8) * scale.  K % 256 == 0 and N % 128 == 0.
-LinearPlan make_linear_plan_w4(const bf16* x, int x_rows, const uint32_t* wq, const bf16* wscales, int M, int N, int K,
-                               bf16* y, int ldy, float* workspace, int* tickets, int grid_limit);
+// Same contract with 4-bit weights, w = (q - 8) * scale, K % 256 == 0 and N % 128 == 0.  `wq` holds one
+// contiguous 16896-byte block per (128-feature tile, 256-k unit), tile-major: [4 k-blocks][2 halves]
+// [128 rows][16 B] of nibbles (a 32-bit word holds k0 k2 k4 k6 k1 k3 k5 k7 from bit 0) then
+// [2 groups][128 rows] bf16 scales.
+LinearPlan make_linear_plan_w4(const bf16* x, int x_rows, const void* wq, int M, int N, int K, bf16* y, int ldy,
+                               float* workspace, int* tickets, int grid_limit);
 void launch_linear_w4(const LinearPlan& plan, cudaStream_t stream);
 size_t linear_w4_workspace_bytes(int mt, int grid);
+void linear_w4_print_prof();  // bench only (CPMCU_W4_PROF)
+size_t linear_w4_weight_bytes(int N, int K);
 // Marlin tensors (packed int32 [K/16, 2N], permuted scales [K/128, N]) -> the layout above.
-void marlin_retile_for_w4(const void* packed, const void* scales, int K, int N, uint32_t* wq, bf16* wscales, cudaStream_t s);
+void marlin_retile_for_w4(const void* packed, const void* scales, int K, int N, void* wq, cudaStream_t s);
 
 // W4A16 GPTQ-Marlin tensor (packed int32 [K/16, 2N] + permuted bf16 scales [K/128, N]) -> bf16 [N, K].
 void marlin_dequant_to_bf16(const void* packed, const void* scales, int K, int N, int group_size, bf16* dst,

@@ -124,14 +124,10 @@ void Engine::lay_out(Pool& p) {
     inv_freq_ = take<float>(p, d / 2);
     for (auto& w : layers_) {
         if (mc_.w4a16) {
-            auto take_q = [&](uint32_t*& q, bf16*& s, size_t n, size_t k) {
-                q = take<uint32_t>(p, n * k / 8);
-                s = take<bf16>(p, (k / 128) * n);
-            };
-            take_q(w.qkv_q, w.qkv_s, qkv_dim_, H);
-            take_q(w.o_q, w.o_s, H, static_cast<size_t>(mc_.hq) * d);
-            take_q(w.gate_up_q, w.gate_up_s, static_cast<size_t>(2) * I, H);
-            take_q(w.down_q, w.down_s, H, I);
+            w.qkv_q = take<uint8_t>(p, linear_w4_weight_bytes(qkv_dim_, H));
+            w.o_q = take<uint8_t>(p, linear_w4_weight_bytes(H, mc_.hq * d));
+            w.gate_up_q = take<uint8_t>(p, linear_w4_weight_bytes(2 * I, H));
+            w.down_q = take<uint8_t>(p, linear_w4_weight_bytes(H, I));
         } else {
             w.qkv = take<bf16>(p, static_cast<size_t>(qkv_dim_) * H);
             w.o = take<bf16>(p, static_cast<size_t>(H) * mc_.hq * d);
@@ -293,10 +289,10 @@ void Engine::load(const std::string& name, const void* src) {
         // fused W4A16 tensors of the reference converter: qkv_proj, o_proj, gate_up_proj, down_proj
         const bool is_scales = sub.find("scales") != std::string::npos;
         if (!is_scales && sub.find("qweight") == std::string::npos) return false;
-        if (sub.find("qkv_proj") != std::string::npos) load_quantized(key + ".qkv", is_scales, src, H, qkv_dim_, w.qkv_q, w.qkv_s);
-        else if (sub.find("o_proj") != std::string::npos) load_quantized(key + ".o", is_scales, src, mc_.hq * d, H, w.o_q, w.o_s);
-        else if (sub.find("gate_up_proj") != std::string::npos) load_quantized(key + ".gu", is_scales, src, H, 2 * I, w.gate_up_q, w.gate_up_s);
-        else if (sub.find("down_proj") != std::string::npos) load_quantized(key + ".down", is_scales, src, I, H, w.down_q, w.down_s);
+        if (sub.find("qkv_proj") != std::string::npos) load_quantized(key + ".qkv", is_scales, src, H, qkv_dim_, w.qkv_q);
+        else if (sub.find("o_proj") != std::string::npos) load_quantized(key + ".o", is_scales, src, mc_.hq * d, H, w.o_q);
+        else if (sub.find("gate_up_proj") != std::string::npos) load_quantized(key + ".gu", is_scales, src, H, 2 * I, w.gate_up_q);
+        else if (sub.find("down_proj") != std::string::npos) load_quantized(key + ".down", is_scales, src, I, H, w.down_q);
         else throw std::invalid_argument("Unsupported quantized tensor " + sub);
         return true;
     };
@@ -375,8 +371,7 @@ void Engine::load(const std::string& name, const void* src) {
     }
 }
 
-void Engine::load_quantized(const std::string& key, bool is_scales, const void* src, int K, int N, uint32_t* wq,
-                            bf16* ws) {
+void Engine::load_quantized(const std::string& key, bool is_scales, const void* src, int K, int N, uint8_t* wq) {
     Runtime& rt = runtime();
     PendingQuant& p = pending_quant_[key];
     const size_t bytes = is_scales ? static_cast<size_t>(K / mc_.group_size) * N * 2 : static_cast<size_t>(K) * N / 2;
@@ -387,7 +382,7 @@ void Engine::load_quantized(const std::string& key, bool is_scales, const void* 
     CUDA_CHECK(cudaStreamSynchronize(rt.stream));
     if (p.qweight != nullptr && p.scales != nullptr) {
         // Marlin tile order -> row-major k-contiguous nibbles + group-major scales for the streaming kernel
-        marlin_retile_for_w4(p.qweight, p.scales, K, N, wq, ws, rt.stream);
+        marlin_retile_for_w4(p.qweight, p.scales, K, N, wq, rt.stream);
         CUDA_CHECK(cudaStreamSynchronize(rt.stream));
         cudaFree(p.qweight);
         cudaFree(p.scales);
@@ -400,10 +395,10 @@ void Engine::build_layer_plans(LayerPlans& lp, const LayerWeights& w, const KVLa
     const int H = mc_.hidden, I = mc_.inter, d = mc_.head_dim;
     const int sms = runtime().num_sms;
     if (w.qkv_q != nullptr) {  // W4A16 layer
-        lp.qkv = make_linear_plan_w4(normed_, rows, w.qkv_q, w.qkv_s, rows, qkv_dim_, H, qkv_, qkv_dim_, gemm_ws_, tickets_, sms);
-        lp.o = make_linear_plan_w4(attn_out_, rows, w.o_q, w.o_s, rows, H, mc_.hq * d, delta_, H, gemm_ws_, tickets_, sms);
-        lp.gate_up = make_linear_plan_w4(normed_, rows, w.gate_up_q, w.gate_up_s, rows, 2 * I, H, gate_up_, 2 * I, gemm_ws_, tickets_, sms);
-        lp.down = make_linear_plan_w4(act_, rows, w.down_q, w.down_s, rows, H, I, delta_, H, gemm_ws_, tickets_, sms);
+        lp.qkv = make_linear_plan_w4(normed_, rows, w.qkv_q, rows, qkv_dim_, H, qkv_, qkv_dim_, gemm_ws_, tickets_, sms);
+        lp.o = make_linear_plan_w4(attn_out_, rows, w.o_q, rows, H, mc_.hq * d, delta_, H, gemm_ws_, tickets_, sms);
+        lp.gate_up = make_linear_plan_w4(normed_, rows, w.gate_up_q, rows, 2 * I, H, gate_up_, 2 * I, gemm_ws_, tickets_, sms);
+        lp.down = make_linear_plan_w4(act_, rows, w.down_q, rows, H, I, delta_, H, gemm_ws_, tickets_, sms);
     } else {
         lp.qkv = make_linear_plan(normed_, rows, w.qkv, rows, qkv_dim_, H, qkv_, qkv_dim_, nullptr, gemm_ws_, tickets_, sms);
         lp.o = make_linear_plan(attn_out_, rows, w.o, rows, H, mc_.hq * d, delta_, H, nullptr, gemm_ws_, tickets_, sms);

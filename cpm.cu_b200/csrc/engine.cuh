@@ -40,9 +40,8 @@ struct LayerWeights {
     bf16* down = nullptr;     // [hidden, inter]
     bf16* ln_attn = nullptr;  // [hidden]
     bf16* ln_ffn = nullptr;   // [hidden]
-    // W4A16 layers: packed nibbles [N][K/8] and scales [K/128][N] per linear instead of the bf16 matrices
-    uint32_t *qkv_q = nullptr, *o_q = nullptr, *gate_up_q = nullptr, *down_q = nullptr;
-    bf16 *qkv_s = nullptr, *o_s = nullptr, *gate_up_s = nullptr, *down_s = nullptr;
+    // W4A16 layers: 4-bit blocks in the streaming layout of the W4A16 GEMM instead of the bf16 matrices
+    uint8_t *qkv_q = nullptr, *o_q = nullptr, *gate_up_q = nullptr, *down_q = nullptr;
 };
 struct KVLayer {
     bf16* k = nullptr;  // [budget, hkv * d]
@@ -168,7 +167,7 @@ private:
         void* scales = nullptr;
     };
     std::map<std::string, PendingQuant> pending_quant_;
-    void load_quantized(const std::string& key, bool is_scales, const void* src, int K, int N, uint32_t* wq, bf16* ws);
+    void load_quantized(const std::string& key, bool is_scales, const void* src, int K, int N, uint8_t* wq);
 
     // activations
     bf16 *x_ = nullptr, *normed_ = nullptr, *qkv_ = nullptr, *attn_out_ = nullptr, *delta_ = nullptr,

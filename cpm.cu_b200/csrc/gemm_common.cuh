@@ -42,11 +42,13 @@ __device__ __forceinline__ int unit_owner(long long u, long long U, int G) {
 
 // Epilogue of the four warps whose (warp & 3) selects the TMEM lane quarter.  `it` walks the same
 // segments as the producer and MMA roles; a.kblocks is the number of work units per tile.  CH = tokens
-// summed per fix-up pass (4 * CH loads in flight per thread).
+// summed per fix-up pass (4 * CH loads in flight per thread).  chain2_off != 0: the MMA role accumulated
+// alternate instructions into a second accumulator that many columns further on; the two are added here.
 template <int MT, int CH>
 __device__ __forceinline__ void run_epilogue(const LinearArgs& a, SegIter it, uint32_t tmem_base, uint64_t* acc_full,
                                              uint64_t* acc_empty, volatile int* abort_flag, volatile int* s_last, int warp,
-                                             int lane, int epi_tid, int g, int G) {
+                                             int lane, int epi_tid, int g, int G, uint32_t chain2_off = 0,
+                                             int acc_stages = 2) {
     const int q = warp & 3;                 // TMEM lane quarter this warp may read
     const int row = q * 32 + lane;          // output feature within the tile
     int acc = 0;
@@ -65,9 +67,8 @@ __device__ __forceinline__ void run_epilogue(const LinearArgs& a, SegIter it, ui
         float* my_ws = a.workspace + (static_cast<size_t>(g) * 2 + (kb0 == 0 ? 1 : 0)) * (MT * BLOCK_N);
         const float bias_v = (a.bias != nullptr && n < a.N) ? __bfloat162float(a.bias[n]) : 0.f;
 
-        if (!ptx::mbar_wait(&acc_full[acc], acc_phase, abort_flag)) break;
+        if (!ptx::mbar_wait_warp(&acc_full[acc], acc_phase, abort_flag)) break;  // also converges the warp
         ptx::tc_fence_after();
-        __syncwarp();  // TMEM loads below are warp-collective
         const uint32_t t_addr = tmem_base + (static_cast<uint32_t>(q * 32) << 16) + acc * MT;
         // partial slot layout: [MT tokens][128 features] fp32: a warp touches one 128-byte line per token
 #pragma unroll 1
@@ -75,6 +76,13 @@ __device__ __forceinline__ void run_epilogue(const LinearArgs& a, SegIter it, ui
             if (c0 >= m_cnt || (a.debug & 2)) break;  // uniform across the CTA
             uint32_t r[16];
             ptx::tmem_ld16(t_addr + c0, r);
+            if (chain2_off != 0) {
+                uint32_t r2[16];
+                ptx::tmem_ld16(t_addr + chain2_off + c0, r2);
+                ptx::tmem_wait_ld();
+#pragma unroll
+                for (int c = 0; c < 16; ++c) r[c] = __float_as_uint(__uint_as_float(r[c]) + __uint_as_float(r2[c]));
+            }
             ptx::tmem_wait_ld();
             if (complete) {
                 if (n < a.N) {
@@ -95,8 +103,7 @@ __device__ __forceinline__ void run_epilogue(const LinearArgs& a, SegIter it, ui
         }
         ptx::tc_fence_before();
         ptx::mbar_arrive(&acc_empty[acc]);
-        acc ^= 1;
-        if (acc == 0) acc_phase ^= 1;
+        if (++acc == acc_stages) { acc = 0; acc_phase ^= 1; }
 
         if (!complete && !(a.debug & (2 | 8))) {
             const long long tile_u0 = static_cast<long long>(tile) * a.kblocks;

@@ -61,10 +61,15 @@ __global__ void marlin_dequant_kernel(const uint32_t* __restrict__ packed, const
 
 __constant__ int16_t c_marlin_invperm[1024];
 
+// Streaming layout of the W4A16 GEMM: one contiguous 16896-byte block per (128-feature tile, 256-k unit),
+// [4 k-blocks of 64][2 halves of 32 k][128 rows][16 B of nibbles] followed by [2 scale groups][128 rows]
+// bf16, so that one untiled bulk copy fills a pipeline stage and a warp reads 512 contiguous bytes.
+constexpr int W4_BLOCK_BYTES = 128 * 256 / 2 + 2 * 128 * 2;
+
 // One thread per output word (n, j): gathers q[k = 8j .. 8j+7][n] from the Marlin tensor and packs
 // them k0 k2 k4 k6 k1 k3 k5 k7 from bit 0, so that (word >> 4i) & 0x000f000f yields the pair
 // (k = 2i, k = 2i + 1) in the two bf16 lanes.
-__global__ void marlin_retile_kernel(const uint32_t* __restrict__ packed, int K, int N, uint32_t* __restrict__ wq) {
+__global__ void marlin_retile_kernel(const uint32_t* __restrict__ packed, int K, int N, uint8_t* __restrict__ blocks) {
     const long long idx = static_cast<long long>(blockIdx.x) * blockDim.x + threadIdx.x;
     const long long words = static_cast<long long>(N) * (K / 8);
     if (idx >= words) return;
@@ -82,14 +87,19 @@ __global__ void marlin_retile_kernel(const uint32_t* __restrict__ packed, int K,
         const int slot = (e & 1) ? 4 + (e >> 1) : (e >> 1);
         out |= q << (4 * slot);
     }
-    wq[idx] = out;
+    const int unit = j >> 5, jw = j & 31;
+    const long long block = static_cast<long long>(n >> 7) * (K / 256) + unit;
+    *reinterpret_cast<uint32_t*>(blocks + block * W4_BLOCK_BYTES + (jw >> 3) * 4096 + ((jw >> 2) & 1) * 2048 + (n & 127) * 16 + (jw & 3) * 4) = out;
 }
 
-__global__ void marlin_unpermute_scales_kernel(const bf16* __restrict__ sperm, long long count, bf16* __restrict__ out) {
+__global__ void marlin_unpermute_scales_kernel(const bf16* __restrict__ sperm, int K, int N, uint8_t* __restrict__ blocks) {
     const long long flat = static_cast<long long>(blockIdx.x) * blockDim.x + threadIdx.x;
-    if (flat >= count) return;
+    if (flat >= static_cast<long long>(K / 128) * N) return;
     const int pos = static_cast<int>(flat & 63);
-    out[flat] = sperm[(flat & ~63LL) + (pos & 7) * 8 + (pos >> 3)];
+    const bf16 v = sperm[(flat & ~63LL) + (pos & 7) * 8 + (pos >> 3)];
+    const int grp = static_cast<int>(flat / N), n = static_cast<int>(flat - static_cast<long long>(grp) * N);
+    const long long block = static_cast<long long>(n >> 7) * (K / 256) + (grp >> 1);
+    *reinterpret_cast<bf16*>(blocks + block * W4_BLOCK_BYTES + 16384 + (grp & 1) * 256 + (n & 127) * 2) = v;
 }
 
 void upload_tables() {
@@ -105,17 +115,20 @@ void upload_tables() {
 
 }  // namespace
 
-void marlin_retile_for_w4(const void* packed, const void* scales, int K, int N, uint32_t* wq, bf16* wscales,
-                          cudaStream_t s) {
+size_t linear_w4_weight_bytes(int N, int K) {
+    return static_cast<size_t>(N / 128) * (K / 256) * W4_BLOCK_BYTES;
+}
+
+void marlin_retile_for_w4(const void* packed, const void* scales, int K, int N, void* blocks, cudaStream_t s) {
     CPM_REQUIRE(K % 256 == 0 && N % 128 == 0, "W4A16 GEMM: K must be a multiple of 256 and N a multiple of 128");
     upload_tables();
     const long long words = static_cast<long long>(N) * (K / 8);
     marlin_retile_kernel<<<static_cast<unsigned>((words + 255) / 256), 256, 0, s>>>(static_cast<const uint32_t*>(packed), K,
-                                                                                   N, wq);
+                                                                                   N, static_cast<uint8_t*>(blocks));
     CUDA_CHECK(cudaGetLastError());
     const long long count = static_cast<long long>(K / 128) * N;
     marlin_unpermute_scales_kernel<<<static_cast<unsigned>((count + 255) / 256), 256, 0, s>>>(
-        static_cast<const bf16*>(scales), count, wscales);
+        static_cast<const bf16*>(scales), K, N, static_cast<uint8_t*>(blocks));
     CUDA_CHECK(cudaGetLastError());
 }
 

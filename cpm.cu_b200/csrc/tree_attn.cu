@@ -102,7 +102,7 @@ tree_attn_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant
             ptx::mbar_init(&v_full[i], 1);
             ptx::mbar_init(&s_bar[i], 1);
             ptx::mbar_init(&o_bar[i], 1);
-            ptx::mbar_init(&p_ready[i], SOFTMAX_THREADS);
+            ptx::mbar_init(&p_ready[i], SOFTMAX_THREADS / 32);  // one arrival per softmax warp
         }
         *abort_flag = 0;
         ptx::mbar_fence_init();
@@ -241,9 +241,9 @@ tree_attn_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant
             const int st = i & 1;
             const uint32_t ph = (i >> 1) & 1;
             const int key0 = (kt_begin + i) * KEYS + ch * 64;  // first key of this thread's 64 columns
-            if (!ptx::mbar_wait(&s_bar[st], ph, abort_flag)) { ok = false; break; }
+            // one polling lane per warp (the shuffle also converges it for the collective TMEM loads)
+            if (!ptx::mbar_wait_warp(&s_bar[st], ph, abort_flag)) { ok = false; break; }
             ptx::tc_fence_after();
-            __syncwarp();  // TMEM loads below are warp-collective
 
             // ---- scores of this thread: 64 columns, kept in registers for both passes
             uint32_t sc[64];
@@ -279,9 +279,8 @@ tree_attn_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant
             const float alpha = (m_run == -INFINITY) ? 1.f : fast_exp2((m_run - m_use) * a.scale_log2);
             const bool rescale = (i > 0) && __any_sync(0xffffffffu, alpha != 1.f);
             if (rescale) {  // O must hold every product issued so far: wait for PV(i-1)
-                if (!ptx::mbar_wait(&o_bar[(i - 1) & 1], ((i - 1) >> 1) & 1, abort_flag)) { ok = false; break; }
+                if (!ptx::mbar_wait_warp(&o_bar[(i - 1) & 1], ((i - 1) >> 1) & 1, abort_flag)) { ok = false; break; }
                 ptx::tc_fence_after();
-                __syncwarp();
 #pragma unroll 1
                 for (int c0 = 0; c0 < 64; c0 += 32) {
                     uint32_t r[32];
@@ -295,7 +294,7 @@ tree_attn_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant
             }
             m_run = m_new;
             if (i >= 2) {  // P stage st was last read by PV(i-2)
-                if (!ptx::mbar_wait(&o_bar[st], ((i - 2) >> 1) & 1, abort_flag)) { ok = false; break; }
+                if (!ptx::mbar_wait_warp(&o_bar[st], ((i - 2) >> 1) & 1, abort_flag)) { ok = false; break; }
             }
 
             // ---- P = 2^((s - m) * scale) in bf16 into the swizzled A-operand tile; row sums in fp32
@@ -322,10 +321,11 @@ tree_attn_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant
             l_run = l_run * alpha + ((ls[0] + ls[1]) + (ls[2] + ls[3]));
             ptx::fence_proxy_async_smem();  // P stores -> visible to the tensor core's async proxy
             ptx::tc_fence_before();         // TMEM reads / rescale ordered before the control warp's next MMA
-            ptx::mbar_arrive(&p_ready[st]);
+            __syncwarp();
+            if ((threadIdx.x & 31) == 0) ptx::mbar_arrive(&p_ready[st]);
         }
         if (ok && n_it > 0) {
-            if (!ptx::mbar_wait(&o_bar[(n_it - 1) & 1], ((n_it - 1) >> 1) & 1, abort_flag)) ok = false;
+            if (!ptx::mbar_wait_warp(&o_bar[(n_it - 1) & 1], ((n_it - 1) >> 1) & 1, abort_flag)) ok = false;
             ptx::tc_fence_after();
         }
         ok = __all_sync(0xffffffffu, ok);  // keep each warp together for the collective TMEM reads

@@ -1,0 +1,72 @@
+"""Per-kernel timing of the two heavy kernels of the speculative step, through the C ABI.
+
+    python cpm.cu_b200/kernel_bench.py linear [M,N,K] [iters]      bf16 weights
+    python cpm.cu_b200/kernel_bench.py linear_w4 [M,N,K] [iters]   4-bit weights (W4A16)
+    python cpm.cu_b200/kernel_bench.py attention [tq,hq,hkv,kv,splits,mask] [iters]
+
+Each case runs `iters` back-to-back launches inside the library, timed with CUDA events on the
+library's stream, rotating over enough separate weight (or KV-cache) copies that no launch finds
+its operands in L2.  Prints one line per case: average microseconds per launch and the weight
+(KV) bytes streamed per second.  Without a shape the shapes of the 8B verify (M=60) and draft
+(M=10) passes are run.  The same command under `ncu -k regex:linear|tree_attn` is how the
+summaries under profiles/ are made.
+"""
+import ctypes
+import os
+import sys
+
+sys.path.insert(0, os.path.dirname(os.path.abspath(__file__)))
+import cpmcu.C as C  # noqa: E402
+
+# qkv, o, gate_up, down, LM head of the 8B shape (hidden 4096, FFN 16384, 32 q / 2 kv heads, vocab 73448)
+LINEAR_SHAPES = [(60, 4608, 4096), (60, 4096, 4096), (60, 32768, 4096), (60, 4096, 16384), (60, 73448, 4096),
+                 (10, 4608, 4096), (10, 4096, 4096), (10, 32768, 4096), (10, 4096, 16384), (10, 73448, 4096),
+                 (10, 4096, 8192)]
+W4_SHAPES = [(60, 4608, 4096), (60, 4096, 4096), (60, 32768, 4096), (60, 4096, 16384)]
+ATTN_CASES = [(60, 32, 2, 4156, 9, 1), (60, 32, 2, 4156, 4, 1), (10, 32, 2, 4116, 32, 1), (7, 32, 2, 4096, 32, 0)]
+
+
+def _us(fn, *args):
+    out = ctypes.c_float()
+    C.call(fn, *args, ctypes.cast(ctypes.pointer(out), ctypes.c_void_p))
+    return out.value
+
+
+def bench_linear(shapes, iters, w4):
+    if w4:
+        os.environ["CPMCU_BENCH_W4"] = "1"
+    for M, N, K in shapes:
+        store = N * K * 2                         # bytes of one bf16 copy; the 4-bit run reads a quarter of it
+        copies = max(1, min(40, (600 << 20) // store + 1))
+        if w4:
+            copies = min(64, 4 * copies)          # same footprint to rotate over
+        us = _us("cpmcu_bench_linear", M, N, K, copies, iters, 0)
+        streamed = store // 4 + (K // 128) * N * 2 if w4 else store
+        print(f"{'linear_w4' if w4 else 'linear'} M={M} N={N} K={K} copies={copies}: {us:.1f} us  "
+              f"{streamed / us / 1e3:.0f} GB/s", flush=True)
+
+
+def bench_attention(cases, iters):
+    for tq, hq, hkv, kv, splits, mask in cases:
+        us = _us("cpmcu_bench_attention", tq, hq, hkv, kv, splits, mask, iters)
+        kv_bytes = 2 * kv * hkv * 128 * 2
+        print(f"attention tq={tq} hq={hq} hkv={hkv} kv={kv} splits={splits} mask={mask}: {us:.1f} us  "
+              f"{kv_bytes / us / 1e3:.0f} GB/s", flush=True)
+
+
+def main(argv):
+    what = argv[1] if len(argv) > 1 else "linear"
+    shape = tuple(int(v) for v in argv[2].split(",")) if len(argv) > 2 else None
+    iters = int(argv[3]) if len(argv) > 3 else 50
+    if what == "linear":
+        bench_linear([shape] if shape else LINEAR_SHAPES, iters, False)
+    elif what == "linear_w4":
+        bench_linear([shape] if shape else W4_SHAPES, iters, True)
+    elif what == "attention":
+        bench_attention([shape] if shape else ATTN_CASES, iters)
+    else:
+        raise SystemExit(__doc__)
+
+
+if __name__ == "__main__":
+    main(sys.argv)

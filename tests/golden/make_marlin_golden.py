@@ -21,7 +21,9 @@ def load_reference_functions(ref_root):
 
 
 def main():
-    ref_root = sys.argv[1] if len(sys.argv) > 1 else "/root/reference"
+    if len(sys.argv) < 2:
+        raise SystemExit("usage: make_marlin_golden.py <path of the reference checkout>")
+    ref_root = sys.argv[1]
     ns = load_reference_functions(ref_root)
     rng = np.random.default_rng(123)
     cases = []

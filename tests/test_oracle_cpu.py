@@ -1,5 +1,5 @@
 """CPU tests of the oracle itself: regression fixtures, ordering rules and the
-invariants of the speculative step (SURVEY appendix A)."""
+invariants of the speculative step."""
 import json
 import os
 
