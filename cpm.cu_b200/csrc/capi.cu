@@ -282,8 +282,8 @@ int cpmcu_linear_bf16(const void* x, const void* w, const void* bias, void* y, i
         const int mt = linear_pick_mt(M);
         DeviceBuf ws(linear_workspace_bytes(mt, limit));
         const size_t tiles = static_cast<size_t>(ceil_div(N, 128)) * ceil_div(M, mt);
-        DeviceBuf tickets(tiles * sizeof(int));
-        CUDA_CHECK(cudaMemsetAsync(tickets.p, 0, tiles * sizeof(int), rt.stream));
+        DeviceBuf tickets(2 * tiles * sizeof(int));
+        CUDA_CHECK(cudaMemsetAsync(tickets.p, 0, 2 * tiles * sizeof(int), rt.stream));
         LinearPlan p = make_linear_plan(static_cast<const bf16*>(x), M, static_cast<const bf16*>(w), M, N, K,
                                         static_cast<bf16*>(y), N, static_cast<const bf16*>(bias),
                                         static_cast<float*>(ws.p), static_cast<int*>(tickets.p), limit);
@@ -305,8 +305,8 @@ int cpmcu_linear_w4a16(const void* x, const void* qweight, const void* scales, v
         marlin_retile_for_w4(qweight, scales, K, N, wq.p, s);
         DeviceBuf work(linear_w4_workspace_bytes(mt, limit));
         const size_t tiles = static_cast<size_t>(N / 128) * ceil_div(M, mt);
-        DeviceBuf tickets(tiles * sizeof(int));
-        CUDA_CHECK(cudaMemsetAsync(tickets.p, 0, tiles * sizeof(int), s));
+        DeviceBuf tickets(2 * tiles * sizeof(int));
+        CUDA_CHECK(cudaMemsetAsync(tickets.p, 0, 2 * tiles * sizeof(int), s));
         LinearPlan p = make_linear_plan_w4(static_cast<const bf16*>(x), M, wq.p, M, N, K, static_cast<bf16*>(y), N,
                                            static_cast<float*>(work.p), static_cast<int*>(tickets.p), limit);
         launch_linear(p, s);
@@ -326,8 +326,8 @@ int cpmcu_bench_linear(int M, int N, int K, int copies, int iters, int grid_limi
         DeviceBuf w(wbytes * copies), x(static_cast<size_t>(M) * K * 2), y(static_cast<size_t>(M) * N * 2);
         DeviceBuf ws(linear_workspace_bytes(mt, limit));
         const size_t tiles = static_cast<size_t>(ceil_div(N, 128)) * ceil_div(M, mt);
-        DeviceBuf tickets(tiles * sizeof(int));
-        CUDA_CHECK(cudaMemsetAsync(tickets.p, 0, tiles * sizeof(int), s));
+        DeviceBuf tickets(2 * tiles * sizeof(int));
+        CUDA_CHECK(cudaMemsetAsync(tickets.p, 0, 2 * tiles * sizeof(int), s));
         CUDA_CHECK(cudaMemsetAsync(w.p, 0x3c, wbytes * copies, s));
         CUDA_CHECK(cudaMemsetAsync(x.p, 0x3c, static_cast<size_t>(M) * K * 2, s));
         const bool w4 = getenv("CPMCU_BENCH_W4") != nullptr;

@@ -40,10 +40,73 @@ __device__ __forceinline__ int unit_owner(long long u, long long U, int G) {
     return static_cast<int>(((u + 1) * G - 1) / U);
 }
 
+__device__ __forceinline__ int ld_acquire(const int* p) {
+    int v;
+    asm volatile("ld.acquire.gpu.global.s32 %0, [%1];" : "=r"(v) : "l"(p) : "memory");
+    return v;
+}
+
+// A split tile this CTA holds a piece of: summed after the CTA's last segment.
+struct PendingTile {
+    int tile, g_first, nseg, m_base, m_cnt, n;
+    float bias;
+};
+
+// Sum tokens [t_begin, t_end) of a split tile over its pieces in CTA order (deterministic) and store them:
+// CH tokens per pass, the coalesced loads of up to four pieces (4 * CH per thread) in flight before the adds.
+template <int MT, int CH>
+__device__ __forceinline__ void sum_pieces(const LinearArgs& a, const PendingTile& p, int t_begin, int t_end, int row) {
+    const int g_last = p.g_first + p.nseg - 1;
+#pragma unroll 1
+    for (int c0 = t_begin; c0 < t_end; c0 += CH) {
+        float sum[CH];
+#pragma unroll
+        for (int c = 0; c < CH; ++c) sum[c] = 0.f;
+#pragma unroll 1
+        for (int g0 = p.g_first; g0 <= g_last; g0 += 4) {
+            float v[4][CH];
+#pragma unroll
+            for (int s = 0; s < 4; ++s) {
+                const int gg = g0 + s;
+                const float* ws = a.workspace + (static_cast<size_t>(gg) * 2 + (gg == p.g_first ? 1 : 0)) * (MT * BLOCK_N) +
+                                  static_cast<size_t>(c0) * BLOCK_N + row;
+#pragma unroll
+                for (int c = 0; c < CH; ++c) v[s][c] = (gg <= g_last && c0 + c < t_end) ? __ldcg(ws + c * BLOCK_N) : 0.f;
+            }
+#pragma unroll
+            for (int s = 0; s < 4; ++s) {
+#pragma unroll
+                for (int c = 0; c < CH; ++c) sum[c] += v[s][c];
+            }
+        }
+        if (p.n < a.N) {
+#pragma unroll
+            for (int c = 0; c < CH; ++c) {
+                if (c0 + c < t_end) {
+                    a.y[static_cast<size_t>(p.m_base + c0 + c) * a.ldy + p.n] = __float2bfloat16(sum[c] + p.bias);
+                }
+            }
+        }
+    }
+}
+
+// Longest a CTA waits for the other pieces of a tile (about 50 ms); they are computed by CTAs of the same
+// launch that finish at about the same time, so only a grid that is not co-resident gets near it.
+constexpr long long kFixupBudgetClocks = 100000000LL;
+
 // Epilogue of the four warps whose (warp & 3) selects the TMEM lane quarter.  `it` walks the same
-// segments as the producer and MMA roles; a.kblocks is the number of work units per tile.  CH = tokens
-// summed per fix-up pass (4 * CH loads in flight per thread).  chain2_off != 0: the MMA role accumulated
-// alternate instructions into a second accumulator that many columns further on; the two are added here.
+// segments as the producer and MMA roles; a.kblocks is the number of work units per tile.
+//
+// Whole tiles are written to y directly.  A piece of a split tile goes to this CTA's workspace slot as
+// fp32 [token][feature] and is counted in tickets[2 * tile].  Tiles cut in two, or with few tokens, are
+// summed on the spot by whichever piece is counted last.  A tile cut into three or more pieces is summed
+// after the CTA's last segment instead: the CTA waits until every piece of that tile has been counted and
+// sums ITS share of the tokens over all pieces, so the fix-up is spread over the CTAs that produced the
+// tile instead of falling to one (tickets[2 * tile + 1] counts departures; the last one clears both
+// counters for the next launch).  That path needs the whole grid resident (grid <= SMs, one CTA per
+// SM).  Pieces are always added in CTA order, so the result does not depend on timing.  CH = tokens
+// summed per pass.  chain2_off != 0: the MMA role accumulated alternate k-blocks into a second
+// accumulator that many columns further on; the two are added here.
 template <int MT, int CH>
 __device__ __forceinline__ void run_epilogue(const LinearArgs& a, SegIter it, uint32_t tmem_base, uint64_t* acc_full,
                                              uint64_t* acc_empty, volatile int* abort_flag, volatile int* s_last, int warp,
@@ -54,6 +117,8 @@ __device__ __forceinline__ void run_epilogue(const LinearArgs& a, SegIter it, ui
     int acc = 0;
     uint32_t acc_phase = 0;
     int tile, kb0, kb1;
+    PendingTile pend[2];
+    int n_pend = 0;
     while (it.next(tile, kb0, kb1)) {
         const int m_tile = tile / a.n_tiles;
         const int n_tile = tile - m_tile * a.n_tiles;
@@ -107,58 +172,62 @@ __device__ __forceinline__ void run_epilogue(const LinearArgs& a, SegIter it, ui
 
         if (!complete && !(a.debug & (2 | 8))) {
             const long long tile_u0 = static_cast<long long>(tile) * a.kblocks;
-            const int g_first = unit_owner(tile_u0, a.total_units, G);
-            const int g_last = unit_owner(tile_u0 + a.kblocks - 1, a.total_units, G);
-            const int nseg = g_last - g_first + 1;
-            __threadfence();
+            PendingTile p;
+            p.tile = tile;
+            p.g_first = unit_owner(tile_u0, a.total_units, G);
+            p.nseg = unit_owner(tile_u0 + a.kblocks - 1, a.total_units, G) - p.g_first + 1;
+            p.m_base = m_base; p.m_cnt = m_cnt; p.n = n; p.bias = bias_v;
+            const bool spread = (p.nseg >= 3 && m_cnt > 16);
+            __threadfence();               // this thread's partials are visible before the count
+            ptx::named_bar_sync(1, 128);
+            if (spread) {
+                if (epi_tid == 0) atomicAdd(&a.tickets[2 * tile], 1);
+                pend[n_pend++] = p;
+            } else {
+                if (epi_tid == 0) {
+                    const int old = atomicAdd(&a.tickets[2 * tile], 1);
+                    const int last = (old == p.nseg - 1) ? 1 : 0;
+                    if (last) a.tickets[2 * tile] = 0;  // ready for the next launch
+                    *s_last = last;
+                }
+                ptx::named_bar_sync(1, 128);
+                const bool is_last = (*s_last != 0);
+                ptx::named_bar_sync(1, 128);  // everyone has read s_last before it can change
+                if (is_last && !(a.debug & 16)) {
+                    __threadfence();
+                    sum_pieces<MT, CH>(a, p, 0, m_cnt, row);
+                }
+            }
+        }
+    }
+
+    // ---- split tiles: wait for the other pieces, sum this CTA's share of the tokens
+    for (int i = 0; i < n_pend; ++i) {
+        const PendingTile& p = pend[i];
+        if (epi_tid == 0) {
+            const long long t0 = clock64();
+            int ok = 1;
+            while (ld_acquire(&a.tickets[2 * p.tile]) < p.nseg) {
+                if (*abort_flag || clock64() - t0 > kFixupBudgetClocks) { ok = 0; *abort_flag = 1; break; }
+            }
+            *s_last = ok;
+        }
+        ptx::named_bar_sync(1, 128);
+        const bool ready = (*s_last != 0);
+        ptx::named_bar_sync(1, 128);  // everyone has read s_last before it can change
+        if (ready && !(a.debug & 16)) {
+            const int piece = g - p.g_first;
+            sum_pieces<MT, CH>(a, p, (p.m_cnt * piece) / p.nseg, (p.m_cnt * (piece + 1)) / p.nseg, row);
+        }
+        if (ready) {
+            // the partials of this tile may be overwritten once every piece's reader has left
             ptx::named_bar_sync(1, 128);
             if (epi_tid == 0) {
-                const int old = atomicAdd(&a.tickets[tile], 1);
-                const int last = (old == nseg - 1) ? 1 : 0;
-                if (last) a.tickets[tile] = 0;  // ready for the next launch
-                *s_last = last;
-            }
-            ptx::named_bar_sync(1, 128);
-            const bool is_last = (*s_last != 0);
-            ptx::named_bar_sync(1, 128);  // everyone has read s_last before it can change
-            if (is_last && !(a.debug & 16)) {
-                __threadfence();
-                // sum the pieces in CTA order (deterministic): CH tokens per pass, the coalesced
-                // loads of up to four pieces (4 * CH per thread) in flight before the first add
-#pragma unroll 1
-                for (int c0 = 0; c0 < m_cnt; c0 += CH) {
-                    float sum[CH];
-#pragma unroll
-                    for (int c = 0; c < CH; ++c) sum[c] = 0.f;
-#pragma unroll 1
-                    for (int g0 = g_first; g0 <= g_last; g0 += 4) {
-                        float v[4][CH];
-#pragma unroll
-                        for (int s = 0; s < 4; ++s) {
-                            const int gg = g0 + s;
-                            const float* ws = a.workspace +
-                                              (static_cast<size_t>(gg) * 2 + (gg == g_first ? 1 : 0)) * (MT * BLOCK_N) +
-                                              static_cast<size_t>(c0) * BLOCK_N + row;
-#pragma unroll
-                            for (int c = 0; c < CH; ++c) {
-                                v[s][c] = (gg <= g_last && c0 + c < m_cnt) ? __ldcg(ws + c * BLOCK_N) : 0.f;
-                            }
-                        }
-#pragma unroll
-                        for (int s = 0; s < 4; ++s) {
-#pragma unroll
-                            for (int c = 0; c < CH; ++c) sum[c] += v[s][c];
-                        }
-                    }
-                    if (n < a.N) {
-#pragma unroll
-                        for (int c = 0; c < CH; ++c) {
-                            if (c0 + c < m_cnt) {
-                                a.y[static_cast<size_t>(m_base + c0 + c) * a.ldy + n] =
-                                    __float2bfloat16(sum[c] + bias_v);
-                            }
-                        }
-                    }
+                const int old = atomicAdd(&a.tickets[2 * p.tile + 1], 1);
+                if (old == p.nseg - 1) {
+                    a.tickets[2 * p.tile + 1] = 0;
+                    __threadfence();
+                    a.tickets[2 * p.tile] = 0;  // ready for the next launch
                 }
             }
         }
