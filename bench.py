@@ -49,13 +49,15 @@ def zipf_prompt(n, vocab, seed, s=1.1):
     return rng.choice(vocab, size=n, p=p).astype(np.int32)
 
 
-def algorithmic_bytes():
-    """Weight bytes one speculative step has to stream (bf16):
-    every target linear once (M = 60), the draft fc + layer + LM head six times."""
+def algorithmic_bytes(w4a16=False):
+    """Weight bytes one speculative step has to stream: every target linear once (M = 60), the draft
+    fc + layer + LM head six times.  bf16 weights are 2 bytes; W4A16 target linears are half a byte per
+    weight plus one bf16 scale per 128."""
     H, I, V = CFG["hidden"], CFG["inter"], CFG["vocab"]
     qkv = (CFG["hq"] + 2 * CFG["hkv"]) * CFG["head_dim"]
     layer = qkv * H + H * CFG["hq"] * CFG["head_dim"] + 2 * I * H + H * I
-    target = (CFG["layers"] * layer + V * H) * 2
+    per_weight = (0.5 + 2.0 / 128) if w4a16 else 2.0
+    target = int(CFG["layers"] * layer * per_weight) + V * H * 2
     draft_pass = (2 * H * H + layer + V * H) * 2
     return target, TREE["num_iter"] * draft_pass
 
@@ -94,22 +96,27 @@ class ClockSampler(threading.Thread):
 
 
 # ---------------------------------------------------------------------------- ours
-def build_model(device_index, seed=1):
-    """Random-init config-2 model, generated on the GPU tensor by tensor and loaded through the
-    reference-shaped Python classes (C.load_model accepts device pointers)."""
+def build_model(device_index, seed=1, w4a16=False):
+    """Random-init config-2 model (config 4 with w4a16: the target's linears as random GPTQ-Marlin int4
+    tensors), generated on the GPU tensor by tensor and loaded through the reference-shaped Python classes
+    (C.load_model accepts device pointers)."""
     import types
 
     import torch
     from cpmcu.speculative.eagle import LLM_with_eagle
+    from cpmcu.speculative.eagle_base_quant.eagle_base_w4a16_marlin_gptq import W4A16GPTQMarlinLLM_with_eagle
     torch.cuda.set_device(device_index)
     os.environ.setdefault("CPMCU_MAX_TOKENS", "8192")
     hf = types.SimpleNamespace(vocab_size=CFG["vocab"], num_hidden_layers=CFG["layers"], hidden_size=CFG["hidden"],
                                intermediate_size=CFG["inter"], num_attention_heads=CFG["hq"],
                                num_key_value_heads=CFG["hkv"], head_dim=CFG["head_dim"], rms_norm_eps=CFG["eps"],
                                rope_theta=CFG["rope_theta"], torch_dtype=torch.bfloat16)
-    llm = LLM_with_eagle(None, None, num_iter=TREE["num_iter"], topk_per_iter=TREE["topk"],
-                         tree_size=TREE["tree_size"], eagle_config={"num_hidden_layers": 1}, config=hf,
-                         dtype=torch.bfloat16, chunk_length=PROMPT_LEN, memory_limit=0.8, fused_step=True)
+    if w4a16:
+        hf.quantization_config = {"group_size": 128, "bits": 4}
+    cls = W4A16GPTQMarlinLLM_with_eagle if w4a16 else LLM_with_eagle
+    llm = cls(None, None, num_iter=TREE["num_iter"], topk_per_iter=TREE["topk"],
+              tree_size=TREE["tree_size"], eagle_config={"num_hidden_layers": 1}, config=hf,
+              dtype=torch.bfloat16, chunk_length=PROMPT_LEN, memory_limit=0.8, fused_step=True)
     llm.init_storage()
     g = torch.Generator(device="cuda").manual_seed(seed)
     H, I, d = CFG["hidden"], CFG["inter"], CFG["head_dim"]
@@ -128,8 +135,20 @@ def build_model(device_index, seed=1):
                    "self_attn.v_proj": rnd(CFG["hkv"] * d, H), "self_attn.o_proj": rnd(H, CFG["hq"] * d),
                    "mlp.gate_proj": rnd(I, H), "mlp.up_proj": rnd(I, H), "mlp.down_proj": rnd(H, I),
                    "input_layernorm": ones, "post_attention_layernorm": ones}
-        for name, t in tensors.items():
-            llm._load(p + name + ".weight", t)
+        if w4a16:
+            # any bit pattern is a valid int4 tensor: uniform nibbles and scales near absmax/7 of N(0, 0.02) groups
+            for fused, (K, N) in {"self_attn.qkv_proj": (H, (CFG["hq"] + 2 * CFG["hkv"]) * d),
+                                  "self_attn.o_proj": (CFG["hq"] * d, H), "mlp.gate_up_proj": (H, 2 * I),
+                                  "mlp.down_proj": (I, H)}.items():
+                qw = torch.randint(-2 ** 31, 2 ** 31 - 1, (K // 16, 2 * N), device="cuda", generator=g, dtype=torch.int64)
+                sc = (torch.rand(K // 128, N, device="cuda", generator=g) * 0.002 + 0.0065).to(torch.bfloat16)
+                llm._load(p + fused + ".qweight", qw.to(torch.int32))
+                llm._load(p + fused + ".scales", sc)
+            for name in ("input_layernorm", "post_attention_layernorm"):
+                llm._load(p + name + ".weight", ones)
+        else:
+            for name, t in tensors.items():
+                llm._load(p + name + ".weight", t)
         if l == CFG["layers"] - 1:
             last = tensors
     # drafter: the target's last layer; fc passes the hidden state through (fc1 = 0, fc2 = I, bias 0)
@@ -156,9 +175,10 @@ def run_ours(args):
         torch.cuda.set_device(local)
         dist.init_process_group("nccl", device_id=torch.device("cuda", local))
     C.load()  # fails loudly if the CUDA library is missing
+    w4 = args.workload == "config4"
     import contextlib
     with contextlib.redirect_stdout(sys.stderr):  # keep stdout for the single JSON line
-        llm = build_model(local, seed=1)
+        llm = build_model(local, seed=1, w4a16=w4)
     from cpmcu.replicas import replica_seed
     prompt = torch.tensor(zipf_prompt(PROMPT_LEN, CFG["vocab"], replica_seed(100, rank)), device="cuda")
     pos = torch.arange(PROMPT_LEN, dtype=torch.int32, device="cuda")
@@ -216,16 +236,20 @@ def run_ours(args):
             pass
         peak = float(peaks.get("hbm_gbs", 6650.0))
         peak_src = "measured" if "hbm_gbs" in peaks else "fallback"
-        tgt_b, draft_b = algorithmic_bytes()
+        tgt_b, draft_b = algorithmic_bytes(w4)
         lin_s = statistics.median(lin_ms) / 1e3
         achieved = (tgt_b + draft_b) / 1e9 / lin_s
         line = {
             "metric": METRIC, "value": tokens_all / dev_max, "unit": UNIT, "n_gpus": world, "steps": args.steps,
             "warmup": args.warmup, "ms_per_step": 1e3 * dev_max / args.steps, "higher_is_better": True,
             "scaling": "weak", "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
-            "config": {"workload": "configs[1]: 8B-shaped bf16 target + 1-layer EAGLE, tree 60 (6 iters x top-10), "
-                                   "4096-token Zipf(1.1) prompt, batch 1, greedy",
-                       "replicas": world, "l2": "inputs larger than L2 (22.6 GB of weights streamed per step)"},
+            "config": {"workload": ("configs[3]: config-2 architecture with W4A16 GPTQ-Marlin target linears (random "
+                                    "int4 tensors), bf16 embeddings / LM head / EAGLE draft, tree 60, "
+                                    if w4 else
+                                    "configs[1]: 8B-shaped bf16 target + 1-layer EAGLE, tree 60 (6 iters x top-10), ")
+                                   + "4096-token Zipf(1.1) prompt, batch 1, greedy",
+                       "replicas": world,
+                       "l2": "inputs larger than L2 (%.1f GB of weights streamed per step)" % ((tgt_b + draft_b) / 1e9)},
             "e2e": {"value": tokens_all / wall_max, "unit": UNIT, "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 128},
             "gpu_launches": int(launches) * args.steps,
             "launches_per_step": int(launches),
@@ -234,7 +258,8 @@ def run_ours(args):
             "prefill_tokens_per_s": PROMPT_LEN / prefill_s,
             "profile_eager_step_ms": {"total": statistics.median(prof_total), "linear": statistics.median(lin_ms),
                                       "attention": statistics.median(att_ms), "linear_launches": lin_n},
-            "roofline": {"bound": "hbm", "kernel": "linear_umma_kernel (all %d launches of a step)" % lin_n,
+            "roofline": {"bound": "hbm", "kernel": "linear_umma_kernel%s (all %d launches of a step)"
+                                                   % (" + linear_w4_umma_kernel" if w4 else "", lin_n),
                          "achieved": achieved, "peak": peak, "unit": "GB/s", "frac": achieved / peak,
                          "peak_source": peak_src, "traffic": None,
                          "algorithmic_bytes_per_step": tgt_b + draft_b},
@@ -344,6 +369,8 @@ def main():
     ap.add_argument("--warmup", type=int, default=5)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--workload", default="config2", choices=["config2", "config4"],
+                    help="config2 = the headline bf16 workload; config4 = the same with a W4A16 GPTQ-Marlin target")
     args = ap.parse_args()
     if args.warmup < 3:
         args.warmup = 3

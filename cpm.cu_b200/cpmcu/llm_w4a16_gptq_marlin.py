@@ -3,9 +3,10 @@ cpmcu/llm_w4a16_gptq_marlin.py:24-463).  Checkpoints carry the fused tensors
 `qkv_proj`, `o_proj`, `gate_up_proj`, `down_proj` as `qweight` (int32, Marlin tile
 order) and `scales` (model dtype); embeddings, norms and the LM head stay bf16.
 
-This build unpacks and dequantises the int4 tensors when they are loaded and runs
-the bf16 streaming GEMM on them, so results follow the W4A16 arithmetic but the
-weights occupy (and stream as) bf16; an int4-streaming GEMM is not built yet."""
+The library re-tiles the int4 tensors when they are loaded (one contiguous block
+of nibbles and scales per 128-row x 256-k unit) and streams them as 4-bit through
+the W4A16 GEMM, which dequantises w = (q - 8) * scale on the way into the tensor
+cores (csrc/gemm_w4_umma.cu)."""
 import math
 
 import torch

@@ -500,7 +500,7 @@ int cpmcu_draft_tree_from_logits(const void* logits, int vocab, int k, int num_i
         CPM_REQUIRE(tree_size - 1 <= st.total_tried, "draft tree: tree larger than the candidate set");
         const int hidden = 8;  // dummy hidden rows: the hidden-state gather is exercised but unused
         DeviceBuf tv((st.total_tried + 64) * 2), tp((st.total_tried + 64) * 4), tpar((k * num_iter + 64) * 4);
-        DeviceBuf fs(64 * 2), fi(64 * 4), fm(64 * 8), sp(64 * 4);
+        DeviceBuf fs(64 * 2), fi(64 * 4), fm(64 * 8), sp(64 * 4), fsrc(64 * 4);
         DeviceBuf h(static_cast<size_t>(32) * hidden * 2), hid(static_cast<size_t>(32) * hidden * 2);
         DeviceBuf scan(draft_scan_workspace_bytes(32, vocab, 32));
         CUDA_CHECK(cudaMemsetAsync(h.p, 0, static_cast<size_t>(32) * hidden * 2, s));
@@ -510,6 +510,7 @@ int cpmcu_draft_tree_from_logits(const void* logits, int vocab, int k, int num_i
         st.fr_score = static_cast<bf16*>(fs.p);
         st.fr_id = static_cast<int32_t*>(fi.p);
         st.fr_mask = static_cast<uint64_t*>(fm.p);
+        st.fr_src = static_cast<int32_t*>(fsrc.p);
         st.sel_pos = static_cast<int32_t*>(sp.p);
         st.token_id_remap = token_id_remap;
         const bf16* lg = static_cast<const bf16*>(logits);

@@ -166,6 +166,10 @@ void launch_add_rms_norm(bf16* x, const bf16* delta, float delta_scale, const bf
                          float eps, cudaStream_t s);
 void launch_embedding(const int32_t* ids, const bf16* table, bf16* out, int ld_out, int rows, int dim, float scale,
                       cudaStream_t s);
+// The same plus, in the same launch, hid_out[r] = h_rows[src[r]] for r < rows (rows of `dim` elements).
+void launch_embedding_gather(const int32_t* ids, const bf16* table, bf16* out, int ld_out, int rows, int dim, float scale,
+                             const bf16* h_rows, int h_ld, const int32_t* src, bf16* hid_out, int hid_ld,
+                             cudaStream_t s);
 // qkv: [rows, (hq + 2 hkv) * d].  Applies NeoX RoPE to q (in place) and k, then
 // writes k,v into the cache at row (*kv_len + kv_off + r) for r < *n_valid
 // (n_valid may be null = rows).  Position of row r: pos[r], or when pos is

@@ -181,9 +181,7 @@ __device__ unsigned long long warp_select(unsigned long long* keys, int n, int k
 //               parent / mask / hidden / token bookkeeping for the next level.
 __global__ void draft_expand_kernel(DraftTreeState st, const unsigned long long* __restrict__ cand, int nseg,
                                     const bf16* __restrict__ logits, int ld, const float2* __restrict__ rowoff,
-                                    int level, const bf16* __restrict__ h_rows, int h_ld,
-                                    const int32_t* __restrict__ last_row_ptr, bf16* __restrict__ hid_out,
-                                    int hid_ld, int hidden) {
+                                    int level, const int32_t* __restrict__ last_row_ptr) {
     grid_dependency_sync();
     extern __shared__ unsigned long long sh_keys[];  // rows * nseg * k candidate keys, then scratch
     const int k = st.k;
@@ -220,13 +218,8 @@ __global__ void draft_expand_kernel(DraftTreeState st, const unsigned long long*
             st.fr_score[i] = s_val[i];
             st.fr_id[i] = st.token_id_remap ? st.token_id_remap[s_pos[i]] : s_pos[i];
             st.fr_mask[i] = 1ull << i;
-        }
-        // frontier hidden state: the last valid row of the catch-up pass, repeated k times
-        const int src = last_row_ptr ? *last_row_ptr : 0;
-        const uint4* s4 = reinterpret_cast<const uint4*>(h_rows + static_cast<size_t>(src) * h_ld);
-        for (int i = threadIdx.x; i < k * (hidden / 8); i += blockDim.x) {
-            const int r = i / (hidden / 8), c = i - r * (hidden / 8);
-            reinterpret_cast<uint4*>(hid_out + static_cast<size_t>(r) * hid_ld)[c] = s4[c];
+            // frontier hidden state: the last valid row of the catch-up pass, for every node
+            st.fr_src[i] = last_row_ptr ? *last_row_ptr : 0;
         }
         return;
     }
@@ -256,13 +249,18 @@ __global__ void draft_expand_kernel(DraftTreeState st, const unsigned long long*
         st.fr_mask[i] = s_oldmask[sel / k] | (1ull << (k * level + i));
         st.fr_score[i] = s_val[sel];
         st.fr_id[i] = st.token_id_remap ? st.token_id_remap[s_pos[sel]] : s_pos[sel];
+        st.fr_src[i] = sel / k;
     }
-    for (int i = threadIdx.x; i < k * (hidden / 8); i += blockDim.x) {
-        const int r = i / (hidden / 8), c = i - r * (hidden / 8);
-        const int src = s_sel[r] / k;
-        reinterpret_cast<uint4*>(hid_out + static_cast<size_t>(r) * hid_ld)[c] =
-            reinterpret_cast<const uint4*>(h_rows + static_cast<size_t>(src) * h_ld)[c];
-    }
+}
+
+// hid_out[r] = h_rows[src[r]]: one CTA per row.
+__global__ void gather_rows_kernel(const bf16* __restrict__ h_rows, int h_ld, const int32_t* __restrict__ src,
+                                   bf16* __restrict__ hid_out, int hid_ld, int hidden) {
+    grid_dependency_sync();
+    const int r = blockIdx.x;
+    const uint4* s4 = reinterpret_cast<const uint4*>(h_rows + static_cast<size_t>(src[r]) * h_ld);
+    uint4* d4 = reinterpret_cast<uint4*>(hid_out + static_cast<size_t>(r) * hid_ld);
+    for (int c = threadIdx.x; c < hidden / 8; c += blockDim.x) d4[c] = s4[c];
 }
 
 // ---- final selection of tree_size-1 candidates + tree arrays.  One CTA.
@@ -377,7 +375,11 @@ void launch_draft_topk_expand(const DraftTreeState& st, const bf16* logits, int 
     }
     launch_kernel(draft_expand_kernel, dim3(1), dim3(32 * (k < 4 ? 4 : k)), shmem, s, st,
                   static_cast<const unsigned long long*>(cand), nseg, logits, ld, static_cast<const float2*>(rowoff), level,
-                  h_rows, h_ld, last_row_ptr, hid_out, hid_ld, hidden);
+                  last_row_ptr);
+    if (hid_out != nullptr) {
+        launch_kernel(gather_rows_kernel, dim3(k), dim3(128), 0, s, h_rows, h_ld, static_cast<const int32_t*>(st.fr_src),
+                      hid_out, hid_ld, hidden);
+    }
 }
 
 void launch_tree_finalize(const DraftTreeState& st, const int32_t* cache_length, int32_t* tree_draft_ids,

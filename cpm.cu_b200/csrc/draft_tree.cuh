@@ -14,6 +14,7 @@ struct DraftTreeState {
     bf16* fr_score = nullptr;             // [k] frontier cumulative scores
     int32_t* fr_id = nullptr;             // [k] frontier token ids (full vocabulary)
     uint64_t* fr_mask = nullptr;          // [k] frontier ancestor masks over draft keys
+    int32_t* fr_src = nullptr;            // [k] row of the level's hidden states each frontier node continues from
     int32_t* sel_pos = nullptr;           // [64] tried index chosen for tree node i+1
     const int32_t* token_id_remap = nullptr;  // FR-Spec: draft id -> full-vocabulary id, or null
 };
@@ -22,9 +23,11 @@ int draft_num_segments(int vocab);
 size_t draft_scan_workspace_bytes(int rows, int vocab, int k);
 
 // log-softmax + top-k of `logits` (1 row at level 0, k rows after) followed by
-// the frontier bookkeeping of that level.  h_rows: the level's output hidden
-// states (row stride h_ld); at level 0 the row *last_row_ptr is repeated k
-// times into hid_out, afterwards hid_out[i] = h_rows[selected parent of i].
+// the frontier bookkeeping of that level.  st.fr_src[i] receives the row of the
+// level's hidden states that frontier node i continues from (*last_row_ptr at level 0,
+// the selected parent afterwards).  If hid_out is not null the rows are also gathered,
+// hid_out[i] = h_rows[fr_src[i]]; the engine passes null and gathers them in the next
+// level's embedding kernel (launch_embedding_gather).
 void launch_draft_topk_expand(const DraftTreeState& st, const bf16* logits, int ld, int vocab, int level,
                               void* scan_ws, const bf16* h_rows, int h_ld, const int32_t* last_row_ptr, bf16* hid_out,
                               int hid_ld, int hidden, cudaStream_t s);

@@ -112,6 +112,33 @@ __global__ void embedding_kernel(const int32_t* __restrict__ ids, const bf16* __
     }
 }
 
+// Embedding rows (blockIdx.y == 0) and, in the same launch, gathered hidden rows
+// hid_out[r] = h_rows[src[r]] (blockIdx.y == 1): the two halves of the draft layer's input.
+__global__ void embedding_gather_kernel(const int32_t* __restrict__ ids, const bf16* __restrict__ table,
+                                        bf16* __restrict__ out, int ld_out, int dim, float scale,
+                                        const bf16* __restrict__ h_rows, int h_ld, const int32_t* __restrict__ src,
+                                        bf16* __restrict__ hid_out, int hid_ld) {
+    grid_dependency_sync();
+    const int row = blockIdx.x;
+    if (blockIdx.y == 1) {
+        const uint4* s4 = reinterpret_cast<const uint4*>(h_rows + static_cast<size_t>(src[row]) * h_ld);
+        uint4* d4 = reinterpret_cast<uint4*>(hid_out + static_cast<size_t>(row) * hid_ld);
+        for (int c = threadIdx.x; c < dim / 8; c += blockDim.x) d4[c] = s4[c];
+        return;
+    }
+    const size_t from = static_cast<size_t>(ids[row]) * dim;
+    const size_t dst = static_cast<size_t>(row) * ld_out;
+    for (int i = threadIdx.x * 8; i < dim; i += blockDim.x * 8) {
+        uint4 v = *reinterpret_cast<const uint4*>(table + from + i);
+        if (scale != 1.0f) {
+            bf16* e = reinterpret_cast<bf16*>(&v);
+#pragma unroll
+            for (int j = 0; j < 8; ++j) e[j] = __float2bfloat16(__bfloat162float(e[j]) * scale);
+        }
+        *reinterpret_cast<uint4*>(out + dst + i) = v;
+    }
+}
+
 // One CTA per token row.  q heads rotate in place; k heads rotate into the
 // cache; v heads are copied into the cache.  The d/2 sines and cosines of the row's
 // position are computed once per CTA; each thread then rotates element pairs
@@ -320,6 +347,16 @@ void launch_embedding(const int32_t* ids, const bf16* table, bf16* out, int ld_o
     if (rows <= 0) return;
     CPM_REQUIRE(dim % 8 == 0 && ld_out % 8 == 0, "embedding: dim must be a multiple of 8");
     launch_kernel(embedding_kernel, dim3(rows), dim3(128), 0, s, ids, table, out, ld_out, dim, scale);
+}
+
+void launch_embedding_gather(const int32_t* ids, const bf16* table, bf16* out, int ld_out, int rows, int dim, float scale,
+                             const bf16* h_rows, int h_ld, const int32_t* src, bf16* hid_out, int hid_ld,
+                             cudaStream_t s) {
+    if (rows <= 0) return;
+    CPM_REQUIRE(dim % 8 == 0 && ld_out % 8 == 0 && h_ld % 8 == 0 && hid_ld % 8 == 0,
+                "embedding: dim and row strides must be multiples of 8");
+    launch_kernel(embedding_gather_kernel, dim3(rows, 2), dim3(128), 0, s, ids, table, out, ld_out, dim, scale, h_rows, h_ld,
+                  src, hid_out, hid_ld);
 }
 
 void launch_rope_append(bf16* qkv, int rows, int hq, int hkv, int d, const float* inv_freq, const int32_t* pos,

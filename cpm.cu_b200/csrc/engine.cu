@@ -200,6 +200,7 @@ void Engine::lay_out(Pool& p) {
         tree_.fr_score = take<bf16>(p, 64);
         tree_.fr_id = take<int32_t>(p, 64);
         tree_.fr_mask = take<uint64_t>(p, 64);
+        tree_.fr_src = take<int32_t>(p, 64);
         tree_.sel_pos = take<int32_t>(p, 64);
     }
     // KV caches last: everything that is left up to the budget
@@ -614,9 +615,12 @@ void Engine::draft_levels(int32_t* tree_ids, int32_t* tree_pos, const int32_t* c
     const bool scale_in = (!ec_.minicpm4_variant && mc_.scale_lmhead != 1.0f);
     bf16* hid_dst = ec_.use_input_norm ? e_hid_ : e_in_ + H;
     const int hid_ld = ec_.use_input_norm ? H : 2 * H;
-    // level 0: logits of the last pending row
+    // level 0: logits of the last pending row.  The frontier's hidden rows are gathered by the next level's
+    // embedding kernel from `h_src` (the expansion kernel only records which row each node continues from).
+    const bf16* h_src = e_h_;
     if (first) {
         const bf16* last = e_h_ + static_cast<size_t>(num_prev_ - 1) * H;
+        h_src = last;
         const bf16* in = last;
         if (scale_in) {
             launch_scale(lm_in_, last, mc_.scale_lmhead, H, s);
@@ -625,22 +629,25 @@ void Engine::draft_levels(int32_t* tree_ids, int32_t* tree_pos, const int32_t* c
         LinearPlan p = make_linear_plan(in, 1, draft_lm_head_, 1, draft_vocab_, H, e_logits_, draft_vocab_, nullptr,
                                         gemm_ws_, tickets_, rt.num_sms);
         launch_linear(p, s);
-        launch_draft_topk_expand(tree_, e_logits_, draft_vocab_, draft_vocab_, 0, scan_ws_, last, H, nullptr, hid_dst,
+        launch_draft_topk_expand(tree_, e_logits_, draft_vocab_, draft_vocab_, 0, scan_ws_, last, H, nullptr, nullptr,
                                  hid_ld, H, s);
     } else {
         if (scale_in) launch_scale(lm_in_, e_h_, mc_.scale_lmhead, static_cast<size_t>(catchup_rows_) * H, s);
         launch_linear(dlm_plan_catchup_, s);
         launch_draft_topk_expand(tree_, e_logits_, draft_vocab_, draft_vocab_, 0, scan_ws_, e_h_, H, st_ + S_LASTROW,
-                                 hid_dst, hid_ld, H, s);
+                                 nullptr, hid_ld, H, s);
     }
     for (int d = 1; d < ec_.num_iter; ++d) {
         if (ec_.use_input_norm) {
-            launch_embedding(tree_.fr_id, embed_, e_emb_, H, k, H, mc_.scale_embed, s);
+            launch_embedding_gather(tree_.fr_id, embed_, e_emb_, H, k, H, mc_.scale_embed, h_src, H, tree_.fr_src, hid_dst,
+                                    hid_ld, s);
             launch_rms_norm(e_emb_, H, in_norm1_, e_in_, 2 * H, k, H, mc_.eps, s);
             launch_rms_norm(e_hid_, H, in_norm2_, e_in_ + H, 2 * H, k, H, mc_.eps, s);
         } else {
-            launch_embedding(tree_.fr_id, embed_, e_in_, 2 * H, k, H, mc_.scale_embed, s);
+            launch_embedding_gather(tree_.fr_id, embed_, e_in_, 2 * H, k, H, mc_.scale_embed, h_src, H, tree_.fr_src, hid_dst,
+                                    hid_ld, s);
         }
+        h_src = e_h_;
         launch_linear(fc_plan_level_, s);
         RowCtx c;
         c.rows = k;
@@ -656,7 +663,7 @@ void Engine::draft_levels(int32_t* tree_ids, int32_t* tree_pos, const int32_t* c
         draft_forward(c, k, eplan_level_, s);
         if (scale_in) launch_scale(lm_in_, e_h_, mc_.scale_lmhead, static_cast<size_t>(k) * H, s);
         launch_linear(dlm_plan_level_, s);
-        launch_draft_topk_expand(tree_, e_logits_, draft_vocab_, draft_vocab_, d, scan_ws_, e_h_, H, nullptr, hid_dst,
+        launch_draft_topk_expand(tree_, e_logits_, draft_vocab_, draft_vocab_, d, scan_ws_, e_h_, H, nullptr, nullptr,
                                  hid_ld, H, s);
     }
     launch_tree_finalize(tree_, cache_length, tree_ids, tree_pos, tree_mask, tree_parent, s);
