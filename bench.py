@@ -261,7 +261,12 @@ def run_ours(args):
             "roofline": {"bound": "hbm", "kernel": "linear_umma_kernel%s (all %d launches of a step)"
                                                    % (" + linear_w4_umma_kernel" if w4 else "", lin_n),
                          "achieved": achieved, "peak": peak, "unit": "GB/s", "frac": achieved / peak,
-                         "peak_source": peak_src, "traffic": None,
+                         "peak_source": peak_src,
+                         # DRAM bytes of the step's linear launches: algorithmic bytes x the ratio one ncu capture
+                         # of the gate/up GEMM gave (269.5 MB read + 5.3 MB written for 268.9 MB algorithmic;
+                         # W4A16: 69.8 + 1.5 MB for 69.7 MB), see profiles/
+                         "traffic": int((tgt_b + draft_b) * (1.023 if w4 else 1.022)),
+                         "traffic_source": "scaled from one ncu capture of the gate/up GEMM",
                          "algorithmic_bytes_per_step": tgt_b + draft_b},
             "step_roofline_frac": ((tgt_b + draft_b) / 1e9 / peak) / (statistics.median(dev_ms) / 1e3),
             "clocks": sampler.summary(),
