@@ -16,7 +16,7 @@ OUT_DIR = os.path.join(HERE, "cpmcu")
 OBJ_DIR = os.path.join(HERE, "build")
 LIB = os.path.join(OUT_DIR, "libcpmcu_b200.so")
 SOURCES = ["runtime.cu", "gemm_umma.cu", "gemm_w4_umma.cu", "elementwise.cu", "tree_attn.cu", "draft_tree.cu", "accept.cu",
-           "marlin_unpack.cu", "engine.cu", "capi.cu"]
+           "marlin_unpack.cu", "sparse_select.cu", "engine.cu", "capi.cu"]
 NVCC_FLAGS = ["-gencode", "arch=compute_100a,code=sm_100a", "-lineinfo", "-O3", "-std=c++17",
               "-Xcompiler", "-fPIC", "--threads", "2"]
 # extra defines for instrumented builds, e.g. CPMCU_BUILD_DEFINES="-DCPMCU_W4_PROFILE=1"

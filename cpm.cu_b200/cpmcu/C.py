@@ -44,6 +44,11 @@ _SIGNATURES = {
     "cpmcu_linear_w4a16": (_c_int, [_c_void_p] * 4 + [_c_int] * 4),
     "cpmcu_bench_linear": (_c_int, [_c_int] * 6 + [_c_void_p]),
     "cpmcu_bench_attention": (_c_int, [_c_int] * 7 + [_c_void_p]),
+    "cpmcu_sparse_attention": (_c_int, [_c_void_p, _c_int, _c_void_p, _c_void_p] + [_c_int] * 4 +
+                               [_c_void_p, _c_int, _c_void_p, _c_int, _c_void_p, _c_int, _c_int, _c_int, _c_void_p,
+                                _c_int]),
+    "cpmcu_sparse_select": (_c_int, [_c_void_p, _c_int, _c_int, _c_int, _c_int, _c_void_p, _c_int, _c_void_p] +
+                            [_c_int] * 6 + [_c_void_p] * 3 + [_c_int, _c_void_p, _c_int]),
     "cpmcu_tree_attention": (_c_int, [_c_void_p, _c_int, _c_void_p, _c_void_p] + [_c_int] * 4 +
                              [_c_void_p, _c_int, _c_void_p, _c_void_p] + [_c_int] * 3 + [_c_void_p, _c_int]),
     "cpmcu_rms_norm": (_c_int, [_c_void_p, _c_void_p, _c_float, _c_void_p, _c_void_p, _c_int, _c_int, _c_float]),

@@ -7,6 +7,7 @@
 
 #include "../../include/cpmcu_b200.h"
 #include "engine.cuh"
+#include "sparse_select.cuh"
 
 namespace {
 
@@ -387,6 +388,82 @@ int cpmcu_tree_attention(const void* q, int q_ld, const void* k_cache, const voi
         p.window = window;
         launch_tree_attention(p, rt.stream);
         sync_and_check("tree_attention");
+        return 0;
+    });
+}
+
+int cpmcu_sparse_attention(const void* q, int q_ld, const void* k_cache, const void* v_cache, int budget, int tq,
+                           int hq, int hkv, const int32_t* kv_len, int kv_len_add, const uint64_t* mask, int mask_k,
+                           const uint64_t* blockmask, int bm_words, int block_window, int splits, void* out,
+                           int out_ld) {
+    return guarded([&] {
+        Runtime& rt = runtime();
+        CPM_REQUIRE(splits >= 1 && splits <= 32, "attention: splits must be in [1,32]");
+        CPM_REQUIRE(budget <= 262144, "block-sparse attention: at most 262144 keys");
+        const size_t rows = static_cast<size_t>(tq) * hq;
+        DeviceBuf ws_o(splits > 1 ? rows * splits * 128 * sizeof(float) : 0);
+        DeviceBuf ws_ml(splits > 1 ? rows * splits * 2 * sizeof(float) : 0);
+        AttnPlan p = make_attn_plan(static_cast<const bf16*>(q), q_ld, static_cast<const bf16*>(k_cache),
+                                    static_cast<const bf16*>(v_cache), budget, tq, hq, hkv, 128, splits,
+                                    static_cast<bf16*>(out), out_ld, static_cast<float*>(ws_o.p),
+                                    static_cast<float*>(ws_ml.p));
+        p.kv_len = kv_len;
+        p.kv_len_add = kv_len_add;
+        p.mask = mask;
+        p.mask_k = mask ? mask_k : 0;
+        p.blockmask = blockmask;
+        p.bm_words = bm_words;
+        p.block_window = block_window;
+        launch_tree_attention(p, rt.stream);
+        sync_and_check("sparse_attention");
+        return 0;
+    });
+}
+
+int cpmcu_sparse_select(const void* q, int q_ld, int tq, int hq, int hkv, const void* k_cache, int budget,
+                        const int32_t* kv_len, int kv_len_add, int sink_window_size, int block_window_size,
+                        int sparse_topk_k, int sparse_switch, int apply_compress_lse, void* c1_out, void* c2_out,
+                        void* scores_out, int score_ld, uint64_t* blockmask_out, int bm_words) {
+    return guarded([&] {
+        Runtime& rt = runtime();
+        cudaStream_t s = rt.stream;
+        const int kv_dim = hkv * 128;
+        CPM_REQUIRE(budget % 64 == 0 && score_ld >= (budget / 16 + 127) / 128 * 128 && score_ld % 8 == 0,
+                    "sparse_select: score rows must hold budget / 16 entries rounded up to 128");
+        SparseBuffers b;
+        DeviceBuf c1(static_cast<size_t>(budget / 16) * kv_dim * 2), c2(static_cast<size_t>(budget / 64) * kv_dim * 2);
+        DeviceBuf done(8), scores(static_cast<size_t>(hkv) * tq * score_ld * 2);
+        DeviceBuf bm(static_cast<size_t>(hkv) * tq * bm_words * 8), ptrs(2 * sizeof(void*));
+        CUDA_CHECK(cudaMemsetAsync(done.p, 0, 8, s));
+        CUDA_CHECK(cudaMemsetAsync(scores.p, 0, static_cast<size_t>(hkv) * tq * score_ld * 2, s));
+        const void* host_ptrs[2] = {k_cache, nullptr};
+        CUDA_CHECK(cudaMemcpyAsync(ptrs.p, host_ptrs, sizeof(host_ptrs), cudaMemcpyHostToDevice, s));
+        b.c1 = static_cast<bf16*>(c1.p);
+        b.c2 = apply_compress_lse ? static_cast<bf16*>(c2.p) : nullptr;
+        b.done = static_cast<int32_t*>(done.p);
+        b.scores = static_cast<bf16*>(scores.p);
+        b.score_ld = score_ld;
+        b.blockmask = static_cast<uint64_t*>(bm.p);
+        b.bm_words = bm_words;
+        b.max_tokens = tq;
+        SparseConfig cfg;
+        cfg.enabled = true;
+        cfg.sink_blocks = sink_window_size;
+        cfg.window_blocks = block_window_size;
+        cfg.topk = sparse_topk_k;
+        cfg.sparse_switch = sparse_switch;
+        cfg.compress_lse = apply_compress_lse != 0;
+        launch_sparse_compress(b, static_cast<bf16* const*>(ptrs.p), 1, kv_dim, kv_len, kv_len_add, budget / 16, s);
+        launch_sparse_select(b, cfg, 0, static_cast<const bf16*>(q), q_ld, tq, hq, hkv, kv_len, kv_len_add, nullptr, s);
+        if (c1_out) CUDA_CHECK(cudaMemcpyAsync(c1_out, c1.p, static_cast<size_t>(budget / 16) * kv_dim * 2, cudaMemcpyDeviceToDevice, s));
+        if (c2_out && apply_compress_lse) {
+            CUDA_CHECK(cudaMemcpyAsync(c2_out, c2.p, static_cast<size_t>(budget / 64) * kv_dim * 2, cudaMemcpyDeviceToDevice, s));
+        }
+        if (scores_out) {
+            CUDA_CHECK(cudaMemcpyAsync(scores_out, scores.p, static_cast<size_t>(hkv) * tq * score_ld * 2, cudaMemcpyDeviceToDevice, s));
+        }
+        CUDA_CHECK(cudaMemcpyAsync(blockmask_out, bm.p, static_cast<size_t>(hkv) * tq * bm_words * 8, cudaMemcpyDeviceToDevice, s));
+        sync_and_check("sparse_select");
         return 0;
     });
 }

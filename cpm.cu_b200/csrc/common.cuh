@@ -197,6 +197,9 @@ struct AttnPlan {
     const uint64_t* mask = nullptr;   // per-token tree mask over the last mask_k keys
     int mask_k = 0;
     int window = 0;                   // >0: block-granular sliding window (tokens)
+    const uint64_t* blockmask = nullptr;  // block-sparse mode: [hkv][tq][bm_words] bits over 64-key blocks
+    int bm_words = 0;
+    int block_window = 0;             // trailing 64-key blocks every token sees in block-sparse mode
     float scale = 0.f;
     bf16* out = nullptr;              // token t, head h at out + t*out_ld + h*d
     int out_ld = 0;

@@ -16,6 +16,13 @@
 //               writes bf16 P into 128-byte-swizzled shared memory
 //   O += P V    tcgen05.mma, A = P (K-major), B = V tile (N-major), O in TMEM
 // K/V tiles of 128 keys arrive by TMA (no multicast) into a two-stage ring.
+//
+// Block-sparse mode (InfLLM-v2 target layers; replaces compute_attn_1rowblock_splitkv_headlevel,
+// src/flash_attn/src/flash_fwd_kernel.h:580-1171 with the iterator of flash_blockmask.h): every
+// (kv head, token) carries a bitmask over 64-key blocks; a token sees block b iff its bit is set or
+// b >= ceil((t + kv_total - tq) / 64) - block_window.  A tile holds 128 / grp tokens, so the CTA
+// visits the union of their blocks (kept as a bitmask over 128-key tiles in shared memory) and each
+// row masks the 64-key halves its own token may not see.
 // gridDim.y key splits each write an unnormalised partial (O, max, sum); a
 // small second kernel merges them.  With one split the kernel normalises and
 // stores bf16 directly.
@@ -34,7 +41,8 @@ constexpr int SMEM_K = SMEM_Q + TILE_BYTES;          // 2 stages
 constexpr int SMEM_V = SMEM_K + 2 * TILE_BYTES;      // 2 stages
 constexpr int SMEM_P = SMEM_V + 2 * TILE_BYTES;      // 2 stages
 constexpr int SMEM_CTRL = SMEM_P + 2 * TILE_BYTES;
-constexpr int SMEM_XCH = SMEM_CTRL + 256;   // 2 x 128 floats
+constexpr int SMEM_UNION = SMEM_CTRL + 128;  // 256 B: bitmask over up to 2048 key tiles (block-sparse mode)
+constexpr int SMEM_XCH = SMEM_CTRL + 512;   // 2 x 128 floats
 constexpr int SMEM_TOTAL = SMEM_XCH + 1024 + 1024;
 constexpr int TMEM_COLS = 512;  // S stage 0: [0,128), S stage 1: [128,256), O: [256,384)
 constexpr int TMEM_O = 256;
@@ -49,6 +57,8 @@ struct AttnArgs {
     const uint64_t* mask;
     int mask_k;
     int window;
+    const uint64_t* blockmask;  // [hkv][tq][bm_words] bits over 64-key blocks, or null
+    int bm_words, block_window;
     float scale_log2;
     bf16* out;
     int out_ld;
@@ -150,9 +160,66 @@ tree_attn_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant
     const int kt_lo = key_lo / KEYS;
     const int kt_hi = (key_hi + KEYS - 1) / KEYS;
     const int n_kt = max(kt_hi - kt_lo, 0);
-    const int kt_begin = kt_lo + static_cast<int>((static_cast<long long>(n_kt) * split) / nsplit);
+    int kt_begin = kt_lo + static_cast<int>((static_cast<long long>(n_kt) * split) / nsplit);
     const int kt_end = kt_lo + static_cast<int>((static_cast<long long>(n_kt) * (split + 1)) / nsplit);
-    const int n_it = kt_end - kt_begin;
+    int n_it = kt_end - kt_begin;
+
+    // ---- block-sparse mode: union of the tile's tokens' blocks, then this split's share of the set tiles
+    const bool sparse = (a.blockmask != nullptr);
+    uint32_t* uni = reinterpret_cast<uint32_t*>(smem + SMEM_UNION);       // 64 words = 2048 key tiles
+    volatile int* sp_info = reinterpret_cast<volatile int*>(abort_flag + 1);  // [0] first tile, [1] count
+    // this row's token: first 64-key block always visible, and its mask row
+    const int win_left = sparse ? (t + causal_base + 63) / 64 - a.block_window : 0;
+    const uint64_t* bm_row = (sparse && row_valid) ? a.blockmask + (static_cast<size_t>(h) * a.tq + t) * a.bm_words : nullptr;
+    if (sparse) {
+        if (tid < 64) uni[tid] = 0u;
+        __syncthreads();
+        const int tok_n = max(min(t0 + a.tok_per_tile, tq_eff) - t0, 0);
+        for (int kt = kt_lo + tid; kt < kt_hi; kt += NTHREADS) {
+            bool any = false;
+            for (int tt = 0; tt < tok_n && !any; ++tt) {
+                const int left = (t0 + tt + causal_base + 63) / 64 - a.block_window;
+                const uint64_t* r = a.blockmask + (static_cast<size_t>(h) * a.tq + t0 + tt) * a.bm_words;
+#pragma unroll
+                for (int hb = 0; hb < 2; ++hb) {
+                    const int b = kt * 2 + hb;
+                    any = any || b >= left || (((b >> 6) < a.bm_words) && ((r[b >> 6] >> (b & 63)) & 1ull));
+                }
+            }
+            if (any) atomicOr(&uni[kt >> 5], 1u << (kt & 31));
+        }
+        __syncthreads();
+        if (tid == 0) {
+            int total = 0;
+            for (int w = 0; w < 64; ++w) total += __popc(uni[w]);
+            const int r0 = static_cast<int>((static_cast<long long>(total) * split) / nsplit);
+            const int r1 = static_cast<int>((static_cast<long long>(total) * (split + 1)) / nsplit);
+            int first = 0, seen = 0;
+            for (int w = 0; w < 64 && r0 < r1; ++w) {  // tile index of the set bit with rank r0
+                const int c = __popc(uni[w]);
+                if (seen + c > r0) {
+                    uint32_t v = uni[w];
+                    for (int k = seen; k < r0; ++k) v &= v - 1;
+                    first = w * 32 + __ffs(v) - 1;
+                    break;
+                }
+                seen += c;
+            }
+            sp_info[0] = first;
+            sp_info[1] = r1 - r0;
+        }
+        __syncthreads();
+        kt_begin = sp_info[0];
+        n_it = sp_info[1];
+    }
+    // key tile of iteration i + 1 given the tile of iteration i (dense: the next one)
+    auto next_tile = [&](int kt) -> int {
+        if (!sparse) return kt + 1;
+        int w = (kt + 1) >> 5;
+        uint32_t v = (w < 64) ? (uni[w] & (0xffffffffu << ((kt + 1) & 31))) : 0u;
+        while (v == 0u && ++w < 64) v = uni[w];
+        return v ? w * 32 + __ffs(v) - 1 : kt + 1;
+    };
 
     float m_run = -INFINITY;  // running max of raw scores (same in both threads of a row)
     float l_run = 0.f;        // this thread's share of the running sum
@@ -165,14 +232,17 @@ tree_attn_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant
             const uint32_t p_addr = ptx::smem_u32(smem + SMEM_P);
             constexpr uint32_t idesc_s = ptx::umma_idesc_bf16(ROWS, KEYS, 0, 0);
             constexpr uint32_t idesc_o = ptx::umma_idesc_bf16(ROWS, D, 0, 1);
+            int k_tile = kt_begin, v_tile = kt_begin;  // tiles of the next K / V load (issued in iteration order)
             auto load_k = [&](int i) {
-                const int st = i & 1, key0 = (kt_begin + i) * KEYS;
+                const int st = i & 1, key0 = k_tile * KEYS;
+                k_tile = next_tile(k_tile);
                 ptx::mbar_arrive_expect_tx(&k_full[st], TILE_BYTES);
                 ptx::tma_load_2d(smem + SMEM_K + st * TILE_BYTES, &tm_k, &k_full[st], h * D, key0);
                 ptx::tma_load_2d(smem + SMEM_K + st * TILE_BYTES + HALF_BYTES, &tm_k, &k_full[st], h * D + 64, key0);
             };
             auto load_v = [&](int i) {
-                const int st = i & 1, key0 = (kt_begin + i) * KEYS;
+                const int st = i & 1, key0 = v_tile * KEYS;
+                v_tile = next_tile(v_tile);
                 ptx::mbar_arrive_expect_tx(&v_full[st], TILE_BYTES);
                 ptx::tma_load_2d(smem + SMEM_V + st * TILE_BYTES, &tm_v, &v_full[st], h * D, key0);
                 ptx::tma_load_2d(smem + SMEM_V + st * TILE_BYTES + HALF_BYTES, &tm_v, &v_full[st], h * D + 64, key0);
@@ -237,10 +307,19 @@ tree_attn_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant
         }
     } else {
         // ================================================= softmax warps
+        int s_tile = kt_begin;
         for (int i = 0; i < n_it && ok; ++i) {
             const int st = i & 1;
             const uint32_t ph = (i >> 1) & 1;
-            const int key0 = (kt_begin + i) * KEYS + ch * 64;  // first key of this thread's 64 columns
+            const int key0 = s_tile * KEYS + ch * 64;  // first key of this thread's 64 columns
+            s_tile = next_tile(s_tile);
+            // block-sparse mode: this row's token may not see this 64-key block at all
+            bool blk_ok = true;
+            if (sparse) {
+                const int b = key0 >> 6;
+                blk_ok = b >= win_left ||
+                         (bm_row != nullptr && (b >> 6) < a.bm_words && ((bm_row[b >> 6] >> (b & 63)) & 1ull));
+            }
             // one polling lane per warp (the shuffle also converges it for the collective TMEM loads)
             if (!ptx::mbar_wait_warp(&s_bar[st], ph, abort_flag)) { ok = false; break; }
             ptx::tc_fence_after();
@@ -251,12 +330,12 @@ tree_attn_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant
             ptx::tmem_ld32(tmem_s, sc);
             ptx::tmem_ld32(tmem_s + 32, sc + 32);
             ptx::tmem_wait_ld();
-            const bool need_mask = (key0 + 64 > limit) || (key0 + 64 > mbeg) || (key0 < key_lo);
+            const bool need_mask = !blk_ok || (key0 + 64 > limit) || (key0 + 64 > mbeg) || (key0 < key_lo);
             if (need_mask) {
 #pragma unroll
                 for (int c = 0; c < 64; ++c) {
                     const int key = key0 + c;
-                    bool vis = key < limit && key >= key_lo;
+                    bool vis = blk_ok && key < limit && key >= key_lo;
                     if (key >= mbeg) vis = vis && ((mword >> (key - mbeg)) & 1ull);
                     if (!vis) sc[c] = 0xff800000u;  // -inf
                 }
@@ -484,6 +563,9 @@ void launch_tree_attention(const AttnPlan& p, cudaStream_t s) {
     a.n_valid = p.n_valid;
     a.mask = p.mask; a.mask_k = p.mask_k;
     a.window = p.window;
+    a.blockmask = p.blockmask; a.bm_words = p.bm_words; a.block_window = p.block_window;
+    CPM_REQUIRE(p.blockmask == nullptr || (p.bm_words >= 1 && p.bm_words <= 64 && p.block_window >= 1),
+                "attention: block mask needs 1..64 words per row and a local window of at least one block");
     a.scale_log2 = p.scale * 1.4426950408889634f;
     a.out = p.out; a.out_ld = p.out_ld;
     a.ws_o = p.ws_o; a.ws_ml = p.ws_ml;

@@ -176,6 +176,25 @@ int cpmcu_tree_attention(const void* q, int q_ld, const void* k_cache, const voi
                          int hq, int hkv, const int32_t* kv_len, int kv_len_add, const int32_t* n_valid,
                          const uint64_t* mask, int mask_k, int window, int splits, void* out, int out_ld);
 
+/* Block-sparse form of cpmcu_tree_attention for the InfLLM-v2 target layers.  reference:
+ * mha_fwd_kvcache with a blockmask, src/flash_attn/flash_api.hpp:292-392 and
+ * src/flash_attn/src/flash_blockmask.h.  blockmask: [hkv][tq][bm_words] bits over 64-key blocks;
+ * token t also sees every block >= ceil((t + kv_total - tq) / 64) - block_window. */
+int cpmcu_sparse_attention(const void* q, int q_ld, const void* k_cache, const void* v_cache, int budget, int tq,
+                           int hq, int hkv, const int32_t* kv_len, int kv_len_add, const uint64_t* mask, int mask_k,
+                           const uint64_t* blockmask, int bm_words, int block_window, int splits, void* out,
+                           int out_ld);
+
+/* InfLLM-v2 block selection of one layer.  reference: MiniCPM4KVCache::compress, mha_fwd_stage1,
+ * maxpooling_func, TopK::prefill, topk_to_uint64_func as called from MiniCPM4Attention::decode,
+ * src/model/minicpm4/minicpm4_attn.cuh:226-290.  L = *kv_len + kv_len_add accepted key rows.
+ * Outputs (device): c1_out [budget/16, hkv*128], c2_out [budget/64, hkv*128] (may be NULL),
+ * scores_out [hkv, tq, score_ld] (may be NULL), blockmask_out [hkv, tq, bm_words]. */
+int cpmcu_sparse_select(const void* q, int q_ld, int tq, int hq, int hkv, const void* k_cache, int budget,
+                        const int32_t* kv_len, int kv_len_add, int sink_window_size, int block_window_size,
+                        int sparse_topk_k, int sparse_switch, int apply_compress_lse, void* c1_out, void* c2_out,
+                        void* scores_out, int score_ld, uint64_t* blockmask_out, int bm_words);
+
 /* Times `iters` back-to-back tree-attention launches (split kernel + merge) with
  * CUDA events on the library's stream, rotating over 8 separate KV caches. */
 int cpmcu_bench_attention(int tq, int hq, int hkv, int kv_total, int splits, int with_mask, int iters,

@@ -19,6 +19,7 @@ import math
 import numpy as np
 import torch
 
+from . import sparse as osparse
 from . import tree as otree
 
 
@@ -100,8 +101,9 @@ def make_weights(cfg, seed, eagle=None, std=0.02, draft_from_last_layer=True, la
 
 
 class OracleModel:
-    def __init__(self, cfg, weights, eagle=None, eagle_weights=None, budget=1024, token_id_remap=None):
+    def __init__(self, cfg, weights, eagle=None, eagle_weights=None, budget=1024, token_id_remap=None, sparse=None):
         self.cfg, self.w = cfg, weights
+        self.sparse = sparse  # oracle.sparse.SparseConfig: InfLLM-v2 block selection in the target layers
         self.eagle, self.ew = eagle, eagle_weights
         self.budget = budget
         self.inv_freq = default_inv_freq(cfg.head_dim, cfg.rope_theta)
@@ -151,7 +153,7 @@ class OracleModel:
         out = torch.cat([a * cos - b * sin, a * sin + b * cos], dim=-1)
         return self.rnd(out).reshape(x.shape[0], nheads * d)
 
-    def attention(self, q, k_cache, v_cache, kv_total, tq_valid, mask=None, mask_k=0, window=0):
+    def attention(self, q, k_cache, v_cache, kv_total, tq_valid, mask=None, mask_k=0, window=0, block_vis=None):
         """Visibility per src/flash_attn/src/mask.h:182-222 with the causal bound of
         flash_api.hpp:318-320: key c visible to row t iff c < kv_total - tq + t + 1 and,
         for the last mask_k keys, bit (c - (kv_total - mask_k)) of mask[t]."""
@@ -184,7 +186,7 @@ class OracleModel:
         scale = 1.0 / math.sqrt(d)
         for h in range(cfg.hq):
             s = (qh[:, h, :] @ K[:, h // grp, :].t()) * scale
-            s = s.masked_fill(~vis, float("-inf"))
+            s = s.masked_fill(~(vis if block_vis is None else vis & block_vis[h // grp]), float("-inf"))
             p = torch.softmax(s, dim=-1)
             p = torch.nan_to_num(p, nan=0.0)
             out[:, h, :] = p @ V[:, h // grp, :]
@@ -192,7 +194,7 @@ class OracleModel:
 
     # ---------------------------------------------------------------- decoder layer
     def layer(self, prefix, w, x, pending, pending_scale, res_scale, pos, k_cache, v_cache, kv_row0, kv_total,
-              tq_valid, mask, mask_k, window, attn_norm=True):
+              tq_valid, mask, mask_k, window, attn_norm=True, select=False):
         """Layer::decode / prefill (src/model/layer.cuh:47-89), Attention (attn.cuh:135-234), GatedFFN (ffn.cuh:72-90).
         Returns (x, pending_delta): the residual stream after the attention add, and the FFN output."""
         cfg = self.cfg
@@ -208,7 +210,15 @@ class OracleModel:
         nv = tq_valid if tq_valid is not None else rows
         k_cache[kv_row0:kv_row0 + nv] = k[:nv]
         v_cache[kv_row0:kv_row0 + nv] = v[:nv]
-        a = self.attention(q, k_cache, v_cache, kv_total, nv, mask, mask_k, window)
+        block_vis = None
+        if select and self.sparse is not None:
+            # InfLLM-v2: kv_row0 is the layer's next_kv_length (rows accepted so far); the rows just appended
+            # take no part in the selection (minicpm4_attn.cuh:96-166, :226-290)
+            bm = osparse.select_blocks(self.sparse, q, k_cache, kv_row0, cfg.hq, cfg.hkv, cfg.head_dim, kv_total)
+            if bm is not None:
+                block_vis = osparse.block_visibility(bm, self.sparse.block_window_size, rows, kv_total)
+                self.trace.setdefault("blockmask", []).append(bm)
+        a = self.attention(q, k_cache, v_cache, kv_total, nv, mask, mask_k, window, block_vis)
         o = self.linear(a, w[prefix + "self_attn.o_proj.weight"])
         x = self.add(x, o, res_scale)
         normed = self.rms_norm(x, w[prefix + "post_attention_layernorm.weight"])
@@ -230,7 +240,8 @@ class OracleModel:
         pending = None
         for l in range(cfg.layers):
             x, pending = self.layer("model.layers.%d." % l, self.w, x, pending, cfg.scale_residual, cfg.scale_residual,
-                                    pos, self.k_cache[l], self.v_cache[l], kv_row0, kv_total, None, mask, mask_k, 0)
+                                    pos, self.k_cache[l], self.v_cache[l], kv_row0, kv_total, None, mask, mask_k, 0,
+                                    select=True)
         x = self.add(x, pending, cfg.scale_residual)
         return self.rms_norm(x, self.w["model.norm.weight"])
 
