@@ -39,6 +39,7 @@ _SIGNATURES = {
     "cpmcu_launches_per_step": (ctypes.c_long, []),
     "cpmcu_total_launches": (ctypes.c_long, []),
     "cpmcu_get_tree": (_c_int, [_c_void_p] * 6),
+    "cpmcu_capture_blockmasks": (_c_int, [_c_void_p]),
     "cpmcu_release": (None, []),
     "cpmcu_linear_bf16": (_c_int, [_c_void_p] * 4 + [_c_int] * 4),
     "cpmcu_linear_w4a16": (_c_int, [_c_void_p] * 4 + [_c_int] * 4),

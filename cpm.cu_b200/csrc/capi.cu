@@ -94,11 +94,36 @@ int cpmcu_init_minicpm4_model(float memory_limit, int vocab_size, int num_hidden
                               int head_dim, float rms_norm_eps, int torch_dtype, int chunk_length,
                               float scale_embed, float scale_lmhead, float scale_residual, int sink_window_size,
                               int block_window_size, int sparse_topk_k, int sparse_switch, int apply_compress_lse) {
-    (void)sink_window_size; (void)block_window_size; (void)sparse_topk_k; (void)apply_compress_lse;
-    if (sparse_switch < (1 << 30)) return not_built("InfLLM-v2 block-sparse attention (init_minicpm4_model with a reachable sparse_switch)");
-    return cpmcu_init_base_model(memory_limit, vocab_size, num_hidden_layers, hidden_size, intermediate_size,
-                                 num_attention_heads, num_key_value_heads, head_dim, rms_norm_eps, torch_dtype,
-                                 chunk_length, scale_embed, scale_lmhead, scale_residual);
+    return guarded([&] {
+        require_bf16(torch_dtype);
+        CPM_REQUIRE(sink_window_size >= 0 && block_window_size >= 1 && sparse_topk_k >= 1 && sparse_switch >= 0,
+                    "init_minicpm4_model: bad block-selection arguments");
+        CPM_REQUIRE(num_attention_heads / num_key_value_heads <= 16,
+                    "init_minicpm4_model: at most 16 query heads per KV head");
+        ModelConfig mc;
+        mc.memory_limit = memory_limit;
+        mc.vocab = vocab_size;
+        mc.layers = num_hidden_layers;
+        mc.hidden = hidden_size;
+        mc.inter = intermediate_size;
+        mc.hq = num_attention_heads;
+        mc.hkv = num_key_value_heads;
+        mc.head_dim = head_dim;
+        mc.eps = rms_norm_eps;
+        mc.chunk_length = chunk_length;
+        mc.scale_embed = scale_embed;
+        mc.scale_lmhead = scale_lmhead;
+        mc.scale_residual = scale_residual;
+        mc.sparse.enabled = true;
+        mc.sparse.sink_blocks = sink_window_size;
+        mc.sparse.window_blocks = block_window_size;
+        mc.sparse.topk = sparse_topk_k;
+        mc.sparse.sparse_switch = sparse_switch;
+        mc.sparse.compress_lse = apply_compress_lse != 0;
+        g_engine.reset();
+        g_engine = std::make_unique<Engine>(mc);
+        return 0;
+    });
 }
 
 int cpmcu_init_w4a16_gptq_marlin_base_model(float memory_limit, int vocab_size, int num_hidden_layers,
@@ -270,6 +295,14 @@ int cpmcu_get_tree(int32_t* ids, int32_t* pos, int32_t* parent, int32_t* gt, uin
         }
         CUDA_CHECK(cudaStreamSynchronize(s));
         return 0;
+    });
+}
+
+int cpmcu_capture_blockmasks(uint64_t* device_buf) {
+    return guarded([&] {
+        Engine& e = engine();
+        e.capture_blockmasks(device_buf);
+        return e.blockmask_words();
     });
 }
 

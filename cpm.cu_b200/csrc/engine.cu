@@ -212,6 +212,19 @@ void Engine::lay_out(Pool& p) {
         ekv_.k = take<bf16>(p, static_cast<size_t>(budget_) * kvd);
         ekv_.v = take<bf16>(p, static_cast<size_t>(budget_) * kvd);
     }
+    if (mc_.sparse.enabled) {
+        // compressed key caches per layer, and the scores / block masks of the layer being run
+        sp_.c1_layer_stride = static_cast<size_t>(budget_ / 16) * kvd;
+        sp_.c2_layer_stride = static_cast<size_t>(budget_ / 64) * kvd;
+        sp_.c1 = take<bf16>(p, sp_.c1_layer_stride * mc_.layers + 8);
+        sp_.c2 = mc_.sparse.compress_lse ? take<bf16>(p, sp_.c2_layer_stride * mc_.layers + 8) : nullptr;
+        sp_.done = take<int32_t>(p, 2);
+        sp_.score_ld = (budget_ / 16 + 127) / 128 * 128;
+        sp_.max_tokens = static_cast<int>(R);
+        sp_.scores = take<bf16>(p, static_cast<size_t>(mc_.hkv) * R * sp_.score_ld + 8);
+        sp_.bm_words = std::max(1, (budget_ / 64 + 63) / 64);
+        sp_.blockmask = take<uint64_t>(p, static_cast<size_t>(mc_.hkv) * R * sp_.bm_words);
+    }
 }
 
 int Engine::init_storage() {
@@ -226,7 +239,13 @@ int Engine::init_storage() {
     Pool count;
     lay_out(count);
     const size_t fixed = count.used + (1 << 20);
-    const size_t per_token = static_cast<size_t>(mc_.layers + (has_eagle_ ? 1 : 0)) * 2 * mc_.hkv * mc_.head_dim * 2;
+    size_t per_token = static_cast<size_t>(mc_.layers + (has_eagle_ ? 1 : 0)) * 2 * mc_.hkv * mc_.head_dim * 2;
+    if (mc_.sparse.enabled) {
+        // c1 + c2 rows per layer (1/16 + 1/64 of a key row), one score per 16 tokens and one mask bit per 64
+        // tokens for each of the hkv * max_rows_ (kv head, query) pairs
+        per_token += static_cast<size_t>(mc_.layers) * mc_.hkv * mc_.head_dim * 2 * 5 / 64 + 1;
+        per_token += static_cast<size_t>(mc_.hkv) * max_rows_ * 2 / 16 + static_cast<size_t>(mc_.hkv) * max_rows_ / 512 + 2;
+    }
     if (fixed + per_token * 256 > limit) {
         throw std::runtime_error("cpmcu_b200: memory_limit too small for the model (" + std::to_string(fixed >> 20) +
                                  " MiB needed before any KV cache)");
@@ -235,6 +254,7 @@ int Engine::init_storage() {
     const char* cap_env = getenv("CPMCU_MAX_TOKENS");
     const size_t cap = cap_env ? static_cast<size_t>(atoll(cap_env)) : (size_t(1) << 20);
     tokens = std::min(tokens, cap);
+    if (mc_.sparse.enabled) tokens = std::min<size_t>(tokens, 262144);  // 4096 selectable blocks, 2048 key tiles
     tokens = tokens / 128 * 128;
     budget_ = static_cast<int>(tokens);
     Pool measure;
@@ -426,7 +446,7 @@ ForwardPlans& Engine::target_plans(int rows) {
 // ------------------------------------------------------------------ forward pieces
 void Engine::layer_forward(LayerPlans& lp, const LayerWeights& w, const KVLayer& kv, const RowCtx& c, bf16* x,
                            const bf16* pending, float pending_scale, bool first_norm, float res_scale,
-                           cudaStream_t s) {
+                           cudaStream_t s, int sparse_layer) {
     const int H = mc_.hidden, rows = c.rows;
     if (first_norm) {
         if (pending) launch_add_rms_norm(x, pending, pending_scale, w.ln_attn, normed_, rows, H, mc_.eps, s);
@@ -444,12 +464,35 @@ void Engine::layer_forward(LayerPlans& lp, const LayerWeights& w, const KVLayer&
     lp.attn.mask = c.mask;
     lp.attn.mask_k = c.mask_k;
     lp.attn.window = c.window;
+    lp.attn.blockmask = nullptr;
+    if (sparse_layer >= 0) {
+        // InfLLM-v2: score the compressed keys of the accepted rows, pick blocks per (kv head, token)
+        launch_sparse_select(sp_, mc_.sparse, sparse_layer, qkv_, qkv_dim_, rows, mc_.hq, mc_.hkv, c.kv_len,
+                             c.kv_append_off, c.n_valid, s);
+        if (bm_capture_ != nullptr) {
+            const size_t per_layer = static_cast<size_t>(mc_.hkv) * max_rows_ * sp_.bm_words;
+            CUDA_CHECK(cudaMemcpyAsync(bm_capture_ + per_layer * sparse_layer, sp_.blockmask,
+                                       static_cast<size_t>(mc_.hkv) * rows * sp_.bm_words * sizeof(uint64_t),
+                                       cudaMemcpyDeviceToDevice, s));
+        }
+        lp.attn.blockmask = sp_.blockmask;
+        lp.attn.bm_words = sp_.bm_words;
+        lp.attn.block_window = mc_.sparse.window_blocks;
+    }
     launch_tree_attention(lp.attn, s);
     launch_linear(lp.o, s);
     launch_add_rms_norm(x, delta_, res_scale, w.ln_ffn, normed_, rows, H, mc_.eps, s);
     launch_linear(lp.gate_up, s);
     launch_silu_gate(gate_up_, act_, rows, mc_.inter, s);
     launch_linear(lp.down, s);
+}
+
+// Bring every layer's compressed key caches up to the accepted rows (all rows below
+// *kv_len + kv_append_off are final: written by earlier passes, compacted by the last fix-up).
+void Engine::sparse_prepare(const RowCtx& c, cudaStream_t s) {
+    if (!mc_.sparse.enabled) return;
+    launch_sparse_compress(sp_, d_cache_ptrs_, mc_.layers, mc_.hkv * mc_.head_dim, c.kv_len, c.kv_append_off,
+                           max_rows_ / 16 + 2, s);
 }
 
 void Engine::lm_head_rows(const bf16* x, int x_rows, int rows, bf16* logits_out, int ld, cudaStream_t s) {
@@ -469,9 +512,11 @@ void Engine::target_forward(ForwardPlans& fp, const RowCtx& c, const int32_t* id
                             bf16* logits_out, int logits_ld, cudaStream_t s) {
     const int H = mc_.hidden, rows = c.rows;
     launch_embedding(ids, embed_, x_, H, rows, H, mc_.scale_embed, s);
+    sparse_prepare(c, s);
     const bf16* pending = nullptr;
     for (int l = 0; l < mc_.layers; ++l) {
-        layer_forward(fp.layers[l], layers_[l], kv_[l], c, x_, pending, mc_.scale_residual, true, mc_.scale_residual, s);
+        layer_forward(fp.layers[l], layers_[l], kv_[l], c, x_, pending, mc_.scale_residual, true, mc_.scale_residual, s,
+                      mc_.sparse.enabled ? l : -1);
         pending = delta_;
     }
     launch_add_rms_norm(x_, pending, mc_.scale_residual, final_norm_, norm_out_, rows, H, mc_.eps, s);
@@ -778,9 +823,11 @@ void Engine::enqueue_step(bool first, cudaStream_t s) {
     const int V = mc_.vocab;
     // target forward; the LM-head plan is cached because its output buffer is engine-owned
     launch_embedding(t_ids_, embed_, x_, H, T, H, mc_.scale_embed, s);
+    sparse_prepare(c, s);
     const bf16* pending = nullptr;
     for (int l = 0; l < mc_.layers; ++l) {
-        layer_forward(fp.layers[l], layers_[l], kv_[l], c, x_, pending, mc_.scale_residual, true, mc_.scale_residual, s);
+        layer_forward(fp.layers[l], layers_[l], kv_[l], c, x_, pending, mc_.scale_residual, true, mc_.scale_residual, s,
+                      mc_.sparse.enabled ? l : -1);
         pending = delta_;
     }
     launch_add_rms_norm(x_, pending, mc_.scale_residual, final_norm_, norm_out_, T, H, mc_.eps, s);

@@ -13,6 +13,7 @@
 
 #include "common.cuh"
 #include "draft_tree.cuh"
+#include "sparse_select.cuh"
 
 struct ModelConfig {
     float memory_limit = 0.8f;
@@ -22,6 +23,7 @@ struct ModelConfig {
     float scale_embed = 1.f, scale_lmhead = 1.f, scale_residual = 1.f;
     bool w4a16 = false;  // target linears arrive as GPTQ-Marlin int4 + scales (embeddings / LM head stay bf16)
     int group_size = 128;
+    SparseConfig sparse;  // InfLLM-v2 block selection in the target layers (init_minicpm4_model)
 };
 
 struct EagleConfig {
@@ -103,6 +105,12 @@ public:
     const bf16* norm_out() const { return norm_out_; }
     const int32_t* tree_buffers(int which) const;
 
+    // ---- test hook: copy every target layer's block mask of each forward pass to `buf`
+    // ([layers][hkv][max_rows][bm_words], device memory owned by the caller; null stops it)
+    void capture_blockmasks(uint64_t* buf) { bm_capture_ = buf; }
+    int blockmask_words() const { return sp_.bm_words; }
+    int max_rows() const { return max_rows_; }
+
 private:
     // ---- memory
     struct Pool {
@@ -118,8 +126,11 @@ private:
     // ---- building blocks
     void build_layer_plans(LayerPlans& lp, const LayerWeights& w, const KVLayer& kv, int rows, int attn_splits);
     ForwardPlans& target_plans(int rows);
+    // sparse_layer >= 0: target layer with InfLLM-v2 block selection (index into the compressed caches)
     void layer_forward(LayerPlans& lp, const LayerWeights& w, const KVLayer& kv, const RowCtx& c, bf16* x,
-                       const bf16* pending, float pending_scale, bool first_norm, float res_scale, cudaStream_t s);
+                       const bf16* pending, float pending_scale, bool first_norm, float res_scale, cudaStream_t s,
+                       int sparse_layer = -1);
+    void sparse_prepare(const RowCtx& c, cudaStream_t s);
     void target_forward(ForwardPlans& fp, const RowCtx& c, const int32_t* ids, bool all_logits, bf16* logits_out,
                         int logits_ld, cudaStream_t s);
     void lm_head_rows(const bf16* x, int x_rows, int rows, bf16* logits_out, int ld, cudaStream_t s);
@@ -182,6 +193,8 @@ private:
     void* scan_ws_ = nullptr;
     void* argmax_ws_ = nullptr;
     bf16** d_cache_ptrs_ = nullptr;
+    uint64_t* bm_capture_ = nullptr;
+    SparseBuffers sp_;  // InfLLM-v2 compressed caches, scores and block masks (sparse target only)
     // device state words
     int32_t* st_ = nullptr;
     enum { S_L = 0, S_NPREV = 1, S_BASE = 2, S_LASTROW = 3, S_ACCEPT = 4, S_ZERO = 5, S_COUNT = 16 };

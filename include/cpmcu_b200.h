@@ -39,8 +39,10 @@ int cpmcu_init_base_model(float memory_limit, int vocab_size, int num_hidden_lay
                           float scale_lmhead, float scale_residual);
 
 /* reference: init_minicpm4_model, src/entry.cu:138-184 (InfLLM-v2 sparse target).
- * Accepted only when the sparse path can never trigger (sparse_switch beyond
- * the context budget); otherwise fails: block-sparse attention is not built. */
+ * Target layers keep compressed key caches (means of 32 keys every 16, of 128 every 64) and, once
+ * they cover sparse_switch tokens, every query token attends only to its sparse_topk_k best
+ * 64-token blocks, the first sink_window_size blocks and the last block_window_size blocks.
+ * At most 16 query heads per KV head and 262144 tokens of context. */
 int cpmcu_init_minicpm4_model(float memory_limit, int vocab_size, int num_hidden_layers, int hidden_size,
                               int intermediate_size, int num_attention_heads, int num_key_value_heads,
                               int head_dim, float rms_norm_eps, int torch_dtype, int chunk_length,
@@ -143,6 +145,11 @@ long cpmcu_launches_per_step(void);
 long cpmcu_total_launches(void);
 /* Copies the engine-owned tree of the last step to HOST arrays of 64 entries
  * (any pointer may be NULL). */
+/* Test hook (sparse target): from now on every forward pass also copies each target layer's block
+ * mask, [hkv][rows][words] packed per layer at stride hkv * max(chunk_length, 64) * words, into
+ * device_buf (caller-owned device memory; NULL stops it).  Returns words per mask row. */
+int cpmcu_capture_blockmasks(uint64_t* device_buf);
+
 int cpmcu_get_tree(int32_t* ids, int32_t* pos, int32_t* parent, int32_t* gt, uint64_t* mask, int32_t* state);
 /* Drops the current model (frees the device pool). */
 void cpmcu_release(void);

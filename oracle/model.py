@@ -120,6 +120,10 @@ class OracleModel:
                 self.remap = torch.as_tensor(np.asarray(token_id_remap), dtype=torch.long)
                 self.draft_head = weights["lm_head.weight"][self.remap]  # remap_copy_kernel, tree_drafter.cuh:79-85
         self.trace = {}
+        # tests may set this to a function (layer, own_mask) -> mask: the attention then uses the returned
+        # block mask instead of the oracle's own selection (both are kept in trace["blockmask_pairs"])
+        self.mask_override = None
+        self._layer_index = 0
 
     # ---------------------------------------------------------------- primitives
     def rnd(self, x):
@@ -216,8 +220,12 @@ class OracleModel:
             # take no part in the selection (minicpm4_attn.cuh:96-166, :226-290)
             bm = osparse.select_blocks(self.sparse, q, k_cache, kv_row0, cfg.hq, cfg.hkv, cfg.head_dim, kv_total)
             if bm is not None:
-                block_vis = osparse.block_visibility(bm, self.sparse.block_window_size, rows, kv_total)
                 self.trace.setdefault("blockmask", []).append(bm)
+                if self.mask_override is not None:
+                    theirs = self.mask_override(self._layer_index, bm)
+                    self.trace.setdefault("blockmask_pairs", []).append((bm, theirs))
+                    bm = theirs
+                block_vis = osparse.block_visibility(bm, self.sparse.block_window_size, rows, kv_total)
         a = self.attention(q, k_cache, v_cache, kv_total, nv, mask, mask_k, window, block_vis)
         o = self.linear(a, w[prefix + "self_attn.o_proj.weight"])
         x = self.add(x, o, res_scale)
@@ -239,6 +247,7 @@ class OracleModel:
         pos = torch.as_tensor(pos, dtype=torch.long)
         pending = None
         for l in range(cfg.layers):
+            self._layer_index = l
             x, pending = self.layer("model.layers.%d." % l, self.w, x, pending, cfg.scale_residual, cfg.scale_residual,
                                     pos, self.k_cache[l], self.v_cache[l], kv_row0, kv_total, None, mask, mask_k, 0,
                                     select=True)
@@ -265,6 +274,23 @@ class OracleModel:
             self.eagle_pos = torch.as_tensor(pos, dtype=torch.long)
             self.num_prev, self.num_history, self.first_draft = n, history, True
         return logits[0]
+
+    def prefill_chunked(self, ids, chunk):
+        """cpmcu/llm.py:225-261: the prompt goes through prefill in chunks of `chunk` tokens; with a drafter
+        the draft model's pass over a chunk is run when the next chunk (or the first draft) supplies the
+        embedding of the token that follows it (src/model/eagle.cuh:405-434)."""
+        logits = None
+        for start in range(0, len(ids), chunk):
+            logits = self.prefill_chunk(list(ids[start:start + chunk]), start)
+        return logits
+
+    def prefill_chunk(self, part, start):
+        """One chunk of prefill_chunked: rows [start, start + len(part))."""
+        if self.eagle is not None and start > 0:
+            self.prev_embed[self.num_prev - 1] = self.embed([part[0]])[0]
+            self._draft_core(self.prev_embed, self.prev_hidden, self.eagle_pos, self.num_history,
+                             self.num_history + self.num_prev, None, None, 0)
+        return self.prefill(part, history=start)
 
     def decode(self, ids, pos, cache_length, mask):
         """Tree verify forward (cpmcu/llm.py:263-283): KV rows written at [L, L+T)."""
@@ -341,11 +367,11 @@ class OracleModel:
         return n, out, path
 
     # ---------------------------------------------------------------- generate loops
-    def generate_spec(self, prompt, num_tokens):
+    def generate_spec(self, prompt, num_tokens, chunk=None):
         """LLM_with_tree_drafter.generate, non-stream greedy path
         (cpmcu/speculative/tree_drafter.py:215-252).  Returns (tokens, accept_lengths, steps)."""
         P = len(prompt)
-        logits = self.prefill(prompt)
+        logits = self.prefill(prompt) if chunk is None else self.prefill_chunked(prompt, chunk)
         root = int(torch.argmax(logits))
         tokens = [root]
         accept, steps = [], []

@@ -29,16 +29,27 @@ def hf_config(cfg):
 
 
 def build_pair(cfg, eagle, seed=0, chunk_length=256, layer_scale=0.6, fc_mode="embed", fc_gain=200.0,
-               token_id_remap=None, fused_step=True, budget=1024):
-    """Returns (oracle_model, library_model) holding identical weights."""
+               token_id_remap=None, fused_step=True, budget=1024, sparse=None, qk_gain=1.0):
+    """Returns (oracle_model, library_model) holding identical weights.  sparse: oracle.sparse.SparseConfig
+    for an InfLLM-v2 target (the reference's apply_sparse=True)."""
     from cpmcu.speculative.eagle import LLM_with_eagle
     w, ew = make_weights(cfg, seed, eagle, layer_scale=layer_scale, fc_mode=fc_mode, fc_gain=fc_gain)
-    oracle = OracleModel(cfg, w, eagle, ew, budget=budget, token_id_remap=token_id_remap)
+    if qk_gain != 1.0:
+        # peaked attention: with flat attention every block scores alike and block selection is a coin toss
+        for name in w:
+            if "q_proj" in name or "k_proj" in name:
+                w[name] = (w[name] * qk_gain).to(torch.bfloat16).float()
+    oracle = OracleModel(cfg, w, eagle, ew, budget=budget, token_id_remap=token_id_remap, sparse=sparse)
+    sparse_kw = {}
+    if sparse is not None:
+        sparse_kw = dict(apply_sparse=True, sink_window_size=sparse.sink_window_size,
+                         block_window_size=sparse.block_window_size, sparse_topk_k=sparse.sparse_topk_k,
+                         sparse_switch=sparse.sparse_switch, apply_compress_lse=sparse.apply_compress_lse)
     llm = LLM_with_eagle(None, None, num_iter=eagle.num_iter, topk_per_iter=eagle.topk, tree_size=eagle.tree_size,
                          eagle_window_size=eagle.window, frspec_vocab_size=eagle.frspec_vocab,
                          use_input_norm=eagle.use_input_norm, use_attn_norm=eagle.use_attn_norm,
                          eagle_config={"num_hidden_layers": 1}, config=hf_config(cfg), dtype=torch.bfloat16,
-                         chunk_length=chunk_length, memory_limit=0.5, fused_step=fused_step)
+                         chunk_length=chunk_length, memory_limit=0.5, fused_step=fused_step, **sparse_kw)
     import os
     os.environ.setdefault("CPMCU_MAX_TOKENS", "4096")
     llm.init_storage()
