@@ -96,7 +96,11 @@ class ClockSampler(threading.Thread):
 
 
 # ---------------------------------------------------------------------------- ours
-def build_model(device_index, seed=1, w4a16=False):
+LONG_PROMPT_LEN = 32768   # config 5
+LONG_CHUNK = 2048         # the reference's default chunk_length: the first chunk is dense, later ones select blocks
+
+
+def build_model(device_index, seed=1, w4a16=False, sparse=False):
     """Random-init config-2 model (config 4 with w4a16: the target's linears as random GPTQ-Marlin int4
     tensors), generated on the GPU tensor by tensor and loaded through the reference-shaped Python classes
     (C.load_model accepts device pointers)."""
@@ -106,7 +110,7 @@ def build_model(device_index, seed=1, w4a16=False):
     from cpmcu.speculative.eagle import LLM_with_eagle
     from cpmcu.speculative.eagle_base_quant.eagle_base_w4a16_marlin_gptq import W4A16GPTQMarlinLLM_with_eagle
     torch.cuda.set_device(device_index)
-    os.environ.setdefault("CPMCU_MAX_TOKENS", "8192")
+    os.environ.setdefault("CPMCU_MAX_TOKENS", "40960" if sparse else "8192")
     hf = types.SimpleNamespace(vocab_size=CFG["vocab"], num_hidden_layers=CFG["layers"], hidden_size=CFG["hidden"],
                                intermediate_size=CFG["inter"], num_attention_heads=CFG["hq"],
                                num_key_value_heads=CFG["hkv"], head_dim=CFG["head_dim"], rms_norm_eps=CFG["eps"],
@@ -114,9 +118,16 @@ def build_model(device_index, seed=1, w4a16=False):
     if w4a16:
         hf.quantization_config = {"group_size": 128, "bits": 4}
     cls = W4A16GPTQMarlinLLM_with_eagle if w4a16 else LLM_with_eagle
+    extra = {}
+    if sparse:
+        # config 5: InfLLM-v2 target (block 64, top-64 blocks + 1 initial block + local window of 2048 tokens),
+        # draft layer with a sliding window of 1024 tokens
+        extra = dict(apply_sparse=True, sink_window_size=1, block_window_size=32, sparse_topk_k=64, sparse_switch=8192,
+                     apply_compress_lse=True, eagle_window_size=1024)
     llm = cls(None, None, num_iter=TREE["num_iter"], topk_per_iter=TREE["topk"],
               tree_size=TREE["tree_size"], eagle_config={"num_hidden_layers": 1}, config=hf,
-              dtype=torch.bfloat16, chunk_length=PROMPT_LEN, memory_limit=0.8, fused_step=True)
+              dtype=torch.bfloat16, chunk_length=LONG_CHUNK if sparse else PROMPT_LEN, memory_limit=0.8,
+              fused_step=True, **extra)
     llm.init_storage()
     g = torch.Generator(device="cuda").manual_seed(seed)
     H, I, d = CFG["hidden"], CFG["inter"], CFG["head_dim"]
@@ -176,19 +187,21 @@ def run_ours(args):
         dist.init_process_group("nccl", device_id=torch.device("cuda", local))
     C.load()  # fails loudly if the CUDA library is missing
     w4 = args.workload == "config4"
+    long_ctx = args.workload == "config5"
+    prompt_len = LONG_PROMPT_LEN if long_ctx else PROMPT_LEN
     import contextlib
     with contextlib.redirect_stdout(sys.stderr):  # keep stdout for the single JSON line
-        llm = build_model(local, seed=1, w4a16=w4)
+        llm = build_model(local, seed=1, w4a16=w4, sparse=long_ctx)
     from cpmcu.replicas import replica_seed
-    prompt = torch.tensor(zipf_prompt(PROMPT_LEN, CFG["vocab"], replica_seed(100, rank)), device="cuda")
-    pos = torch.arange(PROMPT_LEN, dtype=torch.int32, device="cuda")
+    prompt = torch.tensor(zipf_prompt(prompt_len, CFG["vocab"], replica_seed(100, rank)), device="cuda")
+    pos = torch.arange(prompt_len, dtype=torch.int32, device="cuda")
     torch.cuda.synchronize()
     t0 = time.time()
     logits = llm.prefill(prompt, pos)
     torch.cuda.synchronize()
     prefill_s = time.time() - t0
     root = int(logits[0].argmax())
-    C.begin_generation(PROMPT_LEN, root)
+    C.begin_generation(prompt_len, root)
     for _ in range(args.warmup):
         C.spec_step(16)
 
@@ -215,11 +228,12 @@ def run_ours(args):
     launches = C.launches_per_step()
 
     # per-class device time of a few uncaptured steps (CUDA events around every launch)
-    lin_ms, att_ms, lin_n, prof_total = [], [], 0, []
+    lin_ms, att_ms, sel_ms, lin_n, prof_total = [], [], [], 0, []
     for _ in range(3):
         cls, total = C.profile_step()
         lin_ms.append(cls["linear"][0])
         att_ms.append(cls["attention"][0])
+        sel_ms.append(cls["selection"][0])
         lin_n = cls["linear"][1]
         prof_total.append(total)
 
@@ -246,8 +260,12 @@ def run_ours(args):
             "config": {"workload": ("configs[3]: config-2 architecture with W4A16 GPTQ-Marlin target linears (random "
                                     "int4 tensors), bf16 embeddings / LM head / EAGLE draft, tree 60, "
                                     if w4 else
+                                    "configs[4]: config-2 architecture with InfLLM-v2 block-sparse target attention "
+                                    "(block 64, top-64 + 1 initial block + 2048-token window), draft window 1024, "
+                                    "chunked prefill (2048), tree 60, "
+                                    if long_ctx else
                                     "configs[1]: 8B-shaped bf16 target + 1-layer EAGLE, tree 60 (6 iters x top-10), ")
-                                   + "4096-token Zipf(1.1) prompt, batch 1, greedy",
+                                   + "%d-token Zipf(1.1) prompt, batch 1, greedy" % prompt_len,
                        "replicas": world,
                        "l2": "inputs larger than L2 (%.1f GB of weights streamed per step)" % ((tgt_b + draft_b) / 1e9)},
             "e2e": {"value": tokens_all / wall_max, "unit": UNIT, "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 128},
@@ -255,9 +273,10 @@ def run_ours(args):
             "launches_per_step": int(launches),
             "mean_accept_length": statistics.mean(accept),
             "step_device_ms_median": statistics.median(dev_ms),
-            "prefill_tokens_per_s": PROMPT_LEN / prefill_s,
+            "prefill_tokens_per_s": prompt_len / prefill_s,
             "profile_eager_step_ms": {"total": statistics.median(prof_total), "linear": statistics.median(lin_ms),
-                                      "attention": statistics.median(att_ms), "linear_launches": lin_n},
+                                      "attention": statistics.median(att_ms),
+                                      "block_selection": statistics.median(sel_ms), "linear_launches": lin_n},
             "roofline": {"bound": "hbm", "kernel": "linear_umma_kernel%s (all %d launches of a step)"
                                                    % (" + linear_w4_umma_kernel" if w4 else "", lin_n),
                          "achieved": achieved, "peak": peak, "unit": "GB/s", "frac": achieved / peak,
@@ -374,8 +393,9 @@ def main():
     ap.add_argument("--warmup", type=int, default=5)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--no-cpu-baseline", action="store_true")
-    ap.add_argument("--workload", default="config2", choices=["config2", "config4"],
-                    help="config2 = the headline bf16 workload; config4 = the same with a W4A16 GPTQ-Marlin target")
+    ap.add_argument("--workload", default="config2", choices=["config2", "config4", "config5"],
+                    help="config2 = the headline bf16 workload; config4 = the same with a W4A16 GPTQ-Marlin target; "
+                         "config5 = 32768-token prompt, InfLLM-v2 sparse target, draft window 1024")
     args = ap.parse_args()
     if args.warmup < 3:
         args.warmup = 3

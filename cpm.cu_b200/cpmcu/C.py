@@ -212,7 +212,7 @@ def profile_step():
     total = ctypes.c_float()
     call("cpmcu_profile_step", ctypes.cast(ms, _c_void_p), ctypes.cast(cnt, _c_void_p),
          ctypes.cast(ctypes.pointer(total), _c_void_p))
-    return {"linear": (ms[0], cnt[0]), "attention": (ms[1], cnt[1])}, total.value
+    return {"linear": (ms[0], cnt[0]), "attention": (ms[1], cnt[1]), "selection": (ms[2], cnt[2])}, total.value
 
 
 def last_step_ms():

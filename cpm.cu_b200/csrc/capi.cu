@@ -464,9 +464,13 @@ int cpmcu_sparse_select(const void* q, int q_ld, int tq, int hq, int hkv, const 
         CPM_REQUIRE(budget % 64 == 0 && score_ld >= (budget / 16 + 127) / 128 * 128 && score_ld % 8 == 0,
                     "sparse_select: score rows must hold budget / 16 entries rounded up to 128");
         SparseBuffers b;
-        DeviceBuf c1(static_cast<size_t>(budget / 16) * kv_dim * 2), c2(static_cast<size_t>(budget / 64) * kv_dim * 2);
+        // + 16 rows: the scoring kernels read whole 16-key fragments
+        DeviceBuf c1(static_cast<size_t>(budget / 16 + 16) * kv_dim * 2), c2(static_cast<size_t>(budget / 64 + 16) * kv_dim * 2);
+        CUDA_CHECK(cudaMemsetAsync(c1.p, 0, static_cast<size_t>(budget / 16 + 16) * kv_dim * 2, s));
+        CUDA_CHECK(cudaMemsetAsync(c2.p, 0, static_cast<size_t>(budget / 64 + 16) * kv_dim * 2, s));
         DeviceBuf done(8), scores(static_cast<size_t>(hkv) * tq * score_ld * 2);
         DeviceBuf bm(static_cast<size_t>(hkv) * tq * bm_words * 8), ptrs(2 * sizeof(void*));
+        DeviceBuf lse(static_cast<size_t>(hkv) * tq * 16 * (score_ld / 128) * 8);
         CUDA_CHECK(cudaMemsetAsync(done.p, 0, 8, s));
         CUDA_CHECK(cudaMemsetAsync(scores.p, 0, static_cast<size_t>(hkv) * tq * score_ld * 2, s));
         const void* host_ptrs[2] = {k_cache, nullptr};
@@ -475,6 +479,7 @@ int cpmcu_sparse_select(const void* q, int q_ld, int tq, int hq, int hkv, const 
         b.c2 = apply_compress_lse ? static_cast<bf16*>(c2.p) : nullptr;
         b.done = static_cast<int32_t*>(done.p);
         b.scores = static_cast<bf16*>(scores.p);
+        b.lse = static_cast<float2*>(lse.p);
         b.score_ld = score_ld;
         b.blockmask = static_cast<uint64_t*>(bm.p);
         b.bm_words = bm_words;

@@ -216,12 +216,14 @@ void Engine::lay_out(Pool& p) {
         // compressed key caches per layer, and the scores / block masks of the layer being run
         sp_.c1_layer_stride = static_cast<size_t>(budget_ / 16) * kvd;
         sp_.c2_layer_stride = static_cast<size_t>(budget_ / 64) * kvd;
-        sp_.c1 = take<bf16>(p, sp_.c1_layer_stride * mc_.layers + 8);
-        sp_.c2 = mc_.sparse.compress_lse ? take<bf16>(p, sp_.c2_layer_stride * mc_.layers + 8) : nullptr;
+        // + 16 rows: the scoring kernels read whole 16-key fragments
+        sp_.c1 = take<bf16>(p, sp_.c1_layer_stride * mc_.layers + static_cast<size_t>(16) * kvd);
+        sp_.c2 = mc_.sparse.compress_lse ? take<bf16>(p, sp_.c2_layer_stride * mc_.layers + static_cast<size_t>(16) * kvd) : nullptr;
         sp_.done = take<int32_t>(p, 2);
         sp_.score_ld = (budget_ / 16 + 127) / 128 * 128;
         sp_.max_tokens = static_cast<int>(R);
         sp_.scores = take<bf16>(p, static_cast<size_t>(mc_.hkv) * R * sp_.score_ld + 8);
+        sp_.lse = reinterpret_cast<float2*>(p.take(static_cast<size_t>(mc_.hkv) * R * 16 * (sp_.score_ld / 128) * sizeof(float2)));
         sp_.bm_words = std::max(1, (budget_ / 64 + 63) / 64);
         sp_.blockmask = take<uint64_t>(p, static_cast<size_t>(mc_.hkv) * R * sp_.bm_words);
     }

@@ -12,6 +12,8 @@
 // (the reference keeps next_kv_length, c1_len, c2_len on the host), so the kernels can sit inside a
 // captured step.  When selection is not active (compressed length below sparse_switch) the mask
 // kernel writes all-ones masks and the attention kernel visits every block.
+#include <mma.h>
+
 #include "common.cuh"
 #include "sparse_select.cuh"
 
@@ -63,10 +65,14 @@ __global__ void sparse_commit_kernel(const int32_t* __restrict__ kv_len, int kv_
     done[1] = compressed_len(L, C2_STRIDE);
 }
 
-// ---- stage 1: for query token t and kv head g (grid (T, hkv), 256 threads): per head the max and
-// exp-sum of q.k over the LSE keys, then sum over the group's heads of exp(q.k1 - max) / sum for every
-// c1 key.  Thread (key lane kk = tid & 63, head set hs = tid >> 6) handles heads hs, hs + 4, ...
-constexpr int S1_THREADS = 256, S1_KEYS = 64, S1_MAXGRP = 16, S1_HPT = S1_MAXGRP / 4;
+// ---- stage 1.  Scores are a small GEMM (tokens x heads against a few thousand compressed keys, 0.6 GFLOP
+// per layer at 32k context) that is latency- and L2-bound, not tensor-bound: warp-level mma (wmma, 16 x 16 x 16
+// bf16) with the 16 heads of a KV group as the M = 16 fragment is enough and keeps the kernel short.
+//   lse kernel    grid (ceil(T / 8), hkv, key chunks of 128): per (token, head, chunk) the max and exp-sum of
+//                 q.k over the LSE keys; the score kernel merges the chunks
+//   score kernel  grid (ceil(T / 8), hkv, key chunks of 128): exp(q.k1 - max) / sum, summed over the group's
+//                 heads, one 16-key fragment per warp
+constexpr int S1_THREADS = 256, S1_TOK = 8, S1_MAXGRP = 16, S1_QLD = 128 + 8;
 
 struct Stage1Args {
     const bf16* q;       // token t, head h at q + t * q_ld + h * 128
@@ -79,110 +85,174 @@ struct Stage1Args {
     const int32_t* n_valid;
     int sparse_switch, compress_lse;
     float scale_log2;
+    float2* lse;         // [hkv][T][16][lse_chunks]: (max, exp-sum) of q.k per token, head and 128-key chunk of the LSE keys
+    int lse_chunks;
     bf16* scores;        // [hkv][T][score_ld]
     int score_ld, T;
 };
 
-__device__ __forceinline__ void s1_dots(const bf16* __restrict__ ktile, const float* __restrict__ q_s, int kk, int hs, int grp,
-                                        float acc[S1_HPT]) {
+// Q rows of up to 8 tokens x 16 heads of KV group g as bf16 [8][16][S1_QLD] (zero rows beyond grp / T).
+__device__ __forceinline__ void s1_load_q(const Stage1Args& a, int t0, int g, int t_end, bf16* q_s) {
+    for (int i = threadIdx.x; i < S1_TOK * S1_MAXGRP * 16; i += S1_THREADS) {
+        const int c = (i & 15) * 8, h = (i >> 4) & 15, tt = i >> 8;
+        uint4 v = make_uint4(0, 0, 0, 0);
+        if (h < a.grp && t0 + tt < t_end) {
+            v = *reinterpret_cast<const uint4*>(a.q + static_cast<size_t>(t0 + tt) * a.q_ld + (g * a.grp + h) * 128 + c);
+        }
+        *reinterpret_cast<uint4*>(q_s + (tt * S1_MAXGRP + h) * S1_QLD + c) = v;
+    }
+}
+
+using KeyFrag = nvcuda::wmma::fragment<nvcuda::wmma::matrix_b, 16, 16, 16, __nv_bfloat16, nvcuda::wmma::col_major>;
+
+// The 16 keys starting at `keys` (row stride kv_dim) as eight B fragments: loaded once per key fragment,
+// all eight loads in flight together, and reused for every token.
+__device__ __forceinline__ void s1_load_keys(const bf16* keys, int kv_dim, KeyFrag fb[8]) {
 #pragma unroll
-    for (int j = 0; j < S1_HPT; ++j) acc[j] = 0.f;
-    const bf16* krow = ktile + kk * (128 + 8);
-#pragma unroll 4
-    for (int d = 0; d < 128; d += 2) {
-        const __nv_bfloat162 kv = *reinterpret_cast<const __nv_bfloat162*>(krow + d);
-        const float k0 = __low2float(kv), k1 = __high2float(kv);
+    for (int k = 0; k < 8; ++k) nvcuda::wmma::load_matrix_sync(fb[k], keys + k * 16, kv_dim);
+}
+
+// out[16 heads][16 keys] = Q(tt) K(frag)^T.
+__device__ __forceinline__ void s1_frag_scores(const bf16* q_tok, const KeyFrag fb[8], float* out /*[16][16]*/) {
+    using namespace nvcuda;
+    wmma::fragment<wmma::accumulator, 16, 16, 16, float> acc;
+    wmma::fill_fragment(acc, 0.f);
 #pragma unroll
-        for (int j = 0; j < S1_HPT; ++j) {
-            const int h = hs + 4 * j;
-            if (h < grp) acc[j] = fmaf(k1, q_s[h * 128 + d + 1], fmaf(k0, q_s[h * 128 + d], acc[j]));
+    for (int k = 0; k < 8; ++k) {
+        wmma::fragment<wmma::matrix_a, 16, 16, 16, __nv_bfloat16, wmma::row_major> fa;
+        wmma::load_matrix_sync(fa, q_tok + k * 16, S1_QLD);
+        wmma::mma_sync(acc, fa, fb[k], acc);
+    }
+    wmma::store_matrix_sync(out, acc, 16, wmma::mem_row_major);
+    __syncwarp();
+}
+
+__global__ void __launch_bounds__(S1_THREADS) sparse_stage1_lse_kernel(const Stage1Args a) {
+    grid_dependency_sync();
+    __shared__ __align__(32) bf16 q_s[S1_TOK * S1_MAXGRP * S1_QLD];
+    __shared__ __align__(32) float frag[S1_THREADS / 32][256];
+    // after the key loop the fragment buffers hold the per-warp (max, sum) of every (token, head)
+    float (*red_m)[S1_TOK * S1_MAXGRP] = reinterpret_cast<float (*)[S1_TOK * S1_MAXGRP]>(&frag[0][0]);
+    float (*red_s)[S1_TOK * S1_MAXGRP] = reinterpret_cast<float (*)[S1_TOK * S1_MAXGRP]>(&frag[S1_THREADS / 64][0]);
+    const int t0 = blockIdx.x * S1_TOK, g = blockIdx.y;
+    const int L = *a.kv_len + a.kv_add;
+    if (!selection_active(L, a.sparse_switch, a.compress_lse)) return;
+    const int t_end = (a.n_valid != nullptr) ? min(*a.n_valid, a.T) : a.T;
+    if (t0 >= t_end) return;
+    const int nl = compressed_len(L, a.lse_stride);
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    s1_load_q(a, t0, g, t_end, q_s);
+    __syncthreads();
+    // lane: head h = lane & 15, keys (lane >> 4) * 8 .. + 7 of the fragment
+    const int h = lane & 15, kh = lane >> 4;
+    float m[S1_TOK], s[S1_TOK];
+#pragma unroll
+    for (int tt = 0; tt < S1_TOK; ++tt) { m[tt] = -INFINITY; s[tt] = 0.f; }
+    if (blockIdx.z * 128 >= nl) return;
+    const int f = blockIdx.z * (S1_THREADS / 32) + warp;  // one 16-key fragment per warp
+    if (f * 16 < nl) {
+        KeyFrag fb[8];
+        s1_load_keys(a.c_lse + static_cast<size_t>(f) * 16 * a.kv_dim + g * 128, a.kv_dim, fb);
+#pragma unroll
+        for (int tt = 0; tt < S1_TOK; ++tt) {
+            s1_frag_scores(q_s + tt * S1_MAXGRP * S1_QLD, fb, frag[warp]);
+            float mx = m[tt];
+#pragma unroll
+            for (int j = 0; j < 8; ++j) {
+                if (f * 16 + kh * 8 + j < nl) mx = fmaxf(mx, frag[warp][h * 16 + kh * 8 + j]);
+            }
+            float sum = (mx == -INFINITY) ? 0.f : s[tt] * exp2f((m[tt] - mx) * a.scale_log2);
+#pragma unroll
+            for (int j = 0; j < 8; ++j) {
+                if (f * 16 + kh * 8 + j < nl) sum += exp2f((frag[warp][h * 16 + kh * 8 + j] - mx) * a.scale_log2);
+            }
+            m[tt] = mx;
+            s[tt] = sum;
+            __syncwarp();  // frag[warp] is overwritten by the next token
+        }
+    }
+    __syncthreads();  // every warp is done with its fragment buffer
+    // merge the two key halves of a head (lanes h and h + 16), then the eight warps
+#pragma unroll
+    for (int tt = 0; tt < S1_TOK; ++tt) {
+        const float om = __shfl_xor_sync(0xffffffffu, m[tt], 16), os = __shfl_xor_sync(0xffffffffu, s[tt], 16);
+        const float mx = fmaxf(m[tt], om);
+        const float sum = (mx == -INFINITY) ? 0.f
+                                            : (m[tt] == -INFINITY ? 0.f : s[tt] * exp2f((m[tt] - mx) * a.scale_log2)) +
+                                                  (om == -INFINITY ? 0.f : os * exp2f((om - mx) * a.scale_log2));
+        if (kh == 0) { red_m[warp][tt * S1_MAXGRP + h] = mx; red_s[warp][tt * S1_MAXGRP + h] = sum; }
+    }
+    __syncthreads();
+    if (threadIdx.x < S1_TOK * S1_MAXGRP) {
+        const int tt = threadIdx.x >> 4, hh = threadIdx.x & 15;
+        float mx = -INFINITY;
+        const int e = tt * S1_MAXGRP + hh;
+        for (int w = 0; w < S1_THREADS / 32; ++w) mx = fmaxf(mx, red_m[w][e]);
+        float sum = 0.f;
+        for (int w = 0; w < S1_THREADS / 32; ++w) {
+            if (red_m[w][e] != -INFINITY) sum += red_s[w][e] * exp2f((red_m[w][e] - mx) * a.scale_log2);
+        }
+        if (t0 + tt < t_end) {
+            a.lse[((static_cast<size_t>(g) * a.T + t0 + tt) * S1_MAXGRP + hh) * a.lse_chunks + blockIdx.z] = make_float2(mx, sum);
         }
     }
 }
 
-__global__ void __launch_bounds__(S1_THREADS) sparse_stage1_kernel(const Stage1Args a) {
+__global__ void __launch_bounds__(S1_THREADS) sparse_stage1_score_kernel(const Stage1Args a) {
     grid_dependency_sync();
-    __shared__ float q_s[S1_MAXGRP * 128];
-    __shared__ __align__(16) bf16 ktile[S1_KEYS * (128 + 8)];
-    __shared__ float red_m[S1_MAXGRP][S1_KEYS], red_s[S1_MAXGRP][S1_KEYS];
-    __shared__ float head_m[S1_MAXGRP], head_inv[S1_MAXGRP];
-    __shared__ float part[4][S1_KEYS];
-    const int t = blockIdx.x, g = blockIdx.y;
+    __shared__ __align__(32) bf16 q_s[S1_TOK * S1_MAXGRP * S1_QLD];
+    __shared__ __align__(32) float frag[S1_THREADS / 32][256];
+    __shared__ float2 lse_s[S1_TOK][S1_MAXGRP];
+    const int t0 = blockIdx.x * S1_TOK, g = blockIdx.y;
     const int L = *a.kv_len + a.kv_add;
     if (!selection_active(L, a.sparse_switch, a.compress_lse)) return;
-    if (a.n_valid != nullptr && t >= *a.n_valid) return;
+    const int t_end = (a.n_valid != nullptr) ? min(*a.n_valid, a.T) : a.T;
+    if (t0 >= t_end) return;
     const int n1 = compressed_len(L, C1_STRIDE);
-    const int nl = compressed_len(L, a.lse_stride);
-    const int tid = threadIdx.x, kk = tid & 63, hs = tid >> 6;
-    for (int i = tid; i < a.grp * 128; i += S1_THREADS) {
-        q_s[i] = __bfloat162float(a.q[static_cast<size_t>(t) * a.q_ld + (g * a.grp + i / 128) * 128 + (i & 127)]);
-    }
-    auto load_tile = [&](const bf16* base, int k0, int n) {
-        __syncthreads();  // previous tile fully consumed
-        for (int i = tid; i < S1_KEYS * 16; i += S1_THREADS) {
-            const int r = i >> 4, c = (i & 15) * 8;
-            uint4 v = make_uint4(0, 0, 0, 0);
-            if (k0 + r < n) v = *reinterpret_cast<const uint4*>(base + static_cast<size_t>(k0 + r) * a.kv_dim + g * 128 + c);
-            *reinterpret_cast<uint4*>(ktile + r * (128 + 8) + c) = v;
-        }
-        __syncthreads();
-    };
-    // pass 1: running max / exp-sum per head over the LSE keys (each thread: its key lane, its heads)
-    float m[S1_HPT], s[S1_HPT];
-#pragma unroll
-    for (int j = 0; j < S1_HPT; ++j) { m[j] = -INFINITY; s[j] = 0.f; }
-    for (int k0 = 0; k0 < nl; k0 += S1_KEYS) {
-        load_tile(a.c_lse, k0, nl);
-        if (k0 + kk < nl) {
-            float acc[S1_HPT];
-            s1_dots(ktile, q_s, kk, hs, a.grp, acc);
-#pragma unroll
-            for (int j = 0; j < S1_HPT; ++j) {
-                const float mn = fmaxf(m[j], acc[j]);
-                s[j] = s[j] * exp2f((m[j] - mn) * a.scale_log2) + exp2f((acc[j] - mn) * a.scale_log2);
-                m[j] = mn;
-            }
-        }
-    }
-#pragma unroll
-    for (int j = 0; j < S1_HPT; ++j) {
-        const int h = hs + 4 * j;
-        if (h < a.grp) { red_m[h][kk] = m[j]; red_s[h][kk] = s[j]; }
-    }
-    __syncthreads();
-    if (tid < a.grp) {
-        float mx = -INFINITY;
-        for (int i = 0; i < S1_KEYS; ++i) mx = fmaxf(mx, red_m[tid][i]);
-        float sum = 0.f;
-        for (int i = 0; i < S1_KEYS; ++i) {
-            if (red_m[tid][i] != -INFINITY) sum += red_s[tid][i] * exp2f((red_m[tid][i] - mx) * a.scale_log2);
-        }
-        head_m[tid] = (mx == -INFINITY) ? 0.f : mx;
-        head_inv[tid] = 1.f / sum;
-    }
-    __syncthreads();
-    // pass 2: normalised probabilities over the c1 keys, summed over the group's heads
-    bf16* out = a.scores + (static_cast<size_t>(g) * a.T + t) * a.score_ld;
     const int k_round = (n1 + 127) / 128 * 128;
-    for (int k0 = 0; k0 < k_round; k0 += S1_KEYS) {
-        float mine = 0.f;
-        if (k0 < n1) {
-            load_tile(a.c1, k0, n1);
-            if (k0 + kk < n1) {
-                float acc[S1_HPT];
-                s1_dots(ktile, q_s, kk, hs, a.grp, acc);
-#pragma unroll
-                for (int j = 0; j < S1_HPT; ++j) {
-                    const int h = hs + 4 * j;
-                    if (h < a.grp) mine += exp2f((acc[j] - head_m[h]) * a.scale_log2) * head_inv[h];
-                }
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int key0 = (blockIdx.z * (S1_THREADS / 32) + warp) * 16;  // this warp's 16 keys
+    if (blockIdx.z * 128 >= k_round) return;
+    s1_load_q(a, t0, g, t_end, q_s);
+    if (threadIdx.x < S1_TOK * S1_MAXGRP) {
+        // merge the chunk partials of this (token, head): (max, 1 / exp-sum) over all LSE keys
+        const int tt = threadIdx.x >> 4, hh = threadIdx.x & 15;
+        float2 r = make_float2(0.f, 0.f);
+        if (t0 + tt < t_end) {
+            const int nchunk = (compressed_len(L, a.lse_stride) + 127) / 128;
+            const float2* part = a.lse + ((static_cast<size_t>(g) * a.T + t0 + tt) * S1_MAXGRP + hh) * a.lse_chunks;
+            float mx = -INFINITY;
+            for (int c = 0; c < nchunk; ++c) mx = fmaxf(mx, part[c].x);
+            float sum = 0.f;
+            for (int c = 0; c < nchunk; ++c) {
+                if (part[c].x != -INFINITY) sum += part[c].y * exp2f((part[c].x - mx) * a.scale_log2);
             }
-        } else {
-            __syncthreads();
+            r = make_float2(mx == -INFINITY ? 0.f : mx, sum > 0.f ? 1.f / sum : 0.f);
         }
-        part[hs][kk] = mine;
-        __syncthreads();
-        if (hs == 0) out[k0 + kk] = __float2bfloat16((part[0][kk] + part[1][kk]) + (part[2][kk] + part[3][kk]));
+        lse_s[tt][hh] = r;
+    }
+    __syncthreads();
+    const int key = lane & 15, hh0 = (lane >> 4) * 8;  // lane: one key, eight of the sixteen heads
+    KeyFrag fb[8];
+    if (key0 < n1) s1_load_keys(a.c1 + static_cast<size_t>(key0) * a.kv_dim + g * 128, a.kv_dim, fb);
+#pragma unroll 1
+    for (int tt = 0; tt < S1_TOK; ++tt) {
+        if (t0 + tt >= t_end) break;
+        float mine = 0.f;
+        if (key0 < n1) {
+            s1_frag_scores(q_s + tt * S1_MAXGRP * S1_QLD, fb, frag[warp]);
+#pragma unroll
+            for (int j = 0; j < 8; ++j) {
+                const int hh = hh0 + j;
+                if (hh < a.grp) mine += exp2f((frag[warp][hh * 16 + key] - lse_s[tt][hh].x) * a.scale_log2) * lse_s[tt][hh].y;
+            }
+            __syncwarp();
+        }
+        mine += __shfl_xor_sync(0xffffffffu, mine, 16);
+        if (lane < 16) {
+            a.scores[(static_cast<size_t>(g) * a.T + t0 + tt) * a.score_ld + key0 + key] =
+                __float2bfloat16(key0 + key < n1 ? mine : 0.f);
+        }
     }
 }
 
@@ -207,6 +277,102 @@ struct PoolArgs {
     uint64_t* blockmask;  // [hkv][T][bm_words]
     int bm_words;
 };
+
+// Pooled score of block k for query token t (maxpooling_kernel of the reference) as a selection key.
+__device__ __forceinline__ unsigned long long pooled_key(const PoolArgs& a, const bf16* in, int k, int k_len, int q_block) {
+    bf16 v;
+    if (k < a.init_blocks) {
+        v = __ushort_as_bfloat16(0x7f80);  // +inf
+    } else if (q_block - a.local_blocks < k) {
+        v = __ushort_as_bfloat16(0xff80);  // -inf
+    } else {
+        int start = k * 4 - 1, end = start + 5;
+        start = max(start, 0);
+        end = min(end, k_len);
+        float mx = __bfloat162float(in[start]);
+        for (int i = start + 1; i < end; ++i) mx = fmaxf(mx, __bfloat162float(in[i]));
+        v = __float2bfloat16(mx);
+    }
+    return score_key(v, k);
+}
+
+// One warp per (kv head, token) row for up to 32 * PER blocks (block k lives in lane k % 32, slot k / 32).
+// The row's scores are staged in shared memory (coalesced).  Instead of extracting one maximum per round,
+// the k-th largest 16-bit score is found by a bitwise binary search with warp-wide counts (16 steps),
+// every block above it is taken, and the remaining picks among the blocks equal to it go to the lowest
+// indices (ballot + prefix count in index order): the same set as "value descending, lower index first".
+// The mask words are then just ballots of the per-slot decisions.  grid (ceil(T / 4), hkv), 128 threads.
+template <int PER>
+__global__ void __launch_bounds__(128) sparse_pool_topk_warp_kernel(const PoolArgs a) {
+    grid_dependency_sync();
+    __shared__ __align__(16) bf16 row_s[4][32 * PER * 4 + 128];
+    const int lane = threadIdx.x & 31, wid = threadIdx.x >> 5;
+    const int t = blockIdx.x * 4 + wid, g = blockIdx.y;
+    if (t >= a.T) return;
+    uint64_t* out = a.blockmask + (static_cast<size_t>(g) * a.T + t) * a.bm_words;
+    const int L = *a.kv_len + a.kv_add;
+    if (!selection_active(L, a.sparse_switch, a.compress_lse)) {
+        for (int w = lane; w < a.bm_words; w += 32) out[w] = ~0ull;
+        return;
+    }
+    if (a.n_valid != nullptr && t >= *a.n_valid) {
+        for (int w = lane; w < a.bm_words; w += 32) out[w] = 0ull;
+        return;
+    }
+    const int n1 = compressed_len(L, C1_STRIDE);
+    const int k_len = (n1 + 127) / 128 * 128;
+    const int out_len = (L + BLOCK - 1) / BLOCK;
+    const int q_block = (t + L) / BLOCK;
+    const bf16* in = a.scores + (static_cast<size_t>(g) * a.T + t) * a.score_ld;
+    bf16* mine_s = row_s[wid];
+    for (int i = lane * 8; i < k_len && i < 32 * PER * 4 + 128; i += 256) {
+        *reinterpret_cast<uint4*>(mine_s + i) = *reinterpret_cast<const uint4*>(in + i);
+    }
+    __syncwarp();
+    uint32_t val[PER];  // orderable 16-bit score of block j * 32 + lane, 0 = no such block
+    uint32_t valid = 0;
+#pragma unroll
+    for (int j = 0; j < PER; ++j) {
+        const int k = j * 32 + lane;
+        val[j] = (k < out_len) ? static_cast<uint32_t>(pooled_key(a, mine_s, k, k_len, q_block) >> 32) : 0u;
+        valid += val[j] != 0u;
+    }
+    const uint32_t total = __reduce_add_sync(0xffffffffu, valid);
+    uint32_t kth = 1u;                 // everything valid is taken when there are at most topk blocks
+    uint32_t need = 0xffffffffu;       // picks left for the blocks equal to kth
+    if (total > static_cast<uint32_t>(a.topk)) {
+        kth = 0u;
+        for (int bit = 15; bit >= 0; --bit) {
+            const uint32_t cand = kth | (1u << bit);
+            uint32_t c = 0;
+#pragma unroll
+            for (int j = 0; j < PER; ++j) c += val[j] >= cand;
+            if (__reduce_add_sync(0xffffffffu, c) >= static_cast<uint32_t>(a.topk)) kth = cand;
+        }
+        uint32_t gt = 0;
+#pragma unroll
+        for (int j = 0; j < PER; ++j) gt += val[j] > kth;
+        need = static_cast<uint32_t>(a.topk) - __reduce_add_sync(0xffffffffu, gt);
+    }
+    uint32_t halves[PER];  // ballot of slot j = bits 32 (j & 1) .. + 31 of mask word j / 2
+#pragma unroll
+    for (int j = 0; j < PER; ++j) {
+        const bool eq = (val[j] == kth) && (val[j] != 0u);
+        const uint32_t b = __ballot_sync(0xffffffffu, eq);
+        const uint32_t rank = __popc(b & ((1u << lane) - 1u));
+        const bool take = (val[j] > kth) || (eq && rank < need);
+        const uint32_t n_eq = __popc(b);
+        need = (need == 0xffffffffu) ? need : (need > n_eq ? need - n_eq : 0u);
+        halves[j] = __ballot_sync(0xffffffffu, take);
+    }
+#pragma unroll
+    for (int w = 0; w < PER / 2; ++w) {
+        if (lane == (w & 31) && w < a.bm_words) {
+            out[w] = (static_cast<uint64_t>(halves[2 * w + 1]) << 32) | halves[2 * w];
+        }
+    }
+    for (int w = PER / 2 + lane; w < a.bm_words; w += 32) out[w] = 0ull;
+}
 
 __global__ void __launch_bounds__(PT_THREADS) sparse_pool_topk_kernel(const PoolArgs a) {
     grid_dependency_sync();
@@ -283,6 +449,7 @@ __global__ void __launch_bounds__(PT_THREADS) sparse_pool_topk_kernel(const Pool
 
 void launch_sparse_compress(const SparseBuffers& b, bf16* const* caches, int layers, int kv_dim, const int32_t* kv_len,
                             int kv_add, int max_new, cudaStream_t s) {
+    ProfileScope prof(KC_OTHER, s);
     if (max_new < 1) max_new = 1;
     launch_kernel(sparse_compress_kernel, dim3(max_new, layers, b.c2 ? 2 : 1), dim3(128), 0, s, caches, kv_dim, b.c1,
                   b.c1_layer_stride, b.c2, b.c2_layer_stride, kv_len, kv_add, static_cast<const int32_t*>(b.done));
@@ -291,6 +458,7 @@ void launch_sparse_compress(const SparseBuffers& b, bf16* const* caches, int lay
 
 void launch_sparse_select(const SparseBuffers& b, const SparseConfig& cfg, int layer, const bf16* q, int q_ld, int T,
                           int hq, int hkv, const int32_t* kv_len, int kv_add, const int32_t* n_valid, cudaStream_t s) {
+    ProfileScope prof(KC_OTHER, s);
     const int grp = hq / hkv;
     CPM_REQUIRE(grp >= 1 && grp <= S1_MAXGRP, "sparse selection: at most 16 query heads per KV head");
     CPM_REQUIRE(T <= b.max_tokens, "sparse selection: more query tokens than the buffers hold");
@@ -303,7 +471,11 @@ void launch_sparse_select(const SparseBuffers& b, const SparseConfig& cfg, int l
     a.sparse_switch = cfg.sparse_switch; a.compress_lse = cfg.compress_lse ? 1 : 0;
     a.scale_log2 = 1.4426950408889634f / sqrtf(128.f);
     a.scores = b.scores; a.score_ld = b.score_ld; a.T = T;
-    launch_kernel(sparse_stage1_kernel, dim3(T, hkv), dim3(S1_THREADS), 0, s, a);
+    a.lse = b.lse;
+    a.lse_chunks = b.score_ld / 128;
+    launch_kernel(sparse_stage1_lse_kernel, dim3(ceil_div(T, S1_TOK), hkv, cfg.compress_lse ? ceil_div(a.lse_chunks, 4) : a.lse_chunks),
+                  dim3(S1_THREADS), 0, s, a);
+    launch_kernel(sparse_stage1_score_kernel, dim3(ceil_div(T, S1_TOK), hkv, b.score_ld / 128), dim3(S1_THREADS), 0, s, a);
     PoolArgs p;
     p.scores = b.scores; p.score_ld = b.score_ld; p.T = T;
     p.kv_len = kv_len; p.kv_add = kv_add; p.n_valid = n_valid;
@@ -311,5 +483,12 @@ void launch_sparse_select(const SparseBuffers& b, const SparseConfig& cfg, int l
     p.init_blocks = cfg.sink_blocks; p.local_blocks = cfg.window_blocks; p.topk = cfg.topk;
     p.blockmask = b.blockmask; p.bm_words = b.bm_words;
     CPM_REQUIRE(b.bm_words <= 64, "sparse selection: at most 4096 blocks (262144 tokens)");
-    launch_kernel(sparse_pool_topk_kernel, dim3(T, hkv), dim3(PT_THREADS), 0, s, p);
+    const int max_blocks = b.score_ld / 4 + 1;  // score_ld >= budget / 16
+    if (max_blocks <= 512) {
+        launch_kernel(sparse_pool_topk_warp_kernel<16>, dim3(ceil_div(T, 4), hkv), dim3(128), 0, s, p);
+    } else if (max_blocks <= 1024) {
+        launch_kernel(sparse_pool_topk_warp_kernel<32>, dim3(ceil_div(T, 4), hkv), dim3(128), 0, s, p);
+    } else {
+        launch_kernel(sparse_pool_topk_kernel, dim3(T, hkv), dim3(PT_THREADS), 0, s, p);
+    }
 }

@@ -18,6 +18,7 @@ struct SparseBuffers {
     bf16* c2 = nullptr;          // [layers][budget / 64][kv_dim]  means of 128 keys every 64 (compress_lse only)
     size_t c2_layer_stride = 0;
     int32_t* done = nullptr;     // [2] entries of c1 / c2 computed so far (same for every layer)
+    float2* lse = nullptr;       // [hkv][max_tokens][16][score_ld / 128]  (max, exp-sum) per 128-key chunk of the LSE keys
     bf16* scores = nullptr;      // [hkv][max_tokens][score_ld]  stage-1 scores of the layer being run
     int score_ld = 0;
     uint64_t* blockmask = nullptr;  // [hkv][max_tokens][bm_words]

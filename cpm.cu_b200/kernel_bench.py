@@ -3,6 +3,7 @@
     python cpm.cu_b200/kernel_bench.py linear [M,N,K] [iters]      bf16 weights
     python cpm.cu_b200/kernel_bench.py linear_w4 [M,N,K] [iters]   4-bit weights (W4A16)
     python cpm.cu_b200/kernel_bench.py attention [tq,hq,hkv,kv,splits,mask] [iters]
+    python cpm.cu_b200/kernel_bench.py select [tq,hq,hkv,L,budget] [iters]    InfLLM-v2 block selection of one layer
 
 Each case runs `iters` back-to-back launches inside the library, timed with CUDA events on the
 library's stream, rotating over enough separate weight (or KV-cache) copies that no launch finds
@@ -54,6 +55,31 @@ def bench_attention(cases, iters):
               f"{kv_bytes / us / 1e3:.0f} GB/s", flush=True)
 
 
+def bench_select(case, iters):
+    """One layer's block selection (compress from scratch + stage-1 scores + max-pool / top-k / bitmask)
+    through cpmcu_sparse_select; host-clock time per call, for per-kernel times run it under ncu."""
+    import time
+
+    import torch
+    tq, hq, hkv, L, budget = case
+    q = torch.randn(tq, (hq + 2 * hkv) * 128, device="cuda").to(torch.bfloat16)
+    k = torch.randn(budget, hkv * 128, device="cuda").to(torch.bfloat16)
+    score_ld = (budget // 16 + 127) // 128 * 128
+    words = (budget // 64 + 63) // 64
+    bm = torch.zeros(hkv, tq, words, dtype=torch.int64, device="cuda")
+    kv_len = torch.tensor([L], dtype=torch.int32, device="cuda")
+    p = lambda t: ctypes.c_void_p(t.data_ptr())  # noqa: E731
+    torch.cuda.synchronize()
+    for i in range(iters + 1):
+        if i == 1:
+            t0 = time.time()
+        C.call("cpmcu_sparse_select", p(q), q.shape[1], tq, hq, hkv, p(k), budget, p(kv_len), 0, 1, 32, 64, 8192, 1,
+               None, None, None, score_ld, p(bm), words)
+    us = (time.time() - t0) / iters * 1e6
+    print(f"select tq={tq} hq={hq} hkv={hkv} L={L} budget={budget}: {us:.0f} us per call (host clock, "
+          f"includes the compression of all {L // 16} + {L // 64} entries and the buffer set-up)", flush=True)
+
+
 def main(argv):
     what = argv[1] if len(argv) > 1 else "linear"
     shape = tuple(int(v) for v in argv[2].split(",")) if len(argv) > 2 else None
@@ -64,6 +90,8 @@ def main(argv):
         bench_linear([shape] if shape else W4_SHAPES, iters, True)
     elif what == "attention":
         bench_attention([shape] if shape else ATTN_CASES, iters)
+    elif what == "select":
+        bench_select(shape if shape else (60, 32, 2, 32768, 40960), iters if len(argv) > 3 else 3)
     else:
         raise SystemExit(__doc__)
 

@@ -48,18 +48,20 @@ def make_case(T, hq, hkv, L, seed, budget=None):
 
 
 SELECT_CASES = [
-    # T, hq, hkv, L, top, sink, window, lse
-    (12, 8, 2, 1500, 6, 1, 4, True),
-    (60, 32, 2, 3000, 16, 1, 8, True),
-    (7, 8, 2, 2048, 8, 2, 2, False),
-    (16, 4, 1, 1000, 64, 1, 3, True),   # fewer candidate blocks than top-k
+    # T, hq, hkv, L, top, sink, window, lse, budget (None: just above L; the library picks its top-k kernel by budget)
+    (12, 8, 2, 1500, 6, 1, 4, True, None),
+    (60, 32, 2, 3000, 16, 1, 8, True, None),
+    (7, 8, 2, 2048, 8, 2, 2, False, None),
+    (16, 4, 1, 1000, 64, 1, 3, True, None),   # fewer candidate blocks than top-k
+    (9, 8, 2, 3000, 12, 1, 4, True, 40960),   # up to 1024 blocks: 32 keys per lane
+    (9, 8, 2, 3000, 12, 1, 4, True, 69632),   # more than 1024 blocks: block-wide selection
 ]
 
 
-@pytest.mark.parametrize("T,hq,hkv,L,top,sink,window,lse", SELECT_CASES)
-def test_block_selection_matches_oracle(T, hq, hkv, L, top, sink, window, lse):
+@pytest.mark.parametrize("T,hq,hkv,L,top,sink,window,lse,budget", SELECT_CASES)
+def test_block_selection_matches_oracle(T, hq, hkv, L, top, sink, window, lse, budget):
     c = C()
-    q, k, v, budget = make_case(T, hq, hkv, L, seed=L + T)
+    q, k, v, budget = make_case(T, hq, hkv, L, seed=L + T, budget=budget)
     kv_dim = hkv * 128
     score_ld = (budget // 16 + 127) // 128 * 128
     bm_words = ((L + T + 127) // 128 * 128 // 64 + 63) // 64
