@@ -268,7 +268,10 @@ def run_ours(args):
                                    + "%d-token Zipf(1.1) prompt, batch 1, greedy" % prompt_len,
                        "replicas": world,
                        "l2": "inputs larger than L2 (%.1f GB of weights streamed per step)" % ((tgt_b + draft_b) / 1e9)},
-            "e2e": {"value": tokens_all / wall_max, "unit": UNIT, "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 128},
+            "e2e": {"value": tokens_all / wall_max, "unit": UNIT, "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 128,
+                    "note": "host clock around C.spec_step(), the call a user makes per step, including its 128-byte "
+                            "device-to-host read of (accept length, tokens); a step has no host input (root token and "
+                            "lengths are device state; the prompt is copied once before prefill)"},
             "gpu_launches": int(launches) * args.steps,
             "launches_per_step": int(launches),
             "mean_accept_length": statistics.mean(accept),
