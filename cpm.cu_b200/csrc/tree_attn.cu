@@ -26,6 +26,10 @@
 // gridDim.y key splits each write an unnormalised partial (O, max, sum); a
 // small second kernel merges them.  With one split the kernel normalises and
 // stores bf16 directly.
+#include <algorithm>
+#include <cstdio>
+#include <vector>
+
 #include "common.cuh"
 #include "ptx.cuh"
 
@@ -47,7 +51,7 @@ constexpr int SMEM_TOTAL = SMEM_XCH + 1024 + 1024;
 constexpr int TMEM_COLS = 512;  // S stage 0: [0,128), S stage 1: [128,256), O: [256,384)
 constexpr int TMEM_O = 256;
 constexpr int SOFTMAX_THREADS = 256;  // two threads per query row: warps 0-3 keys 0-63 of a tile, warps 4-7 keys 64-127
-constexpr int NTHREADS = SOFTMAX_THREADS + 32;  // + one control warp (TMA and MMA issue)
+constexpr int NTHREADS = SOFTMAX_THREADS + 128;  // + four control warps: K producer, S issuer, PV issuer, V producer
 
 struct AttnArgs {
     int tq, hq, hkv, grp, tok_per_tile, num_mtiles;
@@ -65,7 +69,15 @@ struct AttnArgs {
     float* ws_o;
     float* ws_ml;
     int* error;
+    long long* prof;  // bench only (-DCPMCU_ATTN_PROFILE): clock counters of CTA 0, or null
 };
+
+#ifdef CPMCU_ATTN_PROFILE
+constexpr bool kAttnProf = true;
+#else
+constexpr bool kAttnProf = false;
+#endif
+__device__ __forceinline__ long long prof_clock() { return kAttnProf ? clock64() : 0; }
 
 __device__ __forceinline__ float fast_exp2(float x) {
     float y;
@@ -93,10 +105,11 @@ tree_attn_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant
     volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
     float* xch = reinterpret_cast<float*>(smem + SMEM_XCH);  // [2][128] row maxima / sums of the two column halves
 
+    const long long pt_kernel = prof_clock();
     const int tid = threadIdx.x;
     const int warp = tid >> 5;
     const int lane = tid & 31;
-    const bool is_control = (warp == SOFTMAX_THREADS / 32);
+    const bool is_control = (warp >= SOFTMAX_THREADS / 32);
     const int ch = (warp >> 2) & 1;              // column half of the key tile
     const int row = (warp & 3) * 32 + lane;      // query row of the tile == TMEM lane
     grid_dep_trigger();
@@ -131,6 +144,7 @@ tree_attn_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant
     const uint32_t lane_sel = static_cast<uint32_t>((warp & 3) * 32) << 16;
     const uint32_t tmem_o = tmem_base + lane_sel + TMEM_O + ch * 64;  // this thread's 64 output columns
     grid_dep_wait();  // everything above overlaps the previous kernel's tail
+    const long long pt_dep = prof_clock();
 
     // ---- geometry of this tile
     const int kv_total = *a.kv_len + a.kv_len_add;
@@ -226,92 +240,104 @@ tree_attn_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant
     bool ok = true;
 
     if (is_control) {
-        // ================================================= control warp: TMA + MMA issue
-        if (lane == 0 && n_it > 0) {
-            const uint32_t q_addr = ptx::smem_u32(smem + SMEM_Q);
-            const uint32_t p_addr = ptx::smem_u32(smem + SMEM_P);
-            constexpr uint32_t idesc_s = ptx::umma_idesc_bf16(ROWS, KEYS, 0, 0);
-            constexpr uint32_t idesc_o = ptx::umma_idesc_bf16(ROWS, D, 0, 1);
-            int k_tile = kt_begin, v_tile = kt_begin;  // tiles of the next K / V load (issued in iteration order)
-            auto load_k = [&](int i) {
-                const int st = i & 1, key0 = k_tile * KEYS;
-                k_tile = next_tile(k_tile);
-                ptx::mbar_arrive_expect_tx(&k_full[st], TILE_BYTES);
-                ptx::tma_load_2d(smem + SMEM_K + st * TILE_BYTES, &tm_k, &k_full[st], h * D, key0);
-                ptx::tma_load_2d(smem + SMEM_K + st * TILE_BYTES + HALF_BYTES, &tm_k, &k_full[st], h * D + 64, key0);
-            };
-            auto load_v = [&](int i) {
-                const int st = i & 1, key0 = v_tile * KEYS;
-                v_tile = next_tile(v_tile);
-                ptx::mbar_arrive_expect_tx(&v_full[st], TILE_BYTES);
-                ptx::tma_load_2d(smem + SMEM_V + st * TILE_BYTES, &tm_v, &v_full[st], h * D, key0);
-                ptx::tma_load_2d(smem + SMEM_V + st * TILE_BYTES + HALF_BYTES, &tm_v, &v_full[st], h * D + 64, key0);
-            };
-            auto issue_s = [&](int i) -> bool {  // S(i) = Q K(i)^T into S stage i & 1
+        // ================================================= four control warps: K / V producers, S issuer, PV issuer.
+        // Each runs its loop as a whole warp with warp-uniform control flow (waits poll on one lane) and
+        // elects one lane for the TMA / tcgen05 instructions, whose operands then stay in uniform registers;
+        // one thread doing all three jobs was the bottleneck of a key tile (2.8 us per tile, 16 MMAs + 4 TMA
+        // + 7 waits in one dependent instruction stream).
+        const int role = warp - SOFTMAX_THREADS / 32;
+        if ((role == 0 || role == 3) && n_it > 0) {
+            // ---- producers.  role 0: Q once, then K(i) as soon as S(i-2) has consumed the stage;
+            //      role 3: V(i) as soon as PV(i-2) has (separate warps: the two conditions come true at different times)
+            const bool is_k = (role == 0);
+            int tile = kt_begin;
+            bool w = true;
+            if (is_k) {
+                if (ptx::elect_one()) {
+                    ptx::mbar_arrive_expect_tx(q_bar, TILE_BYTES);
+                    ptx::tma_load_3d(smem + SMEM_Q, &tm_q, q_bar, 0, h * a.grp, t0);
+                    ptx::tma_load_3d(smem + SMEM_Q + HALF_BYTES, &tm_q, q_bar, 64, h * a.grp, t0);
+                }
+                __syncwarp();
+            }
+            uint64_t* freed = is_k ? s_bar : o_bar;
+            uint64_t* full = is_k ? k_full : v_full;
+            const CUtensorMap* tm = is_k ? &tm_k : &tm_v;
+            uint8_t* base = smem + (is_k ? SMEM_K : SMEM_V);
+            for (int i = 0; w && i < n_it; ++i) {
                 const int st = i & 1;
-                if (!ptx::mbar_wait(&k_full[st], (i >> 1) & 1, abort_flag)) return false;
+                const int key0 = tile * KEYS;
+                tile = next_tile(tile);
+                if (i >= 2 && !ptx::mbar_wait_warp(&freed[st], ((i - 2) >> 1) & 1, abort_flag)) { w = false; break; }
+                if (ptx::elect_one()) {
+                    ptx::mbar_arrive_expect_tx(&full[st], TILE_BYTES);
+                    ptx::tma_load_2d(base + st * TILE_BYTES, tm, &full[st], h * D, key0);
+                    ptx::tma_load_2d(base + st * TILE_BYTES + HALF_BYTES, tm, &full[st], h * D + 64, key0);
+                }
+                __syncwarp();
+            }
+        } else if (role == 1 && n_it > 0) {
+            // ---- S issuer: S(i) = Q K(i)^T into S stage i & 1 once softmax(i-2) has read that stage
+            const uint32_t q_addr = ptx::smem_u32(smem + SMEM_Q);
+            constexpr uint32_t idesc_s = ptx::umma_idesc_bf16(ROWS, KEYS, 0, 0);
+            bool w = ptx::mbar_wait_warp(q_bar, 0, abort_flag);
+            for (int i = 0; w && i < n_it; ++i) {
+                const int st = i & 1;
+                if (i >= 2 && !ptx::mbar_wait_warp(&p_ready[st], ((i - 2) >> 1) & 1, abort_flag)) { w = false; break; }
+                if (!ptx::mbar_wait_warp(&k_full[st], (i >> 1) & 1, abort_flag)) { w = false; break; }
                 ptx::tc_fence_after();
                 const uint32_t k_addr = ptx::smem_u32(smem + SMEM_K + st * TILE_BYTES);
+                if (ptx::elect_one()) {
 #pragma unroll
-                for (int dh = 0; dh < 2; ++dh) {
+                    for (int dh = 0; dh < 2; ++dh) {
 #pragma unroll
-                    for (int j = 0; j < 4; ++j) {
-                        const uint64_t da = ptx::umma_desc_sw128(q_addr + dh * HALF_BYTES + j * 32, 16, 1024);
-                        const uint64_t db = ptx::umma_desc_sw128(k_addr + dh * HALF_BYTES + j * 32, 16, 1024);
-                        ptx::umma_ss(tmem_base + st * KEYS, da, db, idesc_s, (dh | j) ? 1u : 0u);
+                        for (int j = 0; j < 4; ++j) {
+                            const uint64_t da = ptx::umma_desc_sw128(q_addr + dh * HALF_BYTES + j * 32, 16, 1024);
+                            const uint64_t db = ptx::umma_desc_sw128(k_addr + dh * HALF_BYTES + j * 32, 16, 1024);
+                            ptx::umma_ss(tmem_base + st * KEYS, da, db, idesc_s, (dh | j) ? 1u : 0u);
+                        }
                     }
+                    ptx::umma_commit(&s_bar[st]);
                 }
-                ptx::umma_commit(&s_bar[st]);
-                return true;
-            };
-            ptx::mbar_arrive_expect_tx(q_bar, TILE_BYTES);
-            ptx::tma_load_3d(smem + SMEM_Q, &tm_q, q_bar, 0, h * a.grp, t0);
-            ptx::tma_load_3d(smem + SMEM_Q + HALF_BYTES, &tm_q, q_bar, 64, h * a.grp, t0);
-            for (int i = 0; i < 2 && i < n_it; ++i) {
-                load_k(i);
-                load_v(i);
+                __syncwarp();
             }
-            bool w = ptx::mbar_wait(q_bar, 0, abort_flag);
-            for (int i = 0; w && i < 2 && i < n_it; ++i) w = issue_s(i);
+        } else if (role == 2 && n_it > 0) {
+            // ---- PV issuer: O += P(i) V(i)
+            const uint32_t p_addr = ptx::smem_u32(smem + SMEM_P);
+            constexpr uint32_t idesc_o = ptx::umma_idesc_bf16(ROWS, D, 0, 1);
+            bool w = true;
             for (int i = 0; w && i < n_it; ++i) {
                 const int st = i & 1;
                 const uint32_t ph = (i >> 1) & 1;
-                // K stage st is free once S(i) has been computed: fetch K(i+2)
-                if (i + 2 < n_it) {
-                    if (!ptx::mbar_wait(&s_bar[st], ph, abort_flag)) { w = false; break; }
-                    load_k(i + 2);
-                }
-                // O += P(i) V(i)
-                if (!ptx::mbar_wait(&p_ready[st], ph, abort_flag)) { w = false; break; }
-                if (!ptx::mbar_wait(&v_full[st], ph, abort_flag)) { w = false; break; }
+                if (!ptx::mbar_wait_warp(&p_ready[st], ph, abort_flag)) { w = false; break; }
+                if (!ptx::mbar_wait_warp(&v_full[st], ph, abort_flag)) { w = false; break; }
                 ptx::tc_fence_after();
                 const uint32_t v_addr = ptx::smem_u32(smem + SMEM_V + st * TILE_BYTES);
                 const uint32_t pa = p_addr + st * TILE_BYTES;
+                if (ptx::elect_one()) {
 #pragma unroll
-                for (int kk = 0; kk < KEYS / 16; ++kk) {
-                    // A: P, K-major: 64-key half (kk / 4), 32 B per 16-key step inside it
-                    const uint64_t da = ptx::umma_desc_sw128(pa + (kk >> 2) * HALF_BYTES + (kk & 3) * 32, 16, 1024);
-                    // B: V, N-major: 16 key rows of 128 B per step; 64-wide d halves HALF_BYTES apart
-                    const uint64_t db = ptx::umma_desc_sw128(v_addr + kk * 16 * 128, HALF_BYTES, 1024);
-                    ptx::umma_ss(tmem_base + TMEM_O, da, db, idesc_o, (i > 0 || kk > 0) ? 1u : 0u);
+                    for (int kk = 0; kk < KEYS / 16; ++kk) {
+                        // A: P, K-major: 64-key half (kk / 4), 32 B per 16-key step inside it
+                        const uint64_t da = ptx::umma_desc_sw128(pa + (kk >> 2) * HALF_BYTES + (kk & 3) * 32, 16, 1024);
+                        // B: V, N-major: 16 key rows of 128 B per step; 64-wide d halves HALF_BYTES apart
+                        const uint64_t db = ptx::umma_desc_sw128(v_addr + kk * 16 * 128, HALF_BYTES, 1024);
+                        ptx::umma_ss(tmem_base + TMEM_O, da, db, idesc_o, (i > 0 || kk > 0) ? 1u : 0u);
+                    }
+                    ptx::umma_commit(&o_bar[st]);
                 }
-                ptx::umma_commit(&o_bar[st]);
-                // S(i+2) reuses S stage st: softmax(i) has read it (p_ready) and K(i+2) is on its way
-                if (i + 2 < n_it) {
-                    if (!issue_s(i + 2)) { w = false; break; }
-                    // V stage st is free once PV(i) has finished
-                    if (!ptx::mbar_wait(&o_bar[st], ph, abort_flag)) { w = false; break; }
-                    load_v(i + 2);
-                }
+                __syncwarp();
             }
         }
     } else {
         // ================================================= softmax warps
         int s_tile = kt_begin;
+        long long pt_s = 0, pt_ld = 0, pt_bar = 0, pt_o = 0, pt_exp = 0;
+        const long long pt_begin = prof_clock();
         for (int i = 0; i < n_it && ok; ++i) {
             const int st = i & 1;
             const uint32_t ph = (i >> 1) & 1;
             const int key0 = s_tile * KEYS + ch * 64;  // first key of this thread's 64 columns
+            const long long pc0 = prof_clock();
             s_tile = next_tile(s_tile);
             // block-sparse mode: this row's token may not see this 64-key block at all
             bool blk_ok = true;
@@ -323,6 +349,7 @@ tree_attn_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant
             // one polling lane per warp (the shuffle also converges it for the collective TMEM loads)
             if (!ptx::mbar_wait_warp(&s_bar[st], ph, abort_flag)) { ok = false; break; }
             ptx::tc_fence_after();
+            const long long pc1 = prof_clock();
 
             // ---- scores of this thread: 64 columns, kept in registers for both passes
             uint32_t sc[64];
@@ -330,14 +357,26 @@ tree_attn_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant
             ptx::tmem_ld32(tmem_s, sc);
             ptx::tmem_ld32(tmem_s + 32, sc + 32);
             ptx::tmem_wait_ld();
-            const bool need_mask = !blk_ok || (key0 + 64 > limit) || (key0 + 64 > mbeg) || (key0 < key_lo);
-            if (need_mask) {
+            // visibility of this thread's 64 keys as one 64-bit word: causal bound, window bound, tree-mask bits,
+            // block selection.  (A per-key chain of comparisons here made the half-empty last token tile of a
+            // verify pass, whose rows see nothing, 2.2 times slower than the full tiles.)
+            uint64_t vb = ~0ull;
+            if (!blk_ok || limit <= key0 || key_lo >= key0 + 64) {
+                vb = 0ull;
+            } else {
+                if (limit < key0 + 64) vb &= (1ull << (limit - key0)) - 1ull;
+                if (key_lo > key0) vb &= ~((1ull << (key_lo - key0)) - 1ull);
+                const int mo = mbeg - key0;  // first column the tree mask applies to (mbeg is huge when there is none)
+                if (mo < 64) {
+                    const uint64_t tm = (mo >= 0) ? ((mo > 0 ? (mword << mo) : mword) | ((1ull << mo) - 1ull))
+                                                  : ((-mo < 64) ? (mword >> (-mo)) : 0ull);
+                    vb &= tm;
+                }
+            }
+            if (vb != ~0ull) {
 #pragma unroll
                 for (int c = 0; c < 64; ++c) {
-                    const int key = key0 + c;
-                    bool vis = blk_ok && key < limit && key >= key_lo;
-                    if (key >= mbeg) vis = vis && ((mword >> (key - mbeg)) & 1ull);
-                    if (!vis) sc[c] = 0xff800000u;  // -inf
+                    if (!((vb >> c) & 1ull)) sc[c] = 0xff800000u;  // -inf
                 }
             }
             float mx[4] = {-INFINITY, -INFINITY, -INFINITY, -INFINITY};
@@ -349,11 +388,18 @@ tree_attn_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant
                 mx[3] = fmaxf(mx[3], __uint_as_float(sc[c + 3]));
             }
             const float m_half = fmaxf(fmaxf(mx[0], mx[1]), fmaxf(mx[2], mx[3]));
+            const long long pc2 = prof_clock();
             xch[ch * ROWS + row] = m_half;
             ptx::named_bar_sync(1, SOFTMAX_THREADS);
             const float m_tile = fmaxf(m_half, xch[(ch ^ 1) * ROWS + row]);
             ptx::named_bar_sync(2, SOFTMAX_THREADS);  // xch is rewritten by the next iteration
-            const float m_new = fmaxf(m_run, m_tile);
+            const long long pc3 = prof_clock();
+            // Lazy running maximum: the reference maximum of a row moves only when the new one is more than
+            // 2^8 above it (or the row had none yet).  Exponentials then stay below 256 (exact enough in bf16 P
+            // and fp32 sums), and O has to be rescaled - which needs the previous PV to have finished and
+            // serialises the pipeline - only on such jumps instead of whenever any row of a warp sees a new maximum.
+            float m_new = m_run;
+            if (m_tile != -INFINITY && (m_run == -INFINITY || (m_tile - m_run) * a.scale_log2 > 8.f)) m_new = m_tile;
             const float m_use = (m_new == -INFINITY) ? 0.f : m_new;
             const float alpha = (m_run == -INFINITY) ? 1.f : fast_exp2((m_run - m_use) * a.scale_log2);
             const bool rescale = (i > 0) && __any_sync(0xffffffffu, alpha != 1.f);
@@ -375,6 +421,7 @@ tree_attn_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant
             if (i >= 2) {  // P stage st was last read by PV(i-2)
                 if (!ptx::mbar_wait_warp(&o_bar[st], ((i - 2) >> 1) & 1, abort_flag)) { ok = false; break; }
             }
+            const long long pc4 = prof_clock();
 
             // ---- P = 2^((s - m) * scale) in bf16 into the swizzled A-operand tile; row sums in fp32
             const float m_off = m_use * a.scale_log2;
@@ -402,6 +449,14 @@ tree_attn_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant
             ptx::tc_fence_before();         // TMEM reads / rescale ordered before the control warp's next MMA
             __syncwarp();
             if ((threadIdx.x & 31) == 0) ptx::mbar_arrive(&p_ready[st]);
+            if (kAttnProf) {
+                const long long pc5 = prof_clock();
+                pt_s += pc1 - pc0; pt_ld += pc2 - pc1; pt_bar += pc3 - pc2; pt_o += pc4 - pc3; pt_exp += pc5 - pc4;
+            }
+        }
+        if (kAttnProf && a.prof != nullptr && blockIdx.x == 0 && blockIdx.y == 0 && tid == 0) {
+            a.prof[0] = prof_clock() - pt_begin; a.prof[1] = pt_s; a.prof[2] = pt_ld; a.prof[3] = pt_bar;
+            a.prof[4] = pt_o; a.prof[5] = pt_exp; a.prof[6] = n_it; a.prof[7] = pt_begin - pt_kernel;
         }
         if (ok && n_it > 0) {
             if (!ptx::mbar_wait_warp(&o_bar[(n_it - 1) & 1], ((n_it - 1) >> 1) & 1, abort_flag)) ok = false;
@@ -468,6 +523,10 @@ tree_attn_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant
         ptx::tmem_dealloc(tmem_base, TMEM_COLS);
     }
     if (tid == 0 && *abort_flag) atomicOr(a.error, ERR_ATTN_TIMEOUT);
+    if (kAttnProf && a.prof != nullptr && tid == 0) {
+        if (blockIdx.x == 0 && blockIdx.y == 0) a.prof[8] = prof_clock() - pt_kernel;
+        a.prof[16 + blockIdx.y * gridDim.x + blockIdx.x] = prof_clock() - pt_dep;  // active time of every CTA
+    }
 }
 
 // Merge split partials: out = sum_s 2^((m_s - M) c) O_s / sum_s 2^((m_s - M) c) l_s.
@@ -570,6 +629,36 @@ void launch_tree_attention(const AttnPlan& p, cudaStream_t s) {
     a.out = p.out; a.out_ld = p.out_ld;
     a.ws_o = p.ws_o; a.ws_ml = p.ws_ml;
     a.error = runtime().d_error;
+    a.prof = nullptr;
+    if (kAttnProf) {
+        static long long* buf = nullptr;
+        if (buf == nullptr) {
+            CUDA_CHECK(cudaMalloc(&buf, 4096 * sizeof(long long)));
+            CUDA_CHECK(cudaMemset(buf, 0, 4096 * sizeof(long long)));
+        }
+        a.prof = buf;
+        static int calls = 0;
+        if (++calls % 32 == 0) {
+            long long hst[9];
+            CUDA_CHECK(cudaMemcpy(hst, buf, sizeof(hst), cudaMemcpyDeviceToHost));
+            fprintf(stderr, "attn prof (CTA 0, softmax thread 0): loop %lld cycles, %lld tiles: wait S %lld, load+max %lld, "
+                            "row-max exchange %lld, rescale + wait PV(i-2) %lld, exp + P store %lld; before the loop %lld, "
+                            "whole kernel %lld\n",
+                    hst[0], hst[6], hst[1], hst[2], hst[3], hst[4], hst[5], hst[7], hst[8]);
+            std::vector<long long> act(a.num_mtiles * p.hkv * p.splits);
+            CUDA_CHECK(cudaMemcpy(act.data(), buf + 16, act.size() * sizeof(long long), cudaMemcpyDeviceToHost));
+            long long lo = act[0], hi = act[0], sum = 0;
+            for (long long v : act) { lo = std::min(lo, v); hi = std::max(hi, v); sum += v; }
+            fprintf(stderr, "attn prof: active cycles per CTA after the dependency wait: min %lld mean %lld max %lld over %zu CTAs\n",
+                    lo, sum / static_cast<long long>(act.size()), hi, act.size());
+            const int gx = a.num_mtiles * p.hkv;
+            for (int sp = 0; sp < p.splits; ++sp) {
+                fprintf(stderr, "  split %d:", sp);
+                for (int x = 0; x < gx; ++x) fprintf(stderr, " %lld", act[sp * gx + x] / 1000);
+                fprintf(stderr, "\n");
+            }
+        }
+    }
     CPM_REQUIRE(p.splits == 1 || (p.ws_o != nullptr && p.ws_ml != nullptr), "attention: split-KV needs a workspace");
     dim3 grid(a.num_mtiles * p.hkv, p.splits);
     launch_kernel(tree_attn_kernel, grid, dim3(NTHREADS), SMEM_TOTAL, s, p.tm_q, p.tm_k, p.tm_v, a);
