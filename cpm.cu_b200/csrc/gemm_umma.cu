@@ -275,6 +275,10 @@ LinearPlan make_linear_plan(const bf16* x, int x_rows, const bf16* w, int M, int
     if (grid < 1) grid = 1;
     if (grid > grid_limit) grid = grid_limit;
     if (m_tiles == 1 && grid_limit >= 64) grid = pick_grid(n_tiles, kblocks, M, static_cast<int>(grid));
+    {
+        static const char* forced = getenv("CPMCU_LINEAR_GRID");  // bench only: sweep the grid size
+        if (forced && atoi(forced) >= 1 && atoi(forced) <= grid_limit && atoi(forced) <= units) grid = atoi(forced);
+    }
     p.grid = static_cast<int>(grid);
     p.tm_w = make_tmap_2d(w, K, N, static_cast<uint64_t>(K) * 2, BLOCK_K, BLOCK_N);
     p.tm_x = make_tmap_2d(x, K, x_rows, static_cast<uint64_t>(K) * 2, BLOCK_K, p.mt);
