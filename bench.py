@@ -49,7 +49,7 @@ def zipf_prompt(n, vocab, seed, s=1.1):
     return rng.choice(vocab, size=n, p=p).astype(np.int32)
 
 
-def algorithmic_bytes(w4a16=False):
+def algorithmic_bytes(w4a16=False, draft_vocab=None):
     """Weight bytes one speculative step has to stream: every target linear once (M = 60), the draft
     fc + layer + LM head six times.  bf16 weights are 2 bytes; W4A16 target linears are half a byte per
     weight plus one bf16 scale per 128."""
@@ -58,7 +58,7 @@ def algorithmic_bytes(w4a16=False):
     layer = qkv * H + H * CFG["hq"] * CFG["head_dim"] + 2 * I * H + H * I
     per_weight = (0.5 + 2.0 / 128) if w4a16 else 2.0
     target = int(CFG["layers"] * layer * per_weight) + V * H * 2
-    draft_pass = (2 * H * H + layer + V * H) * 2
+    draft_pass = (2 * H * H + layer + (draft_vocab or V) * H) * 2
     return target, TREE["num_iter"] * draft_pass
 
 
@@ -100,7 +100,10 @@ LONG_PROMPT_LEN = 32768   # config 5
 LONG_CHUNK = 2048         # the reference's default chunk_length: the first chunk is dense, later ones select blocks
 
 
-def build_model(device_index, seed=1, w4a16=False, sparse=False):
+FRSPEC_VOCAB = 32768      # config 3
+
+
+def build_model(device_index, seed=1, w4a16=False, sparse=False, frspec=False):
     """Random-init config-2 model (config 4 with w4a16: the target's linears as random GPTQ-Marlin int4
     tensors), generated on the GPU tensor by tensor and loaded through the reference-shaped Python classes
     (C.load_model accepts device pointers)."""
@@ -124,6 +127,8 @@ def build_model(device_index, seed=1, w4a16=False, sparse=False):
         # draft layer with a sliding window of 1024 tokens
         extra = dict(apply_sparse=True, sink_window_size=1, block_window_size=32, sparse_topk_k=64, sparse_switch=8192,
                      apply_compress_lse=True, eagle_window_size=1024)
+    if frspec:
+        extra["frspec_vocab_size"] = FRSPEC_VOCAB
     llm = cls(None, None, num_iter=TREE["num_iter"], topk_per_iter=TREE["topk"],
               tree_size=TREE["tree_size"], eagle_config={"num_hidden_layers": 1}, config=hf,
               dtype=torch.bfloat16, chunk_length=LONG_CHUNK if sparse else PROMPT_LEN, memory_limit=0.8,
@@ -136,6 +141,12 @@ def build_model(device_index, seed=1, w4a16=False, sparse=False):
         return (torch.randn(*shape, device="cuda", generator=g, dtype=torch.float32) * 0.02).to(torch.bfloat16)
 
     ones = torch.ones(H, device="cuda", dtype=torch.bfloat16)
+    if frspec:
+        # config 3: the draft LM head keeps the 32768 most frequent ids of a seeded Zipf(1.1) sample of 1M tokens
+        import numpy as np
+        counts = np.bincount(zipf_prompt(1_000_000, CFG["vocab"], seed + 1000), minlength=CFG["vocab"])
+        remap = np.sort(np.argsort(-counts, kind="stable")[:FRSPEC_VOCAB]).astype(np.int32)
+        llm._load("token_id_remap", torch.from_numpy(remap), cls="eagle")   # before lm_head.weight
     llm._load("model.embed_tokens.weight", rnd(CFG["vocab"], H))
     llm._load("lm_head.weight", rnd(CFG["vocab"], H))
     llm._load("model.norm.weight", ones)
@@ -188,10 +199,11 @@ def run_ours(args):
     C.load()  # fails loudly if the CUDA library is missing
     w4 = args.workload == "config4"
     long_ctx = args.workload == "config5"
+    frspec = args.workload == "config3"
     prompt_len = LONG_PROMPT_LEN if long_ctx else PROMPT_LEN
     import contextlib
     with contextlib.redirect_stdout(sys.stderr):  # keep stdout for the single JSON line
-        llm = build_model(local, seed=1, w4a16=w4, sparse=long_ctx)
+        llm = build_model(local, seed=1, w4a16=w4, sparse=long_ctx, frspec=frspec)
     from cpmcu.replicas import replica_seed
     prompt = torch.tensor(zipf_prompt(prompt_len, CFG["vocab"], replica_seed(100, rank)), device="cuda")
     pos = torch.arange(prompt_len, dtype=torch.int32, device="cuda")
@@ -250,7 +262,7 @@ def run_ours(args):
             pass
         peak = float(peaks.get("hbm_gbs", 6650.0))
         peak_src = "measured" if "hbm_gbs" in peaks else "fallback"
-        tgt_b, draft_b = algorithmic_bytes(w4)
+        tgt_b, draft_b = algorithmic_bytes(w4, FRSPEC_VOCAB if frspec else None)
         lin_s = statistics.median(lin_ms) / 1e3
         achieved = (tgt_b + draft_b) / 1e9 / lin_s
         line = {
@@ -264,6 +276,8 @@ def run_ours(args):
                                     "(block 64, top-64 + 1 initial block + 2048-token window), draft window 1024, "
                                     "chunked prefill (2048), tree 60, "
                                     if long_ctx else
+                                    "configs[2]: config 2 with FR-Spec (draft LM head over the 32768 most frequent ids), "
+                                    if frspec else
                                     "configs[1]: 8B-shaped bf16 target + 1-layer EAGLE, tree 60 (6 iters x top-10), ")
                                    + "%d-token Zipf(1.1) prompt, batch 1, greedy" % prompt_len,
                        "replicas": world,
@@ -396,8 +410,8 @@ def main():
     ap.add_argument("--warmup", type=int, default=5)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--no-cpu-baseline", action="store_true")
-    ap.add_argument("--workload", default="config2", choices=["config2", "config4", "config5"],
-                    help="config2 = the headline bf16 workload; config4 = the same with a W4A16 GPTQ-Marlin target; "
+    ap.add_argument("--workload", default="config2", choices=["config2", "config3", "config4", "config5"],
+                    help="config2 = the headline bf16 workload; config3 = the same with an FR-Spec draft vocabulary of 32768; config4 = the same with a W4A16 GPTQ-Marlin target; "
                          "config5 = 32768-token prompt, InfLLM-v2 sparse target, draft window 1024")
     args = ap.parse_args()
     if args.warmup < 3:
