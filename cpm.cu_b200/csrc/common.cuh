@@ -123,18 +123,11 @@ struct LinearPlan {
     int ldy = 0;
     const bf16* bias = nullptr;
     float* workspace = nullptr;  // split-K partials: grid * 2 * mt * 128 floats
-    int* tickets = nullptr;      // one counter per output tile, zero between launches
+    int* tickets = nullptr;      // two counters per output tile (pieces counted, readers gone), zero between launches
     int debug = 0;               // bench-only switches, see gemm_umma.cu
     // W4A16: when wq is set the weights are 4-bit blocks in the streaming layout (see gemm_w4_umma.cu)
     const void* wq = nullptr;
-    // Optional fused epilogue: y = silu(gate) * up where gate/up rows alternate
-    // in 64-row halves of each 128-row weight tile (see make_linear_plan).
-    int epilogue = 0;
-    // Optional row-wise argmax partials (LM head): per (n_tile, m) best value/index.
-    float* amax_val = nullptr;
-    int* amax_idx = nullptr;
 };
-enum LinearEpilogue { EPI_STORE = 0, EPI_SILU_GATE = 1 };
 
 size_t linear_workspace_bytes(int mt, int grid);
 int linear_pick_mt(int M);

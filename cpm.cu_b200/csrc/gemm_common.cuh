@@ -19,7 +19,14 @@ struct LinearArgs {
     int* tickets;
     int* error;
     int debug;  // bench-only switches: 1 = skip the X loads, 2 = skip epilogue stores and the split-K fix-up
+    long long* prof;  // bench only (-DCPMCU_GEMM_PROFILE): [grid][4] clock counters, or null
 };
+
+#ifdef CPMCU_GEMM_PROFILE
+constexpr bool kGemmProf = true;
+#else
+constexpr bool kGemmProf = false;
+#endif
 
 struct SegIter {
     long long u, u_end;
@@ -218,13 +225,17 @@ __device__ __forceinline__ void run_epilogue(const LinearArgs& a, SegIter it, ui
         if (fold) {
             if (epi_tid == 0) a.tickets[2 * tile] = 0;  // every piece has been counted: ready for the next launch
         } else if (!complete && !(a.debug & (2 | 8))) {
-            __threadfence();               // this thread's partials are visible before the count
+            // release: the barrier orders every thread's partials before thread 0's fence and count
             ptx::named_bar_sync(1, 128);
             if (spread) {
-                if (epi_tid == 0) atomicAdd(&a.tickets[2 * tile], 1);
+                if (epi_tid == 0) {
+                    __threadfence();
+                    atomicAdd(&a.tickets[2 * tile], 1);
+                }
                 pend[n_pend++] = p;
             } else {
                 if (epi_tid == 0) {
+                    __threadfence();
                     const int old = atomicAdd(&a.tickets[2 * tile], 1);
                     const int last = (old == p.nseg - 1) ? 1 : 0;
                     if (last) a.tickets[2 * tile] = 0;  // ready for the next launch

@@ -21,6 +21,9 @@
 // (deterministic) and writes the bf16 result.  No CTA ever waits on another.
 #include <algorithm>
 
+#include <cstdio>
+#include <vector>
+
 #include "common.cuh"
 #include "gemm_common.cuh"
 #include "ptx.cuh"
@@ -97,6 +100,7 @@ linear_umma_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_consta
     // Weights never depend on the previous kernel: the producer fills the ring with W tiles
     // first, and only then does the CTA wait for the predecessor grid (activations, workspace).
     if (warp != 0) grid_dep_wait();
+    const long long pt_dep = kGemmProf ? clock64() : 0;
 
     if (warp == 0) {
         // ------------------------------------------------ TMA producer
@@ -190,7 +194,9 @@ linear_umma_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_consta
         // ------------------------------------------------ epilogue (128 threads)
         run_epilogue<MT, (MT < 32) ? MT : 32>(a, it, tmem_base, acc_full, acc_empty, abort_flag, s_last, warp, lane,
                                               threadIdx.x - 64, g, G);
+        if (kGemmProf && a.prof != nullptr && threadIdx.x == 64) a.prof[g * 4 + 1] = clock64() - pt_dep;  // epilogue done
     }
+    if (kGemmProf && a.prof != nullptr && warp == 1 && lane == 0) a.prof[g * 4 + 0] = clock64() - pt_dep;  // last MMA issued
 
     ptx::tc_fence_before();
     __syncthreads();
@@ -304,6 +310,29 @@ void launch_linear(const LinearPlan& p, cudaStream_t stream) {
     {
         static const char* dbg = getenv("CPMCU_LINEAR_DEBUG_ALL");
         if (dbg) a.debug = atoi(dbg);
+    }
+    a.prof = nullptr;
+    if (kGemmProf) {
+        static long long* buf = nullptr;
+        if (buf == nullptr) {
+            CUDA_CHECK(cudaMalloc(&buf, 256 * 4 * sizeof(long long)));
+            CUDA_CHECK(cudaMemset(buf, 0, 256 * 4 * sizeof(long long)));
+        }
+        a.prof = buf;
+        static int calls = 0;
+        if (++calls % 40 == 0) {
+            std::vector<long long> h(p.grid * 4);
+            CUDA_CHECK(cudaMemcpy(h.data(), buf, h.size() * sizeof(long long), cudaMemcpyDeviceToHost));
+            long long lo[2] = {h[0], h[1]}, hi[2] = {h[0], h[1]}, sum[2] = {0, 0};
+            for (int c = 0; c < p.grid; ++c) {
+                for (int k = 0; k < 2; ++k) {
+                    lo[k] = std::min(lo[k], h[c * 4 + k]); hi[k] = std::max(hi[k], h[c * 4 + k]); sum[k] += h[c * 4 + k];
+                }
+            }
+            fprintf(stderr, "gemm prof (previous launch, %d CTAs, cycles after the dependency wait): last MMA issued min %lld "
+                            "mean %lld max %lld; epilogue done min %lld mean %lld max %lld\n",
+                    p.grid, lo[0], sum[0] / p.grid, hi[0], lo[1], sum[1] / p.grid, hi[1]);
+        }
     }
     switch (p.mt) {
         case 16: launch_mt<16>(p, a, stream); break;

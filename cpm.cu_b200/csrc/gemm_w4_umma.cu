@@ -457,6 +457,7 @@ void launch_linear_w4(const LinearPlan& p, cudaStream_t stream) {
     a.error = runtime().d_error;
     static const int debug = getenv("CPMCU_LINEAR_DEBUG") ? atoi(getenv("CPMCU_LINEAR_DEBUG")) : 0;
     a.debug = debug;
+    a.prof = nullptr;
     wa.blocks = static_cast<const uint8_t*>(p.wq);
     wa.prof = kProf ? w4_prof_buffer() : nullptr;
     switch (p.mt) {
