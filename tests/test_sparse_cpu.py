@@ -61,3 +61,26 @@ def test_selection_is_off_before_the_switch():
     q = torch.zeros(1, 2 * 128)
     k = torch.zeros(512, 128)
     assert osparse.select_blocks(cfg, q, k, 300, 2, 1, 128, 301) is None
+
+
+def test_golden_selection_reproduces():
+    """tests/golden/sparse_golden.json (made by tests/golden/make_sparse_golden.py from this oracle)."""
+    import importlib.util
+    import json
+    import os
+    here = os.path.dirname(os.path.abspath(__file__))
+    spec = importlib.util.spec_from_file_location("make_sparse_golden", os.path.join(here, "golden", "make_sparse_golden.py"))
+    mod = importlib.util.module_from_spec(spec)
+    spec.loader.exec_module(mod)
+    gold = json.load(open(os.path.join(here, "golden", "sparse_golden.json")))
+    for case in gold["selection"]:
+        again = mod.selection_case(case["seed"], case["T"], case["hq"], case["hkv"], case["L"], case["top"],
+                                   case["sink"], case["window"], case["lse"])
+        assert again["mask"] == case["mask"]
+        assert abs(again["score_sum"] - case["score_sum"]) <= 1e-6 * abs(case["score_sum"])
+        # every row selects min(top, blocks) blocks and the sink blocks among them
+        blocks = (case["L"] + 63) // 64
+        for head in case["mask"]:
+            for row in head:
+                assert sum(bin(w).count("1") for w in row) == min(case["top"], blocks)
+                assert row[0] & ((1 << case["sink"]) - 1) == (1 << case["sink"]) - 1
