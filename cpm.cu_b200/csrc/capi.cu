@@ -154,9 +154,28 @@ int cpmcu_init_w4a16_gptq_marlin_base_model(float memory_limit, int vocab_size, 
         return 0;
     });
 }
-int cpmcu_init_w4a16_gptq_marlin_minicpm4_model(float, int, int, int, int, int, int, int, float, int, int, int, float,
-                                                float, float, int, int, int, int, int) {
-    return not_built("the W4A16 GPTQ-Marlin sparse target");
+int cpmcu_init_w4a16_gptq_marlin_minicpm4_model(float memory_limit, int vocab_size, int num_hidden_layers,
+                                                int hidden_size, int intermediate_size, int num_attention_heads,
+                                                int num_key_value_heads, int head_dim, float rms_norm_eps,
+                                                int group_size, int torch_dtype, int chunk_length, float scale_embed,
+                                                float scale_lmhead, float scale_residual, int sink_window_size,
+                                                int block_window_size, int sparse_topk_k, int sparse_switch,
+                                                int apply_compress_lse) {
+    // the W4A16 target with InfLLM-v2 block selection: both features are independent in the engine
+    const int rc = cpmcu_init_minicpm4_model(memory_limit, vocab_size, num_hidden_layers, hidden_size, intermediate_size,
+                                             num_attention_heads, num_key_value_heads, head_dim, rms_norm_eps, torch_dtype,
+                                             chunk_length, scale_embed, scale_lmhead, scale_residual, sink_window_size,
+                                             block_window_size, sparse_topk_k, sparse_switch, apply_compress_lse);
+    if (rc != 0) return rc;
+    return guarded([&] {
+        CPM_REQUIRE(group_size == 128, "W4A16: only group_size 128 is supported");
+        ModelConfig mc = engine().config();
+        mc.w4a16 = true;
+        mc.group_size = group_size;
+        g_engine.reset();
+        g_engine = std::make_unique<Engine>(mc);
+        return 0;
+    });
 }
 
 int cpmcu_init_eagle_model(int num_layers, int num_iter, int topk_per_iter, int tree_size, int torch_dtype) {

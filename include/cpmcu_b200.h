@@ -54,7 +54,8 @@ int cpmcu_init_minicpm4_model(float memory_limit, int vocab_size, int num_hidden
  * int32 in Marlin tile order + model-dtype scales, group_size 128).  They are re-tiled when
  * loaded (k-contiguous nibbles, group-major scales) and streamed as 4-bit by the W4A16 GEMM,
  * which dequantises w = (q - 8) * scale on the way into the tensor cores.
- * init_w4a16_gptq_marlin_minicpm4_model (:227-275, sparse + W4A16) is not built: always fails. */
+ * init_w4a16_gptq_marlin_minicpm4_model (:227-275) is the same target with the InfLLM-v2 block
+ * selection of init_minicpm4_model. */
 int cpmcu_init_w4a16_gptq_marlin_base_model(float memory_limit, int vocab_size, int num_hidden_layers,
                                             int hidden_size, int intermediate_size, int num_attention_heads,
                                             int num_key_value_heads, int head_dim, float rms_norm_eps,

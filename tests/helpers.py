@@ -97,17 +97,22 @@ def quantize_target(cfg, w):
     return w, ckpt
 
 
-def build_quant_pair(cfg, eagle, seed=0, chunk_length=256, layer_scale=0.6, fc_gain=200.0, budget=1024):
+def build_quant_pair(cfg, eagle, seed=0, chunk_length=256, layer_scale=0.6, fc_gain=200.0, budget=1024, sparse=None):
     from cpmcu.speculative.eagle_base_quant.eagle_base_w4a16_marlin_gptq import W4A16GPTQMarlinLLM_with_eagle
     import os
     w, ew = make_weights(cfg, seed, eagle, layer_scale=layer_scale, fc_mode="embed", fc_gain=fc_gain)
     wq, ckpt = quantize_target(cfg, w)
-    oracle = OracleModel(cfg, wq, eagle, ew, budget=budget)
+    oracle = OracleModel(cfg, wq, eagle, ew, budget=budget, sparse=sparse)
     hf = hf_config(cfg)
     hf.quantization_config = {"group_size": 128, "bits": 4}
+    sparse_kw = {}
+    if sparse is not None:
+        sparse_kw = dict(apply_sparse=True, sink_window_size=sparse.sink_window_size,
+                         block_window_size=sparse.block_window_size, sparse_topk_k=sparse.sparse_topk_k,
+                         sparse_switch=sparse.sparse_switch, apply_compress_lse=sparse.apply_compress_lse)
     llm = W4A16GPTQMarlinLLM_with_eagle(None, None, num_iter=eagle.num_iter, topk_per_iter=eagle.topk,
                                         tree_size=eagle.tree_size, eagle_config={"num_hidden_layers": 1}, config=hf,
-                                        dtype=torch.bfloat16, chunk_length=chunk_length, memory_limit=0.5)
+                                        dtype=torch.bfloat16, chunk_length=chunk_length, memory_limit=0.5, **sparse_kw)
     os.environ.setdefault("CPMCU_MAX_TOKENS", "4096")
     llm.init_storage()
     llm.load_state_dict_tensors({k: v.to(torch.bfloat16) for k, v in ew.items()}, cls="eagle")

@@ -255,6 +255,21 @@ def test_sparse_spec_decode_with_every_block_selected():
         assert acc == o_acc
 
 
+def test_w4a16_sparse_target_matches_oracle():
+    """init_w4a16_gptq_marlin_minicpm4_model: int4 target linears and InfLLM-v2 selection together (every block
+    selected, so that the comparison with the oracle on the dequantised weights is unambiguous)."""
+    from oracle.model import OracleConfig
+    from oracle.sparse import SparseConfig
+    cfg = OracleConfig(vocab=4096, layers=2, hidden=256, inter=768, hq=2, hkv=1, head_dim=128, dtype="bf16")
+    eagle = EagleOracleConfig(num_iter=3, topk=4, tree_size=12, window=128, minicpm4_variant=True)
+    sp = SparseConfig(sink_window_size=1, block_window_size=2, sparse_topk_k=64, sparse_switch=128, apply_compress_lse=True)
+    oracle, llm = build_quant_pair(cfg, eagle, seed=8, chunk_length=256, sparse=sp, budget=2048)
+    prompt = prompt_ids(500, cfg.vocab, 8)
+    tokens, acc, _, _ = llm.generate(torch.tensor(prompt, device="cuda"), 20)
+    o_tokens, o_acc, steps = oracle.generate_spec(prompt.tolist(), 20, chunk=256)
+    assert_stream_matches(tokens, o_tokens, steps, "w4a16 + sparse vs oracle")
+
+
 def test_errors_are_loud():
     import cpmcu.C as C
     with pytest.raises(RuntimeError):
@@ -263,8 +278,8 @@ def test_errors_are_loud():
         C.init_base_model(0.5, 1000, 1, 256, 704, 2, 1, 128, 1e-5, 0, 128, 1.0, 1.0, 1.0)  # fp16
     with pytest.raises(RuntimeError):  # group size 64 / hidden not a multiple of 128
         C.init_w4a16_gptq_marlin_base_model(0.5, 1000, 1, 256, 704, 2, 1, 128, 1e-5, 64, 1, 128, 1.0, 1.0, 1.0)
-    with pytest.raises(RuntimeError):  # sparse + W4A16 combined is not built
-        C.init_w4a16_gptq_marlin_minicpm4_model(0.5, 1000, 1, 256, 768, 2, 1, 128, 1e-5, 128, 1, 128, 1.0, 1.0, 1.0,
+    with pytest.raises(RuntimeError):  # sparse + W4A16: group size 64 is refused
+        C.init_w4a16_gptq_marlin_minicpm4_model(0.5, 1000, 1, 256, 768, 2, 1, 128, 1e-5, 64, 1, 128, 1.0, 1.0, 1.0,
                                                 1, 32, 32, 8192, False)
     C.init_base_model(0.5, 1000, 1, 256, 704, 2, 1, 128, 1e-5, 1, 128, 1.0, 1.0, 1.0)
     with pytest.raises(RuntimeError):
