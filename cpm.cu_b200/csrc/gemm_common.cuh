@@ -139,28 +139,8 @@ __device__ __forceinline__ void run_epilogue(const LinearArgs& a, SegIter it, ui
         float* my_ws = a.workspace + (static_cast<size_t>(g) * 2 + (kb0 == 0 ? 1 : 0)) * (MT * BLOCK_N);
         const float bias_v = (a.bias != nullptr && n < a.N) ? __bfloat162float(a.bias[n]) : 0.f;
 
-        PendingTile p;
-        bool spread = false, fold = false;
-        if (!complete) {
-            const long long tile_u0 = static_cast<long long>(tile) * a.kblocks;
-            p.tile = tile;
-            p.g_first = unit_owner(tile_u0, a.total_units, G);
-            p.nseg = unit_owner(tile_u0 + a.kblocks - 1, a.total_units, G) - p.g_first + 1;
-            p.m_base = m_base; p.m_cnt = m_cnt; p.n = n; p.bias = bias_v;
-            spread = (p.nseg >= 3 && m_cnt > 16);
-        }
-
         if (!ptx::mbar_wait_warp(&acc_full[acc], acc_phase, abort_flag)) break;  // also converges the warp
         ptx::tc_fence_after();
-        if (!complete && !spread && !(a.debug & (2 | 8))) {
-            // If every other piece of this tile has already been counted, this one is the last: it is added
-            // straight from the accumulator to the others' partials (in CTA order, like every other path)
-            // and never goes through the workspace.
-            if (epi_tid == 0) *s_last = (ld_acquire(&a.tickets[2 * tile]) == p.nseg - 1) ? 1 : 0;
-            ptx::named_bar_sync(1, 128);
-            fold = (*s_last != 0);
-            ptx::named_bar_sync(1, 128);  // everyone has read s_last before it can change
-        }
         const uint32_t t_addr = tmem_base + (static_cast<uint32_t>(q * 32) << 16) + acc * MT;
         // partial slot layout: [MT tokens][128 features] fp32: a warp touches one 128-byte line per token
 #pragma unroll 1
@@ -186,31 +166,6 @@ __device__ __forceinline__ void run_epilogue(const LinearArgs& a, SegIter it, ui
                         }
                     }
                 }
-            } else if (fold) {
-                // sum over the pieces in CTA order, this CTA's piece taken from the registers
-                float sum[16];
-#pragma unroll
-                for (int c = 0; c < 16; ++c) sum[c] = 0.f;
-                for (int gg = p.g_first; gg < p.g_first + p.nseg; ++gg) {
-                    if (gg == g) {
-#pragma unroll
-                        for (int c = 0; c < 16; ++c) sum[c] += __uint_as_float(r[c]);
-                    } else {
-                        const float* ws = a.workspace + (static_cast<size_t>(gg) * 2 + (gg == p.g_first ? 1 : 0)) * (MT * BLOCK_N) +
-                                          static_cast<size_t>(c0) * BLOCK_N + row;
-                        float v[16];
-#pragma unroll
-                        for (int c = 0; c < 16; ++c) v[c] = (c0 + c < m_cnt) ? __ldcg(ws + c * BLOCK_N) : 0.f;
-#pragma unroll
-                        for (int c = 0; c < 16; ++c) sum[c] += v[c];
-                    }
-                }
-                if (n < a.N) {
-#pragma unroll
-                    for (int c = 0; c < 16; ++c) {
-                        if (c0 + c < m_cnt) a.y[static_cast<size_t>(m_base + c0 + c) * a.ldy + n] = __float2bfloat16(sum[c] + bias_v);
-                    }
-                }
             } else if (!(a.debug & 4)) {
 #pragma unroll
                 for (int c = 0; c < 16; ++c) {
@@ -222,20 +177,21 @@ __device__ __forceinline__ void run_epilogue(const LinearArgs& a, SegIter it, ui
         ptx::mbar_arrive(&acc_empty[acc]);
         if (++acc == acc_stages) { acc = 0; acc_phase ^= 1; }
 
-        if (fold) {
-            if (epi_tid == 0) a.tickets[2 * tile] = 0;  // every piece has been counted: ready for the next launch
-        } else if (!complete && !(a.debug & (2 | 8))) {
-            // release: the barrier orders every thread's partials before thread 0's fence and count
+        if (!complete && !(a.debug & (2 | 8))) {
+            const long long tile_u0 = static_cast<long long>(tile) * a.kblocks;
+            PendingTile p;
+            p.tile = tile;
+            p.g_first = unit_owner(tile_u0, a.total_units, G);
+            p.nseg = unit_owner(tile_u0 + a.kblocks - 1, a.total_units, G) - p.g_first + 1;
+            p.m_base = m_base; p.m_cnt = m_cnt; p.n = n; p.bias = bias_v;
+            const bool spread = (p.nseg >= 3 && m_cnt > 16);
+            __threadfence();               // this thread's partials are visible before the count
             ptx::named_bar_sync(1, 128);
             if (spread) {
-                if (epi_tid == 0) {
-                    __threadfence();
-                    atomicAdd(&a.tickets[2 * tile], 1);
-                }
+                if (epi_tid == 0) atomicAdd(&a.tickets[2 * tile], 1);
                 pend[n_pend++] = p;
             } else {
                 if (epi_tid == 0) {
-                    __threadfence();
                     const int old = atomicAdd(&a.tickets[2 * tile], 1);
                     const int last = (old == p.nseg - 1) ? 1 : 0;
                     if (last) a.tickets[2 * tile] = 0;  // ready for the next launch

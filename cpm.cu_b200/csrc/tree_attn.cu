@@ -51,7 +51,7 @@ constexpr int SMEM_TOTAL = SMEM_XCH + 1024 + 1024;
 constexpr int TMEM_COLS = 512;  // S stage 0: [0,128), S stage 1: [128,256), O: [256,384)
 constexpr int TMEM_O = 256;
 constexpr int SOFTMAX_THREADS = 256;  // two threads per query row: warps 0-3 keys 0-63 of a tile, warps 4-7 keys 64-127
-constexpr int NTHREADS = SOFTMAX_THREADS + 128;  // + four control warps: K producer, S issuer, PV issuer, V producer
+constexpr int NTHREADS = SOFTMAX_THREADS + 32;  // + one control warp (TMA and MMA issue)
 
 struct AttnArgs {
     int tq, hq, hkv, grp, tok_per_tile, num_mtiles;
@@ -109,7 +109,7 @@ tree_attn_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant
     const int tid = threadIdx.x;
     const int warp = tid >> 5;
     const int lane = tid & 31;
-    const bool is_control = (warp >= SOFTMAX_THREADS / 32);
+    const bool is_control = (warp == SOFTMAX_THREADS / 32);
     const int ch = (warp >> 2) & 1;              // column half of the key tile
     const int row = (warp & 3) * 32 + lane;      // query row of the tile == TMEM lane
     grid_dep_trigger();
@@ -240,92 +240,83 @@ tree_attn_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant
     bool ok = true;
 
     if (is_control) {
-        // ================================================= four control warps: K / V producers, S issuer, PV issuer.
-        // Each runs its loop as a whole warp with warp-uniform control flow (waits poll on one lane) and
-        // elects one lane for the TMA / tcgen05 instructions, whose operands then stay in uniform registers;
-        // one thread doing all three jobs was the bottleneck of a key tile (2.8 us per tile, 16 MMAs + 4 TMA
-        // + 7 waits in one dependent instruction stream).
-        const int role = warp - SOFTMAX_THREADS / 32;
-        if ((role == 0 || role == 3) && n_it > 0) {
-            // ---- producers.  role 0: Q once, then K(i) as soon as S(i-2) has consumed the stage;
-            //      role 3: V(i) as soon as PV(i-2) has (separate warps: the two conditions come true at different times)
-            const bool is_k = (role == 0);
-            int tile = kt_begin;
-            bool w = true;
-            if (is_k) {
-                if (ptx::elect_one()) {
-                    ptx::mbar_arrive_expect_tx(q_bar, TILE_BYTES);
-                    ptx::tma_load_3d(smem + SMEM_Q, &tm_q, q_bar, 0, h * a.grp, t0);
-                    ptx::tma_load_3d(smem + SMEM_Q + HALF_BYTES, &tm_q, q_bar, 64, h * a.grp, t0);
-                }
-                __syncwarp();
-            }
-            uint64_t* freed = is_k ? s_bar : o_bar;
-            uint64_t* full = is_k ? k_full : v_full;
-            const CUtensorMap* tm = is_k ? &tm_k : &tm_v;
-            uint8_t* base = smem + (is_k ? SMEM_K : SMEM_V);
-            for (int i = 0; w && i < n_it; ++i) {
-                const int st = i & 1;
-                const int key0 = tile * KEYS;
-                tile = next_tile(tile);
-                if (i >= 2 && !ptx::mbar_wait_warp(&freed[st], ((i - 2) >> 1) & 1, abort_flag)) { w = false; break; }
-                if (ptx::elect_one()) {
-                    ptx::mbar_arrive_expect_tx(&full[st], TILE_BYTES);
-                    ptx::tma_load_2d(base + st * TILE_BYTES, tm, &full[st], h * D, key0);
-                    ptx::tma_load_2d(base + st * TILE_BYTES + HALF_BYTES, tm, &full[st], h * D + 64, key0);
-                }
-                __syncwarp();
-            }
-        } else if (role == 1 && n_it > 0) {
-            // ---- S issuer: S(i) = Q K(i)^T into S stage i & 1 once softmax(i-2) has read that stage
+        // ================================================= control warp: TMA + MMA issue
+        if (lane == 0 && n_it > 0) {
             const uint32_t q_addr = ptx::smem_u32(smem + SMEM_Q);
+            const uint32_t p_addr = ptx::smem_u32(smem + SMEM_P);
             constexpr uint32_t idesc_s = ptx::umma_idesc_bf16(ROWS, KEYS, 0, 0);
-            bool w = ptx::mbar_wait_warp(q_bar, 0, abort_flag);
-            for (int i = 0; w && i < n_it; ++i) {
+            constexpr uint32_t idesc_o = ptx::umma_idesc_bf16(ROWS, D, 0, 1);
+            int k_tile = kt_begin, v_tile = kt_begin;  // tiles of the next K / V load (issued in iteration order)
+            auto load_k = [&](int i) {
+                const int st = i & 1, key0 = k_tile * KEYS;
+                k_tile = next_tile(k_tile);
+                ptx::mbar_arrive_expect_tx(&k_full[st], TILE_BYTES);
+                ptx::tma_load_2d(smem + SMEM_K + st * TILE_BYTES, &tm_k, &k_full[st], h * D, key0);
+                ptx::tma_load_2d(smem + SMEM_K + st * TILE_BYTES + HALF_BYTES, &tm_k, &k_full[st], h * D + 64, key0);
+            };
+            auto load_v = [&](int i) {
+                const int st = i & 1, key0 = v_tile * KEYS;
+                v_tile = next_tile(v_tile);
+                ptx::mbar_arrive_expect_tx(&v_full[st], TILE_BYTES);
+                ptx::tma_load_2d(smem + SMEM_V + st * TILE_BYTES, &tm_v, &v_full[st], h * D, key0);
+                ptx::tma_load_2d(smem + SMEM_V + st * TILE_BYTES + HALF_BYTES, &tm_v, &v_full[st], h * D + 64, key0);
+            };
+            auto issue_s = [&](int i) -> bool {  // S(i) = Q K(i)^T into S stage i & 1
                 const int st = i & 1;
-                if (i >= 2 && !ptx::mbar_wait_warp(&p_ready[st], ((i - 2) >> 1) & 1, abort_flag)) { w = false; break; }
-                if (!ptx::mbar_wait_warp(&k_full[st], (i >> 1) & 1, abort_flag)) { w = false; break; }
+                if (!ptx::mbar_wait(&k_full[st], (i >> 1) & 1, abort_flag)) return false;
                 ptx::tc_fence_after();
                 const uint32_t k_addr = ptx::smem_u32(smem + SMEM_K + st * TILE_BYTES);
-                if (ptx::elect_one()) {
 #pragma unroll
-                    for (int dh = 0; dh < 2; ++dh) {
+                for (int dh = 0; dh < 2; ++dh) {
 #pragma unroll
-                        for (int j = 0; j < 4; ++j) {
-                            const uint64_t da = ptx::umma_desc_sw128(q_addr + dh * HALF_BYTES + j * 32, 16, 1024);
-                            const uint64_t db = ptx::umma_desc_sw128(k_addr + dh * HALF_BYTES + j * 32, 16, 1024);
-                            ptx::umma_ss(tmem_base + st * KEYS, da, db, idesc_s, (dh | j) ? 1u : 0u);
-                        }
+                    for (int j = 0; j < 4; ++j) {
+                        const uint64_t da = ptx::umma_desc_sw128(q_addr + dh * HALF_BYTES + j * 32, 16, 1024);
+                        const uint64_t db = ptx::umma_desc_sw128(k_addr + dh * HALF_BYTES + j * 32, 16, 1024);
+                        ptx::umma_ss(tmem_base + st * KEYS, da, db, idesc_s, (dh | j) ? 1u : 0u);
                     }
-                    ptx::umma_commit(&s_bar[st]);
                 }
-                __syncwarp();
+                ptx::umma_commit(&s_bar[st]);
+                return true;
+            };
+            ptx::mbar_arrive_expect_tx(q_bar, TILE_BYTES);
+            ptx::tma_load_3d(smem + SMEM_Q, &tm_q, q_bar, 0, h * a.grp, t0);
+            ptx::tma_load_3d(smem + SMEM_Q + HALF_BYTES, &tm_q, q_bar, 64, h * a.grp, t0);
+            for (int i = 0; i < 2 && i < n_it; ++i) {
+                load_k(i);
+                load_v(i);
             }
-        } else if (role == 2 && n_it > 0) {
-            // ---- PV issuer: O += P(i) V(i)
-            const uint32_t p_addr = ptx::smem_u32(smem + SMEM_P);
-            constexpr uint32_t idesc_o = ptx::umma_idesc_bf16(ROWS, D, 0, 1);
-            bool w = true;
+            bool w = ptx::mbar_wait(q_bar, 0, abort_flag);
+            for (int i = 0; w && i < 2 && i < n_it; ++i) w = issue_s(i);
             for (int i = 0; w && i < n_it; ++i) {
                 const int st = i & 1;
                 const uint32_t ph = (i >> 1) & 1;
-                if (!ptx::mbar_wait_warp(&p_ready[st], ph, abort_flag)) { w = false; break; }
-                if (!ptx::mbar_wait_warp(&v_full[st], ph, abort_flag)) { w = false; break; }
+                // K stage st is free once S(i) has been computed: fetch K(i+2)
+                if (i + 2 < n_it) {
+                    if (!ptx::mbar_wait(&s_bar[st], ph, abort_flag)) { w = false; break; }
+                    load_k(i + 2);
+                }
+                // O += P(i) V(i)
+                if (!ptx::mbar_wait(&p_ready[st], ph, abort_flag)) { w = false; break; }
+                if (!ptx::mbar_wait(&v_full[st], ph, abort_flag)) { w = false; break; }
                 ptx::tc_fence_after();
                 const uint32_t v_addr = ptx::smem_u32(smem + SMEM_V + st * TILE_BYTES);
                 const uint32_t pa = p_addr + st * TILE_BYTES;
-                if (ptx::elect_one()) {
 #pragma unroll
-                    for (int kk = 0; kk < KEYS / 16; ++kk) {
-                        // A: P, K-major: 64-key half (kk / 4), 32 B per 16-key step inside it
-                        const uint64_t da = ptx::umma_desc_sw128(pa + (kk >> 2) * HALF_BYTES + (kk & 3) * 32, 16, 1024);
-                        // B: V, N-major: 16 key rows of 128 B per step; 64-wide d halves HALF_BYTES apart
-                        const uint64_t db = ptx::umma_desc_sw128(v_addr + kk * 16 * 128, HALF_BYTES, 1024);
-                        ptx::umma_ss(tmem_base + TMEM_O, da, db, idesc_o, (i > 0 || kk > 0) ? 1u : 0u);
-                    }
-                    ptx::umma_commit(&o_bar[st]);
+                for (int kk = 0; kk < KEYS / 16; ++kk) {
+                    // A: P, K-major: 64-key half (kk / 4), 32 B per 16-key step inside it
+                    const uint64_t da = ptx::umma_desc_sw128(pa + (kk >> 2) * HALF_BYTES + (kk & 3) * 32, 16, 1024);
+                    // B: V, N-major: 16 key rows of 128 B per step; 64-wide d halves HALF_BYTES apart
+                    const uint64_t db = ptx::umma_desc_sw128(v_addr + kk * 16 * 128, HALF_BYTES, 1024);
+                    ptx::umma_ss(tmem_base + TMEM_O, da, db, idesc_o, (i > 0 || kk > 0) ? 1u : 0u);
                 }
-                __syncwarp();
+                ptx::umma_commit(&o_bar[st]);
+                // S(i+2) reuses S stage st: softmax(i) has read it (p_ready) and K(i+2) is on its way
+                if (i + 2 < n_it) {
+                    if (!issue_s(i + 2)) { w = false; break; }
+                    // V stage st is free once PV(i) has finished
+                    if (!ptx::mbar_wait(&o_bar[st], ph, abort_flag)) { w = false; break; }
+                    load_v(i + 2);
+                }
             }
         }
     } else {
