@@ -110,6 +110,8 @@ int Engine::attn_splits_for(int rows) const {
     const int grp = mc_.hq / mc_.hkv;
     const int mtiles = ceil_div(rows, 128 / grp) * mc_.hkv;
     int s = runtime().num_sms / mtiles;
+    static const char* forced = getenv("CPMCU_ATTN_SPLITS");  // bench only: sweep the number of key splits
+    if (forced && atoi(forced) >= 1) s = atoi(forced);
     return std::max(1, std::min(s, 32));
 }
 
