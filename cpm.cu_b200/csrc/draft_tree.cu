@@ -33,13 +33,13 @@ __device__ __forceinline__ int key_index(unsigned long long k) {
     return static_cast<int>(0xFFFFFFFFu - static_cast<uint32_t>(k & 0xFFFFFFFFull));
 }
 
+// Warp-wide maximum of 64-bit keys as two 32-bit hardware reductions (value half, then the index half
+// among the lanes that hold the winning value).
 __device__ __forceinline__ unsigned long long warp_max_u64(unsigned long long v) {
-#pragma unroll
-    for (int o = 16; o > 0; o >>= 1) {
-        const unsigned long long other = __shfl_xor_sync(0xffffffffu, v, o);
-        v = (other > v) ? other : v;
-    }
-    return v;
+    const uint32_t hi = static_cast<uint32_t>(v >> 32), lo = static_cast<uint32_t>(v);
+    const uint32_t H = __reduce_max_sync(0xffffffffu, hi);
+    const uint32_t L = __reduce_max_sync(0xffffffffu, hi == H ? lo : 0u);
+    return (static_cast<unsigned long long>(H) << 32) | L;
 }
 
 // ---- pass 1: per (row, segment) running max and sum of exp over bf16 logits
@@ -118,7 +118,6 @@ __global__ void lsm_local_topk_kernel(const bf16* __restrict__ logits, int ld, i
                                       unsigned long long* __restrict__ cand, const int32_t* __restrict__ row0,
                                       float2* __restrict__ rowoff) {
     grid_dependency_sync();
-    __shared__ unsigned long long sh_best[SCAN_THREADS / 32];
     __shared__ float sh_red[SCAN_THREADS / 32];
     const int row = blockIdx.y, seg = blockIdx.x;
     const float2 off = row_offset_block(stats + static_cast<size_t>(row) * nseg, nseg, sh_red);
@@ -139,21 +138,36 @@ __global__ void lsm_local_topk_kernel(const bf16* __restrict__ logits, int ld, i
         }
     }
     unsigned long long* out = cand + (static_cast<size_t>(row) * nseg + seg) * k;
+    // each warp extracts the k best of its 256 keys (no block-wide barrier per round), then warp 0 merges
+    // the 8 x k survivors; k <= 32
+    __shared__ unsigned long long wtop[SCAN_THREADS / 32][32];
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     for (int round = 0; round < k; ++round) {
         unsigned long long best = 0ull;
 #pragma unroll
         for (int j = 0; j < SEG / SCAN_THREADS; ++j) best = (keys[j] > best) ? keys[j] : best;
         best = warp_max_u64(best);
-        if ((threadIdx.x & 31) == 0) sh_best[threadIdx.x >> 5] = best;
-        __syncthreads();
-        best = sh_best[0];
-#pragma unroll
-        for (int w = 1; w < SCAN_THREADS / 32; ++w) best = (sh_best[w] > best) ? sh_best[w] : best;
-        __syncthreads();
-        if (threadIdx.x == 0) out[round] = best;
+        if (lane == 0) wtop[warp][round] = best;
 #pragma unroll
         for (int j = 0; j < SEG / SCAN_THREADS; ++j) {
             if (keys[j] == best) keys[j] = 0ull;  // keys are unique (index is part of the key)
+        }
+    }
+    __syncthreads();
+    if (warp == 0) {
+        unsigned long long mine[SCAN_THREADS / 32];
+#pragma unroll
+        for (int w = 0; w < SCAN_THREADS / 32; ++w) mine[w] = (lane < k) ? wtop[w][lane] : 0ull;
+        for (int round = 0; round < k; ++round) {
+            unsigned long long best = 0ull;
+#pragma unroll
+            for (int w = 0; w < SCAN_THREADS / 32; ++w) best = (mine[w] > best) ? mine[w] : best;
+            best = warp_max_u64(best);
+            if (lane == 0) out[round] = best;
+#pragma unroll
+            for (int w = 0; w < SCAN_THREADS / 32; ++w) {
+                if (mine[w] == best) mine[w] = 0ull;
+            }
         }
     }
 }
