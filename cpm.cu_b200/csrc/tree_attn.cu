@@ -529,6 +529,16 @@ __global__ void attn_combine_kernel(const float* __restrict__ ws_o, const float*
     const int row = blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
     const int lane = threadIdx.x & 31;
     if (row >= rows) return;
+    // the first twelve splits' partial outputs are requested before the (max, sum) pairs they are weighted
+    // with: both loads are in flight together instead of one L2 round trip after the other
+    constexpr int B = 12;
+    const float* base = ws_o + static_cast<size_t>(row) * D + lane * 4;
+    const size_t stride = static_cast<size_t>(rows) * D;
+    float4 o[B];
+#pragma unroll
+    for (int j = 0; j < B; ++j) {
+        o[j] = (j < nsplit) ? __ldcg(reinterpret_cast<const float4*>(base + j * stride)) : make_float4(0.f, 0.f, 0.f, 0.f);
+    }
     float m_s = -INFINITY, l_s = 0.f;
     if (lane < nsplit) {
         const float2 ml = *reinterpret_cast<const float2*>(ws_ml + (static_cast<size_t>(lane) * rows + row) * 2);
@@ -537,30 +547,28 @@ __global__ void attn_combine_kernel(const float* __restrict__ ws_o, const float*
     }
     float M = m_s;
 #pragma unroll
-    for (int o = 16; o > 0; o >>= 1) M = fmaxf(M, __shfl_xor_sync(0xffffffffu, M, o));
+    for (int o2 = 16; o2 > 0; o2 >>= 1) M = fmaxf(M, __shfl_xor_sync(0xffffffffu, M, o2));
     const float w_s = (m_s == -INFINITY) ? 0.f : exp2f((m_s - M) * scale_log2);
     float l = w_s * l_s;
 #pragma unroll
-    for (int o = 16; o > 0; o >>= 1) l += __shfl_xor_sync(0xffffffffu, l, o);
+    for (int o2 = 16; o2 > 0; o2 >>= 1) l += __shfl_xor_sync(0xffffffffu, l, o2);
     float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
-    const float* base = ws_o + static_cast<size_t>(row) * D + lane * 4;
-    const size_t stride = static_cast<size_t>(rows) * D;
-    for (int s0 = 0; s0 < nsplit; s0 += 4) {
-        float4 o[4];
-        float w[4];
+    for (int s0 = 0; s0 < nsplit; s0 += B) {
+        if (s0 > 0) {
 #pragma unroll
-        for (int j = 0; j < 4; ++j) {
-            const int s = s0 + j;
-            w[j] = __shfl_sync(0xffffffffu, w_s, s & 31);
-            o[j] = (s < nsplit) ? __ldcg(reinterpret_cast<const float4*>(base + s * stride)) : make_float4(0.f, 0.f, 0.f, 0.f);
-            if (s >= nsplit) w[j] = 0.f;
+            for (int j = 0; j < B; ++j) {
+                const int s = s0 + j;
+                o[j] = (s < nsplit) ? __ldcg(reinterpret_cast<const float4*>(base + s * stride)) : make_float4(0.f, 0.f, 0.f, 0.f);
+            }
         }
 #pragma unroll
-        for (int j = 0; j < 4; ++j) {
-            acc.x += w[j] * o[j].x;
-            acc.y += w[j] * o[j].y;
-            acc.z += w[j] * o[j].z;
-            acc.w += w[j] * o[j].w;
+        for (int j = 0; j < B; ++j) {
+            const int s = s0 + j;
+            const float w = (s < nsplit) ? __shfl_sync(0xffffffffu, w_s, s & 31) : 0.f;
+            acc.x += w * o[j].x;
+            acc.y += w * o[j].y;
+            acc.z += w * o[j].z;
+            acc.w += w * o[j].w;
         }
     }
     const float inv = (l > 0.f) ? 1.f / l : 0.f;
