@@ -39,12 +39,20 @@ __device__ __forceinline__ float block_sum(float v, float* sh) {
 template <bool ADD, int VPT>
 __global__ void rms_norm_kernel(bf16* __restrict__ x, int ldx, const bf16* __restrict__ delta, float delta_scale,
                                 const bf16* __restrict__ w, bf16* __restrict__ y, int ldy, int dim, float eps) {
-    grid_dependency_sync();
+    grid_dep_trigger();
     __shared__ float sh[32];
     const size_t base = static_cast<size_t>(blockIdx.x) * ldx;
     const size_t dbase = static_cast<size_t>(blockIdx.x) * dim;
     const size_t ybase = static_cast<size_t>(blockIdx.x) * ldy;
     const int nvec = dim >> 3;
+    // the norm weights never depend on the previous kernel: fetched before the dependency wait
+    uint4 wv[VPT];
+#pragma unroll
+    for (int j = 0; j < VPT; ++j) {
+        const int v = threadIdx.x + j * blockDim.x;
+        if (v < nvec) wv[j] = __ldg(reinterpret_cast<const uint4*>(w + v * 8));
+    }
+    grid_dep_wait();
     uint4 xv[VPT], dv[VPT];
 #pragma unroll
     for (int j = 0; j < VPT; ++j) {
@@ -83,9 +91,8 @@ __global__ void rms_norm_kernel(bf16* __restrict__ x, int ldx, const bf16* __res
     for (int j = 0; j < VPT; ++j) {
         const int v = threadIdx.x + j * blockDim.x;
         if (v < nvec) {
-            const uint4 wv = *reinterpret_cast<const uint4*>(w + v * 8);
             const bf16* xe = reinterpret_cast<const bf16*>(&xv[j]);
-            const bf16* we = reinterpret_cast<const bf16*>(&wv);
+            const bf16* we = reinterpret_cast<const bf16*>(&wv[j]);
             uint4 ov;
             bf16* oe = reinterpret_cast<bf16*>(&ov);
 #pragma unroll
