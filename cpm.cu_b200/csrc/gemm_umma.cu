@@ -22,6 +22,7 @@
 #include <algorithm>
 
 #include <cstdio>
+#include <cstring>
 #include <vector>
 
 #include "common.cuh"
@@ -284,6 +285,17 @@ LinearPlan make_linear_plan(const bf16* x, int x_rows, const bf16* w, int M, int
     {
         static const char* forced = getenv("CPMCU_LINEAR_GRID");  // bench only: sweep the grid size
         if (forced && atoi(forced) >= 1 && atoi(forced) <= grid_limit && atoi(forced) <= units) grid = atoi(forced);
+        // bench only: per-shape grids, "MxNxK:grid,MxNxK:grid,..."
+        static const char* per_shape = getenv("CPMCU_LINEAR_GRIDS");
+        if (per_shape) {
+            char key[64];
+            snprintf(key, sizeof(key), "%dx%dx%d:", M, N, K);
+            const char* hit = strstr(per_shape, key);
+            if (hit) {
+                const int gsz = atoi(hit + strlen(key));
+                if (gsz >= 1 && gsz <= grid_limit && gsz <= units) grid = gsz;
+            }
+        }
     }
     p.grid = static_cast<int>(grid);
     p.tm_w = make_tmap_2d(w, K, N, static_cast<uint64_t>(K) * 2, BLOCK_K, BLOCK_N);
