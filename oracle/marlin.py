@@ -5,7 +5,9 @@ converter, model_convert/convert_w4a16.py:17-82 (`get_perms`, `marlin_repack_qwe
 `marlin_permute_scales`), and the dequantisation of its kernel, `w = (q - 8) * scale`
 (src/qgemm/gptq_marlin/gptq_marlin.cu:139-162, scalar type kU4B8).  The permutation tables are the
 only constants the reference fixes for this path; the round trip quantise -> repack -> unpack is the
-known-answer test of the layout.
+known-answer test of the layout.  The layout is also checked end to end against the reference's own
+Marlin kernel: tests/test_ref_kernels_gpu.py packs weights with `marlin_pack`, runs the reference's
+gptq_marlin_gemm (oracle/ref_marlin.cu) on them and compares with the library and with x @ dequantize().
 """
 import numpy as np
 

@@ -5,9 +5,14 @@ acceptance and fix-up, and the generate loops.
 TEST INFRASTRUCTURE ONLY: imported by tests/, __graft_entry__.smoke() and the
 cpu_baseline / reference arms of bench.py.  Nothing in the product imports it.
 
-PARITY UNPINNED: the reference has no CPU implementation, no golden vectors and
-cannot be run without a GPU; this file restates its algorithm from the sources
-cited below and is not pinned against reference outputs.
+PARITY: the integer stages this file calls (oracle/tree.py, oracle/sparse.py) are
+pinned bit for bit against the reference's own kernels (tests/test_ref_golden_cpu.py).
+The float composition here (layer order, where values are rounded, attention,
+the generate loops) is UNPINNED: the reference's model classes include its
+attention code, which needs the un-vendored CUTLASS tree, so they cannot be
+compiled or run here; it is restated from the sources cited below.  The row-wise
+kernels and GEMMs it is built from are compared with the reference's own on the
+GPU in tests/test_ref_kernels_gpu.py.
 
 Numerics: `dtype="bf16"` rounds to bf16 exactly where the reference stores the
 model dtype (GEMM outputs, norm outputs, RoPE outputs, activation outputs,

@@ -2,8 +2,11 @@
 scoring, max-pooling to 64-token blocks, top-k -> bitmask, and the key visibility the block-sparse
 attention kernel derives from it (numpy / PyTorch CPU).
 
-TEST INFRASTRUCTURE ONLY (see oracle/tree.py).  PARITY UNPINNED: restated from the sources cited in
-each function; the reference has no CPU implementation or golden vectors for this path.
+TEST INFRASTRUCTURE ONLY (see oracle/tree.py).  PARITY PINNED for `compress`, `maxpool_blocks` and
+`topk_blockmask` against the reference's own kernels (bit-exact against their B200 outputs in
+tests/golden/ref_kernels_golden.json, see tests/test_ref_golden_cpu.py).  UNPINNED for `stage1_scores`
+and `block_visibility`: those restate the reference's attention code, which needs the un-vendored
+CUTLASS tree to compile, from the sources cited in each function.
 """
 import math
 

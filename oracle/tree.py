@@ -3,10 +3,13 @@
 TEST INFRASTRUCTURE ONLY: imported by tests/, __graft_entry__.smoke() and the
 cpu_baseline / reference arms of bench.py.  Nothing in the product imports it.
 
-PARITY UNPINNED: the reference ships no golden vectors, known-answer tests or
-fixtures for this path and cannot run without a GPU, so this restatement is
-anchored on the reference sources only (cited per function), not on reference
-outputs.
+PARITY PINNED against the reference's own device kernels: the reference ships no
+golden vectors for this path and has no CPU implementation, but its kernels for
+these stages compile from its own files (oracle/ref_kernels.cu, oracle/build_ref.py).
+Their outputs on a B200 are committed as tests/golden/ref_kernels_golden.json
+(generator: tests/golden/make_ref_golden.py) and tests/test_ref_golden_cpu.py holds
+this file to them bit for bit: log-softmax + top-k + frontier bookkeeping + final
+selection + tree build (with and without the FR-Spec remap), verify, emitted tokens.
 
 bf16 values are carried as numpy float32 arrays whose values are exactly
 representable in bf16; `bf16_round` performs round-to-nearest-even.
