@@ -235,6 +235,36 @@ int refk_linear(const void* x, const void* w, void* y, int M, int N, int K) {
     return finish();
 }
 
+// Times `iters` back-to-back calls of the reference's linear<T> (cuBLAS) with CUDA events, cycling through
+// `copies` weight buffers so that the weights come from HBM and not from L2.  avg_us: host float.
+int refk_bench_linear(int M, int N, int K, int copies, int iters, float* avg_us) {
+    const Stream S = ref_stream();
+    bf16 *x = nullptr, *y = nullptr, *w = nullptr;
+    const size_t wn = size_t(N) * K;
+    if (cudaMalloc(&x, size_t(M) * K * 2) != cudaSuccess || cudaMalloc(&y, size_t(M) * N * 2) != cudaSuccess ||
+        cudaMalloc(&w, wn * copies * 2) != cudaSuccess)
+        return int(cudaGetLastError());
+    cudaMemset(x, 0x3c, size_t(M) * K * 2);
+    cudaMemset(w, 0x3c, wn * copies * 2);
+    cudaEvent_t e0, e1;
+    cudaEventCreate(&e0);
+    cudaEventCreate(&e1);
+    for (int i = 0; i < 3; ++i) linear<bf16>(S, M, K, N, x, w + wn * (i % copies), y);
+    cudaEventRecord(e0, S.stream);
+    for (int i = 0; i < iters; ++i) linear<bf16>(S, M, K, N, x, w + wn * (i % copies), y);
+    cudaEventRecord(e1, S.stream);
+    const int rc = finish();
+    float ms = 0.f;
+    cudaEventElapsedTime(&ms, e0, e1);
+    *avg_us = ms * 1000.f / iters;
+    cudaEventDestroy(e0);
+    cudaEventDestroy(e1);
+    cudaFree(x);
+    cudaFree(y);
+    cudaFree(w);
+    return rc;
+}
+
 // In-place log-softmax over rows of `dim` bf16 values, then the reference's top-k of each row.
 int refk_log_softmax_topk(void* logits, int rows, int dim, int top, void* out_val, int32_t* out_pos) {
     const Stream S = ref_stream();
