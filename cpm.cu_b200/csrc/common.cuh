@@ -125,6 +125,7 @@ struct LinearPlan {
     float* workspace = nullptr;  // split-K partials: grid * 2 * mt * 128 floats
     int* tickets = nullptr;      // two counters per output tile (pieces counted, readers gone), zero between launches
     int debug = 0;               // bench-only switches, see gemm_umma.cu
+    int cluster = 0;             // > 0: CTAs per tile, pieces summed inside a thread-block cluster (bf16 path)
     // W4A16: when wq is set the weights are 4-bit blocks in the streaming layout (see gemm_w4_umma.cu)
     const void* wq = nullptr;
 };

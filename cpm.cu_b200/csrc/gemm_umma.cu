@@ -208,6 +208,268 @@ linear_umma_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_consta
     if (threadIdx.x == 0 && *abort_flag) atomicOr(a.error, ERR_GEMM_TIMEOUT);
 }
 
+// Split-K inside a thread-block cluster, for launches whose CTAs number CS per output tile: CTA `rank` of
+// cluster `n_tile` accumulates k-blocks [rank * kblocks / CS, (rank + 1) * kblocks / CS) of the tile, then the CS partial tiles
+// are summed through distributed shared memory instead of the global workspace and its tickets: every CTA
+// sends each peer that peer's share of the tokens (ceil(MT / CS), fp32 [source][token][feature] in the idle operand
+// ring), one cluster barrier, and every CTA sums and stores its own tokens in rank order, which is the
+// order the workspace path adds its pieces in.  All waits are the bounded mbarrier waits of the roles; every
+// thread reaches both cluster barriers whatever those waits returned.
+template <int MT, int CS>
+__global__ void __launch_bounds__(NUM_THREADS, 1)
+linear_umma_cluster_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_constant__ CUtensorMap tm_x,
+                           const LinearArgs a) {
+    using C = Cfg<MT>;
+    constexpr int TPR = (MT + CS - 1) / CS;   // tokens summed and stored by each rank
+    static_assert(CS * TPR * BLOCK_N * 4 <= C::STAGES * C::STAGE_BYTES, "reduction buffer exceeds the ring");
+    extern __shared__ uint8_t smem_raw[];
+    uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+    uint8_t* tiles = smem;
+    uint64_t* full = reinterpret_cast<uint64_t*>(smem + C::STAGES * C::STAGE_BYTES);
+    uint64_t* empty = full + C::STAGES;
+    uint64_t* acc_full = empty + C::STAGES;
+    uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(acc_full + 4);
+    volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
+
+    const int warp = threadIdx.x >> 5;
+    const int lane = threadIdx.x & 31;
+    const int rank = static_cast<int>(ptx::cluster_ctarank());
+    const int n_tile = blockIdx.x / CS;
+    const int kb_begin = (a.kblocks * rank) / CS, kb_end = (a.kblocks * (rank + 1)) / CS;
+    const int kpc = kb_end - kb_begin;
+    grid_dep_trigger();
+
+    if (threadIdx.x == 0) {
+        for (int s = 0; s < C::STAGES; ++s) {
+            ptx::mbar_init(&full[s], 1);
+            ptx::mbar_init(&empty[s], 1);
+        }
+        ptx::mbar_init(acc_full, 1);
+        *abort_flag = 0;
+        ptx::mbar_fence_init();
+        ptx::prefetch_tensormap(&tm_w);
+        ptx::prefetch_tensormap(&tm_x);
+    }
+    if (warp == 1) {
+        ptx::tmem_alloc(tmem_slot, C::TMEM_COLS);
+        ptx::tmem_relinquish();
+    }
+    ptx::tc_fence_before();
+    __syncthreads();
+    ptx::tc_fence_after();
+    const uint32_t tmem_base = *tmem_slot;
+    if (warp != 0) grid_dep_wait();
+
+    float v[MT];   // epilogue threads: this CTA's partial sums of feature `row`, all tokens
+#pragma unroll
+    for (int c = 0; c < MT; ++c) v[c] = 0.f;
+    const int q = warp & 3;
+    const int row = q * 32 + lane;
+
+    if (warp == 0) {
+        // ------------------------------------------------ TMA producer (W tiles first: they need no predecessor)
+        if (lane == 0) {
+            const int pre = (kpc < C::STAGES) ? kpc : C::STAGES;
+            for (int i = 0; i < pre; ++i) {
+                ptx::mbar_arrive_expect_tx(&full[i], C::STAGE_BYTES);
+                ptx::tma_load_2d(tiles + i * C::STAGE_BYTES, &tm_w, &full[i], (kb_begin + i) * BLOCK_K, n_tile * BLOCK_N);
+            }
+            grid_dep_wait();
+            int stage = 0;
+            uint32_t phase = 0;
+            bool ok = true;
+            for (int i = 0; i < kpc && ok; ++i) {
+                uint8_t* dst = tiles + stage * C::STAGE_BYTES;
+                const int kb = kb_begin + i;
+                if (i < pre) {
+                    ptx::tma_load_2d(dst + W_TILE_BYTES, &tm_x, &full[stage], kb * BLOCK_K, 0);
+                } else {
+                    if (!ptx::mbar_wait(&empty[stage], phase ^ 1, abort_flag)) { ok = false; break; }
+                    ptx::mbar_arrive_expect_tx(&full[stage], C::STAGE_BYTES);
+                    ptx::tma_load_2d(dst, &tm_w, &full[stage], kb * BLOCK_K, n_tile * BLOCK_N);
+                    ptx::tma_load_2d(dst + W_TILE_BYTES, &tm_x, &full[stage], kb * BLOCK_K, 0);
+                }
+                if (++stage == C::STAGES) { stage = 0; phase ^= 1; }
+            }
+            if (!ok) {
+                const long long t0 = clock64();   // copies already in flight land before peers reuse the ring
+                while (clock64() - t0 < 2000000LL) {}
+            }
+        } else {
+            grid_dep_wait();
+        }
+    } else if (warp == 1) {
+        // ------------------------------------------------ MMA issuer
+        if (lane == 0) {
+            constexpr uint32_t idesc = ptx::umma_idesc_bf16(BLOCK_N, MT, 0, 0);
+            int stage = 0;
+            uint32_t phase = 0;
+            bool ok = true;
+            for (int kb = kb_begin; kb < kb_end; ++kb) {
+                if (!ptx::mbar_wait(&full[stage], phase, abort_flag)) { ok = false; break; }
+                ptx::tc_fence_after();
+                const uint32_t wa = ptx::smem_u32(tiles + stage * C::STAGE_BYTES);
+                const uint32_t xa = wa + W_TILE_BYTES;
+#pragma unroll
+                for (int j = 0; j < BLOCK_K / UMMA_K; ++j) {
+                    const uint64_t da = ptx::umma_desc_sw128(wa + j * UMMA_K * 2, 16, 1024);
+                    const uint64_t db = ptx::umma_desc_sw128(xa + j * UMMA_K * 2, 16, 1024);
+                    ptx::umma_ss(tmem_base, da, db, idesc, (kb > kb_begin || j > 0) ? 1u : 0u);
+                }
+                ptx::umma_commit(&empty[stage]);
+                if (++stage == C::STAGES) { stage = 0; phase ^= 1; }
+            }
+            if (ok) ptx::umma_commit(acc_full);
+        }
+    } else {
+        // ------------------------------------------------ epilogue, part 1: partial sums out of tensor memory
+        if (ptx::mbar_wait_warp(acc_full, 0, abort_flag)) {
+            ptx::tc_fence_after();
+            const uint32_t t_addr = tmem_base + (static_cast<uint32_t>(q * 32) << 16);
+#pragma unroll
+            for (int c0 = 0; c0 < MT; c0 += 16) {
+                uint32_t r[16];
+                ptx::tmem_ld16(t_addr + c0, r);
+                ptx::tmem_wait_ld();
+#pragma unroll
+                for (int c = 0; c < 16; ++c) v[c0 + c] = __uint_as_float(r[c]);
+            }
+            ptx::tc_fence_before();
+        }
+    }
+    __syncwarp();
+    ptx::cluster_sync();   // every CTA of the cluster is past its last MMA: the operand rings are idle
+
+    float* red = reinterpret_cast<float*>(tiles);   // [CS sources][TPR tokens][128 features]
+    int m_cnt = a.M;
+    if (m_cnt > MT) m_cnt = MT;
+    if (warp >= 2) {
+        const uint32_t mine = ptx::smem_u32(red + (rank * TPR) * BLOCK_N + row);
+#pragma unroll
+        for (int d = 0; d < CS; ++d) {
+            if (d != rank) {
+                const uint32_t dst = ptx::cluster_map(mine, static_cast<uint32_t>(d));
+#pragma unroll
+                for (int tt = 0; tt < TPR; ++tt) {
+                    if (d * TPR + tt < MT) {
+                        if (d * TPR + tt < m_cnt) ptx::st_cluster_f32(dst + tt * BLOCK_N * 4, v[(d * TPR + tt) % MT]);
+                    }
+                }
+            }
+        }
+    }
+    __syncwarp();
+    ptx::cluster_sync();   // the peers' shares of this CTA's tokens have arrived
+
+    if (warp >= 2) {
+        const int n = n_tile * BLOCK_N + row;
+        const float bias_v = (a.bias != nullptr && n < a.N) ? __bfloat162float(a.bias[n]) : 0.f;
+#pragma unroll
+        for (int tt = 0; tt < TPR; ++tt) {
+            float own = 0.f;
+#pragma unroll
+            for (int d = 0; d < CS; ++d) {
+                if (d * TPR + tt < MT) {
+                    if (d == rank) own = v[(d * TPR + tt) % MT];
+                }
+            }
+            const int t = rank * TPR + tt;
+            if (t < m_cnt && n < a.N) {
+                float sum = 0.f;
+#pragma unroll
+                for (int s = 0; s < CS; ++s) sum += (s == rank) ? own : red[(s * TPR + tt) * BLOCK_N + row];
+                a.y[static_cast<size_t>(t) * a.ldy + n] = __float2bfloat16(sum + bias_v);
+            }
+        }
+    }
+
+    ptx::tc_fence_before();
+    __syncthreads();
+    if (warp == 1) {
+        ptx::tc_fence_after();
+        ptx::tmem_dealloc(tmem_base, C::TMEM_COLS);
+    }
+    if (threadIdx.x == 0 && *abort_flag) atomicOr(a.error, ERR_GEMM_TIMEOUT);
+}
+
+template <typename K>
+cudaLaunchConfig_t cluster_config(K kernel, int grid, int cs, size_t smem, cudaStream_t stream, cudaLaunchAttribute* attr) {
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = dim3(grid);
+    cfg.blockDim = dim3(NUM_THREADS);
+    cfg.dynamicSmemBytes = smem;
+    cfg.stream = stream;
+    attr[0].id = cudaLaunchAttributeClusterDimension;
+    attr[0].val.clusterDim.x = cs;
+    attr[0].val.clusterDim.y = 1;
+    attr[0].val.clusterDim.z = 1;
+    attr[1].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[1].val.programmaticStreamSerializationAllowed = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = runtime().pdl ? 2 : 1;
+    return cfg;
+}
+
+template <int MT, int CS>
+void configure_cluster_kernel() {
+    static bool configured = false;
+    if (!configured) {
+        CUDA_CHECK(cudaFuncSetAttribute(linear_umma_cluster_kernel<MT, CS>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                        Cfg<MT>::SMEM_BYTES));
+        configured = true;
+    }
+}
+
+// Clusters of CS CTAs of this kernel that the device runs at once (0 when the query fails).
+template <int MT, int CS>
+int max_active_clusters() {
+    static int cached = -1;
+    if (cached < 0) {
+        configure_cluster_kernel<MT, CS>();
+        cudaLaunchAttribute attr[2];
+        cudaLaunchConfig_t cfg = cluster_config(linear_umma_cluster_kernel<MT, CS>, CS * 32, CS, Cfg<MT>::SMEM_BYTES, nullptr, attr);
+        cfg.numAttrs = 1;
+        int n = 0;
+        if (cudaOccupancyMaxActiveClusters(&n, linear_umma_cluster_kernel<MT, CS>, &cfg) != cudaSuccess) {
+            cudaGetLastError();
+            n = 0;
+        }
+        cached = n;
+    }
+    return cached;
+}
+
+template <int MT, int CS>
+void launch_cluster(const LinearPlan& p, const LinearArgs& args, cudaStream_t stream) {
+    configure_cluster_kernel<MT, CS>();
+    cudaLaunchAttribute attr[2];
+    cudaLaunchConfig_t cfg = cluster_config(linear_umma_cluster_kernel<MT, CS>, p.grid, CS, Cfg<MT>::SMEM_BYTES, stream, attr);
+    CUDA_CHECK(cudaLaunchKernelEx(&cfg, linear_umma_cluster_kernel<MT, CS>, p.tm_w, p.tm_x, args));
+    runtime().launches++;
+}
+
+int cluster_capacity(int mt, int cs) {
+    if (cs == 2) return mt == 16 ? max_active_clusters<16, 2>() : mt == 32 ? max_active_clusters<32, 2>() : mt == 64 ? max_active_clusters<64, 2>() : 0;
+    if (cs == 3) return mt == 16 ? max_active_clusters<16, 3>() : mt == 32 ? max_active_clusters<32, 3>() : mt == 64 ? max_active_clusters<64, 3>() : 0;
+    if (cs == 4) return mt == 16 ? max_active_clusters<16, 4>() : mt == 32 ? max_active_clusters<32, 4>() : mt == 64 ? max_active_clusters<64, 4>() : 0;
+    return 0;
+}
+
+bool launch_cluster_any(const LinearPlan& p, const LinearArgs& a, cudaStream_t s) {
+    switch (p.mt * 8 + p.cluster) {
+        case 16 * 8 + 2: launch_cluster<16, 2>(p, a, s); return true;
+        case 16 * 8 + 3: launch_cluster<16, 3>(p, a, s); return true;
+        case 16 * 8 + 4: launch_cluster<16, 4>(p, a, s); return true;
+        case 32 * 8 + 3: launch_cluster<32, 3>(p, a, s); return true;
+        case 64 * 8 + 3: launch_cluster<64, 3>(p, a, s); return true;
+        case 32 * 8 + 2: launch_cluster<32, 2>(p, a, s); return true;
+        case 32 * 8 + 4: launch_cluster<32, 4>(p, a, s); return true;
+        case 64 * 8 + 2: launch_cluster<64, 2>(p, a, s); return true;
+        case 64 * 8 + 4: launch_cluster<64, 4>(p, a, s); return true;
+        default: return false;
+    }
+}
+
 template <int MT>
 void launch_mt(const LinearPlan& p, const LinearArgs& args, cudaStream_t stream) {
     using C = Cfg<MT>;
@@ -298,6 +560,29 @@ LinearPlan make_linear_plan(const bf16* x, int x_rows, const bf16* w, int M, int
         }
     }
     p.grid = static_cast<int>(grid);
+    // CS CTAs per tile with equal k ranges: sum the pieces inside a cluster when the device runs all clusters at once
+    p.cluster = 0;
+    {
+        static const bool off = getenv("CPMCU_LINEAR_NO_CLUSTER") != nullptr;
+        // the grid picker's pieces per tile first; when the device cannot hold that many clusters at once
+        // (its SMs come in groups that need not be multiples of the cluster size), fewer and longer pieces
+        int cs = (m_tiles == 1 && grid % n_tiles == 0) ? static_cast<int>(grid / n_tiles) : 0;
+        if (!off && p.mt <= 64 && cs >= 2 && cs <= 4) {
+            for (; cs >= 2; --cs) {
+                if (kblocks >= 4 * cs && cluster_capacity(p.mt, cs) >= n_tiles) {
+                    p.cluster = cs;
+                    p.grid = n_tiles * cs;
+                    break;
+                }
+            }
+        }
+        static const bool verbose = getenv("CPMCU_LINEAR_VERBOSE") != nullptr;   // bench only
+        if (verbose) {
+            fprintf(stderr, "linear plan M=%d N=%d K=%d: grid %d, %d tiles, cluster %d (device runs %d / %d / %d clusters of 2 / 3 / 4)\n",
+                    M, N, K, p.grid, n_tiles, p.cluster, cluster_capacity(p.mt <= 64 ? p.mt : 64, 2),
+                    cluster_capacity(p.mt <= 64 ? p.mt : 64, 3), cluster_capacity(p.mt <= 64 ? p.mt : 64, 4));
+        }
+    }
     p.tm_w = make_tmap_2d(w, K, N, static_cast<uint64_t>(K) * 2, BLOCK_K, BLOCK_N);
     p.tm_x = make_tmap_2d(x, K, x_rows, static_cast<uint64_t>(K) * 2, BLOCK_K, p.mt);
     return p;
@@ -346,6 +631,7 @@ void launch_linear(const LinearPlan& p, cudaStream_t stream) {
                     p.grid, lo[0], sum[0] / p.grid, hi[0], lo[1], sum[1] / p.grid, hi[1]);
         }
     }
+    if (p.cluster != 0 && launch_cluster_any(p, a, stream)) return;
     switch (p.mt) {
         case 16: launch_mt<16>(p, a, stream); break;
         case 32: launch_mt<32>(p, a, stream); break;
