@@ -87,6 +87,51 @@ void launch_kernel(void (*kernel)(KArgs...), dim3 grid, dim3 block, size_t smem,
     runtime().launches++;
 }
 
+// The same for a kernel that runs as thread-block clusters of `cluster` CTAs (grid.x a multiple of it).
+template <typename... KArgs, typename... Args>
+void launch_kernel_cluster(void (*kernel)(KArgs...), dim3 grid, dim3 block, size_t smem, cudaStream_t s, int cluster,
+                           Args&&... args) {
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = grid;
+    cfg.blockDim = block;
+    cfg.dynamicSmemBytes = smem;
+    cfg.stream = s;
+    cudaLaunchAttribute attr[2];
+    attr[0].id = cudaLaunchAttributeClusterDimension;
+    attr[0].val.clusterDim.x = cluster;
+    attr[0].val.clusterDim.y = 1;
+    attr[0].val.clusterDim.z = 1;
+    attr[1].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[1].val.programmaticStreamSerializationAllowed = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = runtime().pdl ? 2 : 1;
+    CUDA_CHECK(cudaLaunchKernelEx(&cfg, kernel, KArgs(args)...));
+    runtime().launches++;
+}
+
+// Clusters of `cluster` CTAs of this kernel that the device runs at once (0 when the query fails).  The SMs
+// come in groups that need not be multiples of the cluster size, so this can be fewer than SMs / cluster.
+template <typename... KArgs>
+int max_active_clusters(void (*kernel)(KArgs...), dim3 block, size_t smem, int cluster) {
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = dim3(cluster * 32);
+    cfg.blockDim = block;
+    cfg.dynamicSmemBytes = smem;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeClusterDimension;
+    attr[0].val.clusterDim.x = cluster;
+    attr[0].val.clusterDim.y = 1;
+    attr[0].val.clusterDim.z = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = 1;
+    int n = 0;
+    if (cudaOccupancyMaxActiveClusters(&n, kernel, &cfg) != cudaSuccess) {
+        cudaGetLastError();
+        n = 0;
+    }
+    return n;
+}
+
 // Device side of the above.  Every kernel lets its successor start launching at once
 // (the successor can only set up and read constant data until its own wait returns) and
 // waits for its predecessor before it touches anything a previous kernel may have written.

@@ -241,4 +241,57 @@ __device__ __forceinline__ void run_epilogue(const LinearArgs& a, SegIter it, ui
     }
 }
 
+// Second half of split-K inside a thread-block cluster of CS CTAs that hold the CS k-pieces of one output
+// tile (rank = piece).  Called by EVERY thread of the CTA after a cluster barrier that found all operand
+// rings idle; `epi` marks the 128 epilogue threads, whose v[] holds this CTA's partial sums of feature `row`
+// for all MT tokens.  Every CTA sends each peer that peer's share of the tokens (TPR = ceil(MT / CS)) into the
+// peer's `red` buffer (fp32 [source][token][feature], CS * TPR * 128 floats of idle shared memory), one more
+// cluster barrier, then sums and stores its own tokens in rank order: the order the workspace path adds its
+// pieces in.  No waits other than the two hardware barriers, which every thread reaches.
+template <int MT, int CS>
+__device__ __forceinline__ void cluster_reduce_store(const LinearArgs& a, const float (&v)[MT], float* red, int rank,
+                                                     int n_tile, bool epi, int row) {
+    constexpr int TPR = (MT + CS - 1) / CS;
+    int m_cnt = a.M;
+    if (m_cnt > MT) m_cnt = MT;
+    if (epi) {
+        const uint32_t mine = ptx::smem_u32(red + (rank * TPR) * BLOCK_N + row);
+#pragma unroll
+        for (int d = 0; d < CS; ++d) {
+            if (d != rank) {
+                const uint32_t dst = ptx::cluster_map(mine, static_cast<uint32_t>(d));
+#pragma unroll
+                for (int tt = 0; tt < TPR; ++tt) {
+                    if (d * TPR + tt < MT) {
+                        if (d * TPR + tt < m_cnt) ptx::st_cluster_f32(dst + tt * BLOCK_N * 4, v[(d * TPR + tt) % MT]);
+                    }
+                }
+            }
+        }
+    }
+    __syncwarp();
+    ptx::cluster_sync();   // the peers' shares of this CTA's tokens have arrived
+    if (epi) {
+        const int n = n_tile * BLOCK_N + row;
+        const float bias_v = (a.bias != nullptr && n < a.N) ? __bfloat162float(a.bias[n]) : 0.f;
+#pragma unroll
+        for (int tt = 0; tt < TPR; ++tt) {
+            float own = 0.f;
+#pragma unroll
+            for (int d = 0; d < CS; ++d) {
+                if (d * TPR + tt < MT) {
+                    if (d == rank) own = v[(d * TPR + tt) % MT];
+                }
+            }
+            const int t = rank * TPR + tt;
+            if (t < m_cnt && n < a.N) {
+                float sum = 0.f;
+#pragma unroll
+                for (int s = 0; s < CS; ++s) sum += (s == rank) ? own : red[(s * TPR + tt) * BLOCK_N + row];
+                a.y[static_cast<size_t>(t) * a.ldy + n] = __float2bfloat16(sum + bias_v);
+            }
+        }
+    }
+}
+
 }  // namespace gemm

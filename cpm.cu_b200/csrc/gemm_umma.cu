@@ -340,48 +340,7 @@ linear_umma_cluster_kernel(const __grid_constant__ CUtensorMap tm_w, const __gri
     __syncwarp();
     ptx::cluster_sync();   // every CTA of the cluster is past its last MMA: the operand rings are idle
 
-    float* red = reinterpret_cast<float*>(tiles);   // [CS sources][TPR tokens][128 features]
-    int m_cnt = a.M;
-    if (m_cnt > MT) m_cnt = MT;
-    if (warp >= 2) {
-        const uint32_t mine = ptx::smem_u32(red + (rank * TPR) * BLOCK_N + row);
-#pragma unroll
-        for (int d = 0; d < CS; ++d) {
-            if (d != rank) {
-                const uint32_t dst = ptx::cluster_map(mine, static_cast<uint32_t>(d));
-#pragma unroll
-                for (int tt = 0; tt < TPR; ++tt) {
-                    if (d * TPR + tt < MT) {
-                        if (d * TPR + tt < m_cnt) ptx::st_cluster_f32(dst + tt * BLOCK_N * 4, v[(d * TPR + tt) % MT]);
-                    }
-                }
-            }
-        }
-    }
-    __syncwarp();
-    ptx::cluster_sync();   // the peers' shares of this CTA's tokens have arrived
-
-    if (warp >= 2) {
-        const int n = n_tile * BLOCK_N + row;
-        const float bias_v = (a.bias != nullptr && n < a.N) ? __bfloat162float(a.bias[n]) : 0.f;
-#pragma unroll
-        for (int tt = 0; tt < TPR; ++tt) {
-            float own = 0.f;
-#pragma unroll
-            for (int d = 0; d < CS; ++d) {
-                if (d * TPR + tt < MT) {
-                    if (d == rank) own = v[(d * TPR + tt) % MT];
-                }
-            }
-            const int t = rank * TPR + tt;
-            if (t < m_cnt && n < a.N) {
-                float sum = 0.f;
-#pragma unroll
-                for (int s = 0; s < CS; ++s) sum += (s == rank) ? own : red[(s * TPR + tt) * BLOCK_N + row];
-                a.y[static_cast<size_t>(t) * a.ldy + n] = __float2bfloat16(sum + bias_v);
-            }
-        }
-    }
+    cluster_reduce_store<MT, CS>(a, v, reinterpret_cast<float*>(tiles), rank, n_tile, warp >= 2, row);
 
     ptx::tc_fence_before();
     __syncthreads();
@@ -390,24 +349,6 @@ linear_umma_cluster_kernel(const __grid_constant__ CUtensorMap tm_w, const __gri
         ptx::tmem_dealloc(tmem_base, C::TMEM_COLS);
     }
     if (threadIdx.x == 0 && *abort_flag) atomicOr(a.error, ERR_GEMM_TIMEOUT);
-}
-
-template <typename K>
-cudaLaunchConfig_t cluster_config(K kernel, int grid, int cs, size_t smem, cudaStream_t stream, cudaLaunchAttribute* attr) {
-    cudaLaunchConfig_t cfg = {};
-    cfg.gridDim = dim3(grid);
-    cfg.blockDim = dim3(NUM_THREADS);
-    cfg.dynamicSmemBytes = smem;
-    cfg.stream = stream;
-    attr[0].id = cudaLaunchAttributeClusterDimension;
-    attr[0].val.clusterDim.x = cs;
-    attr[0].val.clusterDim.y = 1;
-    attr[0].val.clusterDim.z = 1;
-    attr[1].id = cudaLaunchAttributeProgrammaticStreamSerialization;
-    attr[1].val.programmaticStreamSerializationAllowed = 1;
-    cfg.attrs = attr;
-    cfg.numAttrs = runtime().pdl ? 2 : 1;
-    return cfg;
 }
 
 template <int MT, int CS>
@@ -420,21 +361,12 @@ void configure_cluster_kernel() {
     }
 }
 
-// Clusters of CS CTAs of this kernel that the device runs at once (0 when the query fails).
 template <int MT, int CS>
 int max_active_clusters() {
     static int cached = -1;
     if (cached < 0) {
         configure_cluster_kernel<MT, CS>();
-        cudaLaunchAttribute attr[2];
-        cudaLaunchConfig_t cfg = cluster_config(linear_umma_cluster_kernel<MT, CS>, CS * 32, CS, Cfg<MT>::SMEM_BYTES, nullptr, attr);
-        cfg.numAttrs = 1;
-        int n = 0;
-        if (cudaOccupancyMaxActiveClusters(&n, linear_umma_cluster_kernel<MT, CS>, &cfg) != cudaSuccess) {
-            cudaGetLastError();
-            n = 0;
-        }
-        cached = n;
+        cached = ::max_active_clusters(linear_umma_cluster_kernel<MT, CS>, dim3(NUM_THREADS), Cfg<MT>::SMEM_BYTES, CS);
     }
     return cached;
 }
@@ -442,10 +374,8 @@ int max_active_clusters() {
 template <int MT, int CS>
 void launch_cluster(const LinearPlan& p, const LinearArgs& args, cudaStream_t stream) {
     configure_cluster_kernel<MT, CS>();
-    cudaLaunchAttribute attr[2];
-    cudaLaunchConfig_t cfg = cluster_config(linear_umma_cluster_kernel<MT, CS>, p.grid, CS, Cfg<MT>::SMEM_BYTES, stream, attr);
-    CUDA_CHECK(cudaLaunchKernelEx(&cfg, linear_umma_cluster_kernel<MT, CS>, p.tm_w, p.tm_x, args));
-    runtime().launches++;
+    launch_kernel_cluster(linear_umma_cluster_kernel<MT, CS>, dim3(p.grid), dim3(NUM_THREADS), Cfg<MT>::SMEM_BYTES, stream,
+                          CS, p.tm_w, p.tm_x, args);
 }
 
 int cluster_capacity(int mt, int cs) {

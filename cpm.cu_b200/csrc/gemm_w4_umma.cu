@@ -102,7 +102,9 @@ __device__ __forceinline__ uint32_t lop3_and_or(uint32_t a, uint32_t b, uint32_t
     return r;
 }
 
-template <int MT>
+// CS > 0: the launch runs as clusters of CS CTAs, cluster = output tile, rank = k-piece of it, and the pieces are
+// summed through distributed shared memory (cluster_reduce_store) instead of the workspace and its tickets.
+template <int MT, int CS>
 __global__ void __launch_bounds__(NUM_THREADS, 1)
 linear_w4_umma_kernel(const __grid_constant__ CUtensorMap tm_x, const W4Args wa) {
     using C = Cfg<MT>;
@@ -160,6 +162,16 @@ linear_w4_umma_kernel(const __grid_constant__ CUtensorMap tm_x, const W4Args wa)
     it.u = (a.total_units * g) / G;
     it.u_end = (a.total_units * (g + 1)) / G;
     it.kblocks = a.kblocks;
+    const int c_rank = (CS > 0) ? static_cast<int>(ptx::cluster_ctarank()) : 0;
+    const int c_tile = (CS > 0) ? g / CS : 0;
+    if (CS > 0) {
+        it.u = static_cast<long long>(c_tile) * a.kblocks + (a.kblocks * c_rank) / CS;
+        it.u_end = static_cast<long long>(c_tile) * a.kblocks + (a.kblocks * (c_rank + 1)) / CS;
+    }
+    constexpr int VN = (CS > 0) ? MT : 1;
+    float v[VN];   // cluster mode, epilogue threads: this CTA's partial sums of one feature, all tokens
+#pragma unroll
+    for (int c = 0; c < VN; ++c) v[c] = 0.f;
 
     if (warp == 0) {
         // ------------------------------------------------ W producer (weights only: runs ahead of the dependency wait)
@@ -356,8 +368,32 @@ linear_w4_umma_kernel(const __grid_constant__ CUtensorMap tm_x, const W4Args wa)
     } else {
         // ------------------------------------------------ epilogue (warps 2-5)
         grid_dep_wait();
-        run_epilogue<MT, (MT < 16) ? MT : 16>(a, it, tmem_base, acc_full, acc_empty, abort_flag, s_last, warp, lane,
-                                              threadIdx.x - 64, g, G, C::ACC2_OFF, C::ACC_STAGES);
+        if constexpr (CS == 0) {
+            run_epilogue<MT, (MT < 16) ? MT : 16>(a, it, tmem_base, acc_full, acc_empty, abort_flag, s_last, warp, lane,
+                                                  threadIdx.x - 64, g, G, C::ACC2_OFF, C::ACC_STAGES);
+        } else {
+            if (ptx::mbar_wait_warp(&acc_full[0], 0, abort_flag)) {
+                ptx::tc_fence_after();
+                const uint32_t t_addr = tmem_base + (static_cast<uint32_t>((warp & 3) * 32) << 16);
+#pragma unroll
+                for (int c0 = 0; c0 < MT; c0 += 16) {
+                    uint32_t r[16], r2[16];
+                    ptx::tmem_ld16(t_addr + c0, r);
+                    ptx::tmem_ld16(t_addr + C::ACC2_OFF + c0, r2);
+                    ptx::tmem_wait_ld();
+#pragma unroll
+                    for (int c = 0; c < 16; ++c) v[(c0 + c) % VN] = __uint_as_float(r[c]) + __uint_as_float(r2[c]);
+                }
+                ptx::tc_fence_before();
+            }
+        }
+    }
+    if constexpr (CS > 0) {
+        static_assert(CS * ((MT + CS - 1) / CS) * BLOCK_N * 4 <= C::W_STAGES * W_STAGE_BYTES, "reduction buffer exceeds the weight ring");
+        __syncwarp();
+        ptx::cluster_sync();   // every CTA of the cluster is past its last MMA and dequant pass: the weight rings are idle
+        const bool epi = (warp >= 2 && warp < 6);
+        cluster_reduce_store<MT, CS>(a, v, reinterpret_cast<float*>(smem + C::OFF_W), c_rank, c_tile, epi, (warp & 3) * 32 + lane);
     }
 
     ptx::tc_fence_before();
@@ -383,16 +419,67 @@ long long* w4_prof_buffer() {
     return buf;
 }
 
-template <int MT>
-void launch_mt(const LinearPlan& p, const W4Args& args, cudaStream_t stream) {
-    using C = Cfg<MT>;
+template <int MT, int CS>
+void configure_kernel() {
     static bool configured = false;
     if (!configured) {
-        CUDA_CHECK(cudaFuncSetAttribute(linear_w4_umma_kernel<MT>, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                        C::SMEM_BYTES));
+        CUDA_CHECK(cudaFuncSetAttribute(linear_w4_umma_kernel<MT, CS>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                        Cfg<MT>::SMEM_BYTES));
         configured = true;
     }
-    launch_kernel(linear_w4_umma_kernel<MT>, dim3(p.grid), dim3(NUM_THREADS), C::SMEM_BYTES, stream, p.tm_x, args);
+}
+
+template <int MT>
+void launch_mt(const LinearPlan& p, const W4Args& args, cudaStream_t stream) {
+    configure_kernel<MT, 0>();
+    launch_kernel(linear_w4_umma_kernel<MT, 0>, dim3(p.grid), dim3(NUM_THREADS), Cfg<MT>::SMEM_BYTES, stream, p.tm_x, args);
+}
+
+template <int MT, int CS>
+void launch_cluster(const LinearPlan& p, const W4Args& args, cudaStream_t stream) {
+    configure_kernel<MT, CS>();
+    launch_kernel_cluster(linear_w4_umma_kernel<MT, CS>, dim3(p.grid), dim3(NUM_THREADS), Cfg<MT>::SMEM_BYTES, stream, CS,
+                          p.tm_x, args);
+}
+
+template <int MT, int CS>
+int capacity() {
+    static int cached = -1;
+    if (cached < 0) {
+        configure_kernel<MT, CS>();
+        cached = max_active_clusters(linear_w4_umma_kernel<MT, CS>, dim3(NUM_THREADS), Cfg<MT>::SMEM_BYTES, CS);
+    }
+    return cached;
+}
+
+int cluster_capacity(int mt, int cs) {
+    switch (mt * 8 + cs) {
+        case 16 * 8 + 2: return capacity<16, 2>();
+        case 16 * 8 + 3: return capacity<16, 3>();
+        case 16 * 8 + 4: return capacity<16, 4>();
+        case 32 * 8 + 2: return capacity<32, 2>();
+        case 32 * 8 + 3: return capacity<32, 3>();
+        case 32 * 8 + 4: return capacity<32, 4>();
+        case 64 * 8 + 2: return capacity<64, 2>();
+        case 64 * 8 + 3: return capacity<64, 3>();
+        case 64 * 8 + 4: return capacity<64, 4>();
+        default: return 0;
+    }
+}
+
+bool launch_cluster_any(const LinearPlan& p, const W4Args& a, cudaStream_t s) {
+    switch (p.mt * 8 + p.cluster) {
+        case 16 * 8 + 2: launch_cluster<16, 2>(p, a, s); return true;
+        case 16 * 8 + 3: launch_cluster<16, 3>(p, a, s); return true;
+        case 16 * 8 + 4: launch_cluster<16, 4>(p, a, s); return true;
+        case 32 * 8 + 2: launch_cluster<32, 2>(p, a, s); return true;
+        case 32 * 8 + 3: launch_cluster<32, 3>(p, a, s); return true;
+        case 32 * 8 + 4: launch_cluster<32, 4>(p, a, s); return true;
+        case 64 * 8 + 2: launch_cluster<64, 2>(p, a, s); return true;
+        case 64 * 8 + 3: launch_cluster<64, 3>(p, a, s); return true;
+        case 64 * 8 + 4: launch_cluster<64, 4>(p, a, s); return true;
+        default: return false;
+    }
 }
 
 }  // namespace
@@ -437,6 +524,22 @@ LinearPlan make_linear_plan_w4(const bf16* x, int x_rows, const void* wq, int M,
         grid = best;
     }
     p.grid = static_cast<int>(grid);
+    // pieces of a tile summed inside a thread-block cluster when the device runs all the clusters at once
+    // (same rule as the bf16 path; a piece is at least one 256-k unit)
+    p.cluster = 0;
+    {
+        static const bool off = getenv("CPMCU_LINEAR_NO_CLUSTER") != nullptr;
+        int cs = (m_tiles == 1 && grid % n_tiles == 0) ? static_cast<int>(grid / n_tiles) : 0;
+        if (!off && p.mt <= 64 && cs >= 2 && cs <= 4) {
+            for (; cs >= 2; --cs) {
+                if (units_per_tile >= cs && cluster_capacity(p.mt, cs) >= n_tiles) {
+                    p.cluster = cs;
+                    p.grid = n_tiles * cs;
+                    break;
+                }
+            }
+        }
+    }
     // tokens as (64 k, rows, k-blocks): one box = the four k-blocks of a unit, each a 128-byte-swizzled tile
     p.tm_x = make_tmap_3d(x, BLOCK_K, x_rows, K / BLOCK_K, static_cast<uint64_t>(K) * 2, BLOCK_K * 2, BLOCK_K, p.mt,
                           KB_PER_UNIT);
@@ -460,6 +563,7 @@ void launch_linear_w4(const LinearPlan& p, cudaStream_t stream) {
     a.prof = nullptr;
     wa.blocks = static_cast<const uint8_t*>(p.wq);
     wa.prof = kProf ? w4_prof_buffer() : nullptr;
+    if (p.cluster != 0 && launch_cluster_any(p, wa, stream)) return;
     switch (p.mt) {
         case 16: launch_mt<16>(p, wa, stream); break;
         case 32: launch_mt<32>(p, wa, stream); break;
