@@ -294,7 +294,7 @@ def run_ours(args):
             "profile_eager_step_ms": {"total": statistics.median(prof_total), "linear": statistics.median(lin_ms),
                                       "attention": statistics.median(att_ms),
                                       "block_selection": statistics.median(sel_ms), "linear_launches": lin_n},
-            "roofline": {"bound": "hbm", "kernel": "linear_umma_kernel%s (all %d launches of a step)"
+            "roofline": {"bound": "hbm", "kernel": "linear_umma_kernel + linear_umma_cluster_kernel%s (all %d launches of a step)"
                                                    % (" + linear_w4_umma_kernel" if w4 else "", lin_n),
                          "achieved": achieved, "peak": peak, "unit": "GB/s", "frac": achieved / peak,
                          "peak_source": peak_src,
