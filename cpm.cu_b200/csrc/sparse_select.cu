@@ -72,7 +72,7 @@ __global__ void sparse_commit_kernel(const int32_t* __restrict__ kv_len, int kv_
 //                 q.k over the LSE keys; the score kernel merges the chunks
 //   score kernel  grid (ceil(T / 8), hkv, key chunks of 128): exp(q.k1 - max) / sum, summed over the group's
 //                 heads, one 16-key fragment per warp
-constexpr int S1_THREADS = 256, S1_TOK = 8, S1_MAXGRP = 16, S1_QLD = 128 + 8;
+constexpr int S1_THREADS = 256, S1_MAXGRP = 16, S1_QLD = 128 + 8;
 
 struct Stage1Args {
     const bf16* q;       // token t, head h at q + t * q_ld + h * 128
@@ -91,7 +91,10 @@ struct Stage1Args {
     int score_ld, T;
 };
 
-// Q rows of up to 8 tokens x 16 heads of KV group g as bf16 [8][16][S1_QLD] (zero rows beyond grp / T).
+// Q rows of up to S1_TOK tokens x 16 heads of KV group g as bf16 [S1_TOK][16][S1_QLD] (zero rows beyond grp / T).
+// S1_TOK = tokens per CTA: 8 for prefill chunks (key fragments reused eight times), 2 for decode-sized launches,
+// where the per-warp token loop is the critical path and a four times larger grid shortens it.
+template <int S1_TOK>
 __device__ __forceinline__ void s1_load_q(const Stage1Args& a, int t0, int g, int t_end, bf16* q_s) {
     for (int i = threadIdx.x; i < S1_TOK * S1_MAXGRP * 16; i += S1_THREADS) {
         const int c = (i & 15) * 8, h = (i >> 4) & 15, tt = i >> 8;
@@ -127,6 +130,7 @@ __device__ __forceinline__ void s1_frag_scores(const bf16* q_tok, const KeyFrag 
     __syncwarp();
 }
 
+template <int S1_TOK>
 __global__ void __launch_bounds__(S1_THREADS) sparse_stage1_lse_kernel(const Stage1Args a) {
     grid_dependency_sync();
     __shared__ __align__(32) bf16 q_s[S1_TOK * S1_MAXGRP * S1_QLD];
@@ -141,18 +145,19 @@ __global__ void __launch_bounds__(S1_THREADS) sparse_stage1_lse_kernel(const Sta
     if (t0 >= t_end) return;
     const int nl = compressed_len(L, a.lse_stride);
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-    s1_load_q(a, t0, g, t_end, q_s);
+    if (blockIdx.z * 128 >= nl) return;
+    const int f = blockIdx.z * (S1_THREADS / 32) + warp;  // one 16-key fragment per warp
+    // the key fragment is requested before the query rows: both global round trips overlap
+    KeyFrag fb[8];
+    if (f * 16 < nl) s1_load_keys(a.c_lse + static_cast<size_t>(f) * 16 * a.kv_dim + g * 128, a.kv_dim, fb);
+    s1_load_q<S1_TOK>(a, t0, g, t_end, q_s);
     __syncthreads();
     // lane: head h = lane & 15, keys (lane >> 4) * 8 .. + 7 of the fragment
     const int h = lane & 15, kh = lane >> 4;
     float m[S1_TOK], s[S1_TOK];
 #pragma unroll
     for (int tt = 0; tt < S1_TOK; ++tt) { m[tt] = -INFINITY; s[tt] = 0.f; }
-    if (blockIdx.z * 128 >= nl) return;
-    const int f = blockIdx.z * (S1_THREADS / 32) + warp;  // one 16-key fragment per warp
     if (f * 16 < nl) {
-        KeyFrag fb[8];
-        s1_load_keys(a.c_lse + static_cast<size_t>(f) * 16 * a.kv_dim + g * 128, a.kv_dim, fb);
 #pragma unroll
         for (int tt = 0; tt < S1_TOK; ++tt) {
             s1_frag_scores(q_s + tt * S1_MAXGRP * S1_QLD, fb, frag[warp]);
@@ -198,6 +203,7 @@ __global__ void __launch_bounds__(S1_THREADS) sparse_stage1_lse_kernel(const Sta
     }
 }
 
+template <int S1_TOK>
 __global__ void __launch_bounds__(S1_THREADS) sparse_stage1_score_kernel(const Stage1Args a) {
     grid_dependency_sync();
     __shared__ __align__(32) bf16 q_s[S1_TOK * S1_MAXGRP * S1_QLD];
@@ -213,7 +219,9 @@ __global__ void __launch_bounds__(S1_THREADS) sparse_stage1_score_kernel(const S
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int key0 = (blockIdx.z * (S1_THREADS / 32) + warp) * 16;  // this warp's 16 keys
     if (blockIdx.z * 128 >= k_round) return;
-    s1_load_q(a, t0, g, t_end, q_s);
+    KeyFrag fb[8];   // requested before the query rows and the LSE partials: the global round trips overlap
+    if (key0 < n1) s1_load_keys(a.c1 + static_cast<size_t>(key0) * a.kv_dim + g * 128, a.kv_dim, fb);
+    s1_load_q<S1_TOK>(a, t0, g, t_end, q_s);
     if (threadIdx.x < S1_TOK * S1_MAXGRP) {
         // merge the chunk partials of this (token, head): (max, 1 / exp-sum) over all LSE keys
         const int tt = threadIdx.x >> 4, hh = threadIdx.x & 15;
@@ -233,8 +241,6 @@ __global__ void __launch_bounds__(S1_THREADS) sparse_stage1_score_kernel(const S
     }
     __syncthreads();
     const int key = lane & 15, hh0 = (lane >> 4) * 8;  // lane: one key, eight of the sixteen heads
-    KeyFrag fb[8];
-    if (key0 < n1) s1_load_keys(a.c1 + static_cast<size_t>(key0) * a.kv_dim + g * 128, a.kv_dim, fb);
 #pragma unroll 1
     for (int tt = 0; tt < S1_TOK; ++tt) {
         if (t0 + tt >= t_end) break;
@@ -296,27 +302,30 @@ __device__ __forceinline__ unsigned long long pooled_key(const PoolArgs& a, cons
     return score_key(v, k);
 }
 
-// One warp per (kv head, token) row for up to 32 * PER blocks (block k lives in lane k % 32, slot k / 32).
-// The row's scores are staged in shared memory (coalesced).  Instead of extracting one maximum per round,
-// the k-th largest 16-bit score is found by a bitwise binary search with warp-wide counts (16 steps),
-// every block above it is taken, and the remaining picks among the blocks equal to it go to the lowest
-// indices (ballot + prefix count in index order): the same set as "value descending, lower index first".
-// The mask words are then just ballots of the per-slot decisions.  grid (ceil(T / 4), hkv), 128 threads.
-template <int PER>
-__global__ void __launch_bounds__(128) sparse_pool_topk_warp_kernel(const PoolArgs a) {
+// One CTA of 128 threads per (kv head, token) row for up to 128 * PB blocks; thread i owns the PB consecutive
+// blocks i * PB ...  The row's scores are staged in shared memory (coalesced).  Instead of extracting one
+// maximum per round, the k-th largest 16-bit score is found by a bitwise binary search with block-wide counts
+// (16 steps, one barrier each), every block above it is taken, and the remaining picks among the blocks equal
+// to it go to the lowest indices (exclusive scan of the per-thread counts in thread = index order): the same
+// set as "value descending, lower index first".  grid (T, hkv).
+template <int PB>
+__global__ void __launch_bounds__(128) sparse_pool_topk_block_kernel(const PoolArgs a) {
     grid_dependency_sync();
-    __shared__ __align__(16) bf16 row_s[4][32 * PER * 4 + 128];
-    const int lane = threadIdx.x & 31, wid = threadIdx.x >> 5;
-    const int t = blockIdx.x * 4 + wid, g = blockIdx.y;
-    if (t >= a.T) return;
+    constexpr int CAP = 128 * PB * 4 + 128;   // staged scores: four per block and the pooling halo
+    __shared__ __align__(16) bf16 row_s[CAP];
+    __shared__ uint32_t s_cnt[2][4];
+    __shared__ uint32_t s_tot[2][4];
+    __shared__ unsigned long long s_words[PB * 2];
+    const int tid = threadIdx.x, lane = tid & 31, wid = tid >> 5;
+    const int t = blockIdx.x, g = blockIdx.y;
     uint64_t* out = a.blockmask + (static_cast<size_t>(g) * a.T + t) * a.bm_words;
     const int L = *a.kv_len + a.kv_add;
     if (!selection_active(L, a.sparse_switch, a.compress_lse)) {
-        for (int w = lane; w < a.bm_words; w += 32) out[w] = ~0ull;
+        for (int w = tid; w < a.bm_words; w += 128) out[w] = ~0ull;
         return;
     }
     if (a.n_valid != nullptr && t >= *a.n_valid) {
-        for (int w = lane; w < a.bm_words; w += 32) out[w] = 0ull;
+        for (int w = tid; w < a.bm_words; w += 128) out[w] = 0ull;
         return;
     }
     const int n1 = compressed_len(L, C1_STRIDE);
@@ -324,54 +333,68 @@ __global__ void __launch_bounds__(128) sparse_pool_topk_warp_kernel(const PoolAr
     const int out_len = (L + BLOCK - 1) / BLOCK;
     const int q_block = (t + L) / BLOCK;
     const bf16* in = a.scores + (static_cast<size_t>(g) * a.T + t) * a.score_ld;
-    bf16* mine_s = row_s[wid];
-    for (int i = lane * 8; i < k_len && i < 32 * PER * 4 + 128; i += 256) {
-        *reinterpret_cast<uint4*>(mine_s + i) = *reinterpret_cast<const uint4*>(in + i);
+    for (int i = tid * 8; i < k_len && i < CAP; i += 1024) {
+        *reinterpret_cast<uint4*>(row_s + i) = *reinterpret_cast<const uint4*>(in + i);
     }
-    __syncwarp();
-    uint32_t val[PER];  // orderable 16-bit score of block j * 32 + lane, 0 = no such block
+    if (tid < PB * 2) s_words[tid] = 0ull;
+    __syncthreads();
+    uint32_t val[PB];  // orderable 16-bit score of block tid * PB + j, 0 = no such block
     uint32_t valid = 0;
 #pragma unroll
-    for (int j = 0; j < PER; ++j) {
-        const int k = j * 32 + lane;
-        val[j] = (k < out_len) ? static_cast<uint32_t>(pooled_key(a, mine_s, k, k_len, q_block) >> 32) : 0u;
+    for (int j = 0; j < PB; ++j) {
+        const int k = tid * PB + j;
+        val[j] = (k < out_len) ? static_cast<uint32_t>(pooled_key(a, row_s, k, k_len, q_block) >> 32) : 0u;
         valid += val[j] != 0u;
     }
-    const uint32_t total = __reduce_add_sync(0xffffffffu, valid);
+    // block-wide sum of a per-thread count; `slot` alternates so that one barrier per call is enough
+    auto block_sum = [&](uint32_t v, int slot) {
+        v = __reduce_add_sync(0xffffffffu, v);
+        if (lane == 0) s_cnt[slot][wid] = v;
+        __syncthreads();
+        return s_cnt[slot][0] + s_cnt[slot][1] + s_cnt[slot][2] + s_cnt[slot][3];
+    };
+    const uint32_t total = block_sum(valid, 0);
     uint32_t kth = 1u;                 // everything valid is taken when there are at most topk blocks
     uint32_t need = 0xffffffffu;       // picks left for the blocks equal to kth
-    if (total > static_cast<uint32_t>(a.topk)) {
+    if (total > static_cast<uint32_t>(a.topk)) {   // uniform across the CTA
         kth = 0u;
         for (int bit = 15; bit >= 0; --bit) {
             const uint32_t cand = kth | (1u << bit);
             uint32_t c = 0;
 #pragma unroll
-            for (int j = 0; j < PER; ++j) c += val[j] >= cand;
-            if (__reduce_add_sync(0xffffffffu, c) >= static_cast<uint32_t>(a.topk)) kth = cand;
+            for (int j = 0; j < PB; ++j) c += val[j] >= cand;
+            if (block_sum(c, bit & 1) >= static_cast<uint32_t>(a.topk)) kth = cand;   // slots 1, 0, 1, ... after the 0 above
         }
         uint32_t gt = 0;
 #pragma unroll
-        for (int j = 0; j < PER; ++j) gt += val[j] > kth;
-        need = static_cast<uint32_t>(a.topk) - __reduce_add_sync(0xffffffffu, gt);
+        for (int j = 0; j < PB; ++j) gt += val[j] > kth;
+        need = static_cast<uint32_t>(a.topk) - block_sum(gt, 1);
     }
-    uint32_t halves[PER];  // ballot of slot j = bits 32 (j & 1) .. + 31 of mask word j / 2
+    // blocks equal to kth before this thread's, in index order
+    uint32_t eq = 0;
 #pragma unroll
-    for (int j = 0; j < PER; ++j) {
-        const bool eq = (val[j] == kth) && (val[j] != 0u);
-        const uint32_t b = __ballot_sync(0xffffffffu, eq);
-        const uint32_t rank = __popc(b & ((1u << lane) - 1u));
-        const bool take = (val[j] > kth) || (eq && rank < need);
-        const uint32_t n_eq = __popc(b);
-        need = (need == 0xffffffffu) ? need : (need > n_eq ? need - n_eq : 0u);
-        halves[j] = __ballot_sync(0xffffffffu, take);
-    }
+    for (int j = 0; j < PB; ++j) eq += (val[j] == kth) && (val[j] != 0u);
+    uint32_t incl = eq;
 #pragma unroll
-    for (int w = 0; w < PER / 2; ++w) {
-        if (lane == (w & 31) && w < a.bm_words) {
-            out[w] = (static_cast<uint64_t>(halves[2 * w + 1]) << 32) | halves[2 * w];
-        }
+    for (int o = 1; o < 32; o <<= 1) {
+        const uint32_t up = __shfl_up_sync(0xffffffffu, incl, o);
+        if (lane >= o) incl += up;
     }
-    for (int w = PER / 2 + lane; w < a.bm_words; w += 32) out[w] = 0ull;
+    if (lane == 31) s_tot[0][wid] = incl;
+    __syncthreads();
+    uint32_t rank = incl - eq;
+    for (int w = 0; w < wid; ++w) rank += s_tot[0][w];
+    uint32_t bits = 0;
+#pragma unroll
+    for (int j = 0; j < PB; ++j) {
+        const bool is_eq = (val[j] == kth) && (val[j] != 0u);
+        const bool take = (val[j] > kth) || (is_eq && (need == 0xffffffffu || rank < need));
+        rank += is_eq;
+        bits |= static_cast<uint32_t>(take) << j;
+    }
+    if (bits) atomicOr(&s_words[(tid * PB) >> 6], static_cast<unsigned long long>(bits) << ((tid * PB) & 63));
+    __syncthreads();
+    for (int w = tid; w < a.bm_words; w += 128) out[w] = (w < PB * 2) ? s_words[w] : 0ull;
 }
 
 __global__ void __launch_bounds__(PT_THREADS) sparse_pool_topk_kernel(const PoolArgs a) {
@@ -473,9 +496,14 @@ void launch_sparse_select(const SparseBuffers& b, const SparseConfig& cfg, int l
     a.scores = b.scores; a.score_ld = b.score_ld; a.T = T;
     a.lse = b.lse;
     a.lse_chunks = b.score_ld / 128;
-    launch_kernel(sparse_stage1_lse_kernel, dim3(ceil_div(T, S1_TOK), hkv, cfg.compress_lse ? ceil_div(a.lse_chunks, 4) : a.lse_chunks),
-                  dim3(S1_THREADS), 0, s, a);
-    launch_kernel(sparse_stage1_score_kernel, dim3(ceil_div(T, S1_TOK), hkv, b.score_ld / 128), dim3(S1_THREADS), 0, s, a);
+    const int lse_z = cfg.compress_lse ? ceil_div(a.lse_chunks, 4) : a.lse_chunks;
+    if (T <= 64) {
+        launch_kernel(sparse_stage1_lse_kernel<2>, dim3(ceil_div(T, 2), hkv, lse_z), dim3(S1_THREADS), 0, s, a);
+        launch_kernel(sparse_stage1_score_kernel<2>, dim3(ceil_div(T, 2), hkv, b.score_ld / 128), dim3(S1_THREADS), 0, s, a);
+    } else {
+        launch_kernel(sparse_stage1_lse_kernel<8>, dim3(ceil_div(T, 8), hkv, lse_z), dim3(S1_THREADS), 0, s, a);
+        launch_kernel(sparse_stage1_score_kernel<8>, dim3(ceil_div(T, 8), hkv, b.score_ld / 128), dim3(S1_THREADS), 0, s, a);
+    }
     PoolArgs p;
     p.scores = b.scores; p.score_ld = b.score_ld; p.T = T;
     p.kv_len = kv_len; p.kv_add = kv_add; p.n_valid = n_valid;
@@ -485,9 +513,9 @@ void launch_sparse_select(const SparseBuffers& b, const SparseConfig& cfg, int l
     CPM_REQUIRE(b.bm_words <= 64, "sparse selection: at most 4096 blocks (262144 tokens)");
     const int max_blocks = b.score_ld / 4 + 1;  // score_ld >= budget / 16
     if (max_blocks <= 512) {
-        launch_kernel(sparse_pool_topk_warp_kernel<16>, dim3(ceil_div(T, 4), hkv), dim3(128), 0, s, p);
+        launch_kernel(sparse_pool_topk_block_kernel<4>, dim3(T, hkv), dim3(128), 0, s, p);
     } else if (max_blocks <= 1024) {
-        launch_kernel(sparse_pool_topk_warp_kernel<32>, dim3(ceil_div(T, 4), hkv), dim3(128), 0, s, p);
+        launch_kernel(sparse_pool_topk_block_kernel<8>, dim3(T, hkv), dim3(128), 0, s, p);
     } else {
         launch_kernel(sparse_pool_topk_kernel, dim3(T, hkv), dim3(PT_THREADS), 0, s, p);
     }
