@@ -126,47 +126,55 @@ __global__ void lsm_local_topk_kernel(const bf16* __restrict__ logits, int ld, i
     const bf16* x = logits + static_cast<size_t>(row + (row0 ? *row0 : 0)) * ld;
     const int begin = seg * SEG;
     const int end = min(begin + SEG, vocab);
-    unsigned long long keys[SEG / SCAN_THREADS];
+    // Inside a segment a 32-bit key orders the candidates: (orderable 16-bit value << 16) | (0xFFFF - local index),
+    // larger = earlier in (value desc, index asc) order, 0 = no entry.  One compare, one hardware reduction.
+    static_assert(SEG <= 65536, "local index must fit 16 bits");
+    uint32_t keys[SEG / SCAN_THREADS];
 #pragma unroll
     for (int j = 0; j < SEG / SCAN_THREADS; ++j) {
-        const int i = begin + j * SCAN_THREADS + threadIdx.x;
+        const int local = j * SCAN_THREADS + threadIdx.x;
+        const int i = begin + local;
         if (i < end) {
             const bf16 lp = __float2bfloat16(__bfloat162float(x[i]) - mx - ls);
-            keys[j] = make_key(lp, i);
+            keys[j] = (bf16_orderable(lp) << 16) | static_cast<uint32_t>(0xFFFF - local);
         } else {
-            keys[j] = 0ull;
+            keys[j] = 0u;
         }
     }
     unsigned long long* out = cand + (static_cast<size_t>(row) * nseg + seg) * k;
     // each warp extracts the k best of its 256 keys (no block-wide barrier per round), then warp 0 merges
     // the 8 x k survivors; k <= 32
-    __shared__ unsigned long long wtop[SCAN_THREADS / 32][32];
+    __shared__ uint32_t wtop[SCAN_THREADS / 32][32];
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     for (int round = 0; round < k; ++round) {
-        unsigned long long best = 0ull;
+        uint32_t best = 0u;
 #pragma unroll
-        for (int j = 0; j < SEG / SCAN_THREADS; ++j) best = (keys[j] > best) ? keys[j] : best;
-        best = warp_max_u64(best);
+        for (int j = 0; j < SEG / SCAN_THREADS; ++j) best = max(best, keys[j]);
+        best = __reduce_max_sync(0xffffffffu, best);
         if (lane == 0) wtop[warp][round] = best;
 #pragma unroll
         for (int j = 0; j < SEG / SCAN_THREADS; ++j) {
-            if (keys[j] == best) keys[j] = 0ull;  // keys are unique (index is part of the key)
+            if (keys[j] == best) keys[j] = 0u;  // keys are unique (the index is part of the key)
         }
     }
     __syncthreads();
     if (warp == 0) {
-        unsigned long long mine[SCAN_THREADS / 32];
+        uint32_t mine[SCAN_THREADS / 32];
 #pragma unroll
-        for (int w = 0; w < SCAN_THREADS / 32; ++w) mine[w] = (lane < k) ? wtop[w][lane] : 0ull;
+        for (int w = 0; w < SCAN_THREADS / 32; ++w) mine[w] = (lane < k) ? wtop[w][lane] : 0u;
         for (int round = 0; round < k; ++round) {
-            unsigned long long best = 0ull;
+            uint32_t best = 0u;
 #pragma unroll
-            for (int w = 0; w < SCAN_THREADS / 32; ++w) best = (mine[w] > best) ? mine[w] : best;
-            best = warp_max_u64(best);
-            if (lane == 0) out[round] = best;
+            for (int w = 0; w < SCAN_THREADS / 32; ++w) best = max(best, mine[w]);
+            best = __reduce_max_sync(0xffffffffu, best);
+            if (lane == 0) {
+                // the candidate in the row-wide 64-bit form of make_key(); 0 stays 0 (fewer than k entries)
+                const uint32_t idx = static_cast<uint32_t>(begin) + (0xFFFFu - (best & 0xFFFFu));
+                out[round] = best ? ((static_cast<unsigned long long>(best >> 16) << 32) | (0xFFFFFFFFu - idx)) : 0ull;
+            }
 #pragma unroll
             for (int w = 0; w < SCAN_THREADS / 32; ++w) {
-                if (mine[w] == best) mine[w] = 0ull;
+                if (mine[w] == best) mine[w] = 0u;
             }
         }
     }
