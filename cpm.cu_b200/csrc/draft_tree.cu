@@ -180,17 +180,18 @@ __global__ void lsm_local_topk_kernel(const bf16* __restrict__ logits, int ld, i
     }
 }
 
-// Select the `k` largest of `n` unique keys held in shared memory by one warp;
-// result r (0 = largest) is returned to lane r.
-__device__ unsigned long long warp_select(unsigned long long* keys, int n, int k, int lane) {
-    unsigned long long mine = 0ull;
+// Select the `k` largest of `n` unique 32-bit keys held in shared memory by one warp (the keys are consumed);
+// result r (0 = largest) is returned to lane r.  Callers pack (orderable 16-bit value << 16) | (0xFFFF - position)
+// with positions that rise with the candidate index among equal values.
+__device__ uint32_t warp_select(uint32_t* keys, int n, int k, int lane) {
+    uint32_t mine = 0u;
     for (int round = 0; round < k; ++round) {
-        unsigned long long best = 0ull;
-        for (int i = lane; i < n; i += 32) best = (keys[i] > best) ? keys[i] : best;
-        best = warp_max_u64(best);
+        uint32_t best = 0u;
+        for (int i = lane; i < n; i += 32) best = max(best, keys[i]);
+        best = __reduce_max_sync(0xffffffffu, best);
         if (lane == round) mine = best;
         for (int i = lane; i < n; i += 32) {
-            if (keys[i] == best) keys[i] = 0ull;
+            if (keys[i] == best) keys[i] = 0u;
         }
         __syncwarp();
     }
@@ -205,24 +206,31 @@ __global__ void draft_expand_kernel(DraftTreeState st, const unsigned long long*
                                     const bf16* __restrict__ logits, int ld, const float2* __restrict__ rowoff,
                                     int level, const int32_t* __restrict__ last_row_ptr) {
     grid_dependency_sync();
-    extern __shared__ unsigned long long sh_keys[];  // rows * nseg * k candidate keys, then scratch
+    extern __shared__ unsigned long long sh_keys[];  // rows * nseg * k candidate keys, then as many 32-bit selection keys
     const int k = st.k;
     const int rows = (level == 0) ? 1 : k;
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int per_row = nseg * k;
     __shared__ bf16 s_val[32 * 32];
     __shared__ int s_pos[32 * 32];
-    __shared__ unsigned long long s_ckey[32 * 32];
+    __shared__ uint32_t s_ckey[32 * 32];
     __shared__ int s_sel[32];
     __shared__ uint64_t s_oldmask[32];
 
     if (warp < rows) {
         unsigned long long* mykeys = sh_keys + static_cast<size_t>(warp) * per_row;
-        for (int i = lane; i < per_row; i += 32) mykeys[i] = cand[static_cast<size_t>(warp) * per_row + i];
+        uint32_t* sel = reinterpret_cast<uint32_t*>(sh_keys + static_cast<size_t>(rows) * per_row) + static_cast<size_t>(warp) * per_row;
+        // The list holds segment after segment, each sorted by (value desc, index asc): among equal values the
+        // position in the list rises with the vocabulary index, so (value, position) orders like (value, index).
+        for (int i = lane; i < per_row; i += 32) {
+            const unsigned long long c = cand[static_cast<size_t>(warp) * per_row + i];
+            mykeys[i] = c;
+            sel[i] = c ? ((static_cast<uint32_t>(c >> 32) << 16) | static_cast<uint32_t>(0xFFFF - i)) : 0u;
+        }
         __syncwarp();
-        const unsigned long long got = warp_select(mykeys, per_row, k, lane);
+        const uint32_t got = warp_select(sel, per_row, k, lane);
         if (lane < k) {
-            const int idx = key_index(got);
+            const int idx = got ? key_index(mykeys[0xFFFF - (got & 0xFFFFu)]) : 0;
             const float mx = rowoff[warp].x, ls = rowoff[warp].y;
             const int lrow = warp + ((level == 0 && last_row_ptr) ? *last_row_ptr : 0);
             const bf16 lp = __float2bfloat16(__bfloat162float(logits[static_cast<size_t>(lrow) * ld + idx]) - mx - ls);
@@ -255,13 +263,13 @@ __global__ void draft_expand_kernel(DraftTreeState st, const unsigned long long*
         s_val[i] = v;
         st.tried_val[base + i] = v;
         st.tried_pos[base + i] = s_pos[i];
-        s_ckey[i] = make_key(v, i);
+        s_ckey[i] = (bf16_orderable(v) << 16) | static_cast<uint32_t>(0xFFFF - i);
     }
     if (threadIdx.x < k) s_oldmask[threadIdx.x] = st.fr_mask[threadIdx.x];
     __syncthreads();
     if (warp == 0) {
-        const unsigned long long got = warp_select(s_ckey, kk, k, lane);
-        if (lane < k) s_sel[lane] = key_index(got);
+        const uint32_t got = warp_select(s_ckey, kk, k, lane);
+        if (lane < k) s_sel[lane] = 0xFFFF - static_cast<int>(got & 0xFFFFu);
     }
     __syncthreads();
     if (threadIdx.x < k) {
@@ -387,9 +395,10 @@ void launch_draft_topk_expand(const DraftTreeState& st, const bf16* logits, int 
                   level == 0 ? last_row_ptr : nullptr);
     launch_kernel(lsm_local_topk_kernel, grid, dim3(SCAN_THREADS), 0, s, logits, ld, vocab, static_cast<const float2*>(stats),
                   nseg, k, cand, level == 0 ? last_row_ptr : nullptr, rowoff);
-    const size_t shmem = static_cast<size_t>(rows) * nseg * k * sizeof(unsigned long long);
+    CPM_REQUIRE(nseg * k <= 65535, "draft: candidate list too long for 16-bit positions");
+    const size_t shmem = static_cast<size_t>(rows) * nseg * k * (sizeof(unsigned long long) + sizeof(uint32_t));
     static size_t configured = 0;
-    if (shmem > 48 * 1024 && shmem > configured) {
+    if (shmem > 32 * 1024 && shmem > configured) {   // the kernel also has 11 KB of static shared memory
         CPM_REQUIRE(shmem <= 200 * 1024, "draft: candidate list too large for one CTA");
         CUDA_CHECK(cudaFuncSetAttribute(draft_expand_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                         static_cast<int>(shmem)));
