@@ -33,6 +33,10 @@ LINEAR_CASES = [
     (1, 256, 256, 0), (7, 384, 512, 0), (10, 4200, 1024, 0), (16, 1024, 4096, 0), (60, 4608, 4096, 0),
     (64, 512, 16384, 0), (33, 300, 128, 0), (17, 128, 64, 0), (130, 512, 256, 0), (300, 1024, 512, 0),
     (60, 1000, 2048, 3), (60, 1000, 2048, 7), (10, 4096, 4096, 5), (257, 640, 1024, 11), (1, 73448, 512, 0),
+    # shapes whose tiles are cut into 2-4 k-pieces summed inside a thread-block cluster (o, down, draft fc; 30 and
+    # 64 tokens for the other token tiles; 61 tokens: the last rank's share of the tokens is short)
+    (60, 4096, 4096, 0), (60, 4096, 16384, 0), (10, 4096, 8192, 0), (30, 4096, 4096, 0), (64, 4096, 4096, 0),
+    (61, 4608, 4096, 0), (3, 4608, 4096, 0),
 ]
 
 
@@ -60,6 +64,7 @@ W4_CASES = [
     (1, 128, 256, 0), (7, 384, 512, 0), (10, 4096, 1024, 0), (16, 1024, 4096, 0), (60, 4608, 4096, 0),
     (64, 512, 16384, 0), (33, 256, 256, 0), (130, 512, 256, 0), (300, 1024, 512, 0),
     (60, 1024, 2048, 3), (60, 1024, 2048, 7), (10, 4096, 4096, 5), (257, 640, 1024, 11),
+    (60, 4096, 4096, 0), (60, 4096, 16384, 0), (30, 4608, 4096, 0), (61, 4096, 4096, 0),   # cluster split-K shapes
 ]
 
 
