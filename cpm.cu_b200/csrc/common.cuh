@@ -89,7 +89,7 @@ void launch_kernel(void (*kernel)(KArgs...), dim3 grid, dim3 block, size_t smem,
 
 // The same for a kernel that runs as thread-block clusters of `cluster` CTAs (grid.x a multiple of it).
 template <typename... KArgs, typename... Args>
-void launch_kernel_cluster(void (*kernel)(KArgs...), dim3 grid, dim3 block, size_t smem, cudaStream_t s, dim3 cluster,
+void launch_kernel_cluster(void (*kernel)(KArgs...), dim3 grid, dim3 block, size_t smem, cudaStream_t s, int cluster,
                            Args&&... args) {
     cudaLaunchConfig_t cfg = {};
     cfg.gridDim = grid;
@@ -98,20 +98,15 @@ void launch_kernel_cluster(void (*kernel)(KArgs...), dim3 grid, dim3 block, size
     cfg.stream = s;
     cudaLaunchAttribute attr[2];
     attr[0].id = cudaLaunchAttributeClusterDimension;
-    attr[0].val.clusterDim.x = cluster.x;
-    attr[0].val.clusterDim.y = cluster.y;
-    attr[0].val.clusterDim.z = cluster.z;
+    attr[0].val.clusterDim.x = cluster;
+    attr[0].val.clusterDim.y = 1;
+    attr[0].val.clusterDim.z = 1;
     attr[1].id = cudaLaunchAttributeProgrammaticStreamSerialization;
     attr[1].val.programmaticStreamSerializationAllowed = 1;
     cfg.attrs = attr;
     cfg.numAttrs = runtime().pdl ? 2 : 1;
     CUDA_CHECK(cudaLaunchKernelEx(&cfg, kernel, KArgs(args)...));
     runtime().launches++;
-}
-template <typename... KArgs, typename... Args>
-void launch_kernel_cluster(void (*kernel)(KArgs...), dim3 grid, dim3 block, size_t smem, cudaStream_t s, int cluster,
-                           Args&&... args) {
-    launch_kernel_cluster(kernel, grid, block, smem, s, dim3(cluster, 1, 1), std::forward<Args>(args)...);
 }
 
 // Clusters of `cluster` CTAs of this kernel that the device runs at once (0 when the query fails).  The SMs

@@ -112,8 +112,6 @@ int Engine::attn_splits_for(int rows) const {
     int s = runtime().num_sms / mtiles;
     static const char* forced = getenv("CPMCU_ATTN_SPLITS");  // bench only: sweep the number of key splits
     if (forced && atoi(forced) >= 1) s = atoi(forced);
-    static const char* forced_small = getenv("CPMCU_ATTN_SPLITS_SMALL");  // bench only: launches of up to 16 rows
-    if (forced_small && atoi(forced_small) >= 1 && rows <= 16) s = atoi(forced_small);
     return std::max(1, std::min(s, 32));
 }
 

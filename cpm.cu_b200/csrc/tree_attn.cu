@@ -70,7 +70,6 @@ struct AttnArgs {
     float* ws_ml;
     int* error;
     long long* prof;  // bench only (-DCPMCU_ATTN_PROFILE): clock counters of CTA 0, or null
-    int cluster;      // > 0: the gridDim.y key splits of a tile form one thread-block cluster and merge in shared memory
 };
 
 #ifdef CPMCU_ATTN_PROFILE
@@ -320,11 +319,6 @@ tree_attn_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant
                 }
             }
         }
-        if (a.cluster) {   // the two cluster barriers of the softmax warps' merge (every thread of the cluster arrives)
-            __syncwarp();
-            ptx::cluster_sync();
-            ptx::cluster_sync();
-        }
     } else {
         // ================================================= softmax warps
         int s_tile = kt_begin;
@@ -466,72 +460,7 @@ tree_attn_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant
         xch[ch * ROWS + row] = l_run;
         ptx::named_bar_sync(1, SOFTMAX_THREADS);
         const float l_row = l_run + xch[(ch ^ 1) * ROWS + row];
-        if (a.cluster) {
-            // ---- merge of the key splits inside the cluster (rank = split).  Rows are dealt to the ranks, RPR each;
-            // every CTA sends each owner its unnormalised rows and their (max, sum), the owner weights and adds them
-            // in split order, as the separate merge kernel does, and stores bf16.  Receive buffers: the idle K/V
-            // stages, fp32 [source][4-column group][row][4], and the first P stage for the (max, sum) pairs.
-            const int CS = nsplit;
-            const int RPR = (ROWS + CS - 1) / CS;
-            float* red = reinterpret_cast<float*>(smem + SMEM_K);
-            float2* red_ml = reinterpret_cast<float2*>(smem + SMEM_P);
-            __syncwarp();
-            ptx::cluster_sync();   // every CTA of the cluster is past its last MMA: K, V and P stages are idle
-            {
-                const int owner = row / RPR, r = row - owner * RPR;
-                const uint32_t base = ptx::cluster_map(ptx::smem_u32(red), static_cast<uint32_t>(owner));
-#pragma unroll 1
-                for (int c0 = 0; c0 < 64; c0 += 32) {
-                    uint32_t rr[32];
-                    if (ok && n_it > 0) {  // uniform across the warp
-                        ptx::tmem_ld32(tmem_o + c0, rr);
-                        ptx::tmem_wait_ld();
-                    } else {
-#pragma unroll
-                        for (int c = 0; c < 32; ++c) rr[c] = 0;
-                    }
-#pragma unroll
-                    for (int j = 0; j < 8; ++j) {
-                        const int c4 = ch * 16 + (c0 >> 2) + j;
-                        const uint32_t dst = base + static_cast<uint32_t>(((split * 32 + c4) * RPR + r) * 16);
-                        asm volatile("st.shared::cluster.v4.b32 [%0], {%1, %2, %3, %4};" ::"r"(dst), "r"(rr[j * 4]),
-                                     "r"(rr[j * 4 + 1]), "r"(rr[j * 4 + 2]), "r"(rr[j * 4 + 3])
-                                     : "memory");
-                    }
-                }
-                if (ch == 0) {
-                    const uint32_t dst = ptx::cluster_map(ptx::smem_u32(red_ml + split * RPR + r), static_cast<uint32_t>(owner));
-                    const float mm = (ok && n_it > 0) ? m_run : -INFINITY, ll = (ok && n_it > 0) ? l_row : 0.f;
-                    asm volatile("st.shared::cluster.v2.f32 [%0], {%1, %2};" ::"r"(dst), "f"(mm), "f"(ll) : "memory");
-                }
-            }
-            __syncwarp();
-            ptx::cluster_sync();   // every split's rows have arrived at their owners
-            const int my_rows = min(RPR, ROWS - split * RPR);
-            for (int i = tid; i < my_rows * 32; i += SOFTMAX_THREADS) {
-                const int r = i >> 5, c4 = i & 31;
-                float M = -INFINITY;
-                for (int sp = 0; sp < CS; ++sp) M = fmaxf(M, red_ml[sp * RPR + r].x);
-                float l = 0.f;
-                float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
-                for (int sp = 0; sp < CS; ++sp) {
-                    const float2 ml = red_ml[sp * RPR + r];
-                    const float w = (ml.x == -INFINITY) ? 0.f : exp2f((ml.x - M) * a.scale_log2);
-                    l += w * ml.y;
-                    const float4 o = *reinterpret_cast<const float4*>(red + ((sp * 32 + c4) * RPR + r) * 4);
-                    acc.x += w * o.x; acc.y += w * o.y; acc.z += w * o.z; acc.w += w * o.w;
-                }
-                const int grow = split * RPR + r;            // row of the tile
-                const int tt = t0 + grow / a.grp, hh = h * a.grp + grow % a.grp;
-                if (tt < a.tq) {
-                    const float inv = (l > 0.f) ? 1.f / l : 0.f;
-                    __nv_bfloat162 lo = __floats2bfloat162_rn(acc.x * inv, acc.y * inv);
-                    __nv_bfloat162 hi = __floats2bfloat162_rn(acc.z * inv, acc.w * inv);
-                    uint2 pk = make_uint2(*reinterpret_cast<uint32_t*>(&lo), *reinterpret_cast<uint32_t*>(&hi));
-                    *reinterpret_cast<uint2*>(a.out + static_cast<size_t>(tt) * a.out_ld + hh * D + c4 * 4) = pk;
-                }
-            }
-        } else if (ok) {
+        if (ok) {
             const bool store = (t < a.tq);
             const size_t grow = static_cast<size_t>(store ? t : 0) * a.hq + qh;
             const float inv = (nsplit == 1) ? ((l_row > 0.f) ? 1.f / l_row : 0.f) : 1.f;
@@ -731,19 +660,6 @@ void launch_tree_attention(const AttnPlan& p, cudaStream_t s) {
     }
     CPM_REQUIRE(p.splits == 1 || (p.ws_o != nullptr && p.ws_ml != nullptr), "attention: split-KV needs a workspace");
     dim3 grid(a.num_mtiles * p.hkv, p.splits);
-    // two to eight key splits merge inside a thread-block cluster when the device runs all the clusters at once
-    a.cluster = 0;
-    if (p.splits >= 2 && p.splits <= 8) {
-        static int capacity[9] = {-1, -1, -1, -1, -1, -1, -1, -1, -1};
-        static const bool off = getenv("CPMCU_ATTN_NO_CLUSTER") != nullptr;   // bench only
-        if (capacity[p.splits] < 0)
-            capacity[p.splits] = max_active_clusters(tree_attn_kernel, dim3(NTHREADS), SMEM_TOTAL, p.splits);
-        if (!off && capacity[p.splits] >= static_cast<int>(grid.x)) a.cluster = p.splits;
-    }
-    if (a.cluster) {
-        launch_kernel_cluster(tree_attn_kernel, grid, dim3(NTHREADS), SMEM_TOTAL, s, dim3(1, p.splits, 1), p.tm_q, p.tm_k, p.tm_v, a);
-        return;
-    }
     launch_kernel(tree_attn_kernel, grid, dim3(NTHREADS), SMEM_TOTAL, s, p.tm_q, p.tm_k, p.tm_v, a);
     if (p.splits > 1) {
         const int rows = p.tq * p.hq;
