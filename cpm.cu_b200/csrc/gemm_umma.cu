@@ -215,17 +215,29 @@ linear_umma_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_consta
 // ring), one cluster barrier, and every CTA sums and stores its own tokens in rank order, which is the
 // order the workspace path adds its pieces in.  All waits are the bounded mbarrier waits of the roles; every
 // thread reaches both cluster barriers whatever those waits returned.
+// The cluster kernel gives one or two ring stages to a reduction buffer of its own, so that a peer may write its
+// partial sums as soon as IT is done, whatever this CTA's ring is doing.
+template <int MT, int CS>
+struct ClusterCfg {
+    static constexpr int STAGE_BYTES = Cfg<MT>::STAGE_BYTES;
+    static constexpr int TMEM_COLS = Cfg<MT>::TMEM_COLS;
+    static constexpr int TPR = (MT + CS - 1) / CS;                 // tokens summed and stored by each rank
+    static constexpr int RED_BYTES = (CS * TPR * BLOCK_N * 4 + 1023) / 1024 * 1024;
+    static constexpr int STAGES = Cfg<MT>::STAGES - (RED_BYTES + STAGE_BYTES - 1) / STAGE_BYTES + ((MT >= 64) ? 1 : 0);
+    static constexpr int SMEM_BYTES = STAGES * STAGE_BYTES + RED_BYTES + Cfg<MT>::CTRL_BYTES + 1024;
+    static_assert(SMEM_BYTES <= 232448, "shared memory budget");
+};
+
 template <int MT, int CS>
 __global__ void __launch_bounds__(NUM_THREADS, 1)
 linear_umma_cluster_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_constant__ CUtensorMap tm_x,
                            const LinearArgs a) {
-    using C = Cfg<MT>;
-    constexpr int TPR = (MT + CS - 1) / CS;   // tokens summed and stored by each rank
-    static_assert(CS * TPR * BLOCK_N * 4 <= C::STAGES * C::STAGE_BYTES, "reduction buffer exceeds the ring");
+    using C = ClusterCfg<MT, CS>;
     extern __shared__ uint8_t smem_raw[];
     uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
     uint8_t* tiles = smem;
-    uint64_t* full = reinterpret_cast<uint64_t*>(smem + C::STAGES * C::STAGE_BYTES);
+    float* red = reinterpret_cast<float*>(smem + C::STAGES * C::STAGE_BYTES);   // peers write here; nothing else does
+    uint64_t* full = reinterpret_cast<uint64_t*>(smem + C::STAGES * C::STAGE_BYTES + C::RED_BYTES);
     uint64_t* empty = full + C::STAGES;
     uint64_t* acc_full = empty + C::STAGES;
     uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(acc_full + 4);
@@ -238,6 +250,7 @@ linear_umma_cluster_kernel(const __grid_constant__ CUtensorMap tm_w, const __gri
     const int kb_begin = (a.kblocks * rank) / CS, kb_end = (a.kblocks * (rank + 1)) / CS;
     const int kpc = kb_end - kb_begin;
     grid_dep_trigger();
+    ptx::cluster_arrive_relaxed();   // "this CTA runs": waited for just before the first write to a peer
 
     if (threadIdx.x == 0) {
         for (int s = 0; s < C::STAGES; ++s) {
@@ -338,9 +351,9 @@ linear_umma_cluster_kernel(const __grid_constant__ CUtensorMap tm_w, const __gri
         }
     }
     __syncwarp();
-    ptx::cluster_sync();   // every CTA of the cluster is past its last MMA: the operand rings are idle
+    ptx::cluster_wait();   // every CTA of the cluster has started (arrivals at entry): its shared memory may be written
 
-    cluster_reduce_store<MT, CS>(a, v, reinterpret_cast<float*>(tiles), rank, n_tile, warp >= 2, row);
+    cluster_reduce_store<MT, CS>(a, v, red, rank, n_tile, warp >= 2, row);
 
     ptx::tc_fence_before();
     __syncthreads();
@@ -356,7 +369,7 @@ void configure_cluster_kernel() {
     static bool configured = false;
     if (!configured) {
         CUDA_CHECK(cudaFuncSetAttribute(linear_umma_cluster_kernel<MT, CS>, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                        Cfg<MT>::SMEM_BYTES));
+                                        ClusterCfg<MT, CS>::SMEM_BYTES));
         configured = true;
     }
 }
@@ -366,7 +379,7 @@ int max_active_clusters() {
     static int cached = -1;
     if (cached < 0) {
         configure_cluster_kernel<MT, CS>();
-        cached = ::max_active_clusters(linear_umma_cluster_kernel<MT, CS>, dim3(NUM_THREADS), Cfg<MT>::SMEM_BYTES, CS);
+        cached = ::max_active_clusters(linear_umma_cluster_kernel<MT, CS>, dim3(NUM_THREADS), ClusterCfg<MT, CS>::SMEM_BYTES, CS);
     }
     return cached;
 }
@@ -374,7 +387,7 @@ int max_active_clusters() {
 template <int MT, int CS>
 void launch_cluster(const LinearPlan& p, const LinearArgs& args, cudaStream_t stream) {
     configure_cluster_kernel<MT, CS>();
-    launch_kernel_cluster(linear_umma_cluster_kernel<MT, CS>, dim3(p.grid), dim3(NUM_THREADS), Cfg<MT>::SMEM_BYTES, stream,
+    launch_kernel_cluster(linear_umma_cluster_kernel<MT, CS>, dim3(p.grid), dim3(NUM_THREADS), ClusterCfg<MT, CS>::SMEM_BYTES, stream,
                           CS, p.tm_w, p.tm_x, args);
 }
 

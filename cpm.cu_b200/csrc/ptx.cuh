@@ -258,6 +258,13 @@ __device__ __forceinline__ void cluster_sync() {
     asm volatile("barrier.cluster.arrive.release.aligned;" ::: "memory");
     asm volatile("barrier.cluster.wait.acquire.aligned;" ::: "memory");
 }
+// The same barrier in two halves: the arrival costs nothing, and a wait placed much later finds it complete.
+__device__ __forceinline__ void cluster_arrive_relaxed() {
+    asm volatile("barrier.cluster.arrive.relaxed.aligned;" ::: "memory");
+}
+__device__ __forceinline__ void cluster_wait() {
+    asm volatile("barrier.cluster.wait.aligned;" ::: "memory");
+}
 // Address of this CTA's shared-memory location `addr` in CTA `rank` of the cluster.
 __device__ __forceinline__ uint32_t cluster_map(uint32_t addr, uint32_t rank) {
     uint32_t r;
