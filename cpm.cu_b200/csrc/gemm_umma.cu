@@ -211,10 +211,11 @@ linear_umma_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_consta
 // Split-K inside a thread-block cluster, for launches whose CTAs number CS per output tile: CTA `rank` of
 // cluster `n_tile` accumulates k-blocks [rank * kblocks / CS, (rank + 1) * kblocks / CS) of the tile, then the CS partial tiles
 // are summed through distributed shared memory instead of the global workspace and its tickets: every CTA
-// sends each peer that peer's share of the tokens (ceil(MT / CS), fp32 [source][token][feature] in the idle operand
-// ring), one cluster barrier, and every CTA sums and stores its own tokens in rank order, which is the
-// order the workspace path adds its pieces in.  All waits are the bounded mbarrier waits of the roles; every
-// thread reaches both cluster barriers whatever those waits returned.
+// sends each peer that peer's share of the tokens (ceil(MT / CS), fp32 [source][token][feature] in a buffer next
+// to the operand ring), one cluster barrier, and every CTA sums and stores its own tokens in rank order, which
+// is the order the workspace path adds its pieces in.  A first barrier only says "every CTA of the cluster has
+// started": arrived at on entry, waited for before the first write to a peer.  All other waits are the bounded
+// mbarrier waits of the roles; every thread reaches both cluster barriers whatever those waits returned.
 // The cluster kernel gives one or two ring stages to a reduction buffer of its own, so that a peer may write its
 // partial sums as soon as IT is done, whatever this CTA's ring is doing.
 template <int MT, int CS>
