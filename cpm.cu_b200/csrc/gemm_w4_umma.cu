@@ -54,10 +54,13 @@ constexpr int DEQ_WARPS = 8;
 constexpr int NUM_THREADS = (6 + DEQ_WARPS + 2) * 32;
 constexpr int MAX_MT = 128;                        // 2 chains x 128 + 8 x 32 A columns = 512
 
-template <int MT>
+// CS > 0 (cluster split-K): a reduction buffer of CS * ceil(MT / CS) tokens x 128 features fp32 that peers write,
+// paid for at MT = 64 with one weight stage.
+template <int MT, int CS = 0>
 struct Cfg {
     static constexpr int X_BYTES = MT * BLOCK_K * 2;
-    static constexpr int W_STAGES = (MT <= 32) ? 9 : (MT <= 64) ? 6 : 5;
+    static constexpr int RED_BYTES = (CS > 0) ? (CS * ((MT + (CS > 0 ? CS : 1) - 1) / (CS > 0 ? CS : 1)) * BLOCK_N * 4 + 1023) / 1024 * 1024 : 0;
+    static constexpr int W_STAGES = (MT <= 32) ? 9 : (MT <= 64) ? ((CS > 0) ? 5 : 6) : 5;
     // ring of (A slot in TMEM, token tile in smem) pairs.  A slot comes back only after the MMA that read it
     // has completed and three barrier hand-offs (about a microsecond), so the ring depth, not any role's
     // work, sets the k-block rate: tensor memory goes to slots rather than to a second accumulator stage
@@ -70,7 +73,8 @@ struct Cfg {
     static constexpr int TMEM_COLS = 512;
     static constexpr int OFF_W = 0;
     static constexpr int OFF_X = (OFF_W + W_STAGES * W_STAGE_BYTES + 1023) / 1024 * 1024;
-    static constexpr int OFF_CTRL = OFF_X + SLOTS * X_BYTES;
+    static constexpr int OFF_RED = OFF_X + SLOTS * X_BYTES;
+    static constexpr int OFF_CTRL = OFF_RED + RED_BYTES;
     static constexpr int SMEM_BYTES = OFF_CTRL + 512 + 1024;
     static_assert(ACC2_OFF + ACC_COLS <= TMEM_COLS, "tensor memory budget");
     static_assert(SMEM_BYTES <= 232448, "shared memory budget");
@@ -107,7 +111,7 @@ __device__ __forceinline__ uint32_t lop3_and_or(uint32_t a, uint32_t b, uint32_t
 template <int MT, int CS>
 __global__ void __launch_bounds__(NUM_THREADS, 1)
 linear_w4_umma_kernel(const __grid_constant__ CUtensorMap tm_x, const W4Args wa) {
-    using C = Cfg<MT>;
+    using C = Cfg<MT, CS>;
     const LinearArgs& a = wa.lin;
     extern __shared__ uint8_t smem_raw[];
     uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
@@ -128,6 +132,7 @@ linear_w4_umma_kernel(const __grid_constant__ CUtensorMap tm_x, const W4Args wa)
     const int G = gridDim.x;
     const int g = blockIdx.x;
     grid_dep_trigger();
+    if constexpr (CS > 0) ptx::cluster_arrive_relaxed();   // "this CTA runs": waited for before the first write to a peer
 
     if (threadIdx.x == 0) {
         for (int s = 0; s < C::W_STAGES; ++s) {
@@ -389,11 +394,10 @@ linear_w4_umma_kernel(const __grid_constant__ CUtensorMap tm_x, const W4Args wa)
         }
     }
     if constexpr (CS > 0) {
-        static_assert(CS * ((MT + CS - 1) / CS) * BLOCK_N * 4 <= C::W_STAGES * W_STAGE_BYTES, "reduction buffer exceeds the weight ring");
         __syncwarp();
-        ptx::cluster_sync();   // every CTA of the cluster is past its last MMA and dequant pass: the weight rings are idle
+        ptx::cluster_wait();   // every CTA of the cluster has started (arrivals at entry): its reduction buffer may be written
         const bool epi = (warp >= 2 && warp < 6);
-        cluster_reduce_store<MT, CS>(a, v, reinterpret_cast<float*>(smem + C::OFF_W), c_rank, c_tile, epi, (warp & 3) * 32 + lane);
+        cluster_reduce_store<MT, CS>(a, v, reinterpret_cast<float*>(smem + C::OFF_RED), c_rank, c_tile, epi, (warp & 3) * 32 + lane);
     }
 
     ptx::tc_fence_before();
@@ -424,7 +428,7 @@ void configure_kernel() {
     static bool configured = false;
     if (!configured) {
         CUDA_CHECK(cudaFuncSetAttribute(linear_w4_umma_kernel<MT, CS>, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                        Cfg<MT>::SMEM_BYTES));
+                                        Cfg<MT, CS>::SMEM_BYTES));
         configured = true;
     }
 }
@@ -438,7 +442,7 @@ void launch_mt(const LinearPlan& p, const W4Args& args, cudaStream_t stream) {
 template <int MT, int CS>
 void launch_cluster(const LinearPlan& p, const W4Args& args, cudaStream_t stream) {
     configure_kernel<MT, CS>();
-    launch_kernel_cluster(linear_w4_umma_kernel<MT, CS>, dim3(p.grid), dim3(NUM_THREADS), Cfg<MT>::SMEM_BYTES, stream, CS,
+    launch_kernel_cluster(linear_w4_umma_kernel<MT, CS>, dim3(p.grid), dim3(NUM_THREADS), Cfg<MT, CS>::SMEM_BYTES, stream, CS,
                           p.tm_x, args);
 }
 
@@ -447,7 +451,7 @@ int capacity() {
     static int cached = -1;
     if (cached < 0) {
         configure_kernel<MT, CS>();
-        cached = max_active_clusters(linear_w4_umma_kernel<MT, CS>, dim3(NUM_THREADS), Cfg<MT>::SMEM_BYTES, CS);
+        cached = max_active_clusters(linear_w4_umma_kernel<MT, CS>, dim3(NUM_THREADS), Cfg<MT, CS>::SMEM_BYTES, CS);
     }
     return cached;
 }
