@@ -1,6 +1,6 @@
 // Thin inline-PTX wrappers for the Blackwell (sm_100a) primitives the kernels
-// in this directory use: mbarrier, TMA tiled loads (no cluster multicast
-// anywhere), tcgen05 MMA / TMEM load-store / alloc, and the proxy fences that
+// in this directory use: mbarrier, TMA tiled loads (every CTA fetches its own
+// tiles), tcgen05 MMA / TMEM load-store / alloc, and the proxy fences that
 // order them.  Every wait is bounded: after a clock budget it reports failure
 // so the caller can raise the kernel's error flag and tear down instead of
 // spinning forever.

@@ -15,7 +15,7 @@
 //   softmax     one thread per row reads S with tcgen05.ld, online max/sum,
 //               writes bf16 P into 128-byte-swizzled shared memory
 //   O += P V    tcgen05.mma, A = P (K-major), B = V tile (N-major), O in TMEM
-// K/V tiles of 128 keys arrive by TMA (no multicast) into a two-stage ring.
+// K/V tiles of 128 keys arrive by TMA (each CTA loads its own) into a two-stage ring.
 //
 // Block-sparse mode (InfLLM-v2 target layers; replaces compute_attn_1rowblock_splitkv_headlevel,
 // src/flash_attn/src/flash_fwd_kernel.h:580-1171 with the iterator of flash_blockmask.h): every
