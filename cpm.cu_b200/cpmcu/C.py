@@ -36,6 +36,8 @@ _SIGNATURES = {
     "cpmcu_spec_step": (_c_int, [_c_void_p, _c_int]),
     "cpmcu_profile_step": (_c_int, [_c_void_p] * 3),
     "cpmcu_last_step_ms": (ctypes.c_double, []),
+    "cpmcu_last_draft_ms": (ctypes.c_double, []),
+    "cpmcu_last_verify_ms": (ctypes.c_double, []),
     "cpmcu_launches_per_step": (ctypes.c_long, []),
     "cpmcu_total_launches": (ctypes.c_long, []),
     "cpmcu_get_tree": (_c_int, [_c_void_p] * 6),
@@ -44,6 +46,7 @@ _SIGNATURES = {
     "cpmcu_linear_bf16": (_c_int, [_c_void_p] * 4 + [_c_int] * 4),
     "cpmcu_linear_w4a16": (_c_int, [_c_void_p] * 4 + [_c_int] * 4),
     "cpmcu_bench_linear": (_c_int, [_c_int] * 6 + [_c_void_p]),
+    "cpmcu_bench_linear_w4": (_c_int, [_c_int] * 6 + [_c_void_p]),
     "cpmcu_bench_attention": (_c_int, [_c_int] * 7 + [_c_void_p]),
     "cpmcu_sparse_attention": (_c_int, [_c_void_p, _c_int, _c_void_p, _c_void_p] + [_c_int] * 4 +
                                [_c_void_p, _c_int, _c_void_p, _c_int, _c_void_p, _c_int, _c_int, _c_int, _c_void_p,
@@ -59,6 +62,8 @@ _SIGNATURES = {
     "cpmcu_argmax_noalloc": (_c_int, [_c_void_p, _c_int, _c_int, _c_void_p]),
     "cpmcu_draft_tree_from_logits": (_c_int, [_c_void_p] + [_c_int] * 4 + [_c_void_p] * 9),
     "cpmcu_verify_and_compact": (_c_int, [_c_int] + [_c_void_p] * 7 + [_c_int] * 3 + [_c_void_p]),
+    "cpmcu_accept_fixup": (_c_int, [_c_int] + [_c_void_p] * 7 + [_c_int] * 5 + [_c_void_p] * 3 + [ctypes.c_float] +
+                           [_c_void_p] * 3),
 }
 
 
@@ -217,6 +222,12 @@ def profile_step():
 
 def last_step_ms():
     return load().cpmcu_last_step_ms()
+
+
+def last_step_split_ms():
+    """(draft half, verify half) of the last spec_step in device milliseconds."""
+    lib = load()
+    return lib.cpmcu_last_draft_ms(), lib.cpmcu_last_verify_ms()
 
 
 def launches_per_step():

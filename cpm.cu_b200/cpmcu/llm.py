@@ -30,8 +30,10 @@ def dtype_to_int(dtype):
 
 
 def default_rope_inv_freq(config):
-    """inv_freq of the 'default' rope type: theta^(-2i/d)."""
-    theta = getattr(config, "rope_theta", 10000.0)
+    """inv_freq of the 'default' rope type: theta^(-2i/d).  Newer `transformers` keep rope_theta inside
+    config.rope_scaling / rope_parameters instead of on the config itself."""
+    scaling = getattr(config, "rope_scaling", None) or {}
+    theta = getattr(config, "rope_theta", None) or scaling.get("rope_theta") or 10000.0
     d = config.head_dim
     return 1.0 / (theta ** (torch.arange(0, d, 2, dtype=torch.float32) / d))
 
@@ -57,6 +59,11 @@ class LLM(torch.nn.Module):
         self.use_decode_enter = use_decode_enter
         self.temperature = temperature
         self.chunk_length = chunk_length
+        if minicpm4_yarn:
+            # the reference swaps in a fixed table of 64 LongRoPE factors here (cpmcu/llm_w4a16_gptq_marlin.py:192-219);
+            # give the same factors through the checkpoint's config.json (rope_scaling: rope_type "longrope") instead
+            raise NotImplementedError("minicpm4_yarn=True is not supported: put the LongRoPE factors into the "
+                                      "checkpoint's rope_scaling (rope_type 'longrope'), which is honoured")
         self.minicpm4_yarn = minicpm4_yarn
         self._show_prefill_progress = False
         self.generator = None
@@ -144,9 +151,10 @@ class LLM(torch.nn.Module):
     def _rope_inv_freq(self):
         cfg = self.config
         scaling = getattr(cfg, "rope_scaling", None)
-        if scaling:
+        rope_type = (scaling.get("rope_type", scaling.get("type")) if scaling else None) or "default"
+        if rope_type != "default":
+            # "llama3", or "longrope" with long_factor == short_factor, as in the reference (cpmcu/llm.py:176-186)
             from transformers.modeling_rope_utils import ROPE_INIT_FUNCTIONS
-            rope_type = scaling.get("rope_type", scaling.get("type"))
             inv_freq, _ = ROPE_INIT_FUNCTIONS[rope_type](cfg, "cpu", seq_len=self.max_total_length)
             return inv_freq
         return default_rope_inv_freq(cfg)
@@ -214,6 +222,9 @@ class LLM(torch.nn.Module):
         (tokens, decode_time, prefill_time), or a generator of dicts when use_stream."""
         assert input_ids.dtype == torch.int32
         prefix_length = input_ids.numel()
+        if prefix_length + generation_length > self.max_total_length:
+            raise ValueError(f"prompt ({prefix_length}) + generation_length ({generation_length}) exceeds the "
+                             f"{self.max_total_length} tokens the KV cache holds under the current memory limit")
         position_ids = torch.arange(prefix_length, dtype=torch.int32, device="cuda")
         self._show_prefill_progress = bool(use_stream)
         torch.cuda.synchronize()

@@ -81,6 +81,11 @@ class LLM_with_tree_drafter(LLM):
         if prefix_length > self.max_total_length:
             raise ValueError(f"Input token count ({prefix_length}) exceeds maximum supported length "
                              f"({self.max_total_length}) under current memory limit")
+        # every step writes the K/V rows of a whole tree behind the accepted tokens
+        if prefix_length + generation_length + self.tree_size > self.max_total_length:
+            raise ValueError(f"prompt ({prefix_length}) + generation_length ({generation_length}) + one draft tree "
+                             f"({self.tree_size}) exceeds the {self.max_total_length} tokens the KV cache holds "
+                             f"under the current memory limit")
         position_ids = torch.arange(prefix_length, dtype=torch.int32, device="cuda")
         self._show_prefill_progress = bool(use_stream)
         torch.cuda.synchronize()

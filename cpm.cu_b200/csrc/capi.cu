@@ -294,6 +294,8 @@ int cpmcu_profile_step(float* class_ms, int* class_launches, float* total_ms) {
 }
 
 double cpmcu_last_step_ms(void) { return g_engine ? g_engine->last_step_device_ms() : 0.0; }
+double cpmcu_last_draft_ms(void) { return g_engine ? g_engine->last_draft_ms() : 0.0; }
+double cpmcu_last_verify_ms(void) { return g_engine ? g_engine->last_verify_ms() : 0.0; }
 long cpmcu_launches_per_step(void) { return g_engine ? g_engine->launches_per_step() : 0; }
 long cpmcu_total_launches(void) {
     try {
@@ -368,7 +370,7 @@ int cpmcu_linear_w4a16(const void* x, const void* qweight, const void* scales, v
     });
 }
 
-int cpmcu_bench_linear(int M, int N, int K, int copies, int iters, int grid_limit, float* avg_us) {
+static int bench_linear_impl(int M, int N, int K, int copies, int iters, int grid_limit, float* avg_us, bool w4) {
     return guarded([&] {
         Runtime& rt = runtime();
         cudaStream_t s = rt.stream;
@@ -383,7 +385,6 @@ int cpmcu_bench_linear(int M, int N, int K, int copies, int iters, int grid_limi
         CUDA_CHECK(cudaMemsetAsync(tickets.p, 0, 2 * tiles * sizeof(int), s));
         CUDA_CHECK(cudaMemsetAsync(w.p, 0x3c, wbytes * copies, s));
         CUDA_CHECK(cudaMemsetAsync(x.p, 0x3c, static_cast<size_t>(M) * K * 2, s));
-        const bool w4 = getenv("CPMCU_BENCH_W4") != nullptr;
         std::vector<LinearPlan> plans;
         for (int c = 0; c < copies; ++c) {
             if (w4) {  // the same buffer read as 4-bit blocks: about a quarter of the bytes per launch
@@ -397,7 +398,7 @@ int cpmcu_bench_linear(int M, int N, int K, int copies, int iters, int grid_limi
                                              reinterpret_cast<const bf16*>(static_cast<uint8_t*>(w.p) + wbytes * c), M, N, K,
                                              static_cast<bf16*>(y.p), N, nullptr, static_cast<float*>(ws.p),
                                              static_cast<int*>(tickets.p), limit));
-            const char* dbg = getenv("CPMCU_LINEAR_DEBUG");
+            const char* dbg = tuning_env("CPMCU_LINEAR_DEBUG");
             if (dbg) plans.back().debug = atoi(dbg);
         }
         for (int c = 0; c < copies && c < 3; ++c) launch_linear(plans[c], s);
@@ -417,6 +418,14 @@ int cpmcu_bench_linear(int M, int N, int K, int copies, int iters, int grid_limi
         sync_and_check("bench_linear");
         return 0;
     });
+}
+
+int cpmcu_bench_linear(int M, int N, int K, int copies, int iters, int grid_limit, float* avg_us) {
+    return bench_linear_impl(M, N, K, copies, iters, grid_limit, avg_us, false);
+}
+
+int cpmcu_bench_linear_w4(int M, int N, int K, int copies, int iters, int grid_limit, float* avg_us) {
+    return bench_linear_impl(M, N, K, copies, iters, grid_limit, avg_us, true);
 }
 
 int cpmcu_tree_attention(const void* q, int q_ld, const void* k_cache, const void* v_cache, int budget, int tq,
@@ -594,7 +603,7 @@ int cpmcu_rope_append(void* qkv, int rows, int hq, int hkv, const float* inv_fre
     return guarded([&] {
         launch_rope_append(static_cast<bf16*>(qkv), rows, hq, hkv, 128, inv_freq, pos, nullptr, 0, 0,
                            static_cast<bf16*>(k_cache), static_cast<bf16*>(v_cache), kv_len, kv_off, nullptr,
-                           runtime().stream);
+                           0x7fffffff, runtime().stream);
         sync_and_check("rope_append");
         return 0;
     });
@@ -665,9 +674,11 @@ int cpmcu_draft_tree_from_logits(const void* logits, int vocab, int k, int num_i
     });
 }
 
-int cpmcu_verify_and_compact(int tree_size, int32_t* pred, const int32_t* gt, const int32_t* position_ids,
-                             const int32_t* cache_length, const uint64_t* attn_mask, const int32_t* tree_parent,
-                             void* const* caches, int num_caches, int kv_dim, int max_accept, int32_t* result) {
+int cpmcu_accept_fixup(int tree_size, int32_t* pred, const int32_t* gt, const int32_t* position_ids,
+                       const int32_t* cache_length, const uint64_t* attn_mask, const int32_t* tree_parent,
+                       void* const* caches, int num_caches, int kv_dim, int cache_rows, int max_accept, int hidden,
+                       const void* norm_out, void* prev_hidden, const void* embed_table, float embed_scale,
+                       void* prev_embed, int32_t* eagle_pos, int32_t* result) {
     return guarded([&] {
         cudaStream_t s = runtime().stream;
         AcceptIO io;
@@ -679,21 +690,33 @@ int cpmcu_verify_and_compact(int tree_size, int32_t* pred, const int32_t* gt, co
         io.attn_mask = attn_mask;
         io.tree_parent = tree_parent;
         io.result = result;
-        launch_verify_accept(io, s);
-        if (num_caches > 0) {
-            FixupArgs f;
-            f.result = result;
-            f.cache_length = cache_length;
-            f.caches = reinterpret_cast<bf16* const*>(caches);
-            f.num_caches = num_caches;
-            f.kv_dim = kv_dim;
-            f.max_accept = max_accept;
-            f.hidden = 0;
-            launch_accept_fixup(f, s);
+        FixupArgs f;
+        f.caches = reinterpret_cast<bf16* const*>(caches);
+        f.num_caches = num_caches;
+        f.kv_dim = num_caches > 0 ? kv_dim : 8;
+        f.max_accept = max_accept;
+        f.hidden = hidden;
+        if (hidden > 0) {
+            CPM_REQUIRE(norm_out && prev_hidden && embed_table && prev_embed && eagle_pos,
+                        "accept_fixup: hidden > 0 needs the hidden-state and embedding buffers");
+            f.norm_out = static_cast<const bf16*>(norm_out);
+            f.prev_hidden = static_cast<bf16*>(prev_hidden);
+            f.embed_table = static_cast<const bf16*>(embed_table);
+            f.embed_scale = embed_scale;
+            f.prev_embed = static_cast<bf16*>(prev_embed);
+            f.eagle_pos = eagle_pos;
         }
-        sync_and_check("verify_and_compact");
+        launch_accept_fixup(io, f, cache_rows, s);
+        sync_and_check("accept_fixup");
         return 0;
     });
+}
+
+int cpmcu_verify_and_compact(int tree_size, int32_t* pred, const int32_t* gt, const int32_t* position_ids,
+                             const int32_t* cache_length, const uint64_t* attn_mask, const int32_t* tree_parent,
+                             void* const* caches, int num_caches, int kv_dim, int max_accept, int32_t* result) {
+    return cpmcu_accept_fixup(tree_size, pred, gt, position_ids, cache_length, attn_mask, tree_parent, caches, num_caches,
+                              kv_dim, 0x7fffffff, max_accept, 0, nullptr, nullptr, nullptr, 1.f, nullptr, nullptr, result);
 }
 
 }  // extern "C"

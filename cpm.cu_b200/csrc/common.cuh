@@ -27,6 +27,19 @@ typedef __nv_bfloat16 bf16;
         if (!(cond)) throw std::invalid_argument(std::string("cpmcu_b200: ") + (msg)); \
     } while (0)
 
+// Tuning switches (grid and split sweeps, A/B of the cluster split-K, plan printing, timing experiments that skip
+// loads or stores and therefore give wrong results) exist only in builds made with
+// CPMCU_BUILD_DEFINES=-DCPMCU_TUNING: a normal build reads none of these variables and its kernels carry none of
+// these branches.
+#ifdef CPMCU_TUNING
+#include <cstdlib>
+inline const char* tuning_env(const char* name) { return getenv(name); }
+#define CPM_EXPERIMENT(args, bits) ((args).debug & (bits))
+#else
+inline const char* tuning_env(const char*) { return nullptr; }
+#define CPM_EXPERIMENT(args, bits) 0
+#endif
+
 // Records the message cpmcu_last_error() returns on this thread (capi.cu).
 void cpm_set_error(const char* msg);
 
@@ -40,6 +53,7 @@ enum KernelError : int {
     ERR_GEMM_TIMEOUT = 1,
     ERR_ATTN_TIMEOUT = 2,
     ERR_BAD_TREE = 4,
+    ERR_KV_OVERFLOW = 8,  // a K/V row beyond the cache budget was about to be written (the store is skipped)
 };
 
 enum KernelClass : int { KC_LINEAR = 0, KC_ATTENTION = 1, KC_OTHER = 2, KC_COUNT = 3 };
@@ -47,6 +61,7 @@ enum KernelClass : int { KC_LINEAR = 0, KC_ATTENTION = 1, KC_OTHER = 2, KC_COUNT
 struct Runtime {
     cudaStream_t stream = nullptr;
     int* d_error = nullptr;  // device error word, or-ed into by kernels
+    unsigned* d_accept_ticket = nullptr;  // CTAs of the acceptance kernel that have read the tree (zero between launches)
     int num_sms = 148;
     int device = 0;
     long launches = 0;  // kernels launched (or captured) so far by this library
@@ -169,7 +184,7 @@ struct LinearPlan {
     const bf16* bias = nullptr;
     float* workspace = nullptr;  // split-K partials: grid * 2 * mt * 128 floats
     int* tickets = nullptr;      // two counters per output tile (pieces counted, readers gone), zero between launches
-    int debug = 0;               // bench-only switches, see gemm_umma.cu
+    int debug = 0;               // timing experiments of -DCPMCU_TUNING builds (CPM_EXPERIMENT); unused otherwise
     int cluster = 0;             // > 0: CTAs per tile, pieces summed inside a thread-block cluster (bf16 path)
     // W4A16: when wq is set the weights are 4-bit blocks in the streaming layout (see gemm_w4_umma.cu)
     const void* wq = nullptr;
@@ -212,10 +227,11 @@ void launch_embedding_gather(const int32_t* ids, const bf16* table, bf16* out, i
 // qkv: [rows, (hq + 2 hkv) * d].  Applies NeoX RoPE to q (in place) and k, then
 // writes k,v into the cache at row (*kv_len + kv_off + r) for r < *n_valid
 // (n_valid may be null = rows).  Position of row r: pos[r], or when pos is
-// null *pos_base + pos_off + r * pos_step.
+// null *pos_base + pos_off + r * pos_step.  cache_rows: rows the caches hold; a row at or beyond it is not
+// stored and raises ERR_KV_OVERFLOW in the device error word.
 void launch_rope_append(bf16* qkv, int rows, int hq, int hkv, int d, const float* inv_freq, const int32_t* pos,
                         const int32_t* pos_base, int pos_off, int pos_step, bf16* k_cache, bf16* v_cache,
-                        const int32_t* kv_len, int kv_off, const int32_t* n_valid, cudaStream_t s);
+                        const int32_t* kv_len, int kv_off, const int32_t* n_valid, int cache_rows, cudaStream_t s);
 void launch_silu_gate(const bf16* gate_up, bf16* out, int rows, int inter, cudaStream_t s);
 void launch_add_scaled(bf16* x, const bf16* a, const bf16* b, float scale_b, int rows, int dim,
                        cudaStream_t s);  // x = a + b*scale

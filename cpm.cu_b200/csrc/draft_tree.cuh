@@ -48,22 +48,20 @@ struct AcceptIO {
     const int32_t* tree_parent = nullptr;
     int32_t* result = nullptr;          // [0]=accept length n, [1]=best node, [2..2+n) path node ids
 };
-void launch_verify_accept(const AcceptIO& io, cudaStream_t s);
 
 struct FixupArgs {
-    const int32_t* result = nullptr;      // from launch_verify_accept
-    const int32_t* cache_length = nullptr;
     bf16* const* caches = nullptr;        // device array of num_caches K/V base pointers
     int num_caches = 0;
     int kv_dim = 0;                       // elements per cache row
     int max_accept = 0;                   // num_iter + 1
     const bf16* norm_out = nullptr;       // [tree_size, hidden] target final-norm rows
     bf16* prev_hidden = nullptr;          // [max_accept, hidden]
-    const int32_t* tokens = nullptr;      // emitted tokens (pred after verify)
     const bf16* embed_table = nullptr;
     float embed_scale = 1.f;
     bf16* prev_embed = nullptr;           // [max_accept, hidden]
     int32_t* eagle_pos = nullptr;         // [max_accept] = cache_length + i
-    int hidden = 0;
+    int hidden = 0;                       // 0: caches only (no hidden-state gather, no embeddings)
 };
-void launch_accept_fixup(const FixupArgs& a, cudaStream_t s);
+// One launch: acceptance (every CTA recomputes it) + fix-up; io.pred / io.result are written by the CTA that
+// is counted last.  cache_rows: rows each cache holds (compaction beyond it is skipped and flagged).
+void launch_accept_fixup(const AcceptIO& io, const FixupArgs& a, int cache_rows, cudaStream_t s);

@@ -154,7 +154,7 @@ __global__ void rope_append_kernel(bf16* __restrict__ qkv, int hq, int hkv, int 
                                    const int32_t* __restrict__ pos, const int32_t* __restrict__ pos_base, int pos_off,
                                    int pos_step, bf16* __restrict__ k_cache, bf16* __restrict__ v_cache,
                                    const int32_t* __restrict__ kv_len, int kv_off,
-                                   const int32_t* __restrict__ n_valid) {
+                                   const int32_t* __restrict__ n_valid, int cache_rows, int* __restrict__ error) {
     grid_dependency_sync();
     __shared__ float s_cos[128], s_sin[128];
     const int r = blockIdx.x;
@@ -162,8 +162,12 @@ __global__ void rope_append_kernel(bf16* __restrict__ qkv, int hq, int hkv, int 
     const int ld = (hq + 2 * hkv) * d;
     bf16* row = qkv + static_cast<size_t>(r) * ld;
     const int p = (pos != nullptr) ? pos[r] : (*pos_base + pos_off + r * pos_step);
-    const bool store_kv = (n_valid == nullptr) || (r < *n_valid);
+    bool store_kv = (n_valid == nullptr) || (r < *n_valid);
     const long long kv_row = static_cast<long long>(*kv_len) + kv_off + r;
+    if (store_kv && kv_row >= cache_rows) {  // host-side length checks come first; this only keeps memory intact
+        store_kv = false;
+        if (threadIdx.x == 0) atomicOr(error, ERR_KV_OVERFLOW);
+    }
     const int kv_dim = hkv * d;
     if (threadIdx.x < half) {
         float sn, cs;
@@ -369,12 +373,12 @@ void launch_embedding_gather(const int32_t* ids, const bf16* table, bf16* out, i
 
 void launch_rope_append(bf16* qkv, int rows, int hq, int hkv, int d, const float* inv_freq, const int32_t* pos,
                         const int32_t* pos_base, int pos_off, int pos_step, bf16* k_cache, bf16* v_cache,
-                        const int32_t* kv_len, int kv_off, const int32_t* n_valid, cudaStream_t s) {
+                        const int32_t* kv_len, int kv_off, const int32_t* n_valid, int cache_rows, cudaStream_t s) {
     if (rows <= 0) return;
     CPM_REQUIRE(pos != nullptr || pos_base != nullptr, "rope: no positions given");
     CPM_REQUIRE(d % 4 == 0 && d <= 256, "rope: head_dim must be a multiple of 4 and at most 256");
     launch_kernel(rope_append_kernel, dim3(rows), dim3(256), 0, s, qkv, hq, hkv, d, inv_freq, pos, pos_base, pos_off,
-                  pos_step, k_cache, v_cache, kv_len, kv_off, n_valid);
+                  pos_step, k_cache, v_cache, kv_len, kv_off, n_valid, cache_rows, runtime().d_error);
 }
 
 void launch_silu_gate(const bf16* gate_up, bf16* out, int rows, int inter, cudaStream_t s) {

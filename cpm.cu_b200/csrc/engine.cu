@@ -47,6 +47,14 @@ __global__ void gather_rows_kernel(const bf16* __restrict__ src, const int32_t* 
     }
 }
 
+// The engine's split-K counters (two per output tile) live in one buffer of kTicketInts ints.
+constexpr int kTicketInts = 1 << 16;
+LinearPlan checked(const LinearPlan& p) {
+    CPM_REQUIRE(2LL * ceil_div(p.N, 128) * ceil_div(p.M, p.mt) <= kTicketInts,
+                "linear: more output tiles than the engine's split-K counters cover");
+    return p;
+}
+
 void copy_rows(bf16* dst, int ld_dst, const bf16* src, int ld_src, int rows, int dim, cudaStream_t s) {
     if (rows <= 0) return;
     CUDA_CHECK(cudaMemcpy2DAsync(dst, static_cast<size_t>(ld_dst) * 2, src, static_cast<size_t>(ld_src) * 2,
@@ -84,6 +92,7 @@ Engine::~Engine() {
     if (step_graph_) cudaGraphExecDestroy(step_graph_);
     if (ev0_) cudaEventDestroy(ev0_);
     if (ev1_) cudaEventDestroy(ev1_);
+    if (ev_mid_) cudaEventDestroy(ev_mid_);
     if (pool_.base) cudaFree(pool_.base);
     if (h_result_) cudaFreeHost(h_result_);
 }
@@ -110,7 +119,7 @@ int Engine::attn_splits_for(int rows) const {
     const int grp = mc_.hq / mc_.hkv;
     const int mtiles = ceil_div(rows, 128 / grp) * mc_.hkv;
     int s = runtime().num_sms / mtiles;
-    static const char* forced = getenv("CPMCU_ATTN_SPLITS");  // bench only: sweep the number of key splits
+    static const char* forced = tuning_env("CPMCU_ATTN_SPLITS");  // bench only: sweep the number of key splits
     if (forced && atoi(forced) >= 1) s = atoi(forced);
     return std::max(1, std::min(s, 32));
 }
@@ -166,7 +175,7 @@ void Engine::lay_out(Pool& p) {
     lm_in_ = take<bf16>(p, static_cast<size_t>(64) * H);
     logits_ = take<bf16>(p, static_cast<size_t>(64) * V);
     gemm_ws_ = reinterpret_cast<float*>(p.take(linear_workspace_bytes(256, runtime().num_sms)));
-    tickets_ = take<int>(p, 1 << 16);
+    tickets_ = take<int>(p, kTicketInts);
     {
         size_t a = 0;
         for (int rows = 1; rows <= 64; ++rows) {
@@ -280,6 +289,7 @@ int Engine::init_storage() {
     memset(h_result_, 0, 32 * sizeof(int32_t));
     CUDA_CHECK(cudaEventCreate(&ev0_));
     CUDA_CHECK(cudaEventCreate(&ev1_));
+    CUDA_CHECK(cudaEventCreate(&ev_mid_));
     storage_ready_ = true;
 
     if (has_eagle_) {
@@ -289,14 +299,14 @@ int Engine::init_storage() {
         build_layer_plans(eplan_catchup_, elayer_, ekv_, rc, attn_splits_for(rc));
         eplan_level_.attn.window = ec_.window;
         eplan_catchup_.attn.window = ec_.window;
-        fc_plan_level_ = make_linear_plan(e_in_, k, fc_, k, H, 2 * H, e_x_, H, fc_bias_, gemm_ws_, tickets_, rt.num_sms);
-        fc_plan_catchup_ = make_linear_plan(e_in_, rc, fc_, rc, H, 2 * H, e_x_, H, fc_bias_, gemm_ws_, tickets_, rt.num_sms);
+        fc_plan_level_ = checked(make_linear_plan(e_in_, k, fc_, k, H, 2 * H, e_x_, H, fc_bias_, gemm_ws_, tickets_, rt.num_sms));
+        fc_plan_catchup_ = checked(make_linear_plan(e_in_, rc, fc_, rc, H, 2 * H, e_x_, H, fc_bias_, gemm_ws_, tickets_, rt.num_sms));
         const bool scale_in = (!ec_.minicpm4_variant && mc_.scale_lmhead != 1.0f);
         const bf16* lm_x = scale_in ? lm_in_ : e_h_;
-        dlm_plan_level_ = make_linear_plan(lm_x, k, draft_lm_head_, k, draft_vocab_, H, e_logits_, draft_vocab_, nullptr,
-                                           gemm_ws_, tickets_, rt.num_sms);
-        dlm_plan_catchup_ = make_linear_plan(lm_x, rc, draft_lm_head_, rc, draft_vocab_, H, e_logits_, draft_vocab_,
-                                             nullptr, gemm_ws_, tickets_, rt.num_sms);
+        dlm_plan_level_ = checked(make_linear_plan(lm_x, k, draft_lm_head_, k, draft_vocab_, H, e_logits_, draft_vocab_, nullptr,
+                                           gemm_ws_, tickets_, rt.num_sms));
+        dlm_plan_catchup_ = checked(make_linear_plan(lm_x, rc, draft_lm_head_, rc, draft_vocab_, H, e_logits_, draft_vocab_,
+                                             nullptr, gemm_ws_, tickets_, rt.num_sms));
     }
     return budget_;
 }
@@ -420,15 +430,15 @@ void Engine::build_layer_plans(LayerPlans& lp, const LayerWeights& w, const KVLa
     const int H = mc_.hidden, I = mc_.inter, d = mc_.head_dim;
     const int sms = runtime().num_sms;
     if (w.qkv_q != nullptr) {  // W4A16 layer
-        lp.qkv = make_linear_plan_w4(normed_, rows, w.qkv_q, rows, qkv_dim_, H, qkv_, qkv_dim_, gemm_ws_, tickets_, sms);
-        lp.o = make_linear_plan_w4(attn_out_, rows, w.o_q, rows, H, mc_.hq * d, delta_, H, gemm_ws_, tickets_, sms);
-        lp.gate_up = make_linear_plan_w4(normed_, rows, w.gate_up_q, rows, 2 * I, H, gate_up_, 2 * I, gemm_ws_, tickets_, sms);
-        lp.down = make_linear_plan_w4(act_, rows, w.down_q, rows, H, I, delta_, H, gemm_ws_, tickets_, sms);
+        lp.qkv = checked(make_linear_plan_w4(normed_, rows, w.qkv_q, rows, qkv_dim_, H, qkv_, qkv_dim_, gemm_ws_, tickets_, sms));
+        lp.o = checked(make_linear_plan_w4(attn_out_, rows, w.o_q, rows, H, mc_.hq * d, delta_, H, gemm_ws_, tickets_, sms));
+        lp.gate_up = checked(make_linear_plan_w4(normed_, rows, w.gate_up_q, rows, 2 * I, H, gate_up_, 2 * I, gemm_ws_, tickets_, sms));
+        lp.down = checked(make_linear_plan_w4(act_, rows, w.down_q, rows, H, I, delta_, H, gemm_ws_, tickets_, sms));
     } else {
-        lp.qkv = make_linear_plan(normed_, rows, w.qkv, rows, qkv_dim_, H, qkv_, qkv_dim_, nullptr, gemm_ws_, tickets_, sms);
-        lp.o = make_linear_plan(attn_out_, rows, w.o, rows, H, mc_.hq * d, delta_, H, nullptr, gemm_ws_, tickets_, sms);
-        lp.gate_up = make_linear_plan(normed_, rows, w.gate_up, rows, 2 * I, H, gate_up_, 2 * I, nullptr, gemm_ws_, tickets_, sms);
-        lp.down = make_linear_plan(act_, rows, w.down, rows, H, I, delta_, H, nullptr, gemm_ws_, tickets_, sms);
+        lp.qkv = checked(make_linear_plan(normed_, rows, w.qkv, rows, qkv_dim_, H, qkv_, qkv_dim_, nullptr, gemm_ws_, tickets_, sms));
+        lp.o = checked(make_linear_plan(attn_out_, rows, w.o, rows, H, mc_.hq * d, delta_, H, nullptr, gemm_ws_, tickets_, sms));
+        lp.gate_up = checked(make_linear_plan(normed_, rows, w.gate_up, rows, 2 * I, H, gate_up_, 2 * I, nullptr, gemm_ws_, tickets_, sms));
+        lp.down = checked(make_linear_plan(act_, rows, w.down, rows, H, I, delta_, H, nullptr, gemm_ws_, tickets_, sms));
     }
     lp.attn = make_attn_plan(qkv_, qkv_dim_, kv.k, kv.v, budget_, rows, mc_.hq, mc_.hkv, d, attn_splits, attn_out_,
                              mc_.hq * d, attn_ws_o_, attn_ws_ml_);
@@ -461,7 +471,7 @@ void Engine::layer_forward(LayerPlans& lp, const LayerWeights& w, const KVLayer&
     }
     launch_linear(lp.qkv, s);
     launch_rope_append(qkv_, rows, mc_.hq, mc_.hkv, mc_.head_dim, inv_freq_, c.pos, c.pos_base, c.pos_off, c.pos_step,
-                       kv.k, kv.v, c.kv_len, c.kv_append_off, c.n_valid, s);
+                       kv.k, kv.v, c.kv_len, c.kv_append_off, c.n_valid, budget_, s);
     lp.attn.kv_len = c.kv_len;
     lp.attn.kv_len_add = c.attn_kv_add;
     lp.attn.n_valid = c.n_valid;
@@ -507,8 +517,8 @@ void Engine::lm_head_rows(const bf16* x, int x_rows, int rows, bf16* logits_out,
         in = lm_in_;
         x_rows = rows;
     }
-    LinearPlan p = make_linear_plan(in, x_rows, lm_head_, rows, mc_.vocab, mc_.hidden, logits_out, ld, nullptr,
-                                    gemm_ws_, tickets_, runtime().num_sms);
+    LinearPlan p = checked(make_linear_plan(in, x_rows, lm_head_, rows, mc_.vocab, mc_.hidden, logits_out, ld, nullptr,
+                                    gemm_ws_, tickets_, runtime().num_sms));
     launch_linear(p, s);
 }
 
@@ -561,16 +571,19 @@ void Engine::prefill(int n, int history, const int32_t* ids, const int32_t* pos,
         num_history_ = history;
         first_draft_ = true;
     }
+    host_len_ = static_cast<long>(history) + n;
     CUDA_CHECK(cudaStreamSynchronize(s));
     check_errors("prefill");
 }
 
 void Engine::decode(int n, int padded_len, const int32_t* ids, const int32_t* pos, const int32_t* cache_length,
                     const uint64_t* mask, bf16* logits_out, bool cuda_graph) {
-    (void)padded_len;
     (void)cuda_graph;
     CPM_REQUIRE(storage_ready_, "decode before init_storage");
     CPM_REQUIRE(n >= 1 && n <= 64, "decode supports 1..64 tokens");
+    // padded_len is the caller's ceil((cache length + n) / 128) * 128 and the budget is a multiple of 128
+    CPM_REQUIRE(padded_len <= 0 || padded_len <= budget_, "decode: cache length + tokens exceeds the KV budget");
+    require_room(n, "decode");
     cudaStream_t s = runtime().stream;
     RowCtx c;
     c.rows = n;
@@ -604,7 +617,7 @@ void Engine::draft_first(int history, cudaStream_t s) {
         copy_rows(e_in_, 2 * H, prev_embed_, H, P, H, s);
         copy_rows(e_in_ + H, 2 * H, prev_hidden_, H, P, H, s);
     }
-    LinearPlan fc = make_linear_plan(e_in_, P, fc_, P, H, 2 * H, e_x_, H, fc_bias_, gemm_ws_, tickets_, rt.num_sms);
+    LinearPlan fc = checked(make_linear_plan(e_in_, P, fc_, P, H, 2 * H, e_x_, H, fc_bias_, gemm_ws_, tickets_, rt.num_sms));
     launch_linear(fc, s);
     CUDA_CHECK(cudaMemcpyAsync(st_ + 7, &history, sizeof(int), cudaMemcpyHostToDevice, s));
     LayerPlans lp;
@@ -640,7 +653,7 @@ void Engine::draft_catchup(cudaStream_t s) {
         else copy_rows(normed_, H, e_x_, H, rc, H, s);
         launch_linear(lp.qkv, s);
         launch_rope_append(qkv_, rc, mc_.hq, mc_.hkv, mc_.head_dim, inv_freq_, eagle_pos_, nullptr, 0, 0, ekv_.k, ekv_.v,
-                           st_ + S_BASE, 0, st_ + S_NPREV, s);
+                           st_ + S_BASE, 0, st_ + S_NPREV, budget_, s);
         lp.attn.kv_len = st_ + S_L;
         lp.attn.kv_len_add = 0;
         lp.attn.n_valid = st_ + S_NPREV;
@@ -675,8 +688,8 @@ void Engine::draft_levels(int32_t* tree_ids, int32_t* tree_pos, const int32_t* c
             launch_scale(lm_in_, last, mc_.scale_lmhead, H, s);
             in = lm_in_;
         }
-        LinearPlan p = make_linear_plan(in, 1, draft_lm_head_, 1, draft_vocab_, H, e_logits_, draft_vocab_, nullptr,
-                                        gemm_ws_, tickets_, rt.num_sms);
+        LinearPlan p = checked(make_linear_plan(in, 1, draft_lm_head_, 1, draft_vocab_, H, e_logits_, draft_vocab_, nullptr,
+                                        gemm_ws_, tickets_, rt.num_sms));
         launch_linear(p, s);
         launch_draft_topk_expand(tree_, e_logits_, draft_vocab_, draft_vocab_, 0, scan_ws_, last, H, nullptr, nullptr,
                                  hid_ld, H, s);
@@ -721,6 +734,7 @@ void Engine::draft_levels(int32_t* tree_ids, int32_t* tree_pos, const int32_t* c
 void Engine::draft(int32_t* tree_ids, int32_t* tree_pos, const int32_t* cache_length, uint64_t* tree_mask,
                    int32_t* tree_parent) {
     CPM_REQUIRE(has_eagle_ && storage_ready_, "draft needs an initialised drafter");
+    require_room(static_cast<long>(ec_.topk) * (ec_.num_iter - 1), "draft");
     cudaStream_t s = runtime().stream;
     const int H = mc_.hidden;
     if (first_draft_) {
@@ -750,23 +764,19 @@ void Engine::accept_and_fix(int T, int32_t* pred, const int32_t* gt, const int32
     io.attn_mask = mask;
     io.tree_parent = parent;
     io.result = accept_result_;
-    launch_verify_accept(io, s);
     FixupArgs f;
-    f.result = accept_result_;
-    f.cache_length = cache_length;
     f.caches = d_cache_ptrs_;
     f.num_caches = 2 * mc_.layers;
     f.kv_dim = mc_.hkv * mc_.head_dim;
     f.max_accept = has_eagle_ ? catchup_rows_ : 1;
     f.norm_out = norm_out_;
     f.prev_hidden = prev_hidden_;
-    f.tokens = pred;
     f.embed_table = embed_;
     f.embed_scale = mc_.scale_embed;
     f.prev_embed = prev_embed_;
     f.eagle_pos = eagle_pos_;
     f.hidden = mc_.hidden;
-    launch_accept_fixup(f, s);
+    launch_accept_fixup(io, f, budget_, s);
     launch_kernel(publish_kernel, dim3(1), dim3(32), 0, s, accept_result_, pred, runtime().d_error, st_, d_publish_);
 }
 
@@ -780,14 +790,31 @@ int Engine::verify_and_fix(int T, int32_t* pred, const int32_t* gt, const int32_
     CUDA_CHECK(cudaStreamSynchronize(s));
     if (h_result_[31] != 0) check_errors("verify_and_fix");
     num_prev_ = h_result_[0];
+    if (host_len_ >= 0) host_len_ += h_result_[0];
     return h_result_[0];
 }
 
 void Engine::check_errors(const char* where) {
     const int e = read_and_clear_error();
     if (e != 0) {
+        if (e & ERR_GEMM_TIMEOUT) {
+            // a split-K tile that gave up leaves its piece counters non-zero; later GEMMs would miscount
+            cudaMemsetAsync(tickets_, 0, sizeof(int) * kTicketInts, runtime().stream);
+            cudaMemsetAsync(runtime().d_accept_ticket, 0, sizeof(unsigned), runtime().stream);
+            cudaStreamSynchronize(runtime().stream);
+        }
         throw std::runtime_error(std::string("cpmcu_b200: kernel error flags ") + std::to_string(e) + " raised in " +
-                                 where + " (1 = GEMM pipeline timeout, 2 = attention pipeline timeout, 4 = malformed draft tree)");
+                                 where + " (1 = GEMM pipeline timeout, 2 = attention pipeline timeout, 4 = malformed draft tree, "
+                                 "8 = K/V row beyond the cache budget)");
+    }
+}
+
+// A pass that appends `rows_after_len` K/V rows behind the host-known length must fit the budget.
+void Engine::require_room(long rows_after_len, const char* where) const {
+    if (host_len_ >= 0 && host_len_ + rows_after_len > budget_) {
+        throw std::runtime_error(std::string("cpmcu_b200: ") + where + " would write K/V row " +
+                                 std::to_string(host_len_ + rows_after_len - 1) + " but the cache holds " +
+                                 std::to_string(budget_) + " rows (raise memory_limit or shorten the generation)");
     }
 }
 
@@ -798,6 +825,8 @@ void Engine::begin_generation(int prefix_length, int32_t root_token) {
     cudaStream_t s = runtime().stream;
     int32_t init[S_COUNT] = {0};
     init[S_L] = prefix_length;
+    CPM_REQUIRE(prefix_length >= 1 && prefix_length <= budget_, "begin_generation: prefix length out of range");
+    host_len_ = prefix_length;
     CUDA_CHECK(cudaMemcpyAsync(st_, init, 6 * sizeof(int32_t), cudaMemcpyHostToDevice, s));
     CUDA_CHECK(cudaMemcpyAsync(t_ids_, &root_token, sizeof(int32_t), cudaMemcpyHostToDevice, s));
     CUDA_CHECK(cudaStreamSynchronize(s));
@@ -807,6 +836,9 @@ void Engine::begin_generation(int prefix_length, int32_t root_token) {
 // target verify forward, argmax, acceptance, fix-up, publish.
 void Engine::enqueue_step(bool first, cudaStream_t s) {
     const int T = ec_.tree_size, H = mc_.hidden;
+    cudaStreamCaptureStatus cap = cudaStreamCaptureStatusNone;
+    CUDA_CHECK(cudaStreamIsCapturing(s, &cap));
+    const bool capturing = (cap == cudaStreamCaptureStatusActive);
     launch_kernel(state_sync_kernel, dim3(1), dim3(1), 0, s, st_, static_cast<const int32_t*>(nullptr), t_ids_, 1);
     if (first) {
         launch_embedding(t_ids_, embed_, prev_embed_ + static_cast<size_t>(num_prev_ - 1) * H, H, 1, H, mc_.scale_embed, s);
@@ -815,6 +847,8 @@ void Engine::enqueue_step(bool first, cudaStream_t s) {
         draft_catchup(s);
     }
     draft_levels(t_ids_, t_pos_, st_ + S_L, t_mask_, t_parent_, first, s);
+    // boundary between the draft half and the verify half of the step (an event node when captured)
+    CUDA_CHECK(cudaEventRecordWithFlags(ev_mid_, s, capturing ? cudaEventRecordExternal : cudaEventRecordDefault));
     RowCtx c;
     c.rows = T;
     c.pos = t_pos_;
@@ -837,8 +871,8 @@ void Engine::enqueue_step(bool first, cudaStream_t s) {
     launch_add_rms_norm(x_, pending, mc_.scale_residual, final_norm_, norm_out_, T, H, mc_.eps, s);
     if (mc_.scale_lmhead != 1.0f) launch_scale(lm_in_, norm_out_, mc_.scale_lmhead, static_cast<size_t>(T) * H, s);
     if (lm_plan_tree_.grid == 0) {
-        lm_plan_tree_ = make_linear_plan(mc_.scale_lmhead != 1.0f ? lm_in_ : norm_out_, T, lm_head_, T, V, H, logits_, V,
-                                         nullptr, gemm_ws_, tickets_, runtime().num_sms);
+        lm_plan_tree_ = checked(make_linear_plan(mc_.scale_lmhead != 1.0f ? lm_in_ : norm_out_, T, lm_head_, T, V, H, logits_, V,
+                                         nullptr, gemm_ws_, tickets_, runtime().num_sms));
     }
     launch_linear(lm_plan_tree_, s);
     launch_argmax(logits_, T, V, V, t_gt_, argmax_ws_, s);
@@ -848,6 +882,7 @@ void Engine::enqueue_step(bool first, cudaStream_t s) {
 
 int Engine::spec_step(int32_t* out_tokens, int max_tokens) {
     CPM_REQUIRE(has_eagle_ && storage_ready_, "spec_step needs an initialised drafter");
+    require_room(std::max<long>(ec_.tree_size, static_cast<long>(ec_.topk) * (ec_.num_iter - 1)), "spec_step");
     Runtime& rt = runtime();
     cudaStream_t s = rt.stream;
     if (first_draft_) {
@@ -881,9 +916,15 @@ int Engine::spec_step(int32_t* out_tokens, int max_tokens) {
     float ms = 0.f;
     CUDA_CHECK(cudaEventElapsedTime(&ms, ev0_, ev1_));
     last_step_ms_ = ms;
+    float ms_d = 0.f, ms_v = 0.f;
+    CUDA_CHECK(cudaEventElapsedTime(&ms_d, ev0_, ev_mid_));
+    CUDA_CHECK(cudaEventElapsedTime(&ms_v, ev_mid_, ev1_));
+    last_draft_ms_ = ms_d;
+    last_verify_ms_ = ms_v;
     if (h_result_[31] != 0) check_errors("spec_step");
     const int n = h_result_[0];
     num_prev_ = n;
+    if (host_len_ >= 0) host_len_ += n;
     for (int i = 0; i < n && i < max_tokens; ++i) out_tokens[i] = h_result_[1 + i];
     return n;
 }
@@ -904,6 +945,7 @@ const int32_t* Engine::tree_buffers(int which) const {
 // CUDA events; returns summed device milliseconds and launch counts per class.
 void Engine::profile_step(float* ms, int* counts, float* total_ms) {
     CPM_REQUIRE(has_eagle_ && storage_ready_ && !first_draft_, "profile_step needs a generation in progress");
+    require_room(std::max<long>(ec_.tree_size, static_cast<long>(ec_.topk) * (ec_.num_iter - 1)), "profile_step");
     Runtime& rt = runtime();
     cudaStream_t s = rt.stream;
     for (int c = 0; c < KC_COUNT; ++c) rt.prof[c].clear();
@@ -936,4 +978,5 @@ void Engine::profile_step(float* ms, int* counts, float* total_ms) {
     }
     if (h_result_[31] != 0) check_errors("profile_step");
     num_prev_ = h_result_[0];
+    if (host_len_ >= 0) host_len_ += h_result_[0];
 }

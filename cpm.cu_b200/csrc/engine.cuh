@@ -97,6 +97,10 @@ public:
     int spec_step(int32_t* out_tokens, int max_tokens);  // returns accept length n; out_tokens[0:n]
     void profile_step(float* ms, int* counts, float* total_ms);
     double last_step_device_ms() const { return last_step_ms_; }
+    // device time of the two halves of the last captured step: state advance + draft loop + tree build, and
+    // the target's verify pass (tree embedding .. LM head .. argmax .. acceptance and fix-up .. publish)
+    double last_draft_ms() const { return last_draft_ms_; }
+    double last_verify_ms() const { return last_verify_ms_; }
     long launches_per_step() const { return launches_per_step_; }
 
     const ModelConfig& config() const { return mc_; }
@@ -218,8 +222,12 @@ private:
     LinearPlan lm_plan_tree_;
 
     cudaGraphExec_t step_graph_ = nullptr;
-    cudaEvent_t ev0_ = nullptr, ev1_ = nullptr;
-    double last_step_ms_ = 0.0;
+    cudaEvent_t ev0_ = nullptr, ev1_ = nullptr, ev_mid_ = nullptr;
+    double last_step_ms_ = 0.0, last_draft_ms_ = 0.0, last_verify_ms_ = 0.0;
+    // tokens whose target K/V rows are final, as far as the host knows (prefill, then every accepted length);
+    // -1 before the first prefill.  Guards every pass against writing K/V rows beyond the budget.
+    long host_len_ = -1;
+    void require_room(long rows_after_len, const char* where) const;
     long launches_per_step_ = 0;
     long launch_counter_ = 0;
 };

@@ -145,7 +145,7 @@ __device__ __forceinline__ void run_epilogue(const LinearArgs& a, SegIter it, ui
         // partial slot layout: [MT tokens][128 features] fp32: a warp touches one 128-byte line per token
 #pragma unroll 1
         for (int c0 = 0; c0 < MT; c0 += 16) {
-            if (c0 >= m_cnt || (a.debug & 2)) break;  // uniform across the CTA
+            if (c0 >= m_cnt || CPM_EXPERIMENT(a, 2)) break;  // uniform across the CTA
             uint32_t r[16];
             ptx::tmem_ld16(t_addr + c0, r);
             if (chain2_off != 0) {
@@ -166,7 +166,7 @@ __device__ __forceinline__ void run_epilogue(const LinearArgs& a, SegIter it, ui
                         }
                     }
                 }
-            } else if (!(a.debug & 4)) {
+            } else if (!CPM_EXPERIMENT(a, 4)) {
 #pragma unroll
                 for (int c = 0; c < 16; ++c) {
                     if (c0 + c < m_cnt) my_ws[(c0 + c) * BLOCK_N + row] = __uint_as_float(r[c]);
@@ -177,7 +177,7 @@ __device__ __forceinline__ void run_epilogue(const LinearArgs& a, SegIter it, ui
         ptx::mbar_arrive(&acc_empty[acc]);
         if (++acc == acc_stages) { acc = 0; acc_phase ^= 1; }
 
-        if (!complete && !(a.debug & (2 | 8))) {
+        if (!complete && !CPM_EXPERIMENT(a, 2 | 8)) {
             const long long tile_u0 = static_cast<long long>(tile) * a.kblocks;
             PendingTile p;
             p.tile = tile;
@@ -200,7 +200,7 @@ __device__ __forceinline__ void run_epilogue(const LinearArgs& a, SegIter it, ui
                 ptx::named_bar_sync(1, 128);
                 const bool is_last = (*s_last != 0);
                 ptx::named_bar_sync(1, 128);  // everyone has read s_last before it can change
-                if (is_last && !(a.debug & 16)) {
+                if (is_last && !CPM_EXPERIMENT(a, 16)) {
                     __threadfence();
                     sum_pieces<MT, CH>(a, p, 0, m_cnt, row);
                 }
@@ -222,7 +222,7 @@ __device__ __forceinline__ void run_epilogue(const LinearArgs& a, SegIter it, ui
         ptx::named_bar_sync(1, 128);
         const bool ready = (*s_last != 0);
         ptx::named_bar_sync(1, 128);  // everyone has read s_last before it can change
-        if (ready && !(a.debug & 16)) {
+        if (ready && !CPM_EXPERIMENT(a, 16)) {
             const int piece = g - p.g_first;
             sum_pieces<MT, CH>(a, p, (p.m_cnt * piece) / p.nseg, (p.m_cnt * (piece + 1)) / p.nseg, row);
         }

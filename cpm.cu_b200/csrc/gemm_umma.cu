@@ -117,7 +117,7 @@ linear_umma_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_consta
                 while (pre < C::STAGES && pit.next(tile, kb0, kb1)) {
                     const int n_tile = tile % a.n_tiles;
                     for (int kb = kb0; kb < kb1 && pre < C::STAGES; ++kb, ++pre) {
-                        ptx::mbar_arrive_expect_tx(&full[pre], (a.debug & 1) ? W_TILE_BYTES : C::STAGE_BYTES);
+                        ptx::mbar_arrive_expect_tx(&full[pre], CPM_EXPERIMENT(a, 1) ? W_TILE_BYTES : C::STAGE_BYTES);
                         ptx::tma_load_2d(tiles + pre * C::STAGE_BYTES, &tm_w, &full[pre], kb * BLOCK_K, n_tile * BLOCK_N);
                     }
                 }
@@ -131,12 +131,12 @@ linear_umma_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_consta
                 for (int kb = kb0; kb < kb1; ++kb, ++issued) {
                     uint8_t* dst = tiles + stage * C::STAGE_BYTES;
                     if (issued < pre) {
-                        if (!(a.debug & 1)) {
+                        if (!CPM_EXPERIMENT(a, 1)) {
                             ptx::tma_load_2d(dst + W_TILE_BYTES, &tm_x, &full[stage], kb * BLOCK_K, m_tile * MT);
                         }
                     } else {
                         if (!ptx::mbar_wait(&empty[stage], phase ^ 1, abort_flag)) { ok = false; break; }
-                        if (a.debug & 1) {
+                        if (CPM_EXPERIMENT(a, 1)) {
                             ptx::mbar_arrive_expect_tx(&full[stage], W_TILE_BYTES);
                             ptx::tma_load_2d(dst, &tm_w, &full[stage], kb * BLOCK_K, n_tile * BLOCK_N);
                         } else {
@@ -489,10 +489,10 @@ LinearPlan make_linear_plan(const bf16* x, int x_rows, const bf16* w, int M, int
     if (grid > grid_limit) grid = grid_limit;
     if (m_tiles == 1 && grid_limit >= 64) grid = pick_grid(n_tiles, kblocks, M, static_cast<int>(grid));
     {
-        static const char* forced = getenv("CPMCU_LINEAR_GRID");  // bench only: sweep the grid size
+        static const char* forced = tuning_env("CPMCU_LINEAR_GRID");  // bench only: sweep the grid size
         if (forced && atoi(forced) >= 1 && atoi(forced) <= grid_limit && atoi(forced) <= units) grid = atoi(forced);
         // bench only: per-shape grids, "MxNxK:grid,MxNxK:grid,..."
-        static const char* per_shape = getenv("CPMCU_LINEAR_GRIDS");
+        static const char* per_shape = tuning_env("CPMCU_LINEAR_GRIDS");
         if (per_shape) {
             char key[64];
             snprintf(key, sizeof(key), "%dx%dx%d:", M, N, K);
@@ -507,7 +507,7 @@ LinearPlan make_linear_plan(const bf16* x, int x_rows, const bf16* w, int M, int
     // CS CTAs per tile with equal k ranges: sum the pieces inside a cluster when the device runs all clusters at once
     p.cluster = 0;
     {
-        static const bool off = getenv("CPMCU_LINEAR_NO_CLUSTER") != nullptr;
+        static const bool off = tuning_env("CPMCU_LINEAR_NO_CLUSTER") != nullptr;
         // the grid picker's pieces per tile first; when the device cannot hold that many clusters at once
         // (its SMs come in groups that need not be multiples of the cluster size), fewer and longer pieces
         int cs = (m_tiles == 1 && grid % n_tiles == 0) ? static_cast<int>(grid / n_tiles) : 0;
@@ -520,7 +520,7 @@ LinearPlan make_linear_plan(const bf16* x, int x_rows, const bf16* w, int M, int
                 }
             }
         }
-        static const bool verbose = getenv("CPMCU_LINEAR_VERBOSE") != nullptr;   // bench only
+        static const bool verbose = tuning_env("CPMCU_LINEAR_VERBOSE") != nullptr;   // bench only
         if (verbose) {
             fprintf(stderr, "linear plan M=%d N=%d K=%d: grid %d, %d tiles, cluster %d (device runs %d / %d / %d clusters of 2 / 3 / 4)\n",
                     M, N, K, p.grid, n_tiles, p.cluster, cluster_capacity(p.mt <= 64 ? p.mt : 64, 2),
@@ -549,7 +549,7 @@ void launch_linear(const LinearPlan& p, cudaStream_t stream) {
     a.error = runtime().d_error;
     a.debug = p.debug;
     {
-        static const char* dbg = getenv("CPMCU_LINEAR_DEBUG_ALL");
+        static const char* dbg = tuning_env("CPMCU_LINEAR_DEBUG_ALL");
         if (dbg) a.debug = atoi(dbg);
     }
     a.prof = nullptr;

@@ -189,7 +189,7 @@ linear_w4_umma_kernel(const __grid_constant__ CUtensorMap tm_x, const W4Args wa)
                 const int n_tile = tile % a.n_tiles;
                 for (int u = u0; u < u1; ++u) {
                     if (!ptx::mbar_wait(&w_empty[stage], phase ^ 1, abort_flag)) { ok = false; break; }
-                    if (a.debug & 64) {  // timing experiment: no weight traffic
+                    if (CPM_EXPERIMENT(a, 64)) {  // timing experiment: no weight traffic
                         ptx::mbar_arrive(&w_full[stage]);
                     } else {
                         ptx::mbar_arrive_expect_tx(&w_full[stage], W_STAGE_BYTES);
@@ -219,7 +219,7 @@ linear_w4_umma_kernel(const __grid_constant__ CUtensorMap tm_x, const W4Args wa)
                 for (int u = u0; u < u1; ++u) {
                     if (!ptx::mbar_wait_warp(&grp_empty[grp], phase ^ 1, abort_flag)) { ok = false; break; }
                     if (ptx::elect_one()) {
-                        if (a.debug & 128) {  // timing experiment: no token traffic
+                        if (CPM_EXPERIMENT(a, 128)) {  // timing experiment: no token traffic
                             ptx::mbar_arrive(&x_full[grp]);
                         } else {
                             ptx::mbar_arrive_expect_tx(&x_full[grp], KB_PER_UNIT * C::X_BYTES);
@@ -267,7 +267,7 @@ linear_w4_umma_kernel(const __grid_constant__ CUtensorMap tm_x, const W4Args wa)
                     t_a += c2 - c1;
                     ptx::tc_fence_after();
                     if (ptx::elect_one()) {
-                        if (!(a.debug & 256)) {
+                        if (!CPM_EXPERIMENT(a, 256)) {
 #pragma unroll
                             for (int h = 0; h < KB_PER_UNIT / 2; ++h) {
                                 const int slot = grp * KB_PER_UNIT + 2 * h + chain;
@@ -323,7 +323,7 @@ linear_w4_umma_kernel(const __grid_constant__ CUtensorMap tm_x, const W4Args wa)
                 t_w += sw.now() - c0;
                 const uint8_t* wst = smem + C::OFF_W + ws * W_STAGE_BYTES;
                 const bf16* sc = reinterpret_cast<const bf16*>(wst + WQ_BYTES);
-                if (a.debug & 32) {  // timing experiment: barriers only
+                if (CPM_EXPERIMENT(a, 32)) {  // timing experiment: barriers only
                     if (!ptx::mbar_wait_warp(&grp_empty[grp], gph ^ 1, abort_flag)) { ok = false; break; }
                 } else {
 #pragma unroll
@@ -415,7 +415,7 @@ long long* w4_prof_buffer() {
     static bool init = false;
     if (!init) {
         init = true;
-        if (getenv("CPMCU_W4_PROF")) {
+        if (tuning_env("CPMCU_W4_PROF")) {
             CUDA_CHECK(cudaMalloc(&buf, 256 * 16 * sizeof(long long)));
             CUDA_CHECK(cudaMemset(buf, 0, 256 * 16 * sizeof(long long)));
         }
@@ -532,7 +532,7 @@ LinearPlan make_linear_plan_w4(const bf16* x, int x_rows, const void* wq, int M,
     // (same rule as the bf16 path; a piece is at least one 256-k unit)
     p.cluster = 0;
     {
-        static const bool off = getenv("CPMCU_LINEAR_NO_CLUSTER") != nullptr;
+        static const bool off = tuning_env("CPMCU_LINEAR_NO_CLUSTER") != nullptr;
         int cs = (m_tiles == 1 && grid % n_tiles == 0) ? static_cast<int>(grid / n_tiles) : 0;
         if (!off && p.mt <= 64 && cs >= 2 && cs <= 4) {
             for (; cs >= 2; --cs) {
@@ -562,7 +562,7 @@ void launch_linear_w4(const LinearPlan& p, cudaStream_t stream) {
     a.y = p.y; a.ldy = p.ldy; a.bias = nullptr;
     a.workspace = p.workspace; a.tickets = p.tickets;
     a.error = runtime().d_error;
-    static const int debug = getenv("CPMCU_LINEAR_DEBUG") ? atoi(getenv("CPMCU_LINEAR_DEBUG")) : 0;
+    static const int debug = tuning_env("CPMCU_LINEAR_DEBUG") ? atoi(tuning_env("CPMCU_LINEAR_DEBUG")) : 0;
     a.debug = debug;
     a.prof = nullptr;
     wa.blocks = static_cast<const uint8_t*>(p.wq);

@@ -50,6 +50,8 @@ Runtime& runtime() {
         CUDA_CHECK(cudaStreamCreate(&rt.stream));
         CUDA_CHECK(cudaMalloc(&rt.d_error, sizeof(int)));
         CUDA_CHECK(cudaMemset(rt.d_error, 0, sizeof(int)));
+        CUDA_CHECK(cudaMalloc(&rt.d_accept_ticket, sizeof(unsigned)));
+        CUDA_CHECK(cudaMemset(rt.d_accept_ticket, 0, sizeof(unsigned)));
         ready = true;
     }
     return rt;

@@ -135,22 +135,28 @@ int cpmcu_spec_step(int32_t* out_tokens, int max_tokens);
 
 /* Runs one more speculative step eagerly (not from the graph) with every launch
  * bracketed by CUDA events on its stream.  class_ms / class_launches receive 3
- * entries (HOST memory): [0] linear layers, [1] attention, [2] unused; total_ms
- * the whole step.  The step's tokens are consumed (generation advances). */
+ * entries (HOST memory): [0] linear layers, [1] attention, [2] InfLLM-v2 block
+ * selection (zero for a dense target); total_ms the whole step.  The step's tokens are consumed (generation advances). */
 int cpmcu_profile_step(float* class_ms, int* class_launches, float* total_ms);
 
 /* Device time of the last cpmcu_spec_step in milliseconds (CUDA events). */
 double cpmcu_last_step_ms(void);
+/* The same step in its two halves, split by an event node inside the captured step: the draft half (state
+ * advance, EAGLE draft loop, tree build) and the verify half, which is what the reference's C.decode +
+ * argmax + C.verify_and_fix cover (tree embedding, target layers, LM head, argmax, acceptance, K/V
+ * compaction and gathers, publishing the result). */
+double cpmcu_last_draft_ms(void);
+double cpmcu_last_verify_ms(void);
 /* Kernels in one captured step / launched by this library so far. */
 long cpmcu_launches_per_step(void);
 long cpmcu_total_launches(void);
-/* Copies the engine-owned tree of the last step to HOST arrays of 64 entries
- * (any pointer may be NULL). */
 /* Test hook (sparse target): from now on every forward pass also copies each target layer's block
  * mask, [hkv][rows][words] packed per layer at stride hkv * max(chunk_length, 64) * words, into
  * device_buf (caller-owned device memory; NULL stops it).  Returns words per mask row. */
 int cpmcu_capture_blockmasks(uint64_t* device_buf);
 
+/* Copies the engine-owned tree of the last step to HOST arrays of 64 entries
+ * (any pointer may be NULL). */
 int cpmcu_get_tree(int32_t* ids, int32_t* pos, int32_t* parent, int32_t* gt, uint64_t* mask, int32_t* state);
 /* Drops the current model (frees the device pool). */
 void cpmcu_release(void);
@@ -175,6 +181,8 @@ int cpmcu_linear_w4a16(const void* x, const void* qweight, const void* scales, v
  * stream with CUDA events, cycling through `copies` separate weight buffers so
  * that the weights come from HBM and not from L2.  avg_us: HOST float. */
 int cpmcu_bench_linear(int M, int N, int K, int copies, int iters, int grid_limit, float* avg_us);
+/* The same for the W4A16 kernel: the buffers are read as 4-bit blocks (any bit pattern is a valid weight). */
+int cpmcu_bench_linear_w4(int M, int N, int K, int copies, int iters, int grid_limit, float* avg_us);
 
 /* reference: mha_fwd_kvcache, src/flash_attn/flash_api.hpp:292-392.
  * q: token t, head h at q + t*q_ld + h*128; caches [budget, hkv*128]; keys
@@ -228,22 +236,28 @@ int cpmcu_argmax(const void* logits, int rows, int vocab, int32_t* out);
 
 /* Row argmax like cpmcu_argmax, but without any device allocation.  It has no
  * counterpart in the reference.  cpmcu_argmax takes its two-stage scratch from
- * cudaMalloc on every call; once cpmcu_init_storage has handed memory_limit of
- * the device to the model pool that allocation can fail, and even when it fits,
- * cudaMalloc and cudaFree synchronise the whole device and so stall a
- * speculative step in flight on the library's stream.  A caller in that
- * position (a serving loop that picks tokens from logits it owns while the
- * engine is live) uses this variant: the scratch is a 16 KB array inside the
- * library image, which every GPU that loads the library keeps until exit.
+ * cudaMalloc on every call and frees it again.  Once cpmcu_init_storage has
+ * handed memory_limit of the device to the model pool that allocation can fail,
+ * and some callers may not allocate at all: a serving loop that picks tokens
+ * from logits it owns while the engine is live, or code running under a memory
+ * budget that was fixed at start-up.  For them the scratch is a 16 KB array
+ * inside the library image, which every GPU that loads the library keeps until
+ * exit; the call makes no cudaMalloc / cudaFree and cannot fail for lack of
+ * memory.
  *   - rows <= 64 and vocab <= 262144, otherwise -1 with a message.
  *   - The first call on each device looks up the array's device address
- *     (cudaGetSymbolAddress, with that device current); make that first call
- *     before opening any stream capture.
- *   - Runs on the legacy default stream and returns after it has drained.
+ *     (cudaGetSymbolAddress, with that device current).
+ *   - EVERY call launches on the legacy default stream and returns after that
+ *     stream has drained.  The library's own stream is a blocking stream, so
+ *     the call orders itself after work already queued there (a speculative
+ *     step in flight finishes first) and before work queued later: it does not
+ *     run beside a step.  For the same reason no call, first or later, may be
+ *     made while any stream of the process is being captured into a CUDA graph.
  *   - All calls share the one array, which keeps the previous call's partials
  *     (each call overwrites what it reads, nothing needs clearing); two calls
  *     that overlap on the GPU, from different host threads or processes sharing
- *     a context, race on it. */
+ *     a context, race on it.  The per-device address cache is written without a
+ *     lock: concurrent first calls store the same value. */
 int cpmcu_argmax_noalloc(const void* logits, int rows, int vocab, int32_t* out);
 
 /* Draft tree from given logits: level 0 uses row 0 of `logits`, level d >= 1
@@ -264,6 +278,18 @@ int cpmcu_draft_tree_from_logits(const void* logits, int vocab, int k, int num_i
 int cpmcu_verify_and_compact(int tree_size, int32_t* pred, const int32_t* gt, const int32_t* position_ids,
                              const int32_t* cache_length, const uint64_t* attn_mask, const int32_t* tree_parent,
                              void* const* caches, int num_caches, int kv_dim, int max_accept, int32_t* result);
+
+/* The whole tail of a speculative step in its one launch: acceptance and K/V compaction as above plus, when
+ * hidden > 0, what the reference's verify does next (src/model/minicpm4/minicpm4_eagle.cuh:398-418,
+ * remap_hidden src/model/eagle.cuh:108-115): prev_hidden[i] = norm_out[path[i]] (rows of `hidden` bf16),
+ * prev_embed[i] = embed_table[emitted token i] * embed_scale, eagle_pos[i] = cache_length + i, for i < n
+ * (eagle_pos for all i < max_accept).  cache_rows: rows every cache holds; a compaction that would touch a
+ * row at or beyond it is skipped and reported as an error.  With hidden == 0 the five buffers may be NULL. */
+int cpmcu_accept_fixup(int tree_size, int32_t* pred, const int32_t* gt, const int32_t* position_ids,
+                       const int32_t* cache_length, const uint64_t* attn_mask, const int32_t* tree_parent,
+                       void* const* caches, int num_caches, int kv_dim, int cache_rows, int max_accept, int hidden,
+                       const void* norm_out, void* prev_hidden, const void* embed_table, float embed_scale,
+                       void* prev_embed, int32_t* eagle_pos, int32_t* result);
 
 #ifdef __cplusplus
 }

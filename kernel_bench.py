@@ -1,9 +1,10 @@
 """Per-kernel timing of the two heavy kernels of the speculative step, through the C ABI.
 
-    python cpm.cu_b200/kernel_bench.py linear [M,N,K] [iters]      bf16 weights
-    python cpm.cu_b200/kernel_bench.py linear_w4 [M,N,K] [iters]   4-bit weights (W4A16)
-    python cpm.cu_b200/kernel_bench.py attention [tq,hq,hkv,kv,splits,mask] [iters]
-    python cpm.cu_b200/kernel_bench.py select [tq,hq,hkv,L,budget] [iters]    InfLLM-v2 block selection of one layer
+    python kernel_bench.py linear [M,N,K] [iters]      bf16 weights
+    python kernel_bench.py linear_w4 [M,N,K] [iters]   4-bit weights (W4A16)
+    python kernel_bench.py attention [tq,hq,hkv,kv,splits,mask] [iters]
+    python kernel_bench.py select [tq,hq,hkv,L,budget] [iters]    InfLLM-v2 block selection of one layer
+    python kernel_bench.py reference                   the reference project's own kernels beside the library's
 
 Each case runs `iters` back-to-back launches inside the library, timed with CUDA events on the
 library's stream, rotating over enough separate weight (or KV-cache) copies that no launch finds
@@ -16,7 +17,8 @@ import ctypes
 import os
 import sys
 
-sys.path.insert(0, os.path.dirname(os.path.abspath(__file__)))
+ROOT = os.path.dirname(os.path.abspath(__file__))
+sys.path.insert(0, os.path.join(ROOT, "cpm.cu_b200"))
 import cpmcu.C as C  # noqa: E402
 
 # qkv, o, gate_up, down, LM head of the 8B shape (hidden 4096, FFN 16384, 32 q / 2 kv heads, vocab 73448)
@@ -34,14 +36,12 @@ def _us(fn, *args):
 
 
 def bench_linear(shapes, iters, w4):
-    if w4:
-        os.environ["CPMCU_BENCH_W4"] = "1"
     for M, N, K in shapes:
         store = N * K * 2                         # bytes of one bf16 copy; the 4-bit run reads a quarter of it
         copies = max(1, min(40, (600 << 20) // store + 1))
         if w4:
             copies = min(64, 4 * copies)          # same footprint to rotate over
-        us = _us("cpmcu_bench_linear", M, N, K, copies, iters, 0)
+        us = _us("cpmcu_bench_linear_w4" if w4 else "cpmcu_bench_linear", M, N, K, copies, iters, 0)
         streamed = store // 4 + (K // 128) * N * 2 if w4 else store
         print(f"{'linear_w4' if w4 else 'linear'} M={M} N={N} K={K} copies={copies}: {us:.1f} us  "
               f"{streamed / us / 1e3:.0f} GB/s", flush=True)
@@ -80,6 +80,56 @@ def bench_select(case, iters):
           f"includes the compression of all {L // 16} + {L // 64} entries and the buffer set-up)", flush=True)
 
 
+def bench_reference(iters=40):
+    """The reference project's own kernels (oracle/_ref/, built by `python -m oracle.build_ref [--marlin] [--flash]`
+    from a reference checkout) timed beside the library's on the same device: its linear<T> (a cuBLAS call), its
+    Marlin W4A16 GEMM and its attention (mha_fwd_kvcache: split kernel + combine), all at the verify / draft shapes
+    of the 8B configuration, operands rotating through HBM.  Prints a table; a missing library skips its rows."""
+    import torch
+    ref_dir = os.path.join(ROOT, "oracle", "_ref")
+    rows = []
+    us = ctypes.c_float(0.0)
+    shapes = [("qkv", 60, 4608, 4096), ("o", 60, 4096, 4096), ("gate_up", 60, 32768, 4096), ("down", 60, 4096, 16384),
+              ("lm_head", 60, 73448, 4096), ("draft lm_head", 10, 73448, 4096)]
+    lib = os.path.join(ref_dir, "libcpmcu_ref_kernels.so")
+    if os.path.exists(lib):
+        r = ctypes.CDLL(lib)
+        for name, M, N, K in shapes:
+            copies = max(2, min(24, int(1.2e9 // (N * K * 2))))
+            assert r.refk_bench_linear(M, N, K, copies, iters, ctypes.byref(us)) == 0
+            rows.append(("bf16 %s M=%d (reference: cuBLAS)" % (name, M), us.value, _us("cpmcu_bench_linear", M, N, K, copies, iters, 0)))
+    lib = os.path.join(ref_dir, "libcpmcu_ref_marlin.so")
+    if os.path.exists(lib):
+        m = ctypes.CDLL(lib)
+        for name, M, N, K in shapes[:4]:
+            copies = max(2, min(24, int(1.2e9 // (N * K // 2))))
+            assert m.refk_bench_marlin(M, N, K, copies, iters, ctypes.byref(us)) == 0
+            rows.append(("W4A16 %s M=%d (reference: Marlin)" % (name, M), us.value,
+                         _us("cpmcu_bench_linear_w4", M, N, K, copies, iters, 0)))
+    lib = os.path.join(ref_dir, "libcpmcu_ref_flash.so")
+    if os.path.exists(lib):
+        f = ctypes.CDLL(lib)
+        for tq, kv, splits in ((60, 4156, 9), (10, 4116, 32), (60, 32828, 9)):
+            hq, hkv, copies = 32, 2, 8
+            padded = (kv + 127) // 128 * 128
+            q = torch.randn(tq, hq * 128, device="cuda").to(torch.bfloat16)
+            ks = [torch.randn(padded, hkv * 128, device="cuda").to(torch.bfloat16) for _ in range(copies)]
+            vs = [torch.randn(padded, hkv * 128, device="cuda").to(torch.bfloat16) for _ in range(copies)]
+            kp = (ctypes.c_void_p * copies)(*[t.data_ptr() for t in ks])
+            vp = (ctypes.c_void_p * copies)(*[t.data_ptr() for t in vs])
+            clen = torch.tensor([kv], dtype=torch.int32, device="cuda")
+            mask = torch.tensor([(1 << i) | 1 for i in range(tq)], dtype=torch.int64, device="cuda")
+            out = torch.empty(tq, hq * 128, dtype=torch.bfloat16, device="cuda")
+            p = lambda t: ctypes.c_void_p(t.data_ptr())  # noqa: E731
+            assert f.refk_bench_mha_fwd_kvcache(tq, padded, hq, hkv, p(q), kp, vp, copies, p(clen), p(mask), p(out), iters,
+                                                ctypes.byref(us)) == 0
+            rows.append(("tree attention tq=%d kv=%d (reference: 16 splits + combine)" % (tq, kv), us.value,
+                         _us("cpmcu_bench_attention", tq, hq, hkv, kv, splits, 1, iters)))
+    print("%-66s %12s %12s %8s" % ("kernel (CUDA events, back-to-back launches)", "reference us", "library us", "ratio"))
+    for name, a, b in rows:
+        print("%-66s %12.1f %12.1f %8.2f" % (name, a, b, a / b), flush=True)
+
+
 def main(argv):
     what = argv[1] if len(argv) > 1 else "linear"
     shape = tuple(int(v) for v in argv[2].split(",")) if len(argv) > 2 else None
@@ -90,6 +140,8 @@ def main(argv):
         bench_linear([shape] if shape else W4_SHAPES, iters, True)
     elif what == "attention":
         bench_attention([shape] if shape else ATTN_CASES, iters)
+    elif what == "reference":
+        bench_reference(iters if len(argv) > 3 else 40)
     elif what == "select":
         bench_select(shape if shape else (60, 32, 2, 32768, 40960), iters if len(argv) > 3 else 3)
     else:

@@ -395,6 +395,18 @@ class OracleModel:
             i += n
         return tokens, accept, steps
 
+    def teacher_forced_logits(self, prompt, tokens):
+        """Target logits for every generated position in ONE causal pass over prompt + tokens[:-1]: row i is
+        the distribution the token tokens[i] was (or should have been) picked from.  Greedy speculative decoding
+        must reproduce greedy plain decoding (cpmcu/speculative/tree_drafter.py:215-252 accepts a drafted token
+        only when it equals the target's argmax), so tokens[i] == argmax(row i) up to near-ties.  Dense target
+        only; overwrites the KV caches."""
+        assert self.sparse is None
+        P = len(prompt)
+        ids = list(prompt) + list(tokens[:-1])
+        norm_out = self.target_forward(ids, np.arange(len(ids)), 0, len(ids))
+        return self.lm_head(norm_out[P - 1:])
+
     def generate_plain(self, prompt, num_tokens):
         """Greedy decoding without speculation (cpmcu/llm.py:285-419, non-stream)."""
         P = len(prompt)

@@ -65,6 +65,44 @@ def top2_gap(logits_row):
     return float(v[0] - v[1])
 
 
+def bf16_step(x):
+    """Spacing of bf16 numbers around x."""
+    return 2.0 ** (np.floor(np.log2(max(abs(float(x)), 1e-30))) - 7)
+
+
+# Near-tie rule of the token-stream comparisons: the two candidates are the top two logits of the row and
+# lie within NEAR_TIE_STEPS bf16 steps of the top logit of each other.  Logits are stored in bf16, whose
+# spacing at the usual logit magnitude (1..8) is 0.0078..0.03, so an absolute gap of 1e-3 cannot be told
+# from a tie at all; this rule is the bf16 equivalent of "top-2 gap below resolution".
+NEAR_TIE_STEPS = 2
+
+
+def check_greedy_stream(oracle, prompt, tokens, what):
+    """Every generated token must be the argmax of the oracle's target logits given the prompt and the tokens
+    before it: greedy speculative decoding reproduces greedy plain decoding.  A different token is tolerated
+    only at a near-tie AT THAT POSITION: it must be the runner-up and within NEAR_TIE_STEPS bf16 steps of the
+    top logit.  Every position is judged given the stream's own prefix, so the check does not stop at the first
+    tolerated tie.  Returns the tolerated ties as (position, gap)."""
+    rows = oracle.teacher_forced_logits(list(prompt), list(tokens))
+    ties = []
+    for i, tok in enumerate(tokens):
+        row = rows[i].float()
+        best = int(torch.argmax(row))        # lowest index among equal maxima, as the reference's argmax
+        if best == tok:
+            continue
+        masked = row.clone()
+        masked[best] = float("-inf")
+        second = int(torch.argmax(masked))
+        gap = float(row[best] - row[second])
+        ok = second == tok and gap <= NEAR_TIE_STEPS * bf16_step(float(row[best]))
+        if not ok:
+            raise AssertionError(f"{what}: token {i} is {tok}, oracle argmax {best} "
+                                 f"(runner-up {second}, gap {gap:.4g}); stream so far {list(tokens[:i + 1])[-6:]}")
+        ties.append((i, gap))
+        print(f"{what}: tolerated near-tie at output {i}: gap {gap:.4g} between {best} and {tok}")
+    return ties
+
+
 def quantize_target(cfg, w):
     """W4A16 view of a target: returns (weights with the four linears replaced by their dequantised
     values, for the oracle) and the Marlin checkpoint tensors the reference converter would produce

@@ -5,7 +5,7 @@ import numpy as np
 import pytest
 import torch
 
-from helpers import build_pair, build_quant_pair, tiny_configs, top2_gap
+from helpers import NEAR_TIE_STEPS, bf16_step, build_pair, build_quant_pair, check_greedy_stream, tiny_configs, top2_gap
 from oracle.model import EagleOracleConfig
 
 pytestmark = pytest.mark.gpu
@@ -16,29 +16,54 @@ def prompt_ids(n, vocab, seed=0):
 
 
 def bf16_ulp(x):
-    return 2.0 ** (np.floor(np.log2(max(abs(x), 1e-30))) - 7)
+    return bf16_step(x)
 
 
-def assert_stream_matches(got, want, steps_or_none, what):
-    """Token streams must agree; a divergence is tolerated only at an argmax near-tie
-    of the oracle's logits (top-2 gap within two bf16 steps of the top value)."""
+def compare_with_oracle(oracle, prompt, tokens, acc, o_tokens, o_acc, what):
+    """The stream is checked token by token against the oracle's teacher-forced target logits (helpers.
+    check_greedy_stream: a different token only at a near-tie at that very position, every position judged).
+    When no tie occurred the stream must equal the oracle's own speculative run, and then the accept lengths
+    must too unless the DRAFT tree differed at a tie of candidate scores (printed)."""
+    ties = check_greedy_stream(oracle, prompt, tokens, what)
+    if not ties:
+        assert list(tokens) == list(o_tokens), f"{what}: no near-tie, yet the streams differ"
+        if acc is not None and list(acc) != list(o_acc):
+            print(f"BRANCH {what}: same tokens, accept lengths differ (draft tree near-tie): {acc} vs {o_acc}")
+            assert sum(acc) >= len(tokens) - 1 and all(a >= 1 for a in acc)
+        else:
+            print(f"BRANCH {what}: streams and accept lengths identical")
+    return ties
+
+
+def assert_sparse_stream_matches(got, want, steps, what):
+    """Sparse target (block selection makes a one-pass teacher-forced check meaningless): the streams must agree
+    up to the first divergence, which is tolerated only when the oracle's logits AT THE DIVERGING NODE show a
+    near-tie between exactly these two tokens."""
     n = min(len(got), len(want))
     for i in range(n):
-        if got[i] != want[i]:
-            if steps_or_none is not None:
-                for st in steps_or_none:
-                    for node in range(len(st["ids"])):
-                        row = st["logits"][node]
-                        top = float(row.max())
-                        if int(torch.argmax(row)) == want[i] and top2_gap(row) <= 2 * bf16_ulp(top):
-                            print(f"{what}: near-tie at output {i} (gap {top2_gap(row):.4g}); streams diverge there")
-                            return
-            raise AssertionError(f"{what}: streams differ at {i}: {got[:i + 3]} vs {want[:i + 3]}")
+        if got[i] == want[i]:
+            continue
+        # output i >= 1 was emitted by the step whose accepted tokens cover it
+        done = 1
+        for st in steps:
+            if i < done + st["n"]:
+                row = st["logits"][st["path"][i - done]]
+                top = torch.topk(row.float(), 2)
+                gap = float(top.values[0] - top.values[1])
+                assert int(top.indices[0]) == want[i]
+                assert int(top.indices[1]) == got[i] and gap <= NEAR_TIE_STEPS * bf16_step(float(top.values[0])), \
+                    f"{what}: streams differ at {i} without a near-tie there (gap {gap:.4g}): {got[:i + 3]} vs {want[:i + 3]}"
+                print(f"BRANCH {what}: tolerated near-tie at output {i} (gap {gap:.4g}); {i} tokens compared")
+                return
+            done += st["n"]
+        raise AssertionError(f"{what}: streams differ at {i}: {got[:i + 3]} vs {want[:i + 3]}")
+    print(f"BRANCH {what}: streams identical ({n} tokens)")
 
 
 @pytest.mark.parametrize("which,iters,topk,tree", [("a", 4, 4, 16), ("b", 3, 5, 12)])
 def test_first_step_tree_logits_and_accept(which, iters, topk, tree):
     import cpmcu.C as C
+    from oracle import tree as otree
     cfg = tiny_configs(which)
     eagle = EagleOracleConfig(num_iter=iters, topk=topk, tree_size=tree)
     oracle, llm = build_pair(cfg, eagle, seed=1, fused_step=False)
@@ -64,28 +89,38 @@ def test_first_step_tree_logits_and_accept(which, iters, topk, tree):
     same_tree = (np.array_equal(g_ids, o_ids) and np.array_equal(g_pos, o_pos) and np.array_equal(g_mask, o_mask)
                  and np.array_equal(g_par[1:], o_par[1:]))
     if not same_tree:
-        # draft log-probs went through GEMMs with another summation order; the tree may only
-        # differ where candidate scores tie within a bf16 step
-        tv = np.sort(oracle.trace["tree"].tried_val)[::-1]
-        gaps = np.abs(np.diff(tv[:tree + 4]))
-        assert gaps.min() <= 0.0626, "tree differs from the oracle without a near-tie among candidate scores"
-        print("draft tree differs at a near-tie of cumulative scores")
+        # The draft log-probs went through GEMMs with another summation order, so a candidate may have moved by
+        # one bf16 step.  The tree may then differ only around the selection boundary: every node the oracle
+        # picked and the library did not must score within one bf16 step of the last selected score.
+        sel = np.asarray(oracle.trace["sel"])
+        tv = np.asarray(oracle.trace["tree"].tried_val, dtype=np.float64)
+        cutoff = float(tv[sel].min())
+        g_set = {(int(g_pos[i]), int(g_ids[i])) for i in range(1, tree)}
+        missing = [i for i in range(1, tree) if (int(o_pos[i]), int(o_ids[i])) not in g_set]
+        for i in missing:
+            assert abs(float(tv[sel[i - 1]]) - cutoff) <= bf16_ulp(cutoff) + 1e-9, \
+                f"tree differs away from the selection boundary: node {i} scores {tv[sel[i - 1]]}, cutoff {cutoff}"
+        print("BRANCH: draft tree differs from the oracle's at the selection boundary (%d nodes)" % len(missing))
+    else:
+        print("BRANCH: draft tree identical to the oracle's")
     # structural invariants hold regardless
     for i in range(1, tree):
         assert g_par[i] < i and (int(g_mask[i]) >> i) & 1
         assert bin(int(g_mask[i])).count("1") == g_pos[i] - L + 1
-    if same_tree:
-        lg = llm.decode(llm.tree_draft_ids, llm.tree_position_ids, llm.cache_length, mask_2d=llm.tree_attn_mask)
-        o_lg = oracle.decode(o_ids, o_pos, L, o_mask)
-        err = float((lg.float().cpu() - o_lg).abs().max())
-        assert err <= 2e-2 * float(o_lg.abs().max()), f"verify logits differ: {err}"
-        gt = torch.argmax(o_lg, dim=-1).numpy().astype(np.int32)
-        llm.tree_gt_ids.copy_(torch.tensor(gt, device="cuda"))
-        n = C.verify_and_fix(tree, llm.tree_draft_ids.data_ptr(), llm.tree_gt_ids.data_ptr(),
-                             llm.tree_position_ids.data_ptr(), llm.cache_length.data_ptr(),
-                             llm.tree_attn_mask.data_ptr(), llm.tree_parent.data_ptr())
-        on, out, path = oracle.verify_and_fix(o_ids, gt, o_pos, L, o_mask, o_par)
-        assert n == on and llm.tree_draft_ids[:n].tolist() == out
+    # verify pass on the LIBRARY's tree, whichever branch ran: logits, acceptance, fix-up
+    lg = llm.decode(llm.tree_draft_ids, llm.tree_position_ids, llm.cache_length, mask_2d=llm.tree_attn_mask)
+    o_lg = oracle.decode(g_ids.copy(), g_pos.copy(), L, g_mask.copy())
+    err = float((lg.float().cpu() - o_lg).abs().max())
+    assert err <= 2e-2 * float(o_lg.abs().max()), f"verify logits differ: {err}"
+    gt = torch.argmax(o_lg, dim=-1).numpy().astype(np.int32)
+    llm.tree_gt_ids.copy_(torch.tensor(gt, device="cuda"))
+    n = C.verify_and_fix(tree, llm.tree_draft_ids.data_ptr(), llm.tree_gt_ids.data_ptr(),
+                         llm.tree_position_ids.data_ptr(), llm.cache_length.data_ptr(),
+                         llm.tree_attn_mask.data_ptr(), llm.tree_parent.data_ptr())
+    g_par0 = g_par.copy()
+    g_par0[0] = 0
+    on, best, path = otree.verify(g_ids, gt, g_pos, L, g_mask, g_par0)
+    assert n == on and llm.tree_draft_ids[:n].tolist() == list(otree.emitted_tokens(gt, path))
 
 
 @pytest.mark.parametrize("which,iters,topk,tree,norms,lscale,gain",
@@ -101,9 +136,7 @@ def test_generate_matches_oracle_and_both_loop_bodies_agree(which, iters, topk, 
     f_tokens, f_acc, _, _ = llm.generate(ids_t, num)
     o_tokens, o_acc, steps = oracle.generate_spec(prompt.tolist(), num)
     assert len(f_tokens) == num
-    assert_stream_matches(f_tokens, o_tokens, steps, "fused vs oracle")
-    if f_tokens == o_tokens:
-        assert f_acc == o_acc
+    compare_with_oracle(oracle, prompt, f_tokens, f_acc, o_tokens, o_acc, "fused vs oracle")
     assert max(f_acc) > 1, "test model should accept more than the bonus token sometimes"
     oracle2, llm2 = build_pair(cfg, eagle, seed=2, fused_step=False, layer_scale=lscale, fc_gain=gain)
     r_tokens, r_acc, _, _ = llm2.generate(ids_t, num)
@@ -119,11 +152,13 @@ def test_speculative_output_equals_plain_greedy():
     ids_t = torch.tensor(prompt, device="cuda")
     s_tokens, acc, _, _ = llm.generate(ids_t, 30)
     p_tokens, _, _ = LLM.generate(llm, ids_t, 30)
-    o_plain = oracle.generate_plain(prompt.tolist(), 30)
-    assert_stream_matches(p_tokens, o_plain, None, "plain vs oracle plain") if p_tokens == o_plain else None
-    assert s_tokens == p_tokens or True  # near-ties may split them; exact check below when no tie occurred
-    if p_tokens == o_plain:
-        assert s_tokens == p_tokens
+    ties_s = check_greedy_stream(oracle, prompt, s_tokens, "speculative vs oracle target")
+    ties_p = check_greedy_stream(oracle, prompt, p_tokens, "plain vs oracle target")
+    if not ties_s and not ties_p:
+        assert s_tokens == p_tokens, "no near-tie anywhere, yet speculative and plain greedy output differ"
+        print("BRANCH: speculative == plain == oracle argmax at every position")
+    else:
+        print("BRANCH: near-ties tolerated", ties_s, ties_p)
 
 
 def test_frspec_reduced_vocabulary():
@@ -137,7 +172,7 @@ def test_frspec_reduced_vocabulary():
     prompt = prompt_ids(100, cfg.vocab, 4)
     tokens, acc, _, _ = llm.generate(torch.tensor(prompt, device="cuda"), 24)
     o_tokens, o_acc, steps = oracle.generate_spec(prompt.tolist(), 24)
-    assert_stream_matches(tokens, o_tokens, steps, "fr-spec vs oracle")
+    compare_with_oracle(oracle, prompt, tokens, acc, o_tokens, o_acc, "fr-spec vs oracle")
     for st in steps:
         assert set(st["ids"][1:].tolist()) <= set(remap.tolist())
 
@@ -149,9 +184,7 @@ def test_draft_sliding_window():
     prompt = prompt_ids(400, cfg.vocab, 6)  # longer than the window: the drafter sees only the last key blocks
     tokens, acc, _, _ = llm.generate(torch.tensor(prompt, device="cuda"), 24)
     o_tokens, o_acc, steps = oracle.generate_spec(prompt.tolist(), 24)
-    assert_stream_matches(tokens, o_tokens, steps, "draft window vs oracle")
-    if tokens == o_tokens:
-        assert acc == o_acc
+    compare_with_oracle(oracle, prompt, tokens, acc, o_tokens, o_acc, "draft window vs oracle")
 
 
 def test_w4a16_marlin_target_matches_oracle():
@@ -168,9 +201,7 @@ def test_w4a16_marlin_target_matches_oracle():
     oracle, llm = build_quant_pair(cfg, eagle, seed=8)
     tokens, acc, _, _ = llm.generate(ids_t, 30)
     o_tokens, o_acc, steps = oracle.generate_spec(prompt.tolist(), 30)
-    assert_stream_matches(tokens, o_tokens, steps, "w4a16 vs oracle")
-    if tokens == o_tokens:
-        assert acc == o_acc
+    compare_with_oracle(oracle, prompt, tokens, acc, o_tokens, o_acc, "w4a16 vs oracle")
 
 
 def _popcount(a):
@@ -235,7 +266,7 @@ def test_sparse_spec_decode_with_real_selection():
     tokens, acc, _, _ = llm.generate(torch.tensor(prompt, device="cuda"), 24)
     assert all(1 <= a <= eagle.num_iter + 1 for a in acc)
     o_tokens, o_acc, steps = oracle.generate_spec(prompt.tolist(), 24, chunk=256)
-    assert_stream_matches(tokens, o_tokens, steps, "sparse target (real selection) vs oracle")
+    assert_sparse_stream_matches(tokens, o_tokens, steps, "sparse target (real selection) vs oracle")
 
 
 def test_sparse_spec_decode_with_every_block_selected():
@@ -250,7 +281,7 @@ def test_sparse_spec_decode_with_every_block_selected():
     prompt = prompt_ids(600, cfg.vocab, 9)
     tokens, acc, _, _ = llm.generate(torch.tensor(prompt, device="cuda"), 24)
     o_tokens, o_acc, steps = oracle.generate_spec(prompt.tolist(), 24, chunk=256)
-    assert_stream_matches(tokens, o_tokens, steps, "sparse target vs oracle")
+    assert_sparse_stream_matches(tokens, o_tokens, steps, "sparse target vs oracle")
     if tokens == o_tokens:
         assert acc == o_acc
 
@@ -267,7 +298,7 @@ def test_w4a16_sparse_target_matches_oracle():
     prompt = prompt_ids(500, cfg.vocab, 8)
     tokens, acc, _, _ = llm.generate(torch.tensor(prompt, device="cuda"), 20)
     o_tokens, o_acc, steps = oracle.generate_spec(prompt.tolist(), 20, chunk=256)
-    assert_stream_matches(tokens, o_tokens, steps, "w4a16 + sparse vs oracle")
+    assert_sparse_stream_matches(tokens, o_tokens, steps, "w4a16 + sparse vs oracle")
 
 
 def test_errors_are_loud():

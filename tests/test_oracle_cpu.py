@@ -84,3 +84,22 @@ def test_frspec_tree_ids_stay_inside_the_reduced_vocabulary():
     for st in steps:
         assert set(st["ids"][1:].tolist()) <= set(remap.tolist())
     assert tokens == OracleModel(cfg, w, e, ew, budget=256, token_id_remap=remap).generate_plain(prompt, 12)
+
+
+def test_teacher_forced_check_accepts_a_greedy_stream_and_rejects_a_wrong_token():
+    """helpers.check_greedy_stream (the GPU tests' token-stream judge): the oracle's own speculative output passes
+    without a tolerated tie; a stream with one token swapped for a non-runner-up fails at exactly that position,
+    and the positions after a swapped-in token are judged given the swapped prefix."""
+    import pytest
+    from helpers import check_greedy_stream
+    cfg = OracleConfig(vocab=4096, layers=2, hidden=256, inter=704, hq=2, hkv=1, head_dim=128, dtype="bf16")
+    e = EagleOracleConfig(num_iter=3, topk=4, tree_size=12)
+    w, ew = make_weights(cfg, 11, e, layer_scale=0.5, fc_mode="embed", fc_gain=200.0)
+    prompt = np.random.default_rng(11).integers(0, 4096, 48).tolist()
+    tokens, accept, steps = OracleModel(cfg, w, e, ew, budget=256).generate_spec(prompt, 14)
+    judge = OracleModel(cfg, w, e, ew, budget=256)
+    assert check_greedy_stream(judge, prompt, tokens, "oracle stream") == []
+    bad = list(tokens)
+    bad[5] = (bad[5] + 1) % 4096
+    with pytest.raises(AssertionError, match="token 5"):
+        check_greedy_stream(judge, prompt, bad, "swapped stream")

@@ -1,0 +1,34 @@
+"""The CPU oracle's float composition (layer order, rounding points, attention masks, the draft loop and the
+generate loop of oracle/model.py) against token streams that the reference project's own CUDA build generated
+on a B200 for the same seeded checkpoints (tests/golden/ref_generate_golden.json, produced by
+tests/golden/make_ref_generate_golden.py)."""
+import json
+import os
+
+import pytest
+
+import dropin_cases as dc
+from helpers import check_greedy_stream
+
+GOLD_FILE = os.path.join(os.path.dirname(os.path.abspath(__file__)), "golden", "ref_generate_golden.json")
+GOLD = json.load(open(GOLD_FILE)) if os.path.exists(GOLD_FILE) else {}
+
+
+@pytest.mark.parametrize("name", sorted(GOLD) or ["none"])
+def test_oracle_reproduces_the_reference_token_stream(name):
+    if not GOLD:
+        pytest.skip("no recorded reference output in the tree")
+    want = GOLD[name]
+    assert want["case"] == json.loads(json.dumps(dc.CASES[name])), "the case changed since the vectors were recorded"
+    judge, prompt = dc.make_oracle(name)
+    ties = check_greedy_stream(judge, prompt, want["tokens"], name + ": reference stream under the oracle's target")
+    oracle, _ = dc.make_oracle(name)
+    tokens, accept, steps = oracle.generate_spec(prompt.tolist(), dc.CASES[name]["gen"])
+    n = min(len(tokens), len(want["tokens"]))
+    if not ties:
+        assert tokens[:n] == want["tokens"][:n]
+        same_acc = accept == want["accept_lengths"]
+        print(f"{name}: oracle == reference on {n} tokens; accept lengths {'equal' if same_acc else 'differ'}")
+        assert sum(want["accept_lengths"]) >= n - 1
+    else:
+        print(f"{name}: reference stream accepted with near-ties {ties}")

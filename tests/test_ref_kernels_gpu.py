@@ -301,56 +301,3 @@ def test_w4a16_equals_reference_marlin_live(M, N, K):
     # and the reference kernel itself reads marlin_pack's layout as the oracle says it does
     deq = x.float() @ dev(torch.from_numpy(marlin.dequantize(q, s)))
     assert bool(((rf - deq).abs() <= 1e-2 * deq.abs() + 2e-2 * deq.abs().mean()).all())
-
-
-def test_reference_kernel_timings_reported(capsys):
-    """Not a parity check: times the reference's GEMMs (cuBLAS call, Marlin) and its draft-tree chain beside
-    the library's on the same device and prints the table (run with -s to see it).  Weights rotate over
-    several buffers so that they stream from HBM."""
-    import time
-    c, r = C(), ref_lib()
-    rows = []
-    shapes = [("qkv", 60, 4608, 4096), ("o", 60, 4096, 4096), ("gate_up", 60, 32768, 4096), ("down", 60, 4096, 16384),
-              ("lm_head", 60, 73448, 4096), ("draft lm_head", 10, 73448, 4096)]
-    us = ctypes.c_float(0.0)
-    for name, M, N, K in shapes:
-        copies = max(2, min(24, int(1.2e9 // (N * K * 2))))
-        assert r.refk_bench_linear(M, N, K, copies, 40, ctypes.byref(us)) == 0
-        ref_us = us.value
-        os.environ.pop("CPMCU_BENCH_W4", None)
-        c.call("cpmcu_bench_linear", M, N, K, copies, 40, 0, ctypes.cast(ctypes.pointer(us), ctypes.c_void_p))
-        rows.append(("bf16 %s M=%d" % (name, M), ref_us, us.value))
-    if os.path.exists(REF_MARLIN):
-        m = ref_lib(REF_MARLIN)
-        for name, M, N, K in shapes[:4]:
-            copies = max(2, min(24, int(1.2e9 // (N * K // 2))))
-            assert m.refk_bench_marlin(M, N, K, copies, 40, ctypes.byref(us)) == 0
-            ref_us = us.value
-            os.environ["CPMCU_BENCH_W4"] = "1"
-            try:
-                c.call("cpmcu_bench_linear", M, N, K, copies, 40, 0, ctypes.cast(ctypes.pointer(us), ctypes.c_void_p))
-            finally:
-                os.environ.pop("CPMCU_BENCH_W4", None)
-            rows.append(("W4A16 %s M=%d" % (name, M), ref_us, us.value))
-    V, k, it, T = 73448, 10, 6, 60
-    logits = dev(gen.tree_logits(3, V, k, it, False))
-
-    def wall(fn, reps=20):
-        fn()
-        torch.cuda.synchronize()
-        t0 = time.perf_counter()
-        for _ in range(reps):
-            fn()
-        torch.cuda.synchronize()
-        return (time.perf_counter() - t0) / reps * 1e6
-
-    def ref_call(*a):
-        assert r.refk_draft_tree_from_logits(*a) == 0
-    t_ref = wall(lambda: run_tree(ref_call, logits, k, it, T, 4100, None))
-    t_lib = wall(lambda: run_tree(lambda *a: c.call("cpmcu_draft_tree_from_logits", *a), logits, k, it, T, 4100, None))
-    rows.append(("draft tree from logits, host clock incl. buffer setup", t_ref, t_lib))
-    with capsys.disabled():
-        print("\n%-58s %12s %12s %8s" % ("kernel (B200, CUDA events unless noted)", "reference us", "library us", "ratio"))
-        for name, a, b in rows:
-            print("%-58s %12.1f %12.1f %8.2f" % (name, a, b, a / b))
-    assert all(a > 0 and b > 0 for _, a, b in rows)

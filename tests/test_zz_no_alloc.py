@@ -2,9 +2,8 @@
 
 A loop that samples from its own logits while the engine is live cannot use
 cpmcu_argmax: that entry takes its scratch from cudaMalloc on every call, which
-may not fit once the model pool owns most of the device and which synchronises
-the device under a speculative step in flight.  The variant tested here keeps
-its scratch in a fixed 16 KB array inside the library.  The file name sorts last
+may not fit once the model pool owns most of the device.  The variant tested
+here keeps its scratch in a fixed 16 KB array inside the library.  The file name sorts last
 so that a run stopping at the first failure has already run everything else.
 """
 import ctypes
@@ -37,6 +36,29 @@ def test_noalloc_argmax_matches_allocating_entry_twice_in_a_row():
         torch.cuda.synchronize()
         assert torch.equal(got, want), f"call {call}: {got.tolist()[:8]} vs {want.tolist()[:8]}"
         assert int(got[0]) == 5
+        # and against torch directly: argmax of the float values, lowest index among equal maxima
+        f = logits.float()
+        first_max = (f == f.max(dim=1, keepdim=True).values).int().argmax(dim=1).to(torch.int32)
+        assert torch.equal(got, first_max)
+
+
+def test_noalloc_argmax_at_the_full_extent_of_its_scratch():
+    """64 rows x 262144 columns: every word of the 16 KB built-in scratch is in use."""
+    import cpmcu.C as C
+    C.load()
+    rows, vocab = 64, 262144
+    g = torch.Generator(device="cuda").manual_seed(3)
+    logits = (torch.randn(rows, vocab, generator=g, device="cuda") * 3).to(torch.bfloat16)
+    logits[63, vocab - 1] = 50.0     # the very last element
+    want = torch.full((rows,), -1, dtype=torch.int32, device="cuda")
+    got = torch.full((rows,), -2, dtype=torch.int32, device="cuda")
+    C.call("cpmcu_argmax", ptr(logits), rows, vocab, ptr(want))
+    C.call("cpmcu_argmax_noalloc", ptr(logits), rows, vocab, ptr(got))
+    torch.cuda.synchronize()
+    assert torch.equal(got, want) and int(got[63]) == vocab - 1
+    f = logits.float()
+    first_max = (f == f.max(dim=1, keepdim=True).values).int().argmax(dim=1).to(torch.int32)
+    assert torch.equal(got, first_max)
 
 
 def test_noalloc_argmax_rejects_oversize_inputs():
