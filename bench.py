@@ -51,7 +51,8 @@ WORKLOADS = {
     "config2": dict(index=1, w4a16=False, sparse=False, frspec=False,
                     text="configs[1]: 8B-shaped bf16 target + 1-layer EAGLE, tree 60 (6 iters x top-10), "),
     "config3": dict(index=2, w4a16=False, sparse=False, frspec=True,
-                    text="configs[2]: config 2 with FR-Spec (draft LM head over the 32768 most frequent ids), "),
+                    text="configs[2]: config 2 with FR-Spec (draft LM head over the 32768 most frequent ids; drafter input "
+                         "norms on, as the reference's FR-Spec path requires), "),
     "config4": dict(index=3, w4a16=True, sparse=False, frspec=False,
                     text="configs[3]: config-2 architecture with W4A16 GPTQ-Marlin target linears (random int4 tensors), "
                          "bf16 embeddings / LM head / EAGLE draft, tree 60, "),
@@ -63,7 +64,7 @@ WORKLOADS = {
 # Second weight recipe (not a BASELINE.json configuration): decoder-layer matrices shrunk by ACCEPT_LAYER_SCALE and
 # fc = [gain * I | 0], so that the next token is mostly a function of the current one and the 1-layer drafter can
 # follow the 32-layer target; exercises accept lengths > 1 (catch-up over several rows, compaction, gathers).
-ACCEPT_LAYER_SCALE = float(os.environ.get("CPMCU_BENCH_LAYER_SCALE", "0.25"))
+ACCEPT_LAYER_SCALE = float(os.environ.get("CPMCU_BENCH_LAYER_SCALE", "0.05"))
 ACCEPT_FC_GAIN = float(os.environ.get("CPMCU_BENCH_FC_GAIN", "50"))
 
 
@@ -193,6 +194,11 @@ def iter_weights(seed=1, w4a16=False, frspec=False, accepting=False):
         fc = torch.cat([torch.zeros(H, H, device="cuda"), eye], dim=1)
     yield "eagle", "fc.weight", fc.to(torch.bfloat16)
     yield "eagle", "fc.bias", torch.zeros(H, device="cuda", dtype=torch.bfloat16)
+    if frspec:
+        # the reference takes an FR-Spec vocabulary only on its MiniCPM4 drafter, which it picks when a norm switch
+        # is on (cpmcu/speculative/eagle.py:52-74): config 3 runs with input norms (weights of ones) on both arms
+        yield "eagle", "input_norm1.weight", ones
+        yield "eagle", "input_norm2.weight", ones
 
 
 def hf_config_dict(w4a16):
@@ -228,6 +234,7 @@ def build_model(device_index, seed=1, w4a16=False, sparse=False, frspec=False, a
                      apply_compress_lse=True, eagle_window_size=1024)
     if frspec:
         extra["frspec_vocab_size"] = FRSPEC_VOCAB
+        extra["use_input_norm"] = True
     llm = cls(None, None, num_iter=TREE["num_iter"], topk_per_iter=TREE["topk"],
               tree_size=TREE["tree_size"], eagle_config={"num_hidden_layers": 1}, config=hf,
               dtype=torch.bfloat16, chunk_length=LONG_CHUNK if sparse else PROMPT_LEN, memory_limit=0.8,
@@ -361,7 +368,7 @@ def run_reference_cuda(workload, gen_tokens=256, timeout_s=900):
         if w["w4a16"]:
             cmd.append("--quant")
         if w["frspec"]:
-            cmd += ["--frspec", str(FRSPEC_VOCAB)]
+            cmd += ["--frspec", str(FRSPEC_VOCAB), "--input-norm"]
         if w["sparse"]:
             cmd += ["--sparse", "--window", "1024"]
         env = dict(os.environ)
