@@ -9,7 +9,7 @@ returned (tokens, accept lengths, its own decode and prefill wall times: decode 
 demo computes it, tests/test_generate.py:440-444).  Nothing of this repository's library is imported here.
 
     python baseline/ref_cuda.py --base DIR --eagle DIR --prompt FILE.json --gen N [--quant] [--sparse]
-                                [--frspec V] [--window W] [--chunk C] [--no-graph] [--repeat R] [--out FILE]
+                                [--eagle-quant] [--frspec V] [--window W] [--chunk C] [--no-graph] [--repeat R] [--out FILE]
 
 BENCHMARK / TEST INFRASTRUCTURE.  One environment shim, applied in this process only and not to the reference's
 files: the installed `transformers` no longer lists a "default" entry in ROPE_INIT_FUNCTIONS, which the
@@ -56,7 +56,7 @@ def main():
     ap.add_argument("--no-graph", action="store_true")
     ap.add_argument("--input-norm", action="store_true")
     ap.add_argument("--attn-norm", action="store_true")
-    ap.add_argument("--plain", action="store_true", help="also run LLM.generate-style plain decoding? (unused)")
+    ap.add_argument("--eagle-quant", action="store_true", help="W4A16 drafter (apply_eagle_quant=True)")
     ap.add_argument("--out", default=None)
     args = ap.parse_args()
 
@@ -80,6 +80,7 @@ def main():
         from cpmcu.speculative.eagle import LLM_with_eagle as Cls
     kw = dict(num_iter=args.num_iter, topk_per_iter=args.topk, tree_size=args.tree, eagle_window_size=args.window,
               frspec_vocab_size=args.frspec, use_input_norm=args.input_norm, use_attn_norm=args.attn_norm,
+              apply_eagle_quant=args.eagle_quant,
               dtype=torch.bfloat16, memory_limit=args.memory_limit, chunk_length=args.chunk,
               cuda_graph=not args.no_graph)
     if args.sparse:

@@ -34,6 +34,8 @@ _SIGNATURES = {
     "cpmcu_print_perf_summary": (None, []),
     "cpmcu_begin_generation": (_c_int, [_c_int, _c_int]),
     "cpmcu_spec_step": (_c_int, [_c_void_p, _c_int]),
+    "cpmcu_set_sampling": (_c_int, [ctypes.c_float, ctypes.c_ulonglong]),
+    "cpmcu_sample": (_c_int, [_c_void_p, _c_int, _c_int, ctypes.c_float, ctypes.c_ulonglong, _c_int, _c_void_p]),
     "cpmcu_profile_step": (_c_int, [_c_void_p] * 3),
     "cpmcu_last_step_ms": (ctypes.c_double, []),
     "cpmcu_last_draft_ms": (ctypes.c_double, []),
@@ -201,6 +203,14 @@ def print_perf_summary():
 # ---------------------------------------------------------------- fused step (no reference counterpart)
 def begin_generation(prefix_length, root_token):
     call("cpmcu_begin_generation", prefix_length, root_token)
+
+
+def set_sampling(temperature, seed):
+    call("cpmcu_set_sampling", float(temperature), int(seed) & 0xFFFFFFFFFFFFFFFF)
+
+
+def sample(logits_ptr, rows, vocab, temperature, seed, draw, out_ptr):
+    call("cpmcu_sample", logits_ptr, rows, vocab, float(temperature), int(seed) & 0xFFFFFFFFFFFFFFFF, draw, out_ptr)
 
 
 def spec_step(max_tokens=16):

@@ -67,6 +67,7 @@ class LLM(torch.nn.Module):
         self.minicpm4_yarn = minicpm4_yarn
         self._show_prefill_progress = False
         self.generator = None
+        self.sample_seed = random_seed   # seeds the device-side sampling of the fused speculative step
         if random_seed is not None:
             self.generator = torch.Generator(device="cuda")
             self.generator.manual_seed(random_seed)

@@ -49,8 +49,9 @@ class LLM_with_eagle(LLM_with_tree_drafter):
     def _load(self, name, param, dtype=None, cls=None):
         if cls != self.drafter_type:
             return super()._load(name, param, dtype)
+        import torch
         if name == "token_id_remap":
-            param = param.contiguous().to(dtype=__import__("torch").int32)
+            param = param.contiguous().to(dtype=torch.int32)
             C.load_model(f"{cls}.{name}", param.data_ptr())
             return
         if "embed_tokens" in name:
@@ -58,10 +59,13 @@ class LLM_with_eagle(LLM_with_tree_drafter):
         if dtype is None:
             dtype = self.dtype
         param = param.contiguous()
-        if not self.apply_eagle_quant:
-            param = param.to(dtype)
+        if param.dtype not in (torch.int8, torch.int16, torch.int32):
+            param = param.to(dtype)  # packed int4 tensors of a quantised drafter pass through untouched
         if "fc" in name:
-            if "weight" in name:
+            # the checkpoint's fc holds the embedding half and the hidden-state half side by side along the last
+            # dimension: columns of the bf16 weight; for a quantised drafter the two [H -> H] linears' qweight /
+            # scales tensors concatenated (reference eagle_base_w4a16_marlin_gptq.py:92-99)
+            if "weight" in name or "scales" in name:
                 half = param.shape[-1] // 2
                 first, second = param[..., :half].contiguous(), param[..., half:].contiguous()
                 C.load_model(f"{cls}.{name.replace('fc', 'fc1')}", first.data_ptr())

@@ -93,9 +93,19 @@ class LLM_with_tree_drafter(LLM):
         logits = self.prefill(input_ids, position_ids)
         torch.cuda.synchronize()
         prefill_time = time.time() - t0
-        root = self._pick(logits[0]).item()
+        fused = self.fused_step
+        if fused and self.temperature > 0.0:
+            # device-side sampling inside the captured step; the whole run is a function of the seed
+            seed = self.sample_seed if self.sample_seed is not None else int.from_bytes(__import__("os").urandom(8), "little")
+            C.set_sampling(self.temperature, seed)
+            root_t = torch.empty(1, dtype=torch.int32, device="cuda")
+            C.sample(logits.data_ptr(), 1, logits.shape[-1], self.temperature, seed, 0, root_t.data_ptr())
+            root = int(root_t.item())
+        else:
+            if fused:
+                C.set_sampling(0.0, 0)
+            root = self._pick(logits[0]).item()
         self.tree_draft_ids[0] = root
-        fused = self.fused_step and self.temperature == 0.0
         if fused:
             C.begin_generation(prefix_length, root)
         self.step_device_ms = []

@@ -196,11 +196,14 @@ int cpmcu_init_minicpm4_eagle_model(int num_layers, int num_iter, int topk_per_i
                                     int apply_eagle_quant, int group_size, int eagle_window_size,
                                     int frspec_vocab_size, float residual_scale, int use_input_norm,
                                     int use_attn_norm) {
-    (void)group_size;
-    if (apply_eagle_quant) return not_built("the W4A16 EAGLE drafter (apply_eagle_quant)");
     return guarded([&] {
         require_bf16(torch_dtype);
         EagleConfig ec;
+        ec.quant = apply_eagle_quant != 0;
+        if (ec.quant) {
+            CPM_REQUIRE(group_size == 128, "W4A16 drafter: only group_size 128 is supported");
+            ec.group_size = group_size;
+        }
         ec.num_layers = num_layers;
         ec.num_iter = num_iter;
         ec.topk = topk_per_iter;
@@ -278,6 +281,13 @@ void cpmcu_print_perf_summary(void) {
 int cpmcu_begin_generation(int prefix_length, int32_t root_token) {
     return guarded([&] {
         engine().begin_generation(prefix_length, root_token);
+        return 0;
+    });
+}
+
+int cpmcu_set_sampling(float temperature, unsigned long long seed) {
+    return guarded([&] {
+        engine().set_sampling(temperature, seed);
         return 0;
     });
 }
@@ -617,6 +627,18 @@ int cpmcu_silu_gate(const void* gate_up, void* out, int rows, int inter) {
     });
 }
 
+int cpmcu_sample(const void* logits, int rows, int vocab, float temperature, unsigned long long seed, int draw,
+                 int32_t* out) {
+    return guarded([&] {
+        CPM_REQUIRE(temperature >= 0.f && draw >= 0, "sample: temperature and draw index must not be negative");
+        DeviceBuf ws(argmax_workspace_bytes(rows, vocab));
+        launch_sample(static_cast<const bf16*>(logits), rows, vocab, vocab, out, ws.p, temperature, seed, nullptr, draw,
+                      runtime().stream);
+        sync_and_check("sample");
+        return 0;
+    });
+}
+
 int cpmcu_argmax(const void* logits, int rows, int vocab, int32_t* out) {
     return guarded([&] {
         DeviceBuf ws(argmax_workspace_bytes(rows, vocab));
@@ -646,6 +668,7 @@ int cpmcu_draft_tree_from_logits(const void* logits, int vocab, int k, int num_i
         DeviceBuf fs(64 * 2), fi(64 * 4), fm(64 * 8), sp(64 * 4), fsrc(64 * 4);
         DeviceBuf h(static_cast<size_t>(32) * hidden * 2), hid(static_cast<size_t>(32) * hidden * 2);
         DeviceBuf scan(draft_scan_workspace_bytes(32, vocab, 32));
+        CUDA_CHECK(cudaMemsetAsync(scan.p, 0, 256, runtime().stream));  // the level kernel's ticket
         CUDA_CHECK(cudaMemsetAsync(h.p, 0, static_cast<size_t>(32) * hidden * 2, s));
         st.tried_val = static_cast<bf16*>(tv.p);
         st.tried_pos = static_cast<int32_t*>(tp.p);

@@ -236,8 +236,15 @@ void launch_silu_gate(const bf16* gate_up, bf16* out, int rows, int inter, cudaS
 void launch_add_scaled(bf16* x, const bf16* a, const bf16* b, float scale_b, int rows, int dim,
                        cudaStream_t s);  // x = a + b*scale
 void launch_scale(bf16* out, const bf16* in, float scale, size_t n, cudaStream_t s);
+// x = (a + bias[col]) + b, each sum rounded to bf16 (bias may be null): the two halves of a quantised fc
+void launch_add_bias_add(bf16* x, const bf16* a, const bf16* bias, const bf16* b, int rows, int dim, cudaStream_t s);
 size_t argmax_workspace_bytes(int rows, int vocab);
 void launch_argmax(const bf16* logits, int rows, int vocab, int ld, int32_t* out, void* workspace, cudaStream_t s);
+// Row pick with a temperature: out[r] ~ softmax(logits[r] / temperature), drawn by Gumbel-max with Philox noise
+// keyed by (seed, r, *draw + draw_add, column); temperature <= 0 is launch_argmax.  `draw` (device, may be null)
+// lets a captured step advance its draw index without re-capturing.
+void launch_sample(const bf16* logits, int rows, int vocab, int ld, int32_t* out, void* workspace, float temperature,
+                   unsigned long long seed, const int32_t* draw, int draw_add, cudaStream_t s);
 
 // ---------------------------------------------------------------- attention
 struct AttnPlan {

@@ -10,7 +10,7 @@
 //                                           src/model/eagle.cuh:11-127
 //   build_dynamic_tree_kernel               src/model/eagle.cuh:188-218
 // The reference runs ~12 tiny launches and three device copies per level plus a
-// host round trip for the tree; here a level is three launches and the tree one.
+// host round trip for the tree; here a level is one launch and the tree one.
 #include "common.cuh"
 #include "draft_tree.cuh"
 
@@ -42,46 +42,9 @@ __device__ __forceinline__ unsigned long long warp_max_u64(unsigned long long v)
     return (static_cast<unsigned long long>(H) << 32) | L;
 }
 
-// ---- pass 1: per (row, segment) running max and sum of exp over bf16 logits
-__global__ void lsm_stats_kernel(const bf16* __restrict__ logits, int ld, int vocab, float2* __restrict__ stats,
-                                 int nseg, const int32_t* __restrict__ row0) {
-    grid_dependency_sync();
-    __shared__ float sh_m[SCAN_THREADS / 32];
-    __shared__ float sh_s[SCAN_THREADS / 32];
-    const int row = blockIdx.y, seg = blockIdx.x;
-    const bf16* x = logits + static_cast<size_t>(row + (row0 ? *row0 : 0)) * ld;
-    const int begin = seg * SEG;
-    const int end = min(begin + SEG, vocab);
-    float v[SEG / SCAN_THREADS];
-    float m = -INFINITY;
-#pragma unroll
-    for (int j = 0; j < SEG / SCAN_THREADS; ++j) {
-        const int i = begin + j * SCAN_THREADS + threadIdx.x;
-        v[j] = (i < end) ? __bfloat162float(x[i]) : -INFINITY;
-        m = fmaxf(m, v[j]);
-    }
-#pragma unroll
-    for (int o = 16; o > 0; o >>= 1) m = fmaxf(m, __shfl_xor_sync(0xffffffffu, m, o));
-    if ((threadIdx.x & 31) == 0) sh_m[threadIdx.x >> 5] = m;
-    __syncthreads();
-    m = sh_m[0];
-#pragma unroll
-    for (int w = 1; w < SCAN_THREADS / 32; ++w) m = fmaxf(m, sh_m[w]);
-    float s = 0.f;
-    if (m > -INFINITY) {
-#pragma unroll
-        for (int j = 0; j < SEG / SCAN_THREADS; ++j) s += expf(v[j] - m);  // exp(-inf) = 0 for padding
-    }
-#pragma unroll
-    for (int o = 16; o > 0; o >>= 1) s += __shfl_xor_sync(0xffffffffu, s, o);
-    if ((threadIdx.x & 31) == 0) sh_s[threadIdx.x >> 5] = s;
-    __syncthreads();
-    if (threadIdx.x == 0) {
-        float t = 0.f;
-#pragma unroll
-        for (int w = 0; w < SCAN_THREADS / 32; ++w) t += sh_s[w];
-        stats[static_cast<size_t>(row) * nseg + seg] = make_float2(m, t);
-    }
+__device__ __forceinline__ bf16 bf16_from_orderable(uint32_t o) {
+    const uint16_t b = (o & 0x8000u) ? static_cast<uint16_t>(o & 0x7FFFu) : static_cast<uint16_t>(~o);
+    return __ushort_as_bfloat16(b);
 }
 
 // Row-wide log-sum-exp offset from the segment partials, computed by one CTA with a
@@ -112,74 +75,6 @@ __device__ __forceinline__ float2 row_offset_block(const float2* __restrict__ st
     return make_float2(m, logf(sum));
 }
 
-// ---- pass 2: lp = bf16(x - max - log(sum)); segment-local top-k by (lp desc, index asc)
-__global__ void lsm_local_topk_kernel(const bf16* __restrict__ logits, int ld, int vocab,
-                                      const float2* __restrict__ stats, int nseg, int k,
-                                      unsigned long long* __restrict__ cand, const int32_t* __restrict__ row0,
-                                      float2* __restrict__ rowoff) {
-    grid_dependency_sync();
-    __shared__ float sh_red[SCAN_THREADS / 32];
-    const int row = blockIdx.y, seg = blockIdx.x;
-    const float2 off = row_offset_block(stats + static_cast<size_t>(row) * nseg, nseg, sh_red);
-    if (seg == 0 && threadIdx.x == 0) rowoff[row] = off;  // the expansion kernel reuses the exact values
-    const float mx = off.x, ls = off.y;
-    const bf16* x = logits + static_cast<size_t>(row + (row0 ? *row0 : 0)) * ld;
-    const int begin = seg * SEG;
-    const int end = min(begin + SEG, vocab);
-    // Inside a segment a 32-bit key orders the candidates: (orderable 16-bit value << 16) | (0xFFFF - local index),
-    // larger = earlier in (value desc, index asc) order, 0 = no entry.  One compare, one hardware reduction.
-    static_assert(SEG <= 65536, "local index must fit 16 bits");
-    uint32_t keys[SEG / SCAN_THREADS];
-#pragma unroll
-    for (int j = 0; j < SEG / SCAN_THREADS; ++j) {
-        const int local = j * SCAN_THREADS + threadIdx.x;
-        const int i = begin + local;
-        if (i < end) {
-            const bf16 lp = __float2bfloat16(__bfloat162float(x[i]) - mx - ls);
-            keys[j] = (bf16_orderable(lp) << 16) | static_cast<uint32_t>(0xFFFF - local);
-        } else {
-            keys[j] = 0u;
-        }
-    }
-    unsigned long long* out = cand + (static_cast<size_t>(row) * nseg + seg) * k;
-    // each warp extracts the k best of its 256 keys (no block-wide barrier per round), then warp 0 merges
-    // the 8 x k survivors; k <= 32
-    __shared__ uint32_t wtop[SCAN_THREADS / 32][32];
-    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-    for (int round = 0; round < k; ++round) {
-        uint32_t best = 0u;
-#pragma unroll
-        for (int j = 0; j < SEG / SCAN_THREADS; ++j) best = max(best, keys[j]);
-        best = __reduce_max_sync(0xffffffffu, best);
-        if (lane == 0) wtop[warp][round] = best;
-#pragma unroll
-        for (int j = 0; j < SEG / SCAN_THREADS; ++j) {
-            if (keys[j] == best) keys[j] = 0u;  // keys are unique (the index is part of the key)
-        }
-    }
-    __syncthreads();
-    if (warp == 0) {
-        uint32_t mine[SCAN_THREADS / 32];
-#pragma unroll
-        for (int w = 0; w < SCAN_THREADS / 32; ++w) mine[w] = (lane < k) ? wtop[w][lane] : 0u;
-        for (int round = 0; round < k; ++round) {
-            uint32_t best = 0u;
-#pragma unroll
-            for (int w = 0; w < SCAN_THREADS / 32; ++w) best = max(best, mine[w]);
-            best = __reduce_max_sync(0xffffffffu, best);
-            if (lane == 0) {
-                // the candidate in the row-wide 64-bit form of make_key(); 0 stays 0 (fewer than k entries)
-                const uint32_t idx = static_cast<uint32_t>(begin) + (0xFFFFu - (best & 0xFFFFu));
-                out[round] = best ? ((static_cast<unsigned long long>(best >> 16) << 32) | (0xFFFFFFFFu - idx)) : 0ull;
-            }
-#pragma unroll
-            for (int w = 0; w < SCAN_THREADS / 32; ++w) {
-                if (mine[w] == best) mine[w] = 0u;
-            }
-        }
-    }
-}
-
 // Select the `k` largest of `n` unique 32-bit keys held in shared memory by one warp (the keys are consumed);
 // result r (0 = largest) is returned to lane r.  Callers pack (orderable 16-bit value << 16) | (0xFFFF - position)
 // with positions that rise with the candidate index among equal values.
@@ -198,44 +93,207 @@ __device__ uint32_t warp_select(uint32_t* keys, int n, int k, int lane) {
     return mine;
 }
 
-// ---- pass 3 + frontier expansion.  One CTA, one warp per frontier row.
-// level 0: rows = 1; seeds the frontier from the single row's top-k.
-// level d >= 1: rows = k; cumulative scores, history append, top-k of k*k,
-//               parent / mask / hidden / token bookkeeping for the next level.
-__global__ void draft_expand_kernel(DraftTreeState st, const unsigned long long* __restrict__ cand, int nseg,
-                                    const bf16* __restrict__ logits, int ld, const float2* __restrict__ rowoff,
-                                    int level, const int32_t* __restrict__ last_row_ptr) {
+// The same over unique 64-bit keys (value << 32 | ~index).
+__device__ unsigned long long warp_select64(unsigned long long* keys, int n, int k, int lane) {
+    unsigned long long mine = 0ull;
+    for (int round = 0; round < k; ++round) {
+        unsigned long long best = 0ull;
+        for (int i = lane; i < n; i += 32) best = (keys[i] > best) ? keys[i] : best;
+        best = warp_max_u64(best);
+        if (lane == round) mine = best;
+        for (int i = lane; i < n; i += 32) {
+            if (keys[i] == best) keys[i] = 0ull;
+        }
+        __syncwarp();
+    }
+    return mine;
+}
+
+// One launch per draft level: log-softmax statistics, top-k and frontier expansion.
+//
+// Every CTA owns one (row, 2048-entry vocabulary segment): it reduces the segment's (max, sum of exp) and extracts
+// the segment's k largest LOGITS.  The CTA that is counted last on the ticket, i.e. after every segment of every row
+// is in global memory, turns the candidates into log-probabilities lp = bf16(x - max - log(sum)) (the reference's
+// in-place log_softmax stores the model dtype), picks each row's k best by (lp descending, index ascending) and runs
+// the level's bookkeeping.  No grid-wide wait: only the last CTA reads what the others wrote.
+//
+// Exactness of picking by logit first: lp is a non-decreasing function of the logit, but bf16 rounding maps many
+// logits to one lp, and among equal lp the reference prefers the LOWER index, which a segment's logit order does not
+// know.  An element outside a segment's k best logits can only belong to the row's answer if that segment's own k-th
+// candidate still reaches the answer's threshold lp (all k of its candidates compete in the top bucket); the last
+// CTA detects that and re-selects such a row exactly from the full logit row.  With 36 segments and k = 10 this needs
+// ten of a row's best entries inside one segment; the small vocabularies of the tests take the path routinely.
+__global__ void draft_level_kernel(DraftTreeState st, const bf16* __restrict__ logits, int ld, int vocab, int nseg,
+                                   float2* __restrict__ stats, unsigned long long* __restrict__ cand,
+                                   unsigned* __restrict__ ticket, int level, const int32_t* __restrict__ last_row_ptr) {
     grid_dependency_sync();
-    extern __shared__ unsigned long long sh_keys[];  // rows * nseg * k candidate keys, then as many 32-bit selection keys
+    extern __shared__ unsigned long long sh_keys[];  // last CTA: one candidate list (nseg * k keys) per warp
+    __shared__ float sh_m[SCAN_THREADS / 32];
+    __shared__ float sh_s[SCAN_THREADS / 32];
+    __shared__ uint32_t wtop[SCAN_THREADS / 32][32];
+    __shared__ int s_last;
     const int k = st.k;
     const int rows = (level == 0) ? 1 : k;
+    const int row = blockIdx.y, seg = blockIdx.x;
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-    const int per_row = nseg * k;
+    const int row0 = (level == 0 && last_row_ptr) ? *last_row_ptr : 0;
+    {
+        const bf16* x = logits + static_cast<size_t>(row + row0) * ld;
+        const int begin = seg * SEG;
+        const int end = min(begin + SEG, vocab);
+        // Inside a segment a 32-bit key orders the logits: (orderable 16-bit value << 16) | (0xFFFF - local index),
+        // larger = earlier in (value desc, index asc) order, 0 = no entry.  One compare, one hardware reduction.
+        static_assert(SEG <= 65536, "local index must fit 16 bits");
+        float v[SEG / SCAN_THREADS];
+        uint32_t keys[SEG / SCAN_THREADS];
+        float m = -INFINITY;
+#pragma unroll
+        for (int j = 0; j < SEG / SCAN_THREADS; ++j) {
+            const int local = j * SCAN_THREADS + threadIdx.x;
+            const int i = begin + local;
+            if (i < end) {
+                const bf16 xv = x[i];
+                v[j] = __bfloat162float(xv);
+                keys[j] = (bf16_orderable(xv) << 16) | static_cast<uint32_t>(0xFFFF - local);
+            } else {
+                v[j] = -INFINITY;
+                keys[j] = 0u;
+            }
+            m = fmaxf(m, v[j]);
+        }
+#pragma unroll
+        for (int o = 16; o > 0; o >>= 1) m = fmaxf(m, __shfl_xor_sync(0xffffffffu, m, o));
+        if (lane == 0) sh_m[warp] = m;
+        __syncthreads();
+        m = sh_m[0];
+#pragma unroll
+        for (int w = 1; w < SCAN_THREADS / 32; ++w) m = fmaxf(m, sh_m[w]);
+        float sum = 0.f;
+        if (m > -INFINITY) {
+#pragma unroll
+            for (int j = 0; j < SEG / SCAN_THREADS; ++j) sum += expf(v[j] - m);  // exp(-inf) = 0 for padding
+        }
+#pragma unroll
+        for (int o = 16; o > 0; o >>= 1) sum += __shfl_xor_sync(0xffffffffu, sum, o);
+        if (lane == 0) sh_s[warp] = sum;
+        // each warp extracts the k best of its 256 keys (no block-wide barrier per round), then warp 0 merges
+        // the 8 x k survivors; k <= 32
+        for (int round = 0; round < k; ++round) {
+            uint32_t best = 0u;
+#pragma unroll
+            for (int j = 0; j < SEG / SCAN_THREADS; ++j) best = max(best, keys[j]);
+            best = __reduce_max_sync(0xffffffffu, best);
+            if (lane == 0) wtop[warp][round] = best;
+#pragma unroll
+            for (int j = 0; j < SEG / SCAN_THREADS; ++j) {
+                if (keys[j] == best) keys[j] = 0u;  // keys are unique (the index is part of the key)
+            }
+        }
+        __syncthreads();
+        if (threadIdx.x == 0) {
+            float t = 0.f;
+#pragma unroll
+            for (int w = 0; w < SCAN_THREADS / 32; ++w) t += sh_s[w];
+            stats[static_cast<size_t>(row) * nseg + seg] = make_float2(m, t);
+        }
+        if (warp == 0) {
+            unsigned long long* out = cand + (static_cast<size_t>(row) * nseg + seg) * k;
+            uint32_t mine[SCAN_THREADS / 32];
+#pragma unroll
+            for (int w = 0; w < SCAN_THREADS / 32; ++w) mine[w] = (lane < k) ? wtop[w][lane] : 0u;
+            for (int round = 0; round < k; ++round) {
+                uint32_t best = 0u;
+#pragma unroll
+                for (int w = 0; w < SCAN_THREADS / 32; ++w) best = max(best, mine[w]);
+                best = __reduce_max_sync(0xffffffffu, best);
+                if (lane == 0) {
+                    // (orderable logit << 32) | ~index, the row-wide form of make_key(); 0 stays 0 (fewer than k entries)
+                    const uint32_t idx = static_cast<uint32_t>(begin) + (0xFFFFu - (best & 0xFFFFu));
+                    out[round] = best ? ((static_cast<unsigned long long>(best >> 16) << 32) | (0xFFFFFFFFu - idx)) : 0ull;
+                }
+#pragma unroll
+                for (int w = 0; w < SCAN_THREADS / 32; ++w) {
+                    if (mine[w] == best) mine[w] = 0u;
+                }
+            }
+        }
+    }
+    // ---- ticket: the last CTA to get here sees every CTA's statistics and candidates
+    __syncthreads();
+    if (threadIdx.x == 0) {
+        __threadfence();
+        s_last = (atomicAdd(ticket, 1u) == gridDim.x * gridDim.y - 1) ? 1 : 0;
+        __threadfence();
+    }
+    __syncthreads();
+    if (!s_last) return;
+    if (threadIdx.x == 0) *ticket = 0u;  // ready for the next launch
+
+    __shared__ float2 s_off[32];
     __shared__ bf16 s_val[32 * 32];
     __shared__ int s_pos[32 * 32];
     __shared__ uint32_t s_ckey[32 * 32];
     __shared__ int s_sel[32];
     __shared__ uint64_t s_oldmask[32];
-
-    if (warp < rows) {
+    for (int r = 0; r < rows; ++r) {   // same block-wide reduction tree for every row: results do not depend on timing
+        const float2 off = row_offset_block(stats + static_cast<size_t>(r) * nseg, nseg, sh_m);
+        if (threadIdx.x == 0) s_off[r] = off;
+    }
+    __syncthreads();
+    const int per_row = nseg * k;
+    constexpr int NW = SCAN_THREADS / 32;
+    for (int r = warp; r < rows; r += NW) {
         unsigned long long* mykeys = sh_keys + static_cast<size_t>(warp) * per_row;
-        uint32_t* sel = reinterpret_cast<uint32_t*>(sh_keys + static_cast<size_t>(rows) * per_row) + static_cast<size_t>(warp) * per_row;
-        // The list holds segment after segment, each sorted by (value desc, index asc): among equal values the
-        // position in the list rises with the vocabulary index, so (value, position) orders like (value, index).
+        const float mx = s_off[r].x, ls = s_off[r].y;
+        // candidates as (orderable lp << 32) | ~index: unique, ordered like (lp desc, index asc)
         for (int i = lane; i < per_row; i += 32) {
-            const unsigned long long c = cand[static_cast<size_t>(warp) * per_row + i];
-            mykeys[i] = c;
-            sel[i] = c ? ((static_cast<uint32_t>(c >> 32) << 16) | static_cast<uint32_t>(0xFFFF - i)) : 0u;
+            const unsigned long long c = cand[static_cast<size_t>(r) * per_row + i];
+            unsigned long long key = 0ull;
+            if (c) {
+                const bf16 lp = __float2bfloat16(__bfloat162float(bf16_from_orderable(static_cast<uint32_t>(c >> 32))) - mx - ls);
+                key = (static_cast<unsigned long long>(bf16_orderable(lp)) << 32) | (c & 0xFFFFFFFFull);
+            }
+            mykeys[i] = key;
         }
         __syncwarp();
-        const uint32_t got = warp_select(sel, per_row, k, lane);
-        if (lane < k) {
-            const int idx = got ? key_index(mykeys[0xFFFF - (got & 0xFFFFu)]) : 0;
-            const float mx = rowoff[warp].x, ls = rowoff[warp].y;
-            const int lrow = warp + ((level == 0 && last_row_ptr) ? *last_row_ptr : 0);
-            const bf16 lp = __float2bfloat16(__bfloat162float(logits[static_cast<size_t>(lrow) * ld + idx]) - mx - ls);
-            s_val[warp * k + lane] = lp;
-            s_pos[warp * k + lane] = idx;
+        // note every segment's last (k-th) candidate before the selection consumes the list: lane l holds the
+        // segments l, l + 32, l + 64, l + 96
+        unsigned long long lasts[4] = {0ull, 0ull, 0ull, 0ull};
+        for (int sg = lane, j = 0; sg < nseg && j < 4; sg += 32, ++j) lasts[j] = mykeys[sg * k + (k - 1)];
+        unsigned long long got = warp_select64(mykeys, per_row, k, lane);
+        {
+            // threshold = the row's k-th best key.  A segment whose own k-th candidate still reaches the threshold
+            // lp may hide further entries of the threshold bucket (with lower indices): re-select such a row exactly.
+            const unsigned long long kth = __shfl_sync(0xffffffffu, got, k - 1);
+            const uint32_t tau = static_cast<uint32_t>(kth >> 32);
+            bool saturated = false;
+#pragma unroll
+            for (int j = 0; j < 4; ++j) {
+                if (kth != 0ull && lasts[j] != 0ull && static_cast<uint32_t>(lasts[j] >> 32) >= tau) saturated = true;
+            }
+            if (__any_sync(0xffffffffu, saturated)) {
+                // k rounds of "largest key below the previous pick" over the whole logit row
+                const bf16* x = logits + static_cast<size_t>(r + row0) * ld;
+                unsigned long long prev = ~0ull;
+                got = 0ull;
+                for (int round = 0; round < k; ++round) {
+                    unsigned long long best = 0ull;
+                    for (int i = lane; i < vocab; i += 32) {
+                        const bf16 lp = __float2bfloat16(__bfloat162float(x[i]) - mx - ls);
+                        const unsigned long long key = make_key(lp, i);
+                        if (key < prev && key > best) best = key;
+                    }
+                    best = warp_max_u64(best);
+                    if (lane == round) got = best;
+                    prev = best;
+                }
+            }
+            if (lane < k) {
+                const int idx = got ? key_index(got) : 0;
+                const bf16 lp = __float2bfloat16(__bfloat162float(logits[static_cast<size_t>(r + row0) * ld + idx]) - mx - ls);
+                s_val[r * k + lane] = lp;
+                s_pos[r * k + lane] = idx;
+            }
         }
     }
     __syncthreads();
@@ -376,7 +434,7 @@ size_t draft_scan_workspace_bytes(int rows, int vocab, int k) {
     const int nseg = draft_num_segments(vocab);
     (void)rows;
     return static_cast<size_t>(32) * nseg * (sizeof(float2) + static_cast<size_t>(k) * sizeof(unsigned long long)) + 1024;
-}
+}  // the first word is the level kernel's ticket and must be zero before the first launch
 
 void launch_draft_topk_expand(const DraftTreeState& st, const bf16* logits, int ld, int vocab, int level,
                               void* scan_ws, const bf16* h_rows, int h_ld, const int32_t* last_row_ptr, bf16* hid_out,
@@ -386,27 +444,22 @@ void launch_draft_topk_expand(const DraftTreeState& st, const bf16* logits, int 
     const int nseg = draft_num_segments(vocab);
     CPM_REQUIRE(k >= 1 && k <= 32, "draft: topk_per_iter must be in [1,32]");
     CPM_REQUIRE(hidden % 8 == 0, "draft: hidden size must be a multiple of 8");
-    float2* stats = reinterpret_cast<float2*>(scan_ws);
-    float2* rowoff = reinterpret_cast<float2*>(reinterpret_cast<uint8_t*>(scan_ws) +
-                                               align_up(static_cast<int64_t>(32) * nseg * sizeof(float2), 256));
-    unsigned long long* cand = reinterpret_cast<unsigned long long*>(reinterpret_cast<uint8_t*>(rowoff) + 256);
-    dim3 grid(nseg, rows);
-    launch_kernel(lsm_stats_kernel, grid, dim3(SCAN_THREADS), 0, s, logits, ld, vocab, stats, nseg,
-                  level == 0 ? last_row_ptr : nullptr);
-    launch_kernel(lsm_local_topk_kernel, grid, dim3(SCAN_THREADS), 0, s, logits, ld, vocab, static_cast<const float2*>(stats),
-                  nseg, k, cand, level == 0 ? last_row_ptr : nullptr, rowoff);
-    CPM_REQUIRE(nseg * k <= 65535, "draft: candidate list too long for 16-bit positions");
-    const size_t shmem = static_cast<size_t>(rows) * nseg * k * (sizeof(unsigned long long) + sizeof(uint32_t));
+    CPM_REQUIRE(nseg <= 128, "draft: vocabulary larger than 262144 entries");
+    // workspace: [ticket | statistics 32 x nseg | candidates 32 x nseg x k]; the ticket is zero between launches
+    unsigned* ticket = reinterpret_cast<unsigned*>(scan_ws);
+    float2* stats = reinterpret_cast<float2*>(reinterpret_cast<uint8_t*>(scan_ws) + 256);
+    unsigned long long* cand = reinterpret_cast<unsigned long long*>(
+        reinterpret_cast<uint8_t*>(stats) + align_up(static_cast<int64_t>(32) * nseg * sizeof(float2), 256));
+    const size_t shmem = static_cast<size_t>(SCAN_THREADS / 32) * nseg * k * sizeof(unsigned long long);
     static size_t configured = 0;
-    if (shmem > 32 * 1024 && shmem > configured) {   // the kernel also has 11 KB of static shared memory
-        CPM_REQUIRE(shmem <= 200 * 1024, "draft: candidate list too large for one CTA");
-        CUDA_CHECK(cudaFuncSetAttribute(draft_expand_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
+    if (shmem > 24 * 1024 && shmem > configured) {   // the kernel also has 22 KB of static shared memory
+        CPM_REQUIRE(shmem <= 200 * 1024, "draft: candidate lists too large for one CTA");
+        CUDA_CHECK(cudaFuncSetAttribute(draft_level_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                         static_cast<int>(shmem)));
         configured = shmem;
     }
-    launch_kernel(draft_expand_kernel, dim3(1), dim3(32 * (k < 4 ? 4 : k)), shmem, s, st,
-                  static_cast<const unsigned long long*>(cand), nseg, logits, ld, static_cast<const float2*>(rowoff), level,
-                  last_row_ptr);
+    launch_kernel(draft_level_kernel, dim3(nseg, rows), dim3(SCAN_THREADS), shmem, s, st, logits, ld, vocab, nseg, stats, cand,
+                  ticket, level, last_row_ptr);
     if (hid_out != nullptr) {
         launch_kernel(gather_rows_kernel, dim3(k), dim3(128), 0, s, h_rows, h_ld, static_cast<const int32_t*>(st.fr_src),
                       hid_out, hid_ld, hidden);

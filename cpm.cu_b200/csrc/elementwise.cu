@@ -258,8 +258,40 @@ __device__ __forceinline__ void am_better(float& best, int& bi, float v, int i) 
     if (v > best || (v == best && i < bi)) { best = v; bi = i; }
 }
 
+// Philox4x32-10 (Salmon, Moraes, Dror, Shaw: "Parallel random numbers: as easy as 1, 2, 3", SC 2011): a
+// counter-based generator, so the noise of element i of row r at draw c is a pure function of (seed, r, c, i)
+// and a sampled step is reproducible whatever the launch shape.
+__device__ __forceinline__ uint4 philox4x32_10(uint4 ctr, uint2 key) {
+#pragma unroll
+    for (int round = 0; round < 10; ++round) {
+        const uint32_t hi0 = __umulhi(0xD2511F53u, ctr.x), lo0 = 0xD2511F53u * ctr.x;
+        const uint32_t hi1 = __umulhi(0xCD9E8D57u, ctr.z), lo1 = 0xCD9E8D57u * ctr.z;
+        ctr = make_uint4(hi1 ^ ctr.y ^ key.x, lo1, hi0 ^ ctr.w ^ key.y, lo0);
+        key.x += 0x9E3779B9u;
+        key.y += 0xBB67AE85u;
+    }
+    return ctr;
+}
+
+// Sampling parameters of the row pick: temperature <= 0 means plain argmax.  With a temperature the pick is
+// argmax_i(logit_i / temperature + G_i), G_i independent standard Gumbel noise: the Gumbel-max form of drawing
+// from softmax(logits / temperature) (what the reference does with torch.multinomial,
+// cpmcu/speculative/tree_drafter.py:230-231), which keeps the two-stage argmax structure.
+struct PickNoise {
+    float inv_temperature;        // 0: no noise
+    unsigned long long seed;
+    const int32_t* draw;          // device counter of draws so far (may be null), plus
+    int draw_add;
+};
+
+__device__ __forceinline__ float gumbel_from_bits(uint32_t bits) {
+    const float u = (static_cast<float>(bits >> 8) + 0.5f) * (1.0f / 16777216.0f);  // (0, 1), 24 bits
+    return -logf(-logf(u));
+}
+
+template <bool NOISY>
 __global__ void argmax_partial_kernel(const bf16* __restrict__ logits, int vocab, int ld, int nchunk,
-                                      float* __restrict__ pval, int* __restrict__ pidx) {
+                                      float* __restrict__ pval, int* __restrict__ pidx, PickNoise noise) {
     grid_dependency_sync();
     __shared__ float sv[32];
     __shared__ int si[32];
@@ -268,20 +300,47 @@ __global__ void argmax_partial_kernel(const bf16* __restrict__ logits, int vocab
     const int begin = chunk * AM_CHUNK, end = min(begin + AM_CHUNK, vocab);
     float best = -INFINITY;
     int bi = 0x7fffffff;
+    const uint32_t draw = NOISY ? static_cast<uint32_t>((noise.draw ? *noise.draw : 0) + noise.draw_add) : 0u;
+    const uint2 key = make_uint2(static_cast<uint32_t>(noise.seed), static_cast<uint32_t>(noise.seed >> 32));
+    // value of element i: the logit, or logit / temperature + Gumbel noise; one Philox block serves 4 elements
+    auto value4 = [&](const bf16* e, int i, float* out) {   // i a multiple of 4
+        if constexpr (NOISY) {
+            const uint4 r = philox4x32_10(make_uint4(static_cast<uint32_t>(i >> 2), static_cast<uint32_t>(row), draw, 0u), key);
+            out[0] = __bfloat162float(e[0]) * noise.inv_temperature + gumbel_from_bits(r.x);
+            out[1] = __bfloat162float(e[1]) * noise.inv_temperature + gumbel_from_bits(r.y);
+            out[2] = __bfloat162float(e[2]) * noise.inv_temperature + gumbel_from_bits(r.z);
+            out[3] = __bfloat162float(e[3]) * noise.inv_temperature + gumbel_from_bits(r.w);
+        } else {
+#pragma unroll
+            for (int j = 0; j < 4; ++j) out[j] = __bfloat162float(e[j]);
+        }
+    };
+    auto value1 = [&](int i) -> float {
+        const float v = __bfloat162float(x[i]);
+        if constexpr (NOISY) {
+            const uint4 r = philox4x32_10(make_uint4(static_cast<uint32_t>(i >> 2), static_cast<uint32_t>(row), draw, 0u), key);
+            const uint32_t bits = (i & 3) == 0 ? r.x : (i & 3) == 1 ? r.y : (i & 3) == 2 ? r.z : r.w;
+            return v * noise.inv_temperature + gumbel_from_bits(bits);
+        }
+        return v;
+    };
     const bool aligned = ((reinterpret_cast<uintptr_t>(x + begin) & 15) == 0);
     if (aligned) {
         for (int i = begin + threadIdx.x * 8; i < end; i += blockDim.x * 8) {
             if (i + 8 <= end) {
                 const uint4 v = *reinterpret_cast<const uint4*>(x + i);
                 const bf16* e = reinterpret_cast<const bf16*>(&v);
+                float f[8];
+                value4(e, i, f);
+                value4(e + 4, i + 4, f + 4);
 #pragma unroll
-                for (int j = 0; j < 8; ++j) am_better(best, bi, __bfloat162float(e[j]), i + j);
+                for (int j = 0; j < 8; ++j) am_better(best, bi, f[j], i + j);
             } else {
-                for (int j = i; j < end; ++j) am_better(best, bi, __bfloat162float(x[j]), j);
+                for (int j = i; j < end; ++j) am_better(best, bi, value1(j), j);
             }
         }
     } else {
-        for (int i = begin + threadIdx.x; i < end; i += blockDim.x) am_better(best, bi, __bfloat162float(x[i]), i);
+        for (int i = begin + threadIdx.x; i < end; i += blockDim.x) am_better(best, bi, value1(i), i);
     }
 #pragma unroll
     for (int o = 16; o > 0; o >>= 1) {
@@ -394,6 +453,22 @@ void launch_add_scaled(bf16* x, const bf16* a, const bf16* b, float scale_b, int
     launch_kernel(add_scaled_kernel, dim3(static_cast<unsigned>((n / 2 + 255) / 256)), dim3(256), 0, s, x, a, b, scale_b, n);
 }
 
+__global__ void add_bias_add_kernel(bf16* __restrict__ x, const bf16* __restrict__ a, const bf16* __restrict__ bias,
+                                    const bf16* __restrict__ b, int dim, size_t n) {
+    grid_dependency_sync();
+    const size_t i = static_cast<size_t>(blockIdx.x) * blockDim.x + threadIdx.x;
+    if (i >= n) return;
+    float v = __bfloat162float(a[i]);
+    if (bias != nullptr) v = __bfloat162float(__float2bfloat16(v + __bfloat162float(bias[i % dim])));
+    x[i] = __float2bfloat16(v + __bfloat162float(b[i]));
+}
+
+void launch_add_bias_add(bf16* x, const bf16* a, const bf16* bias, const bf16* b, int rows, int dim, cudaStream_t s) {
+    const size_t n = static_cast<size_t>(rows) * dim;
+    if (n == 0) return;
+    launch_kernel(add_bias_add_kernel, dim3(static_cast<unsigned>((n + 255) / 256)), dim3(256), 0, s, x, a, bias, b, dim, n);
+}
+
 void launch_scale(bf16* out, const bf16* in, float scale, size_t n, cudaStream_t s) {
     if (n == 0) return;
     launch_kernel(scale_kernel, dim3(static_cast<unsigned>((n + 255) / 256)), dim3(256), 0, s, out, in, scale, n);
@@ -404,11 +479,25 @@ size_t argmax_workspace_bytes(int rows, int vocab) {
 }
 
 void launch_argmax(const bf16* logits, int rows, int vocab, int ld, int32_t* out, void* workspace, cudaStream_t s) {
+    launch_sample(logits, rows, vocab, ld, out, workspace, 0.f, 0ull, nullptr, 0, s);
+}
+
+void launch_sample(const bf16* logits, int rows, int vocab, int ld, int32_t* out, void* workspace, float temperature,
+                   unsigned long long seed, const int32_t* draw, int draw_add, cudaStream_t s) {
     if (rows <= 0) return;
     const int nchunk = ceil_div(vocab, AM_CHUNK);
     float* pval = static_cast<float*>(workspace);
     int* pidx = reinterpret_cast<int*>(pval + static_cast<size_t>(rows) * nchunk);
-    launch_kernel(argmax_partial_kernel, dim3(nchunk, rows), dim3(256), 0, s, logits, vocab, ld, nchunk, pval, pidx);
+    PickNoise noise;
+    noise.inv_temperature = temperature > 0.f ? 1.0f / temperature : 0.f;
+    noise.seed = seed;
+    noise.draw = draw;
+    noise.draw_add = draw_add;
+    if (temperature > 0.f) {
+        launch_kernel(argmax_partial_kernel<true>, dim3(nchunk, rows), dim3(256), 0, s, logits, vocab, ld, nchunk, pval, pidx, noise);
+    } else {
+        launch_kernel(argmax_partial_kernel<false>, dim3(nchunk, rows), dim3(256), 0, s, logits, vocab, ld, nchunk, pval, pidx, noise);
+    }
     launch_kernel(argmax_merge_kernel, dim3(rows), dim3(32), 0, s, static_cast<const float*>(pval),
                   static_cast<const int*>(pidx), nchunk, out);
 }
@@ -453,8 +542,8 @@ extern "C" int cpmcu_argmax_noalloc(const void* logits, int rows, int vocab, int
     float* pval = static_cast<float*>(scratch_addr[dev]);
     int* pidx = reinterpret_cast<int*>(pval + static_cast<size_t>(rows) * nchunk);
     // Both stages overwrite every scratch word they later read, so nothing has to be cleared.
-    argmax_partial_kernel<<<dim3(nchunk, rows), 256, 0, cudaStreamLegacy>>>(static_cast<const bf16*>(logits), vocab, vocab,
-                                                                            nchunk, pval, pidx);
+    argmax_partial_kernel<false><<<dim3(nchunk, rows), 256, 0, cudaStreamLegacy>>>(static_cast<const bf16*>(logits), vocab,
+                                                                                   vocab, nchunk, pval, pidx, PickNoise{});
     argmax_merge_kernel<<<rows, 32, 0, cudaStreamLegacy>>>(pval, pidx, nchunk, out);
     e = cudaGetLastError();
     if (e == cudaSuccess) e = cudaStreamSynchronize(cudaStreamLegacy);

@@ -25,6 +25,7 @@ __global__ void state_sync_kernel(int32_t* st, const int32_t* cache_length, int3
     st[1] = n;
     st[2] = L - n;
     st[3] = (n > 0) ? n - 1 : 0;
+    if (fused) st[8] += 1;  // S_DRAW: index of this step's sampling draw
 }
 
 __global__ void publish_kernel(const int32_t* result, const int32_t* tokens, const int* error, int32_t* st,
@@ -104,6 +105,11 @@ void Engine::attach_eagle(const EagleConfig& ec) {
     CPM_REQUIRE(ec.topk >= 1 && ec.topk <= 32 && ec.topk <= ec.tree_size - 1, "topk_per_iter out of range");
     CPM_REQUIRE(ec.num_iter >= 1 && ec.num_iter <= 15, "num_iter out of range");
     CPM_REQUIRE(ec.topk * ec.num_iter <= 64, "draft keys (topk * num_iter) exceed the 64-bit mask");
+    if (ec.quant) {
+        CPM_REQUIRE(ec.group_size == 128, "W4A16 drafter: only group_size 128 is supported");
+        CPM_REQUIRE(mc_.hidden % 256 == 0 && mc_.inter % 256 == 0 && (mc_.hq * mc_.head_dim) % 256 == 0 && mc_.hidden % 128 == 0,
+                    "W4A16 drafter: hidden, intermediate and attention widths must be multiples of 256");
+    }
     ec_ = ec;
     has_eagle_ = true;
     draft_vocab_ = (ec.frspec_vocab > 0 && ec.frspec_vocab != mc_.vocab) ? ec.frspec_vocab : mc_.vocab;
@@ -149,14 +155,23 @@ void Engine::lay_out(Pool& p) {
         w.ln_ffn = take<bf16>(p, H);
     }
     if (has_eagle_) {
-        fc_ = take<bf16>(p, static_cast<size_t>(H) * 2 * H);
         fc_bias_ = take<bf16>(p, H);
         in_norm1_ = take<bf16>(p, H);
         in_norm2_ = take<bf16>(p, H);
-        elayer_.qkv = take<bf16>(p, static_cast<size_t>(qkv_dim_) * H);
-        elayer_.o = take<bf16>(p, static_cast<size_t>(H) * mc_.hq * d);
-        elayer_.gate_up = take<bf16>(p, static_cast<size_t>(2) * I * H);
-        elayer_.down = take<bf16>(p, static_cast<size_t>(H) * I);
+        if (ec_.quant) {
+            fc1_q_ = take<uint8_t>(p, linear_w4_weight_bytes(H, H));
+            fc2_q_ = take<uint8_t>(p, linear_w4_weight_bytes(H, H));
+            elayer_.qkv_q = take<uint8_t>(p, linear_w4_weight_bytes(qkv_dim_, H));
+            elayer_.o_q = take<uint8_t>(p, linear_w4_weight_bytes(H, mc_.hq * d));
+            elayer_.gate_up_q = take<uint8_t>(p, linear_w4_weight_bytes(2 * I, H));
+            elayer_.down_q = take<uint8_t>(p, linear_w4_weight_bytes(H, I));
+        } else {
+            fc_ = take<bf16>(p, static_cast<size_t>(H) * 2 * H);
+            elayer_.qkv = take<bf16>(p, static_cast<size_t>(qkv_dim_) * H);
+            elayer_.o = take<bf16>(p, static_cast<size_t>(H) * mc_.hq * d);
+            elayer_.gate_up = take<bf16>(p, static_cast<size_t>(2) * I * H);
+            elayer_.down = take<bf16>(p, static_cast<size_t>(H) * I);
+        }
         elayer_.ln_attn = take<bf16>(p, H);
         elayer_.ln_ffn = take<bf16>(p, H);
         token_id_remap_ = take<int32_t>(p, draft_vocab_);
@@ -299,8 +314,15 @@ int Engine::init_storage() {
         build_layer_plans(eplan_catchup_, elayer_, ekv_, rc, attn_splits_for(rc));
         eplan_level_.attn.window = ec_.window;
         eplan_catchup_.attn.window = ec_.window;
-        fc_plan_level_ = checked(make_linear_plan(e_in_, k, fc_, k, H, 2 * H, e_x_, H, fc_bias_, gemm_ws_, tickets_, rt.num_sms));
-        fc_plan_catchup_ = checked(make_linear_plan(e_in_, rc, fc_, rc, H, 2 * H, e_x_, H, fc_bias_, gemm_ws_, tickets_, rt.num_sms));
+        if (ec_.quant) {
+            fc_plan_level_ = checked(make_linear_plan_w4(e_in_, k, fc1_q_, k, H, H, e_x_, H, gemm_ws_, tickets_, rt.num_sms));
+            fc2_plan_level_ = checked(make_linear_plan_w4(ein_hidden(), k, fc2_q_, k, H, H, delta_, H, gemm_ws_, tickets_, rt.num_sms));
+            fc_plan_catchup_ = checked(make_linear_plan_w4(e_in_, rc, fc1_q_, rc, H, H, e_x_, H, gemm_ws_, tickets_, rt.num_sms));
+            fc2_plan_catchup_ = checked(make_linear_plan_w4(ein_hidden(), rc, fc2_q_, rc, H, H, delta_, H, gemm_ws_, tickets_, rt.num_sms));
+        } else {
+            fc_plan_level_ = checked(make_linear_plan(e_in_, k, fc_, k, H, 2 * H, e_x_, H, fc_bias_, gemm_ws_, tickets_, rt.num_sms));
+            fc_plan_catchup_ = checked(make_linear_plan(e_in_, rc, fc_, rc, H, 2 * H, e_x_, H, fc_bias_, gemm_ws_, tickets_, rt.num_sms));
+        }
         const bool scale_in = (!ec_.minicpm4_variant && mc_.scale_lmhead != 1.0f);
         const bf16* lm_x = scale_in ? lm_in_ : e_h_;
         dlm_plan_level_ = checked(make_linear_plan(lm_x, k, draft_lm_head_, k, draft_vocab_, H, e_logits_, draft_vocab_, nullptr,
@@ -348,7 +370,13 @@ void Engine::load(const std::string& name, const void* src) {
     std::smatch m;
     if (name.rfind("eagle", 0) == 0) {
         CPM_REQUIRE(has_eagle_, "eagle weight given but no drafter was initialised");
-        if (name.rfind("eagle.fc1", 0) == 0) {
+        if (ec_.quant && (name.rfind("eagle.fc1", 0) == 0 || name.rfind("eagle.fc2", 0) == 0) &&
+            name.find("bias") == std::string::npos) {
+            const bool second = name.rfind("eagle.fc2", 0) == 0;
+            const bool is_scales = name.find("scales") != std::string::npos;
+            CPM_REQUIRE(is_scales || name.find("qweight") != std::string::npos, "Unsupported name " + name);
+            load_quantized(second ? "E.fc2" : "E.fc1", is_scales, src, H, H, second ? fc2_q_ : fc1_q_);
+        } else if (name.rfind("eagle.fc1", 0) == 0) {
             if (name.find("weight") != std::string::npos) {
                 CUDA_CHECK(cudaMemcpy2DAsync(fc_, static_cast<size_t>(2) * H * 2, src, static_cast<size_t>(H) * 2,
                                              static_cast<size_t>(H) * 2, H, cudaMemcpyDefault, rt.stream));
@@ -374,6 +402,7 @@ void Engine::load(const std::string& name, const void* src) {
             copy(inv_freq_, static_cast<size_t>(d / 2) * 4);
         } else if (std::regex_search(name, m, layer_re)) {
             CPM_REQUIRE(std::stoi(m[1]) == 0, "drafter has a single layer");
+            if (ec_.quant && load_quant_layer(elayer_, "E", m[2])) return;
             load_layer(elayer_, m[2]);
         } else {
             throw std::invalid_argument("Unsupported name (layer_idx not found): " + name);
@@ -606,19 +635,35 @@ void Engine::draft_forward(const RowCtx& c, int rows, LayerPlans& lp, cudaStream
     launch_add_scaled(e_h_, e_x_, delta_, ec_.residual_scale, c.rows, mc_.hidden, s);
 }
 
+// x = fc1(embedding half) + b + fc2(hidden half) into e_x_.  bf16 drafter: one GEMM over K = 2H with the bias in
+// its epilogue.  W4A16 drafter: two int4 GEMMs and one add, each rounded as the reference rounds them
+// (src/model/minicpm4/minicpm4_eagle.cuh:228-243).
+void Engine::draft_fc(int rows, const LinearPlan& fc, const LinearPlan& fc2, cudaStream_t s) {
+    launch_linear(fc, s);
+    if (!ec_.quant) return;
+    launch_linear(fc2, s);
+    launch_add_bias_add(e_x_, e_x_, fc_bias_, delta_, rows, mc_.hidden, s);
+}
+
 // Draft pass over the num_prev_ rows left by prefill (reference eagle_prefill).
 void Engine::draft_first(int history, cudaStream_t s) {
     const int H = mc_.hidden, P = num_prev_;
     Runtime& rt = runtime();
     if (ec_.use_input_norm) {
-        launch_rms_norm(prev_embed_, H, in_norm1_, e_in_, 2 * H, P, H, mc_.eps, s);
-        launch_rms_norm(prev_hidden_, H, in_norm2_, e_in_ + H, 2 * H, P, H, mc_.eps, s);
+        launch_rms_norm(prev_embed_, H, in_norm1_, e_in_, ein_ld(), P, H, mc_.eps, s);
+        launch_rms_norm(prev_hidden_, H, in_norm2_, ein_hidden(), ein_ld(), P, H, mc_.eps, s);
     } else {
-        copy_rows(e_in_, 2 * H, prev_embed_, H, P, H, s);
-        copy_rows(e_in_ + H, 2 * H, prev_hidden_, H, P, H, s);
+        copy_rows(e_in_, ein_ld(), prev_embed_, H, P, H, s);
+        copy_rows(ein_hidden(), ein_ld(), prev_hidden_, H, P, H, s);
     }
-    LinearPlan fc = checked(make_linear_plan(e_in_, P, fc_, P, H, 2 * H, e_x_, H, fc_bias_, gemm_ws_, tickets_, rt.num_sms));
-    launch_linear(fc, s);
+    if (ec_.quant) {
+        LinearPlan f1 = checked(make_linear_plan_w4(e_in_, P, fc1_q_, P, H, H, e_x_, H, gemm_ws_, tickets_, rt.num_sms));
+        LinearPlan f2 = checked(make_linear_plan_w4(ein_hidden(), P, fc2_q_, P, H, H, delta_, H, gemm_ws_, tickets_, rt.num_sms));
+        draft_fc(P, f1, f2, s);
+    } else {
+        LinearPlan fc = checked(make_linear_plan(e_in_, P, fc_, P, H, 2 * H, e_x_, H, fc_bias_, gemm_ws_, tickets_, rt.num_sms));
+        draft_fc(P, fc, fc, s);
+    }
     CUDA_CHECK(cudaMemcpyAsync(st_ + 7, &history, sizeof(int), cudaMemcpyHostToDevice, s));
     LayerPlans lp;
     build_layer_plans(lp, elayer_, ekv_, P, 1);
@@ -637,13 +682,13 @@ void Engine::draft_first(int history, cudaStream_t s) {
 void Engine::draft_catchup(cudaStream_t s) {
     const int H = mc_.hidden, rc = catchup_rows_;
     if (ec_.use_input_norm) {
-        launch_rms_norm(prev_embed_, H, in_norm1_, e_in_, 2 * H, rc, H, mc_.eps, s);
-        launch_rms_norm(prev_hidden_, H, in_norm2_, e_in_ + H, 2 * H, rc, H, mc_.eps, s);
+        launch_rms_norm(prev_embed_, H, in_norm1_, e_in_, ein_ld(), rc, H, mc_.eps, s);
+        launch_rms_norm(prev_hidden_, H, in_norm2_, ein_hidden(), ein_ld(), rc, H, mc_.eps, s);
     } else {
-        copy_rows(e_in_, 2 * H, prev_embed_, H, rc, H, s);
-        copy_rows(e_in_ + H, 2 * H, prev_hidden_, H, rc, H, s);
+        copy_rows(e_in_, ein_ld(), prev_embed_, H, rc, H, s);
+        copy_rows(ein_hidden(), ein_ld(), prev_hidden_, H, rc, H, s);
     }
-    launch_linear(fc_plan_catchup_, s);
+    draft_fc(rc, fc_plan_catchup_, fc2_plan_catchup_, s);
     // layer_forward takes kv_len for both append and attention; the catch-up needs
     // different bases (append at L-n, attend over L), so split it here.
     {
@@ -675,8 +720,8 @@ void Engine::draft_levels(int32_t* tree_ids, int32_t* tree_pos, const int32_t* c
     const int H = mc_.hidden, k = ec_.topk;
     Runtime& rt = runtime();
     const bool scale_in = (!ec_.minicpm4_variant && mc_.scale_lmhead != 1.0f);
-    bf16* hid_dst = ec_.use_input_norm ? e_hid_ : e_in_ + H;
-    const int hid_ld = ec_.use_input_norm ? H : 2 * H;
+    bf16* hid_dst = ec_.use_input_norm ? e_hid_ : ein_hidden();
+    const int hid_ld = ec_.use_input_norm ? H : ein_ld();
     // level 0: logits of the last pending row.  The frontier's hidden rows are gathered by the next level's
     // embedding kernel from `h_src` (the expansion kernel only records which row each node continues from).
     const bf16* h_src = e_h_;
@@ -703,14 +748,14 @@ void Engine::draft_levels(int32_t* tree_ids, int32_t* tree_pos, const int32_t* c
         if (ec_.use_input_norm) {
             launch_embedding_gather(tree_.fr_id, embed_, e_emb_, H, k, H, mc_.scale_embed, h_src, H, tree_.fr_src, hid_dst,
                                     hid_ld, s);
-            launch_rms_norm(e_emb_, H, in_norm1_, e_in_, 2 * H, k, H, mc_.eps, s);
-            launch_rms_norm(e_hid_, H, in_norm2_, e_in_ + H, 2 * H, k, H, mc_.eps, s);
+            launch_rms_norm(e_emb_, H, in_norm1_, e_in_, ein_ld(), k, H, mc_.eps, s);
+            launch_rms_norm(e_hid_, H, in_norm2_, ein_hidden(), ein_ld(), k, H, mc_.eps, s);
         } else {
-            launch_embedding_gather(tree_.fr_id, embed_, e_in_, 2 * H, k, H, mc_.scale_embed, h_src, H, tree_.fr_src, hid_dst,
+            launch_embedding_gather(tree_.fr_id, embed_, e_in_, ein_ld(), k, H, mc_.scale_embed, h_src, H, tree_.fr_src, hid_dst,
                                     hid_ld, s);
         }
         h_src = e_h_;
-        launch_linear(fc_plan_level_, s);
+        draft_fc(k, fc_plan_level_, fc2_plan_level_, s);
         RowCtx c;
         c.rows = k;
         c.pos_base = cache_length;
@@ -819,6 +864,19 @@ void Engine::require_room(long rows_after_len, const char* where) const {
 }
 
 // ------------------------------------------------------------------ fused step
+void Engine::set_sampling(float temperature, unsigned long long seed) {
+    CPM_REQUIRE(temperature >= 0.f, "temperature must not be negative");
+    if ((temperature > 0.f) != (temperature_ > 0.f) || temperature != temperature_ || seed != sample_seed_) {
+        // temperature and seed are baked into the captured step
+        if (step_graph_) {
+            cudaGraphExecDestroy(step_graph_);
+            step_graph_ = nullptr;
+        }
+    }
+    temperature_ = temperature;
+    sample_seed_ = seed;
+}
+
 void Engine::begin_generation(int prefix_length, int32_t root_token) {
     CPM_REQUIRE(has_eagle_ && storage_ready_, "begin_generation needs an initialised drafter");
     CPM_REQUIRE(first_draft_, "begin_generation must follow prefill");
@@ -827,7 +885,7 @@ void Engine::begin_generation(int prefix_length, int32_t root_token) {
     init[S_L] = prefix_length;
     CPM_REQUIRE(prefix_length >= 1 && prefix_length <= budget_, "begin_generation: prefix length out of range");
     host_len_ = prefix_length;
-    CUDA_CHECK(cudaMemcpyAsync(st_, init, 6 * sizeof(int32_t), cudaMemcpyHostToDevice, s));
+    CUDA_CHECK(cudaMemcpyAsync(st_, init, S_COUNT * sizeof(int32_t), cudaMemcpyHostToDevice, s));
     CUDA_CHECK(cudaMemcpyAsync(t_ids_, &root_token, sizeof(int32_t), cudaMemcpyHostToDevice, s));
     CUDA_CHECK(cudaStreamSynchronize(s));
 }
@@ -875,7 +933,7 @@ void Engine::enqueue_step(bool first, cudaStream_t s) {
                                          nullptr, gemm_ws_, tickets_, runtime().num_sms));
     }
     launch_linear(lm_plan_tree_, s);
-    launch_argmax(logits_, T, V, V, t_gt_, argmax_ws_, s);
+    launch_sample(logits_, T, V, V, t_gt_, argmax_ws_, temperature_, sample_seed_, st_ + S_DRAW, 0, s);
     accept_and_fix(T, t_ids_, t_gt_, t_pos_, st_ + S_L, t_mask_, t_parent_, s);
     CUDA_CHECK(cudaMemcpyAsync(h_result_, d_publish_, 32 * sizeof(int32_t), cudaMemcpyDeviceToHost, s));
 }

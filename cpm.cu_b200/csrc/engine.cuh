@@ -33,6 +33,10 @@ struct EagleConfig {
     float residual_scale = 1.f;
     bool use_input_norm = false, use_attn_norm = false;
     bool minicpm4_variant = false;  // draft LM head skips scale_lmhead (reference quirk)
+    // W4A16 drafter (reference apply_eagle_quant, src/entry.cu:83-96): fc1, fc2 and the draft layer's four linears
+    // arrive as GPTQ-Marlin int4 tensors; fc1 and fc2 are then two GEMMs (the bf16 drafter runs them as one)
+    bool quant = false;
+    int group_size = 128;
 };
 
 struct LayerWeights {
@@ -94,6 +98,10 @@ public:
     // fused step: draft -> tree -> verify -> accept in one CUDA graph, state on the device.
     // begin_generation() is called once after prefill with the first root token.
     void begin_generation(int prefix_length, int32_t root_token);
+    // temperature > 0: the fused step picks the target's token at every tree node by sampling from
+    // softmax(logits / temperature) instead of argmax (reference cpmcu/speculative/tree_drafter.py:230-231), on the
+    // device and inside the captured step; the draw index advances with every step, so a run is a function of the seed
+    void set_sampling(float temperature, unsigned long long seed);
     int spec_step(int32_t* out_tokens, int max_tokens);  // returns accept length n; out_tokens[0:n]
     void profile_step(float* ms, int* counts, float* total_ms);
     double last_step_device_ms() const { return last_step_ms_; }
@@ -168,6 +176,7 @@ private:
     // draft weights
     bf16* fc_ = nullptr;       // [hidden, 2*hidden]: columns [0,H) act on the token embedding, [H,2H) on the hidden state
     bf16* fc_bias_ = nullptr;
+    uint8_t *fc1_q_ = nullptr, *fc2_q_ = nullptr;  // W4A16 drafter: [H -> H] each, streaming 4-bit layout
     bf16* in_norm1_ = nullptr;
     bf16* in_norm2_ = nullptr;
     LayerWeights elayer_;
@@ -201,7 +210,7 @@ private:
     SparseBuffers sp_;  // InfLLM-v2 compressed caches, scores and block masks (sparse target only)
     // device state words
     int32_t* st_ = nullptr;
-    enum { S_L = 0, S_NPREV = 1, S_BASE = 2, S_LASTROW = 3, S_ACCEPT = 4, S_ZERO = 5, S_COUNT = 16 };
+    enum { S_L = 0, S_NPREV = 1, S_BASE = 2, S_LASTROW = 3, S_ACCEPT = 4, S_ZERO = 5, S_DRAW = 8, S_COUNT = 16 };
     int32_t* eagle_pos_ = nullptr;
     int32_t* accept_result_ = nullptr;  // [2 + 16]
     int32_t* d_publish_ = nullptr;      // [32]: n, tokens, error word (copied to the host)
@@ -219,6 +228,12 @@ private:
     std::map<int, std::unique_ptr<ForwardPlans>> plans_;
     LayerPlans eplan_level_, eplan_catchup_;
     LinearPlan fc_plan_level_, fc_plan_catchup_, dlm_plan_level_, dlm_plan_catchup_;
+    LinearPlan fc2_plan_level_, fc2_plan_catchup_;  // W4A16 drafter: the hidden-state half of fc
+    // Where the drafter's fc input rows live: bf16 drafter [rows, 2H] (embedding | hidden state side by side, one
+    // GEMM over K = 2H); W4A16 drafter two [rows, H] matrices (the int4 kernel wants densely packed rows).
+    int ein_ld() const { return ec_.quant ? mc_.hidden : 2 * mc_.hidden; }
+    bf16* ein_hidden() const { return ec_.quant ? e_in_ + static_cast<size_t>(max_rows_) * mc_.hidden : e_in_ + mc_.hidden; }
+    void draft_fc(int rows, const LinearPlan& fc, const LinearPlan& fc2, cudaStream_t s);
     LinearPlan lm_plan_tree_;
 
     cudaGraphExec_t step_graph_ = nullptr;
@@ -227,6 +242,8 @@ private:
     // tokens whose target K/V rows are final, as far as the host knows (prefill, then every accepted length);
     // -1 before the first prefill.  Guards every pass against writing K/V rows beyond the budget.
     long host_len_ = -1;
+    float temperature_ = 0.f;
+    unsigned long long sample_seed_ = 0;
     void require_room(long rows_after_len, const char* where) const;
     long launches_per_step_ = 0;
     long launch_counter_ = 0;

@@ -75,7 +75,8 @@ int cpmcu_init_eagle_model(int num_layers, int num_iter, int topk_per_iter, int 
 
 /* reference: init_minicpm4_eagle_model, src/entry.cu:303-341 (optional input
  * norms / attention norm, FR-Spec reduced draft vocabulary, draft sliding
- * window, residual scale).  apply_eagle_quant must be 0. */
+ * window, residual scale).  apply_eagle_quant: fc1, fc2 and the draft layer's linears are W4A16 GPTQ-Marlin
+ * tensors (group_size 128), src/entry.cu:83-96, src/model/minicpm4/minicpm4_eagle.cuh:77-94. */
 int cpmcu_init_minicpm4_eagle_model(int num_layers, int num_iter, int topk_per_iter, int tree_size, int torch_dtype,
                                     int apply_eagle_quant, int group_size, int eagle_window_size,
                                     int frspec_vocab_size, float residual_scale, int use_input_norm,
@@ -128,6 +129,13 @@ void cpmcu_print_perf_summary(void);
  * root_token is the first generated token.  No counterpart in the reference
  * (its loop lives in cpmcu/speculative/tree_drafter.py:215-252). */
 int cpmcu_begin_generation(int prefix_length, int32_t root_token);
+
+/* Sampling mode of the fused step (temperature 0 = greedy, the default): with a temperature the step picks the
+ * target's token at every tree node as cpmcu_sample does, inside the captured step, draw index = number of steps
+ * since cpmcu_begin_generation (the root token is draw 0: cpmcu_sample on the prefill logits).  Call it before
+ * cpmcu_begin_generation; a change re-captures the step.  No counterpart in the reference's C module (its
+ * sampling is torch code in the Python loop). */
+int cpmcu_set_sampling(float temperature, unsigned long long seed);
 
 /* One speculative step on engine-owned buffers.  Writes the n emitted tokens
  * to out_tokens (HOST memory, at most max_tokens) and returns n, or -1. */
@@ -233,6 +241,13 @@ int cpmcu_silu_gate(const void* gate_up, void* out, int rows, int inter);
 /* Row argmax (lowest index wins ties); reference: torch argmax in
  * cpmcu/speculative/tree_drafter.py:233. */
 int cpmcu_argmax(const void* logits, int rows, int vocab, int32_t* out);
+
+/* One token per row drawn from softmax(logits[r] / temperature); reference: torch.multinomial over
+ * F.softmax(logits / temperature), cpmcu/speculative/tree_drafter.py:99-100,230-231.  The draw is
+ * argmax(logit / temperature + Gumbel noise) with Philox4x32-10 noise keyed by (seed, row, draw, column), so it
+ * is a pure function of its arguments; temperature == 0 is cpmcu_argmax. */
+int cpmcu_sample(const void* logits, int rows, int vocab, float temperature, unsigned long long seed, int draw,
+                 int32_t* out);
 
 /* Row argmax like cpmcu_argmax, but without any device allocation.  It has no
  * counterpart in the reference.  cpmcu_argmax takes its two-stage scratch from

@@ -5,6 +5,8 @@
     python kernel_bench.py attention [tq,hq,hkv,kv,splits,mask] [iters]
     python kernel_bench.py select [tq,hq,hkv,L,budget] [iters]    InfLLM-v2 block selection of one layer
     python kernel_bench.py reference                   the reference project's own kernels beside the library's
+    python kernel_bench.py tail [iters]                the integer tail of a step at the 8B shapes: draft tree from
+                                                       logits (log-softmax, top-k, expansion, tree) and acceptance + fix-up
 
 Each case runs `iters` back-to-back launches inside the library, timed with CUDA events on the
 library's stream, rotating over enough separate weight (or KV-cache) copies that no launch finds
@@ -130,6 +132,69 @@ def bench_reference(iters=40):
         print("%-66s %12.1f %12.1f %8.2f" % (name, a, b, a / b), flush=True)
 
 
+def bench_tail(iters=5):
+    """The latency-bound integer stages at the headline shapes, through their kernel-level entry points: the draft
+    tree from given logits (V = 73448, top-k 10, 6 iterations, 60 nodes: per level log-softmax statistics, local
+    top-k and expansion, then the tree) and acceptance + K/V compaction + gathers (64 caches of 256-wide rows, hidden
+    4096).  Host-clock time per call (each call synchronises); run under ncu for the per-kernel device times."""
+    import time
+
+    import torch
+    V, k, it, T, H = 73448, 10, 6, 60, 4096
+    g = torch.Generator(device="cuda").manual_seed(1)
+    p = lambda t: ctypes.c_void_p(t.data_ptr()) if t is not None else None  # noqa: E731
+    logits = (torch.randn(1 + (it - 1) * k, V, generator=g, device="cuda") * 2).to(torch.bfloat16)
+    tt = k + k * k * (it - 1)
+    ids = torch.zeros(64, dtype=torch.int32, device="cuda")
+    pos = torch.zeros(64, dtype=torch.int32, device="cuda")
+    mask = torch.zeros(64, dtype=torch.int64, device="cuda")
+    par = torch.zeros(64, dtype=torch.int32, device="cuda")
+    tv = torch.zeros(tt + 64, dtype=torch.bfloat16, device="cuda")
+    tp = torch.zeros(tt + 64, dtype=torch.int32, device="cuda")
+    tpar = torch.zeros(k * it + 64, dtype=torch.int32, device="cuda")
+    cl = torch.tensor([4096], dtype=torch.int32, device="cuda")
+    torch.cuda.synchronize()
+    for i in range(iters + 1):
+        if i == 1:
+            t0 = time.time()
+        C.call("cpmcu_draft_tree_from_logits", p(logits), V, k, it, T, None, p(cl), p(ids), p(pos), p(mask), p(par), p(tv),
+               p(tp), p(tpar))
+    print(f"draft tree from logits V={V} k={k} iters={it} T={T}: {(time.time() - t0) / iters * 1e6:.0f} us per call "
+          f"(host clock, {3 * it + 1} launches)", flush=True)
+    rows, kvd, ncache = 4352, 256, 64
+    caches = [torch.randn(rows, kvd, device="cuda", generator=g).to(torch.bfloat16) for _ in range(ncache)]
+    cptr = torch.tensor([c.data_ptr() for c in caches], dtype=torch.int64, device="cuda")
+    gt = torch.randint(0, V, (64,), device="cuda", generator=g).to(torch.int32)
+    # a chain 0 -> 1 -> 2 -> 3 is drafted correctly: accept length 4
+    pred = gt.clone()
+    tree_par = torch.zeros(64, dtype=torch.int32, device="cuda")
+    tree_pos = torch.full((64,), 4097, dtype=torch.int32, device="cuda")
+    import numpy as np
+    tree_mask = torch.from_numpy(np.array([(1 << i) | 1 for i in range(64)], dtype=np.uint64).view(np.int64)).to("cuda")
+    for i in range(1, 4):
+        tree_par[i] = i - 1
+        tree_pos[i] = 4096 + i
+        tree_mask[i] = (1 << (i + 1)) - 1   # i <= 3
+        pred[i] = gt[i - 1]
+    tree_pos[0] = 4096
+    norm_out = torch.randn(64, H, device="cuda", generator=g).to(torch.bfloat16)
+    prev_hidden = torch.zeros(8, H, dtype=torch.bfloat16, device="cuda")
+    prev_embed = torch.zeros(8, H, dtype=torch.bfloat16, device="cuda")
+    embed = torch.randn(V, H, device="cuda", generator=g).to(torch.bfloat16)
+    epos = torch.zeros(8, dtype=torch.int32, device="cuda")
+    result = torch.zeros(32, dtype=torch.int32, device="cuda")
+    torch.cuda.synchronize()
+    for i in range(iters + 1):
+        if i == 1:
+            t0 = time.time()
+        pr = pred.clone()
+        C.call("cpmcu_accept_fixup", T, p(pr), p(gt), p(tree_pos), p(cl), p(tree_mask), p(tree_par), p(cptr), ncache, kvd, rows,
+               7, H, p(norm_out), p(prev_hidden), p(embed), 1.0, p(prev_embed), p(epos), p(result))
+    assert int(result[0]) == 4
+    print(f"acceptance + fix-up T={T}, {ncache} caches x {kvd}, hidden {H}, accept length 4: "
+          f"{(time.time() - t0) / iters * 1e6:.0f} us per call (host clock, 1 launch)", flush=True)
+
+
 def main(argv):
     what = argv[1] if len(argv) > 1 else "linear"
     shape = tuple(int(v) for v in argv[2].split(",")) if len(argv) > 2 else None
@@ -140,6 +205,8 @@ def main(argv):
         bench_linear([shape] if shape else W4_SHAPES, iters, True)
     elif what == "attention":
         bench_attention([shape] if shape else ATTN_CASES, iters)
+    elif what == "tail":
+        bench_tail(int(argv[2]) if len(argv) > 2 else 5)
     elif what == "reference":
         bench_reference(iters if len(argv) > 3 else 40)
     elif what == "select":

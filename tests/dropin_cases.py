@@ -37,6 +37,8 @@ CASES = {
                    fc_gain=200.0, chunk=512),
     "quant": dict(cfg="q", eagle=dict(num_iter=4, topk=4, tree_size=16), seed=8, prompt=120, gen=30, layer_scale=0.6,
                   fc_gain=200.0, chunk=256, quant=True),
+    "quant_draft": dict(cfg="q", eagle=dict(num_iter=4, topk=4, tree_size=16, minicpm4_variant=True), seed=13, prompt=120,
+                        gen=36, layer_scale=0.6, fc_gain=200.0, chunk=256, quant=True, quant_draft=True),
     "headline_tree": dict(cfg="c", eagle=dict(num_iter=6, topk=10, tree_size=60), seed=12, prompt=300, gen=48,
                           layer_scale=0.3, fc_gain=8.0, chunk=512),
 }
@@ -63,6 +65,9 @@ def make_oracle(name, budget=1024):
     if CASES[name].get("quant"):
         from helpers import quantize_target
         w, _ = quantize_target(cfg, w)
+    if CASES[name].get("quant_draft"):
+        from helpers import quantize_eagle
+        ew, _ = quantize_eagle(cfg, ew)
     return OracleModel(cfg, w, eagle, ew, budget=budget, token_id_remap=remap), prompt
 
 
@@ -79,12 +84,17 @@ def write_case(name, root):
     else:
         tensors = {k: v.to(torch.bfloat16) for k, v in w.items()}
     etensors = {k: v.to(torch.bfloat16) for k, v in ew.items()}
+    eagle_config = None
+    if c.get("quant_draft"):
+        from helpers import quantize_eagle
+        _, etensors = quantize_eagle(cfg, ew)
+        eagle_config = {"quantization_config": {"group_size": 128, "bits": 4}}
     if remap is not None:
         etensors["token_id_remap"] = torch.from_numpy(remap)
     config = synth_ckpt.base_config(cfg.vocab, cfg.layers, cfg.hidden, cfg.inter, cfg.hq, cfg.hkv, cfg.head_dim, cfg.eps,
                                     cfg.rope_theta, extra)
     base_dir, eagle_dir = os.path.join(root, name, "base"), os.path.join(root, name, "eagle")
-    synth_ckpt.write_checkpoint(base_dir, eagle_dir, config, tensors.items(), etensors.items())
+    synth_ckpt.write_checkpoint(base_dir, eagle_dir, config, tensors.items(), etensors.items(), eagle_config)
     return base_dir, eagle_dir, prompt
 
 
@@ -106,4 +116,6 @@ def reference_command(name, base_dir, eagle_dir, prompt_file, out_file, memory_l
         cmd += ["--window", str(e["window"])]
     if c.get("quant"):
         cmd.append("--quant")
+    if c.get("quant_draft"):
+        cmd.append("--eagle-quant")
     return cmd

@@ -135,11 +135,59 @@ def quantize_target(cfg, w):
     return w, ckpt
 
 
-def build_quant_pair(cfg, eagle, seed=0, chunk_length=256, layer_scale=0.6, fc_gain=200.0, budget=1024, sparse=None):
+def quantize_eagle(cfg, ew):
+    """W4A16 view of a drafter: returns (weights with fc and the layer's linears replaced by their dequantised
+    values, for the oracle) and the checkpoint tensors of a quantised drafter as the reference loads them:
+    `layers.0.*` fused like a target layer, `fc.qweight` / `fc.scales` = the two [H -> H] halves (embedding half,
+    hidden-state half) quantised separately and concatenated along the last dimension, `fc.bias` bf16
+    (cpmcu/speculative/eagle_base_quant/eagle_base_w4a16_marlin_gptq.py:80-103)."""
+    from oracle import marlin
+    ew = dict(ew)
+    ckpt = {}
+    H = cfg.hidden
+
+    def quant(full):                                   # full: [N, K] float
+        q, s = marlin.quantize_sym_int4(full.t().contiguous().numpy())
+        packed, sperm = marlin.marlin_pack(q, s)
+        deq = torch.from_numpy(marlin.dequantize(q, s)).t().contiguous()
+        return torch.from_numpy(packed.copy()), torch.from_numpy(sperm.copy()).to(torch.bfloat16), deq
+
+    groups = {"self_attn.qkv_proj": ["self_attn.q_proj", "self_attn.k_proj", "self_attn.v_proj"],
+              "self_attn.o_proj": ["self_attn.o_proj"], "mlp.gate_up_proj": ["mlp.gate_proj", "mlp.up_proj"],
+              "mlp.down_proj": ["mlp.down_proj"]}
+    for fused, parts in groups.items():
+        qw, sc, deq = quant(torch.cat([ew["layers.0." + n + ".weight"] for n in parts], dim=0))
+        row = 0
+        for n in parts:
+            rows = ew["layers.0." + n + ".weight"].shape[0]
+            ew["layers.0." + n + ".weight"] = deq[row:row + rows].clone()
+            row += rows
+        ckpt["layers.0." + fused + ".qweight"] = qw
+        ckpt["layers.0." + fused + ".scales"] = sc
+    q1, s1, d1 = quant(ew["fc.weight"][:, :H])
+    q2, s2, d2 = quant(ew["fc.weight"][:, H:])
+    ew["fc.weight"] = torch.cat([d1, d2], dim=1)
+    ckpt["fc.qweight"] = torch.cat([q1, q2], dim=-1)
+    ckpt["fc.scales"] = torch.cat([s1, s2], dim=-1)
+    for name in ew:
+        if "layernorm" in name or name in ("fc.bias", "input_norm1.weight", "input_norm2.weight"):
+            ckpt[name] = ew[name].to(torch.bfloat16)
+    return ew, ckpt
+
+
+def build_quant_pair(cfg, eagle, seed=0, chunk_length=256, layer_scale=0.6, fc_gain=200.0, budget=1024, sparse=None,
+                     quant_draft=False):
     from cpmcu.speculative.eagle_base_quant.eagle_base_w4a16_marlin_gptq import W4A16GPTQMarlinLLM_with_eagle
     import os
     w, ew = make_weights(cfg, seed, eagle, layer_scale=layer_scale, fc_mode="embed", fc_gain=fc_gain)
     wq, ckpt = quantize_target(cfg, w)
+    eckpt = {k: v.to(torch.bfloat16) for k, v in ew.items()}
+    econfig = {"num_hidden_layers": 1}
+    extra = {}
+    if quant_draft:
+        ew, eckpt = quantize_eagle(cfg, ew)
+        econfig["quantization_config"] = {"group_size": 128, "bits": 4}
+        extra = dict(apply_eagle_quant=True, use_input_norm=eagle.use_input_norm, use_attn_norm=eagle.use_attn_norm)
     oracle = OracleModel(cfg, wq, eagle, ew, budget=budget, sparse=sparse)
     hf = hf_config(cfg)
     hf.quantization_config = {"group_size": 128, "bits": 4}
@@ -149,10 +197,11 @@ def build_quant_pair(cfg, eagle, seed=0, chunk_length=256, layer_scale=0.6, fc_g
                          block_window_size=sparse.block_window_size, sparse_topk_k=sparse.sparse_topk_k,
                          sparse_switch=sparse.sparse_switch, apply_compress_lse=sparse.apply_compress_lse)
     llm = W4A16GPTQMarlinLLM_with_eagle(None, None, num_iter=eagle.num_iter, topk_per_iter=eagle.topk,
-                                        tree_size=eagle.tree_size, eagle_config={"num_hidden_layers": 1}, config=hf,
-                                        dtype=torch.bfloat16, chunk_length=chunk_length, memory_limit=0.5, **sparse_kw)
+                                        tree_size=eagle.tree_size, eagle_config=econfig, config=hf,
+                                        dtype=torch.bfloat16, chunk_length=chunk_length, memory_limit=0.5, **sparse_kw,
+                                        **extra)
     os.environ.setdefault("CPMCU_MAX_TOKENS", "4096")
     llm.init_storage()
-    llm.load_state_dict_tensors({k: v.to(torch.bfloat16) for k, v in ew.items()}, cls="eagle")
+    llm.load_state_dict_tensors(eckpt, cls="eagle")
     llm.load_state_dict_tensors(ckpt)
     return oracle, llm

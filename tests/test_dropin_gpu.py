@@ -51,7 +51,7 @@ def library_generate(name, base_dir, eagle_dir, prompt, stream=False):
     llm = cls(eagle_dir, base_dir, num_iter=e["num_iter"], topk_per_iter=e["topk"], tree_size=e["tree_size"],
               eagle_window_size=e.get("window", 0), frspec_vocab_size=e.get("frspec_vocab", 0),
               use_input_norm=e.get("use_input_norm", False), use_attn_norm=e.get("use_attn_norm", False),
-              dtype=torch.bfloat16, memory_limit=0.3, chunk_length=c["chunk"], cuda_graph=True)
+              apply_eagle_quant=bool(c.get("quant_draft")), dtype=torch.bfloat16, memory_limit=0.3, chunk_length=c["chunk"], cuda_graph=True)
     assert llm.tokenizer is not None and llm.config.vocab_size == dc.CFGS[c["cfg"]]["vocab"]
     llm.init_storage()
     llm.load_from_hf()

@@ -204,6 +204,23 @@ def test_w4a16_marlin_target_matches_oracle():
     compare_with_oracle(oracle, prompt, tokens, acc, o_tokens, o_acc, "w4a16 vs oracle")
 
 
+@pytest.mark.parametrize("norms", [False, True])
+def test_w4a16_drafter_matches_oracle(norms):
+    """apply_eagle_quant=True: fc1, fc2 and the draft layer's linears arrive as GPTQ-Marlin int4 tensors (the
+    reference's default demo configuration); the oracle runs on the dequantised weights."""
+    from oracle.model import OracleConfig
+    cfg = OracleConfig(vocab=4096, layers=2, hidden=256, inter=768, hq=2, hkv=1, head_dim=128, dtype="bf16")
+    eagle = EagleOracleConfig(num_iter=4, topk=4, tree_size=16, use_input_norm=norms, use_attn_norm=norms,
+                              minicpm4_variant=True)
+    oracle, llm = build_quant_pair(cfg, eagle, seed=13, quant_draft=True)
+    prompt = prompt_ids(120, cfg.vocab, 13)
+    ids_t = torch.tensor(prompt, device="cuda")
+    tokens, acc, _, _ = llm.generate(ids_t, 36)
+    o_tokens, o_acc, steps = oracle.generate_spec(prompt.tolist(), 36)
+    compare_with_oracle(oracle, prompt, tokens, acc, o_tokens, o_acc, "w4a16 drafter vs oracle")
+    assert max(acc) > 1
+
+
 def _popcount(a):
     return int(np.unpackbits(np.ascontiguousarray(a).view(np.uint8)).sum())
 
