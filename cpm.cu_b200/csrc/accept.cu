@@ -74,6 +74,7 @@ __global__ void accept_fixup_kernel(AcceptIO io, FixupArgs a, int cache_rows, in
     const int vec_per_row = a.kv_dim / 8;
     const int kv_threads = a.num_caches * vec_per_row;
     const int hid_vec = a.hidden / 8;
+    const int prev_vec = (a.prev_ld > 0 ? a.prev_ld : a.hidden) / 8;
     const int gid = blockIdx.x * blockDim.x + tid;
     if (gid < kv_threads) {
         if (L + n_fix > cache_rows) {  // host-side length checks come first; this only keeps memory intact
@@ -96,7 +97,7 @@ __global__ void accept_fixup_kernel(AcceptIO io, FixupArgs a, int cache_rows, in
         if (rest < a.max_accept * hid_vec) {  // next draft hidden states
             const int i = rest / hid_vec, v = rest - i * hid_vec;
             if (i < n_fix) {
-                reinterpret_cast<uint4*>(a.prev_hidden)[static_cast<size_t>(i) * hid_vec + v] =
+                reinterpret_cast<uint4*>(a.prev_hidden)[static_cast<size_t>(i) * prev_vec + v] =
                     reinterpret_cast<const uint4*>(a.norm_out)[static_cast<size_t>(s_path[i]) * hid_vec + v];
             }
         } else if (rest < 2 * a.max_accept * hid_vec) {  // embeddings of the emitted tokens
@@ -109,7 +110,7 @@ __global__ void accept_fixup_kernel(AcceptIO io, FixupArgs a, int cache_rows, in
 #pragma unroll
                     for (int j = 0; j < 8; ++j) p[j] = __float2bfloat16(__bfloat162float(p[j]) * a.embed_scale);
                 }
-                reinterpret_cast<uint4*>(a.prev_embed)[static_cast<size_t>(i) * hid_vec + v] = e;
+                reinterpret_cast<uint4*>(a.prev_embed)[static_cast<size_t>(i) * prev_vec + v] = e;
             }
             if (v == 0 && i < a.max_accept) a.eagle_pos[i] = L + i;
         }
@@ -139,7 +140,7 @@ __global__ void accept_fixup_kernel(AcceptIO io, FixupArgs a, int cache_rows, in
 void launch_accept_fixup(const AcceptIO& io, const FixupArgs& a, int cache_rows, cudaStream_t s) {
     CPM_REQUIRE(io.tree_size >= 1 && io.tree_size <= 64, "verify: tree_size must be in [1,64]");
     CPM_REQUIRE(a.max_accept >= 1 && a.max_accept <= MAX_PATH, "fixup: accept length bound out of range");
-    CPM_REQUIRE(a.kv_dim % 8 == 0 && a.hidden % 8 == 0, "fixup: row sizes must be multiples of 8 elements");
+    CPM_REQUIRE(a.kv_dim % 8 == 0 && a.hidden % 8 == 0 && a.prev_ld % 8 == 0, "fixup: row sizes must be multiples of 8 elements");
     const long long threads = static_cast<long long>(a.num_caches) * (a.kv_dim / 8) +
                               2LL * a.max_accept * (a.hidden / 8);
     const unsigned grid = static_cast<unsigned>(threads > 0 ? (threads + 255) / 256 : 1);

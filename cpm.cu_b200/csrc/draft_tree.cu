@@ -11,6 +11,8 @@
 //   build_dynamic_tree_kernel               src/model/eagle.cuh:188-218
 // The reference runs ~12 tiny launches and three device copies per level plus a
 // host round trip for the tree; here a level is one launch and the tree one.
+#include <algorithm>
+
 #include "common.cuh"
 #include "draft_tree.cuh"
 
@@ -47,34 +49,6 @@ __device__ __forceinline__ bf16 bf16_from_orderable(uint32_t o) {
     return __ushort_as_bfloat16(b);
 }
 
-// Row-wide log-sum-exp offset from the segment partials, computed by one CTA with a
-// fixed reduction tree (deterministic): returns (max, log(sum exp(x - max))) to all threads.
-__device__ __forceinline__ float2 row_offset_block(const float2* __restrict__ st, int nseg, float* sh) {
-    float m = -INFINITY;
-    for (int s = threadIdx.x; s < nseg; s += blockDim.x) m = fmaxf(m, st[s].x);
-#pragma unroll
-    for (int o = 16; o > 0; o >>= 1) m = fmaxf(m, __shfl_xor_sync(0xffffffffu, m, o));
-    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, nw = blockDim.x >> 5;
-    if (lane == 0) sh[warp] = m;
-    __syncthreads();
-    m = sh[0];
-    for (int w = 1; w < nw; ++w) m = fmaxf(m, sh[w]);
-    __syncthreads();
-    float sum = 0.f;
-    for (int s = threadIdx.x; s < nseg; s += blockDim.x) {
-        const float2 v = st[s];
-        sum += v.y * expf(v.x - m);
-    }
-#pragma unroll
-    for (int o = 16; o > 0; o >>= 1) sum += __shfl_xor_sync(0xffffffffu, sum, o);
-    if (lane == 0) sh[warp] = sum;
-    __syncthreads();
-    sum = sh[0];
-    for (int w = 1; w < nw; ++w) sum += sh[w];
-    __syncthreads();
-    return make_float2(m, logf(sum));
-}
-
 // Select the `k` largest of `n` unique 32-bit keys held in shared memory by one warp (the keys are consumed);
 // result r (0 = largest) is returned to lane r.  Callers pack (orderable 16-bit value << 16) | (0xFFFF - position)
 // with positions that rise with the candidate index among equal values.
@@ -93,29 +67,14 @@ __device__ uint32_t warp_select(uint32_t* keys, int n, int k, int lane) {
     return mine;
 }
 
-// The same over unique 64-bit keys (value << 32 | ~index).
-__device__ unsigned long long warp_select64(unsigned long long* keys, int n, int k, int lane) {
-    unsigned long long mine = 0ull;
-    for (int round = 0; round < k; ++round) {
-        unsigned long long best = 0ull;
-        for (int i = lane; i < n; i += 32) best = (keys[i] > best) ? keys[i] : best;
-        best = warp_max_u64(best);
-        if (lane == round) mine = best;
-        for (int i = lane; i < n; i += 32) {
-            if (keys[i] == best) keys[i] = 0ull;
-        }
-        __syncwarp();
-    }
-    return mine;
-}
-
 // One launch per draft level: log-softmax statistics, top-k and frontier expansion.
 //
 // Every CTA owns one (row, 2048-entry vocabulary segment): it reduces the segment's (max, sum of exp) and extracts
-// the segment's k largest LOGITS.  The CTA that is counted last on the ticket, i.e. after every segment of every row
-// is in global memory, turns the candidates into log-probabilities lp = bf16(x - max - log(sum)) (the reference's
-// in-place log_softmax stores the model dtype), picks each row's k best by (lp descending, index ascending) and runs
-// the level's bookkeeping.  No grid-wide wait: only the last CTA reads what the others wrote.
+// the segment's k largest LOGITS (written in index order, with the k-th largest value beside the statistics).  The
+// CTA that is counted last on the ticket, i.e. after every segment of every row is in global memory, turns the
+// candidates into log-probabilities lp = bf16(x - max - log(sum)) (the reference's in-place log_softmax stores the
+// model dtype), picks each row's k best by (lp descending, index ascending) and runs the level's bookkeeping.  No
+// grid-wide wait: only the last CTA reads what the others wrote.
 //
 // Exactness of picking by logit first: lp is a non-decreasing function of the logit, but bf16 rounding maps many
 // logits to one lp, and among equal lp the reference prefers the LOWER index, which a segment's logit order does not
@@ -124,10 +83,12 @@ __device__ unsigned long long warp_select64(unsigned long long* keys, int n, int
 // CTA detects that and re-selects such a row exactly from the full logit row.  With 36 segments and k = 10 this needs
 // ten of a row's best entries inside one segment; the small vocabularies of the tests take the path routinely.
 __global__ void draft_level_kernel(DraftTreeState st, const bf16* __restrict__ logits, int ld, int vocab, int nseg,
-                                   float2* __restrict__ stats, unsigned long long* __restrict__ cand,
-                                   unsigned* __restrict__ ticket, int level, const int32_t* __restrict__ last_row_ptr) {
+                                   float4* __restrict__ stats, unsigned long long* __restrict__ cand,
+                                   unsigned* __restrict__ ticket, int level, const int32_t* __restrict__ last_row_ptr,
+                                   int group_rows) {
     grid_dependency_sync();
-    extern __shared__ unsigned long long sh_keys[];  // last CTA: one candidate list (nseg * k keys) per warp
+    // last CTA: candidate lists of `group_rows` rows (64-bit (logit, ~index) entries, then 32-bit selection keys)
+    extern __shared__ unsigned long long sh_keys[];
     __shared__ float sh_m[SCAN_THREADS / 32];
     __shared__ float sh_s[SCAN_THREADS / 32];
     __shared__ uint32_t wtop[SCAN_THREADS / 32][32];
@@ -190,31 +151,39 @@ __global__ void draft_level_kernel(DraftTreeState st, const bf16* __restrict__ l
             }
         }
         __syncthreads();
-        if (threadIdx.x == 0) {
-            float t = 0.f;
-#pragma unroll
-            for (int w = 0; w < SCAN_THREADS / 32; ++w) t += sh_s[w];
-            stats[static_cast<size_t>(row) * nseg + seg] = make_float2(m, t);
-        }
         if (warp == 0) {
-            unsigned long long* out = cand + (static_cast<size_t>(row) * nseg + seg) * k;
             uint32_t mine[SCAN_THREADS / 32];
 #pragma unroll
             for (int w = 0; w < SCAN_THREADS / 32; ++w) mine[w] = (lane < k) ? wtop[w][lane] : 0u;
+            uint32_t picked = 0u;  // lane r: the segment's r-th largest logit
             for (int round = 0; round < k; ++round) {
                 uint32_t best = 0u;
 #pragma unroll
                 for (int w = 0; w < SCAN_THREADS / 32; ++w) best = max(best, mine[w]);
                 best = __reduce_max_sync(0xffffffffu, best);
-                if (lane == 0) {
-                    // (orderable logit << 32) | ~index, the row-wide form of make_key(); 0 stays 0 (fewer than k entries)
-                    const uint32_t idx = static_cast<uint32_t>(begin) + (0xFFFFu - (best & 0xFFFFu));
-                    out[round] = best ? ((static_cast<unsigned long long>(best >> 16) << 32) | (0xFFFFFFFFu - idx)) : 0ull;
-                }
+                if (lane == round) picked = best;
 #pragma unroll
                 for (int w = 0; w < SCAN_THREADS / 32; ++w) {
                     if (mine[w] == best) mine[w] = 0u;
                 }
+            }
+            // write the k candidates in index order (empty entries last): among equal lp the position in the row's
+            // list, segment after segment, then rises with the vocabulary index
+            const uint32_t lidx = (lane < k && picked) ? (0xFFFFu - (picked & 0xFFFFu)) : 0x10000u + lane;
+            int rank = 0;
+            for (int o = 0; o < k; ++o) rank += (__shfl_sync(0xffffffffu, lidx, o) < lidx) ? 1 : 0;
+            if (lane < k) {
+                const uint32_t idx = static_cast<uint32_t>(begin) + (lidx & 0xFFFFu);
+                // (orderable logit << 32) | ~index, the row-wide form of make_key(); 0 = no entry
+                cand[(static_cast<size_t>(row) * nseg + seg) * k + rank] =
+                    picked ? ((static_cast<unsigned long long>(picked >> 16) << 32) | (0xFFFFFFFFu - idx)) : 0ull;
+            }
+            const uint32_t kth = __shfl_sync(0xffffffffu, picked, k - 1);  // 0 when the segment has fewer than k entries
+            if (lane == 0) {
+                float t = 0.f;
+#pragma unroll
+                for (int w = 0; w < SCAN_THREADS / 32; ++w) t += sh_s[w];
+                stats[static_cast<size_t>(row) * nseg + seg] = make_float4(m, t, __uint_as_float(kth >> 16), 0.f);
             }
         }
     }
@@ -229,53 +198,67 @@ __global__ void draft_level_kernel(DraftTreeState st, const bf16* __restrict__ l
     if (!s_last) return;
     if (threadIdx.x == 0) *ticket = 0u;  // ready for the next launch
 
-    __shared__ float2 s_off[32];
     __shared__ bf16 s_val[32 * 32];
     __shared__ int s_pos[32 * 32];
     __shared__ uint32_t s_ckey[32 * 32];
     __shared__ int s_sel[32];
     __shared__ uint64_t s_oldmask[32];
-    for (int r = 0; r < rows; ++r) {   // same block-wide reduction tree for every row: results do not depend on timing
-        const float2 off = row_offset_block(stats + static_cast<size_t>(r) * nseg, nseg, sh_m);
-        if (threadIdx.x == 0) s_off[r] = off;
-    }
-    __syncthreads();
     const int per_row = nseg * k;
     constexpr int NW = SCAN_THREADS / 32;
-    for (int r = warp; r < rows; r += NW) {
-        unsigned long long* mykeys = sh_keys + static_cast<size_t>(warp) * per_row;
-        const float mx = s_off[r].x, ls = s_off[r].y;
-        // candidates as (orderable lp << 32) | ~index: unique, ordered like (lp desc, index asc)
-        for (int i = lane; i < per_row; i += 32) {
-            const unsigned long long c = cand[static_cast<size_t>(r) * per_row + i];
-            unsigned long long key = 0ull;
-            if (c) {
-                const bf16 lp = __float2bfloat16(__bfloat162float(bf16_from_orderable(static_cast<uint32_t>(c >> 32))) - mx - ls);
-                key = (static_cast<unsigned long long>(bf16_orderable(lp)) << 32) | (c & 0xFFFFFFFFull);
-            }
-            mykeys[i] = key;
-        }
-        __syncwarp();
-        // note every segment's last (k-th) candidate before the selection consumes the list: lane l holds the
-        // segments l, l + 32, l + 64, l + 96
-        unsigned long long lasts[4] = {0ull, 0ull, 0ull, 0ull};
-        for (int sg = lane, j = 0; sg < nseg && j < 4; sg += 32, ++j) lasts[j] = mykeys[sg * k + (k - 1)];
-        unsigned long long got = warp_select64(mykeys, per_row, k, lane);
-        {
-            // threshold = the row's k-th best key.  A segment whose own k-th candidate still reaches the threshold
-            // lp may hide further entries of the threshold bucket (with lower indices): re-select such a row exactly.
-            const unsigned long long kth = __shfl_sync(0xffffffffu, got, k - 1);
-            const uint32_t tau = static_cast<uint32_t>(kth >> 32);
-            bool saturated = false;
+    for (int g0 = 0; g0 < rows; g0 += group_rows) {
+        const int gn = min(group_rows, rows - g0);
+        uint32_t* sel_keys = reinterpret_cast<uint32_t*>(sh_keys + static_cast<size_t>(group_rows) * per_row);
+        // one coalesced pass brings the group's candidate lists on chip
+        for (int i = threadIdx.x; i < gn * per_row; i += SCAN_THREADS) sh_keys[i] = cand[static_cast<size_t>(g0) * per_row + i];
+        __syncthreads();
+        for (int rr = warp; rr < gn; rr += NW) {
+            const int r = g0 + rr;
+            unsigned long long* mycand = sh_keys + static_cast<size_t>(rr) * per_row;
+            uint32_t* mysel = sel_keys + static_cast<size_t>(rr) * per_row;
+            // row-wide log-sum-exp offset from the segment partials, fixed reduction order within the warp
+            const float4* rst = stats + static_cast<size_t>(r) * nseg;
+            float mx = -INFINITY;
+            for (int sg = lane; sg < nseg; sg += 32) mx = fmaxf(mx, rst[sg].x);
 #pragma unroll
-            for (int j = 0; j < 4; ++j) {
-                if (kth != 0ull && lasts[j] != 0ull && static_cast<uint32_t>(lasts[j] >> 32) >= tau) saturated = true;
+            for (int o = 16; o > 0; o >>= 1) mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, o));
+            float sum = 0.f;
+            for (int sg = lane; sg < nseg; sg += 32) {
+                const float4 q = rst[sg];
+                sum += q.y * expf(q.x - mx);
             }
+#pragma unroll
+            for (int o = 16; o > 0; o >>= 1) sum += __shfl_xor_sync(0xffffffffu, sum, o);
+            const float ls = logf(sum);
+            // selection keys: (orderable lp << 16) | (0xFFFF - position in the list)
+            for (int i = lane; i < per_row; i += 32) {
+                const unsigned long long c = mycand[i];
+                uint32_t key = 0u;
+                if (c) {
+                    const bf16 lp = __float2bfloat16(__bfloat162float(bf16_from_orderable(static_cast<uint32_t>(c >> 32))) - mx - ls);
+                    key = (bf16_orderable(lp) << 16) | static_cast<uint32_t>(0xFFFF - i);
+                }
+                mysel[i] = key;
+            }
+            __syncwarp();
+            uint32_t got = warp_select(mysel, per_row, k, lane);
+            // threshold = the row's k-th best lp.  A segment whose own k-th candidate still reaches it may hide further
+            // entries of the threshold bucket (with lower indices): re-select such a row exactly.
+            const uint32_t kth = __shfl_sync(0xffffffffu, got, k - 1);
+            const uint32_t tau = kth >> 16;
+            bool saturated = false;
+            for (int sg = lane; sg < nseg; sg += 32) {
+                const uint32_t xk = __float_as_uint(rst[sg].z);
+                if (kth != 0u && xk != 0u) {
+                    const bf16 lp = __float2bfloat16(__bfloat162float(bf16_from_orderable(xk)) - mx - ls);
+                    if (bf16_orderable(lp) >= tau) saturated = true;
+                }
+            }
+            bf16 my_lp = __float2bfloat16(0.f);
+            int my_idx = 0;
             if (__any_sync(0xffffffffu, saturated)) {
                 // k rounds of "largest key below the previous pick" over the whole logit row
                 const bf16* x = logits + static_cast<size_t>(r + row0) * ld;
-                unsigned long long prev = ~0ull;
-                got = 0ull;
+                unsigned long long prev = ~0ull, mine64 = 0ull;
                 for (int round = 0; round < k; ++round) {
                     unsigned long long best = 0ull;
                     for (int i = lane; i < vocab; i += 32) {
@@ -284,19 +267,25 @@ __global__ void draft_level_kernel(DraftTreeState st, const bf16* __restrict__ l
                         if (key < prev && key > best) best = key;
                     }
                     best = warp_max_u64(best);
-                    if (lane == round) got = best;
+                    if (lane == round) mine64 = best;
                     prev = best;
                 }
+                if (mine64) {
+                    my_idx = key_index(mine64);
+                    my_lp = __float2bfloat16(__bfloat162float(x[my_idx]) - mx - ls);
+                }
+            } else if (got) {
+                const unsigned long long c = mycand[0xFFFF - (got & 0xFFFFu)];
+                my_idx = key_index(c);
+                my_lp = __float2bfloat16(__bfloat162float(bf16_from_orderable(static_cast<uint32_t>(c >> 32))) - mx - ls);
             }
             if (lane < k) {
-                const int idx = got ? key_index(got) : 0;
-                const bf16 lp = __float2bfloat16(__bfloat162float(logits[static_cast<size_t>(r + row0) * ld + idx]) - mx - ls);
-                s_val[r * k + lane] = lp;
-                s_pos[r * k + lane] = idx;
+                s_val[r * k + lane] = my_lp;
+                s_pos[r * k + lane] = my_idx;
             }
         }
+        __syncthreads();
     }
-    __syncthreads();
 
     if (level == 0) {
         if (threadIdx.x < k) {
@@ -433,7 +422,7 @@ int draft_num_segments(int vocab) { return ceil_div(vocab, SEG); }
 size_t draft_scan_workspace_bytes(int rows, int vocab, int k) {
     const int nseg = draft_num_segments(vocab);
     (void)rows;
-    return static_cast<size_t>(32) * nseg * (sizeof(float2) + static_cast<size_t>(k) * sizeof(unsigned long long)) + 1024;
+    return static_cast<size_t>(32) * nseg * (sizeof(float4) + static_cast<size_t>(k) * sizeof(unsigned long long)) + 1024;
 }  // the first word is the level kernel's ticket and must be zero before the first launch
 
 void launch_draft_topk_expand(const DraftTreeState& st, const bf16* logits, int ld, int vocab, int level,
@@ -447,19 +436,23 @@ void launch_draft_topk_expand(const DraftTreeState& st, const bf16* logits, int 
     CPM_REQUIRE(nseg <= 128, "draft: vocabulary larger than 262144 entries");
     // workspace: [ticket | statistics 32 x nseg | candidates 32 x nseg x k]; the ticket is zero between launches
     unsigned* ticket = reinterpret_cast<unsigned*>(scan_ws);
-    float2* stats = reinterpret_cast<float2*>(reinterpret_cast<uint8_t*>(scan_ws) + 256);
+    float4* stats = reinterpret_cast<float4*>(reinterpret_cast<uint8_t*>(scan_ws) + 256);
     unsigned long long* cand = reinterpret_cast<unsigned long long*>(
-        reinterpret_cast<uint8_t*>(stats) + align_up(static_cast<int64_t>(32) * nseg * sizeof(float2), 256));
-    const size_t shmem = static_cast<size_t>(SCAN_THREADS / 32) * nseg * k * sizeof(unsigned long long);
+        reinterpret_cast<uint8_t*>(stats) + align_up(static_cast<int64_t>(32) * nseg * sizeof(float4), 256));
+    // the last CTA takes the rows in groups whose candidate lists (8 + 4 bytes per entry) fit its shared memory
+    const size_t per_row_bytes = static_cast<size_t>(nseg) * k * (sizeof(unsigned long long) + sizeof(uint32_t));
+    CPM_REQUIRE(nseg * k <= 65535, "draft: candidate list too long for 16-bit positions");
+    CPM_REQUIRE(per_row_bytes <= 160 * 1024, "draft: a row's candidate list is too large for one CTA");
+    const int group_rows = static_cast<int>(std::max<size_t>(1, std::min<size_t>(rows, (160 * 1024) / per_row_bytes)));
+    const size_t shmem = group_rows * per_row_bytes;
     static size_t configured = 0;
-    if (shmem > 24 * 1024 && shmem > configured) {   // the kernel also has 22 KB of static shared memory
-        CPM_REQUIRE(shmem <= 200 * 1024, "draft: candidate lists too large for one CTA");
+    if (shmem > 24 * 1024 && shmem > configured) {   // the kernel also has about 12 KB of static shared memory
         CUDA_CHECK(cudaFuncSetAttribute(draft_level_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize,
-                                        static_cast<int>(shmem)));
-        configured = shmem;
+                                        static_cast<int>(160 * 1024)));
+        configured = 160 * 1024;
     }
     launch_kernel(draft_level_kernel, dim3(nseg, rows), dim3(SCAN_THREADS), shmem, s, st, logits, ld, vocab, nseg, stats, cand,
-                  ticket, level, last_row_ptr);
+                  ticket, level, last_row_ptr, group_rows);
     if (hid_out != nullptr) {
         launch_kernel(gather_rows_kernel, dim3(k), dim3(128), 0, s, h_rows, h_ld, static_cast<const int32_t*>(st.fr_src),
                       hid_out, hid_ld, hidden);

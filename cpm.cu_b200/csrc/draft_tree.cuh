@@ -61,6 +61,7 @@ struct FixupArgs {
     bf16* prev_embed = nullptr;           // [max_accept, hidden]
     int32_t* eagle_pos = nullptr;         // [max_accept] = cache_length + i
     int hidden = 0;                       // 0: caches only (no hidden-state gather, no embeddings)
+    int prev_ld = 0;                      // row stride of prev_hidden / prev_embed in elements (0 = hidden)
 };
 // One launch: acceptance (every CTA recomputes it) + fix-up; io.pred / io.result are written by the CTA that
 // is counted last.  cache_rows: rows each cache holds (compaction beyond it is skipped and flagged).

@@ -310,8 +310,8 @@ int Engine::init_storage() {
     if (has_eagle_) {
         tree_.token_id_remap = (draft_vocab_ != mc_.vocab) ? token_id_remap_ : nullptr;
         const int H = mc_.hidden, k = ec_.topk, rc = catchup_rows_;
-        build_layer_plans(eplan_level_, elayer_, ekv_, k, attn_splits_for(k));
-        build_layer_plans(eplan_catchup_, elayer_, ekv_, rc, attn_splits_for(rc));
+        build_draft_plans(eplan_level_, k, attn_splits_for(k));
+        build_draft_plans(eplan_catchup_, rc, attn_splits_for(rc));
         eplan_level_.attn.window = ec_.window;
         eplan_catchup_.attn.window = ec_.window;
         if (ec_.quant) {
@@ -473,6 +473,16 @@ void Engine::build_layer_plans(LayerPlans& lp, const LayerWeights& w, const KVLa
                              mc_.hq * d, attn_ws_o_, attn_ws_ml_);
 }
 
+void Engine::build_draft_plans(LayerPlans& lp, int rows, int attn_splits) {
+    build_layer_plans(lp, elayer_, ekv_, rows, attn_splits);
+    if (!ec_.use_attn_norm) {
+        const int H = mc_.hidden, sms = runtime().num_sms;
+        lp.qkv = elayer_.qkv_q != nullptr
+                     ? checked(make_linear_plan_w4(e_x_, rows, elayer_.qkv_q, rows, qkv_dim_, H, qkv_, qkv_dim_, gemm_ws_, tickets_, sms))
+                     : checked(make_linear_plan(e_x_, rows, elayer_.qkv, rows, qkv_dim_, H, qkv_, qkv_dim_, nullptr, gemm_ws_, tickets_, sms));
+    }
+}
+
 ForwardPlans& Engine::target_plans(int rows) {
     auto it = plans_.find(rows);
     if (it != plans_.end()) return *it->second;
@@ -496,7 +506,7 @@ void Engine::layer_forward(LayerPlans& lp, const LayerWeights& w, const KVLayer&
         else launch_rms_norm(x, H, w.ln_attn, normed_, H, rows, H, mc_.eps, s);
     } else {
         if (pending) launch_add_scaled(x, x, pending, pending_scale, rows, H, s);
-        copy_rows(normed_, H, x, H, rows, H, s);
+        // (only the draft layer runs without a first norm; its q/k/v plan reads x directly: build_draft_plans)
     }
     launch_linear(lp.qkv, s);
     launch_rope_append(qkv_, rows, mc_.hq, mc_.hkv, mc_.head_dim, inv_freq_, c.pos, c.pos_base, c.pos_off, c.pos_step,
@@ -666,7 +676,7 @@ void Engine::draft_first(int history, cudaStream_t s) {
     }
     CUDA_CHECK(cudaMemcpyAsync(st_ + 7, &history, sizeof(int), cudaMemcpyHostToDevice, s));
     LayerPlans lp;
-    build_layer_plans(lp, elayer_, ekv_, P, 1);
+    build_draft_plans(lp, P, 1);
     RowCtx c;
     c.rows = P;
     c.pos = eagle_pos_;
@@ -684,10 +694,7 @@ void Engine::draft_catchup(cudaStream_t s) {
     if (ec_.use_input_norm) {
         launch_rms_norm(prev_embed_, H, in_norm1_, e_in_, ein_ld(), rc, H, mc_.eps, s);
         launch_rms_norm(prev_hidden_, H, in_norm2_, ein_hidden(), ein_ld(), rc, H, mc_.eps, s);
-    } else {
-        copy_rows(e_in_, ein_ld(), prev_embed_, H, rc, H, s);
-        copy_rows(ein_hidden(), ein_ld(), prev_hidden_, H, rc, H, s);
-    }
+    }  // without input norms the fix-up of the previous step wrote the rows straight into the fc input
     draft_fc(rc, fc_plan_catchup_, fc2_plan_catchup_, s);
     // layer_forward takes kv_len for both append and attention; the catch-up needs
     // different bases (append at L-n, attend over L), so split it here.
@@ -695,7 +702,6 @@ void Engine::draft_catchup(cudaStream_t s) {
         LayerPlans& lp = eplan_catchup_;
         const LayerWeights& w = elayer_;
         if (ec_.use_attn_norm) launch_rms_norm(e_x_, H, w.ln_attn, normed_, H, rc, H, mc_.eps, s);
-        else copy_rows(normed_, H, e_x_, H, rc, H, s);
         launch_linear(lp.qkv, s);
         launch_rope_append(qkv_, rc, mc_.hq, mc_.hkv, mc_.head_dim, inv_freq_, eagle_pos_, nullptr, 0, 0, ekv_.k, ekv_.v,
                            st_ + S_BASE, 0, st_ + S_NPREV, budget_, s);
@@ -815,10 +821,13 @@ void Engine::accept_and_fix(int T, int32_t* pred, const int32_t* gt, const int32
     f.kv_dim = mc_.hkv * mc_.head_dim;
     f.max_accept = has_eagle_ ? catchup_rows_ : 1;
     f.norm_out = norm_out_;
-    f.prev_hidden = prev_hidden_;
+    // without input norms the next catch-up pass takes these rows as its fc input as they are: write them there
+    const bool direct = has_eagle_ && !ec_.use_input_norm;
+    f.prev_ld = direct ? ein_ld() : mc_.hidden;
+    f.prev_hidden = direct ? ein_hidden() : prev_hidden_;
     f.embed_table = embed_;
     f.embed_scale = mc_.scale_embed;
-    f.prev_embed = prev_embed_;
+    f.prev_embed = direct ? e_in_ : prev_embed_;
     f.eagle_pos = eagle_pos_;
     f.hidden = mc_.hidden;
     launch_accept_fixup(io, f, budget_, s);

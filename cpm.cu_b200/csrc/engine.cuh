@@ -138,6 +138,8 @@ private:
     // ---- building blocks
     void build_layer_plans(LayerPlans& lp, const LayerWeights& w, const KVLayer& kv, int rows, int attn_splits);
     ForwardPlans& target_plans(int rows);
+    // plans of the draft layer; without an attention norm its q/k/v GEMM reads the fc output in place
+    void build_draft_plans(LayerPlans& lp, int rows, int attn_splits);
     // sparse_layer >= 0: target layer with InfLLM-v2 block selection (index into the compressed caches)
     void layer_forward(LayerPlans& lp, const LayerWeights& w, const KVLayer& kv, const RowCtx& c, bf16* x,
                        const bf16* pending, float pending_scale, bool first_norm, float res_scale, cudaStream_t s,

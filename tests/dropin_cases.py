@@ -1,6 +1,7 @@
 """Tiny seeded models as on-disk checkpoints (Hugging Face style directories written by baseline/synth_ckpt.py):
 the cases that the drop-in tests feed, unchanged, to the reference project's own CUDA build and to this library,
 and from which tests/golden/make_ref_generate_golden.py records what the reference generated."""
+import math
 import os
 import sys
 
@@ -39,6 +40,14 @@ CASES = {
                   fc_gain=200.0, chunk=256, quant=True),
     "quant_draft": dict(cfg="q", eagle=dict(num_iter=4, topk=4, tree_size=16, minicpm4_variant=True), seed=13, prompt=120,
                         gen=36, layer_scale=0.6, fc_gain=200.0, chunk=256, quant=True, quant_draft=True),
+    # muP-scaled checkpoints (MiniCPM style: scale_emb, dim_model_base -> LM-head input scale, scale_depth -> residual
+    # scale).  The plain drafter scales its LM-head input like the target; the MiniCPM4 drafter does not
+    # (src/model/minicpm4/minicpm4_eagle.cuh:26,95-99 holds the head as a plain Linear) and scales its residual.
+    "mup_plain": dict(cfg="a", eagle=dict(num_iter=4, topk=4, tree_size=16), seed=15, prompt=110, gen=36, layer_scale=0.6,
+                      fc_gain=40.0, chunk=256, mup=dict(scale_emb=6.0, dim_model_base=128, scale_depth=1.2)),
+    "mup_minicpm4": dict(cfg="c", eagle=dict(num_iter=3, topk=5, tree_size=12, use_input_norm=True, use_attn_norm=True,
+                                             minicpm4_variant=True), seed=16, prompt=110, gen=36, layer_scale=0.3,
+                         fc_gain=8.0, chunk=256, mup=dict(scale_emb=6.0, dim_model_base=512, scale_depth=1.4)),
     "headline_tree": dict(cfg="c", eagle=dict(num_iter=6, topk=10, tree_size=60), seed=12, prompt=300, gen=48,
                           layer_scale=0.3, fc_gain=8.0, chunk=512),
 }
@@ -47,8 +56,17 @@ CASES = {
 def case_parts(name):
     """(OracleConfig, EagleOracleConfig, weights, eagle weights, remap or None, prompt ids) of a case."""
     c = CASES[name]
-    cfg = OracleConfig(dtype="bf16", **CFGS[c["cfg"]])
-    eagle = EagleOracleConfig(**c["eagle"])
+    shape = CFGS[c["cfg"]]
+    mup = c.get("mup")
+    scales, eagle_kw = {}, dict(c["eagle"])
+    if mup:
+        # the constructors' arithmetic, cpmcu/llm.py:63-67 and cpmcu/speculative/eagle.py:43
+        scales = dict(scale_embed=mup["scale_emb"], scale_lmhead=mup["dim_model_base"] / shape["hidden"],
+                      scale_residual=mup["scale_depth"] / math.sqrt(shape["layers"]))
+        if eagle_kw.get("minicpm4_variant"):
+            eagle_kw["residual_scale"] = mup["scale_depth"] / math.sqrt(shape["layers"] + 1)
+    cfg = OracleConfig(dtype="bf16", **shape, **scales)
+    eagle = EagleOracleConfig(**eagle_kw)
     w, ew = make_weights(cfg, c["seed"], eagle, layer_scale=c["layer_scale"], fc_mode="embed", fc_gain=c["fc_gain"])
     remap = None
     if eagle.frspec_vocab:
@@ -91,6 +109,8 @@ def write_case(name, root):
         eagle_config = {"quantization_config": {"group_size": 128, "bits": 4}}
     if remap is not None:
         etensors["token_id_remap"] = torch.from_numpy(remap)
+    if c.get("mup"):
+        extra = dict(extra or {}, **c["mup"])
     config = synth_ckpt.base_config(cfg.vocab, cfg.layers, cfg.hidden, cfg.inter, cfg.hq, cfg.hkv, cfg.head_dim, cfg.eps,
                                     cfg.rope_theta, extra)
     base_dir, eagle_dir = os.path.join(root, name, "base"), os.path.join(root, name, "eagle")

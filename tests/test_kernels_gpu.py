@@ -393,3 +393,76 @@ def test_verify_and_compact_bit_exact(T, seed):
     for j in range(num_caches):
         ref = otree.compact_rows(caches[j].clone().view(torch.int16).numpy(), L, path)
         assert np.array_equal(d_caches[j].cpu().view(torch.int16).numpy(), ref)
+
+
+@pytest.mark.parametrize("T,seed,scale,prev_rows", [(16, 0, 1.0, 5), (60, 1, 1.0, 7), (60, 2, 12.0, 7), (64, 3, 1.0, 16), (60, 5, 0.5, 3)])
+def test_accept_fixup_gathers_hidden_states_embeddings_and_positions(T, seed, scale, prev_rows):
+    """The whole one-launch tail of a step (reference MiniCPM4EagleImpl::verify, src/model/minicpm4/
+    minicpm4_eagle.cuh:398-418): acceptance, K/V compaction, and for the next draft pass the gather of the target's
+    final-norm rows along the accepted path (remap_hidden, src/model/eagle.cuh:108-115), the embeddings of the emitted
+    tokens (scaled by scale_emb) and their positions; all bit for bit, capped at the drafter's row budget."""
+    from oracle import tree as otree
+    c = C()
+    rng = np.random.default_rng(100 + seed)
+    L, H, V = 70 + seed, 512, 1000
+    masks, parent = random_tree_masks(T, rng)
+    depth = [bin(m).count("1") for m in masks]
+    pos = np.array([L + dd - 1 for dd in depth], dtype=np.int32)
+    ids = rng.integers(0, V, T).astype(np.int32)
+    gt = rng.integers(0, V, T).astype(np.int32)
+    for i in range(1, T):
+        if rng.random() < 0.7:
+            ids[i] = gt[parent[i]]
+    num_caches, kv_dim, rows = 4, 256, L + T + 8
+    g = torch.Generator().manual_seed(seed)
+    caches = [torch.randn(rows, kv_dim, generator=g).to(torch.bfloat16) for _ in range(num_caches)]
+    d_caches = [dev(x) for x in caches]
+    ptrs = dev(torch.tensor([x.data_ptr() for x in d_caches], dtype=torch.int64))
+    norm_out = dev(torch.randn(64, H, generator=g).to(torch.bfloat16))
+    embed = dev(torch.randn(V, H, generator=g).to(torch.bfloat16))
+    prev_hidden = torch.full((16, H), 7.0, dtype=torch.bfloat16, device="cuda")
+    prev_embed = torch.full((16, H), 7.0, dtype=torch.bfloat16, device="cuda")
+    eagle_pos = torch.full((16,), -1, dtype=torch.int32, device="cuda")
+    d_ids = dev(torch.tensor(ids))
+    result = torch.zeros(18, dtype=torch.int32, device="cuda")
+    mask_t = dev(torch.tensor(np.array(masks, dtype=np.uint64).view(np.int64)))
+    par_t = dev(torch.tensor(np.array(parent, dtype=np.int32)))
+    gt_t, pos_t, len_t = dev(torch.tensor(gt)), dev(torch.tensor(pos)), dev(torch.tensor([L], dtype=torch.int32))
+    c.call("cpmcu_accept_fixup", T, ptr(d_ids), ptr(gt_t), ptr(pos_t), ptr(len_t), ptr(mask_t), ptr(par_t), ptr(ptrs),
+           num_caches, kv_dim, rows, prev_rows, H, ptr(norm_out), ptr(prev_hidden), ptr(embed), scale, ptr(prev_embed),
+           ptr(eagle_pos), ptr(result))
+    n, best, path = otree.verify(ids, gt, pos, L, masks, parent)
+    tokens = otree.emitted_tokens(gt, path)
+    res = result.cpu().numpy()
+    assert res[0] == n and res[1] == best and list(res[2:2 + n]) == path
+    assert d_ids[:n].cpu().tolist() == tokens
+    m = min(n, prev_rows)                      # the drafter keeps at most its row budget
+    assert torch.equal(prev_hidden[:m], norm_out[torch.tensor(path[:m], device="cuda")])
+    want_emb = embed[torch.tensor(tokens[:m], device="cuda")]
+    if scale != 1.0:
+        want_emb = (want_emb.float() * scale).to(torch.bfloat16)
+    assert torch.equal(prev_embed[:m], want_emb)
+    assert eagle_pos[:prev_rows].cpu().tolist() == [L + i for i in range(prev_rows)]
+    assert float(prev_hidden[m:].float().min()) == 7.0 and float(prev_embed[m:].float().min()) == 7.0   # untouched
+    for j in range(num_caches):
+        ref = otree.compact_rows(caches[j].clone().view(torch.int16).numpy(), L, path[:m])
+        assert np.array_equal(d_caches[j].cpu().view(torch.int16).numpy(), ref)
+
+
+def test_accept_fixup_refuses_to_compact_past_the_cache():
+    """cache_rows guards the compaction: rows at or beyond it are not touched and the call reports the overflow."""
+    c = C()
+    T, L = 4, 10
+    caches = [torch.zeros(12, 256, dtype=torch.bfloat16, device="cuda")]
+    ptrs = dev(torch.tensor([caches[0].data_ptr()], dtype=torch.int64))
+    ids = dev(torch.tensor([5, 6, 7, 8], dtype=torch.int32))
+    gt = dev(torch.tensor([6, 7, 8, 9], dtype=torch.int32))          # the chain 0-1-2-3 is accepted: n = 4
+    pos = dev(torch.tensor([10, 11, 12, 13], dtype=torch.int32))
+    mask = dev(torch.tensor([1, 3, 7, 15], dtype=torch.int64))
+    par = dev(torch.tensor([0, 0, 1, 2], dtype=torch.int32))
+    result = torch.zeros(18, dtype=torch.int32, device="cuda")
+    len_t = dev(torch.tensor([L], dtype=torch.int32))
+    with pytest.raises(RuntimeError, match="kernel error flags 8"):
+        c.call("cpmcu_accept_fixup", T, ptr(ids), ptr(gt), ptr(pos), ptr(len_t), ptr(mask), ptr(par), ptr(ptrs), 1, 256, 12,
+               7, 0, None, None, None, 1.0, None, None, ptr(result))
+    assert float(caches[0].float().abs().max()) == 0.0
