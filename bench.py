@@ -58,8 +58,8 @@ WORKLOADS = {
                          "bf16 embeddings / LM head / EAGLE draft, tree 60, "),
     "config5": dict(index=4, w4a16=False, sparse=True, frspec=False,
                     text="configs[4]: config-2 architecture with InfLLM-v2 block-sparse target attention (block 64, "
-                         "top-64 + 1 initial block + 2048-token window), draft window 1024, chunked prefill (2048), "
-                         "tree 60, "),
+                         "top-64 + 1 initial block + 2048-token window), draft window 1024 (drafter input norms on, as the "
+                         "reference's windowed drafter requires), chunked prefill (2048), tree 60, "),
 }
 # Second weight recipe (not a BASELINE.json configuration): decoder-layer matrices shrunk by ACCEPT_LAYER_SCALE and
 # fc = [gain * I | 0], so that the next token is mostly a function of the current one and the 1-layer drafter can
@@ -139,7 +139,7 @@ class ClockSampler(threading.Thread):
 
 
 # ---------------------------------------------------------------------------- synthetic weights
-def iter_weights(seed=1, w4a16=False, frspec=False, accepting=False):
+def iter_weights(seed=1, w4a16=False, frspec=False, accepting=False, input_norm=False):
     """Yields (cls, name, tensor) with cls None (target) or "eagle", tensors on the GPU, in an order both
     loaders accept (token_id_remap before lm_head).  Headline recipe: N(0, 0.02) everywhere, drafter = the
     target's last layer with fc passing the hidden state through (fc1 = 0, fc2 = I, bias 0).  config 4: the
@@ -194,9 +194,10 @@ def iter_weights(seed=1, w4a16=False, frspec=False, accepting=False):
         fc = torch.cat([torch.zeros(H, H, device="cuda"), eye], dim=1)
     yield "eagle", "fc.weight", fc.to(torch.bfloat16)
     yield "eagle", "fc.bias", torch.zeros(H, device="cuda", dtype=torch.bfloat16)
-    if frspec:
-        # the reference takes an FR-Spec vocabulary only on its MiniCPM4 drafter, which it picks when a norm switch
-        # is on (cpmcu/speculative/eagle.py:52-74): config 3 runs with input norms (weights of ones) on both arms
+    if frspec or input_norm:
+        # the reference takes an FR-Spec vocabulary or a draft window only on its MiniCPM4 drafter, which it picks when a
+        # norm switch is on (cpmcu/speculative/eagle.py:52-74): configs 3 and 5 run with input norms (weights of ones)
+        # on both arms
         yield "eagle", "input_norm1.weight", ones
         yield "eagle", "input_norm2.weight", ones
 
@@ -231,7 +232,7 @@ def build_model(device_index, seed=1, w4a16=False, sparse=False, frspec=False, a
         # config 5: InfLLM-v2 target (block 64, top-64 blocks + 1 initial block + local window of 2048 tokens),
         # draft layer with a sliding window of 1024 tokens
         extra = dict(apply_sparse=True, sink_window_size=1, block_window_size=32, sparse_topk_k=64, sparse_switch=8192,
-                     apply_compress_lse=True, eagle_window_size=1024)
+                     apply_compress_lse=True, eagle_window_size=1024, use_input_norm=True)
     if frspec:
         extra["frspec_vocab_size"] = FRSPEC_VOCAB
         extra["use_input_norm"] = True
@@ -240,7 +241,7 @@ def build_model(device_index, seed=1, w4a16=False, sparse=False, frspec=False, a
               dtype=torch.bfloat16, chunk_length=LONG_CHUNK if sparse else PROMPT_LEN, memory_limit=0.8,
               fused_step=True, **extra)
     llm.init_storage()
-    for kind, name, t in iter_weights(seed, w4a16, frspec, accepting):
+    for kind, name, t in iter_weights(seed, w4a16, frspec, accepting, input_norm=sparse):
         llm._load(name, t, cls=kind)
     llm._load("model.rotary_emb.inv_freq", llm._rope_inv_freq(), dtype=torch.float32)
     torch.cuda.empty_cache()
@@ -330,7 +331,7 @@ def summarise(res, workload, peak):
     return out
 
 
-def run_reference_cuda(workload, gen_tokens=256, timeout_s=900):
+def run_reference_cuda(workload, gen_tokens=256, timeout_s=900, cuda_graph=True):
     """The reference project's own CUDA build on this GPU (baseline B1): writes the workload's synthetic
     checkpoint as safetensors + config.json, runs baseline/ref_cuda.py in a process of its own (the reference's
     LLM_with_eagle: init_storage, load_from_hf, generate with cuda_graph=True, one chunk), and returns what its
@@ -354,7 +355,7 @@ def run_reference_cuda(workload, gen_tokens=256, timeout_s=900):
         return {"build": "ok", "run": "skipped", "reason": "no scratch space for a 17 GB checkpoint"}
     try:
         base_dir, eagle_dir = os.path.join(root, "base"), os.path.join(root, "eagle")
-        gen = list_split(iter_weights(1, w["w4a16"], w["frspec"], False))
+        gen = list_split(iter_weights(1, w["w4a16"], w["frspec"], False, input_norm=w["sparse"]))
         synth_ckpt.write_checkpoint(base_dir, eagle_dir, hf_config_dict(w["w4a16"]), gen[0], gen[1])
         torch.cuda.empty_cache()
         prompt_len = LONG_PROMPT_LEN if w["sparse"] else PROMPT_LEN
@@ -370,7 +371,9 @@ def run_reference_cuda(workload, gen_tokens=256, timeout_s=900):
         if w["frspec"]:
             cmd += ["--frspec", str(FRSPEC_VOCAB), "--input-norm"]
         if w["sparse"]:
-            cmd += ["--sparse", "--window", "1024"]
+            cmd += ["--sparse", "--window", "1024", "--input-norm"]   # the draft window needs the MiniCPM4 drafter
+        if not cuda_graph:
+            cmd.append("--no-graph")
         env = dict(os.environ)
         env.pop("CPMCU_MAX_TOKENS", None)
         proc = subprocess.run(cmd, capture_output=True, text=True, timeout=timeout_s, env=env)
@@ -533,7 +536,10 @@ def run_ours(args):
             line["speedup_vs_reference_cuda"] = {"e2e": line["e2e"]["value"] / ref["tokens_per_s"],
                                                  "target": 2.0, "met": line["e2e"]["value"] / ref["tokens_per_s"] >= 2.0}
         if not args.no_cpu_baseline:
-            line["cpu_baseline"] = cpu_step_baseline(line["mean_accept_length"])
+            try:
+                line["cpu_baseline"] = cpu_step_baseline(line["mean_accept_length"])
+            except Exception as e:
+                line["cpu_baseline"] = {"error": repr(e)[:300]}
     elif rank == 0 and world == 1 and not args.no_cpu_baseline and not args.no_extras:
         line["cpu_baseline"] = cpu_step_baseline(line["mean_accept_length"])
     if rank == 0:

@@ -63,10 +63,16 @@ extern "C" {
 
 const char* cpmcu_last_error(void) { return g_error.c_str(); }
 
-int cpmcu_init_base_model(float memory_limit, int vocab_size, int num_hidden_layers, int hidden_size,
-                          int intermediate_size, int num_attention_heads, int num_key_value_heads, int head_dim,
-                          float rms_norm_eps, int torch_dtype, int chunk_length, float scale_embed,
-                          float scale_lmhead, float scale_residual) {
+namespace {
+struct SparseArgs {
+    int sink_window_size, block_window_size, sparse_topk_k, sparse_switch, apply_compress_lse;
+};
+
+// The four target initialisers differ only in two switches: int4 linears (group_size > 0) and block selection.
+int init_target(float memory_limit, int vocab_size, int num_hidden_layers, int hidden_size, int intermediate_size,
+                int num_attention_heads, int num_key_value_heads, int head_dim, float rms_norm_eps, int torch_dtype,
+                int chunk_length, float scale_embed, float scale_lmhead, float scale_residual, int group_size,
+                const SparseArgs* sp) {
     return guarded([&] {
         require_bf16(torch_dtype);
         ModelConfig mc;
@@ -83,10 +89,37 @@ int cpmcu_init_base_model(float memory_limit, int vocab_size, int num_hidden_lay
         mc.scale_embed = scale_embed;
         mc.scale_lmhead = scale_lmhead;
         mc.scale_residual = scale_residual;
+        if (group_size > 0) {
+            mc.w4a16 = true;
+            mc.group_size = group_size;
+        }
+        if (sp != nullptr) {
+            CPM_REQUIRE(sp->sink_window_size >= 0 && sp->block_window_size >= 1 && sp->sparse_topk_k >= 1 &&
+                            sp->sparse_switch >= 0,
+                        "init_minicpm4_model: bad block-selection arguments");
+            CPM_REQUIRE(num_key_value_heads >= 1 && num_attention_heads / num_key_value_heads <= 16,
+                        "init_minicpm4_model: at most 16 query heads per KV head");
+            mc.sparse.enabled = true;
+            mc.sparse.sink_blocks = sp->sink_window_size;
+            mc.sparse.window_blocks = sp->block_window_size;
+            mc.sparse.topk = sp->sparse_topk_k;
+            mc.sparse.sparse_switch = sp->sparse_switch;
+            mc.sparse.compress_lse = sp->apply_compress_lse != 0;
+        }
         g_engine.reset();  // one model per process, like the reference's global
         g_engine = std::make_unique<Engine>(mc);
         return 0;
     });
+}
+}  // namespace
+
+int cpmcu_init_base_model(float memory_limit, int vocab_size, int num_hidden_layers, int hidden_size,
+                          int intermediate_size, int num_attention_heads, int num_key_value_heads, int head_dim,
+                          float rms_norm_eps, int torch_dtype, int chunk_length, float scale_embed,
+                          float scale_lmhead, float scale_residual) {
+    return init_target(memory_limit, vocab_size, num_hidden_layers, hidden_size, intermediate_size, num_attention_heads,
+                       num_key_value_heads, head_dim, rms_norm_eps, torch_dtype, chunk_length, scale_embed, scale_lmhead,
+                       scale_residual, 0, nullptr);
 }
 
 int cpmcu_init_minicpm4_model(float memory_limit, int vocab_size, int num_hidden_layers, int hidden_size,
@@ -94,36 +127,10 @@ int cpmcu_init_minicpm4_model(float memory_limit, int vocab_size, int num_hidden
                               int head_dim, float rms_norm_eps, int torch_dtype, int chunk_length,
                               float scale_embed, float scale_lmhead, float scale_residual, int sink_window_size,
                               int block_window_size, int sparse_topk_k, int sparse_switch, int apply_compress_lse) {
-    return guarded([&] {
-        require_bf16(torch_dtype);
-        CPM_REQUIRE(sink_window_size >= 0 && block_window_size >= 1 && sparse_topk_k >= 1 && sparse_switch >= 0,
-                    "init_minicpm4_model: bad block-selection arguments");
-        CPM_REQUIRE(num_attention_heads / num_key_value_heads <= 16,
-                    "init_minicpm4_model: at most 16 query heads per KV head");
-        ModelConfig mc;
-        mc.memory_limit = memory_limit;
-        mc.vocab = vocab_size;
-        mc.layers = num_hidden_layers;
-        mc.hidden = hidden_size;
-        mc.inter = intermediate_size;
-        mc.hq = num_attention_heads;
-        mc.hkv = num_key_value_heads;
-        mc.head_dim = head_dim;
-        mc.eps = rms_norm_eps;
-        mc.chunk_length = chunk_length;
-        mc.scale_embed = scale_embed;
-        mc.scale_lmhead = scale_lmhead;
-        mc.scale_residual = scale_residual;
-        mc.sparse.enabled = true;
-        mc.sparse.sink_blocks = sink_window_size;
-        mc.sparse.window_blocks = block_window_size;
-        mc.sparse.topk = sparse_topk_k;
-        mc.sparse.sparse_switch = sparse_switch;
-        mc.sparse.compress_lse = apply_compress_lse != 0;
-        g_engine.reset();
-        g_engine = std::make_unique<Engine>(mc);
-        return 0;
-    });
+    const SparseArgs sp = {sink_window_size, block_window_size, sparse_topk_k, sparse_switch, apply_compress_lse};
+    return init_target(memory_limit, vocab_size, num_hidden_layers, hidden_size, intermediate_size, num_attention_heads,
+                       num_key_value_heads, head_dim, rms_norm_eps, torch_dtype, chunk_length, scale_embed, scale_lmhead,
+                       scale_residual, 0, &sp);
 }
 
 int cpmcu_init_w4a16_gptq_marlin_base_model(float memory_limit, int vocab_size, int num_hidden_layers,
@@ -131,29 +138,12 @@ int cpmcu_init_w4a16_gptq_marlin_base_model(float memory_limit, int vocab_size, 
                                             int num_key_value_heads, int head_dim, float rms_norm_eps,
                                             int group_size, int torch_dtype, int chunk_length, float scale_embed,
                                             float scale_lmhead, float scale_residual) {
-    return guarded([&] {
-        require_bf16(torch_dtype);
-        ModelConfig mc;
-        mc.memory_limit = memory_limit;
-        mc.vocab = vocab_size;
-        mc.layers = num_hidden_layers;
-        mc.hidden = hidden_size;
-        mc.inter = intermediate_size;
-        mc.hq = num_attention_heads;
-        mc.hkv = num_key_value_heads;
-        mc.head_dim = head_dim;
-        mc.eps = rms_norm_eps;
-        mc.chunk_length = chunk_length;
-        mc.scale_embed = scale_embed;
-        mc.scale_lmhead = scale_lmhead;
-        mc.scale_residual = scale_residual;
-        mc.w4a16 = true;
-        mc.group_size = group_size;
-        g_engine.reset();
-        g_engine = std::make_unique<Engine>(mc);
-        return 0;
-    });
+    if (group_size <= 0) return guarded([&]() -> int { throw std::invalid_argument("cpmcu_b200: W4A16: only group_size 128 is supported"); });
+    return init_target(memory_limit, vocab_size, num_hidden_layers, hidden_size, intermediate_size, num_attention_heads,
+                       num_key_value_heads, head_dim, rms_norm_eps, torch_dtype, chunk_length, scale_embed, scale_lmhead,
+                       scale_residual, group_size, nullptr);
 }
+
 int cpmcu_init_w4a16_gptq_marlin_minicpm4_model(float memory_limit, int vocab_size, int num_hidden_layers,
                                                 int hidden_size, int intermediate_size, int num_attention_heads,
                                                 int num_key_value_heads, int head_dim, float rms_norm_eps,
@@ -162,20 +152,11 @@ int cpmcu_init_w4a16_gptq_marlin_minicpm4_model(float memory_limit, int vocab_si
                                                 int block_window_size, int sparse_topk_k, int sparse_switch,
                                                 int apply_compress_lse) {
     // the W4A16 target with InfLLM-v2 block selection: both features are independent in the engine
-    const int rc = cpmcu_init_minicpm4_model(memory_limit, vocab_size, num_hidden_layers, hidden_size, intermediate_size,
-                                             num_attention_heads, num_key_value_heads, head_dim, rms_norm_eps, torch_dtype,
-                                             chunk_length, scale_embed, scale_lmhead, scale_residual, sink_window_size,
-                                             block_window_size, sparse_topk_k, sparse_switch, apply_compress_lse);
-    if (rc != 0) return rc;
-    return guarded([&] {
-        CPM_REQUIRE(group_size == 128, "W4A16: only group_size 128 is supported");
-        ModelConfig mc = engine().config();
-        mc.w4a16 = true;
-        mc.group_size = group_size;
-        g_engine.reset();
-        g_engine = std::make_unique<Engine>(mc);
-        return 0;
-    });
+    if (group_size <= 0) return guarded([&]() -> int { throw std::invalid_argument("cpmcu_b200: W4A16: only group_size 128 is supported"); });
+    const SparseArgs sp = {sink_window_size, block_window_size, sparse_topk_k, sparse_switch, apply_compress_lse};
+    return init_target(memory_limit, vocab_size, num_hidden_layers, hidden_size, intermediate_size, num_attention_heads,
+                       num_key_value_heads, head_dim, rms_norm_eps, torch_dtype, chunk_length, scale_embed, scale_lmhead,
+                       scale_residual, group_size, &sp);
 }
 
 int cpmcu_init_eagle_model(int num_layers, int num_iter, int topk_per_iter, int tree_size, int torch_dtype) {

@@ -19,7 +19,7 @@
 namespace {
 
 constexpr int SEG = 2048;          // vocabulary entries per CTA in the scan kernels
-constexpr int SCAN_THREADS = 256;  // SEG / 8 entries per thread
+constexpr int SCAN_THREADS = 512;  // 4 entries per thread; 16 warps, so the last CTA takes up to 16 rows in one pass
 
 // Order-preserving key: larger key == earlier in (value desc, index asc) order.
 __device__ __forceinline__ uint32_t bf16_orderable(bf16 v) {

@@ -160,7 +160,7 @@ def bench_tail(iters=5):
         C.call("cpmcu_draft_tree_from_logits", p(logits), V, k, it, T, None, p(cl), p(ids), p(pos), p(mask), p(par), p(tv),
                p(tp), p(tpar))
     print(f"draft tree from logits V={V} k={k} iters={it} T={T}: {(time.time() - t0) / iters * 1e6:.0f} us per call "
-          f"(host clock, {3 * it + 1} launches)", flush=True)
+          f"(host clock, {it + 1} launches)", flush=True)
     rows, kvd, ncache = 4352, 256, 64
     caches = [torch.randn(rows, kvd, device="cuda", generator=g).to(torch.bfloat16) for _ in range(ncache)]
     cptr = torch.tensor([c.data_ptr() for c in caches], dtype=torch.int64, device="cuda")

@@ -60,14 +60,30 @@ def assert_sparse_stream_matches(got, want, steps, what):
     print(f"BRANCH {what}: streams identical ({n} tokens)")
 
 
-@pytest.mark.parametrize("which,iters,topk,tree", [("a", 4, 4, 16), ("b", 3, 5, 12)])
+@pytest.mark.parametrize("which,iters,topk,tree", [("a", 4, 4, 16), ("b", 3, 5, 12), ("headline", 6, 10, 60)])
 def test_first_step_tree_logits_and_accept(which, iters, topk, tree):
+    """Prefill logits, the draft tree, the verify logits on the library's own tree, acceptance and fix-up against the
+    oracle.  "headline" is ONE target layer and the drafter at the width of the 8B configuration (hidden 4096,
+    32 q / 2 kv heads, FFN 16384, vocabulary 73448) with the headline tree (6 x top-10, 60 nodes) over a 4096-token
+    prompt: every GEMM, the attention and the draft level run at the shapes the benchmark times."""
+    import os
+
     import cpmcu.C as C
     from oracle import tree as otree
-    cfg = tiny_configs(which)
+    from oracle.model import OracleConfig
+    if which == "headline":
+        cfg = OracleConfig(vocab=73448, layers=1, hidden=4096, inter=16384, hq=32, hkv=2, head_dim=128, dtype="bf16")
+        os.environ["CPMCU_MAX_TOKENS"] = "8192"
+        n_prompt, chunk, budget = 4096, 4096, 4352
+    else:
+        cfg = tiny_configs(which)
+        n_prompt, chunk, budget = 150, 256, 1024
     eagle = EagleOracleConfig(num_iter=iters, topk=topk, tree_size=tree)
-    oracle, llm = build_pair(cfg, eagle, seed=1, fused_step=False)
-    prompt = prompt_ids(150, cfg.vocab, 1)
+    try:
+        oracle, llm = build_pair(cfg, eagle, seed=1, fused_step=False, chunk_length=chunk, budget=budget)
+    finally:
+        os.environ["CPMCU_MAX_TOKENS"] = "4096"
+    prompt = prompt_ids(n_prompt, cfg.vocab, 1)
     ids_t = torch.tensor(prompt, device="cuda")
     pos_t = torch.arange(len(prompt), dtype=torch.int32, device="cuda")
     logits = llm.prefill(ids_t, pos_t)
@@ -88,10 +104,27 @@ def test_first_step_tree_logits_and_accept(which, iters, topk, tree):
     g_par = llm.tree_parent.cpu().numpy()
     same_tree = (np.array_equal(g_ids, o_ids) and np.array_equal(g_pos, o_pos) and np.array_equal(g_mask, o_mask)
                  and np.array_equal(g_par[1:], o_par[1:]))
-    if not same_tree:
-        # The draft log-probs went through GEMMs with another summation order, so a candidate may have moved by
-        # one bf16 step.  The tree may then differ only around the selection boundary: every node the oracle
-        # picked and the library did not must score within one bf16 step of the last selected score.
+    # The first two draft levels, whatever happened to the rest of the tree: every child of the root must be one of
+    # the oracle's k best tokens of the level-0 row, and every grandchild one of the k best of its parent's level-1
+    # row, up to one bf16 step of log-probability at the k-th place (the draft logits went through GEMMs with another
+    # summation order).  This is the drafter's LM head + log-softmax + top-k at M = 1 and M = k rows.
+    lv = oracle.trace["levels"]
+    lp0 = np.asarray(lv[0], dtype=np.float64)
+    top0 = [int(t) for t in np.argsort(-lp0, kind="stable")[:topk]]
+    kth0 = float(np.sort(lp0)[-topk])
+    for i in range(1, tree):
+        if g_pos[i] == L + 1:
+            assert lp0[g_ids[i]] >= kth0 - bf16_ulp(kth0) - 1e-9, f"depth-1 node {i} (token {g_ids[i]}) is not a top-{topk} token"
+        elif g_pos[i] == L + 2 and int(g_ids[g_par[i]]) in top0 and len(lv) > 1:
+            row = np.asarray(lv[1][top0.index(int(g_ids[g_par[i]]))], dtype=np.float64)
+            kth = float(np.sort(row)[-topk])
+            assert row[g_ids[i]] >= kth - bf16_ulp(kth) - 1e-9, f"depth-2 node {i} (token {g_ids[i]}) is not a top-{topk} child"
+    if not same_tree and which != "headline":
+        # A candidate may have moved by one bf16 step.  The tree may then differ only around the selection boundary:
+        # every node the oracle picked and the library did not must score within one bf16 step of the last selected
+        # score.  (At the headline width log-probabilities sit near -11, where a bf16 step is 0.0625: cumulative
+        # scores tie in droves, a flip inside a level's frontier re-routes whole subtrees, and only the per-level
+        # check above and the verify pass below are meaningful.)
         sel = np.asarray(oracle.trace["sel"])
         tv = np.asarray(oracle.trace["tree"].tried_val, dtype=np.float64)
         cutoff = float(tv[sel].min())
@@ -101,6 +134,9 @@ def test_first_step_tree_logits_and_accept(which, iters, topk, tree):
             assert abs(float(tv[sel[i - 1]]) - cutoff) <= bf16_ulp(cutoff) + 1e-9, \
                 f"tree differs away from the selection boundary: node {i} scores {tv[sel[i - 1]]}, cutoff {cutoff}"
         print("BRANCH: draft tree differs from the oracle's at the selection boundary (%d nodes)" % len(missing))
+    elif not same_tree:
+        common = len({(int(g_pos[i]), int(g_ids[i])) for i in range(1, tree)} & {(int(o_pos[i]), int(o_ids[i])) for i in range(1, tree)})
+        print("BRANCH: headline-width draft tree shares %d of %d nodes with the oracle's" % (common, tree - 1))
     else:
         print("BRANCH: draft tree identical to the oracle's")
     # structural invariants hold regardless
