@@ -186,6 +186,8 @@ struct LinearPlan {
     int* tickets = nullptr;      // two counters per output tile (pieces counted, readers gone), zero between launches
     int debug = 0;               // timing experiments of -DCPMCU_TUNING builds (CPM_EXPERIMENT); unused otherwise
     int cluster = 0;             // > 0: CTAs per tile, pieces summed inside a thread-block cluster (bf16 path)
+    int wave_tiles = 0;          // several token tiles: tiles computed whole, in waves of `grid` (the rest is cut along K)
+    int tail_grid = 0;           // CTAs that share the tiles after wave_tiles (0 = all)
     // W4A16: when wq is set the weights are 4-bit blocks in the streaming layout (see gemm_w4_umma.cu)
     const void* wq = nullptr;
 };

@@ -20,6 +20,10 @@ struct LinearArgs {
     int* error;
     int debug;  // bench-only switches: 1 = skip the X loads, 2 = skip epilogue stores and the split-K fix-up
     long long* prof;  // bench only (-DCPMCU_GEMM_PROFILE): [grid][4] clock counters, or null
+    // Tiles [0, wave_tiles) are computed whole, tile g + i * gridDim.x by CTA g; total_units counts the k-blocks of
+    // the tiles from wave_tiles on, which the first tail_grid CTAs (0 = all) share in equal contiguous pieces.
+    int wave_tiles = 0;
+    int tail_grid = 0;
 };
 
 #ifdef CPMCU_GEMM_PROFILE
@@ -28,19 +32,80 @@ constexpr bool kGemmProf = true;
 constexpr bool kGemmProf = false;
 #endif
 
+// The work of one CTA: whole tiles wave_tile, wave_tile + stride, ... below wave_tiles, then the k-blocks
+// [u, u_end) of the line of (tile, k-block) units that starts at tile wave_tiles.
 struct SegIter {
     long long u, u_end;
     int kblocks;
+    int wave_tile = 0, wave_tiles = 0, stride = 1;
     __device__ bool next(int& tile, int& kb0, int& kb1) {
+        if (wave_tile < wave_tiles) {
+            tile = wave_tile;
+            kb0 = 0;
+            kb1 = kblocks;
+            wave_tile += stride;
+            return true;
+        }
         if (u >= u_end) return false;
-        tile = static_cast<int>(u / kblocks);
-        kb0 = static_cast<int>(u - static_cast<long long>(tile) * kblocks);
+        const int t = static_cast<int>(u / kblocks);
+        tile = wave_tiles + t;
+        kb0 = static_cast<int>(u - static_cast<long long>(t) * kblocks);
         long long rem = u_end - u;
         kb1 = (kb0 + rem < kblocks) ? static_cast<int>(kb0 + rem) : kblocks;
         u += kb1 - kb0;
         return true;
     }
 };
+
+// Work of CTA g of G.  With wave_tiles = 0 (every launch of a single token tile) this is plain stream-K: the
+// line of all (tile, k-block) units cut into G equal pieces.  Launches with several token tiles run whole tiles
+// in waves first: the CTAs of a wave walk K in step, so tiles that share a weight or an activation slab find it
+// in L2 instead of each fetching it from HBM at a different time; only the last, partial wave is cut along K.
+__device__ __forceinline__ SegIter make_seg_iter(const LinearArgs& a, int g, int G) {
+    SegIter it;
+    it.kblocks = a.kblocks;
+    it.wave_tiles = a.wave_tiles;
+    it.wave_tile = g;
+    it.stride = G;
+    const int gt = a.tail_grid > 0 ? a.tail_grid : G;
+    if (g < gt) {
+        it.u = (a.total_units * g) / gt;
+        it.u_end = (a.total_units * (g + 1)) / gt;
+    } else {
+        it.u = it.u_end = 0;
+    }
+    return it;
+}
+
+// Tile number -> (token tile, feature tile).  Token tiles are taken in bands of RASTER_BAND; inside a band the
+// token tile runs fastest, so the tiles a wave of CTAs works on at one time cover few feature tiles x all token
+// tiles of the band: every weight slab is fetched from HBM once per band and the band's activations stay in L2.
+constexpr int RASTER_BAND = 16;
+__device__ __forceinline__ void tile_to_mn(const LinearArgs& a, int tile, int& m_tile, int& n_tile) {
+    if (a.m_tiles == 1) {
+        m_tile = 0;
+        n_tile = tile;
+        return;
+    }
+    const int band_tiles = RASTER_BAND * a.n_tiles;
+    const int band = tile / band_tiles;
+    const int r = tile - band * band_tiles;
+    int bm = a.m_tiles - band * RASTER_BAND;
+    if (bm > RASTER_BAND) bm = RASTER_BAND;
+    n_tile = r / bm;
+    m_tile = band * RASTER_BAND + (r - n_tile * bm);
+}
+
+// Host side of make_seg_iter for a launch with several token tiles: whole waves of `grid` tiles, and the CTAs
+// that share the rest (pieces of at least eight k-blocks).
+inline void plan_waves(long long tiles, int kblocks, int grid, int& wave_tiles, int& tail_grid) {
+    wave_tiles = static_cast<int>((tiles / grid) * grid);
+    const long long tail_units = (tiles - wave_tiles) * kblocks;
+    long long gt = tail_units / 8;
+    if (gt < 1) gt = 1;
+    if (gt > grid) gt = grid;
+    tail_grid = static_cast<int>(gt);
+}
 
 // CTA that owns work unit u when [0,U) is cut into G pieces starting at floor(g*U/G).
 __device__ __forceinline__ int unit_owner(long long u, long long U, int G) {
@@ -127,8 +192,8 @@ __device__ __forceinline__ void run_epilogue(const LinearArgs& a, SegIter it, ui
     PendingTile pend[2];
     int n_pend = 0;
     while (it.next(tile, kb0, kb1)) {
-        const int m_tile = tile / a.n_tiles;
-        const int n_tile = tile - m_tile * a.n_tiles;
+        int m_tile, n_tile;
+        tile_to_mn(a, tile, m_tile, n_tile);
         const int m_base = m_tile * MT;
         const int n = n_tile * BLOCK_N + row;
         int m_cnt = a.M - m_base;
@@ -178,11 +243,12 @@ __device__ __forceinline__ void run_epilogue(const LinearArgs& a, SegIter it, ui
         if (++acc == acc_stages) { acc = 0; acc_phase ^= 1; }
 
         if (!complete && !CPM_EXPERIMENT(a, 2 | 8)) {
-            const long long tile_u0 = static_cast<long long>(tile) * a.kblocks;
+            const long long tile_u0 = static_cast<long long>(tile - a.wave_tiles) * a.kblocks;
+            const int gt = a.tail_grid > 0 ? a.tail_grid : G;
             PendingTile p;
             p.tile = tile;
-            p.g_first = unit_owner(tile_u0, a.total_units, G);
-            p.nseg = unit_owner(tile_u0 + a.kblocks - 1, a.total_units, G) - p.g_first + 1;
+            p.g_first = unit_owner(tile_u0, a.total_units, gt);
+            p.nseg = unit_owner(tile_u0 + a.kblocks - 1, a.total_units, gt) - p.g_first + 1;
             p.m_base = m_base; p.m_cnt = m_cnt; p.n = n; p.bias = bias_v;
             const bool spread = (p.nseg >= 3 && m_cnt > 16);
             __threadfence();               // this thread's partials are visible before the count

@@ -94,10 +94,7 @@ linear_umma_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_consta
     ptx::tc_fence_after();
     const uint32_t tmem_base = *tmem_slot;
 
-    SegIter it;
-    it.u = (a.total_units * g) / G;
-    it.u_end = (a.total_units * (g + 1)) / G;
-    it.kblocks = a.kblocks;
+    SegIter it = make_seg_iter(a, g, G);
     // Weights never depend on the previous kernel: the producer fills the ring with W tiles
     // first, and only then does the CTA wait for the predecessor grid (activations, workspace).
     if (warp != 0) grid_dep_wait();
@@ -115,7 +112,8 @@ linear_umma_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_consta
             {
                 SegIter pit = it;
                 while (pre < C::STAGES && pit.next(tile, kb0, kb1)) {
-                    const int n_tile = tile % a.n_tiles;
+                    int m_tile, n_tile;
+                    tile_to_mn(a, tile, m_tile, n_tile);
                     for (int kb = kb0; kb < kb1 && pre < C::STAGES; ++kb, ++pre) {
                         ptx::mbar_arrive_expect_tx(&full[pre], CPM_EXPERIMENT(a, 1) ? W_TILE_BYTES : C::STAGE_BYTES);
                         ptx::tma_load_2d(tiles + pre * C::STAGE_BYTES, &tm_w, &full[pre], kb * BLOCK_K, n_tile * BLOCK_N);
@@ -126,8 +124,8 @@ linear_umma_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_consta
             // ---- phase 2: the matching X tiles, then the steady-state ring
             int issued = 0;
             while (ok && it.next(tile, kb0, kb1)) {
-                const int m_tile = tile / a.n_tiles;
-                const int n_tile = tile - m_tile * a.n_tiles;
+                int m_tile, n_tile;
+                tile_to_mn(a, tile, m_tile, n_tile);
                 for (int kb = kb0; kb < kb1; ++kb, ++issued) {
                     uint8_t* dst = tiles + stage * C::STAGE_BYTES;
                     if (issued < pre) {
@@ -504,6 +502,10 @@ LinearPlan make_linear_plan(const bf16* x, int x_rows, const bf16* w, int M, int
         }
     }
     p.grid = static_cast<int>(grid);
+    if (m_tiles > 1) {
+        static const bool flat = tuning_env("CPMCU_LINEAR_NO_WAVES") != nullptr;   // bench only: plain stream-K
+        if (!flat) plan_waves(static_cast<long long>(n_tiles) * m_tiles, kblocks, p.grid, p.wave_tiles, p.tail_grid);
+    }
     // CS CTAs per tile with equal k ranges: sum the pieces inside a cluster when the device runs all clusters at once
     p.cluster = 0;
     {
@@ -543,7 +545,9 @@ void launch_linear(const LinearPlan& p, cudaStream_t stream) {
     a.n_tiles = ceil_div(p.N, BLOCK_N);
     a.m_tiles = ceil_div(p.M, p.mt);
     a.kblocks = p.K / BLOCK_K;
-    a.total_units = static_cast<long long>(a.n_tiles) * a.m_tiles * a.kblocks;
+    a.wave_tiles = p.wave_tiles;
+    a.tail_grid = p.tail_grid;
+    a.total_units = (static_cast<long long>(a.n_tiles) * a.m_tiles - a.wave_tiles) * a.kblocks;
     a.y = p.y; a.ldy = p.ldy; a.bias = p.bias;
     a.workspace = p.workspace; a.tickets = p.tickets;
     a.error = runtime().d_error;

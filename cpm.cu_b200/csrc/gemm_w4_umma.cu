@@ -163,10 +163,7 @@ linear_w4_umma_kernel(const __grid_constant__ CUtensorMap tm_x, const W4Args wa)
     const uint32_t tmem_base = *tmem_slot;
 
     // work units are 256-k super-blocks: a.kblocks = K / 256 units per tile
-    SegIter it;
-    it.u = (a.total_units * g) / G;
-    it.u_end = (a.total_units * (g + 1)) / G;
-    it.kblocks = a.kblocks;
+    SegIter it = make_seg_iter(a, g, G);
     const int c_rank = (CS > 0) ? static_cast<int>(ptx::cluster_ctarank()) : 0;
     const int c_tile = (CS > 0) ? g / CS : 0;
     if (CS > 0) {
@@ -186,7 +183,8 @@ linear_w4_umma_kernel(const __grid_constant__ CUtensorMap tm_x, const W4Args wa)
             int tile, u0, u1;
             bool ok = true;
             while (ok && it.next(tile, u0, u1)) {
-                const int n_tile = tile % a.n_tiles;
+                int m_tile, n_tile;
+                tile_to_mn(a, tile, m_tile, n_tile);
                 for (int u = u0; u < u1; ++u) {
                     if (!ptx::mbar_wait(&w_empty[stage], phase ^ 1, abort_flag)) { ok = false; break; }
                     if (CPM_EXPERIMENT(a, 64)) {  // timing experiment: no weight traffic
@@ -215,7 +213,8 @@ linear_w4_umma_kernel(const __grid_constant__ CUtensorMap tm_x, const W4Args wa)
             int tile, u0, u1;
             bool ok = true;
             while (ok && it.next(tile, u0, u1)) {
-                const int m_tile = tile / a.n_tiles;
+                int m_tile, n_tile;
+                tile_to_mn(a, tile, m_tile, n_tile);
                 for (int u = u0; u < u1; ++u) {
                     if (!ptx::mbar_wait_warp(&grp_empty[grp], phase ^ 1, abort_flag)) { ok = false; break; }
                     if (ptx::elect_one()) {
@@ -528,6 +527,10 @@ LinearPlan make_linear_plan_w4(const bf16* x, int x_rows, const void* wq, int M,
         grid = best;
     }
     p.grid = static_cast<int>(grid);
+    if (m_tiles > 1) {
+        static const bool flat = tuning_env("CPMCU_LINEAR_NO_WAVES") != nullptr;   // bench only: plain stream-K
+        if (!flat) plan_waves(static_cast<long long>(n_tiles) * m_tiles, units_per_tile, p.grid, p.wave_tiles, p.tail_grid);
+    }
     // pieces of a tile summed inside a thread-block cluster when the device runs all the clusters at once
     // (same rule as the bf16 path; a piece is at least one 256-k unit)
     p.cluster = 0;
@@ -558,7 +561,9 @@ void launch_linear_w4(const LinearPlan& p, cudaStream_t stream) {
     a.n_tiles = p.N / BLOCK_N;
     a.m_tiles = ceil_div(p.M, p.mt);
     a.kblocks = p.K / SUPER_K;  // work units per tile
-    a.total_units = static_cast<long long>(a.n_tiles) * a.m_tiles * a.kblocks;
+    a.wave_tiles = p.wave_tiles;
+    a.tail_grid = p.tail_grid;
+    a.total_units = (static_cast<long long>(a.n_tiles) * a.m_tiles - a.wave_tiles) * a.kblocks;
     a.y = p.y; a.ldy = p.ldy; a.bias = nullptr;
     a.workspace = p.workspace; a.tickets = p.tickets;
     a.error = runtime().d_error;

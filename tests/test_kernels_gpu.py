@@ -37,6 +37,9 @@ LINEAR_CASES = [
     # 64 tokens for the other token tiles; 61 tokens: the last rank's share of the tokens is short)
     (60, 4096, 4096, 0), (60, 4096, 16384, 0), (10, 4096, 8192, 0), (30, 4096, 4096, 0), (64, 4096, 4096, 0),
     (61, 4608, 4096, 0), (3, 4608, 4096, 0),
+    # prefill-sized launches (several token tiles): whole tiles in waves over the grid, the last partial wave cut along
+    # K; 4100 tokens = two bands of token tiles, the second one tile high
+    (700, 1024, 512, 7), (520, 384, 2048, 5), (2048, 4608, 512, 0), (4100, 1280, 256, 0),
 ]
 
 
@@ -65,6 +68,7 @@ W4_CASES = [
     (64, 512, 16384, 0), (33, 256, 256, 0), (130, 512, 256, 0), (300, 1024, 512, 0),
     (60, 1024, 2048, 3), (60, 1024, 2048, 7), (10, 4096, 4096, 5), (257, 640, 1024, 11),
     (60, 4096, 4096, 0), (60, 4096, 16384, 0), (30, 4608, 4096, 0), (61, 4096, 4096, 0),   # cluster split-K shapes
+    (700, 1024, 512, 7), (4100, 1280, 256, 0), (1000, 512, 2048, 9),                       # waves of whole tiles + a cut tail
 ]
 
 
