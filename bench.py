@@ -254,11 +254,16 @@ def measure(llm, prompt_len, seed, steps, warmup, local, barrier=None, profile=T
     import cpmcu.C as C
     prompt = torch.tensor(zipf_prompt(prompt_len, CFG["vocab"], seed), device="cuda")
     pos = torch.arange(prompt_len, dtype=torch.int32, device="cuda")
-    torch.cuda.synchronize()
-    t0 = time.time()
-    logits = llm.prefill(prompt, pos)
-    torch.cuda.synchronize()
-    prefill_s = time.time() - t0
+    # prefill as the reference's demo measures it: one warm-up pass, then the better of two (each pass rebuilds the
+    # whole context from position 0; the generation below continues from the last one)
+    prefill_runs = []
+    for _ in range(3):
+        torch.cuda.synchronize()
+        t0 = time.time()
+        logits = llm.prefill(prompt, pos)
+        torch.cuda.synchronize()
+        prefill_runs.append(time.time() - t0)
+    prefill_s = min(prefill_runs[1:])
     C.begin_generation(prompt_len, int(logits[0].argmax()))
     for _ in range(warmup):
         C.spec_step(16)
@@ -284,7 +289,7 @@ def measure(llm, prompt_len, seed, steps, warmup, local, barrier=None, profile=T
     sampler.stop_flag.set()
     sampler.join(timeout=2)
     res = dict(tokens=tokens, dev_ms=dev_ms, draft_ms=draft_ms, verify_ms=verify_ms, accept=accept, wall=wall,
-               prefill_s=prefill_s, launches=int(C.launches_per_step()), clocks=sampler.summary(),
+               prefill_s=prefill_s, prefill_first_s=prefill_runs[0], launches=int(C.launches_per_step()), clocks=sampler.summary(),
                context=prompt_len + sum(accept) // 2)
     if profile:
         # per-class device time of a few uncaptured steps (CUDA events around every launch)

@@ -339,6 +339,18 @@ int cpmcu_linear_bf16(const void* x, const void* w, const void* bias, void* y, i
     });
 }
 
+int cpmcu_linear_swiglu_bf16(const void* x, const void* w, void* out, int rows, int inter, int K, int grid_limit) {
+    return guarded([&] {
+        Runtime& rt = runtime();
+        const int limit = (grid_limit > 0) ? grid_limit : rt.num_sms;
+        LinearPlan p = make_linear_swiglu_plan(static_cast<const bf16*>(x), rows, static_cast<const bf16*>(w), rows, inter, K,
+                                               static_cast<bf16*>(out), inter, limit);
+        launch_linear(p, rt.stream);
+        sync_and_check("linear_swiglu");
+        return 0;
+    });
+}
+
 int cpmcu_linear_w4a16(const void* x, const void* qweight, const void* scales, void* y, int M, int N, int K,
                        int grid_limit) {
     return guarded([&] {
@@ -383,6 +395,12 @@ static int bench_linear_impl(int M, int N, int K, int copies, int iters, int gri
                                                     static_cast<uint8_t*>(w.p) + linear_w4_weight_bytes(N, K) * c,
                                                     M, N, K, static_cast<bf16*>(y.p), N,
                                                     static_cast<float*>(ws.p), static_cast<int*>(tickets.p), limit));
+                continue;
+            }
+            if (tuning_env("CPMCU_BENCH_SWIGLU")) {  // bench only: N / 2 gate rows + N / 2 up rows, activation in the epilogue
+                plans.push_back(make_linear_swiglu_plan(static_cast<const bf16*>(x.p), M,
+                                                        reinterpret_cast<const bf16*>(static_cast<uint8_t*>(w.p) + wbytes * c), M,
+                                                        N / 2, K, static_cast<bf16*>(y.p), N / 2, limit));
                 continue;
             }
             plans.push_back(make_linear_plan(static_cast<const bf16*>(x.p), M,

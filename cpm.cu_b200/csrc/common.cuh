@@ -173,6 +173,13 @@ CUtensorMap make_tmap_3d(const void* base, uint64_t d0, uint64_t d1, uint64_t d2
 
 // ---------------------------------------------------------------- GEMM
 // Y[M,N] = X[M,K] * W[N,K]^T (+ bias[N]); bf16 in, fp32 accumulate in TMEM.
+// silu(g) * u as the reference's kernel computes it (src/model/activation.cuh:12-16: g * (1 / (1 + expf(-g))) * u in
+// fp32, built with --use_fast_math, i.e. the ex2.approx form of expf and an approximate reciprocal).
+__device__ __forceinline__ float silu_mul(float g, float u) {
+    const float s = __fdividef(1.0f, 1.0f + __expf(-g));
+    return g * s * u;
+}
+
 struct LinearPlan {
     CUtensorMap tm_w;   // W  [N,K], box 64 x 128
     CUtensorMap tm_x;   // X  [Mrows,K], box 64 x MT
@@ -188,6 +195,7 @@ struct LinearPlan {
     int cluster = 0;             // > 0: CTAs per tile, pieces summed inside a thread-block cluster (bf16 path)
     int wave_tiles = 0;          // several token tiles: tiles computed whole, in waves of `grid` (the rest is cut along K)
     int tail_grid = 0;           // CTAs that share the tiles after wave_tiles (0 = all)
+    int swiglu = 0;              // SwiGLU epilogue: w = [gate ; up], N = output features, y = silu(gate) * up
     // W4A16: when wq is set the weights are 4-bit blocks in the streaming layout (see gemm_w4_umma.cu)
     const void* wq = nullptr;
 };
@@ -196,6 +204,8 @@ size_t linear_workspace_bytes(int mt, int grid);
 int linear_pick_mt(int M);
 LinearPlan make_linear_plan(const bf16* x, int x_rows, const bf16* w, int M, int N, int K, bf16* y, int ldy,
                             const bf16* bias, float* workspace, int* tickets, int grid_limit);
+LinearPlan make_linear_swiglu_plan(const bf16* x, int x_rows, const bf16* w, int M, int inter, int K, bf16* act, int ld,
+                                   int grid_limit);
 void launch_linear(const LinearPlan& plan, cudaStream_t stream);
 // Same contract with 4-bit weights, w = (q - 8) * scale, K % 256 == 0 and N % 128 == 0.  `wq` holds one
 // contiguous 16896-byte block per (128-feature tile, 256-k unit), tile-major: [4 k-blocks][2 halves]

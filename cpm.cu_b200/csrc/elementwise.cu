@@ -221,8 +221,7 @@ __global__ void silu_gate_kernel(const bf16* __restrict__ gate_up, bf16* __restr
     bf16* oe = reinterpret_cast<bf16*>(&ov);
 #pragma unroll
     for (int e = 0; e < 8; ++e) {
-        const float x = __bfloat162float(ge[e]);
-        oe[e] = __float2bfloat16(x * (1.0f / (1.0f + expf(-x))) * __bfloat162float(ue[e]));
+        oe[e] = __float2bfloat16(silu_mul(__bfloat162float(ge[e]), __bfloat162float(ue[e])));
     }
     *reinterpret_cast<uint4*>(out + static_cast<size_t>(r) * inter + c) = ov;
 }

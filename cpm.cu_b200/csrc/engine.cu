@@ -50,6 +50,8 @@ __global__ void gather_rows_kernel(const bf16* __restrict__ src, const int32_t* 
 
 // The engine's split-K counters (two per output tile) live in one buffer of kTicketInts ints.
 constexpr int kTicketInts = 1 << 16;
+// Row count from which the gate/up projection runs with the SwiGLU epilogue (whole 256-token tiles in waves).
+constexpr int kSwigluFusedRows = 512;
 LinearPlan checked(const LinearPlan& p) {
     CPM_REQUIRE(2LL * ceil_div(p.N, 128) * ceil_div(p.M, p.mt) <= kTicketInts,
                 "linear: more output tiles than the engine's split-K counters cover");
@@ -466,7 +468,11 @@ void Engine::build_layer_plans(LayerPlans& lp, const LayerWeights& w, const KVLa
     } else {
         lp.qkv = checked(make_linear_plan(normed_, rows, w.qkv, rows, qkv_dim_, H, qkv_, qkv_dim_, nullptr, gemm_ws_, tickets_, sms));
         lp.o = checked(make_linear_plan(attn_out_, rows, w.o, rows, H, mc_.hq * d, delta_, H, nullptr, gemm_ws_, tickets_, sms));
-        lp.gate_up = checked(make_linear_plan(normed_, rows, w.gate_up, rows, 2 * I, H, gate_up_, 2 * I, nullptr, gemm_ws_, tickets_, sms));
+        // prefill-sized passes apply the activation in the gate/up GEMM's epilogue and never store the projections
+        static const bool unfused = tuning_env("CPMCU_NO_SWIGLU_FUSE") != nullptr;   // bench only
+        lp.gate_up = (rows >= kSwigluFusedRows && I % 64 == 0 && !unfused)
+                         ? make_linear_swiglu_plan(normed_, rows, w.gate_up, rows, I, H, act_, I, sms)
+                         : checked(make_linear_plan(normed_, rows, w.gate_up, rows, 2 * I, H, gate_up_, 2 * I, nullptr, gemm_ws_, tickets_, sms));
         lp.down = checked(make_linear_plan(act_, rows, w.down, rows, H, I, delta_, H, nullptr, gemm_ws_, tickets_, sms));
     }
     lp.attn = make_attn_plan(qkv_, qkv_dim_, kv.k, kv.v, budget_, rows, mc_.hq, mc_.hkv, d, attn_splits, attn_out_,
@@ -536,7 +542,7 @@ void Engine::layer_forward(LayerPlans& lp, const LayerWeights& w, const KVLayer&
     launch_linear(lp.o, s);
     launch_add_rms_norm(x, delta_, res_scale, w.ln_ffn, normed_, rows, H, mc_.eps, s);
     launch_linear(lp.gate_up, s);
-    launch_silu_gate(gate_up_, act_, rows, mc_.inter, s);
+    if (!lp.gate_up.swiglu) launch_silu_gate(gate_up_, act_, rows, mc_.inter, s);
     launch_linear(lp.down, s);
 }
 
@@ -568,6 +574,8 @@ void Engine::target_forward(ForwardPlans& fp, const RowCtx& c, const int32_t* id
     sparse_prepare(c, s);
     const bf16* pending = nullptr;
     for (int l = 0; l < mc_.layers; ++l) {
+        // chunk-sized plans are built per call, each layer's while the GPU works on the layers before it
+        if (fp.lazy) build_layer_plans(fp.layers[l], layers_[l], kv_[l], rows, 1);
         layer_forward(fp.layers[l], layers_[l], kv_[l], c, x_, pending, mc_.scale_residual, true, mc_.scale_residual, s,
                       mc_.sparse.enabled ? l : -1);
         pending = delta_;
@@ -597,11 +605,42 @@ void Engine::prefill(int n, int history, const int32_t* ids, const int32_t* pos,
     c.kv_len = st_ + 6;
     c.kv_append_off = 0;
     c.attn_kv_add = n;
-    ForwardPlans fp;  // chunk-sized plans are built per call
+    ForwardPlans fp;
     fp.rows = n;
+    fp.lazy = true;
     fp.layers.resize(mc_.layers);
-    for (int l = 0; l < mc_.layers; ++l) build_layer_plans(fp.layers[l], layers_[l], kv_[l], n, 1);
+    static const bool prof_prefill = tuning_env("CPMCU_PROFILE_PREFILL") != nullptr;   // bench only
+    if (prof_prefill) {
+        for (int k = 0; k < KC_COUNT; ++k) rt.prof[k].clear();
+        rt.profile = true;
+    }
     target_forward(fp, c, ids, false, logits_out, mc_.vocab, s);
+    if (prof_prefill) {
+        // CUDA events around every launch of the pass: time per kernel class, and the GEMMs of the last layer
+        rt.profile = false;
+        CUDA_CHECK(cudaStreamSynchronize(s));
+        const char* names[KC_COUNT] = {"linear", "attention", "other"};
+        for (int k = 0; k < KC_COUNT; ++k) {
+            double sum = 0.0;
+            std::vector<float> each;
+            for (auto& pr : rt.prof[k]) {
+                float x = 0.f;
+                cudaEventElapsedTime(&x, pr.first, pr.second);
+                sum += x;
+                each.push_back(x);
+                cudaEventDestroy(pr.first);
+                cudaEventDestroy(pr.second);
+            }
+            fprintf(stderr, "prefill profile: %s %.2f ms over %zu launches", names[k], sum, each.size());
+            if (k == KC_LINEAR && each.size() >= 9) {
+                const size_t b = each.size() - 5;
+                fprintf(stderr, " (last layer qkv %.0f o %.0f gate_up %.0f down %.0f us)", each[b] * 1e3, each[b + 1] * 1e3,
+                        each[b + 2] * 1e3, each[b + 3] * 1e3);
+            }
+            fprintf(stderr, "\n");
+            rt.prof[k].clear();
+        }
+    }
     if (has_eagle_) {
         if (n > 1) launch_embedding(ids + 1, embed_, prev_embed_, H, n - 1, H, mc_.scale_embed, s);
         copy_rows(prev_hidden_, H, norm_out_, H, n, H, s);
@@ -715,7 +754,7 @@ void Engine::draft_catchup(cudaStream_t s) {
         launch_linear(lp.o, s);
         launch_add_rms_norm(e_x_, delta_, ec_.residual_scale, w.ln_ffn, normed_, rc, H, mc_.eps, s);
         launch_linear(lp.gate_up, s);
-        launch_silu_gate(gate_up_, act_, rc, mc_.inter, s);
+        if (!lp.gate_up.swiglu) launch_silu_gate(gate_up_, act_, rc, mc_.inter, s);
         launch_linear(lp.down, s);
         launch_add_scaled(e_h_, e_x_, delta_, ec_.residual_scale, rc, H, s);
     }

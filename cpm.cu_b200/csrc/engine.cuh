@@ -75,6 +75,7 @@ struct LayerPlans {
 };
 struct ForwardPlans {
     int rows = 0;
+    bool lazy = false;   // layers[l] is built by target_forward right before layer l is launched
     std::vector<LayerPlans> layers;
 };
 

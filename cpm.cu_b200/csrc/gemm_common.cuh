@@ -24,7 +24,14 @@ struct LinearArgs {
     // the tiles from wave_tiles on, which the first tail_grid CTAs (0 = all) share in equal contiguous pieces.
     int wave_tiles = 0;
     int tail_grid = 0;
+    // SwiGLU epilogue (whole tiles only): a weight tile is 64 gate rows followed by the 64 up rows of the same
+    // features, N counts output features (the gate half), y[token][feature] = silu(gate) * up.
+    int swiglu = 0;
 };
+
+// Shared memory the SwiGLU epilogue exchanges up-projection values through: two buffers of
+// [2 warps][16 tokens][32 lanes] floats.
+constexpr int SWIGLU_XCH_BYTES = 2 * 2 * 16 * 32 * 4;
 
 #ifdef CPMCU_GEMM_PROFILE
 constexpr bool kGemmProf = true;
@@ -183,7 +190,7 @@ template <int MT, int CH>
 __device__ __forceinline__ void run_epilogue(const LinearArgs& a, SegIter it, uint32_t tmem_base, uint64_t* acc_full,
                                              uint64_t* acc_empty, volatile int* abort_flag, volatile int* s_last, int warp,
                                              int lane, int epi_tid, int g, int G, uint32_t chain2_off = 0,
-                                             int acc_stages = 2) {
+                                             int acc_stages = 2, float* swiglu_xch = nullptr) {
     const int q = warp & 3;                 // TMEM lane quarter this warp may read
     const int row = q * 32 + lane;          // output feature within the tile
     int acc = 0;
@@ -191,10 +198,55 @@ __device__ __forceinline__ void run_epilogue(const LinearArgs& a, SegIter it, ui
     int tile, kb0, kb1;
     PendingTile pend[2];
     int n_pend = 0;
+    int xi = 0;  // SwiGLU exchange buffer of the next 16-token batch
     while (it.next(tile, kb0, kb1)) {
         int m_tile, n_tile;
         tile_to_mn(a, tile, m_tile, n_tile);
         const int m_base = m_tile * MT;
+        if (a.swiglu != 0 && swiglu_xch != nullptr) {
+            // Lanes 0-63 of the accumulator hold the gate projection of 64 features, lanes 64-127 the up projection
+            // of the same features.  Both are rounded to bf16 as the unfused pair of kernels stores them; the two
+            // warps of the gate half pass theirs through shared memory and the two warps of the up half (the ones
+            // that share no scheduler with the producer or the MMA warp) store silu(gate) * up.
+            int m_cnt = a.M - m_base;
+            if (m_cnt > MT) m_cnt = MT;
+            const int n_out = n_tile * 64 + (row & 63);
+            if (!ptx::mbar_wait_warp(&acc_full[acc], acc_phase, abort_flag)) break;
+            ptx::tc_fence_after();
+            const uint32_t t_addr = tmem_base + (static_cast<uint32_t>(q * 32) << 16) + acc * MT;
+#pragma unroll 1
+            for (int c0 = 0; c0 < MT; c0 += 16) {
+                if (c0 >= m_cnt) break;  // uniform across the CTA
+                uint32_t r[16];
+                ptx::tmem_ld16(t_addr + c0, r);
+                ptx::tmem_wait_ld();
+                float* xb = swiglu_xch + (xi & 1) * (2 * 16 * 32);
+                ++xi;
+                if (q < 2) {
+#pragma unroll
+                    for (int c = 0; c < 16; ++c) {
+                        xb[(q * 16 + c) * 32 + lane] = __bfloat162float(__float2bfloat16(__uint_as_float(r[c])));
+                    }
+                }
+                // the batch after the next one reuses this buffer: its writers pass the next batch's barrier only
+                // after this batch's readers have arrived there
+                ptx::named_bar_sync(1, 128);
+                if (q >= 2 && n_out < a.N) {
+#pragma unroll
+                    for (int c = 0; c < 16; ++c) {
+                        if (c0 + c < m_cnt) {
+                            const float uv = __bfloat162float(__float2bfloat16(__uint_as_float(r[c])));
+                            const float gv = xb[((q - 2) * 16 + c) * 32 + lane];
+                            a.y[static_cast<size_t>(m_base + c0 + c) * a.ldy + n_out] = __float2bfloat16(silu_mul(gv, uv));
+                        }
+                    }
+                }
+            }
+            ptx::tc_fence_before();
+            ptx::mbar_arrive(&acc_empty[acc]);
+            if (++acc == acc_stages) { acc = 0; acc_phase ^= 1; }
+            continue;
+        }
         const int n = n_tile * BLOCK_N + row;
         int m_cnt = a.M - m_base;
         if (m_cnt > MT) m_cnt = MT;

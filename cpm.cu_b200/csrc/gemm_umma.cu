@@ -45,7 +45,8 @@ struct Cfg {
     static constexpr int STAGES = (MT <= 16) ? 10 : (MT <= 32) ? 9 : (MT <= 64) ? 8 : (MT <= 128) ? 6 : 4;
     static constexpr int TMEM_COLS = (2 * MT < 32) ? 32 : 2 * MT;
     static constexpr int CTRL_BYTES = 256;
-    static constexpr int SMEM_BYTES = STAGES * STAGE_BYTES + CTRL_BYTES + 1024;
+    static constexpr int XCH_BYTES = (MT >= 128) ? SWIGLU_XCH_BYTES : 0;   // SwiGLU epilogue: prefill-sized launches only
+    static constexpr int SMEM_BYTES = STAGES * STAGE_BYTES + CTRL_BYTES + XCH_BYTES + 1024;
 };
 
 template <int MT>
@@ -63,6 +64,7 @@ linear_umma_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_consta
     uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(acc_empty + 2);
     volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
     volatile int* s_last = abort_flag + 1;
+    float* swiglu_xch = (C::XCH_BYTES > 0) ? reinterpret_cast<float*>(smem + C::STAGES * C::STAGE_BYTES + C::CTRL_BYTES) : nullptr;
 
     const int warp = threadIdx.x >> 5;
     const int lane = threadIdx.x & 31;
@@ -107,6 +109,12 @@ linear_umma_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_consta
             uint32_t phase = 0;
             int tile, kb0, kb1;
             bool ok = true;
+            // one 128-row weight tile: rows n_tile * 128 ..., or (SwiGLU) 64 gate rows then the 64 up rows of the same
+            // features through a 3-D map over [2][features][K]
+            auto load_w = [&](uint8_t* dst, uint64_t* bar, int kb, int n_tile) {
+                if (a.swiglu != 0) ptx::tma_load_3d(dst, &tm_w, bar, kb * BLOCK_K, n_tile * 64, 0);
+                else ptx::tma_load_2d(dst, &tm_w, bar, kb * BLOCK_K, n_tile * BLOCK_N);
+            };
             // ---- phase 1: W tiles of the first STAGES k-blocks, before the dependency wait
             int pre = 0;
             {
@@ -116,7 +124,7 @@ linear_umma_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_consta
                     tile_to_mn(a, tile, m_tile, n_tile);
                     for (int kb = kb0; kb < kb1 && pre < C::STAGES; ++kb, ++pre) {
                         ptx::mbar_arrive_expect_tx(&full[pre], CPM_EXPERIMENT(a, 1) ? W_TILE_BYTES : C::STAGE_BYTES);
-                        ptx::tma_load_2d(tiles + pre * C::STAGE_BYTES, &tm_w, &full[pre], kb * BLOCK_K, n_tile * BLOCK_N);
+                        load_w(tiles + pre * C::STAGE_BYTES, &full[pre], kb, n_tile);
                     }
                 }
             }
@@ -136,10 +144,10 @@ linear_umma_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_consta
                         if (!ptx::mbar_wait(&empty[stage], phase ^ 1, abort_flag)) { ok = false; break; }
                         if (CPM_EXPERIMENT(a, 1)) {
                             ptx::mbar_arrive_expect_tx(&full[stage], W_TILE_BYTES);
-                            ptx::tma_load_2d(dst, &tm_w, &full[stage], kb * BLOCK_K, n_tile * BLOCK_N);
+                            load_w(dst, &full[stage], kb, n_tile);
                         } else {
                             ptx::mbar_arrive_expect_tx(&full[stage], C::STAGE_BYTES);
-                            ptx::tma_load_2d(dst, &tm_w, &full[stage], kb * BLOCK_K, n_tile * BLOCK_N);
+                            load_w(dst, &full[stage], kb, n_tile);
                             ptx::tma_load_2d(dst + W_TILE_BYTES, &tm_x, &full[stage], kb * BLOCK_K, m_tile * MT);
                         }
                     }
@@ -192,7 +200,7 @@ linear_umma_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_consta
     } else {
         // ------------------------------------------------ epilogue (128 threads)
         run_epilogue<MT, (MT < 32) ? MT : 32>(a, it, tmem_base, acc_full, acc_empty, abort_flag, s_last, warp, lane,
-                                              threadIdx.x - 64, g, G);
+                                              threadIdx.x - 64, g, G, 0, 2, swiglu_xch);
         if (kGemmProf && a.prof != nullptr && threadIdx.x == 64) a.prof[g * 4 + 1] = clock64() - pt_dep;  // epilogue done
     }
     if (kGemmProf && a.prof != nullptr && warp == 1 && lane == 0) a.prof[g * 4 + 0] = clock64() - pt_dep;  // last MMA issued
@@ -534,6 +542,28 @@ LinearPlan make_linear_plan(const bf16* x, int x_rows, const bf16* w, int M, int
     return p;
 }
 
+// act[M, inter] = silu(X Wg^T) * (X Wu^T) with w = [gate rows (inter) ; up rows (inter)], both projections rounded to
+// bf16 before the product like the unfused pair (GEMM, then silu_gate_kernel).  Whole tiles only, in waves.
+LinearPlan make_linear_swiglu_plan(const bf16* x, int x_rows, const bf16* w, int M, int inter, int K, bf16* act, int ld,
+                                   int grid_limit) {
+    CPM_REQUIRE(M >= 1 && inter >= 64 && inter % 64 == 0, "linear: SwiGLU width must be a multiple of 64");
+    CPM_REQUIRE(K >= BLOCK_K && K % BLOCK_K == 0, "linear: K must be a multiple of 64");
+    CPM_REQUIRE((reinterpret_cast<uintptr_t>(x) & 15) == 0 && (reinterpret_cast<uintptr_t>(w) & 15) == 0,
+                "linear: operands must be 16-byte aligned");
+    LinearPlan p;
+    p.M = M; p.N = inter; p.K = K;
+    p.mt = M <= 128 ? 128 : 256;
+    p.y = act; p.ldy = ld; p.bias = nullptr;
+    p.swiglu = 1;
+    const long long tiles = static_cast<long long>(inter / 64) * ceil_div(M, p.mt);
+    p.grid = static_cast<int>(std::min<long long>(tiles, grid_limit));
+    p.wave_tiles = static_cast<int>(tiles);   // no tile is cut: nothing goes through the workspace
+    p.tail_grid = 1;
+    p.tm_w = make_tmap_3d(w, K, inter, 2, static_cast<uint64_t>(K) * 2, static_cast<uint64_t>(inter) * K * 2, BLOCK_K, 64, 2);
+    p.tm_x = make_tmap_2d(x, K, x_rows, static_cast<uint64_t>(K) * 2, BLOCK_K, p.mt);
+    return p;
+}
+
 void launch_linear(const LinearPlan& p, cudaStream_t stream) {
     if (p.wq != nullptr) {  // 4-bit weights
         launch_linear_w4(p, stream);
@@ -547,6 +577,11 @@ void launch_linear(const LinearPlan& p, cudaStream_t stream) {
     a.kblocks = p.K / BLOCK_K;
     a.wave_tiles = p.wave_tiles;
     a.tail_grid = p.tail_grid;
+    a.swiglu = p.swiglu;
+    if (p.swiglu) {   // N = output features; a tile covers 64 of them (gate + up rows)
+        a.n_tiles = ceil_div(p.N, 64);
+        CPM_REQUIRE(p.mt >= 128 && p.cluster == 0, "linear: the SwiGLU epilogue needs a prefill-sized token tile");
+    }
     a.total_units = (static_cast<long long>(a.n_tiles) * a.m_tiles - a.wave_tiles) * a.kblocks;
     a.y = p.y; a.ldy = p.ldy; a.bias = p.bias;
     a.workspace = p.workspace; a.tickets = p.tickets;

@@ -55,6 +55,7 @@ constexpr int NTHREADS = SOFTMAX_THREADS + 32;  // + one control warp (TMA and M
 
 struct AttnArgs {
     int tq, hq, hkv, grp, tok_per_tile, num_mtiles;
+    int heavy_first;  // causal prefill: token tiles are handed out last-to-first, longest key range first
     const int32_t* kv_len;
     int kv_len_add;
     const int32_t* n_valid;
@@ -113,7 +114,8 @@ tree_attn_kernel(const __grid_constant__ CUtensorMap tm_q, const __grid_constant
     const int ch = (warp >> 2) & 1;              // column half of the key tile
     const int row = (warp & 3) * 32 + lane;      // query row of the tile == TMEM lane
     grid_dep_trigger();
-    const int mt = blockIdx.x % a.num_mtiles;
+    const int mt_in = blockIdx.x % a.num_mtiles;
+    const int mt = a.heavy_first ? a.num_mtiles - 1 - mt_in : mt_in;
     const int h = blockIdx.x / a.num_mtiles;  // kv head
     const int split = blockIdx.y;
     const int nsplit = gridDim.y;
@@ -617,6 +619,9 @@ void launch_tree_attention(const AttnPlan& p, cudaStream_t s) {
     a.grp = p.hq / p.hkv;
     a.tok_per_tile = ROWS / a.grp;
     a.num_mtiles = ceil_div(p.tq, a.tok_per_tile);
+    // One split over many token tiles is a causal prefill: a tile's work grows with its position, and CTAs are
+    // dispatched in blockIdx order, so the longest tiles go first and the short ones fill the tail.
+    a.heavy_first = (p.splits == 1 && a.num_mtiles > 1) ? 1 : 0;
     a.kv_len = p.kv_len; a.kv_len_add = p.kv_len_add;
     a.n_valid = p.n_valid;
     a.mask = p.mask; a.mask_k = p.mask_k;

@@ -238,6 +238,12 @@ int cpmcu_rope_append(void* qkv, int rows, int hq, int hkv, const float* inv_fre
 /* reference: gated_silu_interleaved, src/model/activation.cuh:7-18. */
 int cpmcu_silu_gate(const void* gate_up, void* out, int rows, int inter);
 
+/* The gate/up projection and the activation of GatedFFN::prefill (src/model/ffn.cuh:72-86) in one launch, for
+ * prefill-sized row counts: out[rows, inter] = silu(x Wg^T) * (x Wu^T), w = [gate rows ; up rows] of K columns,
+ * both projections rounded to bf16 before the product: bit-identical to cpmcu_linear_bf16 followed by
+ * cpmcu_silu_gate.  inter % 64 == 0, K % 64 == 0. */
+int cpmcu_linear_swiglu_bf16(const void* x, const void* w, void* out, int rows, int inter, int K, int grid_limit);
+
 /* Row argmax (lowest index wins ties); reference: torch argmax in
  * cpmcu/speculative/tree_drafter.py:233. */
 int cpmcu_argmax(const void* logits, int rows, int vocab, int32_t* out);

@@ -98,6 +98,26 @@ def test_linear_w4a16_matches_dequantised_matmul(M, N, K, grid):
     assert torch.equal(y, y2)                          # ticketed split-K sums in a fixed order
 
 
+@pytest.mark.parametrize("M,inter,K,grid", [(100, 128, 128, 0), (129, 192, 256, 0), (600, 256, 512, 7), (2048, 2304, 512, 0),
+                                            (4100, 640, 256, 0)])
+def test_linear_with_swiglu_epilogue_equals_linear_then_silu_gate(M, inter, K, grid):
+    """Prefill's fused gate/up projection + activation against the two separate launches: bit-identical, because the
+    epilogue rounds both projections to bf16 before the product exactly as the stored intermediate would be."""
+    c = C()
+    g = torch.Generator().manual_seed(M * 31 + inter * 7 + K)
+    x = dev(torch.randn(M, K, generator=g).to(torch.bfloat16))
+    w = dev((torch.randn(2 * inter, K, generator=g) * 0.08).to(torch.bfloat16))
+    gu = torch.empty(M, 2 * inter, dtype=torch.bfloat16, device="cuda")
+    c.call("cpmcu_linear_bf16", ptr(x), ptr(w), None, ptr(gu), M, 2 * inter, K, grid)
+    want = torch.empty(M, inter, dtype=torch.bfloat16, device="cuda")
+    c.call("cpmcu_silu_gate", ptr(gu), ptr(want), M, inter)
+    got = torch.full((M, inter), float("nan"), dtype=torch.bfloat16, device="cuda")
+    c.call("cpmcu_linear_swiglu_bf16", ptr(x), ptr(w), ptr(got), M, inter, K, grid)
+    assert torch.isfinite(got.float()).all()
+    assert float(want.float().abs().max()) > 0.1
+    assert torch.equal(got, want)
+
+
 def test_linear_is_deterministic():
     c = C()
     g = torch.Generator().manual_seed(5)
