@@ -218,6 +218,13 @@ class LLM(torch.nn.Module):
     def _text(self, token):
         return self.tokenizer.decode([token], skip_special_tokens=False) if self.tokenizer is not None else ""
 
+    def _text_after(self, prev_token, tokens):
+        """Text of `tokens` as it reads after `prev_token` (the reference decodes with one token of context)."""
+        if self.tokenizer is None:
+            return ""
+        both = self.tokenizer.decode([prev_token] + list(tokens), skip_special_tokens=False)
+        return both[len(self.tokenizer.decode([prev_token], skip_special_tokens=False)):]
+
     def generate(self, input_ids, generation_length=100, teminators=[], use_stream=False):
         """Greedy / sampled decoding without speculation.  Returns
         (tokens, decode_time, prefill_time), or a generator of dicts when use_stream."""
@@ -250,21 +257,24 @@ class LLM(torch.nn.Module):
                 yield token
 
         if use_stream:
+            # the reference's stream (cpmcu/llm.py:334-397): each token's text is decoded with the previous token as
+            # context (correct spacing); decode_time counts from after the first token, which comes from prefill
             def stream():
-                start = time.time()
                 done = token in teminators
                 yield {"token": token, "text": self._text(token), "is_finished": done or generation_length == 1,
                        "prefill_time": prefill_time, "decode_time": 0.0}
                 if done:
                     return
-                produced = 1
+                start = time.time()
+                produced, prev = 1, token
                 for tok in steps():
                     produced += 1
                     done = tok in teminators or produced == generation_length
-                    yield {"token": tok, "text": self._text(tok), "is_finished": done, "prefill_time": 0.0,
+                    yield {"token": tok, "text": self._text_after(prev, [tok]), "is_finished": done, "prefill_time": 0.0,
                            "decode_time": time.time() - start}
                     if done:
                         return
+                    prev = tok
             return stream()
 
         tokens = [token]

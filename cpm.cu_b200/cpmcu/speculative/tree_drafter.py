@@ -120,22 +120,31 @@ class LLM_with_tree_drafter(LLM):
                 i += len(emitted)
 
         if use_stream:
+            # The reference's stream (cpmcu/speculative/tree_drafter.py:117-212): one dict per token; the text of a
+            # step's tokens is decoded together with the previous token for correct spacing and handed to the
+            # step's first token, which alone carries the step's accept_length; its last token carries decode_time.
             def stream():
-                start = time.time()
-                done = root in teminators or generation_length == 1
+                done = root in teminators
                 yield {"token": root, "text": self._text(root), "is_finished": done, "accept_length": 1,
                        "prefill_time": prefill_time, "decode_time": 0.0}
                 if done:
                     return
+                start = time.time()
+                prev = root
                 for emitted, i in steps():
-                    room = generation_length - 1 - i
-                    for j, tok in enumerate(emitted[:room]):
-                        last = tok in teminators or (i + j + 1 == generation_length - 1)
-                        yield {"token": tok, "text": self._text(tok), "is_finished": last,
-                               "accept_length": len(emitted), "prefill_time": 0.0,
-                               "decode_time": time.time() - start}
-                        if last:
+                    n = len(emitted)
+                    new_text = self._text_after(prev, emitted)
+                    for j, tok in enumerate(emitted):
+                        if i + j >= generation_length - 1:
+                            break
+                        terminal = tok in teminators
+                        yield {"token": tok, "text": new_text if j == 0 else "",
+                               "is_finished": terminal or (i + j == generation_length - 2),
+                               "accept_length": n if j == 0 else 0, "prefill_time": 0.0,
+                               "decode_time": time.time() - start if j == n - 1 else 0.0}
+                        if terminal:
                             return
+                    prev = emitted[-1]
             return stream()
 
         tokens = [root]

@@ -50,8 +50,6 @@ __global__ void gather_rows_kernel(const bf16* __restrict__ src, const int32_t* 
 
 // The engine's split-K counters (two per output tile) live in one buffer of kTicketInts ints.
 constexpr int kTicketInts = 1 << 16;
-// Row count from which the gate/up projection runs with the SwiGLU epilogue (whole 256-token tiles in waves).
-constexpr int kSwigluFusedRows = 512;
 LinearPlan checked(const LinearPlan& p) {
     CPM_REQUIRE(2LL * ceil_div(p.N, 128) * ceil_div(p.M, p.mt) <= kTicketInts,
                 "linear: more output tiles than the engine's split-K counters cover");
@@ -468,9 +466,10 @@ void Engine::build_layer_plans(LayerPlans& lp, const LayerWeights& w, const KVLa
     } else {
         lp.qkv = checked(make_linear_plan(normed_, rows, w.qkv, rows, qkv_dim_, H, qkv_, qkv_dim_, nullptr, gemm_ws_, tickets_, sms));
         lp.o = checked(make_linear_plan(attn_out_, rows, w.o, rows, H, mc_.hq * d, delta_, H, nullptr, gemm_ws_, tickets_, sms));
-        // prefill-sized passes apply the activation in the gate/up GEMM's epilogue and never store the projections
+        // the activation is applied in the gate/up GEMM's epilogue and the two projections are never stored, whenever
+        // the whole-tile schedule that needs fills the GPU
         static const bool unfused = tuning_env("CPMCU_NO_SWIGLU_FUSE") != nullptr;   // bench only
-        lp.gate_up = (rows >= kSwigluFusedRows && I % 64 == 0 && !unfused)
+        lp.gate_up = (!unfused && linear_swiglu_fits(rows, I, sms))
                          ? make_linear_swiglu_plan(normed_, rows, w.gate_up, rows, I, H, act_, I, sms)
                          : checked(make_linear_plan(normed_, rows, w.gate_up, rows, 2 * I, H, gate_up_, 2 * I, nullptr, gemm_ws_, tickets_, sms));
         lp.down = checked(make_linear_plan(act_, rows, w.down, rows, H, I, delta_, H, nullptr, gemm_ws_, tickets_, sms));

@@ -45,7 +45,7 @@ struct Cfg {
     static constexpr int STAGES = (MT <= 16) ? 10 : (MT <= 32) ? 9 : (MT <= 64) ? 8 : (MT <= 128) ? 6 : 4;
     static constexpr int TMEM_COLS = (2 * MT < 32) ? 32 : 2 * MT;
     static constexpr int CTRL_BYTES = 256;
-    static constexpr int XCH_BYTES = (MT >= 128) ? SWIGLU_XCH_BYTES : 0;   // SwiGLU epilogue: prefill-sized launches only
+    static constexpr int XCH_BYTES = SWIGLU_XCH_BYTES;   // SwiGLU epilogue: gate values on their way to the up warps
     static constexpr int SMEM_BYTES = STAGES * STAGE_BYTES + CTRL_BYTES + XCH_BYTES + 1024;
 };
 
@@ -542,6 +542,29 @@ LinearPlan make_linear_plan(const bf16* x, int x_rows, const bf16* w, int M, int
     return p;
 }
 
+// Grid of a SwiGLU launch: its tiles (64 features x one token tile) are never cut along K.  One token tile: the
+// largest grid that gives every CTA the same number of tiles; more: one CTA per SM, tiles in waves.
+static int swiglu_grid(int n_tiles, int m_tiles, int grid_limit) {
+    const long long tiles = static_cast<long long>(n_tiles) * m_tiles;
+    if (tiles <= grid_limit) return static_cast<int>(tiles);
+    if (m_tiles > 1) return grid_limit;
+    int g = grid_limit;
+    while (n_tiles % g != 0) --g;
+    return g;
+}
+
+// Whether the whole-tile schedule keeps the SMs about as busy as the stream-K schedule of the unfused GEMM would
+// (launches smaller than the grid limit always qualify: they are a single wave either way).
+bool linear_swiglu_fits(int M, int inter, int grid_limit) {
+    if (inter < 64 || inter % 64 != 0) return false;
+    const int n_tiles = inter / 64, m_tiles = ceil_div(M, linear_pick_mt(M));
+    const long long tiles = static_cast<long long>(n_tiles) * m_tiles;
+    if (tiles <= grid_limit) return true;
+    const int g = swiglu_grid(n_tiles, m_tiles, grid_limit);
+    const long long waves = (tiles + g - 1) / g;
+    return static_cast<double>(tiles) >= 0.85 * static_cast<double>(waves) * grid_limit;
+}
+
 // act[M, inter] = silu(X Wg^T) * (X Wu^T) with w = [gate rows (inter) ; up rows (inter)], both projections rounded to
 // bf16 before the product like the unfused pair (GEMM, then silu_gate_kernel).  Whole tiles only, in waves.
 LinearPlan make_linear_swiglu_plan(const bf16* x, int x_rows, const bf16* w, int M, int inter, int K, bf16* act, int ld,
@@ -552,11 +575,11 @@ LinearPlan make_linear_swiglu_plan(const bf16* x, int x_rows, const bf16* w, int
                 "linear: operands must be 16-byte aligned");
     LinearPlan p;
     p.M = M; p.N = inter; p.K = K;
-    p.mt = M <= 128 ? 128 : 256;
+    p.mt = linear_pick_mt(M);
     p.y = act; p.ldy = ld; p.bias = nullptr;
     p.swiglu = 1;
     const long long tiles = static_cast<long long>(inter / 64) * ceil_div(M, p.mt);
-    p.grid = static_cast<int>(std::min<long long>(tiles, grid_limit));
+    p.grid = swiglu_grid(inter / 64, ceil_div(M, p.mt), grid_limit);
     p.wave_tiles = static_cast<int>(tiles);   // no tile is cut: nothing goes through the workspace
     p.tail_grid = 1;
     p.tm_w = make_tmap_3d(w, K, inter, 2, static_cast<uint64_t>(K) * 2, static_cast<uint64_t>(inter) * K * 2, BLOCK_K, 64, 2);
@@ -580,7 +603,7 @@ void launch_linear(const LinearPlan& p, cudaStream_t stream) {
     a.swiglu = p.swiglu;
     if (p.swiglu) {   // N = output features; a tile covers 64 of them (gate + up rows)
         a.n_tiles = ceil_div(p.N, 64);
-        CPM_REQUIRE(p.mt >= 128 && p.cluster == 0, "linear: the SwiGLU epilogue needs a prefill-sized token tile");
+        CPM_REQUIRE(p.cluster == 0 && p.wave_tiles == a.n_tiles * a.m_tiles, "linear: the SwiGLU epilogue needs whole tiles");
     }
     a.total_units = (static_cast<long long>(a.n_tiles) * a.m_tiles - a.wave_tiles) * a.kblocks;
     a.y = p.y; a.ldy = p.ldy; a.bias = p.bias;

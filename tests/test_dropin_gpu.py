@@ -60,7 +60,14 @@ def library_generate(name, base_dir, eagle_dir, prompt, stream=False):
         out = list(llm.generate(ids, c["gen"], teminators=[], use_stream=True))
         assert all(set(d) >= {"token", "text", "is_finished", "accept_length", "prefill_time", "decode_time"} for d in out)
         assert out[-1]["is_finished"] and not any(d["is_finished"] for d in out[:-1])
-        tokens, acc = [d["token"] for d in out], None
+        # the reference's consumer (tests/test_generate.py:365-404) collects accept_length > 0 as one entry per step
+        # and takes the last decode_time > 0 as the total: the first token reports 1, then only a step's first token
+        # reports the step's accept length and only its last token a decode time
+        tokens = [d["token"] for d in out]
+        acc = [d["accept_length"] for d in out if d["accept_length"] > 0]
+        assert acc[0] == 1 and sum(acc[1:]) >= len(tokens) - 1 and out[0]["prefill_time"] > 0
+        assert all(d["prefill_time"] == 0.0 for d in out[1:]) and out[-1]["decode_time"] >= 0
+        acc = acc[1:]
     else:
         tokens, acc, decode_s, prefill_s = llm.generate(ids, c["gen"], teminators=[])
         assert decode_s > 0 and prefill_s > 0
@@ -100,9 +107,10 @@ def test_same_checkpoint_through_load_from_hf_matches_reference(name, tmp_path):
 def test_stream_mode_yields_the_same_tokens(tmp_path):
     name = "plain"
     base_dir, eagle_dir, prompt = dc.write_case(name, str(tmp_path))
-    tokens, _ = library_generate(name, base_dir, eagle_dir, prompt)
-    s_tokens, _ = library_generate(name, base_dir, eagle_dir, prompt, stream=True)
+    tokens, acc = library_generate(name, base_dir, eagle_dir, prompt)
+    s_tokens, s_acc = library_generate(name, base_dir, eagle_dir, prompt, stream=True)
     assert s_tokens == tokens
+    assert s_acc == acc      # one accept length per step, as the non-stream call returns them
 
 
 def test_minicpm4_yarn_is_refused(tmp_path):

@@ -99,16 +99,20 @@ def test_linear_w4a16_matches_dequantised_matmul(M, N, K, grid):
 
 
 @pytest.mark.parametrize("M,inter,K,grid", [(100, 128, 128, 0), (129, 192, 256, 0), (600, 256, 512, 7), (2048, 2304, 512, 0),
-                                            (4100, 640, 256, 0)])
+                                            (4100, 640, 256, 0), (1, 64, 64, 0), (7, 320, 256, 0), (10, 2048, 512, 0),
+                                            (60, 16384, 4096, 0), (33, 11008, 1024, 0), (60, 1024, 2048, 3)])
 def test_linear_with_swiglu_epilogue_equals_linear_then_silu_gate(M, inter, K, grid):
-    """Prefill's fused gate/up projection + activation against the two separate launches: bit-identical, because the
-    epilogue rounds both projections to bf16 before the product exactly as the stored intermediate would be."""
+    """The fused gate/up projection + activation against the two separate launches, at decode, draft and prefill row
+    counts: bit-identical, because the epilogue rounds both projections to bf16 before the product exactly as the
+    stored intermediate would be."""
     c = C()
     g = torch.Generator().manual_seed(M * 31 + inter * 7 + K)
     x = dev(torch.randn(M, K, generator=g).to(torch.bfloat16))
     w = dev((torch.randn(2 * inter, K, generator=g) * 0.08).to(torch.bfloat16))
     gu = torch.empty(M, 2 * inter, dtype=torch.bfloat16, device="cuda")
-    c.call("cpmcu_linear_bf16", ptr(x), ptr(w), None, ptr(gu), M, 2 * inter, K, grid)
+    # one CTA: every tile is accumulated whole, in k order, as the fused launch does (a launch that cuts tiles along K
+    # adds its fp32 partial sums in another order, which moves an occasional bf16 rounding of a projection by one step)
+    c.call("cpmcu_linear_bf16", ptr(x), ptr(w), None, ptr(gu), M, 2 * inter, K, 1)
     want = torch.empty(M, inter, dtype=torch.bfloat16, device="cuda")
     c.call("cpmcu_silu_gate", ptr(gu), ptr(want), M, inter)
     got = torch.full((M, inter), float("nan"), dtype=torch.bfloat16, device="cuda")
@@ -116,6 +120,11 @@ def test_linear_with_swiglu_epilogue_equals_linear_then_silu_gate(M, inter, K, g
     assert torch.isfinite(got.float()).all()
     assert float(want.float().abs().max()) > 0.1
     assert torch.equal(got, want)
+    # against the launch as the engine would make it without the fusion (tiles possibly cut along K): one bf16 step
+    c.call("cpmcu_linear_bf16", ptr(x), ptr(w), None, ptr(gu), M, 2 * inter, K, grid)
+    c.call("cpmcu_silu_gate", ptr(gu), ptr(want), M, inter)
+    diff = (got.float() - want.float()).abs()
+    assert bool((diff <= 2.0 ** -7 * want.float().abs() + 1e-6).all())
 
 
 def test_linear_is_deterministic():
