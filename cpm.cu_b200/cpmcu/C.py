@@ -49,6 +49,7 @@ _SIGNATURES = {
     "cpmcu_linear_w4a16": (_c_int, [_c_void_p] * 4 + [_c_int] * 4),
     "cpmcu_bench_linear": (_c_int, [_c_int] * 6 + [_c_void_p]),
     "cpmcu_bench_linear_w4": (_c_int, [_c_int] * 6 + [_c_void_p]),
+    "cpmcu_bench_linear_swiglu": (_c_int, [_c_int] * 6 + [_c_void_p]),
     "cpmcu_bench_attention": (_c_int, [_c_int] * 7 + [_c_void_p]),
     "cpmcu_sparse_attention": (_c_int, [_c_void_p, _c_int, _c_void_p, _c_void_p] + [_c_int] * 4 +
                                [_c_void_p, _c_int, _c_void_p, _c_int, _c_void_p, _c_int, _c_int, _c_int, _c_void_p,

@@ -373,7 +373,8 @@ int cpmcu_linear_w4a16(const void* x, const void* qweight, const void* scales, v
     });
 }
 
-static int bench_linear_impl(int M, int N, int K, int copies, int iters, int grid_limit, float* avg_us, bool w4) {
+static int bench_linear_impl(int M, int N, int K, int copies, int iters, int grid_limit, float* avg_us, bool w4,
+                             bool swiglu = false) {
     return guarded([&] {
         Runtime& rt = runtime();
         cudaStream_t s = rt.stream;
@@ -397,7 +398,7 @@ static int bench_linear_impl(int M, int N, int K, int copies, int iters, int gri
                                                     static_cast<float*>(ws.p), static_cast<int*>(tickets.p), limit));
                 continue;
             }
-            if (tuning_env("CPMCU_BENCH_SWIGLU")) {  // bench only: N / 2 gate rows + N / 2 up rows, activation in the epilogue
+            if (swiglu) {  // N / 2 gate rows + N / 2 up rows, activation in the epilogue
                 plans.push_back(make_linear_swiglu_plan(static_cast<const bf16*>(x.p), M,
                                                         reinterpret_cast<const bf16*>(static_cast<uint8_t*>(w.p) + wbytes * c), M,
                                                         N / 2, K, static_cast<bf16*>(y.p), N / 2, limit));
@@ -435,6 +436,10 @@ int cpmcu_bench_linear(int M, int N, int K, int copies, int iters, int grid_limi
 
 int cpmcu_bench_linear_w4(int M, int N, int K, int copies, int iters, int grid_limit, float* avg_us) {
     return bench_linear_impl(M, N, K, copies, iters, grid_limit, avg_us, true);
+}
+
+int cpmcu_bench_linear_swiglu(int M, int inter, int K, int copies, int iters, int grid_limit, float* avg_us) {
+    return bench_linear_impl(M, 2 * inter, K, copies, iters, grid_limit, avg_us, false, true);
 }
 
 int cpmcu_tree_attention(const void* q, int q_ld, const void* k_cache, const void* v_cache, int budget, int tq,

@@ -191,6 +191,8 @@ int cpmcu_linear_w4a16(const void* x, const void* qweight, const void* scales, v
 int cpmcu_bench_linear(int M, int N, int K, int copies, int iters, int grid_limit, float* avg_us);
 /* The same for the W4A16 kernel: the buffers are read as 4-bit blocks (any bit pattern is a valid weight). */
 int cpmcu_bench_linear_w4(int M, int N, int K, int copies, int iters, int grid_limit, float* avg_us);
+/* The same for the gate/up projection with the SwiGLU epilogue (cpmcu_linear_swiglu_bf16): 2 * inter weight rows. */
+int cpmcu_bench_linear_swiglu(int M, int inter, int K, int copies, int iters, int grid_limit, float* avg_us);
 
 /* reference: mha_fwd_kvcache, src/flash_attn/flash_api.hpp:292-392.
  * q: token t, head h at q + t*q_ld + h*128; caches [budget, hkv*128]; keys

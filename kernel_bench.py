@@ -2,6 +2,7 @@
 
     python kernel_bench.py linear [M,N,K] [iters]      bf16 weights
     python kernel_bench.py linear_w4 [M,N,K] [iters]   4-bit weights (W4A16)
+    python kernel_bench.py linear_swiglu [M,inter,K] [iters]   gate/up projection with the SwiGLU epilogue
     python kernel_bench.py attention [tq,hq,hkv,kv,splits,mask] [iters]
     python kernel_bench.py select [tq,hq,hkv,L,budget] [iters]    InfLLM-v2 block selection of one layer
     python kernel_bench.py reference                   the reference project's own kernels beside the library's
@@ -47,6 +48,14 @@ def bench_linear(shapes, iters, w4):
         streamed = store // 4 + (K // 128) * N * 2 if w4 else store
         print(f"{'linear_w4' if w4 else 'linear'} M={M} N={N} K={K} copies={copies}: {us:.1f} us  "
               f"{streamed / us / 1e3:.0f} GB/s", flush=True)
+
+
+def bench_linear_swiglu(shapes, iters):
+    for M, inter, K in shapes:
+        store = 2 * inter * K * 2                 # gate and up rows
+        copies = max(1, min(40, (600 << 20) // store + 1))
+        us = _us("cpmcu_bench_linear_swiglu", M, inter, K, copies, iters, 0)
+        print(f"linear_swiglu M={M} inter={inter} K={K} copies={copies}: {us:.1f} us  {store / us / 1e3:.0f} GB/s", flush=True)
 
 
 def bench_attention(cases, iters):
@@ -203,6 +212,8 @@ def main(argv):
         bench_linear([shape] if shape else LINEAR_SHAPES, iters, False)
     elif what == "linear_w4":
         bench_linear([shape] if shape else W4_SHAPES, iters, True)
+    elif what == "linear_swiglu":
+        bench_linear_swiglu([shape] if shape else [(60, 16384, 4096), (10, 16384, 4096), (4096, 16384, 4096)], iters)
     elif what == "attention":
         bench_attention([shape] if shape else ATTN_CASES, iters)
     elif what == "tail":

@@ -111,7 +111,8 @@ def test_linear_with_swiglu_epilogue_equals_linear_then_silu_gate(M, inter, K, g
     w = dev((torch.randn(2 * inter, K, generator=g) * 0.08).to(torch.bfloat16))
     gu = torch.empty(M, 2 * inter, dtype=torch.bfloat16, device="cuda")
     # one CTA: every tile is accumulated whole, in k order, as the fused launch does (a launch that cuts tiles along K
-    # adds its fp32 partial sums in another order, which moves an occasional bf16 rounding of a projection by one step)
+    # adds its fp32 partial sums in another order, which moves an occasional bf16 rounding of a projection by one step,
+    # hence the second comparison below allows a few bf16 steps of the product)
     c.call("cpmcu_linear_bf16", ptr(x), ptr(w), None, ptr(gu), M, 2 * inter, K, 1)
     want = torch.empty(M, inter, dtype=torch.bfloat16, device="cuda")
     c.call("cpmcu_silu_gate", ptr(gu), ptr(want), M, inter)
@@ -124,7 +125,7 @@ def test_linear_with_swiglu_epilogue_equals_linear_then_silu_gate(M, inter, K, g
     c.call("cpmcu_linear_bf16", ptr(x), ptr(w), None, ptr(gu), M, 2 * inter, K, grid)
     c.call("cpmcu_silu_gate", ptr(gu), ptr(want), M, inter)
     diff = (got.float() - want.float()).abs()
-    assert bool((diff <= 2.0 ** -7 * want.float().abs() + 1e-6).all())
+    assert bool((diff <= 2.0 ** -6 * want.float().abs() + 1e-6).all())
 
 
 def test_linear_is_deterministic():
