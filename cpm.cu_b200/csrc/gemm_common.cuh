@@ -27,6 +27,7 @@ struct LinearArgs {
     // SwiGLU epilogue (whole tiles only): a weight tile is 64 gate rows followed by the 64 up rows of the same
     // features, N counts output features (the gate half), y[token][feature] = silu(gate) * up.
     int swiglu = 0;
+    int band = 16;   // token tiles per raster band (tile_to_mn)
 };
 
 // Shared memory the SwiGLU epilogue exchanges up-projection values through: two buffers of
@@ -39,13 +40,25 @@ constexpr bool kGemmProf = true;
 constexpr bool kGemmProf = false;
 #endif
 
-// The work of one CTA: whole tiles wave_tile, wave_tile + stride, ... below wave_tiles, then the k-blocks
-// [u, u_end) of the line of (tile, k-block) units that starts at tile wave_tiles.
+// The work of one CTA: the k-blocks [u, u_end) of the line of (tile, k-block) units that starts at tile wave_tiles,
+// then the whole tiles wave_tile, wave_tile + stride, ... below wave_tiles.
 struct SegIter {
     long long u, u_end;
     int kblocks;
     int wave_tile = 0, wave_tiles = 0, stride = 1;
+    // The cut tiles come first: the piece counted last sums the tile in the epilogue warps while the MMA warp is
+    // already on the CTA's whole tiles, so the fix-up through the workspace hides behind them instead of ending
+    // the kernel.
     __device__ bool next(int& tile, int& kb0, int& kb1) {
+        if (u < u_end) {
+            const int t = static_cast<int>(u / kblocks);
+            tile = wave_tiles + t;
+            kb0 = static_cast<int>(u - static_cast<long long>(t) * kblocks);
+            long long rem = u_end - u;
+            kb1 = (kb0 + rem < kblocks) ? static_cast<int>(kb0 + rem) : kblocks;
+            u += kb1 - kb0;
+            return true;
+        }
         if (wave_tile < wave_tiles) {
             tile = wave_tile;
             kb0 = 0;
@@ -53,21 +66,14 @@ struct SegIter {
             wave_tile += stride;
             return true;
         }
-        if (u >= u_end) return false;
-        const int t = static_cast<int>(u / kblocks);
-        tile = wave_tiles + t;
-        kb0 = static_cast<int>(u - static_cast<long long>(t) * kblocks);
-        long long rem = u_end - u;
-        kb1 = (kb0 + rem < kblocks) ? static_cast<int>(kb0 + rem) : kblocks;
-        u += kb1 - kb0;
-        return true;
+        return false;
     }
 };
 
 // Work of CTA g of G.  With wave_tiles = 0 (every launch of a single token tile) this is plain stream-K: the
 // line of all (tile, k-block) units cut into G equal pieces.  Launches with several token tiles run whole tiles
-// in waves first: the CTAs of a wave walk K in step, so tiles that share a weight or an activation slab find it
-// in L2 instead of each fetching it from HBM at a different time; only the last, partial wave is cut along K.
+// in waves: the CTAs of a wave walk K in step, so tiles that share a weight or an activation slab find it
+// in L2 instead of each fetching it from HBM at a different time; only the tiles of the partial wave are cut along K.
 __device__ __forceinline__ SegIter make_seg_iter(const LinearArgs& a, int g, int G) {
     SegIter it;
     it.kblocks = a.kblocks;
@@ -84,23 +90,33 @@ __device__ __forceinline__ SegIter make_seg_iter(const LinearArgs& a, int g, int
     return it;
 }
 
-// Tile number -> (token tile, feature tile).  Token tiles are taken in bands of RASTER_BAND; inside a band the
+// Tile number -> (token tile, feature tile).  Token tiles are taken in bands of a.band; inside a band the
 // token tile runs fastest, so the tiles a wave of CTAs works on at one time cover few feature tiles x all token
 // tiles of the band: every weight slab is fetched from HBM once per band and the band's activations stay in L2.
-constexpr int RASTER_BAND = 16;
 __device__ __forceinline__ void tile_to_mn(const LinearArgs& a, int tile, int& m_tile, int& n_tile) {
     if (a.m_tiles == 1) {
         m_tile = 0;
         n_tile = tile;
         return;
     }
-    const int band_tiles = RASTER_BAND * a.n_tiles;
+    const int band_tiles = a.band * a.n_tiles;
     const int band = tile / band_tiles;
     const int r = tile - band * band_tiles;
-    int bm = a.m_tiles - band * RASTER_BAND;
-    if (bm > RASTER_BAND) bm = RASTER_BAND;
+    int bm = a.m_tiles - band * a.band;
+    if (bm > a.band) bm = a.band;
     n_tile = r / bm;
-    m_tile = band * RASTER_BAND + (r - n_tile * bm);
+    m_tile = band * a.band + (r - n_tile * bm);
+}
+
+// Token tiles per band: as many as keep the band's activations (band * mt rows of K bf16) within half of the
+// 126 MB L2, at most 16.  With K = 16384 and 256-token tiles that is 8: a band of 16 (134 MB) was re-read from HBM by
+// every wave (1.1 GB of DRAM reads for 268 MB of operands in one ncu capture of the 4096-token down projection).
+inline int raster_band(int mt, int K) {
+    const long long rows = (64LL << 20) / (static_cast<long long>(K) * 2);
+    int band = static_cast<int>(rows / mt);
+    if (band < 1) band = 1;
+    if (band > 16) band = 16;
+    return band;
 }
 
 // Host side of make_seg_iter for a launch with several token tiles: whole waves of `grid` tiles, and the CTAs
@@ -199,7 +215,44 @@ __device__ __forceinline__ void run_epilogue(const LinearArgs& a, SegIter it, ui
     PendingTile pend[2];
     int n_pend = 0;
     int xi = 0;  // SwiGLU exchange buffer of the next 16-token batch
+    // ---- split tiles: wait for the other pieces, sum this CTA's share of the tokens
+    auto flush_pending = [&]() {
+        for (int i = 0; i < n_pend; ++i) {
+            const PendingTile& p = pend[i];
+            if (epi_tid == 0) {
+                const long long t0 = clock64();
+                int ok = 1;
+                while (ld_acquire(&a.tickets[2 * p.tile]) < p.nseg) {
+                    if (*abort_flag || clock64() - t0 > kFixupBudgetClocks) { ok = 0; *abort_flag = 1; break; }
+                }
+                *s_last = ok;
+            }
+            ptx::named_bar_sync(1, 128);
+            const bool ready = (*s_last != 0);
+            ptx::named_bar_sync(1, 128);  // everyone has read s_last before it can change
+            if (ready && !CPM_EXPERIMENT(a, 16)) {
+                const int piece = g - p.g_first;
+                sum_pieces<MT, CH>(a, p, (p.m_cnt * piece) / p.nseg, (p.m_cnt * (piece + 1)) / p.nseg, row);
+            }
+            if (ready) {
+                // the partials of this tile may be overwritten once every piece's reader has left
+                ptx::named_bar_sync(1, 128);
+                if (epi_tid == 0) {
+                    const int old = atomicAdd(&a.tickets[2 * p.tile + 1], 1);
+                    if (old == p.nseg - 1) {
+                        a.tickets[2 * p.tile + 1] = 0;
+                        __threadfence();
+                        a.tickets[2 * p.tile] = 0;  // ready for the next launch
+                    }
+                }
+            }
+        }
+        n_pend = 0;
+    };
     while (it.next(tile, kb0, kb1)) {
+        // the cut tiles of a launch come before its whole tiles: their sums are done here, while the MMA warp
+        // works on the whole tiles, not at the end of the kernel
+        if (n_pend > 0 && tile < a.wave_tiles) flush_pending();
         int m_tile, n_tile;
         tile_to_mn(a, tile, m_tile, n_tile);
         const int m_base = m_tile * MT;
@@ -326,37 +379,7 @@ __device__ __forceinline__ void run_epilogue(const LinearArgs& a, SegIter it, ui
         }
     }
 
-    // ---- split tiles: wait for the other pieces, sum this CTA's share of the tokens
-    for (int i = 0; i < n_pend; ++i) {
-        const PendingTile& p = pend[i];
-        if (epi_tid == 0) {
-            const long long t0 = clock64();
-            int ok = 1;
-            while (ld_acquire(&a.tickets[2 * p.tile]) < p.nseg) {
-                if (*abort_flag || clock64() - t0 > kFixupBudgetClocks) { ok = 0; *abort_flag = 1; break; }
-            }
-            *s_last = ok;
-        }
-        ptx::named_bar_sync(1, 128);
-        const bool ready = (*s_last != 0);
-        ptx::named_bar_sync(1, 128);  // everyone has read s_last before it can change
-        if (ready && !CPM_EXPERIMENT(a, 16)) {
-            const int piece = g - p.g_first;
-            sum_pieces<MT, CH>(a, p, (p.m_cnt * piece) / p.nseg, (p.m_cnt * (piece + 1)) / p.nseg, row);
-        }
-        if (ready) {
-            // the partials of this tile may be overwritten once every piece's reader has left
-            ptx::named_bar_sync(1, 128);
-            if (epi_tid == 0) {
-                const int old = atomicAdd(&a.tickets[2 * p.tile + 1], 1);
-                if (old == p.nseg - 1) {
-                    a.tickets[2 * p.tile + 1] = 0;
-                    __threadfence();
-                    a.tickets[2 * p.tile] = 0;  // ready for the next launch
-                }
-            }
-        }
-    }
+    flush_pending();
 }
 
 // Second half of split-K inside a thread-block cluster of CS CTAs that hold the CS k-pieces of one output

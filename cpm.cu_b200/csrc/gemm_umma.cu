@@ -601,6 +601,7 @@ void launch_linear(const LinearPlan& p, cudaStream_t stream) {
     a.wave_tiles = p.wave_tiles;
     a.tail_grid = p.tail_grid;
     a.swiglu = p.swiglu;
+    a.band = raster_band(p.mt, p.K);
     if (p.swiglu) {   // N = output features; a tile covers 64 of them (gate + up rows)
         a.n_tiles = ceil_div(p.N, 64);
         CPM_REQUIRE(p.cluster == 0 && p.wave_tiles == a.n_tiles * a.m_tiles, "linear: the SwiGLU epilogue needs whole tiles");

@@ -563,6 +563,7 @@ void launch_linear_w4(const LinearPlan& p, cudaStream_t stream) {
     a.kblocks = p.K / SUPER_K;  // work units per tile
     a.wave_tiles = p.wave_tiles;
     a.tail_grid = p.tail_grid;
+    a.band = raster_band(p.mt, p.K);
     a.total_units = (static_cast<long long>(a.n_tiles) * a.m_tiles - a.wave_tiles) * a.kblocks;
     a.y = p.y; a.ldy = p.ldy; a.bias = nullptr;
     a.workspace = p.workspace; a.tickets = p.tickets;
