@@ -50,7 +50,18 @@ CASES = {
                          fc_gain=8.0, chunk=256, mup=dict(scale_emb=6.0, dim_model_base=512, scale_depth=1.4)),
     "headline_tree": dict(cfg="c", eagle=dict(num_iter=6, topk=10, tree_size=60), seed=12, prompt=300, gen=48,
                           layer_scale=0.3, fc_gain=8.0, chunk=512),
+    # a prompt of two prefill chunks, the first of 13 token tiles: the prefill-sized schedules (whole GEMM tiles in
+    # waves, the SwiGLU epilogue, causal attention over thousands of keys) and the drafter's deferred pass over the
+    # previous chunk, against the reference build's own chunked prefill
+    "long_prompt": dict(cfg="c", eagle=dict(num_iter=4, topk=6, tree_size=24), seed=21, prompt=3400, gen=32,
+                        layer_scale=0.3, fc_gain=8.0, chunk=3328, max_tokens=8192),
 }
+
+
+def oracle_chunk(name):
+    """The chunk length to hand the oracle's generate_spec: None for a prompt of one chunk."""
+    c = CASES[name]
+    return c["chunk"] if c["prompt"] > c["chunk"] else None
 
 
 def case_parts(name):
@@ -86,6 +97,7 @@ def make_oracle(name, budget=1024):
     if CASES[name].get("quant_draft"):
         from helpers import quantize_eagle
         ew, _ = quantize_eagle(cfg, ew)
+    budget = max(budget, CASES[name].get("max_tokens", 0))
     return OracleModel(cfg, w, eagle, ew, budget=budget, token_id_remap=remap), prompt
 
 

@@ -5,7 +5,9 @@ case it writes the checkpoint directories, runs baseline/ref_cuda.py (the refere
 W4A16GPTQMarlinLLM_with_eagle: init_storage, load_from_hf, generate) in a process of its own and stores the token
 stream and the accept lengths:
 
-    python tests/golden/make_ref_generate_golden.py [OUT.json]      (default: tests/golden/ref_generate_golden.json)
+    python tests/golden/make_ref_generate_golden.py [OUT.json] [--only case,case]
+                                                     (default: every case into tests/golden/ref_generate_golden.json;
+                                                      --only records the named cases and keeps the others' entries)
 
 tests/test_ref_generate_golden_cpu.py holds the CPU oracle against these vectors; tests/test_dropin_gpu.py holds
 the library against them (and against the live reference when its build is in the tree)."""
@@ -40,10 +42,19 @@ def run_reference(name, root):
 
 
 def main():
-    out = sys.argv[1] if len(sys.argv) > 1 else os.path.join(HERE, "ref_generate_golden.json")
+    args = sys.argv[1:]
+    only = None
+    if "--only" in args:
+        i = args.index("--only")
+        only = args[i + 1].split(",")
+        del args[i:i + 2]
+    out = args[0] if args else os.path.join(HERE, "ref_generate_golden.json")
     gold = {}
+    if only is not None and os.path.exists(out):
+        with open(out) as f:
+            gold = json.load(f)
     with tempfile.TemporaryDirectory() as root:
-        for name in dc.CASES:
+        for name in (only if only is not None else dc.CASES):
             try:
                 gold[name] = run_reference(name, root)
                 print(name, "tokens", len(gold[name]["tokens"]), "accept", gold[name]["accept_lengths"], flush=True)

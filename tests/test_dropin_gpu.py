@@ -47,7 +47,7 @@ def library_generate(name, base_dir, eagle_dir, prompt, stream=False):
     c = dc.CASES[name]
     e = c["eagle"]
     cls = W4A16GPTQMarlinLLM_with_eagle if c.get("quant") else LLM_with_eagle
-    os.environ["CPMCU_MAX_TOKENS"] = "4096"
+    os.environ["CPMCU_MAX_TOKENS"] = str(c.get("max_tokens", 4096))
     llm = cls(eagle_dir, base_dir, num_iter=e["num_iter"], topk_per_iter=e["topk"], tree_size=e["tree_size"],
               eagle_window_size=e.get("window", 0), frspec_vocab_size=e.get("frspec_vocab", 0),
               use_input_norm=e.get("use_input_norm", False), use_attn_norm=e.get("use_attn_norm", False),

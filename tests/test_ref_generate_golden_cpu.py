@@ -23,7 +23,7 @@ def test_oracle_reproduces_the_reference_token_stream(name):
     judge, prompt = dc.make_oracle(name)
     ties = check_greedy_stream(judge, prompt, want["tokens"], name + ": reference stream under the oracle's target")
     oracle, _ = dc.make_oracle(name)
-    tokens, accept, steps = oracle.generate_spec(prompt.tolist(), dc.CASES[name]["gen"])
+    tokens, accept, steps = oracle.generate_spec(prompt.tolist(), dc.CASES[name]["gen"], chunk=dc.oracle_chunk(name))
     n = min(len(tokens), len(want["tokens"]))
     if not ties:
         assert tokens[:n] == want["tokens"][:n]
