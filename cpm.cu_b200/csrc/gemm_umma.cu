@@ -579,9 +579,13 @@ LinearPlan make_linear_swiglu_plan(const bf16* x, int x_rows, const bf16* w, int
     p.y = act; p.ldy = ld; p.bias = nullptr;
     p.swiglu = 1;
     const long long tiles = static_cast<long long>(inter / 64) * ceil_div(M, p.mt);
-    p.grid = swiglu_grid(inter / 64, ceil_div(M, p.mt), grid_limit);
-    p.wave_tiles = static_cast<int>(tiles);   // no tile is cut: nothing goes through the workspace
-    p.tail_grid = 1;
+    const int m_tiles = ceil_div(M, p.mt);
+    p.grid = swiglu_grid(inter / 64, m_tiles, grid_limit);
+    // No tile is cut, nothing goes through the workspace.  Several token tiles: whole tiles in waves.  One token tile:
+    // the grid divides the tiles, and every CTA takes consecutive ones (one contiguous run of gate rows and one of up
+    // rows per CTA instead of two scattered 64-row slabs per tile).
+    p.wave_tiles = (m_tiles > 1) ? static_cast<int>(tiles) : 0;
+    p.tail_grid = (m_tiles > 1) ? 1 : p.grid;
     p.tm_w = make_tmap_3d(w, K, inter, 2, static_cast<uint64_t>(K) * 2, static_cast<uint64_t>(inter) * K * 2, BLOCK_K, 64, 2);
     p.tm_x = make_tmap_2d(x, K, x_rows, static_cast<uint64_t>(K) * 2, BLOCK_K, p.mt);
     return p;
@@ -604,7 +608,9 @@ void launch_linear(const LinearPlan& p, cudaStream_t stream) {
     a.band = raster_band(p.mt, p.K);
     if (p.swiglu) {   // N = output features; a tile covers 64 of them (gate + up rows)
         a.n_tiles = ceil_div(p.N, 64);
-        CPM_REQUIRE(p.cluster == 0 && p.wave_tiles == a.n_tiles * a.m_tiles, "linear: the SwiGLU epilogue needs whole tiles");
+        CPM_REQUIRE(p.cluster == 0 && (p.wave_tiles == a.n_tiles * a.m_tiles ||
+                                       (a.m_tiles == 1 && p.wave_tiles == 0 && a.n_tiles % p.grid == 0)),
+                    "linear: the SwiGLU epilogue needs whole tiles");
     }
     a.total_units = (static_cast<long long>(a.n_tiles) * a.m_tiles - a.wave_tiles) * a.kblocks;
     a.y = p.y; a.ldy = p.ldy; a.bias = p.bias;
