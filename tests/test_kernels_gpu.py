@@ -206,6 +206,10 @@ ATTN_CASES = [
     (16, 2, 1, 300, "tree", 1), (16, 2, 1, 300, "tree", 3), (60, 32, 2, 1000, "tree", 4), (60, 32, 2, 129, "tree", 9),
     (10, 8, 2, 517, "tree", 5), (200, 4, 2, 0, "causal", 1), (130, 8, 2, 100, "causal", 1),
     (7, 32, 2, 777, "valid3", 6), (1, 32, 2, 400, "causal", 8), (64, 16, 1, 64, "tree", 2),
+    # prefill-sized passes (four or more token tiles, one split): two token tiles per CTA; odd tile counts, a window,
+    # a long prefix, rows beyond the valid count
+    (600, 32, 2, 300, "causal", 1), (500, 4, 2, 1000, "causal", 1, 384), (300, 16, 1, 0, "causal", 1),
+    (1000, 8, 2, 1040, "causal", 1), (260, 4, 2, 900, "valid3", 1), (72, 32, 2, 1900, "causal", 1, 256),
 ]
 
 
