@@ -62,6 +62,7 @@ _SIGNATURES = {
     "cpmcu_rope_append": (_c_int, [_c_void_p, _c_int, _c_int, _c_int] + [_c_void_p] * 5 + [_c_int]),
     "cpmcu_silu_gate": (_c_int, [_c_void_p, _c_void_p, _c_int, _c_int]),
     "cpmcu_linear_swiglu_bf16": (_c_int, [_c_void_p] * 3 + [_c_int] * 4),
+    "cpmcu_debug_linear_schedule": (_c_int, [_c_int] * 4 + [_c_void_p, _c_int]),
     "cpmcu_argmax": (_c_int, [_c_void_p, _c_int, _c_int, _c_void_p]),
     "cpmcu_argmax_noalloc": (_c_int, [_c_void_p, _c_int, _c_int, _c_void_p]),
     "cpmcu_draft_tree_from_logits": (_c_int, [_c_void_p] + [_c_int] * 4 + [_c_void_p] * 9),

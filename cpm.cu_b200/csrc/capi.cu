@@ -339,6 +339,17 @@ int cpmcu_linear_bf16(const void* x, const void* w, const void* bias, void* y, i
     });
 }
 
+int cpmcu_debug_linear_schedule(int M, int N, int K, int grid_limit, int32_t* out, int cap) {
+    int n = -1;
+    const int rc = guarded([&] {
+        CPM_REQUIRE(M >= 1 && N >= 1 && K >= 64 && K % 64 == 0 && grid_limit >= 1 && out != nullptr && cap >= 1,
+                    "debug_linear_schedule: bad arguments");
+        n = linear_schedule_dump(M, N, K, grid_limit, out, cap);
+        return 0;
+    });
+    return rc < 0 ? rc : n;
+}
+
 int cpmcu_linear_swiglu_bf16(const void* x, const void* w, void* out, int rows, int inter, int K, int grid_limit) {
     return guarded([&] {
         Runtime& rt = runtime();

@@ -204,6 +204,7 @@ size_t linear_workspace_bytes(int mt, int grid);
 int linear_pick_mt(int M);
 LinearPlan make_linear_plan(const bf16* x, int x_rows, const bf16* w, int M, int N, int K, bf16* y, int ldy,
                             const bf16* bias, float* workspace, int* tickets, int grid_limit);
+int linear_schedule_dump(int M, int N, int K, int grid_limit, int32_t* out, int cap);
 bool linear_swiglu_fits(int M, int inter, int grid_limit);
 LinearPlan make_linear_swiglu_plan(const bf16* x, int x_rows, const bf16* w, int M, int inter, int K, bf16* act, int ld,
                                    int grid_limit);

@@ -49,7 +49,7 @@ struct SegIter {
     // The cut tiles come first: the piece counted last sums the tile in the epilogue warps while the MMA warp is
     // already on the CTA's whole tiles, so the fix-up through the workspace hides behind them instead of ending
     // the kernel.
-    __device__ bool next(int& tile, int& kb0, int& kb1) {
+    __host__ __device__ bool next(int& tile, int& kb0, int& kb1) {
         if (u < u_end) {
             const int t = static_cast<int>(u / kblocks);
             tile = wave_tiles + t;
@@ -74,7 +74,7 @@ struct SegIter {
 // line of all (tile, k-block) units cut into G equal pieces.  Launches with several token tiles run whole tiles
 // in waves: the CTAs of a wave walk K in step, so tiles that share a weight or an activation slab find it
 // in L2 instead of each fetching it from HBM at a different time; only the tiles of the partial wave are cut along K.
-__device__ __forceinline__ SegIter make_seg_iter(const LinearArgs& a, int g, int G) {
+__host__ __device__ __forceinline__ SegIter make_seg_iter(const LinearArgs& a, int g, int G) {
     SegIter it;
     it.kblocks = a.kblocks;
     it.wave_tiles = a.wave_tiles;
@@ -93,7 +93,7 @@ __device__ __forceinline__ SegIter make_seg_iter(const LinearArgs& a, int g, int
 // Tile number -> (token tile, feature tile).  Token tiles are taken in bands of a.band; inside a band the
 // token tile runs fastest, so the tiles a wave of CTAs works on at one time cover few feature tiles x all token
 // tiles of the band: every weight slab is fetched from HBM once per band and the band's activations stay in L2.
-__device__ __forceinline__ void tile_to_mn(const LinearArgs& a, int tile, int& m_tile, int& n_tile) {
+__host__ __device__ __forceinline__ void tile_to_mn(const LinearArgs& a, int tile, int& m_tile, int& n_tile) {
     if (a.m_tiles == 1) {
         m_tile = 0;
         n_tile = tile;
@@ -120,18 +120,19 @@ inline int raster_band(int mt, int K) {
 }
 
 // Host side of make_seg_iter for a launch with several token tiles: whole waves of `grid` tiles, and the CTAs
-// that share the rest (pieces of at least eight k-blocks).
+// that share the rest (pieces of at least eight k-blocks, or whole tiles when a tile has fewer).
 inline void plan_waves(long long tiles, int kblocks, int grid, int& wave_tiles, int& tail_grid) {
     wave_tiles = static_cast<int>((tiles / grid) * grid);
     const long long tail_units = (tiles - wave_tiles) * kblocks;
     long long gt = tail_units / 8;
+    if (gt < tiles - wave_tiles) gt = tiles - wave_tiles;
     if (gt < 1) gt = 1;
     if (gt > grid) gt = grid;
     tail_grid = static_cast<int>(gt);
 }
 
 // CTA that owns work unit u when [0,U) is cut into G pieces starting at floor(g*U/G).
-__device__ __forceinline__ int unit_owner(long long u, long long U, int G) {
+__host__ __device__ __forceinline__ int unit_owner(long long u, long long U, int G) {
     return static_cast<int>(((u + 1) * G - 1) / U);
 }
 

@@ -476,6 +476,50 @@ static int pick_grid(int n_tiles, int kblocks, int m_valid, int limit) {
     return best_g;
 }
 
+// CTAs of a launch before the cluster and wave decisions: at least four k-blocks each.
+static long long base_grid(int n_tiles, int m_tiles, int kblocks, int M, int grid_limit) {
+    const long long units = static_cast<long long>(n_tiles) * m_tiles * kblocks;
+    long long grid = units / 4;
+    if (grid < 1) grid = 1;
+    if (grid > grid_limit) grid = grid_limit;
+    if (m_tiles == 1 && grid_limit >= 64) grid = pick_grid(n_tiles, kblocks, M, static_cast<int>(grid));
+    return grid;
+}
+
+// Host-side walk of the work distribution make_linear_plan + launch_linear give a launch (without the cluster
+// variant, which cuts every tile into equal pieces): for every CTA its segments as six ints
+// (cta, tile, token tile, feature tile, first k-block, end k-block), in the order the CTA runs them.  The same
+// iterator and raster functions the kernels use, compiled for the host.  Returns the number of segments, or -1 when
+// `cap` segments do not hold them.
+int linear_schedule_dump(int M, int N, int K, int grid_limit, int32_t* out, int cap) {
+    LinearArgs a = {};
+    const int mt = linear_pick_mt(M);
+    a.M = M; a.N = N; a.K = K;
+    a.n_tiles = ceil_div(N, BLOCK_N);
+    a.m_tiles = ceil_div(M, mt);
+    a.kblocks = K / BLOCK_K;
+    const int grid = static_cast<int>(base_grid(a.n_tiles, a.m_tiles, a.kblocks, M, grid_limit));
+    a.wave_tiles = 0;
+    a.tail_grid = 0;
+    if (a.m_tiles > 1) plan_waves(static_cast<long long>(a.n_tiles) * a.m_tiles, a.kblocks, grid, a.wave_tiles, a.tail_grid);
+    a.total_units = (static_cast<long long>(a.n_tiles) * a.m_tiles - a.wave_tiles) * a.kblocks;
+    a.band = raster_band(mt, K);
+    int n = 0;
+    for (int g = 0; g < grid; ++g) {
+        SegIter it = make_seg_iter(a, g, grid);
+        int tile, kb0, kb1;
+        while (it.next(tile, kb0, kb1)) {
+            if (n >= cap) return -1;
+            int m_tile, n_tile;
+            tile_to_mn(a, tile, m_tile, n_tile);
+            int32_t* o = out + static_cast<size_t>(n) * 6;
+            o[0] = g; o[1] = tile; o[2] = m_tile; o[3] = n_tile; o[4] = kb0; o[5] = kb1;
+            ++n;
+        }
+    }
+    return n;
+}
+
 LinearPlan make_linear_plan(const bf16* x, int x_rows, const bf16* w, int M, int N, int K, bf16* y, int ldy,
                             const bf16* bias, float* workspace, int* tickets, int grid_limit) {
     CPM_REQUIRE(M >= 1 && N >= 1 && K >= BLOCK_K, "linear: empty problem");
@@ -490,10 +534,7 @@ LinearPlan make_linear_plan(const bf16* x, int x_rows, const bf16* w, int M, int
     p.workspace = workspace; p.tickets = tickets;
     const int n_tiles = ceil_div(N, BLOCK_N), m_tiles = ceil_div(M, p.mt), kblocks = K / BLOCK_K;
     const long long units = static_cast<long long>(n_tiles) * m_tiles * kblocks;
-    long long grid = units / 4;  // at least four k-blocks per CTA
-    if (grid < 1) grid = 1;
-    if (grid > grid_limit) grid = grid_limit;
-    if (m_tiles == 1 && grid_limit >= 64) grid = pick_grid(n_tiles, kblocks, M, static_cast<int>(grid));
+    long long grid = base_grid(n_tiles, m_tiles, kblocks, M, grid_limit);
     {
         static const char* forced = tuning_env("CPMCU_LINEAR_GRID");  // bench only: sweep the grid size
         if (forced && atoi(forced) >= 1 && atoi(forced) <= grid_limit && atoi(forced) <= units) grid = atoi(forced);

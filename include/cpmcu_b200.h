@@ -185,6 +185,13 @@ int cpmcu_linear_bf16(const void* x, const void* w, const void* bias, void* y, i
 int cpmcu_linear_w4a16(const void* x, const void* qweight, const void* scales, void* y, int M, int N, int K,
                        int grid_limit);
 
+/* Host only, no GPU needed: the work distribution of cpmcu_linear_bf16(M, N, K, grid_limit) as the kernels walk it
+ * (the iterator and raster code of the kernels compiled for the host; a launch that uses the cluster variant cuts
+ * every tile into equal pieces instead).  out: HOST int32[cap][6] = (cta, tile, token tile, feature tile, first
+ * k-block, end k-block) per segment, in each CTA's execution order.  Returns the segment count, -1 on error or
+ * when cap is too small. */
+int cpmcu_debug_linear_schedule(int M, int N, int K, int grid_limit, int32_t* out, int cap);
+
 /* Times `iters` back-to-back launches of the linear kernel on the library's
  * stream with CUDA events, cycling through `copies` separate weight buffers so
  * that the weights come from HBM and not from L2.  avg_us: HOST float. */
