@@ -330,7 +330,11 @@ int cpmcu_linear_bf16(const void* x, const void* w, const void* bias, void* y, i
         const size_t tiles = static_cast<size_t>(ceil_div(N, 128)) * ceil_div(M, mt);
         DeviceBuf tickets(2 * tiles * sizeof(int));
         CUDA_CHECK(cudaMemsetAsync(tickets.p, 0, 2 * tiles * sizeof(int), rt.stream));
-        LinearPlan p = make_linear_plan(static_cast<const bf16*>(x), M, static_cast<const bf16*>(w), M, N, K,
+        // the caller's row-major W in the kernels' tile-major layout
+        DeviceBuf wt(linear_weight_elems(N, K) * sizeof(bf16));
+        CUDA_CHECK(cudaMemsetAsync(wt.p, 0, linear_weight_elems(N, K) * sizeof(bf16), rt.stream));
+        retile_weight_rows(w, N, K, static_cast<bf16*>(wt.p), K, 0, 0, 0, rt.stream);
+        LinearPlan p = make_linear_plan(static_cast<const bf16*>(x), M, static_cast<const bf16*>(wt.p), M, N, K,
                                         static_cast<bf16*>(y), N, static_cast<const bf16*>(bias),
                                         static_cast<float*>(ws.p), static_cast<int*>(tickets.p), limit);
         launch_linear(p, rt.stream);
@@ -354,7 +358,12 @@ int cpmcu_linear_swiglu_bf16(const void* x, const void* w, void* out, int rows, 
     return guarded([&] {
         Runtime& rt = runtime();
         const int limit = (grid_limit > 0) ? grid_limit : rt.num_sms;
-        LinearPlan p = make_linear_swiglu_plan(static_cast<const bf16*>(x), rows, static_cast<const bf16*>(w), rows, inter, K,
+        // gate rows and up rows into the tiles of their 64-feature groups
+        DeviceBuf wt(linear_weight_elems(2 * inter, K) * sizeof(bf16));
+        retile_weight_rows(w, inter, K, static_cast<bf16*>(wt.p), K, 1, 0, 0, rt.stream);
+        retile_weight_rows(static_cast<const bf16*>(w) + static_cast<size_t>(inter) * K, inter, K, static_cast<bf16*>(wt.p), K, 2, 0,
+                           0, rt.stream);
+        LinearPlan p = make_linear_swiglu_plan(static_cast<const bf16*>(x), rows, static_cast<const bf16*>(wt.p), rows, inter, K,
                                                static_cast<bf16*>(out), inter, limit);
         launch_linear(p, rt.stream);
         sync_and_check("linear_swiglu");
@@ -392,7 +401,7 @@ static int bench_linear_impl(int M, int N, int K, int copies, int iters, int gri
         CPM_REQUIRE(copies >= 1 && copies <= 64 && iters >= 1, "bench_linear: bad repetition counts");
         const int limit = (grid_limit > 0) ? grid_limit : rt.num_sms;
         const int mt = linear_pick_mt(M);
-        const size_t wbytes = static_cast<size_t>(N) * K * 2;
+        const size_t wbytes = linear_weight_elems(N, K) * 2;   // any contents: the buffer is read as tile-major weights
         DeviceBuf w(wbytes * copies), x(static_cast<size_t>(M) * K * 2), y(static_cast<size_t>(M) * N * 2);
         DeviceBuf ws(linear_workspace_bytes(mt, limit));
         const size_t tiles = static_cast<size_t>(ceil_div(N, 128)) * ceil_div(M, mt);

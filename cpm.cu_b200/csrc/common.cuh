@@ -200,6 +200,19 @@ struct LinearPlan {
     const void* wq = nullptr;
 };
 
+// Weight layout of the bf16 GEMMs ("tile-major"): W [N, K] is stored as ceil(N / 128) x (K / 64) blocks of 128 rows x
+// 64 elements, each block 16 KB of consecutive memory, blocks of a 128-row tile consecutive along K.  The kernels
+// fetch one block per TMA copy; from a row-major W the same copy gathers 128 segments of 128 B that lie K * 2 bytes
+// apart, one DRAM page each, and the GEMMs of the step ran at 5.4-6.3 TB/s instead of 6.5-8 TB/s.  Rows beyond N are
+// zero.  With `mode` 1 / 2 the source rows are the gate / up projection of a SwiGLU pair and go to rows 0-63 / 64-127 of
+// the tile of their 64-feature group, so one tile holds both projections of the same features.
+size_t linear_weight_elems(int N, int K);
+// src: `rows` x `src_cols` row-major bf16, device OR host memory; they become rows [row_offset, row_offset + rows) (or
+// the gate / up slots) and columns [k_offset, k_offset + src_cols) of the tile-major matrix `dst` with K columns.
+void retile_weight_rows(const void* src, int rows, int src_cols, bf16* dst, int K, int mode, int row_offset, int k_offset,
+                        cudaStream_t s);
+// dst row i = src row idx[i], both tile-major with K columns (FR-Spec draft head).
+void gather_retiled_rows(const bf16* src, const int32_t* idx, int rows, bf16* dst, int K, cudaStream_t s);
 size_t linear_workspace_bytes(int mt, int grid);
 int linear_pick_mt(int M);
 LinearPlan make_linear_plan(const bf16* x, int x_rows, const bf16* w, int M, int N, int K, bf16* y, int ldy,
@@ -246,7 +259,9 @@ void launch_embedding_gather(const int32_t* ids, const bf16* table, bf16* out, i
 void launch_rope_append(bf16* qkv, int rows, int hq, int hkv, int d, const float* inv_freq, const int32_t* pos,
                         const int32_t* pos_base, int pos_off, int pos_step, bf16* k_cache, bf16* v_cache,
                         const int32_t* kv_len, int kv_off, const int32_t* n_valid, int cache_rows, cudaStream_t s);
-void launch_silu_gate(const bf16* gate_up, bf16* out, int rows, int inter, cudaStream_t s);
+// interleaved: gate_up is [rows, 2 * inter] with gate / up of features 64 t .. 64 t + 63 in columns 128 t .. 128 t + 63 /
+// 128 t + 64 .. 128 t + 127 (the output of a GEMM over SwiGLU-interleaved weight tiles) instead of [gate | up] halves
+void launch_silu_gate(const bf16* gate_up, bf16* out, int rows, int inter, cudaStream_t s, bool interleaved = false);
 void launch_add_scaled(bf16* x, const bf16* a, const bf16* b, float scale_b, int rows, int dim,
                        cudaStream_t s);  // x = a + b*scale
 void launch_scale(bf16* out, const bf16* in, float scale, size_t n, cudaStream_t s);

@@ -207,14 +207,17 @@ __global__ void rope_append_kernel(bf16* __restrict__ qkv, int hq, int hkv, int 
     }
 }
 
-__global__ void silu_gate_kernel(const bf16* __restrict__ gate_up, bf16* __restrict__ out, int inter) {
+__global__ void silu_gate_kernel(const bf16* __restrict__ gate_up, bf16* __restrict__ out, int inter, int interleaved) {
     grid_dependency_sync();
     const int r = blockIdx.y;
     const int c = (blockIdx.x * blockDim.x + threadIdx.x) * 8;
     if (c >= inter) return;
     const bf16* g = gate_up + static_cast<size_t>(r) * 2 * inter;
-    const uint4 gv = *reinterpret_cast<const uint4*>(g + c);
-    const uint4 uv = *reinterpret_cast<const uint4*>(g + inter + c);
+    // [gate | up] halves, or per 64 features 64 gate columns followed by their 64 up columns
+    const int gc = interleaved ? (c / 64) * 128 + (c % 64) : c;
+    const int uc = interleaved ? gc + 64 : inter + c;
+    const uint4 gv = *reinterpret_cast<const uint4*>(g + gc);
+    const uint4 uv = *reinterpret_cast<const uint4*>(g + uc);
     const bf16* ge = reinterpret_cast<const bf16*>(&gv);
     const bf16* ue = reinterpret_cast<const bf16*>(&uv);
     uint4 ov;
@@ -439,11 +442,89 @@ void launch_rope_append(bf16* qkv, int rows, int hq, int hkv, int d, const float
                   pos_step, k_cache, v_cache, kv_len, kv_off, n_valid, cache_rows, runtime().d_error);
 }
 
-void launch_silu_gate(const bf16* gate_up, bf16* out, int rows, int inter, cudaStream_t s) {
+void launch_silu_gate(const bf16* gate_up, bf16* out, int rows, int inter, cudaStream_t s, bool interleaved) {
     if (rows <= 0) return;
     CPM_REQUIRE(inter % 8 == 0, "silu_gate: width must be a multiple of 8");
+    CPM_REQUIRE(!interleaved || inter % 64 == 0, "silu_gate: interleaved columns come in groups of 64");
     dim3 grid(ceil_div(inter / 8, 256), rows);
-    launch_kernel(silu_gate_kernel, grid, dim3(256), 0, s, gate_up, out, inter);
+    launch_kernel(silu_gate_kernel, grid, dim3(256), 0, s, gate_up, out, inter, interleaved ? 1 : 0);
+}
+
+// ---------------------------------------------------------------- tile-major GEMM weights
+namespace {
+
+// element offset of (row, k) in a tile-major matrix with K columns
+__device__ __forceinline__ size_t tile_major_offset(int row, int k, int K) {
+    const size_t block = static_cast<size_t>(row >> 7) * (K >> 6) + (k >> 6);
+    return block * (128 * 64) + static_cast<size_t>(row & 127) * 64 + (k & 63);
+}
+
+__device__ __forceinline__ int retile_dst_row(int r, int mode, int row_offset) {
+    if (mode == 0) return row_offset + r;
+    return (r >> 6) * 128 + (mode == 2 ? 64 : 0) + (r & 63);   // gate / up slot of the 64-feature group
+}
+
+// one thread per 8 elements (16 bytes) of the source; src holds rows [first_row, first_row + rows) of the matrix
+__global__ void retile_rows_kernel(const bf16* __restrict__ src, int first_row, int rows, int src_cols,
+                                   bf16* __restrict__ dst, int K, int mode, int row_offset, int k_offset) {
+    const size_t idx = static_cast<size_t>(blockIdx.x) * blockDim.x + threadIdx.x;
+    const int per_row = src_cols / 8;
+    if (idx >= static_cast<size_t>(rows) * per_row) return;
+    const int r = static_cast<int>(idx / per_row), c8 = static_cast<int>(idx - static_cast<size_t>(r) * per_row);
+    const uint4 v = *reinterpret_cast<const uint4*>(src + static_cast<size_t>(r) * src_cols + c8 * 8);
+    *reinterpret_cast<uint4*>(dst + tile_major_offset(retile_dst_row(first_row + r, mode, row_offset), k_offset + c8 * 8, K)) = v;
+}
+
+__global__ void gather_retiled_kernel(const bf16* __restrict__ src, const int32_t* __restrict__ idx, bf16* __restrict__ dst,
+                                      int K) {
+    const int d = blockIdx.x, s = idx[d];
+    for (int k = threadIdx.x * 8; k < K; k += blockDim.x * 8) {
+        *reinterpret_cast<uint4*>(dst + tile_major_offset(d, k, K)) = *reinterpret_cast<const uint4*>(src + tile_major_offset(s, k, K));
+    }
+}
+
+}  // namespace
+
+size_t linear_weight_elems(int N, int K) { return static_cast<size_t>(ceil_div(N, 128)) * 128 * K; }
+
+void retile_weight_rows(const void* src, int rows, int src_cols, bf16* dst, int K, int mode, int row_offset, int k_offset,
+                        cudaStream_t s) {
+    if (rows <= 0) return;
+    CPM_REQUIRE(src_cols % 8 == 0 && K % 64 == 0 && k_offset % 8 == 0 && k_offset + src_cols <= K, "retile: bad column range");
+    CPM_REQUIRE(mode >= 0 && mode <= 2 && (mode == 0 || row_offset == 0), "retile: bad row mapping");
+    cudaPointerAttributes attr = {};
+    const bool on_device = cudaPointerGetAttributes(&attr, src) == cudaSuccess &&
+                           (attr.type == cudaMemoryTypeDevice || attr.type == cudaMemoryTypeManaged);
+    cudaGetLastError();  // an unregistered host pointer is not an error here
+    auto run = [&](const bf16* rows_on_device, int first_row, int n) {
+        const size_t threads = static_cast<size_t>(n) * (src_cols / 8);
+        retile_rows_kernel<<<static_cast<unsigned>((threads + 255) / 256), 256, 0, s>>>(rows_on_device, first_row, n, src_cols, dst,
+                                                                                      K, mode, row_offset, k_offset);
+        CUDA_CHECK(cudaGetLastError());
+    };
+    if (on_device) {
+        run(static_cast<const bf16*>(src), 0, rows);
+        return;
+    }
+    // host memory: through a staging buffer, a slab of rows at a time
+    const size_t row_bytes = static_cast<size_t>(src_cols) * 2;
+    const int slab = static_cast<int>(std::max<size_t>(1, (static_cast<size_t>(64) << 20) / row_bytes));
+    bf16* stage = nullptr;
+    CUDA_CHECK(cudaMalloc(&stage, static_cast<size_t>(std::min(slab, rows)) * row_bytes));
+    for (int r0 = 0; r0 < rows; r0 += slab) {
+        const int n = std::min(slab, rows - r0);
+        CUDA_CHECK(cudaMemcpyAsync(stage, static_cast<const uint8_t*>(src) + static_cast<size_t>(r0) * row_bytes,
+                                   static_cast<size_t>(n) * row_bytes, cudaMemcpyHostToDevice, s));
+        run(stage, r0, n);
+        CUDA_CHECK(cudaStreamSynchronize(s));   // the staging buffer is reused
+    }
+    cudaFree(stage);
+}
+
+void gather_retiled_rows(const bf16* src, const int32_t* idx, int rows, bf16* dst, int K, cudaStream_t s) {
+    if (rows <= 0) return;
+    gather_retiled_kernel<<<rows, 128, 0, s>>>(src, idx, dst, K);
+    CUDA_CHECK(cudaGetLastError());
 }
 
 void launch_add_scaled(bf16* x, const bf16* a, const bf16* b, float scale_b, int rows, int dim, cudaStream_t s) {

@@ -40,14 +40,6 @@ __global__ void publish_kernel(const int32_t* result, const int32_t* tokens, con
     if (threadIdx.x < 16) out[1 + threadIdx.x] = (threadIdx.x < n) ? tokens[threadIdx.x] : -1;
 }
 
-__global__ void gather_rows_kernel(const bf16* __restrict__ src, const int32_t* __restrict__ idx, bf16* __restrict__ dst,
-                                   int dim) {
-    const size_t s = static_cast<size_t>(idx[blockIdx.x]) * dim, d = static_cast<size_t>(blockIdx.x) * dim;
-    for (int i = threadIdx.x * 8; i < dim; i += blockDim.x * 8) {
-        *reinterpret_cast<uint4*>(dst + d + i) = *reinterpret_cast<const uint4*>(src + s + i);
-    }
-}
-
 // The engine's split-K counters (two per output tile) live in one buffer of kTicketInts ints.
 constexpr int kTicketInts = 1 << 16;
 LinearPlan checked(const LinearPlan& p) {
@@ -141,7 +133,7 @@ void Engine::lay_out(Pool& p) {
     const size_t R = max_rows_;
     // weights
     embed_ = take<bf16>(p, static_cast<size_t>(V) * H);
-    lm_head_ = take<bf16>(p, static_cast<size_t>(V) * H);
+    lm_head_ = take<bf16>(p, linear_weight_elems(V, H));   // GEMM weights are tile-major, rows padded to 128
     final_norm_ = take<bf16>(p, H);
     inv_freq_ = take<float>(p, d / 2);
     for (auto& w : layers_) {
@@ -151,10 +143,10 @@ void Engine::lay_out(Pool& p) {
             w.gate_up_q = take<uint8_t>(p, linear_w4_weight_bytes(2 * I, H));
             w.down_q = take<uint8_t>(p, linear_w4_weight_bytes(H, I));
         } else {
-            w.qkv = take<bf16>(p, static_cast<size_t>(qkv_dim_) * H);
-            w.o = take<bf16>(p, static_cast<size_t>(H) * mc_.hq * d);
-            w.gate_up = take<bf16>(p, static_cast<size_t>(2) * I * H);
-            w.down = take<bf16>(p, static_cast<size_t>(H) * I);
+            w.qkv = take<bf16>(p, linear_weight_elems(qkv_dim_, H));
+            w.o = take<bf16>(p, linear_weight_elems(H, mc_.hq * d));
+            w.gate_up = take<bf16>(p, gate_up_elems());
+            w.down = take<bf16>(p, linear_weight_elems(H, I));
         }
         w.ln_attn = take<bf16>(p, H);
         w.ln_ffn = take<bf16>(p, H);
@@ -171,16 +163,16 @@ void Engine::lay_out(Pool& p) {
             elayer_.gate_up_q = take<uint8_t>(p, linear_w4_weight_bytes(2 * I, H));
             elayer_.down_q = take<uint8_t>(p, linear_w4_weight_bytes(H, I));
         } else {
-            fc_ = take<bf16>(p, static_cast<size_t>(H) * 2 * H);
-            elayer_.qkv = take<bf16>(p, static_cast<size_t>(qkv_dim_) * H);
-            elayer_.o = take<bf16>(p, static_cast<size_t>(H) * mc_.hq * d);
-            elayer_.gate_up = take<bf16>(p, static_cast<size_t>(2) * I * H);
-            elayer_.down = take<bf16>(p, static_cast<size_t>(H) * I);
+            fc_ = take<bf16>(p, linear_weight_elems(H, 2 * H));
+            elayer_.qkv = take<bf16>(p, linear_weight_elems(qkv_dim_, H));
+            elayer_.o = take<bf16>(p, linear_weight_elems(H, mc_.hq * d));
+            elayer_.gate_up = take<bf16>(p, gate_up_elems());
+            elayer_.down = take<bf16>(p, linear_weight_elems(H, I));
         }
         elayer_.ln_attn = take<bf16>(p, H);
         elayer_.ln_ffn = take<bf16>(p, H);
         token_id_remap_ = take<int32_t>(p, draft_vocab_);
-        bf16* dl = (draft_vocab_ != V) ? take<bf16>(p, static_cast<size_t>(draft_vocab_) * H) : lm_head_;
+        bf16* dl = (draft_vocab_ != V) ? take<bf16>(p, linear_weight_elems(draft_vocab_, H)) : lm_head_;
         draft_lm_head_ = dl;
     }
     // activations
@@ -358,15 +350,22 @@ void Engine::load(const std::string& name, const void* src) {
         else throw std::invalid_argument("Unsupported quantized tensor " + sub);
         return true;
     };
+    // a GEMM weight (or the rows / columns one checkpoint tensor contributes to a fused one) into the tile-major layout
+    auto retile = [&](bf16* dst, int rows, int src_cols, int K, int mode, int row_offset, int k_offset) {
+        retile_weight_rows(src, rows, src_cols, dst, K, mode, row_offset, k_offset, rt.stream);
+        CUDA_CHECK(cudaStreamSynchronize(rt.stream));
+    };
     auto load_layer = [&](LayerWeights& w, const std::string& sub) {
-        const size_t qn = static_cast<size_t>(mc_.hq) * d * H, kn = static_cast<size_t>(mc_.hkv) * d * H;
-        if (sub.find("q_proj") != std::string::npos) copy(w.qkv, qn * 2);
-        else if (sub.find("k_proj") != std::string::npos) copy(w.qkv + qn, kn * 2);
-        else if (sub.find("v_proj") != std::string::npos) copy(w.qkv + qn + kn, kn * 2);
-        else if (sub.find("o_proj") != std::string::npos) copy(w.o, static_cast<size_t>(H) * mc_.hq * d * 2);
-        else if (sub.find("gate_proj") != std::string::npos) copy(w.gate_up, static_cast<size_t>(I) * H * 2);
-        else if (sub.find("up_proj") != std::string::npos) copy(w.gate_up + static_cast<size_t>(I) * H, static_cast<size_t>(I) * H * 2);
-        else if (sub.find("down_proj") != std::string::npos) copy(w.down, static_cast<size_t>(H) * I * 2);
+        const int qr = mc_.hq * d, kr = mc_.hkv * d;
+        // gate and up rows share the tiles of their 64-feature groups (SwiGLU epilogue) when the width allows
+        const bool il = gate_up_interleaved();
+        if (sub.find("q_proj") != std::string::npos) retile(w.qkv, qr, H, H, 0, 0, 0);
+        else if (sub.find("k_proj") != std::string::npos) retile(w.qkv, kr, H, H, 0, qr, 0);
+        else if (sub.find("v_proj") != std::string::npos) retile(w.qkv, kr, H, H, 0, qr + kr, 0);
+        else if (sub.find("o_proj") != std::string::npos) retile(w.o, H, mc_.hq * d, mc_.hq * d, 0, 0, 0);
+        else if (sub.find("gate_proj") != std::string::npos) retile(w.gate_up, I, H, H, il ? 1 : 0, 0, 0);
+        else if (sub.find("up_proj") != std::string::npos) retile(w.gate_up, I, H, H, il ? 2 : 0, il ? 0 : I, 0);
+        else if (sub.find("down_proj") != std::string::npos) retile(w.down, H, I, I, 0, 0, 0);
         else if (sub.find("input_layernorm") != std::string::npos) copy(w.ln_attn, static_cast<size_t>(H) * 2);
         else if (sub.find("post_attention_layernorm") != std::string::npos) copy(w.ln_ffn, static_cast<size_t>(H) * 2);
         else throw std::invalid_argument("Unsupported name " + sub);
@@ -383,17 +382,13 @@ void Engine::load(const std::string& name, const void* src) {
             load_quantized(second ? "E.fc2" : "E.fc1", is_scales, src, H, H, second ? fc2_q_ : fc1_q_);
         } else if (name.rfind("eagle.fc1", 0) == 0) {
             if (name.find("weight") != std::string::npos) {
-                CUDA_CHECK(cudaMemcpy2DAsync(fc_, static_cast<size_t>(2) * H * 2, src, static_cast<size_t>(H) * 2,
-                                             static_cast<size_t>(H) * 2, H, cudaMemcpyDefault, rt.stream));
-                CUDA_CHECK(cudaStreamSynchronize(rt.stream));
+                retile(fc_, H, H, 2 * H, 0, 0, 0);   // columns [0, H) of the fused [H, 2H] matrix
             } else if (name.find("bias") != std::string::npos) {
                 copy(fc_bias_, static_cast<size_t>(H) * 2);
             } else throw std::invalid_argument("Unsupported name " + name);
         } else if (name.rfind("eagle.fc2", 0) == 0) {
             CPM_REQUIRE(name.find("weight") != std::string::npos, "Unsupported name " + name);
-            CUDA_CHECK(cudaMemcpy2DAsync(fc_ + H, static_cast<size_t>(2) * H * 2, src, static_cast<size_t>(H) * 2,
-                                         static_cast<size_t>(H) * 2, H, cudaMemcpyDefault, rt.stream));
-            CUDA_CHECK(cudaStreamSynchronize(rt.stream));
+            retile(fc_, H, H, 2 * H, 0, 0, H);       // columns [H, 2H)
         } else if (name.rfind("eagle.token_id_remap", 0) == 0) {
             copy(token_id_remap_, static_cast<size_t>(draft_vocab_) * 4);
             remap_loaded_ = true;
@@ -419,13 +414,12 @@ void Engine::load(const std::string& name, const void* src) {
     } else if (name.rfind("model.norm", 0) == 0) {
         copy(final_norm_, static_cast<size_t>(H) * 2);
     } else if (name.rfind("lm_head", 0) == 0) {
-        copy(lm_head_, static_cast<size_t>(mc_.vocab) * H * 2);
+        retile(lm_head_, mc_.vocab, H, H, 0, 0, 0);
         if (has_eagle_ && draft_vocab_ != mc_.vocab) {
             // FR-Spec: the draft head is the rows of the full head picked by token_id_remap,
             // which therefore has to be loaded first (reference minicpm4_eagle.cuh:215-218)
             CPM_REQUIRE(remap_loaded_, "eagle.token_id_remap must be loaded before lm_head");
-            gather_rows_kernel<<<draft_vocab_, 128, 0, rt.stream>>>(lm_head_, token_id_remap_, draft_lm_head_, H);
-            CUDA_CHECK(cudaGetLastError());
+            gather_retiled_rows(lm_head_, token_id_remap_, draft_vocab_, draft_lm_head_, H, rt.stream);
             CUDA_CHECK(cudaStreamSynchronize(rt.stream));
         }
     } else if (name.find("rotary_emb") != std::string::npos) {
@@ -474,7 +468,7 @@ void Engine::build_layer_plans(LayerPlans& lp, const LayerWeights& w, const KVLa
         // the activation is applied in the gate/up GEMM's epilogue and the two projections are never stored, whenever
         // the whole-tile schedule that needs fills the GPU
         static const bool unfused = tuning_env("CPMCU_NO_SWIGLU_FUSE") != nullptr;   // bench only
-        lp.gate_up = (!unfused && linear_swiglu_fits(rows, I, sms))
+        lp.gate_up = (!unfused && gate_up_interleaved() && linear_swiglu_fits(rows, I, sms))
                          ? make_linear_swiglu_plan(normed_, rows, w.gate_up, rows, I, H, act_, I, sms)
                          : checked(make_linear_plan(normed_, rows, w.gate_up, rows, 2 * I, H, gate_up_, 2 * I, nullptr, gemm_ws_, tickets_, sms));
         lp.down = checked(make_linear_plan(act_, rows, w.down, rows, H, I, delta_, H, nullptr, gemm_ws_, tickets_, sms));
@@ -546,7 +540,7 @@ void Engine::layer_forward(LayerPlans& lp, const LayerWeights& w, const KVLayer&
     launch_linear(lp.o, s);
     launch_add_rms_norm(x, delta_, res_scale, w.ln_ffn, normed_, rows, H, mc_.eps, s);
     launch_linear(lp.gate_up, s);
-    if (!lp.gate_up.swiglu) launch_silu_gate(gate_up_, act_, rows, mc_.inter, s);
+    if (!lp.gate_up.swiglu) launch_silu_gate(gate_up_, act_, rows, mc_.inter, s, w.gate_up != nullptr && gate_up_interleaved());
     launch_linear(lp.down, s);
 }
 
@@ -758,7 +752,7 @@ void Engine::draft_catchup(cudaStream_t s) {
         launch_linear(lp.o, s);
         launch_add_rms_norm(e_x_, delta_, ec_.residual_scale, w.ln_ffn, normed_, rc, H, mc_.eps, s);
         launch_linear(lp.gate_up, s);
-        if (!lp.gate_up.swiglu) launch_silu_gate(gate_up_, act_, rc, mc_.inter, s);
+        if (!lp.gate_up.swiglu) launch_silu_gate(gate_up_, act_, rc, mc_.inter, s, w.gate_up != nullptr && gate_up_interleaved());
         launch_linear(lp.down, s);
         launch_add_scaled(e_h_, e_x_, delta_, ec_.residual_scale, rc, H, s);
     }

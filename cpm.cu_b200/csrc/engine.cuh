@@ -159,6 +159,10 @@ private:
     void enqueue_step(bool first, cudaStream_t s);
     void check_errors(const char* where);
     int attn_splits_for(int rows) const;
+    // bf16 gate/up weights: gate and up rows of a 64-feature group share one 128-row tile when the width is a multiple
+    // of 64; otherwise [gate ; up] as in the checkpoint
+    bool gate_up_interleaved() const { return mc_.inter % 64 == 0; }
+    size_t gate_up_elems() const { return linear_weight_elems(2 * mc_.inter, mc_.hidden); }
 
     ModelConfig mc_;
     EagleConfig ec_;

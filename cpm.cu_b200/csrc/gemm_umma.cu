@@ -11,7 +11,9 @@
 // the accumulator in TMEM is Y^T: lane = output feature, column = token.  Both
 // operands are K-major and arrive through TMA with 128-byte swizzle into a
 // multi-stage shared-memory ring; one thread issues tcgen05.mma; four epilogue
-// warps read TMEM back with tcgen05.ld.
+// warps read TMEM back with tcgen05.ld.  W is held tile-major (one contiguous
+// 16 KB block per 128-row tile and 64-column k-block, see linear_weight_elems),
+// so a weight fetch is one sequential burst instead of 128 strided segments.
 //
 // Scheduling.  The (tile, k-block) work units are laid out in one line and cut
 // into gridDim.x equal pieces (stream-K), so every SM streams the same number
@@ -109,11 +111,10 @@ linear_umma_kernel(const __grid_constant__ CUtensorMap tm_w, const __grid_consta
             uint32_t phase = 0;
             int tile, kb0, kb1;
             bool ok = true;
-            // one 128-row weight tile: rows n_tile * 128 ..., or (SwiGLU) 64 gate rows then the 64 up rows of the same
-            // features through a 3-D map over [2][features][K]
+            // one k-block of a 128-row weight tile: one contiguous 16 KB block of the tile-major weights (for a SwiGLU
+            // launch the tile holds 64 gate rows and the 64 up rows of the same features)
             auto load_w = [&](uint8_t* dst, uint64_t* bar, int kb, int n_tile) {
-                if (a.swiglu != 0) ptx::tma_load_3d(dst, &tm_w, bar, kb * BLOCK_K, n_tile * 64, 0);
-                else ptx::tma_load_2d(dst, &tm_w, bar, kb * BLOCK_K, n_tile * BLOCK_N);
+                ptx::tma_load_2d(dst, &tm_w, bar, 0, (n_tile * a.kblocks + kb) * BLOCK_N);
             };
             // ---- phase 1: W tiles of the first STAGES k-blocks, before the dependency wait
             int pre = 0;
@@ -292,7 +293,7 @@ linear_umma_cluster_kernel(const __grid_constant__ CUtensorMap tm_w, const __gri
             const int pre = (kpc < C::STAGES) ? kpc : C::STAGES;
             for (int i = 0; i < pre; ++i) {
                 ptx::mbar_arrive_expect_tx(&full[i], C::STAGE_BYTES);
-                ptx::tma_load_2d(tiles + i * C::STAGE_BYTES, &tm_w, &full[i], (kb_begin + i) * BLOCK_K, n_tile * BLOCK_N);
+                ptx::tma_load_2d(tiles + i * C::STAGE_BYTES, &tm_w, &full[i], 0, (n_tile * a.kblocks + kb_begin + i) * BLOCK_N);
             }
             grid_dep_wait();
             int stage = 0;
@@ -306,7 +307,7 @@ linear_umma_cluster_kernel(const __grid_constant__ CUtensorMap tm_w, const __gri
                 } else {
                     if (!ptx::mbar_wait(&empty[stage], phase ^ 1, abort_flag)) { ok = false; break; }
                     ptx::mbar_arrive_expect_tx(&full[stage], C::STAGE_BYTES);
-                    ptx::tma_load_2d(dst, &tm_w, &full[stage], kb * BLOCK_K, n_tile * BLOCK_N);
+                    ptx::tma_load_2d(dst, &tm_w, &full[stage], 0, (n_tile * a.kblocks + kb) * BLOCK_N);
                     ptx::tma_load_2d(dst + W_TILE_BYTES, &tm_x, &full[stage], kb * BLOCK_K, 0);
                 }
                 if (++stage == C::STAGES) { stage = 0; phase ^= 1; }
@@ -476,6 +477,13 @@ static int pick_grid(int n_tiles, int kblocks, int m_valid, int limit) {
     return best_g;
 }
 
+// Tensor map of tile-major weights (linear_weight_elems): every (128-row tile, 64-column k-block) is one box of 128
+// consecutive 128-byte rows.
+static CUtensorMap make_weight_tmap(const bf16* w, int N, int K) {
+    return make_tmap_2d(w, BLOCK_K, static_cast<uint64_t>(ceil_div(N, BLOCK_N)) * (K / BLOCK_K) * BLOCK_N, BLOCK_K * 2, BLOCK_K,
+                        BLOCK_N);
+}
+
 // CTAs of a launch before the cluster and wave decisions: at least four k-blocks each.
 static long long base_grid(int n_tiles, int m_tiles, int kblocks, int M, int grid_limit) {
     const long long units = static_cast<long long>(n_tiles) * m_tiles * kblocks;
@@ -578,7 +586,7 @@ LinearPlan make_linear_plan(const bf16* x, int x_rows, const bf16* w, int M, int
                     cluster_capacity(p.mt <= 64 ? p.mt : 64, 3), cluster_capacity(p.mt <= 64 ? p.mt : 64, 4));
         }
     }
-    p.tm_w = make_tmap_2d(w, K, N, static_cast<uint64_t>(K) * 2, BLOCK_K, BLOCK_N);
+    p.tm_w = make_weight_tmap(w, N, K);
     p.tm_x = make_tmap_2d(x, K, x_rows, static_cast<uint64_t>(K) * 2, BLOCK_K, p.mt);
     return p;
 }
@@ -606,8 +614,9 @@ bool linear_swiglu_fits(int M, int inter, int grid_limit) {
     return static_cast<double>(tiles) >= 0.85 * static_cast<double>(waves) * grid_limit;
 }
 
-// act[M, inter] = silu(X Wg^T) * (X Wu^T) with w = [gate rows (inter) ; up rows (inter)], both projections rounded to
-// bf16 before the product like the unfused pair (GEMM, then silu_gate_kernel).  Whole tiles only, in waves.
+// act[M, inter] = silu(X Wg^T) * (X Wu^T); w holds the two projections as tile-major tiles of 64 gate rows + the 64 up
+// rows of the same features (retile_weight_rows modes 1 and 2); both projections are rounded to bf16 before the product
+// like the unfused pair (GEMM, then silu_gate_kernel).  Whole tiles only.
 LinearPlan make_linear_swiglu_plan(const bf16* x, int x_rows, const bf16* w, int M, int inter, int K, bf16* act, int ld,
                                    int grid_limit) {
     CPM_REQUIRE(M >= 1 && inter >= 64 && inter % 64 == 0, "linear: SwiGLU width must be a multiple of 64");
@@ -627,7 +636,7 @@ LinearPlan make_linear_swiglu_plan(const bf16* x, int x_rows, const bf16* w, int
     // rows per CTA instead of two scattered 64-row slabs per tile).
     p.wave_tiles = (m_tiles > 1) ? static_cast<int>(tiles) : 0;
     p.tail_grid = (m_tiles > 1) ? 1 : p.grid;
-    p.tm_w = make_tmap_3d(w, K, inter, 2, static_cast<uint64_t>(K) * 2, static_cast<uint64_t>(inter) * K * 2, BLOCK_K, 64, 2);
+    p.tm_w = make_weight_tmap(w, 2 * inter, K);
     p.tm_x = make_tmap_2d(x, K, x_rows, static_cast<uint64_t>(K) * 2, BLOCK_K, p.mt);
     return p;
 }
